@@ -1,0 +1,213 @@
+/*
+ * ypk.h - C ABI of the B200 persistent-kernel decode runtime.
+ *
+ * This is the boundary a host binding links against.  It replaces the
+ * three-function CPython launcher the reference JIT-compiles per model
+ * (python/yirage/persistent_kernel.py:16-94: init_func / launch_func /
+ * finalize_func) and the extern "C" entry points those forward to
+ * (include/yirage/persistent_kernel/persistent_kernel.cuh:1036
+ * init_persistent_kernel, :1253 launch_persistent_kernel, :1320
+ * finalize_persistent_kernel).  The reference entry points take a
+ * std::vector by value and keep one process-global RuntimeConfig; here every
+ * call takes plain pointers and sizes and works on an explicit handle.
+ *
+ * All functions return 0 on success or a negative ypk_error.  A message for
+ * the last failure on a handle is available from ypk_last_error().
+ * A handle is not thread-safe; several handles may coexist in a process.
+ * The caller owns every tensor it binds and must keep it alive and unmoved
+ * while the handle exists (same convention as the reference, which bakes the
+ * pointers into generated code, src/kernel/runtime.cc:763).  Buffers created
+ * with ypk_alloc_tensor / ypk_shuffle_tensor belong to the handle and are
+ * released by ypk_destroy (the reference leaks them, runtime.cc:778-790).
+ */
+#ifndef YPK_H_
+#define YPK_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define YPK_ABI_VERSION 1
+
+typedef struct ypk_handle ypk_handle;
+
+enum ypk_error {
+  YPK_OK = 0,
+  YPK_ERR_INVALID = -1,    /* bad argument / malformed graph            */
+  YPK_ERR_CUDA = -2,       /* a CUDA runtime call failed                 */
+  YPK_ERR_TIMEOUT = -3,    /* a bounded device-side wait ran out         */
+  YPK_ERR_STATE = -4,      /* call made in the wrong order               */
+  YPK_ERR_UNSUPPORTED = -5 /* shape or option outside what is built      */
+};
+
+/* Element types; numeric values follow the reference's task-graph JSON
+ * (include/yirage/type.h:84-119). */
+enum ypk_dtype {
+  YPK_F16 = 940,
+  YPK_BF16 = 941,
+  YPK_F32 = 942,
+  YPK_I32 = 955,
+  YPK_I64 = 965
+};
+
+/* Task kinds executed by the worker CTAs.  These are the fused forms of the
+ * reference's TaskType list (persistent_kernel/runtime_header.h:62-124). */
+enum ypk_task_type {
+  YPK_TASK_NOP = 0,
+  YPK_TASK_EMBED = 1,         /* embedding.cuh:42-70                      */
+  YPK_TASK_LINEAR = 2,        /* [rmsnorm+] x.W^T [+residual | silu*mul]  */
+  YPK_TASK_ATTENTION = 3,     /* paged GQA decode, RoPE, append, split-KV */
+  YPK_TASK_ARGMAX_PARTIAL = 4,
+  YPK_TASK_ARGMAX_REDUCE = 5,
+  YPK_TASK_RMSNORM = 6,       /* stand-alone norm (unfused graphs)        */
+  YPK_TASK_SILU_MUL = 7,      /* stand-alone silu(g)*u                    */
+  YPK_TASK_ALLREDUCE = 8,     /* push partial to peers + local reduce     */
+  YPK_TASK_LINEAR_KN = 9,     /* x.W with W stored [K,N] (graph surface)  */
+  YPK_TASK_LINEAR_UMMA = 10,  /* tcgen05/TMEM tile linear, batch > 8      */
+  YPK_TASK_ELEMENTWISE = 11,  /* silu / mul / add on the graph surface    */
+  YPK_TASK_TYPE_COUNT
+};
+
+/* ypk_task.flags */
+#define YPK_F_NORM 0x1u        /* LINEAR: fold RMSNorm(x)*norm_w in front  */
+#define YPK_F_RESIDUAL 0x2u    /* LINEAR: add residual[b, n]               */
+#define YPK_F_SILU_MUL 0x4u    /* LINEAR: rows come as 8 gate + 8 up       */
+#define YPK_F_F16 0x8u         /* operands are fp16 instead of bf16        */
+#define YPK_F_ROPE 0x10u       /* ATTENTION: rotate new q/k                */
+#define YPK_F_NORM_NOWEIGHT 0x40u /* LINEAR: RMSNorm without a weight      */
+
+#define YPK_TASK_NPTR 8
+#define YPK_TASK_NINT 16
+#define YPK_TASK_NFLT 4
+
+/* A pointer operand of a task, as passed to ypk_load_graph: tensor slot + 1 in
+ * the top 16 bits, byte offset in the low 48.  0 means "no tensor". */
+#define YPK_REF(slot, byte_off) \
+  ((((uint64_t)(slot) + 1u) << 48) | ((uint64_t)(byte_off) & 0xFFFFFFFFFFFFull))
+
+/* One unit of work for a worker CTA.  Mirrors the role of TaskDesc
+ * (persistent_kernel/runtime_header.h:136-269) with run-time shapes instead
+ * of template arguments.  176 bytes, 16-byte aligned.
+ *
+ * LINEAR:  ptr = {x, W, out, norm_w, residual}
+ *          iarg = {K, row0, nrows, ldx, ldw, ldout, ldres, out_col0}
+ *          farg = {eps}
+ * EMBED:   ptr = {ids(int64), table, out}; iarg = {hidden, col0, ncols,
+ *                  ldtable, ldout}
+ * ATTENTION: ptr = {qkv, k_cache, v_cache, out, cos, sin, scratch, counters}
+ *          iarg = {request, kv_head, split, nsplit, q_per_kv, num_kv_heads,
+ *                  ld_qkv, ld_out, max_rows}
+ * ARGMAX_PARTIAL: ptr = {logits, part_val, part_idx}; iarg = {col0, ncols,
+ *                  ldlogits, part, nparts}
+ * ARGMAX_REDUCE: ptr = {part_val, part_idx, out(int64)}; iarg = {nparts}
+ * RMSNORM: ptr = {x, w, out}; iarg = {K, row0, nrows, ldx, ldout}; farg = {eps}
+ * SILU_MUL: ptr = {in, out}; iarg = {col0, ncols, group, ldin, ldout}
+ * The number of batch rows is the active-token count of the iteration (mode 1) or the
+ * `batch` argument of ypk_launch (mode 0).
+ */
+typedef struct ypk_task {
+  int32_t type;
+  uint32_t flags;
+  int32_t dep_event;   /* -1: none.  Run when counter[dep] >= dep_count*iter */
+  int32_t dep_count;
+  int32_t trig_event;  /* -1: none.  counter[trig] += 1 when done           */
+  int32_t op_id;       /* index of the graph operator this task came from   */
+  uint64_t ptr[YPK_TASK_NPTR];
+  int32_t iarg[YPK_TASK_NINT];
+  float farg[YPK_TASK_NFLT];
+  int32_t reserved[2];
+} ypk_task;
+
+/* Serving parameters; the meta pointers are the ten caller-owned tensors the
+ * reference passes to init_func (persistent_kernel.py:1291-1316), same order. */
+typedef struct ypk_config {
+  int32_t abi_version;        /* YPK_ABI_VERSION                           */
+  int32_t device;             /* CUDA ordinal                              */
+  int32_t world_size, rank;   /* tensor-parallel group                     */
+  int32_t num_workers;        /* worker CTAs; 0 = one per SM               */
+  int32_t mode;               /* 0: one pass per launch (operator graphs)
+                                 1: offline serving, batching on device    */
+  int32_t max_seq_length;
+  int32_t max_num_batched_requests;
+  int32_t max_num_batched_tokens;
+  int32_t max_num_pages;
+  int32_t page_size;
+  int32_t total_num_requests;
+  int64_t eos_token_id;
+  uint64_t wait_budget_ns;    /* bound of every device-side wait; 0 = 2 s  */
+  void *step;                 /* int32 [total_num_requests]                */
+  void *tokens;               /* int64 [total_num_requests, max_seq_length]*/
+  void *input_tokens;         /* int64 [max_num_batched_tokens]            */
+  void *output_tokens;        /* int64 [max_num_batched_tokens]            */
+  void *num_new_tokens;       /* int32 [total_num_requests]                */
+  void *prompt_lengths;       /* int32 [total_num_requests]                */
+  void *qo_indptr;            /* int32 [max_num_batched_requests + 1]      */
+  void *paged_kv_indptr;      /* int32 [max_num_batched_requests + 1]      */
+  void *paged_kv_indices;     /* int32 [max_num_pages]                     */
+  void *paged_kv_last_page_len; /* int32 [max_num_batched_requests]        */
+  void *profiler_buffer;      /* optional uint64 ring, may be NULL         */
+  uint64_t profiler_bytes;
+} ypk_config;
+
+typedef struct ypk_status {
+  int32_t error;          /* 0 or a ypk_error raised on the device          */
+  int32_t fail_worker;    /* CTA that gave up                               */
+  int32_t fail_task;      /* task index it was on (-1 if none)              */
+  int32_t fail_event;     /* event it waited for (-1 if none)               */
+  int64_t iterations;     /* iterations completed since create/reset        */
+  int32_t finished;       /* 1 when every request has retired               */
+  int32_t active_tokens;  /* tokens in the batch that is pending            */
+  int64_t tasks_executed; /* worker-side task executions, last launch       */
+} ypk_status;
+
+/* Library / build information. */
+int ypk_abi_version(void);
+const char *ypk_last_error(const ypk_handle *h);
+
+/* Lifetime (init_persistent_kernel / finalize_persistent_kernel). */
+int ypk_create(const ypk_config *cfg, ypk_handle **out);
+int ypk_destroy(ypk_handle *h);
+
+/* Tensor registry: IODesc TorchTensor / CUDAMallocTensor / ShuffledTorchTensor
+ * (src/kernel/graph.cc:338-437). */
+int ypk_bind_tensor(ypk_handle *h, int32_t slot, const char *name, void *dev_ptr,
+                    uint64_t bytes);
+int ypk_alloc_tensor(ypk_handle *h, int32_t slot, const char *name, uint64_t bytes);
+/* dst = row-interleave of n_src row-major matrices with the same row length:
+ * the destination is a sequence of blocks, block g holding rows
+ * [g*gran[i], (g+1)*gran[i]) of source i for i = 0..n_src-1
+ * (materialisation of shuffle_tensors, src/kernel/runtime.cc:804-842). */
+int ypk_shuffle_tensor(ypk_handle *h, int32_t dst_slot, const char *name, int32_t n_src,
+                       const int32_t *src_slots, const int32_t *rows, const int32_t *gran,
+                       uint64_t row_bytes);
+int ypk_tensor_ptr(ypk_handle *h, int32_t slot, void **dev_ptr, uint64_t *bytes);
+
+/* Task graph: tasks in execution order, events as (trigger count) per event,
+ * and the per-worker queues: worker w runs tasks
+ * queue[queue_off[w] .. queue_off[w+1]) in that order every iteration. */
+int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks,
+                   int32_t num_events, const int32_t *queue, const int32_t *queue_off,
+                   int32_t num_queues);
+
+/* init_kernel (persistent_kernel.cuh:107-132): zero step[], request slots,
+ * refill the free-page queue. */
+int ypk_reset(ypk_handle *h);
+
+/* launch_persistent_kernel: run the megakernel on `stream` (a cudaStream_t,
+ * may be NULL for the default stream).  mode 1 runs until every request has
+ * retired or max_iterations (>0) iterations have completed, whichever comes
+ * first; mode 0 runs the graph once for `batch` rows.  Returns after the
+ * kernel has finished (the reference call is synchronous too). */
+int ypk_launch(ypk_handle *h, void *stream, int32_t max_iterations, int32_t batch);
+/* Same, but returns right after enqueueing; pair with ypk_wait. */
+int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_t batch);
+int ypk_wait(ypk_handle *h);
+
+int ypk_get_status(ypk_handle *h, ypk_status *out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* YPK_H_ */

@@ -1,0 +1,333 @@
+// Device-side plumbing shared by every task of the persistent megakernel:
+// the run-time descriptor handed to the kernel, shared-memory map, mbarrier /
+// bulk-copy (TMA engine) wrappers, acquire/release helpers and bounded waits.
+//
+// Structure of one worker CTA (one per SM, 288 threads):
+//   warps 0..7  consumers: wait for the task's dependency event, stage the
+//               activations, do the arithmetic, publish the trigger event;
+//   warp  8     producer: walks the same per-worker task queue on its own and
+//               streams the bytes that do not depend on activations (weight
+//               rows, cached K/V tiles) into a 4-stage shared-memory ring with
+//               cp.async.bulk + mbarrier, so HBM stays busy while the consumers
+//               sit on an event.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include "../../include/ypk.h"
+
+namespace ypk {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kBlockThreads = kConsumerThreads + 32;  // + producer warp
+constexpr int kProducerWarp = kConsumerWarps;
+
+constexpr int kStages = 4;
+constexpr int kStageBytes = 34816;               // 34 KB
+constexpr int kStageCols = 512;                  // weight columns per ring stage
+constexpr int kRowPitch = kStageCols * 2 + 16;   // 1040 B: odd multiple of 16 -> no bank conflicts
+constexpr int kRowBlock = 32;                    // weight rows per ring stage (one per lane)
+constexpr int kMaxBatch = 8;                     // tokens handled per pass of the GEMV
+constexpr int kMaxAccRows = 256;                 // rows of one LINEAR task when K is chunked
+
+constexpr int kKvTile = 64;                      // cached tokens per ring stage
+constexpr int kHeadDim = 128;
+constexpr int kKPitch = kHeadDim * 2 + 16;       // 272 B per K row in shared memory
+constexpr int kVOffset = kKvTile * kKPitch;      // V tile follows the K tile
+constexpr int kMaxNewTokens = 8;                 // new tokens of one request per iteration
+
+// Shared-memory map (dynamic shared memory, bytes).
+constexpr int kOffRing = 0;
+constexpr int kOffXs = kOffRing + kStages * kStageBytes;   // 139264
+constexpr int kXsBytes = 65536;
+constexpr int kOffPart = kOffXs + kXsBytes;                // 204800
+constexpr int kPartBytes = 2 * kConsumerWarps * kRowBlock * kMaxBatch * 4;  // 16384
+constexpr int kOffAcc = kOffPart + kPartBytes;             // 221184
+constexpr int kAccBytes = kMaxAccRows * kMaxBatch * 4;     // 8192
+constexpr int kOffMisc = kOffAcc + kAccBytes;              // 229376
+constexpr int kMiscBytes = 1024;
+constexpr int kSmemBytes = kOffMisc + kMiscBytes;          // 230400 <= 232448
+constexpr int kScratchSmemBytes = kXsBytes + kPartBytes + kAccBytes;  // 90112, contiguous from kOffXs
+
+// Layout of the misc area.
+struct __align__(16) Misc {
+  unsigned long long full_bar[kStages];
+  unsigned long long empty_bar[kStages];
+  float rnorm[kMaxBatch];
+  unsigned long long ctrl_word;  // broadcast of the published control word
+  int flag;                      // generic broadcast slot for the consumers
+  int abort_flag;                // set when this CTA has seen an abort
+  ypk_task ctask;                // consumer copy of the current task
+  ypk_task ptask;                // producer copy of the current task
+};
+static_assert(sizeof(Misc) <= kMiscBytes, "misc area too small");
+static_assert(sizeof(ypk_task) == 176, "ypk_task layout changed");
+
+// Control block in global memory (unsigned long long words).
+enum CtrlWord {
+  kCtrlPublished = 0,  // iteration << 32 | state << 16 | active tokens
+  kCtrlAbort = 1,      // 0 or error code
+  kCtrlFailInfo = 2,   // worker << 40 | (task & 0xfffff) << 20 | (event & 0xfffff)
+  kCtrlTasksDone = 3,
+  kCtrlFinished = 4,
+  kCtrlWords = 8
+};
+constexpr unsigned kStateRun = 0, kStateStop = 1;
+
+struct Runtime {
+  const ypk_task *tasks;
+  const int *queue;
+  const int *queue_off;
+  unsigned long long *events;
+  unsigned long long *ctrl;
+  // continuous batching state (caller-owned meta tensors + library-owned slots)
+  int *step;
+  long long *tokens;
+  long long *input_tokens;
+  long long *output_tokens;
+  int *prompt_len;
+  int *qo_indptr;
+  int *kv_indptr;
+  int *kv_indices;
+  int *kv_last_len;
+  int *request_ids;   // [max_req]
+  int *page_queue;    // [max_pages]
+  int *kv_tmp;        // [max_pages] scratch copy of kv_indices for the batcher
+  int *bstate;        // [0] next request id, [1] page queue head, [2] tail
+  long long eos;
+  long long base_iter;
+  unsigned long long budget_ns;
+  int mode, max_seq, max_req, max_tok, max_pages, page_size, total_req;
+  int max_iters, fixed_batch, resume_pending, rank, world;
+  int end_event, end_count;  // event every task of the last operator triggers
+};
+
+// ---------------------------------------------------------------- PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ unsigned long long globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long *p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long *p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_u64(unsigned long long *p, unsigned long long v) {
+  asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_add_u64(unsigned long long *p, unsigned long long v) {
+  asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Global -> shared bulk copy through the TMA engine; completion is counted in
+// bytes on `bar`.  dst, src 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes,
+                                         unsigned long long *bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void bulk_g2s_hint(void *dst, const void *src, uint32_t bytes,
+                                              unsigned long long *bar, unsigned long long policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1], %2, [%3], %4;" ::"r"(smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ unsigned long long policy_evict_first() {
+  unsigned long long p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void consumer_bar() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+}
+
+// Packed fp32x2 arithmetic (two FMAs per issue slot on sm_100).
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b,
+                                                   unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+  unsigned long long d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+__device__ __forceinline__ float2 unpack2(unsigned long long v) {
+  float2 r;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+  return r;
+}
+// Two packed 16-bit floats -> fp32x2.
+template <bool F16>
+__device__ __forceinline__ unsigned long long cvt_pair(uint32_t p) {
+  if constexpr (F16) {
+    float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&p));
+    return pack2(f.x, f.y);
+  } else {
+    unsigned long long d;
+    uint32_t lo = p << 16, hi = p & 0xffff0000u;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+  }
+}
+template <bool F16>
+__device__ __forceinline__ float cvt_one(uint16_t v) {
+  if constexpr (F16) {
+    return __half2float(__ushort_as_half(v));
+  } else {
+    return __uint_as_float(static_cast<uint32_t>(v) << 16);
+  }
+}
+template <bool F16>
+__device__ __forceinline__ uint16_t cvt_out(float v) {
+  if constexpr (F16) {
+    return __half_as_ushort(__float2half_rn(v));
+  } else {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+  }
+}
+__device__ __forceinline__ float bf16_round(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+// ------------------------------------------------------------ bounded waiting
+// Every wait in the kernel goes through one of these.  When the budget runs
+// out the waiter records who gave up, raises the global abort word and
+// returns false; every other waiter sees the abort word and returns false too,
+// so the grid drains instead of hanging.
+struct WaitCtx {
+  const Runtime *rt;
+  Misc *misc;
+  int worker;
+  int task;
+  bool failed;  // sticky: once a wait of this warp has given up, later waits return at once
+};
+
+__device__ __forceinline__ bool abort_seen(const WaitCtx &w) {
+  return ld_relaxed_u64(w.rt->ctrl + kCtrlAbort) != 0ull;
+}
+__device__ __noinline__ void raise_abort(const WaitCtx &w, int code, int event) {
+  unsigned long long info = (static_cast<unsigned long long>(w.worker) << 40) |
+                            ((static_cast<unsigned long long>(w.task) & 0xfffffull) << 20) |
+                            (static_cast<unsigned long long>(event) & 0xfffffull);
+  unsigned long long old = atomicCAS(w.rt->ctrl + kCtrlAbort, 0ull,
+                                     static_cast<unsigned long long>(static_cast<unsigned>(-code)));
+  if (old == 0ull) {
+    w.rt->ctrl[kCtrlFailInfo] = info;
+    __threadfence();
+  }
+}
+
+// Wait until *ctr >= need (acquire).  One thread calls this.
+__device__ __forceinline__ bool wait_counter(const WaitCtx &w, const unsigned long long *ctr,
+                                             unsigned long long need, int event) {
+  if (ld_acquire_u64(ctr) >= need) return true;
+  unsigned long long t0 = globaltimer();
+  for (uint32_t it = 1;; ++it) {
+    if (ld_acquire_u64(ctr) >= need) return true;
+    __nanosleep(20);
+    if ((it & 63u) == 0u) {
+      if (abort_seen(w)) return false;
+      if (globaltimer() - t0 > w.rt->budget_ns) {
+        raise_abort(w, YPK_ERR_TIMEOUT, event);
+        return false;
+      }
+    }
+  }
+}
+
+// Wait for a phase of an mbarrier.  Called by all 32 lanes of a warp together; the
+// outcome is the same for every lane, so control flow stays warp-uniform.  After a
+// failure the caller keeps walking its loops (skipping the work) so that CTA-level
+// barriers still line up; every later wait returns false immediately.
+__device__ __forceinline__ bool wait_mbar(WaitCtx &w, unsigned long long *bar, uint32_t parity) {
+  if (w.failed) return false;
+  if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+  const unsigned long long t0 = globaltimer();
+  for (uint32_t it = 1;; ++it) {
+    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+    if ((it & 127u) == 0u) {
+      const bool seen = abort_seen(w);
+      const bool late = globaltimer() - t0 > w.rt->budget_ns;
+      if (__any_sync(0xffffffffu, seen || late)) {
+        if ((threadIdx.x & 31) == 0 && !seen) raise_abort(w, YPK_ERR_TIMEOUT, -2);
+        w.failed = true;
+        return false;
+      }
+    }
+  }
+}
+
+// Position in the shared-memory ring; producer and consumers each keep one and
+// advance it identically.
+struct RingPos {
+  uint32_t slot = 0;
+  uint32_t phase = 0;
+  uint32_t count = 0;  // stages passed so far
+  __device__ __forceinline__ void advance() {
+    ++count;
+    if (++slot == kStages) {
+      slot = 0;
+      phase ^= 1u;
+    }
+  }
+};
+
+// Columns of K staged per pass for a batch of `b` tokens (fp32 copy of the
+// activations has to fit the 64 KB x area); multiple of kStageCols.
+__device__ __forceinline__ int chunk_cols(int b, int K) {
+  int kc = (kXsBytes / 4 / b) / kStageCols * kStageCols;
+  return kc < K ? kc : K;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+}  // namespace ypk

@@ -1,0 +1,244 @@
+// Small tasks of the decode graph: embedding gather, arg-max sampling, stand-alone
+// RMSNorm and SiLU*mul (used when a graph does not match the fused LINEAR forms), and the
+// on-device continuous batcher that runs between iterations.
+#pragma once
+#include "device_common.cuh"
+
+namespace ypk {
+
+// out[b, col0:col0+ncols] = table[ids[b], col0:col0+ncols]; a negative id gives zeros
+// (tasks/ampere/embedding.cuh:42-70).
+__device__ __forceinline__ void embed_task(const ypk_task &t, int batch) {
+  const long long *ids = reinterpret_cast<const long long *>(t.ptr[0]);
+  const uint16_t *table = reinterpret_cast<const uint16_t *>(t.ptr[1]);
+  uint16_t *out = reinterpret_cast<uint16_t *>(t.ptr[2]);
+  const int col0 = t.iarg[1], ncols = t.iarg[2], ldt = t.iarg[3], ldo = t.iarg[4];
+  const int vec = ncols / 8;
+  for (int idx = threadIdx.x; idx < batch * vec; idx += kConsumerThreads) {
+    const int b = idx / vec, c = (idx - b * vec) * 8 + col0;
+    const long long id = __ldcg(ids + b);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (id >= 0) v = __ldg(reinterpret_cast<const uint4 *>(table + size_t(id) * ldt + c));
+    *reinterpret_cast<uint4 *>(out + size_t(b) * ldo + c) = v;
+  }
+}
+
+// Per-chunk (max, first index) of bf16 logits (tasks/blackwell/argmax_sm100.cuh:78-114;
+// ties resolve to the lowest index here, which is what torch.argmax does).
+__device__ __forceinline__ void argmax_partial_task(const ypk_task &t, int batch) {
+  const uint16_t *logits = reinterpret_cast<const uint16_t *>(t.ptr[0]);
+  uint16_t *pval = reinterpret_cast<uint16_t *>(t.ptr[1]);
+  long long *pidx = reinterpret_cast<long long *>(t.ptr[2]);
+  const int col0 = t.iarg[0], ncols = t.iarg[1], ld = t.iarg[2], part = t.iarg[3],
+            nparts = t.iarg[4];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int b = warp; b < batch; b += kConsumerWarps) {
+    const uint16_t *row = logits + size_t(b) * ld + col0;
+    float best = -INFINITY;
+    int bidx = 0x7fffffff;
+    for (int c = lane; c < ncols; c += 32) {
+      const float v = cvt_one<false>(__ldcg(row + c));
+      if (v > best) {  // strict: the first (lowest) index of a lane wins
+        best = v;
+        bidx = c;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bidx, o);
+      if (ov > best || (ov == best && oi < bidx)) {
+        best = ov;
+        bidx = oi;
+      }
+    }
+    if (lane == 0) {
+      pval[size_t(b) * nparts + part] = __bfloat16_as_ushort(__float2bfloat16_rn(best));
+      pidx[size_t(b) * nparts + part] = bidx == 0x7fffffff ? col0 : col0 + bidx;
+    }
+  }
+}
+
+// Final reduction over the chunks (argmax_sm100.cuh:116-167), token id as int64.
+__device__ __forceinline__ void argmax_reduce_task(const ypk_task &t, int batch) {
+  const uint16_t *pval = reinterpret_cast<const uint16_t *>(t.ptr[0]);
+  const long long *pidx = reinterpret_cast<const long long *>(t.ptr[1]);
+  long long *out = reinterpret_cast<long long *>(t.ptr[2]);
+  const int nparts = t.iarg[0];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int b = warp; b < batch; b += kConsumerWarps) {
+    float best = -INFINITY;
+    long long bidx = 0x7fffffffffffffffll;
+    for (int p = lane; p < nparts; p += 32) {
+      const float v = cvt_one<false>(__ldcg(pval + size_t(b) * nparts + p));
+      const long long i = __ldcg(pidx + size_t(b) * nparts + p);
+      if (v > best || (v == best && i < bidx)) {
+        best = v;
+        bidx = i;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const long long oi = __shfl_xor_sync(0xffffffffu, bidx, o);
+      if (ov > best || (ov == best && oi < bidx)) {
+        best = ov;
+        bidx = oi;
+      }
+    }
+    if (lane == 0) out[b] = bidx;
+  }
+}
+
+// out[b, :] = bf16(x * rsqrt(mean(x^2) + eps) * w) for rows [row0, row0+nrows) of the batch
+// (tasks/hopper/rmsnorm_hopper.cuh:20-155).  ptr = {x, w, out}; iarg = {K, row0, nrows, ldx, ldout}.
+__device__ __forceinline__ void rmsnorm_task(const ypk_task &t, int batch) {
+  const uint16_t *x = reinterpret_cast<const uint16_t *>(t.ptr[0]);
+  const uint16_t *w = reinterpret_cast<const uint16_t *>(t.ptr[1]);
+  uint16_t *out = reinterpret_cast<uint16_t *>(t.ptr[2]);
+  const int K = t.iarg[0], row0 = t.iarg[1], ldx = t.iarg[3], ldo = t.iarg[4];
+  const int row1 = min(batch, row0 + t.iarg[2]);
+  const float eps = t.farg[0];
+  const bool f16 = (t.flags & YPK_F_F16) != 0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int b = row0 + warp; b < row1; b += kConsumerWarps) {
+    float ss = 0.f;
+    for (int k = lane; k < K; k += 32) {
+      const uint16_t v = __ldcg(x + size_t(b) * ldx + k);
+      const float f = f16 ? cvt_one<true>(v) : cvt_one<false>(v);
+      ss += f * f;
+    }
+    const float rn = rsqrtf(warp_sum(ss) / float(K) + eps);
+    for (int k = lane; k < K; k += 32) {
+      const uint16_t v = __ldcg(x + size_t(b) * ldx + k);
+      const float f = f16 ? cvt_one<true>(v) : cvt_one<false>(v);
+      const float wf = w ? (f16 ? cvt_one<true>(__ldg(w + k)) : cvt_one<false>(__ldg(w + k))) : 1.f;
+      const float y = f * rn * wf;
+      out[size_t(b) * ldo + k] = f16 ? cvt_out<true>(y) : cvt_out<false>(y);
+    }
+  }
+}
+
+// out[b, j] = bf16(silu(gate)) * up for output columns [col0, col0+ncols); the input row
+// holds groups of (gs gate | gs up) columns (tasks/ampere/silu_mul.cuh:19-42).
+// ptr = {in, out}; iarg = {col0, ncols, gs, ldin, ldout}.
+__device__ __forceinline__ void silu_mul_task(const ypk_task &t, int batch) {
+  const uint16_t *in = reinterpret_cast<const uint16_t *>(t.ptr[0]);
+  uint16_t *out = reinterpret_cast<uint16_t *>(t.ptr[1]);
+  const int col0 = t.iarg[0], ncols = t.iarg[1], gs = t.iarg[2], ldi = t.iarg[3], ldo = t.iarg[4];
+  for (int idx = threadIdx.x; idx < batch * ncols; idx += kConsumerThreads) {
+    const int b = idx / ncols, j = col0 + (idx - b * ncols);
+    const int grp = j / gs, within = j - grp * gs;
+    const float g = cvt_one<false>(__ldcg(in + size_t(b) * ldi + size_t(grp) * 2 * gs + within));
+    const float u = cvt_one<false>(__ldcg(in + size_t(b) * ldi + size_t(grp) * 2 * gs + gs + within));
+    const float s = bf16_round(g / (1.0f + __expf(-g)));
+    out[size_t(b) * ldo + j] = cvt_out<false>(s * u);
+  }
+}
+
+// ------------------------------------------------------------ batcher
+// Continuous batching between iterations, one thread (the reference runs the same
+// logic in scheduler 0: persistent_kernel.cuh:169-322).  Retires finished requests and
+// frees their pages, compacts the active ones, admits new requests, chunks prefill to
+// the token budget (and to kMaxNewTokens per request), copies the iteration's input
+// tokens and rebuilds qo_indptr / paged_kv_indptr / paged_kv_indices.
+// paged_kv_last_page_len is written in [1, page_size].
+// `first` skips the finalisation of a previous batch.  Returns the number of active
+// tokens of the next iteration (0 = everything retired).
+__device__ __noinline__ int prepare_next_batch(const Runtime &rt, bool first) {
+  const int MR = rt.max_req, MT = rt.max_tok, MP = rt.max_pages, PS = rt.page_size;
+  int head = rt.bstate[1], tail = rt.bstate[2];
+  if (!first) {
+    for (int i = 0; i < MR; ++i) {
+      const int req = rt.request_ids[i];
+      if (req < 0) continue;
+      const int step = rt.step[req];
+      const int qo = rt.qo_indptr[i];
+      const int ntok = rt.qo_indptr[i + 1] - qo;
+      const int plen = rt.prompt_len[req];
+      for (int j = 0; j < ntok; ++j) {
+        if (step + j + 1 >= plen && step + j + 1 < rt.max_seq) {
+          rt.tokens[size_t(req) * rt.max_seq + step + j + 1] = __ldcg(rt.output_tokens + qo + j);
+        }
+      }
+      rt.step[req] = step + ntok;
+      const bool full = step + ntok + 1 >= rt.max_seq;
+      const bool eos = step + ntok >= plen && step + ntok < rt.max_seq &&
+                       rt.tokens[size_t(req) * rt.max_seq + step + ntok] == rt.eos;
+      if (full || eos) {
+        rt.request_ids[i] = -1;
+        const int kv = rt.kv_indptr[i];
+        const int np = rt.kv_indptr[i + 1] - kv;
+        for (int j = 0; j < np; ++j) {
+          rt.page_queue[tail % MP] = rt.kv_indices[kv + j];
+          ++tail;
+        }
+      }
+    }
+  }
+  int nreq = 0, ntok = 0, npages = 0;
+  // Surviving requests keep their pages.  A request that grows can push the compacted
+  // list past the old position of a later request, so rebuild from a copy.
+  {
+    const int nold_total = rt.kv_indptr[MR];
+    for (int j = 0; j < nold_total; ++j) rt.kv_tmp[j] = rt.kv_indices[j];
+  }
+  for (int i = 0; i < MR; ++i) {
+    const int req = rt.request_ids[i];
+    if (req < 0) continue;
+    const int kv = rt.kv_indptr[i];
+    const int nold = rt.kv_indptr[i + 1] - kv;
+    const int step = rt.step[req];
+    int nnew = rt.prompt_len[req] - step;
+    nnew = nnew > 0 ? min(min(nnew, MT - ntok), kMaxNewTokens) : min(1, MT - ntok);
+    // nreq <= i, so the indptr entries overwritten below have been consumed already.
+    for (int j = 0; j < nold; ++j) rt.kv_indices[npages + j] = rt.kv_tmp[kv + j];
+    rt.request_ids[nreq] = req;
+    rt.qo_indptr[nreq] = ntok;
+    rt.kv_indptr[nreq] = npages;
+    for (int j = 0; j < nnew; ++j)
+      rt.input_tokens[ntok + j] = rt.tokens[size_t(req) * rt.max_seq + step + j];
+    const int total = step + nnew;
+    const int need = (total + PS - 1) / PS;
+    for (int j = nold; j < need; ++j) {
+      rt.kv_indices[npages + j] = rt.page_queue[head % MP];
+      ++head;
+    }
+    const int have = max(need, nold);
+    rt.kv_last_len[nreq] = total > 0 ? (total - 1) % PS + 1 : 0;
+    npages += have;
+    ntok += nnew;
+    ++nreq;
+  }
+  while (nreq < MR && ntok < MT) {
+    const int req = rt.bstate[0];
+    if (req >= rt.total_req) break;
+    int nnew = min(min(rt.prompt_len[req], MT - ntok), kMaxNewTokens);
+    const int need = (nnew + PS - 1) / PS;
+    if (npages + need > MP || (tail - head) < need) break;  // no page budget yet
+    rt.request_ids[nreq] = req;
+    rt.qo_indptr[nreq] = ntok;
+    rt.kv_indptr[nreq] = npages;
+    for (int j = 0; j < nnew; ++j)
+      rt.input_tokens[ntok + j] = rt.tokens[size_t(req) * rt.max_seq + j];
+    for (int j = 0; j < need; ++j) {
+      rt.kv_indices[npages + j] = rt.page_queue[head % MP];
+      ++head;
+    }
+    rt.kv_last_len[nreq] = nnew > 0 ? (nnew - 1) % PS + 1 : 0;
+    npages += need;
+    ntok += nnew;
+    ++nreq;
+    rt.bstate[0] = req + 1;
+  }
+  for (int i = nreq; i < MR; ++i) rt.request_ids[i] = -1;
+  for (int i = nreq; i <= MR; ++i) {
+    rt.qo_indptr[i] = ntok;
+    rt.kv_indptr[i] = npages;
+  }
+  rt.bstate[1] = head;
+  rt.bstate[2] = tail;
+  return ntok;
+}
+
+}  // namespace ypk

@@ -1,0 +1,706 @@
+// Host side of the C ABI declared in include/ypk.h: handle, tensor registry, graph
+// loading/validation, launch and status.  The device code lives in megakernel.cuh.
+//
+// A handle created with cfg.device == -1 is a host-only handle: it validates and
+// resolves graphs exactly like a real one but owns no device memory and cannot launch.
+// It exists so that graph validation can be exercised on a machine without a GPU.
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/ypk.h"
+#include "megakernel.cuh"
+
+using namespace ypk;
+
+namespace {
+
+struct Slot {
+  void *ptr = nullptr;
+  uint64_t bytes = 0;
+  bool owned = false;
+  bool used = false;
+  std::string name;
+};
+
+}  // namespace
+
+struct ypk_handle {
+  ypk_config cfg;
+  bool host_only = false;
+  int num_workers = 0;
+  int sm_count = 0;
+  std::vector<Slot> slots;
+  std::vector<ypk_task> tasks;  // resolved copies
+  std::vector<int32_t> queue, queue_off;
+  int num_events = 0;
+  int end_event = -1, end_count = 0;
+  bool graph_loaded = false;
+  // device state
+  ypk_task *d_tasks = nullptr;
+  int *d_queue = nullptr, *d_queue_off = nullptr;
+  unsigned long long *d_events = nullptr, *d_ctrl = nullptr;
+  int *d_request_ids = nullptr, *d_page_queue = nullptr, *d_kv_tmp = nullptr, *d_bstate = nullptr;
+  // progress
+  long long base_iter = 0;
+  int pending_tokens = 0;
+  bool resume_pending = false;
+  bool finished = false;
+  bool in_flight = false;
+  cudaStream_t stream = nullptr;
+  ypk_status status;
+  std::string err;
+};
+
+namespace {
+
+thread_local std::string g_err;
+
+int fail(ypk_handle *h, int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (h) h->err = buf;
+  g_err = buf;
+  return code;
+}
+
+#define CUDA_TRY(h, call)                                                              \
+  do {                                                                                 \
+    cudaError_t e_ = (call);                                                           \
+    if (e_ != cudaSuccess)                                                             \
+      return fail(h, YPK_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e_));    \
+  } while (0)
+
+Slot *get_slot(ypk_handle *h, int32_t slot, bool create) {
+  if (slot < 0 || slot >= 65534) return nullptr;
+  if (size_t(slot) >= h->slots.size()) {
+    if (!create) return nullptr;
+    h->slots.resize(size_t(slot) + 1);
+  }
+  return &h->slots[size_t(slot)];
+}
+
+void release_slot(ypk_handle *h, Slot &s) {
+  if (s.owned && s.ptr && !h->host_only) cudaFree(s.ptr);
+  s = Slot();
+}
+
+// Resolve one encoded operand; checks that [offset, offset+need) lies inside the tensor.
+int resolve(ypk_handle *h, int ti, int pi, uint64_t ref, uint64_t need, uint64_t align,
+            uint64_t *out) {
+  if (ref == 0) {
+    *out = 0;
+    return need == 0 ? YPK_OK
+                     : fail(h, YPK_ERR_INVALID, "task %d: operand %d is required", ti, pi);
+  }
+  const int slot = int(ref >> 48) - 1;
+  const uint64_t off = ref & 0xFFFFFFFFFFFFull;
+  Slot *s = get_slot(h, slot, false);
+  if (!s || !s->used)
+    return fail(h, YPK_ERR_INVALID, "task %d: operand %d names unbound tensor slot %d", ti, pi,
+                slot);
+  if (off + need > s->bytes)
+    return fail(h, YPK_ERR_INVALID,
+                "task %d: operand %d reaches byte %llu of tensor '%s' (%llu bytes)", ti, pi,
+                (unsigned long long)(off + need), s->name.c_str(), (unsigned long long)s->bytes);
+  const uint64_t addr = reinterpret_cast<uint64_t>(s->ptr) + off;
+  if (align && addr % align)
+    return fail(h, YPK_ERR_INVALID, "task %d: operand %d of tensor '%s' is not %llu-byte aligned",
+                ti, pi, s->name.c_str(), (unsigned long long)align);
+  *out = addr;
+  return YPK_OK;
+}
+
+// Shape checks + pointer resolution for one task.  `mb` = largest batch the graph can see.
+int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
+  *out = in;
+  const int mb = h->cfg.max_num_batched_tokens > 0 ? h->cfg.max_num_batched_tokens : 1;
+  const int32_t *a = in.iarg;
+  uint64_t need[YPK_TASK_NPTR] = {0}, align[YPK_TASK_NPTR] = {0};
+  bool required[YPK_TASK_NPTR] = {false};
+  auto rows = [](int ld, int n, int cols) -> uint64_t {  // bytes spanned by n rows of 16-bit
+    return n <= 0 ? 0 : (uint64_t(n - 1) * ld + cols) * 2u;
+  };
+  switch (in.type) {
+    case YPK_TASK_NOP: break;
+    case YPK_TASK_LINEAR: {
+      const int K = a[0], row0 = a[1], nrows = a[2], ldx = a[3], ldw = a[4], ldo = a[5],
+                ldr = a[6], oc0 = a[7];
+      if (K <= 0 || K % 64 || nrows <= 0 || nrows > kMaxAccRows || row0 < 0)
+        return fail(h, YPK_ERR_UNSUPPORTED,
+                    "task %d: LINEAR needs K %% 64 == 0 and 1..%d rows (K=%d rows=%d)", ti,
+                    kMaxAccRows, K, nrows);
+      if (ldx % 8 || ldw % 8 || ldx < K || ldw < K)
+        return fail(h, YPK_ERR_INVALID, "task %d: LINEAR strides (ldx=%d ldw=%d K=%d)", ti, ldx,
+                    ldw, K);
+      const bool silu = in.flags & YPK_F_SILU_MUL;
+      if (silu && (row0 % 16 || nrows % 16))
+        return fail(h, YPK_ERR_INVALID, "task %d: SILU_MUL rows must come in 16-row granules", ti);
+      if ((in.flags & YPK_F_NORM) && (in.flags & YPK_F_NORM_NOWEIGHT))
+        return fail(h, YPK_ERR_INVALID, "task %d: NORM and NORM_NOWEIGHT together", ti);
+      const int ocols0 = silu ? oc0 + row0 / 2 : oc0 + row0;
+      const int ocols = silu ? nrows / 2 : nrows;
+      need[0] = rows(ldx, mb, K); align[0] = 16; required[0] = true;
+      need[1] = rows(ldw, row0 + nrows, K); align[1] = 16; required[1] = true;
+      need[2] = rows(ldo, mb, ocols0 + ocols); align[2] = 2; required[2] = true;
+      if (in.flags & YPK_F_NORM) { need[3] = uint64_t(K) * 2; align[3] = 16; required[3] = true; }
+      if (in.flags & YPK_F_RESIDUAL) {
+        need[4] = rows(ldr, mb, ocols0 + ocols); align[4] = 2; required[4] = true;
+      }
+      break;
+    }
+    case YPK_TASK_EMBED: {
+      const int col0 = a[1], ncols = a[2], ldt = a[3], ldo = a[4];
+      if (ncols <= 0 || ncols % 8 || col0 % 8 || ldt % 8 || ldo % 8)
+        return fail(h, YPK_ERR_INVALID, "task %d: EMBED columns must be multiples of 8", ti);
+      need[0] = uint64_t(mb) * 8; align[0] = 8; required[0] = true;
+      need[1] = uint64_t(col0 + ncols) * 2; align[1] = 16; required[1] = true;
+      need[2] = rows(ldo, mb, col0 + ncols); align[2] = 16; required[2] = true;
+      break;
+    }
+    case YPK_TASK_ATTENTION: {
+      const int r = a[0], kvh = a[1], split = a[2], nsplit = a[3], G = a[4], hkv = a[5],
+                ldq = a[6], ldo = a[7], max_rows = a[8];
+      if (G < 1 || G > 8 || hkv < 1 || kvh < 0 || kvh >= hkv || nsplit < 1 || split < 0 ||
+          split >= nsplit || r < 0 || r >= h->cfg.max_num_batched_requests)
+        return fail(h, YPK_ERR_UNSUPPORTED,
+                    "task %d: ATTENTION needs 1..8 q heads per kv head (got %d), head_dim 128", ti,
+                    G);
+      if (h->cfg.page_size <= 0 || h->cfg.page_size % kKvTile)
+        return fail(h, YPK_ERR_UNSUPPORTED, "ATTENTION needs page_size %% %d == 0 (got %d)",
+                    kKvTile, h->cfg.page_size);
+      if (max_rows < G * kMaxNewTokens)
+        return fail(h, YPK_ERR_INVALID, "task %d: ATTENTION scratch rows %d < %d", ti, max_rows,
+                    G * kMaxNewTokens);
+      if (!h->cfg.qo_indptr || !h->cfg.paged_kv_indptr || !h->cfg.paged_kv_indices ||
+          !h->cfg.paged_kv_last_page_len)
+        return fail(h, YPK_ERR_INVALID, "ATTENTION needs the paged-KV meta tensors in ypk_config");
+      const uint64_t cache_bytes =
+          uint64_t(h->cfg.max_num_pages) * h->cfg.page_size * hkv * kHeadDim * 2u;
+      need[0] = rows(ldq, mb, hkv * (G + 2) * kHeadDim); align[0] = 16; required[0] = true;
+      need[1] = cache_bytes; align[1] = 16; required[1] = true;
+      need[2] = cache_bytes; align[2] = 16; required[2] = true;
+      need[3] = rows(ldo, mb, hkv * G * kHeadDim); align[3] = 2; required[3] = true;
+      if (in.flags & YPK_F_ROPE) {
+        need[4] = need[5] = uint64_t(kHeadDim) * 2; align[4] = align[5] = 2;
+        required[4] = required[5] = true;
+      }
+      if (nsplit > 1) {
+        need[6] = uint64_t(h->cfg.max_num_batched_requests) * hkv * nsplit * max_rows *
+                  kAttnRowFloats * 4u;
+        need[7] = uint64_t(h->cfg.max_num_batched_requests) * hkv * 4u;
+        align[6] = 16; align[7] = 4; required[6] = required[7] = true;
+      }
+      break;
+    }
+    case YPK_TASK_ARGMAX_PARTIAL: {
+      const int col0 = a[0], ncols = a[1], ld = a[2], part = a[3], nparts = a[4];
+      if (ncols <= 0 || part < 0 || part >= nparts)
+        return fail(h, YPK_ERR_INVALID, "task %d: ARGMAX_PARTIAL part %d of %d", ti, part, nparts);
+      need[0] = rows(ld, mb, col0 + ncols); align[0] = 2; required[0] = true;
+      need[1] = uint64_t(mb) * nparts * 2; align[1] = 2; required[1] = true;
+      need[2] = uint64_t(mb) * nparts * 8; align[2] = 8; required[2] = true;
+      break;
+    }
+    case YPK_TASK_ARGMAX_REDUCE: {
+      const int nparts = a[0];
+      if (nparts <= 0) return fail(h, YPK_ERR_INVALID, "task %d: ARGMAX_REDUCE nparts", ti);
+      need[0] = uint64_t(mb) * nparts * 2; align[0] = 2; required[0] = true;
+      need[1] = uint64_t(mb) * nparts * 8; align[1] = 8; required[1] = true;
+      need[2] = uint64_t(mb) * 8; align[2] = 8; required[2] = true;
+      break;
+    }
+    case YPK_TASK_RMSNORM: {
+      const int K = a[0], ldx = a[3], ldo = a[4];
+      if (K <= 0) return fail(h, YPK_ERR_INVALID, "task %d: RMSNORM K", ti);
+      need[0] = rows(ldx, mb, K); align[0] = 2; required[0] = true;
+      if (in.ptr[1]) { need[1] = uint64_t(K) * 2; align[1] = 2; }
+      need[2] = rows(ldo, mb, K); align[2] = 2; required[2] = true;
+      break;
+    }
+    case YPK_TASK_SILU_MUL: {
+      const int col0 = a[0], ncols = a[1], gs = a[2], ldi = a[3], ldo = a[4];
+      if (gs <= 0 || ncols <= 0) return fail(h, YPK_ERR_INVALID, "task %d: SILU_MUL shape", ti);
+      need[0] = rows(ldi, mb, 2 * (col0 + ncols)); align[0] = 2; required[0] = true;
+      need[1] = rows(ldo, mb, col0 + ncols); align[1] = 2; required[1] = true;
+      break;
+    }
+    default:
+      return fail(h, YPK_ERR_UNSUPPORTED, "task %d: task type %d is not built", ti, in.type);
+  }
+  for (int p = 0; p < YPK_TASK_NPTR; ++p) {
+    if (!required[p] && in.ptr[p] == 0) {
+      out->ptr[p] = 0;
+      continue;
+    }
+    if (required[p] && in.ptr[p] == 0)
+      return fail(h, YPK_ERR_INVALID, "task %d (type %d): operand %d is required", ti, in.type, p);
+    int rc = resolve(h, ti, p, in.ptr[p], need[p], align[p], &out->ptr[p]);
+    if (rc) return rc;
+  }
+  if (in.dep_event >= h->num_events || in.trig_event >= h->num_events)
+    return fail(h, YPK_ERR_INVALID, "task %d: event index out of range", ti);
+  if (in.dep_event >= 0 && in.dep_count <= 0)
+    return fail(h, YPK_ERR_INVALID, "task %d: dependency without a trigger count", ti);
+  return YPK_OK;
+}
+
+void free_graph(ypk_handle *h) {
+  if (!h->host_only) {
+    if (h->d_tasks) cudaFree(h->d_tasks);
+    if (h->d_queue) cudaFree(h->d_queue);
+    if (h->d_queue_off) cudaFree(h->d_queue_off);
+    if (h->d_events) cudaFree(h->d_events);
+  }
+  h->d_tasks = nullptr;
+  h->d_queue = h->d_queue_off = nullptr;
+  h->d_events = nullptr;
+  h->graph_loaded = false;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ypk_abi_version(void) { return YPK_ABI_VERSION; }
+
+const char *ypk_last_error(const ypk_handle *h) { return h ? h->err.c_str() : g_err.c_str(); }
+
+int ypk_create(const ypk_config *cfg, ypk_handle **out) {
+  if (!cfg || !out) return fail(nullptr, YPK_ERR_INVALID, "ypk_create: null argument");
+  if (cfg->abi_version != YPK_ABI_VERSION)
+    return fail(nullptr, YPK_ERR_INVALID, "ypk_create: ABI version %d, library has %d",
+                cfg->abi_version, YPK_ABI_VERSION);
+  if (cfg->mode != 0 && cfg->mode != 1)
+    return fail(nullptr, YPK_ERR_INVALID, "ypk_create: mode must be 0 or 1");
+  if (cfg->world_size < 1 || cfg->rank < 0 || cfg->rank >= cfg->world_size)
+    return fail(nullptr, YPK_ERR_INVALID, "ypk_create: rank %d of world %d", cfg->rank,
+                cfg->world_size);
+  if (cfg->mode == 1) {
+    if (!cfg->step || !cfg->tokens || !cfg->input_tokens || !cfg->output_tokens ||
+        !cfg->prompt_lengths || !cfg->qo_indptr || !cfg->paged_kv_indptr ||
+        !cfg->paged_kv_indices || !cfg->paged_kv_last_page_len)
+      return fail(nullptr, YPK_ERR_INVALID, "ypk_create: serving mode needs every meta tensor");
+    if (cfg->max_seq_length <= 0 || cfg->max_num_batched_requests <= 0 ||
+        cfg->max_num_batched_tokens <= 0 || cfg->max_num_batched_tokens > 0xffff ||
+        cfg->max_num_pages <= 0 || cfg->page_size <= 0 || cfg->total_num_requests <= 0)
+      return fail(nullptr, YPK_ERR_INVALID, "ypk_create: serving sizes must be positive");
+  }
+  ypk_handle *h = new ypk_handle();
+  h->cfg = *cfg;
+  if (h->cfg.wait_budget_ns == 0) h->cfg.wait_budget_ns = 2000000000ull;
+  memset(&h->status, 0, sizeof h->status);
+  h->status.fail_task = h->status.fail_event = h->status.fail_worker = -1;
+  h->host_only = cfg->device < 0;
+  if (h->host_only) {
+    h->sm_count = 148;
+    h->num_workers = cfg->num_workers > 0 ? cfg->num_workers : h->sm_count;
+    *out = h;
+    return YPK_OK;
+  }
+  cudaError_t e = cudaSetDevice(cfg->device);
+  if (e != cudaSuccess) {
+    int rc = fail(nullptr, YPK_ERR_CUDA, "cudaSetDevice(%d): %s", cfg->device,
+                  cudaGetErrorString(e));
+    delete h;
+    return rc;
+  }
+  cudaDeviceProp prop;
+  e = cudaGetDeviceProperties(&prop, cfg->device);
+  if (e == cudaSuccess && prop.major != 10) {
+    int rc = fail(nullptr, YPK_ERR_UNSUPPORTED,
+                  "device %d is sm_%d%d; this library is built for sm_100a only", cfg->device,
+                  prop.major, prop.minor);
+    delete h;
+    return rc;
+  }
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(ypk_megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemBytes);
+  int per_sm = 0;
+  if (e == cudaSuccess)
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ypk_megakernel, kBlockThreads,
+                                                      kSmemBytes);
+  if (e != cudaSuccess || per_sm < 1) {
+    int rc = fail(nullptr, YPK_ERR_CUDA, "megakernel cannot be made resident: %s",
+                  e != cudaSuccess ? cudaGetErrorString(e) : "0 blocks per SM");
+    delete h;
+    return rc;
+  }
+  h->sm_count = prop.multiProcessorCount;
+  h->num_workers = cfg->num_workers > 0 ? cfg->num_workers : h->sm_count;
+  if (h->num_workers > h->sm_count * per_sm) h->num_workers = h->sm_count * per_sm;
+  if (cudaMalloc(&h->d_ctrl, kCtrlWords * 8) != cudaSuccess ||
+      cudaMemset(h->d_ctrl, 0, kCtrlWords * 8) != cudaSuccess) {
+    int rc = fail(nullptr, YPK_ERR_CUDA, "control block allocation failed");
+    delete h;
+    return rc;
+  }
+  if (cfg->mode == 1) {
+    const int MR = cfg->max_num_batched_requests, MP = cfg->max_num_pages;
+    if (cudaMalloc(&h->d_request_ids, MR * 4) != cudaSuccess ||
+        cudaMalloc(&h->d_page_queue, MP * 4) != cudaSuccess ||
+        cudaMalloc(&h->d_kv_tmp, MP * 4) != cudaSuccess ||
+        cudaMalloc(&h->d_bstate, 16) != cudaSuccess) {
+      int rc = fail(nullptr, YPK_ERR_CUDA, "batcher state allocation failed");
+      ypk_destroy(h);
+      return rc;
+    }
+    int rc = ypk_reset(h);
+    if (rc) {
+      g_err = h->err;
+      ypk_destroy(h);
+      return rc;
+    }
+  }
+  *out = h;
+  return YPK_OK;
+}
+
+int ypk_destroy(ypk_handle *h) {
+  if (!h) return YPK_OK;
+  if (!h->host_only) {
+    cudaSetDevice(h->cfg.device);
+    if (h->in_flight) cudaStreamSynchronize(h->stream);
+  }
+  free_graph(h);
+  for (auto &s : h->slots) release_slot(h, s);
+  if (!h->host_only) {
+    if (h->d_ctrl) cudaFree(h->d_ctrl);
+    if (h->d_request_ids) cudaFree(h->d_request_ids);
+    if (h->d_page_queue) cudaFree(h->d_page_queue);
+    if (h->d_kv_tmp) cudaFree(h->d_kv_tmp);
+    if (h->d_bstate) cudaFree(h->d_bstate);
+  }
+  delete h;
+  return YPK_OK;
+}
+
+int ypk_bind_tensor(ypk_handle *h, int32_t slot, const char *name, void *dev_ptr,
+                    uint64_t bytes) {
+  if (!h) return fail(nullptr, YPK_ERR_INVALID, "null handle");
+  if (!dev_ptr || bytes == 0) return fail(h, YPK_ERR_INVALID, "bind_tensor: empty tensor");
+  Slot *s = get_slot(h, slot, true);
+  if (!s) return fail(h, YPK_ERR_INVALID, "bind_tensor: bad slot %d", slot);
+  release_slot(h, *s);
+  s->ptr = dev_ptr;
+  s->bytes = bytes;
+  s->used = true;
+  s->name = name ? name : "";
+  return YPK_OK;
+}
+
+int ypk_alloc_tensor(ypk_handle *h, int32_t slot, const char *name, uint64_t bytes) {
+  if (!h) return fail(nullptr, YPK_ERR_INVALID, "null handle");
+  if (bytes == 0) return fail(h, YPK_ERR_INVALID, "alloc_tensor: zero bytes");
+  Slot *s = get_slot(h, slot, true);
+  if (!s) return fail(h, YPK_ERR_INVALID, "alloc_tensor: bad slot %d", slot);
+  release_slot(h, *s);
+  if (h->host_only) {
+    // distinct, 256-byte aligned fake addresses so that alignment checks still mean something
+    static uint64_t next_fake = 0x100000000ull;
+    s->ptr = reinterpret_cast<void *>(next_fake);
+    next_fake += (bytes + 255) / 256 * 256;
+  } else {
+    CUDA_TRY(h, cudaSetDevice(h->cfg.device));
+    CUDA_TRY(h, cudaMalloc(&s->ptr, bytes));
+    CUDA_TRY(h, cudaMemset(s->ptr, 0, bytes));
+    s->owned = true;
+  }
+  s->bytes = bytes;
+  s->used = true;
+  s->name = name ? name : "";
+  return YPK_OK;
+}
+
+int ypk_shuffle_tensor(ypk_handle *h, int32_t dst_slot, const char *name, int32_t n_src,
+                       const int32_t *src_slots, const int32_t *rows, const int32_t *gran,
+                       uint64_t row_bytes) {
+  if (!h) return fail(nullptr, YPK_ERR_INVALID, "null handle");
+  if (n_src < 1 || n_src > 8 || !src_slots || !rows || !gran || row_bytes == 0)
+    return fail(h, YPK_ERR_INVALID, "shuffle_tensor: bad arguments");
+  int64_t total_rows = 0, block_rows = 0, groups = -1;
+  for (int i = 0; i < n_src; ++i) {
+    Slot *s = get_slot(h, src_slots[i], false);
+    if (!s || !s->used) return fail(h, YPK_ERR_INVALID, "shuffle_tensor: source %d unbound", i);
+    if (rows[i] <= 0 || gran[i] <= 0 || rows[i] % gran[i])
+      return fail(h, YPK_ERR_INVALID, "shuffle_tensor: rows %d not a multiple of granule %d",
+                  rows[i], gran[i]);
+    if (uint64_t(rows[i]) * row_bytes > s->bytes)
+      return fail(h, YPK_ERR_INVALID, "shuffle_tensor: source %d smaller than rows*row_bytes", i);
+    const int64_t g = rows[i] / gran[i];
+    if (groups >= 0 && g != groups)
+      return fail(h, YPK_ERR_INVALID, "shuffle_tensor: sources disagree on the group count");
+    groups = g;
+    total_rows += rows[i];
+    block_rows += gran[i];
+  }
+  int rc = ypk_alloc_tensor(h, dst_slot, name, uint64_t(total_rows) * row_bytes);
+  if (rc) return rc;
+  if (h->host_only) return YPK_OK;
+  Slot *d = get_slot(h, dst_slot, false);
+  int64_t row_in_block = 0;
+  for (int i = 0; i < n_src; ++i) {
+    Slot *s = get_slot(h, src_slots[i], false);
+    // block g of the destination, rows [row_in_block, row_in_block+gran[i]) <- source rows
+    // [g*gran[i], (g+1)*gran[i]): one strided 2-D copy per source.
+    CUDA_TRY(h, cudaMemcpy2D(static_cast<char *>(d->ptr) + row_in_block * row_bytes,
+                             size_t(block_rows) * row_bytes, s->ptr, size_t(gran[i]) * row_bytes,
+                             size_t(gran[i]) * row_bytes, size_t(groups),
+                             cudaMemcpyDeviceToDevice));
+    row_in_block += gran[i];
+  }
+  return YPK_OK;
+}
+
+int ypk_tensor_ptr(ypk_handle *h, int32_t slot, void **dev_ptr, uint64_t *bytes) {
+  if (!h) return fail(nullptr, YPK_ERR_INVALID, "null handle");
+  Slot *s = get_slot(h, slot, false);
+  if (!s || !s->used) return fail(h, YPK_ERR_INVALID, "tensor_ptr: slot %d unbound", slot);
+  if (dev_ptr) *dev_ptr = s->ptr;
+  if (bytes) *bytes = s->bytes;
+  return YPK_OK;
+}
+
+int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int32_t num_events,
+                   const int32_t *queue, const int32_t *queue_off, int32_t num_queues) {
+  if (!h) return fail(nullptr, YPK_ERR_INVALID, "null handle");
+  if (h->in_flight) return fail(h, YPK_ERR_STATE, "load_graph while a launch is in flight");
+  if (!tasks || num_tasks <= 0 || num_events < 0 || !queue || !queue_off || num_queues <= 0)
+    return fail(h, YPK_ERR_INVALID, "load_graph: bad arguments");
+  if (num_queues > h->num_workers)
+    return fail(h, YPK_ERR_INVALID, "load_graph: %d queues for %d workers", num_queues,
+                h->num_workers);
+  if (num_tasks > 0xfffff) return fail(h, YPK_ERR_UNSUPPORTED, "load_graph: too many tasks");
+  h->num_events = num_events;
+  if (queue_off[0] != 0 || queue_off[num_queues] != num_tasks)
+    return fail(h, YPK_ERR_INVALID, "load_graph: queues must cover every task exactly once");
+  std::vector<char> seen(size_t(num_tasks), 0);
+  for (int w = 0; w < num_queues; ++w) {
+    if (queue_off[w + 1] < queue_off[w])
+      return fail(h, YPK_ERR_INVALID, "load_graph: queue offsets must not decrease");
+    int prev = -1;
+    for (int q = queue_off[w]; q < queue_off[w + 1]; ++q) {
+      const int ti = queue[q];
+      if (ti < 0 || ti >= num_tasks || seen[size_t(ti)])
+        return fail(h, YPK_ERR_INVALID, "load_graph: task %d queued twice or out of range", ti);
+      // Tasks are numbered in dependency order; a queue that runs them out of order
+      // can wait on an event that its own later task has to produce.
+      if (ti < prev)
+        return fail(h, YPK_ERR_INVALID, "load_graph: queue %d is not in task order", w);
+      prev = ti;
+      seen[size_t(ti)] = 1;
+    }
+  }
+  std::vector<ypk_task> resolved(static_cast<size_t>(num_tasks));
+  std::vector<int> trig_count(size_t(num_events), 0), last_trig(size_t(num_events), -1);
+  for (int i = 0; i < num_tasks; ++i) {
+    int rc = check_task(h, i, tasks[i], &resolved[size_t(i)]);
+    if (rc) return rc;
+    if (tasks[i].trig_event >= 0) {
+      trig_count[size_t(tasks[i].trig_event)]++;
+      last_trig[size_t(tasks[i].trig_event)] = i;
+    }
+  }
+  for (int i = 0; i < num_tasks; ++i) {
+    const ypk_task &t = tasks[i];
+    if (t.dep_event < 0) continue;
+    if (trig_count[size_t(t.dep_event)] != t.dep_count)
+      return fail(h, YPK_ERR_INVALID,
+                  "task %d waits for %d triggers of event %d but %d tasks trigger it", i,
+                  t.dep_count, t.dep_event, trig_count[size_t(t.dep_event)]);
+    // every producer of the awaited event must come earlier in task order
+    if (last_trig[size_t(t.dep_event)] >= i)
+      return fail(h, YPK_ERR_INVALID, "task %d waits for event %d that task %d triggers", i,
+                  t.dep_event, last_trig[size_t(t.dep_event)]);
+  }
+  h->end_event = tasks[num_tasks - 1].trig_event;
+  h->end_count = h->end_event >= 0 ? trig_count[size_t(h->end_event)] : 0;
+
+  free_graph(h);
+  h->tasks.swap(resolved);
+  h->queue.assign(queue, queue + num_tasks);
+  h->queue_off.assign(queue_off, queue_off + num_queues + 1);
+  // workers beyond num_queues get empty queues
+  while (int(h->queue_off.size()) < h->num_workers + 1) h->queue_off.push_back(num_tasks);
+  if (!h->host_only) {
+    CUDA_TRY(h, cudaSetDevice(h->cfg.device));
+    CUDA_TRY(h, cudaMalloc(&h->d_tasks, sizeof(ypk_task) * size_t(num_tasks)));
+    CUDA_TRY(h, cudaMalloc(&h->d_queue, 4 * size_t(num_tasks)));
+    CUDA_TRY(h, cudaMalloc(&h->d_queue_off, 4 * h->queue_off.size()));
+    CUDA_TRY(h, cudaMalloc(&h->d_events, 8 * size_t(num_events + 1)));
+    CUDA_TRY(h, cudaMemcpy(h->d_tasks, h->tasks.data(), sizeof(ypk_task) * size_t(num_tasks),
+                           cudaMemcpyHostToDevice));
+    CUDA_TRY(h, cudaMemcpy(h->d_queue, h->queue.data(), 4 * size_t(num_tasks),
+                           cudaMemcpyHostToDevice));
+    CUDA_TRY(h, cudaMemcpy(h->d_queue_off, h->queue_off.data(), 4 * h->queue_off.size(),
+                           cudaMemcpyHostToDevice));
+    CUDA_TRY(h, cudaMemset(h->d_events, 0, 8 * size_t(num_events + 1)));
+  }
+  h->base_iter = 0;
+  h->resume_pending = false;
+  h->pending_tokens = 0;
+  h->graph_loaded = true;
+  return YPK_OK;
+}
+
+int ypk_reset(ypk_handle *h) {
+  if (!h) return fail(nullptr, YPK_ERR_INVALID, "null handle");
+  if (h->in_flight) return fail(h, YPK_ERR_STATE, "reset while a launch is in flight");
+  h->base_iter = 0;
+  h->resume_pending = false;
+  h->pending_tokens = 0;
+  h->finished = false;
+  memset(&h->status, 0, sizeof h->status);
+  h->status.fail_task = h->status.fail_event = h->status.fail_worker = -1;
+  if (h->host_only) return YPK_OK;
+  CUDA_TRY(h, cudaSetDevice(h->cfg.device));
+  CUDA_TRY(h, cudaMemset(h->d_ctrl, 0, kCtrlWords * 8));
+  if (h->d_events) CUDA_TRY(h, cudaMemset(h->d_events, 0, 8 * size_t(h->num_events + 1)));
+  if (h->cfg.mode == 1) {
+    const ypk_config &c = h->cfg;
+    const int MR = c.max_num_batched_requests, MP = c.max_num_pages;
+    CUDA_TRY(h, cudaMemset(c.step, 0, 4 * size_t(c.total_num_requests)));
+    CUDA_TRY(h, cudaMemset(c.qo_indptr, 0, 4 * size_t(MR + 1)));
+    CUDA_TRY(h, cudaMemset(c.paged_kv_indptr, 0, 4 * size_t(MR + 1)));
+    CUDA_TRY(h, cudaMemset(h->d_request_ids, 0xff, 4 * size_t(MR)));
+    std::vector<int> pages(static_cast<size_t>(MP));
+    for (int i = 0; i < MP; ++i) pages[size_t(i)] = i;
+    CUDA_TRY(h, cudaMemcpy(h->d_page_queue, pages.data(), 4 * size_t(MP), cudaMemcpyHostToDevice));
+    const int bstate[4] = {0, 0, MP, 0};
+    CUDA_TRY(h, cudaMemcpy(h->d_bstate, bstate, 16, cudaMemcpyHostToDevice));
+  }
+  return YPK_OK;
+}
+
+int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_t batch) {
+  if (!h) return fail(nullptr, YPK_ERR_INVALID, "null handle");
+  if (h->host_only) return fail(h, YPK_ERR_STATE, "host-only handle cannot launch");
+  if (!h->graph_loaded) return fail(h, YPK_ERR_STATE, "launch before load_graph");
+  if (h->in_flight) return fail(h, YPK_ERR_STATE, "a launch is already in flight");
+  if (h->status.error) return fail(h, YPK_ERR_STATE, "handle is in a failed state; reset it");
+  const ypk_config &c = h->cfg;
+  if (c.mode == 0 && (batch < 1 || batch > (c.max_num_batched_tokens > 0 ? c.max_num_batched_tokens : 1)))
+    return fail(h, YPK_ERR_INVALID, "launch: batch %d outside 1..max_num_batched_tokens", batch);
+  if (c.mode == 1 && h->finished) return YPK_OK;  // nothing left to do
+  CUDA_TRY(h, cudaSetDevice(c.device));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Runtime rt;
+  memset(&rt, 0, sizeof rt);
+  rt.tasks = h->d_tasks;
+  rt.queue = h->d_queue;
+  rt.queue_off = h->d_queue_off;
+  rt.events = h->d_events;
+  rt.ctrl = h->d_ctrl;
+  rt.step = static_cast<int *>(c.step);
+  rt.tokens = static_cast<long long *>(c.tokens);
+  rt.input_tokens = static_cast<long long *>(c.input_tokens);
+  rt.output_tokens = static_cast<long long *>(c.output_tokens);
+  rt.prompt_len = static_cast<int *>(c.prompt_lengths);
+  rt.qo_indptr = static_cast<int *>(c.qo_indptr);
+  rt.kv_indptr = static_cast<int *>(c.paged_kv_indptr);
+  rt.kv_indices = static_cast<int *>(c.paged_kv_indices);
+  rt.kv_last_len = static_cast<int *>(c.paged_kv_last_page_len);
+  rt.request_ids = h->d_request_ids;
+  rt.page_queue = h->d_page_queue;
+  rt.kv_tmp = h->d_kv_tmp;
+  rt.bstate = h->d_bstate;
+  rt.eos = c.eos_token_id;
+  rt.base_iter = h->base_iter;
+  rt.budget_ns = c.wait_budget_ns;
+  rt.mode = c.mode;
+  rt.max_seq = c.max_seq_length;
+  rt.max_req = c.max_num_batched_requests;
+  rt.max_tok = c.max_num_batched_tokens;
+  rt.max_pages = c.max_num_pages;
+  rt.page_size = c.page_size;
+  rt.total_req = c.total_num_requests;
+  rt.max_iters = max_iterations;
+  rt.fixed_batch = batch;
+  rt.resume_pending = h->resume_pending ? 1 : 0;
+  rt.rank = c.rank;
+  rt.world = c.world_size;
+  rt.end_event = h->end_event;
+  rt.end_count = h->end_count;
+  // The control word a new launch starts from: last completed iteration, stopped, and
+  // the size of the batch that is waiting (if any).
+  const unsigned long long words[kCtrlWords] = {
+      (static_cast<unsigned long long>(h->base_iter) << 32) |
+          (static_cast<unsigned long long>(kStateStop) << 16) |
+          static_cast<unsigned long long>(h->pending_tokens),
+      0ull, 0ull, 0ull, 0ull, 0ull, 0ull, 0ull};
+  CUDA_TRY(h, cudaMemcpyAsync(h->d_ctrl, words, sizeof words, cudaMemcpyHostToDevice, st));
+  void *args[] = {&rt};
+  // Workers wait on each other, so they must all be resident: a cooperative launch
+  // refuses to start otherwise instead of deadlocking.
+  CUDA_TRY(h, cudaLaunchCooperativeKernel((const void *)ypk_megakernel, dim3(h->num_workers),
+                                          dim3(kBlockThreads), args, kSmemBytes, st));
+  h->stream = st;
+  h->in_flight = true;
+  return YPK_OK;
+}
+
+int ypk_wait(ypk_handle *h) {
+  if (!h) return fail(nullptr, YPK_ERR_INVALID, "null handle");
+  if (!h->in_flight) return YPK_OK;
+  CUDA_TRY(h, cudaSetDevice(h->cfg.device));
+  cudaError_t e = cudaStreamSynchronize(h->stream);
+  h->in_flight = false;
+  if (e != cudaSuccess) {
+    h->status.error = YPK_ERR_CUDA;
+    return fail(h, YPK_ERR_CUDA, "megakernel failed: %s", cudaGetErrorString(e));
+  }
+  unsigned long long words[kCtrlWords];
+  CUDA_TRY(h, cudaMemcpy(words, h->d_ctrl, sizeof words, cudaMemcpyDeviceToHost));
+  h->status.tasks_executed = (int64_t)words[kCtrlTasksDone];
+  if (words[kCtrlAbort]) {
+    const unsigned long long info = words[kCtrlFailInfo];
+    h->status.error = -int(words[kCtrlAbort]);
+    h->status.fail_worker = int(info >> 40);
+    h->status.fail_task = int((info >> 20) & 0xfffff);
+    int ev = int(info & 0xfffff);
+    if (ev & 0x80000) ev |= ~0xfffff;  // sign-extend the 20-bit field
+    h->status.fail_event = ev;
+    return fail(h, h->status.error,
+                "device wait timed out: worker %d, task %d, event %d (negative: -2 ring "
+                "barrier, -3 iteration word)",
+                h->status.fail_worker, h->status.fail_task, h->status.fail_event);
+  }
+  if (h->cfg.mode == 0) {
+    h->base_iter += 1;
+    h->status.iterations = h->base_iter;
+    return YPK_OK;
+  }
+  const unsigned long long w = words[kCtrlPublished];
+  const long long pub_iter = (long long)(w >> 32);
+  const int ntok = int(w & 0xffffull);
+  h->base_iter = pub_iter - 1;  // the published iteration itself did not run
+  h->pending_tokens = ntok;
+  h->resume_pending = ntok > 0;
+  h->finished = words[kCtrlFinished] != 0 || ntok == 0;
+  h->status.iterations = h->base_iter;
+  h->status.finished = h->finished ? 1 : 0;
+  h->status.active_tokens = ntok;
+  return YPK_OK;
+}
+
+int ypk_launch(ypk_handle *h, void *stream, int32_t max_iterations, int32_t batch) {
+  int rc = ypk_launch_async(h, stream, max_iterations, batch);
+  if (rc) return rc;
+  return ypk_wait(h);
+}
+
+int ypk_get_status(ypk_handle *h, ypk_status *out) {
+  if (!h || !out) return fail(h, YPK_ERR_INVALID, "get_status: null argument");
+  *out = h->status;
+  return YPK_OK;
+}
+
+}  // extern "C"
