@@ -183,6 +183,11 @@ int ypk_shuffle_tensor(ypk_handle *h, int32_t dst_slot, const char *name, int32_
                        const int32_t *src_slots, const int32_t *rows, const int32_t *gran,
                        uint64_t row_bytes);
 int ypk_tensor_ptr(ypk_handle *h, int32_t slot, void **dev_ptr, uint64_t *bytes);
+/* Device-to-device copy of `bytes` bytes of a registered tensor, starting at byte_off,
+ * into caller memory on the same device (inspection of runtime-owned intermediates;
+ * the reference has no counterpart, its intermediates are unreachable from Python). */
+int ypk_read_tensor(ypk_handle *h, int32_t slot, uint64_t byte_off, void *dst_dev_ptr,
+                    uint64_t bytes);
 
 /* Task graph: tasks in execution order, events as (trigger count) per event,
  * and the per-worker queues: worker w runs tasks

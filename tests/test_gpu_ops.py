@@ -1,0 +1,173 @@
+"""Parity of the task kernels against the CPU oracle, through the PersistentKernel surface
+and the C ABI, one operator per graph.  Tolerance: max-abs 2e-2 + relative 1e-2 against
+the fp32 oracle on the same bf16/fp16 inputs; ids and indices bit-exact."""
+import pytest
+import torch
+
+import yirage_b200 as yr
+from oracle import decode_oracle as O
+from tests.util import assert_close, onepass_kernel, randn
+
+pytestmark = pytest.mark.gpu
+
+
+def run_linear(B, K, Nrows, *, norm=False, residual=False, dtype=torch.bfloat16, seed=0,
+               eps=1e-6, max_tokens=8):
+    x = randn((max_tokens, K), seed, 1.0, dtype)
+    w = randn((Nrows, K), seed + 1, 0.02, dtype)
+    nw = randn((K,), seed + 2, 0.1, dtype, mean=1.0)
+    res = randn((max_tokens, Nrows), seed + 3, 1.0, dtype)
+    ypk = onepass_kernel(max_tokens)
+    ydt = yr.bfloat16 if dtype == torch.bfloat16 else yr.float16
+    xt = ypk.attach_input(x, "x")
+    wt = ypk.attach_input(w, "w")
+    out = torch.zeros(max_tokens, Nrows, dtype=dtype, device="cuda")
+    ot = ypk.attach_input(out, "out")
+    src = xt
+    if norm:
+        nwt = ypk.attach_input(nw, "nw")
+        tmp = ypk.new_tensor(dims=(max_tokens, K), dtype=ydt, name="normed")
+        ypk.rmsnorm_layer(xt, nwt, tmp, (max_tokens, 1, 1), (128, 1, 1), eps=eps)
+        src = tmp
+    if residual:
+        rt = ypk.attach_input(res, "res")
+        ypk.linear_with_residual_layer(src, wt, rt, ot, (Nrows // 64, 1, 1), (128, 1, 1))
+    else:
+        ypk.linear_layer(src, wt, ot, (Nrows // 64, 1, 1), (128, 1, 1))
+    ypk.compile()
+    ypk(batch=B)
+    torch.cuda.synchronize()
+    xin = x[:B].cpu()
+    if norm:
+        xin = O.rmsnorm(xin, nw.cpu(), eps)
+    want = O.linear(xin, w.cpu(), res[:B].cpu() if residual else None)
+    assert_close(out[:B], want, f"linear B={B} K={K} N={Nrows} norm={norm} res={residual}")
+    assert torch.all(out[B:] == 0), "rows beyond the batch must stay untouched"
+    ypk.finalize()
+
+
+@pytest.mark.parametrize("B", [1, 2, 3, 5, 8])
+def test_linear_plain(B):
+    run_linear(B, 512, 320)
+
+
+@pytest.mark.parametrize("B,K,N", [(1, 4096, 4096), (8, 4096, 4096), (4, 1792, 256), (1, 14336, 296)])
+def test_linear_shapes(B, K, N):
+    run_linear(B, K, N, seed=3)
+
+
+def test_linear_rmsnorm_fused_cfg1_fp16():
+    # BASELINE config 1: X [8,4096] fp16 ~N(0,1), norm weight ~N(1,0.1), eps 1e-6,
+    # W [4096,4096] fp16 ~N(0,0.02)
+    run_linear(8, 4096, 4096, norm=True, dtype=torch.float16, seed=0, eps=1e-6)
+
+
+@pytest.mark.parametrize("B", [1, 8])
+def test_linear_norm_residual(B):
+    run_linear(B, 1024, 512, norm=True, residual=True, seed=5, eps=1e-5)
+
+
+def test_linear_batch_above_eight_restreams():
+    run_linear(11, 512, 192, max_tokens=16, seed=9)
+
+
+@pytest.mark.parametrize("B,H,I", [(1, 512, 1024), (8, 4096, 1792), (3, 1024, 2048)])
+def test_gated_mlp_fused(B, H, I):
+    """rmsnorm -> linear(gate|up) -> silu_mul -> linear(down)+residual, the MLP half of a
+    layer (BASELINE config 2 at reduced width)."""
+    MT = 8
+    x = randn((MT, H), 1)
+    nw = randn((H,), 2, 0.1, mean=1.0)
+    wg, wu = randn((I, H), 3, 0.02), randn((I, H), 4, 0.02)
+    wd = randn((H, I), 5, 0.02)
+    ypk = onepass_kernel(MT)
+    xt, nwt = ypk.attach_input(x, "x"), ypk.attach_input(nw, "nw")
+    wgt, wut, wdt = ypk.attach_input(wg, "wg"), ypk.attach_input(wu, "wu"), ypk.attach_input(wd, "wd")
+    out = torch.zeros(MT, H, dtype=torch.bfloat16, device="cuda")
+    ot = ypk.attach_input(out, "out")
+    normed = ypk.new_tensor(dims=(MT, H), name="normed")
+    mid = ypk.new_tensor(dims=(MT, 2 * I), name="mid")
+    act = ypk.new_tensor(dims=(MT, I), name="act")
+    groups = 8
+    wgu = ypk.shuffle_tensors([wgt, wut], 0, groups, "wgu")
+    ypk.rmsnorm_layer(xt, nwt, normed, (MT, 1, 1), (128, 1, 1), eps=1e-5)
+    ypk.linear_layer(normed, wgu, mid, (2 * groups, 1, 1), (128, 1, 1))
+    ypk.silu_mul_layer(mid, act, (groups, 1, 1), (128, 1, 1))
+    ypk.linear_with_residual_layer(act, wdt, xt, ot, (H // 64, 1, 1), (128, 1, 1))
+    ypk.compile()
+    assert [o.kind for o in ypk.lower().ops] == ["linear", "linear"], "gate/up + silu must fuse"
+    ypk(batch=B)
+    torch.cuda.synchronize()
+    xc = x[:B].cpu()
+    h = O.rmsnorm(xc, nw.cpu(), 1e-5)
+    want = xc.float() + O.gated_mlp(h, wg.cpu(), wu.cpu(), wd.cpu())
+    assert_close(out[:B], want, f"gated mlp B={B}")
+    ypk.finalize()
+
+
+def test_unfused_rmsnorm_and_silu_mul_tasks():
+    """A norm whose output is read twice and a silu_mul on a plain tensor cannot fuse and run
+    as their own tasks."""
+    MT, H, groups = 4, 512, 4
+    x = randn((MT, H), 11)
+    nw = randn((H,), 12, 0.1, mean=1.0)
+    ypk = onepass_kernel(MT)
+    xt, nwt = ypk.attach_input(x, "x"), ypk.attach_input(nw, "nw")
+    normed_t = torch.zeros(MT, H, dtype=torch.bfloat16, device="cuda")
+    act_t = torch.zeros(MT, H // 2, dtype=torch.bfloat16, device="cuda")
+    normed, act = ypk.attach_input(normed_t, "normed"), ypk.attach_input(act_t, "act")
+    ypk.rmsnorm_layer(xt, nwt, normed, (MT, 1, 1), (128, 1, 1), eps=1e-6)
+    ypk.silu_mul_layer(normed, act, (groups, 1, 1), (128, 1, 1))
+    ypk.compile()
+    ypk(batch=3)
+    torch.cuda.synchronize()
+    want_n = O.rmsnorm(x[:3].cpu(), nw.cpu(), 1e-6, "bf16")
+    assert_close(normed_t[:3], want_n, "rmsnorm task")
+    gs = H // 2 // groups
+    v = normed_t[:3].cpu().float().view(3, groups, 2, gs)
+    want_a = O.silu_mul(v[:, :, 0], v[:, :, 1], "bf16").reshape(3, -1)
+    assert_close(act_t[:3], want_a, "silu_mul task")
+    ypk.finalize()
+
+
+def test_embedding_gather_is_bit_exact():
+    MT, V, H = 8, 1000, 1024
+    table = randn((V, H), 21, 0.02)
+    ids = torch.tensor([[5], [999], [0], [-1], [17], [17], [3], [512]], dtype=torch.int64, device="cuda")
+    out = torch.full((MT, H), 7.0, dtype=torch.bfloat16, device="cuda")
+    ypk = onepass_kernel(MT)
+    ypk.embed_layer(ypk.attach_input(ids, "ids"), ypk.attach_input(table, "table"),
+                    ypk.attach_input(out, "out"), (1, 1, 1), (128, 1, 1), input_source=1)
+    ypk.compile()
+    ypk(batch=6)
+    torch.cuda.synchronize()
+    want = table[ids[:6, 0].clamp(min=0)].clone()
+    want[3] = 0  # negative id -> zeros
+    assert torch.equal(out[:6], want)
+    assert torch.all(out[6:] == 7.0)
+    ypk.finalize()
+
+
+def test_argmax_is_bit_exact_with_planted_and_tied_maxima():
+    MT, V, parts = 8, 4096, 128
+    logits = randn((MT, V), 31)
+    logits[0, 4095] = 100.0            # last column
+    logits[1, 0] = 100.0               # first column
+    logits[2, 77] = logits[2, 3000] = 50.0   # tie across chunks: lowest index wins
+    logits[3, 1024] = logits[3, 1025] = 60.0  # tie inside a chunk
+    logits[4] = -5.0                   # all equal
+    pv = torch.zeros(MT, parts, dtype=torch.bfloat16, device="cuda")
+    pi = torch.zeros(MT, parts, dtype=torch.int64, device="cuda")
+    out = torch.full((MT, 1), -1, dtype=torch.int64, device="cuda")
+    ypk = onepass_kernel(MT)
+    lt, pvt, pit = ypk.attach_input(logits, "logits"), ypk.attach_input(pv, "pv"), ypk.attach_input(pi, "pi")
+    ot = ypk.attach_input(out, "out")
+    ypk.argmax_partial_layer(lt, (pvt, pit), (parts, 1, 1), (128, 1, 1))
+    ypk.argmax_reduce_layer((pvt, pit), ot, (1, 1, 1), (128, 1, 1))
+    ypk.compile()
+    ypk(batch=MT)
+    torch.cuda.synchronize()
+    want = O.argmax_lowest(logits.cpu().float())
+    assert out[:, 0].cpu().tolist() == want.tolist()
+    assert want.tolist()[:5] == [4095, 0, 77, 1024, 0]
+    ypk.finalize()

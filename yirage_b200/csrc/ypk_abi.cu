@@ -469,6 +469,20 @@ int ypk_tensor_ptr(ypk_handle *h, int32_t slot, void **dev_ptr, uint64_t *bytes)
   return YPK_OK;
 }
 
+int ypk_read_tensor(ypk_handle *h, int32_t slot, uint64_t byte_off, void *dst_dev_ptr,
+                    uint64_t bytes) {
+  if (!h) return fail(nullptr, YPK_ERR_INVALID, "null handle");
+  if (h->host_only) return fail(h, YPK_ERR_STATE, "host-only handle has no device memory");
+  Slot *s = get_slot(h, slot, false);
+  if (!s || !s->used) return fail(h, YPK_ERR_INVALID, "read_tensor: slot %d unbound", slot);
+  if (!dst_dev_ptr || byte_off + bytes > s->bytes)
+    return fail(h, YPK_ERR_INVALID, "read_tensor: range outside tensor '%s'", s->name.c_str());
+  CUDA_TRY(h, cudaSetDevice(h->cfg.device));
+  CUDA_TRY(h, cudaMemcpy(dst_dev_ptr, static_cast<char *>(s->ptr) + byte_off, bytes,
+                         cudaMemcpyDeviceToDevice));
+  return YPK_OK;
+}
+
 int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int32_t num_events,
                    const int32_t *queue, const int32_t *queue_off, int32_t num_queues) {
   if (!h) return fail(nullptr, YPK_ERR_INVALID, "null handle");

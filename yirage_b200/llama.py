@@ -1,0 +1,256 @@
+"""Llama-style decode graph on the PersistentKernel surface, plus synthetic weights.
+
+build_decode_kernel() issues the same sequence of PersistentKernel calls as the
+reference demo does for a Llama-3 model (demo/llama3/demo.py:325-349 attach inputs,
+:351-465 intermediate tensors, :472-484 embedding, :487-684 one transformer layer,
+:687-747 final norm / lm_head / arg-max, :750-812 compile), but takes plain tensors
+instead of a Hugging Face module so that random-init models of any Llama shape can be
+built directly on the GPU (the 70B-shaped configuration never exists on the host).
+"""
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import torch
+
+from . import core
+from .persistent_kernel import PersistentKernel
+
+
+@dataclass
+class LlamaShape:
+    hidden_size: int = 4096
+    intermediate_size: int = 14336
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    vocab_size: int = 128256
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 500000.0
+
+    @staticmethod
+    def llama3_8b():
+        return LlamaShape()
+
+    @staticmethod
+    def llama3_70b():
+        return LlamaShape(hidden_size=8192, intermediate_size=28672, num_hidden_layers=80,
+                          num_attention_heads=64, num_key_value_heads=8)
+
+    def decode_weight_bytes(self, world_size=1, padded_vocab=None):
+        """bf16 bytes of weights one rank streams per decode step (norm weights ignored)."""
+        h, f = self.hidden_size, self.intermediate_size
+        qkv = (self.num_attention_heads + 2 * self.num_key_value_heads) * self.head_dim * h
+        o = self.num_attention_heads * self.head_dim * h
+        per_layer = (qkv + o + 3 * f * h) // world_size
+        v = padded_vocab or self.vocab_size
+        return 2 * (self.num_hidden_layers * per_layer + v * h)
+
+
+def padded_vocab(vocab_size: int) -> int:
+    """The demo pads the lm_head to a multiple of 2048 rows (demo/llama3/demo.py:208)."""
+    return (vocab_size + 2047) // 2048 * 2048
+
+
+def rope_tables(shape: LlamaShape, max_pos: int, device):
+    """bf16 cos/sin [max_pos, head_dim]: fp32 angles, half table repeated
+    (demo/llama3/models/modeling_llama3.py:71-89)."""
+    d = shape.head_dim
+    inv_freq = 1.0 / (shape.rope_theta ** (torch.arange(0, d, 2, dtype=torch.int64,
+                                                        device=device).float() / d))
+    pos = torch.arange(max_pos, dtype=torch.float32, device=device)
+    emb = torch.cat((pos[:, None] * inv_freq[None, :],) * 2, dim=-1)
+    return emb.cos().to(torch.bfloat16).contiguous(), emb.sin().to(torch.bfloat16).contiguous()
+
+
+def init_weights(shape: LlamaShape, device, seed: int, world_size: int = 1, rank: int = 0,
+                 std: float = 0.02, dtype=torch.bfloat16) -> Dict:
+    """Random-init weights ~N(0, std) (norm weights 1), already sharded for `rank`:
+    q/k/v/gate/up split by output rows, o/down split by input columns
+    (modeling_llama3.py:98-100,174-185).  Every rank draws the full tensor from the same
+    seeded generator and keeps its slice, so the shards of all ranks form one model."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+
+    def full(rows, cols):
+        return torch.randn(rows, cols, generator=g, device=device, dtype=torch.float32).mul_(std).to(dtype)
+
+    def rows_shard(t):
+        n = t.shape[0] // world_size
+        return t[rank * n:(rank + 1) * n].contiguous()
+
+    def cols_shard(t):
+        n = t.shape[1] // world_size
+        return t[:, rank * n:(rank + 1) * n].contiguous()
+
+    h, f, d = shape.hidden_size, shape.intermediate_size, shape.head_dim
+    hq, hkv = shape.num_attention_heads, shape.num_key_value_heads
+    w = {"embed": full(shape.vocab_size, h), "layers": []}
+    for _ in range(shape.num_hidden_layers):
+        L = {
+            "input_norm": torch.ones(h, device=device, dtype=dtype),
+            "q": rows_shard(full(hq * d, h)),
+            "k": rows_shard(full(hkv * d, h)),
+            "v": rows_shard(full(hkv * d, h)),
+            "o": cols_shard(full(h, hq * d)),
+            "post_norm": torch.ones(h, device=device, dtype=dtype),
+            "gate": rows_shard(full(f, h)),
+            "up": rows_shard(full(f, h)),
+            "down": cols_shard(full(h, f)),
+        }
+        w["layers"].append(L)
+    w["final_norm"] = torch.ones(h, device=device, dtype=dtype)
+    w["lm_head"] = full(shape.vocab_size, h)
+    return w
+
+
+def _gate_up_groups(rows: int) -> int:
+    """Number of (gate|up) groups the demo asks shuffle_tensors for: half the task count
+    its grid heuristic picks for the fused gate/up projection (demo/llama3/demo.py:120-130,
+    617-624).  Only the layout of an unfused mlp_mid depends on it."""
+    size = 2 * rows
+    if size / 96 > 400 and size % 256 == 0:
+        return size // 256 // 2
+    for grid in (96, 80, 64, 48):
+        if size % grid == 0 and (size // grid >= 128 or size // grid == 64):
+            return max(1, grid // 2)
+    return 1
+
+
+def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tensor,
+                        prompt_lengths: torch.Tensor, max_num_batched_requests: int,
+                        max_num_batched_tokens: int, max_num_pages: int, page_size: int,
+                        eos_token_id: int = -1, world_size: int = 1, rank: int = 0,
+                        num_workers: int = 128, use_model_eps: bool = True,
+                        k_cache: Optional[torch.Tensor] = None,
+                        v_cache: Optional[torch.Tensor] = None, compile: bool = True,
+                        dry_run: bool = False):
+    """Build (and compile) the decode megakernel for `weights`.  Returns (ypk, state) where
+    state holds the meta tensors, caches and rope tables the kernel works on."""
+    dev = tokens.device
+    total_requests, max_seq_length = tokens.shape
+    h, d = shape.hidden_size, shape.head_dim
+    hq, hkv = shape.num_attention_heads // world_size, shape.num_key_value_heads // world_size
+    inter = shape.intermediate_size // world_size
+    vpad = padded_vocab(shape.vocab_size)
+    MT, MR = max_num_batched_tokens, max_num_batched_requests
+    i32 = dict(dtype=torch.int32, device=dev)
+    meta = {
+        "step": torch.zeros(total_requests, **i32),
+        "tokens": tokens,
+        "input_tokens": torch.zeros(MT, 1, dtype=torch.int64, device=dev),
+        "output_tokens": torch.zeros(MT, 1, dtype=torch.int64, device=dev),
+        "num_new_tokens": torch.ones(total_requests, **i32),
+        "prompt_lengths": prompt_lengths,
+        "qo_indptr_buffer": torch.zeros(MR + 1, **i32),
+        "paged_kv_indptr_buffer": torch.zeros(MR + 1, **i32),
+        "paged_kv_indices_buffer": torch.zeros(max_num_pages, **i32),
+        "paged_kv_last_page_len_buffer": torch.zeros(MR, **i32),
+    }
+    if k_cache is None:
+        k_cache = torch.zeros(shape.num_hidden_layers, max_num_pages, page_size, hkv, d,
+                              dtype=torch.bfloat16, device=dev)
+        v_cache = torch.zeros_like(k_cache)
+    cos, sin = rope_tables(shape, max(max_seq_length, 64), dev)
+    lm_head = torch.cat((weights["lm_head"],
+                         torch.zeros(vpad - shape.vocab_size, h, dtype=torch.bfloat16, device=dev)), 0)
+
+    ypk = PersistentKernel(
+        mode="offline", world_size=world_size, mpi_rank=rank, num_workers=num_workers,
+        num_local_schedulers=0, num_remote_schedulers=0, max_seq_length=max_seq_length,
+        max_num_batched_requests=MR, max_num_batched_tokens=MT, max_num_pages=max_num_pages,
+        page_size=page_size, eos_token_id=eos_token_id, meta_tensors=meta,
+        profiler_tensor=None, trace_name="", spec_decode_config=None, use_cutlass_kernel=True)
+    if use_model_eps:
+        ypk.rms_norm_eps = shape.rms_norm_eps
+
+    x_tok = ypk.attach_input(meta["input_tokens"], name="input_token")
+    cos_t = ypk.attach_input(cos, name="cos_position_embedding")
+    sin_t = ypk.attach_input(sin, name="sin_position_embedding")
+    embed_w = ypk.attach_input(weights["embed"], name="embed_tokens")
+
+    def tmp(name, cols, dt=core.bfloat16, shared=False):
+        return ypk.new_tensor(dims=(MT, cols), dtype=dt, name=name,
+                              io_category="nvshmem_tensor" if shared and world_size > 1 else "cuda_tensor")
+
+    embed_out = tmp("embed_out", h)
+    rmsnorm_out = tmp("rmsnorm_out", h)
+    attn_in = tmp("attn_in", (hq + 2 * hkv) * d)
+    attn_out = tmp("attn_out", hq * d)
+    attn_proj_out = tmp("attn_proj_out", h, shared=True)
+    allreduce_buf = ypk.new_tensor(dims=(world_size, MT, h), dtype=core.bfloat16,
+                                   name="all_reduce_buf",
+                                   io_category="nvshmem_tensor" if world_size > 1 else "cuda_tensor")
+    attn_allreduce_out = tmp("attn_allreduce_out", h, shared=True)
+    mlp_mid = tmp("mlp_mid", 2 * inter)
+    silu_mul_out = tmp("silu_mul_out", inter)
+    mlp_out = tmp("mlp_out", h, shared=True)
+    mlp_final = tmp("mlp_final", h, shared=True)
+    argmax_in = tmp("argmax_in", vpad)
+    argmax_part_value = tmp("argmax_part_value", num_workers)
+    argmax_part_index = tmp("argmax_part_index", num_workers, dt=core.int64)
+    argmax_out = ypk.attach_input(meta["output_tokens"], name="output_token")
+
+    ypk.embed_layer(input=x_tok, weight=embed_w, output=embed_out, grid_dim=(1, 1, 1),
+                    block_dim=(128, 1, 1), input_source=1)
+    x = embed_out
+    for li, L in enumerate(weights["layers"]):
+        w_norm = ypk.attach_input(L["input_norm"], name=f"layer_{li}_input_layernorm")
+        w_q = ypk.attach_input(L["q"], name=f"layer_{li}_q_proj")
+        w_k = ypk.attach_input(L["k"], name=f"layer_{li}_k_proj")
+        w_v = ypk.attach_input(L["v"], name=f"layer_{li}_v_proj")
+        w_qkv = ypk.shuffle_tensors(inputs=[w_q, w_k, w_v], shuffled_dim=0, num_groups=hkv,
+                                    name=f"layer_{li}_qkv_proj")
+        ypk.rmsnorm_layer(input=x, weight=w_norm, output=rmsnorm_out, grid_dim=(MT, 1, 1),
+                          block_dim=(128, 1, 1))
+        ypk.linear_layer(input=rmsnorm_out, weight=w_qkv, output=attn_in, grid_dim=(96, 1, 1),
+                         block_dim=(128, 1, 1))
+        kc = ypk.attach_input(k_cache[li], name=f"layer_{li}_k_cache")
+        vc = ypk.attach_input(v_cache[li], name=f"layer_{li}_v_cache")
+        ypk.paged_attention_layer(input=attn_in, k_cache=kc, v_cache=vc, q_norm=None, k_norm=None,
+                                  cos_pos_embed=cos_t, sin_pos_embed=sin_t, output=attn_out,
+                                  grid_dim=(MR, hkv, 1), block_dim=(128, 1, 1))
+        w_o = ypk.attach_input(L["o"], name=f"layer_{li}_o_proj")
+        ypk.linear_with_residual_layer(input=attn_out, weight=w_o, residual=x, output=attn_proj_out,
+                                       grid_dim=(h // 64, 1, 1), block_dim=(128, 1, 1))
+        x = attn_proj_out
+        if world_size > 1:
+            ypk.allreduce_layer(input=attn_proj_out, buffer=allreduce_buf, output=attn_allreduce_out,
+                                grid_dim=(h // 64, 1, 1), block_dim=(128, 1, 1))
+            x = attn_allreduce_out
+        w_norm2 = ypk.attach_input(L["post_norm"], name=f"layer_{li}_post_attn_layernorm")
+        w_gate = ypk.attach_input(L["gate"], name=f"layer_{li}_gate_proj")
+        w_up = ypk.attach_input(L["up"], name=f"layer_{li}_up_proj")
+        groups = _gate_up_groups(inter)
+        w_gu = ypk.shuffle_tensors(inputs=[w_gate, w_up], shuffled_dim=0, num_groups=groups,
+                                   name=f"layer_{li}_gatedup_proj")
+        ypk.rmsnorm_layer(input=x, weight=w_norm2, output=rmsnorm_out, grid_dim=(MT, 1, 1),
+                          block_dim=(128, 1, 1))
+        ypk.linear_layer(input=rmsnorm_out, weight=w_gu, output=mlp_mid,
+                         grid_dim=(2 * groups, 1, 1), block_dim=(128, 1, 1))
+        ypk.silu_mul_layer(input=mlp_mid, output=silu_mul_out, grid_dim=(groups, 1, 1),
+                           block_dim=(128, 1, 1))
+        w_down = ypk.attach_input(L["down"], name=f"layer_{li}_down_proj")
+        ypk.linear_with_residual_layer(input=silu_mul_out, weight=w_down, residual=x,
+                                       output=mlp_out, grid_dim=(h // 64, 1, 1),
+                                       block_dim=(128, 1, 1))
+        x = mlp_out
+        if world_size > 1:
+            ypk.allreduce_layer(input=mlp_out, buffer=allreduce_buf, output=mlp_final,
+                                grid_dim=(h // 64, 1, 1), block_dim=(128, 1, 1))
+            x = mlp_final
+    w_fn = ypk.attach_input(weights["final_norm"], name="model_norm_weight")
+    w_lm = ypk.attach_input(lm_head, name="lm_head")
+    ypk.rmsnorm_layer(input=x, weight=w_fn, output=rmsnorm_out, grid_dim=(MT, 1, 1),
+                      block_dim=(128, 1, 1))
+    ypk.linear_layer(input=rmsnorm_out, weight=w_lm, output=argmax_in,
+                     grid_dim=(vpad // 256, 1, 1), block_dim=(128, 1, 1))
+    ypk.argmax_partial_layer(input=argmax_in, output=(argmax_part_value, argmax_part_index),
+                             grid_dim=(num_workers, 1, 1), block_dim=(128, 1, 1))
+    ypk.argmax_reduce_layer(input=(argmax_part_value, argmax_part_index), output=argmax_out,
+                            grid_dim=(1, 1, 1), block_dim=(128, 1, 1))
+    state = {"meta": meta, "k_cache": k_cache, "v_cache": v_cache, "cos": cos, "sin": sin,
+             "lm_head": lm_head, "tensors": {"argmax_in": argmax_in, "attn_out": attn_out}}
+    if compile:
+        ypk.compile(dry_run=dry_run)
+    return ypk, state

@@ -1,0 +1,570 @@
+"""Host-side task-graph generation for the persistent megakernel.
+
+Takes the operators registered through the PersistentKernel layer builders and produces
+what the C ABI's ypk_load_graph wants: a task table in dependency order, one event per
+operator, and a per-worker queue.  This is the counterpart of the reference's
+Graph::generate_task_graph (src/kernel/runtime.cc:53-600,1416-1449) and of the shape
+derivation in src/kernel/task_register.cc, with three differences that come from the
+B200 design:
+
+  * operators are fused before tasks are cut: rmsnorm -> linear becomes one LINEAR task
+    with the norm folded in, linear(gate|up) -> silu_mul becomes a LINEAR task with the
+    SiLU*mul epilogue (so mlp_mid and rmsnorm_out are never written);
+  * the reference cuts an operator into grid_dim tasks and lets scheduler warps deal them
+    round-robin at run time; here grid_dim is a hint: every linear operator is cut into
+    one contiguous row slab per worker CTA, sized so that the *cumulative* weight bytes
+    per worker stay level across operators, and the queues are fixed ahead of time;
+  * dependencies are whole-operator events (every task of operator i waits for all tasks
+    of operator i-1), which is what the reference's chain of consecutive operators
+    degenerates to for these graphs (runtime.cc:446-503).
+
+Nothing here touches the GPU; it is plain Python and is unit-tested on CPU.
+"""
+import json
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+from . import _native as N
+from .core import DTensor, bfloat16, float16, float32, int32, int64
+
+MAX_TASK_ROWS = 256          # kMaxAccRows in device_common.cuh
+KV_TILE = 64
+HEAD_DIM = 128
+MAX_NEW_TOKENS = 8           # kMaxNewTokens
+ATTN_ROW_FLOATS = HEAD_DIM + 2
+MAX_SPLITS = 16
+
+
+@dataclass
+class RegisteredTask:
+    """What a layer builder recorded: reference task name, operands in TB-graph order,
+    launch hints and integer parameters."""
+    name: str
+    operands: List[Optional[DTensor]]
+    grid_dim: Tuple[int, int, int]
+    block_dim: Tuple[int, int, int]
+    params: List[int] = field(default_factory=list)
+    attrs: dict = field(default_factory=dict)
+
+
+@dataclass
+class FusedOp:
+    kind: str                       # embed | linear | attention | argmax_partial | ...
+    src: List[RegisteredTask]
+    t: Dict[str, Optional[DTensor]]  # named operands
+    flags: int = 0
+    attrs: dict = field(default_factory=dict)
+
+
+@dataclass
+class TaskSpec:
+    type: int
+    flags: int = 0
+    op_id: int = 0
+    ptr: List[Optional[Tuple[DTensor, int]]] = field(default_factory=lambda: [None] * N.NPTR)
+    iarg: List[int] = field(default_factory=lambda: [0] * N.NINT)
+    farg: List[float] = field(default_factory=lambda: [0.0] * N.NFLT)
+    dep_event: int = -1
+    dep_count: int = 0
+    trig_event: int = -1
+    worker: int = 0
+    weight_bytes: int = 0
+
+
+@dataclass
+class LoweredGraph:
+    ops: List[FusedOp]
+    tasks: List[TaskSpec]
+    num_events: int
+    queue: List[int]
+    queue_off: List[int]
+    shuffles: List[dict]            # {dst, sources, rows, gran, row_bytes}
+    internal: List[DTensor]         # scratch tensors the runtime has to allocate
+    worker_bytes: List[int]         # weight bytes streamed per worker per iteration
+
+    @property
+    def num_tasks(self):
+        return len(self.tasks)
+
+
+_SUFFIXES = ("_sm100", "_hopper", "_swapAB", "_cutlass")
+
+
+def canonical_name(name: str) -> str:
+    """Strip the architecture suffixes the reference appends per compute capability
+    (persistent_kernel.py:372,604-609,822-833,981-1011)."""
+    changed = True
+    while changed:
+        changed = False
+        for s in _SUFFIXES:
+            if name.endswith(s):
+                name = name[: -len(s)]
+                changed = True
+    return name
+
+
+# ---------------------------------------------------------------------------- fusion
+def _reads(rt: RegisteredTask) -> List[DTensor]:
+    name = canonical_name(rt.name)
+    ops = rt.operands
+    n_out = {"argmax_partial": 2}.get(name, 1)
+    return [t for t in ops[: len(ops) - n_out] if t is not None]
+
+
+def _writes(rt: RegisteredTask) -> List[DTensor]:
+    name = canonical_name(rt.name)
+    ops = rt.operands
+    n_out = {"argmax_partial": 2}.get(name, 1)
+    return [t for t in ops[len(ops) - n_out:] if t is not None]
+
+
+def _dead_after(regs: List[RegisteredTask], start: int, t: DTensor) -> bool:
+    """True if nothing from regs[start:] reads `t` before it is written again."""
+    for rt in regs[start:]:
+        if any(x is t for x in _reads(rt)):
+            return False
+        if any(x is t for x in _writes(rt)):
+            return True
+    return True
+
+
+def fuse(regs: List[RegisteredTask], default_eps: float) -> List[FusedOp]:
+    out: List[FusedOp] = []
+    i = 0
+    n = len(regs)
+    while i < n:
+        rt = regs[i]
+        name = canonical_name(rt.name)
+        if name == "embedding":
+            ids, table, o = rt.operands
+            out.append(FusedOp("embed", [rt], {"ids": ids, "table": table, "out": o}))
+            i += 1
+        elif name in ("rmsnorm", "linear", "linear_with_residual"):
+            norm_rt = None
+            j = i
+            if name == "rmsnorm":
+                x, nw, y = rt.operands
+                nxt = regs[i + 1] if i + 1 < n else None
+                if (nxt is not None and canonical_name(nxt.name) in ("linear", "linear_with_residual")
+                        and nxt.operands[0] is y and _dead_after(regs, i + 2, y)):
+                    norm_rt = rt
+                    j = i + 1
+                else:
+                    out.append(FusedOp("rmsnorm", [rt], {"x": x, "w": nw, "out": y},
+                                       attrs={"eps": rt.attrs.get("eps", default_eps)}))
+                    i += 1
+                    continue
+            lin = regs[j]
+            lname = canonical_name(lin.name)
+            if lname == "linear":
+                xin, w, y = lin.operands
+                res = None
+            else:
+                xin, w, res, y = lin.operands
+            flags = 0
+            t = {"x": xin, "w": w, "out": y, "norm_w": None, "res": res}
+            attrs = {"eps": default_eps}
+            srcs = [lin]
+            if norm_rt is not None:
+                t["x"] = norm_rt.operands[0]
+                t["norm_w"] = norm_rt.operands[1]
+                flags |= N.F_NORM
+                attrs["eps"] = norm_rt.attrs.get("eps", default_eps)
+                srcs = [norm_rt, lin]
+            if res is not None:
+                flags |= N.F_RESIDUAL
+            k = j + 1
+            nxt = regs[k] if k < n else None
+            if (res is None and nxt is not None and canonical_name(nxt.name) == "silu_mul"
+                    and nxt.operands[0] is y and w.kind == "shuffled" and len(w.sources) == 2
+                    and w.sources[0].dims == w.sources[1].dims
+                    and w.sources[0].dims[0] % 8 == 0 and _dead_after(regs, k + 1, y)):
+                flags |= N.F_SILU_MUL
+                t["out"] = nxt.operands[1]
+                srcs.append(nxt)
+                k += 1
+            out.append(FusedOp("linear", srcs, t, flags, attrs))
+            i = k
+        elif name == "paged_attention":
+            qkv, kc, vc, qn, kn, cos, sin, o = rt.operands
+            if qn is not None or kn is not None:
+                raise NotImplementedError("q/k RMSNorm inside attention (Qwen3) is not built yet")
+            flags = N.F_ROPE if (cos is not None and sin is not None) else 0
+            out.append(FusedOp("attention", [rt], {"qkv": qkv, "k_cache": kc, "v_cache": vc,
+                                                    "cos": cos, "sin": sin, "out": o}, flags,
+                               {"num_q_heads": rt.params[0], "num_kv_heads": rt.params[1]}))
+            i += 1
+        elif name == "silu_mul":
+            x, o = rt.operands
+            out.append(FusedOp("silu_mul", [rt], {"in": x, "out": o},
+                               attrs={"groups": rt.grid_dim[0]}))
+            i += 1
+        elif name == "argmax_partial":
+            x, pv, pi = rt.operands
+            out.append(FusedOp("argmax_partial", [rt], {"in": x, "val": pv, "idx": pi},
+                               attrs={"nparts": rt.grid_dim[0]}))
+            i += 1
+        elif name == "argmax_reduce":
+            pv, pi, o = rt.operands
+            out.append(FusedOp("argmax_reduce", [rt], {"val": pv, "idx": pi, "out": o}))
+            i += 1
+        elif name == "allreduce":
+            x, buf, o = rt.operands
+            out.append(FusedOp("allreduce", [rt], {"in": x, "buf": buf, "out": o},
+                               attrs={"world": rt.params[0], "rank": rt.params[1]}))
+            i += 1
+        else:
+            raise NotImplementedError(f"task '{rt.name}' is outside the decode hot path")
+    return out
+
+
+# ------------------------------------------------------------------------- balancing
+def level_partition(n_units: int, unit_bytes: int, loads: List[float]) -> List[int]:
+    """Split n_units equal units over the workers so that load[i] + count[i]*unit_bytes is
+    as level as possible (water-filling).  Returns the count per worker."""
+    W = len(loads)
+    if n_units <= 0:
+        return [0] * W
+    lo, hi = min(loads), max(loads) + float(n_units) * unit_bytes
+    for _ in range(60):
+        mid = 0.5 * (lo + hi)
+        got = sum(max(0.0, (mid - l) / unit_bytes) for l in loads)
+        if got < n_units:
+            lo = mid
+        else:
+            hi = mid
+    ideal = [max(0.0, (hi - l) / unit_bytes) for l in loads]
+    counts = [int(math.floor(x)) for x in ideal]
+    rem = n_units - sum(counts)
+    order = sorted(range(W), key=lambda i: (ideal[i] - counts[i]), reverse=True)
+    k = 0
+    while rem > 0:
+        counts[order[k % W]] += 1
+        rem -= 1
+        k += 1
+    while rem < 0:  # floor can only undershoot, but keep the invariant explicit
+        idx = max(range(W), key=lambda i: counts[i])
+        counts[idx] -= 1
+        rem += 1
+    assert sum(counts) == n_units and min(counts) >= 0
+    return counts
+
+
+# --------------------------------------------------------------------------- lowering
+def _is16(t: DTensor):
+    return t.dtype in (bfloat16, float16)
+
+
+def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_requests: int,
+          max_seq_length: int, page_size: int, world_size: int = 1, rank: int = 0,
+          default_eps: float = 1e-6, new_tensor=None) -> LoweredGraph:
+    """Fuse, cut into tasks, assign to workers.  `new_tensor(dims, dtype, name)` creates
+    runtime-owned scratch tensors (attention split partials and arrival counters)."""
+    ops = fuse(regs, default_eps)
+    W = num_workers
+    loads = [0.0] * W
+    tasks: List[TaskSpec] = []
+    shuffles: List[dict] = []
+    internal: List[DTensor] = []
+    shuffled_done: Dict[int, dict] = {}
+    rr = 0  # rotating start for round-robin placed tasks
+
+    def scratch(dims, dt, name):
+        if new_tensor is None:
+            raise RuntimeError("lowering needs a tensor factory for scratch buffers")
+        t = new_tensor(dims, dt, name)
+        internal.append(t)
+        return t
+
+    attn_scratch = None
+    attn_counters = None
+    prev_event, prev_count = -1, 0
+
+    for oi, op in enumerate(ops):
+        first = len(tasks)
+        ev = oi
+        if op.kind == "embed":
+            ids, table, o = op.t["ids"], op.t["table"], op.t["out"]
+            hidden = table.dims[1]
+            if hidden % 8:
+                raise ValueError("embedding width must be a multiple of 8")
+            ntask = max(1, min(8, hidden // 1024))
+            cols = hidden // ntask // 8 * 8
+            c = 0
+            for k in range(ntask):
+                nc = cols if k < ntask - 1 else hidden - c
+                ts = TaskSpec(N.TASK_EMBED, op_id=oi)
+                ts.ptr[0], ts.ptr[1], ts.ptr[2] = (ids, 0), (table, 0), (o, 0)
+                ts.iarg[:5] = [hidden, c, nc, table.dims[1], o.dims[1]]
+                ts.worker = (rr + k) % W
+                tasks.append(ts)
+                c += nc
+            rr += ntask
+        elif op.kind == "linear":
+            x, w, o = op.t["x"], op.t["w"], op.t["out"]
+            nw, res = op.t["norm_w"], op.t["res"]
+            if not (_is16(x) and x.dtype == w.dtype == o.dtype):
+                raise ValueError("linear operands must share a 16-bit float type")
+            K = w.dims[1]
+            if x.dims[1] != K:
+                raise ValueError(f"linear: input width {x.dims[1]} != weight K {K}")
+            if K % 64:
+                raise NotImplementedError(f"linear needs K % 64 == 0 (got {K})")
+            Nrows = w.dims[0]
+            silu = bool(op.flags & N.F_SILU_MUL)
+            flags = op.flags | (N.F_F16 if x.dtype == float16 else 0)
+            if (flags & N.F_RESIDUAL) and world_size > 1 and rank != 0:
+                # partial sums are added across ranks afterwards: the residual goes in once
+                flags &= ~N.F_RESIDUAL
+            gran = 16 if silu else 1
+            if w.kind == "shuffled" and id(w) not in shuffled_done:
+                srcs = w.sources
+                if silu:
+                    g = [8, 8]
+                else:
+                    if any(s.dims[0] % w.num_groups for s in srcs):
+                        raise ValueError("shuffle_tensors: rows not divisible by num_groups")
+                    g = [s.dims[0] // w.num_groups for s in srcs]
+                sh = {"dst": w, "sources": list(srcs), "rows": [s.dims[0] for s in srcs],
+                      "gran": g, "row_bytes": K * w.dtype.itemsize}
+                shuffles.append(sh)
+                shuffled_done[id(w)] = sh
+            elif w.kind == "shuffled" and silu and shuffled_done[id(w)]["gran"] != [8, 8]:
+                raise ValueError("a shuffled weight is used both fused and unfused")
+            expect_out = Nrows // 2 if silu else Nrows
+            if o.dims[1] < expect_out:
+                raise ValueError(f"linear: output width {o.dims[1]} < {expect_out}")
+            units = Nrows // gran
+            if Nrows % gran:
+                raise ValueError("fused gate/up weight rows must be a multiple of 16")
+            unit_bytes = gran * K * 2
+            counts = level_partition(units, unit_bytes, loads)
+            r = 0
+            for wk in range(W):
+                nrows = counts[wk] * gran
+                loads[wk] += counts[wk] * unit_bytes
+                while nrows > 0:
+                    take = min(nrows, MAX_TASK_ROWS)
+                    ts = TaskSpec(N.TASK_LINEAR, flags=flags, op_id=oi)
+                    ts.ptr[0], ts.ptr[1], ts.ptr[2] = (x, 0), (w, 0), (o, 0)
+                    if nw is not None:
+                        ts.ptr[3] = (nw, 0)
+                    if flags & N.F_RESIDUAL:
+                        ts.ptr[4] = (res, 0)
+                    ts.iarg[:8] = [K, r, take, x.dims[1], w.dims[1], o.dims[1],
+                                   res.dims[1] if res is not None else 0, 0]
+                    ts.farg[0] = float(op.attrs.get("eps", default_eps))
+                    ts.worker = wk
+                    ts.weight_bytes = take * K * 2
+                    tasks.append(ts)
+                    r += take
+                    nrows -= take
+            assert r == Nrows
+        elif op.kind == "attention":
+            qkv, kc, vc, o = op.t["qkv"], op.t["k_cache"], op.t["v_cache"], op.t["out"]
+            hq, hkv = op.attrs["num_q_heads"], op.attrs["num_kv_heads"]
+            if kc.dims[3] != HEAD_DIM:
+                raise NotImplementedError("attention is built for head_dim 128")
+            if hq % hkv or hq // hkv > 8:
+                raise NotImplementedError("attention needs 1..8 q heads per kv head")
+            if page_size % KV_TILE:
+                raise NotImplementedError(f"attention needs page_size % {KV_TILE} == 0")
+            G = hq // hkv
+            if qkv.dims[1] != hkv * (G + 2) * HEAD_DIM:
+                raise ValueError("packed qkv width does not match the head counts")
+            max_tiles = (max_seq_length + KV_TILE - 1) // KV_TILE
+            nsplit = max(1, min(W // max(1, max_requests * hkv), max_tiles, MAX_SPLITS))
+            max_rows = G * MAX_NEW_TOKENS
+            if nsplit > 1:
+                need = max_requests * hkv * nsplit * max_rows * ATTN_ROW_FLOATS
+                if attn_scratch is None or attn_scratch.dims[0] < need:
+                    attn_scratch = scratch((need,), float32, "attn_split_scratch")
+                    attn_counters = scratch((max_requests * hkv,), int32, "attn_split_counters")
+            k = 0
+            for r in range(max_requests):
+                for h in range(hkv):
+                    for s in range(nsplit):
+                        ts = TaskSpec(N.TASK_ATTENTION, flags=op.flags, op_id=oi)
+                        ts.ptr[0], ts.ptr[1], ts.ptr[2], ts.ptr[3] = (qkv, 0), (kc, 0), (vc, 0), (o, 0)
+                        if op.flags & N.F_ROPE:
+                            ts.ptr[4], ts.ptr[5] = (op.t["cos"], 0), (op.t["sin"], 0)
+                        if nsplit > 1:
+                            ts.ptr[6], ts.ptr[7] = (attn_scratch, 0), (attn_counters, 0)
+                        ts.iarg[:9] = [r, h, s, nsplit, G, hkv, qkv.dims[1], o.dims[1], max_rows]
+                        # splits of one (request, head) go to different workers
+                        ts.worker = (rr + k) % W
+                        tasks.append(ts)
+                        k += 1
+            rr += k
+        elif op.kind == "argmax_partial":
+            x, pv, pi = op.t["in"], op.t["val"], op.t["idx"]
+            nparts = op.attrs["nparts"]
+            V = x.dims[1]
+            if V % nparts:
+                raise ValueError("argmax_partial: vocabulary not divisible by the task count")
+            if pv.dims[1] < nparts or pi.dims[1] < nparts:
+                raise ValueError("argmax_partial: partial buffers narrower than the task count")
+            per = V // nparts
+            for p in range(nparts):
+                ts = TaskSpec(N.TASK_ARGMAX_PARTIAL, op_id=oi)
+                ts.ptr[0], ts.ptr[1], ts.ptr[2] = (x, 0), (pv, 0), (pi, 0)
+                ts.iarg[:5] = [p * per, per, x.dims[1], p, pv.dims[1]]
+                ts.worker = (rr + p) % W
+                tasks.append(ts)
+            rr += nparts
+            op.attrs["ld_parts"] = pv.dims[1]
+        elif op.kind == "argmax_reduce":
+            pv, pi, o = op.t["val"], op.t["idx"], op.t["out"]
+            # only the first `nparts` columns of the partial buffers were written
+            nparts = None
+            for prev in reversed(ops[:oi]):
+                if prev.kind == "argmax_partial" and prev.t["val"] is pv:
+                    nparts = prev.attrs["nparts"]
+                    break
+            if nparts is None or nparts != pv.dims[1]:
+                if nparts is None:
+                    nparts = pv.dims[1]
+                elif nparts != pv.dims[1]:
+                    raise NotImplementedError(
+                        "argmax partial buffers must be exactly as wide as the task count")
+            ts = TaskSpec(N.TASK_ARGMAX_REDUCE, op_id=oi)
+            ts.ptr[0], ts.ptr[1], ts.ptr[2] = (pv, 0), (pi, 0), (o, 0)
+            ts.iarg[0] = nparts
+            ts.worker = 0
+            tasks.append(ts)
+        elif op.kind == "rmsnorm":
+            x, nw, o = op.t["x"], op.t["w"], op.t["out"]
+            ntask = min(max_tokens, W)
+            per = (max_tokens + ntask - 1) // ntask
+            for k in range(ntask):
+                ts = TaskSpec(N.TASK_RMSNORM, op_id=oi,
+                              flags=N.F_F16 if x.dtype == float16 else 0)
+                ts.ptr[0], ts.ptr[2] = (x, 0), (o, 0)
+                if nw is not None:
+                    ts.ptr[1] = (nw, 0)
+                ts.iarg[:5] = [x.dims[1], k * per, per, x.dims[1], o.dims[1]]
+                ts.farg[0] = float(op.attrs.get("eps", default_eps))
+                ts.worker = (rr + k) % W
+                tasks.append(ts)
+            rr += ntask
+        elif op.kind == "silu_mul":
+            x, o = op.t["in"], op.t["out"]
+            inter = o.dims[1]
+            groups = max(1, op.attrs.get("groups", 1))
+            if x.dims[1] != 2 * inter or inter % groups:
+                raise ValueError("silu_mul: input must be twice as wide as the output")
+            gs = inter // groups
+            ntask = min(W, groups)
+            per_groups = (groups + ntask - 1) // ntask
+            k = 0
+            g0 = 0
+            while g0 < groups:
+                ng = min(per_groups, groups - g0)
+                ts = TaskSpec(N.TASK_SILU_MUL, op_id=oi)
+                ts.ptr[0], ts.ptr[1] = (x, 0), (o, 0)
+                ts.iarg[:5] = [g0 * gs, ng * gs, gs, x.dims[1], o.dims[1]]
+                ts.worker = (rr + k) % W
+                tasks.append(ts)
+                g0 += ng
+                k += 1
+            rr += k
+        elif op.kind == "allreduce":
+            raise NotImplementedError("in-graph all-reduce is lowered by the tensor-parallel path")
+        else:
+            raise NotImplementedError(op.kind)
+        count = len(tasks) - first
+        for ts in tasks[first:]:
+            ts.trig_event = ev
+            ts.dep_event = prev_event
+            ts.dep_count = prev_count
+        prev_event, prev_count = ev, count
+
+    # queues: tasks of a worker in task (= operator) order
+    per_worker: List[List[int]] = [[] for _ in range(W)]
+    for ti, ts in enumerate(tasks):
+        per_worker[ts.worker].append(ti)
+    queue, queue_off = [], [0]
+    for wk in range(W):
+        queue.extend(per_worker[wk])
+        queue_off.append(len(queue))
+    worker_bytes = [0] * W
+    for ts in tasks:
+        worker_bytes[ts.worker] += ts.weight_bytes
+    return LoweredGraph(ops, tasks, len(ops), queue, queue_off, shuffles, internal, worker_bytes)
+
+
+# ------------------------------------------------------------------------- simulation
+def simulate(g: LoweredGraph, iterations: int = 2):
+    """Host model of the device protocol (the reference's sanity_check, runtime.cc:540-600):
+    workers run their queues in order, a task may start once its dependency counter has
+    reached dep_count * iteration.  Returns the number of executions per task; raises if
+    the graph deadlocks."""
+    ntask = len(g.tasks)
+    counters = [0] * g.num_events
+    executed = [0] * ntask
+    for it in range(1, iterations + 1):
+        heads = [g.queue_off[w] for w in range(len(g.queue_off) - 1)]
+        remaining = ntask
+        while remaining:
+            progressed = False
+            for w in range(len(heads)):
+                while heads[w] < g.queue_off[w + 1]:
+                    ts = g.tasks[g.queue[heads[w]]]
+                    if ts.dep_event >= 0 and counters[ts.dep_event] < ts.dep_count * it:
+                        break
+                    if ts.trig_event >= 0:
+                        counters[ts.trig_event] += 1
+                    executed[g.queue[heads[w]]] += 1
+                    heads[w] += 1
+                    remaining -= 1
+                    progressed = True
+            if not progressed:
+                raise RuntimeError(f"task graph deadlocks in iteration {it}")
+    return executed
+
+
+# ------------------------------------------------------------------------------- JSON
+_REF_TASK_TYPE = {  # TaskType numbers of the reference (runtime_header.h:62-124)
+    N.TASK_EMBED: 101, N.TASK_LINEAR: 253, N.TASK_ATTENTION: 257, N.TASK_ARGMAX_PARTIAL: 259,
+    N.TASK_ARGMAX_REDUCE: 258, N.TASK_RMSNORM: 154, N.TASK_SILU_MUL: 118, N.TASK_ALLREDUCE: 199,
+}
+
+
+def to_json(g: LoweredGraph) -> str:
+    """Task graph in the layout of the reference's task_graph.json (runtime.cc:847-1318):
+    all_tasks / all_events / first_tasks, operands named by the name given at
+    attach_input / new_tensor, offsets in bytes."""
+    def operand(ref):
+        if ref is None:
+            return {"base_ptr": "nullptr", "offset": 0, "dims": [], "strides": [], "data_type": 999}
+        t, off = ref
+        return {"base_ptr": t.name or f"tensor_{t.guid}", "offset": off, "dims": list(t.dims),
+                "strides": list(t.strides), "data_type": t.dtype.code}
+
+    tasks = []
+    for ti, ts in enumerate(g.tasks):
+        tasks.append({
+            "task_type": _REF_TASK_TYPE.get(ts.type, ts.type),
+            "ypk_task_type": N.TASK_NAMES[ts.type],
+            "variant_id": ts.flags,
+            "inputs": [operand(p) for p in ts.ptr if p is not None],
+            "outputs": [],
+            "trigger_event": ts.trig_event,
+            "dependent_event": ts.dep_event,
+            "dependent_count": ts.dep_count,
+            "worker": ts.worker,
+            "op_id": ts.op_id,
+            "iarg": list(ts.iarg),
+            "request_id": ts.iarg[0] if ts.type == N.TASK_ATTENTION else -1,
+        })
+    events = []
+    for e in range(g.num_events):
+        ids = [i for i, ts in enumerate(g.tasks) if ts.dep_event == e]
+        events.append({"event_type": 902,  # EVENT_EMPTY: consumers poll the counter
+                       "num_triggers": sum(1 for ts in g.tasks if ts.trig_event == e),
+                       "first_task_id": ids[0] if ids else 0,
+                       "last_task_id": ids[-1] + 1 if ids else 0})
+    first = [i for i, ts in enumerate(g.tasks) if ts.dep_event < 0]
+    return json.dumps({"all_tasks": tasks, "all_events": events, "first_tasks": first,
+                       "queues": {"queue": g.queue, "queue_off": g.queue_off}})
