@@ -164,8 +164,9 @@ __device__ __forceinline__ void attn_tile(const char *ksm, const char *vsm, cons
   }
 }
 
-// Layout of one merged/partial row in shared or global scratch: 128 outputs, m, l.
-constexpr int kAttnRowFloats = kHeadDim + 2;
+// Layout of one merged/partial row in shared or global scratch: 128 outputs, m, l, and two
+// floats of padding so that every row starts on a 16-byte boundary (float4 stores).
+constexpr int kAttnRowFloats = kHeadDim + 4;
 
 template <int TM>
 __device__ __forceinline__ void attention_consume_t(WaitCtx &wc, char *smem, Misc *misc,

@@ -32,7 +32,7 @@ MAX_TASK_ROWS = 256          # kMaxAccRows in device_common.cuh
 KV_TILE = 64
 HEAD_DIM = 128
 MAX_NEW_TOKENS = 8           # kMaxNewTokens
-ATTN_ROW_FLOATS = HEAD_DIM + 2
+ATTN_ROW_FLOATS = HEAD_DIM + 4   # kAttnRowFloats in task_attention.cuh
 MAX_SPLITS = 16
 
 

@@ -9,6 +9,7 @@ grid_dim / block_dim arguments of the builders are accepted as hints only.
 """
 import ctypes as C
 import os
+import sys
 from typing import Optional
 
 import torch
@@ -447,8 +448,7 @@ class PersistentKernel:
         return self._handle.status()
 
     def __del__(self):
-        import sys
-        if sys.is_finalizing():
+        if sys is None or sys.is_finalizing():
             return
         try:
             if not self.__finalized__:
