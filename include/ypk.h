@@ -98,7 +98,8 @@ enum ypk_task_type {
  *                  ldtable, ldout}
  * ATTENTION: ptr = {qkv, k_cache, v_cache, out, cos, sin, scratch, counters}
  *          iarg = {request, kv_head, split, nsplit, q_per_kv, num_kv_heads,
- *                  ld_qkv, ld_out, max_rows}
+ *                  ld_qkv, ld_out, max_rows}; iarg[9], iarg[10] are filled in by
+ *                  ypk_load_graph (TMA tensor maps of the two caches)
  * ARGMAX_PARTIAL: ptr = {logits, part_val, part_idx}; iarg = {col0, ncols,
  *                  ldlogits, part, nparts}
  * ARGMAX_REDUCE: ptr = {part_val, part_idx, out(int64)}; iarg = {nparts}
@@ -147,7 +148,12 @@ typedef struct ypk_config {
   void *paged_kv_indptr;      /* int32 [max_num_batched_requests + 1]      */
   void *paged_kv_indices;     /* int32 [max_num_pages]                     */
   void *paged_kv_last_page_len; /* int32 [max_num_batched_requests]        */
-  void *profiler_buffer;      /* optional uint64 ring, may be NULL         */
+  void *profiler_buffer;      /* optional device buffer, may be NULL: 8 uint64 per
+                                 (worker, queue position), rewritten every iteration:
+                                 {iteration<<32 | task, t_fetch, t_dependency_met,
+                                 t_done, t_inputs_staged, t_last_stage, 0, 0} in
+                                 globaltimer ns; needs workers * longest queue * 64
+                                 bytes                                */
   uint64_t profiler_bytes;
 } ypk_config;
 

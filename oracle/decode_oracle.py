@@ -153,7 +153,8 @@ def allreduce_sum(partials: List[torch.Tensor], rounding="bf16"):
 class BatchState:
     """Host model of the on-device continuous batcher (persistent_kernel.cuh:107-132,
     169-322) with this build's two deliberate differences: paged_kv_last_page_len lies in
-    [1, page_size] and a request contributes at most 8 new tokens per iteration."""
+    [1, page_size] and a request contributes at most max_new_per_request new tokens per
+    iteration (8, or 32 // q-heads-per-kv-head if that is smaller)."""
     total_requests: int
     max_requests: int
     max_tokens: int

@@ -1,0 +1,146 @@
+"""Host logic of the task-graph generator: fusion, balanced row partition, events,
+queues, the protocol simulator, JSON export, and validation of a whole Llama graph by the
+native library on a host-only handle (no GPU)."""
+import json
+
+import pytest
+import torch
+
+import yirage_b200 as yr
+from yirage_b200 import _native as N
+from yirage_b200 import llama, lowering
+
+
+def small_graph(world_size=1, rank=0, layers=2):
+    shape = llama.LlamaShape(hidden_size=512, intermediate_size=1024, num_hidden_layers=layers,
+                             num_attention_heads=8, num_key_value_heads=2, vocab_size=2048)
+    w = llama.init_weights(shape, "cpu", 0)
+    tokens = torch.zeros(2, 128, dtype=torch.int64)
+    pl = torch.tensor([5, 7], dtype=torch.int32)
+    return shape, llama.build_decode_kernel(
+        shape, w, tokens=tokens, prompt_lengths=pl, max_num_batched_requests=2,
+        max_num_batched_tokens=8, max_num_pages=8, page_size=64, compile=False)[0]
+
+
+def test_demo_layer_sequence_fuses_to_five_operators_per_layer():
+    _, ypk = small_graph()
+    g = ypk.lower(148)
+    kinds = [o.kind for o in g.ops]
+    assert kinds == ["embed"] + ["linear", "attention", "linear", "linear", "linear"] * 2 + \
+        ["linear", "argmax_partial", "argmax_reduce"]
+    qkv, o_proj, gate_up, down = g.ops[1], g.ops[3], g.ops[4], g.ops[5]
+    assert qkv.flags & N.F_NORM and not qkv.flags & N.F_RESIDUAL
+    assert o_proj.flags & N.F_RESIDUAL and not o_proj.flags & N.F_NORM
+    assert gate_up.flags & N.F_NORM and gate_up.flags & N.F_SILU_MUL
+    assert gate_up.t["out"].name == "silu_mul_out", "mlp_mid must not be materialised"
+    assert down.flags & N.F_RESIDUAL
+    # fused gate/up weights are interleaved in 8-row granules, qkv per kv head
+    gran = {sh["dst"].name: sh["gran"] for sh in g.shuffles}
+    assert gran["layer_0_gatedup_proj"] == [8, 8]
+    assert gran["layer_0_qkv_proj"] == [4 * 128, 128, 128]
+
+
+def test_every_task_runs_once_per_iteration_and_graph_cannot_deadlock():
+    _, ypk = small_graph()
+    g = ypk.lower(148)
+    assert set(lowering.simulate(g, iterations=3)) == {3}
+    # whole-operator events: the dependency count equals the producer's task count
+    per_op = {}
+    for ts in g.tasks:
+        per_op[ts.op_id] = per_op.get(ts.op_id, 0) + 1
+    for ts in g.tasks:
+        if ts.op_id == 0:
+            assert ts.dep_event == -1
+        else:
+            assert ts.dep_event == ts.op_id - 1 and ts.dep_count == per_op[ts.op_id - 1]
+    # queues are in task order
+    for a, b in zip(g.queue_off[:-1], g.queue_off[1:]):
+        assert g.queue[a:b] == sorted(g.queue[a:b])
+
+
+def test_a_broken_dependency_is_caught_by_the_simulator():
+    _, ypk = small_graph()
+    g = ypk.lower(148)
+    g.tasks[-1].dep_count += 1          # waits for a trigger nobody sends
+    with pytest.raises(RuntimeError, match="deadlock"):
+        lowering.simulate(g, iterations=1)
+
+
+def test_weight_rows_are_covered_exactly_once_and_bytes_are_level():
+    shape, ypk = small_graph()
+    g = ypk.lower(148)
+    for oi, op in enumerate(g.ops):
+        if op.kind != "linear":
+            continue
+        rows = sorted((ts.iarg[1], ts.iarg[2]) for ts in g.tasks if ts.op_id == oi)
+        pos = 0
+        for r0, n in rows:
+            assert r0 == pos and 0 < n <= lowering.MAX_TASK_ROWS
+            pos += n
+        assert pos == op.t["w"].dims[0]
+    total = shape.decode_weight_bytes(1, llama.padded_vocab(shape.vocab_size))
+    assert sum(g.worker_bytes) == total
+    assert max(g.worker_bytes) - min(g.worker_bytes) <= 2 * 16 * 1024 * 2  # two granules of the widest K
+
+
+def test_level_partition_water_fills():
+    counts = lowering.level_partition(10, 100, [0.0, 300.0, 0.0, 0.0])
+    assert sum(counts) == 10 and counts[1] <= 2 and max(counts) - min(c for i, c in enumerate(counts) if i != 1) <= 1
+    assert lowering.level_partition(0, 10, [0.0, 0.0]) == [0, 0]
+    assert sum(lowering.level_partition(7, 5, [1e9, 0.0, 0.0])) == 7
+
+
+def test_unfusable_patterns_stay_separate():
+    ypk = yr.PersistentKernel(mode="onepass", world_size=1, mpi_rank=0, num_workers=128,
+                              num_local_schedulers=0, num_remote_schedulers=0, max_seq_length=64,
+                              max_num_batched_requests=1, max_num_batched_tokens=8, max_num_pages=1,
+                              page_size=64, eos_token_id=-1, meta_tensors={})
+    x = ypk.attach_input(torch.zeros(8, 512, dtype=torch.bfloat16), "x")
+    nw = ypk.attach_input(torch.zeros(512, dtype=torch.bfloat16), "nw")
+    w1 = ypk.attach_input(torch.zeros(256, 512, dtype=torch.bfloat16), "w1")
+    w2 = ypk.attach_input(torch.zeros(256, 512, dtype=torch.bfloat16), "w2")
+    normed = ypk.new_tensor(dims=(8, 512), name="normed")
+    o1, o2 = ypk.new_tensor(dims=(8, 256), name="o1"), ypk.new_tensor(dims=(8, 256), name="o2")
+    ypk.rmsnorm_layer(x, nw, normed, (8, 1, 1), (128, 1, 1))
+    ypk.linear_layer(normed, w1, o1, (4, 1, 1), (128, 1, 1))
+    ypk.linear_layer(normed, w2, o2, (4, 1, 1), (128, 1, 1))   # second reader of `normed`
+    assert [o.kind for o in ypk.lower(148).ops] == ["rmsnorm", "linear", "linear"]
+
+
+def test_out_of_scope_builders_say_so():
+    _, ypk = small_graph()
+    with pytest.raises(NotImplementedError):
+        ypk.moe_topk_softmax_routing_layer()
+    with pytest.raises(NotImplementedError):
+        yr.PersistentKernel(mode="online", world_size=1, mpi_rank=0, num_workers=1,
+                            num_local_schedulers=0, num_remote_schedulers=0, max_seq_length=1,
+                            max_num_batched_requests=1, max_num_batched_tokens=1, max_num_pages=1,
+                            page_size=64, eos_token_id=0, meta_tensors={})
+
+
+def test_task_graph_json_follows_the_reference_layout():
+    _, ypk = small_graph()
+    res = ypk.kn_graph.generate_task_graph(num_gpus=1, my_gpu_id=0)
+    assert set(res) == {"json_file", "cuda_code"}
+    j = json.loads(res["json_file"])
+    assert {"all_tasks", "all_events", "first_tasks"} <= set(j)
+    t = j["all_tasks"][10]
+    assert {"task_type", "variant_id", "inputs", "outputs", "trigger_event", "dependent_event"} <= set(t)
+    assert t["inputs"][0]["base_ptr"] and t["inputs"][0]["data_type"] in (940, 941, 955, 965)
+    assert sum(e["num_triggers"] for e in j["all_events"]) == len(j["all_tasks"])
+
+
+def test_native_library_accepts_the_lowered_llama_graph(native_lib):
+    _, ypk = small_graph()
+    ypk.compile(dry_run=True)          # host-only handle: bind, shuffle, validate, resolve
+    with pytest.raises(RuntimeError):
+        ypk()                          # no device, no launch - and no silent fallback
+    ypk.finalize()
+
+
+def test_compile_without_a_gpu_fails_loudly():
+    if torch.cuda.is_available():
+        pytest.skip("needs a machine without a GPU")
+    _, ypk = small_graph()
+    with pytest.raises(RuntimeError, match="no CPU execution path"):
+        ypk.compile()

@@ -24,32 +24,40 @@ constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kBlockThreads = kConsumerThreads + 32;  // + producer warp
 constexpr int kProducerWarp = kConsumerWarps;
 
-constexpr int kStages = 4;
+constexpr int kStages = 5;
 constexpr int kStageBytes = 34816;               // 34 KB
-constexpr int kStageCols = 512;                  // weight columns per ring stage
-constexpr int kRowPitch = kStageCols * 2 + 16;   // 1040 B: odd multiple of 16 -> no bank conflicts
-constexpr int kRowBlock = 32;                    // weight rows per ring stage (one per lane)
-constexpr int kMaxBatch = 8;                     // tokens handled per pass of the GEMV
+// GEMV: a stage is 16 weight rows x 1024 columns, 2 KB per row
+constexpr int kStageCols = 1024;                 // weight columns per ring stage
+constexpr int kRowPitch = kStageCols * 2 + 16;   // 2064 B: 8 rows -> 8 distinct 16-byte bank groups
+constexpr int kRowBlock = 16;                    // weight rows per ring stage (M of the MMA)
+constexpr int kWarpCols = kStageCols / kConsumerWarps;  // 128 columns of every stage per warp
+constexpr int kMaxBatch = 8;                     // tokens per pass (N of the MMA)
 constexpr int kMaxAccRows = 256;                 // rows of one LINEAR task when K is chunked
 
 constexpr int kKvTile = 64;                      // cached tokens per ring stage
 constexpr int kHeadDim = 128;
-constexpr int kKPitch = kHeadDim * 2 + 16;       // 272 B per K row in shared memory
-constexpr int kVOffset = kKvTile * kKPitch;      // V tile follows the K tile
+constexpr int kKPitch = kHeadDim * 2 + 16;       // 272 B per row of the q / new-token tiles
+// A cached K/V stage is four TMA boxes of 64 tokens x 64 dims (128 B rows, 128-byte
+// swizzle): K dims 0..63, K dims 64..127, V dims 0..63, V dims 64..127.
+constexpr int kKvBoxBytes = kKvTile * 128;       // 8192
+constexpr int kVOffset = 2 * kKvBoxBytes;        // V boxes follow the K boxes
 constexpr int kMaxNewTokens = 8;                 // new tokens of one request per iteration
+constexpr int kMaxAttnRows = 32;                 // new tokens x q heads per kv head, per task
 
 // Shared-memory map (dynamic shared memory, bytes).
 constexpr int kOffRing = 0;
-constexpr int kOffXs = kOffRing + kStages * kStageBytes;   // 139264
-constexpr int kXsBytes = 65536;
-constexpr int kOffPart = kOffXs + kXsBytes;                // 204800
-constexpr int kPartBytes = 2 * kConsumerWarps * kRowBlock * kMaxBatch * 4;  // 16384
-constexpr int kOffAcc = kOffPart + kPartBytes;             // 221184
+constexpr int kOffXs = kOffRing + kStages * kStageBytes;   // 174080
+constexpr int kXsBytes = 36864;                            // activations of a pass, 16-bit
+constexpr int kOffPart = kOffXs + kXsBytes;                // 210944
+constexpr int kPartBytes = 2 * kConsumerWarps * kRowBlock * kMaxBatch * 4;  // 8192
+constexpr int kOffRes = kOffPart + kPartBytes;             // 219136
+constexpr int kResBytes = kMaxAccRows * kMaxBatch * 2;     // 4096: residual slice of a task
+constexpr int kOffAcc = kOffRes + kResBytes;               // 223232
 constexpr int kAccBytes = kMaxAccRows * kMaxBatch * 4;     // 8192
-constexpr int kOffMisc = kOffAcc + kAccBytes;              // 229376
+constexpr int kOffMisc = kOffAcc + kAccBytes;              // 231424
 constexpr int kMiscBytes = 1024;
-constexpr int kSmemBytes = kOffMisc + kMiscBytes;          // 230400 <= 232448
-constexpr int kScratchSmemBytes = kXsBytes + kPartBytes + kAccBytes;  // 90112, contiguous from kOffXs
+constexpr int kSmemBytes = kOffMisc + kMiscBytes;          // 232448 = 227 KB, the per-CTA maximum
+constexpr int kScratchSmemBytes = kXsBytes + kPartBytes + kResBytes + kAccBytes;  // 57344 from kOffXs
 
 // Layout of the misc area.
 struct __align__(16) Misc {
@@ -58,6 +66,7 @@ struct __align__(16) Misc {
   float rnorm[kMaxBatch];
   unsigned long long ctrl_word;  // broadcast of the published control word
   int flag;                      // generic broadcast slot for the consumers
+  unsigned long long *prof_rec;  // timeline record of the current task (thread 0), or null
   int abort_flag;                // set when this CTA has seen an abort
   ypk_task ctask;                // consumer copy of the current task
   ypk_task ptask;                // producer copy of the current task
@@ -101,7 +110,14 @@ struct Runtime {
   unsigned long long budget_ns;
   int mode, max_seq, max_req, max_tok, max_pages, page_size, total_req;
   int max_iters, fixed_batch, resume_pending, rank, world;
+  int max_new_tokens;  // prefill chunk of one request per iteration (<= kMaxNewTokens)
   int end_event, end_count;  // event every task of the last operator triggers
+  // optional per-task timeline: 8 words per (worker, queue position), overwritten every
+  // iteration: {iteration << 32 | task, t_fetch, t_dependency_met, t_done, t_inputs_staged,
+  // t_last_stage_consumed, 0, 0} (globaltimer ns; the last two only for LINEAR tasks)
+  const void *tmaps;   // array of 128-byte TMA tensor maps (K/V caches), or null
+  unsigned long long *prof;
+  int prof_stride;  // records per worker
 };
 
 // ---------------------------------------------------------------- PTX helpers
@@ -168,6 +184,16 @@ __device__ __forceinline__ void bulk_g2s_hint(void *dst, const void *src, uint32
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
       "[%0], [%1], %2, [%3], %4;" ::"r"(smem_u32(dst)),
       "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+// Tiled TMA load of one box of a rank-3 tensor map into shared memory; (x, y, z) are element
+// coordinates from the innermost dimension outwards, x * element size a multiple of 16 B.
+__device__ __forceinline__ void tma_load_3d(void *dst, const void *tmap, int x, int y, int z,
+                                            unsigned long long *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(smem_u32(dst)),
+      "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
       : "memory");
 }
 __device__ __forceinline__ unsigned long long policy_evict_first() {
@@ -312,10 +338,10 @@ struct RingPos {
   }
 };
 
-// Columns of K staged per pass for a batch of `b` tokens (fp32 copy of the
-// activations has to fit the 64 KB x area); multiple of kStageCols.
+// Columns of K staged per pass for a batch of `b` tokens: b rows of 16-bit activations
+// (row pitch = columns + 8) have to fit the x area; multiple of kStageCols.
 __device__ __forceinline__ int chunk_cols(int b, int K) {
-  int kc = (kXsBytes / 4 / b) / kStageCols * kStageCols;
+  const int kc = (kXsBytes / 2 / b - 8) / kStageCols * kStageCols;
   return kc < K ? kc : K;
 }
 

@@ -68,6 +68,8 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const Runtime
 
   const int q0 = __ldg(rt.queue_off + worker), q1 = __ldg(rt.queue_off + worker + 1);
   WaitCtx wc{&rt, misc, worker, -1, false};
+  // swizzled TMA boxes assume ring stages on 1 KB boundaries
+  if (tid == 0 && (smem_u32(smem) & 1023u) != 0u) raise_abort(wc, YPK_ERR_STATE, -4);
   RingPos pos;
   long long iter = rt.base_iter;
   long long tasks_done = 0;
@@ -142,6 +144,14 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const Runtime
         wc.task = ti;
         consumer_bar();
         const ypk_task &t = misc->ctask;
+        unsigned long long *prec = nullptr;
+        if (rt.prof != nullptr && tid == 0 && q - q0 < rt.prof_stride) {
+          prec = rt.prof + (size_t(worker) * rt.prof_stride + (q - q0)) * 8;
+          prec[0] = (static_cast<unsigned long long>(iter) << 32) | unsigned(ti);
+          prec[1] = globaltimer();
+          prec[4] = prec[5] = prec[6] = prec[7] = 0ull;
+        }
+        if (tid == 0) misc->prof_rec = prec;
         if (t.dep_event >= 0) {
           if (tid == 0) {
             const unsigned long long need =
@@ -151,6 +161,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const Runtime
           consumer_bar();
           ok = misc->flag != 0;
         }
+        if (prec) prec[2] = globaltimer();
         if (ok) {
           switch (t.type) {
             case YPK_TASK_LINEAR: linear_consume(wc, smem, misc, t, batch, pos); break;
@@ -163,15 +174,17 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const Runtime
             default: break;
           }
           // a wait that gave up inside the task is known to one warp only: agree on it.
-          // The fence orders every thread's global writes before the trigger below.
           if (wc.failed) misc->abort_flag = 1;
-          __threadfence();
           consumer_bar();
           ok = misc->abort_flag == 0;
+          // The barrier orders every thread's global writes before thread 0; its gpu-scope
+          // release on the counter is cumulative over them, so a waiter that acquires the
+          // counter sees the task's output.
           if (ok && t.trig_event >= 0 && tid == 0) {
             red_release_add_u64(rt.events + t.trig_event, 1ull);
           }
         }
+        if (prec) prec[3] = globaltimer();
         consumer_bar();  // ctask may be overwritten from here on
         ++tasks_done;
       }

@@ -6,19 +6,25 @@
 // [q_per_kv q heads | k | v], rotate-half RoPE on the new q and k with bf16 cos/sin rows
 // (tasks/blackwell/rotary_embedding_sm100.cuh:56-73), the rotated k and v of the new
 // tokens are written into their page slots, causal softmax with scale 1/sqrt(128) in
-// fp32, bf16 output.  Differences by design: the sequence is split across CTAs
-// (split-KV) and the partial results are merged by whichever split finishes last, the
-// K/V tiles arrive through the producer warp's bulk copies instead of cp.async, and the
-// sequence length is (pages-1)*page_size + last_page_len with last_page_len in
-// [1, page_size] (the reference's 0-when-full convention under-counts by a page,
-// attention_sm100.cuh:101-102).
+// fp32, P rounded to bf16 before P.V (as the reference's mma does), bf16 output.
+// Differences by design: the sequence is split across CTAs (split-KV) and, inside a CTA,
+// across warps; partial results are merged in shared memory and, across CTAs, by whichever
+// split finishes last; the K/V tiles arrive through the producer warp's bulk copies
+// instead of cp.async; and the sequence length is (pages-1)*page_size + last_page_len with
+// last_page_len in [1, page_size] (the reference's 0-when-full convention under-counts by
+// a page, attention_sm100.cuh:101-102).
 //
-// Mapping: a ring stage holds 64 cached tokens (K rows at 272-byte pitch, then V rows).
-// A warp owns (q head g, token half th) units; lane <-> token for Q.K (16-byte K reads,
-// q read as shared-memory broadcasts), warp-shuffle max/sum for the online softmax, then
-// lane <-> 4 head dims for P.V with p broadcast by shuffle.
+// Mapping: a ring stage holds 64 cached tokens of one kv head, fetched as four tiled-TMA
+// boxes (K / V x low / high 64 dims) with the 128-byte swizzle that keeps ldmatrix conflict
+// free.  The query rows (new tokens x q heads of the
+// group, <= 32) form one or two 16-row MMA tiles.  Every 64-token stage is owned by ONE
+// warp, which runs the whole flash-attention step on it with m16n8k16 MMAs: S = Q.K^T
+// (K as the col-major operand straight from its rows), online softmax in the log2 domain
+// on the accumulator fragments (row max/sum by quad shuffles), P.V with V through
+// ldmatrix.trans.  Warps own stages round-robin, so up to five tiles are in flight.
 #pragma once
 #include "device_common.cuh"
+#include "task_linear.cuh"  // ldmatrix_x4, mma_16816
 
 namespace ypk {
 
@@ -43,9 +49,13 @@ __device__ __forceinline__ AttnShape attn_shape(const Runtime &rt, const ypk_tas
   s.seq_len = (npages - 1) * rt.page_size + __ldcg(rt.kv_last_len + r);
   s.cached = s.seq_len - s.T;
   const int tiles = (s.cached + kKvTile - 1) / kKvTile;
-  const int tps = max(1, (tiles + nsplit - 1) / nsplit);
+  // a split is worth its partial write and its share of the cross-CTA combine only once a
+  // CTA has two tiles per consumer warp; below that one CTA takes the whole sequence
+  const int want = min(nsplit, (tiles + 2 * kConsumerWarps - 1) / (2 * kConsumerWarps));
+  const int tps = max(1, (tiles + max(want, 1) - 1) / max(want, 1));
   s.nact = tiles > 0 ? (tiles + tps - 1) / tps : 1;
-  s.active = s.T > 0 && s.T <= kMaxNewTokens && npages > 0 && split < s.nact;
+  s.active = s.T > 0 && s.T <= kMaxNewTokens && s.T * t.iarg[4] <= kMaxAttnRows && npages > 0 &&
+             split < s.nact;
   s.tile0 = min(tiles, split * tps);
   s.tile1 = min(tiles, s.tile0 + tps);
   s.handles_new = split == s.nact - 1;
@@ -59,105 +69,195 @@ __device__ __forceinline__ bool attention_produce(WaitCtx &wc, char *smem, Misc 
   const int lane = threadIdx.x & 31;
   const AttnShape s = attn_shape(rt, t);
   if (!s.active) return true;
-  const int h = t.iarg[1], hkv = t.iarg[5];
-  const char *kc = reinterpret_cast<const char *>(t.ptr[1]);
-  const char *vc = reinterpret_cast<const char *>(t.ptr[2]);
+  const int h = t.iarg[1];
+  const char *ktm = static_cast<const char *>(rt.tmaps) + size_t(t.iarg[9]) * 128;
+  const char *vtm = static_cast<const char *>(rt.tmaps) + size_t(t.iarg[10]) * 128;
   for (int tile = s.tile0; tile < s.tile1; ++tile) {
     const int tok0 = tile * kKvTile;
-    const int ntok = min(kKvTile, s.cached - tok0);
     const int page = __ldcg(rt.kv_indices + s.kv0 + tok0 / rt.page_size);
     const size_t row0 = size_t(page) * rt.page_size + (tok0 % rt.page_size);
     if (!wait_mbar(wc, &misc->empty_bar[pos.slot], pos.phase ^ 1u)) return false;
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // consumers may have zero-padded
     char *stage = smem + kOffRing + pos.slot * kStageBytes;
-    if (lane == 0) mbar_expect_tx(&misc->full_bar[pos.slot], uint32_t(ntok) * kHeadDim * 4u);
-    __syncwarp();
-    for (int i = lane; i < ntok; i += 32) {
-      const size_t off = ((row0 + i) * hkv + h) * (kHeadDim * 2);
-      bulk_g2s(stage + i * kKPitch, kc + off, kHeadDim * 2, &misc->full_bar[pos.slot]);
-      bulk_g2s(stage + kVOffset + i * (kHeadDim * 2), vc + off, kHeadDim * 2,
-               &misc->full_bar[pos.slot]);
+    // One K or V row of a kv head is only 256 contiguous bytes; as separate bulk copies they
+    // are limited by the TMA engine's per-copy cost and as cp.async by one warp's loads in
+    // flight.  The tiled TMA path moves a 64-token x 64-dim box (8 KB) per instruction.  The
+    // box is always 64 tokens: a tile never crosses a page (page_size % 64 == 0), rows past
+    // the sequence end are masked by the consumer.
+    if (lane == 0) {
+      mbar_expect_tx(&misc->full_bar[pos.slot], 4u * kKvBoxBytes);
+      const int z = int(row0);
+      tma_load_3d(stage, ktm, 0, h, z, &misc->full_bar[pos.slot]);
+      tma_load_3d(stage + kKvBoxBytes, ktm, 64, h, z, &misc->full_bar[pos.slot]);
+      tma_load_3d(stage + kVOffset, vtm, 0, h, z, &misc->full_bar[pos.slot]);
+      tma_load_3d(stage + kVOffset + kKvBoxBytes, vtm, 64, h, z, &misc->full_bar[pos.slot]);
     }
+    __syncwarp();
     pos.advance();
   }
   return true;
 }
 
 // ------------------------------------------------------------------ consumer
-// Online-softmax state of one (unit, q row): running max (log2 domain), running sum,
-// and 4 output dims per lane.
-template <int TM>
-struct AttnState {
-  float m[2][TM], l[2][TM], o[2][TM][4];
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(smem_row)));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  return uint32_t(__bfloat16_as_ushort(__float2bfloat16_rn(lo))) |
+         (uint32_t(__bfloat16_as_ushort(__float2bfloat16_rn(hi))) << 16);
+}
+
+// Flash-attention state of one warp for a 16-row query tile.  A lane holds rows
+// lane/4 ("lo") and lane/4 + 8 ("hi"); per 8-wide block of head dims the four values are
+// {lo[d], lo[d+1], hi[d], hi[d+1]} with d = (lane % 4) * 2.
+struct AttnAcc {
+  float o[kHeadDim / 8][4];
+  float m[2];   // running max (log2 domain), rows lo / hi
+  float l[2];   // this lane's share of the running sum
 };
 
-template <int TM>
-__device__ __forceinline__ void attn_tile(const char *ksm, const char *vsm, const float *qs,
-                                          int ntok, bool causal, int T, int G, int warp, int lane,
-                                          AttnState<TM> &st) {
+// One 64-token tile (or the new-token mini tile): S = Q K^T, online softmax, O += P V.
+// ksm / vsm: rows of 128 bf16 at kKPitch.  `ntok` valid tokens; when `causal`, token j is
+// visible to query row (t, g) only if j <= t (rows are numbered t * G + g).
+// SWZ: ksm / vsm are TMA stages (two 64x128-byte boxes each, 128-byte swizzle: the 16-byte
+// chunk c of row r sits at chunk c ^ (r & 7)); otherwise plain rows at kKPitch.
+template <bool SWZ>
+__device__ __forceinline__ void attn_tile_mma(const char *qsm, const char *ksm, char *vsm,
+                                              int ntok, bool causal, int G, int row_base,
+                                              int lane, AttnAcc &acc) {
+  // 1/sqrt(128) * log2(e): scores live in the log2 domain so exp2f can be used
+  const float qscale = 0.08838834764831845f * 1.4426950408889634f;
+  const int nblk = (ntok + 7) >> 3;        // 8-token blocks with at least one valid token
+  const int nk16 = (ntok + 15) >> 4;       // 16-token steps of P.V
+  if (ntok < nk16 * 16) {
+    // P is zero for the padding tokens of the last 16-token step, but 0 * (stale bytes that
+    // happen to be Inf/NaN) would poison the row: clear those V rows.  The generic-proxy
+    // stores are fenced against the bulk copy that refills the stage later.
+    for (int i = lane; i < (nk16 * 16 - ntok) * (kHeadDim / 8); i += 32) {
+      const int row = ntok + i / (kHeadDim / 8), c = i % (kHeadDim / 8);
+      char *dst = SWZ ? vsm + (c >> 3) * kKvBoxBytes + row * 128 + (c & 7) * 16  // whole row: any order
+                      : vsm + row * kKPitch + c * 16;
+      *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+  }
+  float s[kKvTile / 8][4];
 #pragma unroll
-  for (int uu = 0; uu < 2; ++uu) {
-    const int u = warp + kConsumerWarps * uu;
-    if (u >= 2 * G) break;
-    const int g = u >> 1, th = u & 1;
-    const int tok = th * 32 + lane;
-    const bool valid = tok < ntok;
-    const int nhalf = min(32, ntok - th * 32);
-    if (nhalf <= 0) continue;
-    unsigned long long sacc[TM];
+  for (int nb = 0; nb < kKvTile / 8; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
+
+  // lane-constant address parts
+  const char *qrow = qsm + (row_base + ((lane >> 3) & 1) * 8 + (lane & 7)) * kKPitch +
+                     ((lane >> 4) & 1) * 16;
+  const char *krow = ksm + (lane & 7) * kKPitch + (lane >> 3) * 16;   // plain layout
+  const int sw = lane & 7;  // row & 7 of every ldmatrix row this lane addresses
+  // The asm statements keep program order and a warp issues in order, so fragment loads are
+  // grouped four at a time ahead of the MMAs that use them: their latencies overlap.
 #pragma unroll
-    for (int t = 0; t < TM; ++t) sacc[t] = 0ull;
-    const uint4 *kp = reinterpret_cast<const uint4 *>(ksm + tok * kKPitch);
-#pragma unroll 2
-    for (int s8 = 0; s8 < kHeadDim / 8; ++s8) {
-      uint4 kv = make_uint4(0u, 0u, 0u, 0u);
-      if (valid) kv = kp[s8];
-      const unsigned long long k0 = cvt_pair<false>(kv.x), k1 = cvt_pair<false>(kv.y),
-                               k2 = cvt_pair<false>(kv.z), k3 = cvt_pair<false>(kv.w);
+  for (int kp = 0; kp < kHeadDim / 32; ++kp) {   // pairs of 16-wide steps over the head dim
+    uint32_t q0[4], q1[4];
+    ldmatrix_x4(q0, qrow + kp * 64);
+    ldmatrix_x4(q1, qrow + kp * 64 + 32);
 #pragma unroll
-      for (int t = 0; t < TM; ++t) {
-        if (t < T) {
-          const ulonglong2 *qp =
-              reinterpret_cast<const ulonglong2 *>(qs + (t * G + g) * kHeadDim + s8 * 8);
-          const ulonglong2 qa = qp[0], qb = qp[1];
-          sacc[t] = fma2(k0, qa.x, sacc[t]);
-          sacc[t] = fma2(k1, qa.y, sacc[t]);
-          sacc[t] = fma2(k2, qb.x, sacc[t]);
-          sacc[t] = fma2(k3, qb.y, sacc[t]);
+    for (int nq = 0; nq < kKvTile / 32; ++nq) {   // groups of four 8-token blocks
+      if (nq * 4 < nblk) {
+        uint32_t kf[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int nb = nq * 4 + j;
+          if constexpr (SWZ) {
+            const int cg = kp * 4 + (lane >> 3);  // 16-byte chunk of the 256-byte row
+            ldmatrix_x4(kf[j], ksm + (cg >> 3) * kKvBoxBytes + (nb * 8 + sw) * 128 +
+                                   (((cg & 7) ^ sw) << 4));
+          } else {
+            ldmatrix_x4(kf[j], krow + nb * 8 * kKPitch + kp * 64);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          mma_16816<false>(s[nq * 4 + j], q0, kf[j][0], kf[j][1]);
+          mma_16816<false>(s[nq * 4 + j], q1, kf[j][2], kf[j][3]);
         }
       }
     }
-    float p[TM];
+  }
+  // scale, mask, row max
+  const int r_lo = row_base + (lane >> 2), r_hi = r_lo + 8;
+  const int t_lo = r_lo / G, t_hi = r_hi / G;
+  float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int t = 0; t < TM; ++t) {
-      p[t] = 0.f;
-      if (t < T) {
-        const float2 f = unpack2(sacc[t]);
-        const bool vis = valid && (!causal || tok <= t);
-        const float sc = vis ? f.x + f.y : -INFINITY;
-        const float mx = warp_max(sc);
-        const float m_new = fmaxf(st.m[uu][t], mx);
-        if (m_new != -INFINITY) {
-          const float corr = exp2f(st.m[uu][t] - m_new);  // exp2f(-inf) = 0 on first use
-          p[t] = vis ? exp2f(sc - m_new) : 0.f;
-          st.l[uu][t] = st.l[uu][t] * corr + warp_sum(p[t]);
+  for (int nb = 0; nb < kKvTile / 8; ++nb) {
 #pragma unroll
-          for (int d = 0; d < 4; ++d) st.o[uu][t][d] *= corr;
-          st.m[uu][t] = m_new;
-        }
-      }
+    for (int e = 0; e < 4; ++e) {
+      const int tok = nb * 8 + (lane & 3) * 2 + (e & 1);
+      const int tq = (e & 2) ? t_hi : t_lo;
+      const bool vis = nb < nblk && tok < ntok && (!causal || tok <= tq);
+      s[nb][e] = vis ? s[nb][e] * qscale : -INFINITY;
+      mx[e >> 1] = fmaxf(mx[e >> 1], s[nb][e]);
     }
-    const char *vp = vsm + (th * 32) * (kHeadDim * 2) + lane * 8;
-    for (int j = 0; j < nhalf; ++j) {
-      const uint2 vv = *reinterpret_cast<const uint2 *>(vp + j * (kHeadDim * 2));
-      const float2 v01 = unpack2(cvt_pair<false>(vv.x)), v23 = unpack2(cvt_pair<false>(vv.y));
+  }
+  float corr[2];
 #pragma unroll
-      for (int t = 0; t < TM; ++t) {
-        if (t < T) {
-          const float pj = __shfl_sync(0xffffffffu, p[t], j);
-          st.o[uu][t][0] += pj * v01.x;
-          st.o[uu][t][1] += pj * v01.y;
-          st.o[uu][t][2] += pj * v23.x;
-          st.o[uu][t][3] += pj * v23.y;
+  for (int h = 0; h < 2; ++h) {
+    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+    const float m_new = fmaxf(acc.m[h], mx[h]);
+    // a row that has seen nothing yet keeps m = -inf; use 0 as the exponent base then
+    const float base = m_new == -INFINITY ? 0.f : m_new;
+    corr[h] = exp2f(acc.m[h] - base);   // exp2f(-inf) = 0
+    acc.m[h] = m_new;
+    mx[h] = base;
+    acc.l[h] *= corr[h];
+  }
+  // p = exp2(s - m), packed to bf16 A fragments of the P.V product
+  uint32_t pf[kKvTile / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < kKvTile / 16; ++kk) {
+    float p[8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      p[e] = exp2f(s[2 * kk][e] - mx[e >> 1]);
+      p[4 + e] = exp2f(s[2 * kk + 1][e] - mx[e >> 1]);
+    }
+    acc.l[0] += (p[0] + p[1]) + (p[4] + p[5]);
+    acc.l[1] += (p[2] + p[3]) + (p[6] + p[7]);
+    pf[kk][0] = pack_bf16(p[0], p[1]);
+    pf[kk][1] = pack_bf16(p[2], p[3]);
+    pf[kk][2] = pack_bf16(p[4], p[5]);
+    pf[kk][3] = pack_bf16(p[6], p[7]);
+  }
+#pragma unroll
+  for (int nb = 0; nb < kHeadDim / 8; ++nb) {
+    acc.o[nb][0] *= corr[0];
+    acc.o[nb][1] *= corr[0];
+    acc.o[nb][2] *= corr[1];
+    acc.o[nb][3] *= corr[1];
+  }
+  // O += P V: V rows are the k dimension, so its fragments come transposed
+  const char *vrow = vsm + ((lane & 7) + ((lane >> 3) & 1) * 8) * kKPitch + (lane >> 4) * 16;
+#pragma unroll
+  for (int kk = 0; kk < kKvTile / 16; ++kk) {
+    if (kk < nk16) {
+#pragma unroll
+      for (int nq = 0; nq < kHeadDim / 64; ++nq) {   // groups of four 16-dim pairs
+        uint32_t vf[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int np = nq * 4 + j;
+          if constexpr (SWZ) {
+            const int cg = np * 2 + (lane >> 4);
+            const int row = kk * 16 + sw + ((lane >> 3) & 1) * 8;
+            ldmatrix_x4_trans(vf[j], vsm + (cg >> 3) * kKvBoxBytes + row * 128 + (((cg & 7) ^ sw) << 4));
+          } else {
+            ldmatrix_x4_trans(vf[j], vrow + kk * 16 * kKPitch + np * 32);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          mma_16816<false>(acc.o[2 * (nq * 4 + j)], pf[kk], vf[j][0], vf[j][1]);
+          mma_16816<false>(acc.o[2 * (nq * 4 + j) + 1], pf[kk], vf[j][2], vf[j][3]);
         }
       }
     }
@@ -165,13 +265,42 @@ __device__ __forceinline__ void attn_tile(const char *ksm, const char *vsm, cons
 }
 
 // Layout of one merged/partial row in shared or global scratch: 128 outputs, m, l, and two
-// floats of padding so that every row starts on a 16-byte boundary (float4 stores).
+// floats of padding so that every row starts on a 16-byte boundary.
 constexpr int kAttnRowFloats = kHeadDim + 4;
 
-template <int TM>
-__device__ __forceinline__ void attention_consume_t(WaitCtx &wc, char *smem, Misc *misc,
-                                                    const Runtime &rt, const ypk_task &t,
-                                                    const AttnShape &s, RingPos &pos) {
+// A warp's state for its 16-row tile -> shared memory [16][kAttnRowFloats].
+// `hi` = false skips rows 8..15 (a decode step has at most 8 query rows).
+__device__ __forceinline__ void attn_store_state(float *dst, const AttnAcc &acc, int lane,
+                                                 bool hi = true) {
+  const int r = lane >> 2, c = (lane & 3) * 2;
+  float l0 = acc.l[0], l1 = acc.l[1];
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+#pragma unroll
+  for (int nb = 0; nb < kHeadDim / 8; ++nb) {
+    *reinterpret_cast<float2 *>(dst + r * kAttnRowFloats + nb * 8 + c) =
+        make_float2(acc.o[nb][0], acc.o[nb][1]);
+    if (hi)
+      *reinterpret_cast<float2 *>(dst + (r + 8) * kAttnRowFloats + nb * 8 + c) =
+          make_float2(acc.o[nb][2], acc.o[nb][3]);
+  }
+  if ((lane & 3) == 0) {
+    dst[r * kAttnRowFloats + kHeadDim] = acc.m[0];
+    dst[r * kAttnRowFloats + kHeadDim + 1] = l0;
+    if (hi) {
+      dst[(r + 8) * kAttnRowFloats + kHeadDim] = acc.m[1];
+      dst[(r + 8) * kAttnRowFloats + kHeadDim + 1] = l1;
+    }
+  }
+}
+
+__device__ __forceinline__ void attention_consume(WaitCtx &wc, char *smem, Misc *misc,
+                                                  const Runtime &rt, const ypk_task &t,
+                                                  RingPos &pos) {
+  const AttnShape s = attn_shape(rt, t);
+  if (!s.active) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int r = t.iarg[0], h = t.iarg[1], split = t.iarg[2], nsplit = t.iarg[3];
   const int G = t.iarg[4], hkv = t.iarg[5], ld_qkv = t.iarg[6], ld_out = t.iarg[7];
@@ -186,135 +315,189 @@ __device__ __forceinline__ void attention_consume_t(WaitCtx &wc, char *smem, Mis
   unsigned int *counters = reinterpret_cast<unsigned int *>(t.ptr[7]);
   const bool rope = (t.flags & YPK_F_ROPE) != 0;
   const int T = s.T, rows = T * G;
+  const int nm = (rows + 15) >> 4;            // 16-row query tiles: 1 or 2
+  const int nslots = kConsumerWarps / nm;     // warps that share the tiles of one query tile
+  const int mt = warp / nslots, slot = warp - mt * nslots;
 
-  float *qs = reinterpret_cast<float *>(smem + kOffXs);                  // [rows][128] fp32
-  char *knew = smem + kOffXs + 64 * kHeadDim * 4;                         // [T] rows, K pitch
-  char *vnew = knew + kMaxNewTokens * kKPitch;                            // [T][256 B]
-  // 1/sqrt(128) * log2(e): scores live in the log2 domain so exp2f can be used
-  const float qscale = 0.08838834764831845f * 1.4426950408889634f;
+  // shared-memory scratch of the task (everything from kOffXs up to the misc area)
+  char *qsm = smem + kOffXs;                                    // [32][272 B] bf16 q rows
+  char *knew = qsm + kMaxAttnRows * kKPitch;                    // [16][272 B]
+  char *vnew = knew + 16 * kKPitch;                             // [16][272 B]
+  float *mrg = reinterpret_cast<float *>(smem + kOffXs);        // merge: [4 warps][16][132] fp32
 
-  // Stage q (rotated, rounded to bf16 like the reference's shared-memory copy, scaled)
-  // and, in the split that owns the new tokens, the rotated k and v; append those to the
-  // cache page.
+  // Stage q (rotated, rounded to bf16) and, in the split that owns the new tokens, the
+  // rotated k and v; append those to the cache page.  One thread handles 8 consecutive dims
+  // with 16-byte loads of the values, their rotate-half partners and the cos/sin row.
+  if (s.handles_new) {
+    for (int i = tid; i < 16 * (kHeadDim / 8); i += kConsumerThreads) {   // clear rows T..15 of v
+      const int row = i >> 4;
+      if (row >= T) *reinterpret_cast<uint4 *>(vnew + row * kKPitch + (i & 15) * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
   const int heads_to_stage = G + (s.handles_new ? 2 : 0);
-  for (int idx = tid; idx < T * heads_to_stage * kHeadDim; idx += kConsumerThreads) {
-    const int d = idx & (kHeadDim - 1);
-    const int hh = (idx >> 7) % heads_to_stage;
-    const int tk = idx / (heads_to_stage * kHeadDim);
+  for (int idx = tid; idx < T * heads_to_stage * (kHeadDim / 8); idx += kConsumerThreads) {
+    const int c = idx & 15;                       // 8-dim chunk of the head
+    const int hh = (idx >> 4) % heads_to_stage;
+    const int tk = idx / (heads_to_stage * 16);
+    const int d0 = c * 8;
     const int pos_t = s.seq_len - T + tk;
     const uint16_t *src = qkv + size_t(s.qo0 + tk) * ld_qkv + size_t(h) * (G + 2) * kHeadDim +
                           hh * kHeadDim;
-    float v = cvt_one<false>(__ldcg(src + d));
+    uint4 pk = __ldcg(reinterpret_cast<const uint4 *>(src + d0));
     if (rope && hh <= G) {  // q heads and k, not v
-      const float other = cvt_one<false>(__ldcg(src + (d ^ 64)));
-      const float c = cvt_one<false>(__ldcg(cosp + size_t(pos_t) * kHeadDim + d));
-      const float sn = cvt_one<false>(__ldcg(sinp + size_t(pos_t) * kHeadDim + d));
-      v = d < 64 ? v * c - other * sn : v * c + other * sn;
+      const uint4 ov = __ldcg(reinterpret_cast<const uint4 *>(src + (d0 ^ 64)));
+      const uint4 cv = __ldcg(reinterpret_cast<const uint4 *>(cosp + size_t(pos_t) * kHeadDim + d0));
+      const uint4 sv = __ldcg(reinterpret_cast<const uint4 *>(sinp + size_t(pos_t) * kHeadDim + d0));
+      const uint32_t pv[4] = {pk.x, pk.y, pk.z, pk.w}, po[4] = {ov.x, ov.y, ov.z, ov.w},
+                     pc[4] = {cv.x, cv.y, cv.z, cv.w}, ps[4] = {sv.x, sv.y, sv.z, sv.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 v2 = unpack2(cvt_pair<false>(pv[i])), o2 = unpack2(cvt_pair<false>(po[i])),
+                     c2 = unpack2(cvt_pair<false>(pc[i])), s2 = unpack2(cvt_pair<false>(ps[i]));
+        const float sgn = d0 < 64 ? -1.f : 1.f;
+        o[i] = pack_bf16(v2.x * c2.x + sgn * (o2.x * s2.x), v2.y * c2.y + sgn * (o2.y * s2.y));
+      }
+      pk = make_uint4(o[0], o[1], o[2], o[3]);
     }
-    v = bf16_round(v);
     if (hh < G) {
-      qs[(tk * G + hh) * kHeadDim + d] = v * qscale;
+      *reinterpret_cast<uint4 *>(qsm + (tk * G + hh) * kKPitch + d0 * 2) = pk;
     } else {
-      const uint16_t bits = __bfloat16_as_ushort(__float2bfloat16_rn(v));
       const int page = __ldcg(rt.kv_indices + s.kv0 + pos_t / rt.page_size);
       const size_t off =
-          ((size_t(page) * rt.page_size + (pos_t % rt.page_size)) * hkv + h) * kHeadDim + d;
+          ((size_t(page) * rt.page_size + (pos_t % rt.page_size)) * hkv + h) * kHeadDim + d0;
       if (hh == G) {
-        reinterpret_cast<uint16_t *>(knew + tk * kKPitch)[d] = bits;
-        kcache[off] = bits;
+        *reinterpret_cast<uint4 *>(knew + tk * kKPitch + d0 * 2) = pk;
+        *reinterpret_cast<uint4 *>(kcache + off) = pk;
       } else {
-        reinterpret_cast<uint16_t *>(vnew + tk * (kHeadDim * 2))[d] = bits;
-        vcache[off] = bits;
+        *reinterpret_cast<uint4 *>(vnew + tk * kKPitch + d0 * 2) = pk;
+        *reinterpret_cast<uint4 *>(vcache + off) = pk;
       }
     }
   }
   consumer_bar();
+  if (tid == 0 && misc->prof_rec) misc->prof_rec[4] = globaltimer();
 
-  AttnState<TM> st;
+  AttnAcc acc;
 #pragma unroll
-  for (int uu = 0; uu < 2; ++uu)
-#pragma unroll
-    for (int tt = 0; tt < TM; ++tt) {
-      st.m[uu][tt] = -INFINITY;
-      st.l[uu][tt] = 0.f;
-#pragma unroll
-      for (int d = 0; d < 4; ++d) st.o[uu][tt][d] = 0.f;
-    }
+  for (int nb = 0; nb < kHeadDim / 8; ++nb) acc.o[nb][0] = acc.o[nb][1] = acc.o[nb][2] = acc.o[nb][3] = 0.f;
+  acc.m[0] = acc.m[1] = -INFINITY;
+  acc.l[0] = acc.l[1] = 0.f;
 
+  // Every warp passes every stage (so that ring positions stay in step) but computes only
+  // on the tiles it owns; the others are released as soon as they have landed.
   for (int tile = s.tile0; tile < s.tile1; ++tile) {
     const int ntok = min(kKvTile, s.cached - tile * kKvTile);
     const bool got = wait_mbar(wc, &misc->full_bar[pos.slot], pos.phase);
-    const char *stage = smem + kOffRing + pos.slot * kStageBytes;
-    if (got) attn_tile<TM>(stage, stage + kVOffset, qs, ntok, false, T, G, warp, lane, st);
+    if (got && (tile - s.tile0) % nslots == slot) {
+      char *stage = smem + kOffRing + pos.slot * kStageBytes;
+      attn_tile_mma<true>(qsm, stage, stage + kVOffset, ntok, false, G, mt * 16, lane, acc);
+    }
     __syncwarp();
     if (lane == 0 && got) mbar_arrive(&misc->empty_bar[pos.slot]);
     pos.advance();
   }
-  if (s.handles_new) attn_tile<TM>(knew, vnew, qs, T, true, T, G, warp, lane, st);
-  consumer_bar();  // q / knew / vnew are dead from here on; reuse the area for the merge
+  // the new tokens: causal among themselves; the last slot of the group is the one with
+  // the fewest cached tiles
+  if (s.handles_new && slot == nslots - 1)
+    attn_tile_mma<false>(qsm, knew, vnew, T, true, G, mt * 16, lane, acc);
+  consumer_bar();  // q / knew / vnew are dead from here on; the area becomes the merge buffer
+  if (tid == 0 && misc->prof_rec) misc->prof_rec[5] = globaltimer();
 
-  // Per-unit partials -> shared memory: [unit][t] rows of (o[128], m, l).
-  float *pm = reinterpret_cast<float *>(smem + kOffXs);
-#pragma unroll
-  for (int uu = 0; uu < 2; ++uu) {
-    const int u = warp + kConsumerWarps * uu;
-    if (u < 2 * G) {
-#pragma unroll
-      for (int tt = 0; tt < TM; ++tt) {
-        if (tt < T) {
-          float *row = pm + (u * T + tt) * kAttnRowFloats;
-          *reinterpret_cast<float4 *>(row + lane * 4) =
-              make_float4(st.o[uu][tt][0], st.o[uu][tt][1], st.o[uu][tt][2], st.o[uu][tt][3]);
-          if (lane == 0) {
-            row[kHeadDim] = st.m[uu][tt];
-            row[kHeadDim + 1] = st.l[uu][tt];
-          }
-        }
-      }
-    }
-  }
-  consumer_bar();
-
-  // Merge the two token halves of every (t, g) row; either finish here (single split)
-  // or park the partial in global scratch for the last-arriving split to combine.
   const bool single = s.nact == 1;
   float *my_scr =
       scratch + ((size_t(r) * hkv + h) * nsplit + split) * size_t(max_rows) * kAttnRowFloats;
-  for (int idx = tid; idx < rows * kHeadDim; idx += kConsumerThreads) {
-    const int d = idx & (kHeadDim - 1);
-    const int row = idx >> 7;          // t * G + g
-    const int tk = row / G, g = row - tk * G;
-    const float *a = pm + ((2 * g) * T + tk) * kAttnRowFloats;
-    const float *b = pm + ((2 * g + 1) * T + tk) * kAttnRowFloats;
-    const float ma = a[kHeadDim], mb = b[kHeadDim];
-    const float m = fmaxf(ma, mb);
-    const float ca = ma == -INFINITY ? 0.f : exp2f(ma - m);
-    const float cb = mb == -INFINITY ? 0.f : exp2f(mb - m);
-    const float l = a[kHeadDim + 1] * ca + b[kHeadDim + 1] * cb;
-    const float o = a[d] * ca + b[d] * cb;
-    if (single) {
-      out[size_t(s.qo0 + tk) * ld_out + size_t(h * G + g) * kHeadDim + d] =
-          __bfloat16_as_ushort(__float2bfloat16_rn(o / l));
-    } else {
-      float *dst = my_scr + row * kAttnRowFloats;
-      dst[d] = o;
-      if (d == 0) {
-        dst[kHeadDim] = m;
-        dst[kHeadDim + 1] = l;
+  // merge states are [16 rows][132] per warp, or [8 rows][132] when only 8 rows are live
+  const int kStateFloats = (rows <= 8 ? 8 : 16) * kAttnRowFloats;
+  // Merge the warps of a query tile, four states at a time, then finish rows [mt*16, ..).
+  auto finalize = [&](int mtile, int nstates) {
+    const int row_lo = mtile * 16, nrow = min(16, rows - row_lo);
+    for (int idx = tid; idx < nrow * kHeadDim; idx += kConsumerThreads) {
+      const int d = idx & (kHeadDim - 1), rr = idx >> 7;
+      float m = -INFINITY;
+      for (int w = 0; w < nstates; ++w)
+        m = fmaxf(m, mrg[w * kStateFloats + rr * kAttnRowFloats + kHeadDim]);
+      float l = 0.f, o = 0.f;
+      for (int w = 0; w < nstates; ++w) {
+        const float *pr = mrg + w * kStateFloats + rr * kAttnRowFloats;
+        const float c = pr[kHeadDim] == -INFINITY ? 0.f : exp2f(pr[kHeadDim] - m);
+        l += pr[kHeadDim + 1] * c;
+        o += pr[d] * c;
+      }
+      const int row = row_lo + rr, tk = row / G, g = row - tk * G;
+      if (single) {
+        out[size_t(s.qo0 + tk) * ld_out + size_t(h * G + g) * kHeadDim + d] =
+            __bfloat16_as_ushort(__float2bfloat16_rn(o / l));
+      } else {
+        float *dst = my_scr + row * kAttnRowFloats;
+        dst[d] = o;
+        if (d == 0) {
+          dst[kHeadDim] = m;
+          dst[kHeadDim + 1] = l;
+        }
       }
     }
+  };
+  if (rows <= 8) {
+    // decode: eight 8-row states fit the buffer at once
+    attn_store_state(mrg + warp * kStateFloats, acc, lane, false);
+    consumer_bar();
+    finalize(0, kConsumerWarps);
+  } else if (nm == 1) {
+    // eight states: warps 4..7 hand theirs to warps 0..3, which fold them in
+    if (warp >= 4) attn_store_state(mrg + (warp - 4) * kStateFloats, acc, lane);
+    consumer_bar();
+    if (warp < 4) {
+      const float *ps = mrg + warp * kStateFloats;
+      const int rr = lane >> 2, c = (lane & 3) * 2;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const float *pr = ps + (rr + hh * 8) * kAttnRowFloats;
+        const float mo = pr[kHeadDim], lo = pr[kHeadDim + 1];
+        const float m_new = fmaxf(acc.m[hh], mo);
+        const float base = m_new == -INFINITY ? 0.f : m_new;
+        const float ca = exp2f(acc.m[hh] - base), cb = exp2f(mo - base);
+        // acc.l is a per-lane share; the partner's l is the full row sum: add it on one lane
+        acc.l[hh] = acc.l[hh] * ca + ((lane & 3) == 0 ? lo * cb : 0.f);
+        acc.m[hh] = m_new;
+#pragma unroll
+        for (int nb = 0; nb < kHeadDim / 8; ++nb) {
+          const float2 po = *reinterpret_cast<const float2 *>(pr + nb * 8 + c);
+          acc.o[nb][2 * hh] = acc.o[nb][2 * hh] * ca + po.x * cb;
+          acc.o[nb][2 * hh + 1] = acc.o[nb][2 * hh + 1] * ca + po.y * cb;
+        }
+      }
+    }
+    consumer_bar();
+    if (warp < 4) attn_store_state(mrg + warp * kStateFloats, acc, lane);
+    consumer_bar();
+    finalize(0, 4);
+  } else {
+    if (warp < 4) attn_store_state(mrg + warp * kStateFloats, acc, lane);
+    consumer_bar();
+    finalize(0, 4);
+    consumer_bar();
+    if (warp >= 4) attn_store_state(mrg + (warp - 4) * kStateFloats, acc, lane);
+    consumer_bar();
+    finalize(1, 4);
   }
   if (single) return;
 
-  __threadfence();
+  // Arrival: the barrier orders every thread's partial before thread 0, whose acq_rel
+  // increment publishes it (release) and, for the last arriver, makes the other splits'
+  // partials visible (acquire); the second barrier passes that on to the whole CTA.
   consumer_bar();
   if (tid == 0) {
-    const unsigned old = atomicAdd(counters + r * hkv + h, 1u);
+    unsigned old;
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;"
+                 : "=r"(old)
+                 : "l"(counters + r * hkv + h)
+                 : "memory");
     misc->flag = (old == unsigned(s.nact - 1)) ? 1 : 0;
   }
   consumer_bar();
+  if (tid == 0 && misc->prof_rec) misc->prof_rec[6] = globaltimer();
   if (misc->flag) {
-    __threadfence();
     const float *base = scratch + (size_t(r) * hkv + h) * nsplit * size_t(max_rows) * kAttnRowFloats;
     for (int idx = tid; idx < rows * kHeadDim; idx += kConsumerThreads) {
       const int d = idx & (kHeadDim - 1);
@@ -335,18 +518,6 @@ __device__ __forceinline__ void attention_consume_t(WaitCtx &wc, char *smem, Mis
           __bfloat16_as_ushort(__float2bfloat16_rn(o / l));
     }
     if (tid == 0) counters[r * hkv + h] = 0u;
-  }
-}
-
-__device__ __forceinline__ void attention_consume(WaitCtx &wc, char *smem, Misc *misc,
-                                                  const Runtime &rt, const ypk_task &t,
-                                                  RingPos &pos) {
-  const AttnShape s = attn_shape(rt, t);
-  if (!s.active) return;
-  if (s.T == 1) {
-    attention_consume_t<1>(wc, smem, misc, rt, t, s, pos);
-  } else {
-    attention_consume_t<kMaxNewTokens>(wc, smem, misc, rt, t, s, pos);
   }
 }
 

@@ -6,13 +6,17 @@
 // tasks/ampere/silu_mul.cuh:19-42; fused semantics as in tasks/ampere/norm_linear.cuh:412-427,
 // where the division by the RMS happens after the matmul).
 //
-// Data movement: W is [N, K] row-major (torch nn.Linear.weight), so the rows of a
-// worker are contiguous in HBM.  The producer warp streams them in stages of
-// 32 rows x 512 columns (one 1 KB cp.async.bulk per row, issued by 32 lanes at once)
-// into the ring; row pitch 1040 B keeps the consumers' 16-byte reads conflict free.
-// Consumers: lane <-> weight row, warp <-> 64-column slice of the stage, activations
-// pre-scaled and held in shared memory as fp32 and read as warp-wide broadcasts,
-// packed fp32x2 FMAs, fp32 accumulation, one fixed-order cross-warp sum per row block.
+// This is the decode-time GEMV: 2 bytes of weight per 2*batch flops, i.e. bound by HBM.
+// Data movement: W is [N, K] row-major (torch nn.Linear.weight), so the rows of a worker are
+// contiguous in HBM.  The producer warp streams them through the shared-memory ring in
+// stages of 16 rows x 1024 columns, one 2 KB cp.async.bulk per row (row pitch 2064 B so that
+// 8 rows hit 8 different 16-byte bank groups).  Arithmetic: the batch is padded to the 8
+// columns of a warp-level m16n8k16 MMA (bf16/fp16 in, fp32 accumulate) and the 16 weight
+// rows of the stage are its M side, so one ldmatrix + one mma handle 512 bytes of weights
+// whatever the batch; warp w owns the 128-column slice w of every stage and the eight
+// partial 16x8 tiles are summed in a fixed order once per row block.  The activations of the
+// pass sit in shared memory as 16-bit values already multiplied by the norm weight; batch
+// rows beyond the real batch alias the last real row (their MMA columns are never stored).
 #pragma once
 #include "device_common.cuh"
 
@@ -50,8 +54,8 @@ __device__ __forceinline__ LinearArgs linear_args(const ypk_task &t) {
 }
 
 // ------------------------------------------------------------------ producer
-// Traversal (must match linear_consume): batch groups -> K chunks -> row blocks
-// -> 512-column stages.
+// Traversal (must match linear_consume): batch groups -> K chunks -> 16-row blocks
+// -> 1024-column stages.
 __device__ __forceinline__ bool linear_produce(WaitCtx &wc, char *smem, Misc *misc,
                                                const ypk_task &t, int batch, RingPos &pos,
                                                unsigned long long policy) {
@@ -68,6 +72,9 @@ __device__ __forceinline__ bool linear_produce(WaitCtx &wc, char *smem, Misc *mi
         for (int ks = 0; ks < klen; ks += kStageCols) {
           const int ncols = min(kStageCols, klen - ks);
           if (!wait_mbar(wc, &misc->empty_bar[pos.slot], pos.phase ^ 1u)) return false;
+          // the slot may last have been written through the generic proxy (attention tiles
+          // arrive by cp.async, partial tiles are zero-padded by the consumers)
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           char *stage = smem + kOffRing + pos.slot * kStageBytes;
           if (lane == 0) mbar_expect_tx(&misc->full_bar[pos.slot], uint32_t(nr) * ncols * 2u);
           __syncwarp();
@@ -86,28 +93,26 @@ __device__ __forceinline__ bool linear_produce(WaitCtx &wc, char *smem, Misc *mi
 }
 
 // ------------------------------------------------------------------ consumer
-template <int B, bool F16>
-__device__ __forceinline__ void linear_stage_math(const char *stage, const float *xs, int xs_ld,
-                                                  int kofs, int ncols, int nr, int warp, int lane,
-                                                  unsigned long long (&acc)[B]) {
-  const int c0 = warp * 64;
-  if (c0 >= ncols || lane >= nr) return;
-  const uint4 *wp = reinterpret_cast<const uint4 *>(stage + lane * kRowPitch + c0 * 2);
-  const float *xb = xs + kofs + c0;
-#pragma unroll 4
-  for (int s = 0; s < 8; ++s) {
-    const uint4 wv = wp[s];
-    const unsigned long long w0 = cvt_pair<F16>(wv.x), w1 = cvt_pair<F16>(wv.y),
-                             w2 = cvt_pair<F16>(wv.z), w3 = cvt_pair<F16>(wv.w);
-#pragma unroll
-    for (int b = 0; b < B; ++b) {
-      const ulonglong2 *xp = reinterpret_cast<const ulonglong2 *>(xb + b * xs_ld + s * 8);
-      const ulonglong2 xa = xp[0], xc = xp[1];
-      acc[b] = fma2(w0, xa.x, acc[b]);
-      acc[b] = fma2(w1, xa.y, acc[b]);
-      acc[b] = fma2(w2, xc.x, acc[b]);
-      acc[b] = fma2(w3, xc.y, acc[b]);
-    }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(smem_row)));
+}
+template <bool F16>
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                          uint32_t b1) {
+  if constexpr (F16) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   }
 }
 
@@ -119,11 +124,13 @@ __device__ __forceinline__ float silu_mul_ref(float g, float u) {
   return s * ur;
 }
 
-// Writes the finished values of `nr` rows starting at task row r0.
-// val(r, b) returns the fp32 dot product (before the RMS scale).
+// Writes the finished values of `nr` rows starting at task row r0.  val(r, b) returns the
+// fp32 dot product (before the RMS scale); res_s holds the residual slice of the task,
+// [batch][nrows] 16-bit, staged in shared memory when the task started.
 template <bool F16, typename ValFn>
-__device__ __forceinline__ void linear_epilogue(const LinearArgs &a, const Misc *misc, int r0,
-                                                int nr, int b0, int bc, int tid, ValFn val) {
+__device__ __forceinline__ void linear_epilogue(const LinearArgs &a, const Misc *misc,
+                                                const uint16_t *res_s, int r0, int nr, int b0,
+                                                int bc, int tid, ValFn val) {
   const bool norm = (a.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT)) != 0;
   if (a.flags & YPK_F_SILU_MUL) {
     const int nout = nr >> 1;  // 16-row granules: 8 gate rows then 8 up rows
@@ -145,165 +152,227 @@ __device__ __forceinline__ void linear_epilogue(const LinearArgs &a, const Misc 
       float v = val(r, b);
       if (norm) v *= misc->rnorm[b];
       const int col = a.out_col0 + a.row0 + r0 + r;
-      if (a.flags & YPK_F_RESIDUAL) {
-        const uint16_t rv = __ldcg(reinterpret_cast<const uint16_t *>(a.res) +
-                                   size_t(b0 + b) * a.ldres + col);
-        // fp32 add, one rounding
-        v += cvt_one<F16>(rv);
-      }
+      if (a.flags & YPK_F_RESIDUAL) v += cvt_one<F16>(res_s[b * a.nrows + r0 + r]);  // fp32 add
       reinterpret_cast<uint16_t *>(a.out)[size_t(b0 + b) * a.ldout + col] = cvt_out<F16>(v);
     }
   }
 }
 
-template <int B, bool F16>
+// Sum of the per-warp statistics -> misc->rnorm.  `red` is [8 warps][8] floats of scratch.
+__device__ __forceinline__ void publish_rnorm(const LinearArgs &a, Misc *misc, float *red,
+                                              const float (&ss)[kMaxBatch], int B, int tid) {
+  const int warp = tid >> 5, lane = tid & 31;
+#pragma unroll
+  for (int b = 0; b < kMaxBatch; ++b) {
+    const float s = warp_sum(ss[b]);
+    if (lane == 0) red[warp * kMaxBatch + b] = s;
+  }
+  consumer_bar();
+  if (tid < B) {
+    float s = 0.f;
+    for (int w = 0; w < kConsumerWarps; ++w) s += red[w * kMaxBatch + tid];
+    misc->rnorm[tid] = rsqrtf(s / float(a.K) + a.eps);
+  }
+  consumer_bar();
+}
+
+template <bool F16>
 __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Misc *misc,
-                                                     const LinearArgs &a, int b0, RingPos &pos) {
+                                                     const LinearArgs &a, int b0, int B,
+                                                     RingPos &pos) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  float *xs = reinterpret_cast<float *>(smem + kOffXs);
-  float *part = reinterpret_cast<float *>(smem + kOffPart);
-  float *accs = reinterpret_cast<float *>(smem + kOffAcc);
+  uint16_t *xs = reinterpret_cast<uint16_t *>(smem + kOffXs);
+  float *part = reinterpret_cast<float *>(smem + kOffPart);          // [2][8 warps][16][8]
+  uint16_t *res_s = reinterpret_cast<uint16_t *>(smem + kOffRes);    // [B][nrows]
+  float *accs = reinterpret_cast<float *>(smem + kOffAcc);           // [nrows][8] when chunked
   const uint16_t *x = reinterpret_cast<const uint16_t *>(a.x) + size_t(b0) * a.ldx;
   const uint16_t *nw = reinterpret_cast<const uint16_t *>(a.norm_w);
   const bool norm = (a.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT)) != 0;
   const bool has_nw = (a.flags & YPK_F_NORM) != 0;
-
-  // RMS statistics over the full K (fp32, as rmsnorm_hopper.cuh accumulates).
-  if (norm) {
-    float ss[B];
-#pragma unroll
-    for (int b = 0; b < B; ++b) ss[b] = 0.f;
-    for (int k = tid * 8; k < a.K; k += kConsumerThreads * 8) {
-#pragma unroll
-      for (int b = 0; b < B; ++b) {
-        const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(x + size_t(b) * a.ldx + k));
-        const uint32_t p[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = unpack2(cvt_pair<F16>(p[i]));
-          ss[b] += f.x * f.x + f.y * f.y;
-        }
-      }
-    }
-    float *red = part;  // [warp][B]
-#pragma unroll
-    for (int b = 0; b < B; ++b) {
-      const float s = warp_sum(ss[b]);
-      if (lane == 0) red[warp * B + b] = s;
-    }
-    consumer_bar();
-    if (tid < B) {
-      float s = 0.f;
-      for (int w = 0; w < kConsumerWarps; ++w) s += red[w * B + tid];
-      misc->rnorm[tid] = rsqrtf(s / float(a.K) + a.eps);
-    }
-    // rnorm and `red` are separated from their next use by the barriers below
-  }
+  constexpr int kPartHalf = kConsumerWarps * kRowBlock * kMaxBatch;
 
   const int KC = chunk_cols(B, a.K);
   const bool chunked = KC < a.K;
+  const int xpitch = KC + 8;  // elements; +16 bytes keeps the batch rows on distinct banks
   if (chunked) {
-    for (int i = tid; i < a.nrows * B; i += kConsumerThreads) accs[i] = 0.f;
+    for (int i = tid; i < a.nrows * kMaxBatch; i += kConsumerThreads) accs[i] = 0.f;
   }
+  if (a.flags & YPK_F_RESIDUAL) {
+    for (int i = tid; i < a.nrows * B; i += kConsumerThreads) {
+      const int b = i / a.nrows, r = i - b * a.nrows;
+      res_s[i] = __ldcg(reinterpret_cast<const uint16_t *>(a.res) + size_t(b0 + b) * a.ldres +
+                        a.out_col0 + a.row0 + r);
+    }
+  }
+  float ss[kMaxBatch];
+#pragma unroll
+  for (int b = 0; b < kMaxBatch; ++b) ss[b] = 0.f;
+
+  // lane-constant parts of the ldmatrix addresses
+  const int a_row = ((lane >> 3) & 1) * 8 + (lane & 7);      // row of the 16-row block
+  const int a_kof = ((lane >> 4) & 1) * 8;                   // k offset inside a 16-wide step
+  const int b_row = min(lane & 7, B - 1);                    // batch row (aliased beyond B)
+  const int b_kof = (lane >> 3) * 8;                         // k offset inside a 32-wide pair
+
   int pb = 0;
+  bool rnorm_ready = !norm;
   for (int k0 = 0; k0 < a.K; k0 += KC) {
     const int klen = min(KC, a.K - k0);
-    consumer_bar();  // everyone is done with the previous contents of xs / red
-    // stage x[b, k0 : k0+klen] * norm_w as fp32
-    for (int k = tid * 8; k < klen; k += kConsumerThreads * 8) {
-      float wn[8];
-      if (has_nw) {
-        const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(nw + k0 + k));
-        const uint32_t p[4] = {v.x, v.y, v.z, v.w};
+    consumer_bar();  // the previous pass is done with xs
+    // Stage x[b, k0:k0+klen] into shared memory as 16-bit values.  Without a norm this is a
+    // plain copy and goes global -> shared with 16-byte cp.async (one round trip whatever
+    // K).  With a norm the values pass through registers: multiplied by the norm weight and
+    // squared into the RMS statistics (fp32, as rmsnorm_hopper.cuh); the loads of four
+    // iterations are issued before the first is used.
+    if (!norm) {
+      for (int k = tid * 8; k < klen; k += kConsumerThreads * 8) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = unpack2(cvt_pair<F16>(p[i]));
-          wn[2 * i] = f.x;
-          wn[2 * i + 1] = f.y;
+        for (int b = 0; b < kMaxBatch; ++b) {
+          if (b < B) {
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                             smem_u32(xs + b * xpitch + k)),
+                         "l"(x + size_t(b) * a.ldx + k0 + k)
+                         : "memory");
+          }
         }
       }
+      asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+    } else {
+      constexpr int kU = 4;
+      for (int kb = tid * 8; kb < klen; kb += kConsumerThreads * 8 * kU) {
+        uint4 wnv[kU];
 #pragma unroll
-      for (int b = 0; b < B; ++b) {
-        const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(x + size_t(b) * a.ldx + k0 + k));
-        const uint32_t p[4] = {v.x, v.y, v.z, v.w};
-        float f[8];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 t2 = unpack2(cvt_pair<F16>(p[i]));
-          f[2 * i] = t2.x;
-          f[2 * i + 1] = t2.y;
+        for (int u = 0; u < kU; ++u) {
+          const int k = kb + u * kConsumerThreads * 8;
+          wnv[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (has_nw && k < klen) wnv[u] = __ldcg(reinterpret_cast<const uint4 *>(nw + k0 + k));
         }
-        if (has_nw) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) f[i] *= wn[i];
+        for (int b = 0; b < kMaxBatch; ++b) {
+          if (b < B) {
+            uint4 xv[kU];
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+              const int k = kb + u * kConsumerThreads * 8;
+              xv[u] = make_uint4(0u, 0u, 0u, 0u);
+              if (k < klen)
+                xv[u] = __ldcg(reinterpret_cast<const uint4 *>(x + size_t(b) * a.ldx + k0 + k));
+            }
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+              const int k = kb + u * kConsumerThreads * 8;
+              if (k < klen) {
+                const uint32_t p[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
+                const uint32_t q[4] = {wnv[u].x, wnv[u].y, wnv[u].z, wnv[u].w};
+                uint32_t o[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float2 f = unpack2(cvt_pair<F16>(p[i]));
+                  ss[b] += f.x * f.x + f.y * f.y;
+                  if (has_nw) {
+                    const float2 g = unpack2(cvt_pair<F16>(q[i]));
+                    o[i] = uint32_t(cvt_out<F16>(f.x * g.x)) |
+                           (uint32_t(cvt_out<F16>(f.y * g.y)) << 16);
+                  } else {
+                    o[i] = p[i];
+                  }
+                }
+                *reinterpret_cast<uint4 *>(xs + b * xpitch + k) = make_uint4(o[0], o[1], o[2], o[3]);
+              }
+            }
+          }
         }
-        float4 *dst = reinterpret_cast<float4 *>(xs + b * KC + k);
-        dst[0] = make_float4(f[0], f[1], f[2], f[3]);
-        dst[1] = make_float4(f[4], f[5], f[6], f[7]);
       }
     }
     consumer_bar();
+    if (tid == 0 && misc->prof_rec && k0 == 0) misc->prof_rec[4] = globaltimer();
 
     for (int r0 = 0; r0 < a.nrows; r0 += kRowBlock) {
       const int nr = min(kRowBlock, a.nrows - r0);
-      unsigned long long acc[B];
-#pragma unroll
-      for (int b = 0; b < B; ++b) acc[b] = 0ull;
+      float d[4] = {0.f, 0.f, 0.f, 0.f};
       for (int ks = 0; ks < klen; ks += kStageCols) {
         const int ncols = min(kStageCols, klen - ks);
         const bool got = wait_mbar(wc, &misc->full_bar[pos.slot], pos.phase);
-        if (got) {
-          linear_stage_math<B, F16>(smem + kOffRing + pos.slot * kStageBytes, xs, KC, ks, ncols,
-                                    nr, warp, lane, acc);
+        const int c0 = warp * kWarpCols;
+        if (got && c0 < ncols) {
+          const char *stage = smem + kOffRing + pos.slot * kStageBytes;
+          const char *ap = stage + a_row * kRowPitch + (c0 + a_kof) * 2;
+          const uint16_t *bp = xs + b_row * xpitch + ks + c0 + b_kof;
+          const int nsteps = min(kWarpCols, ncols - c0) / 32;  // pairs of 16-wide k steps
+          if (nsteps == kWarpCols / 32) {
+            // full slice: all twelve fragment loads first (the asm statements keep program
+            // order and a warp issues in order), then the eight MMAs on two accumulators
+            uint32_t bf[4][4], a0[4][4], a1[4][4];
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+              ldmatrix_x4(bf[s], bp + s * 32);
+              ldmatrix_x4(a0[s], ap + s * 64);
+              ldmatrix_x4(a1[s], ap + s * 64 + 32);
+            }
+            float e[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+              mma_16816<F16>(d, a0[s], bf[s][0], bf[s][1]);
+              mma_16816<F16>(e, a1[s], bf[s][2], bf[s][3]);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) d[i] += e[i];
+          } else {
+            for (int s = 0; s < nsteps; ++s) {
+              uint32_t bf[4], a0[4], a1[4];
+              ldmatrix_x4(bf, bp + s * 32);
+              ldmatrix_x4(a0, ap + s * 64);
+              ldmatrix_x4(a1, ap + s * 64 + 32);
+              mma_16816<F16>(d, a0, bf[0], bf[1]);
+              mma_16816<F16>(d, a1, bf[2], bf[3]);
+            }
+          }
         }
         __syncwarp();
         if (lane == 0 && got) mbar_arrive(&misc->empty_bar[pos.slot]);
         pos.advance();
       }
-      float *pp = part + pb * (kConsumerWarps * kRowBlock * kMaxBatch);
-#pragma unroll
-      for (int b = 0; b < B; ++b) {
-        const float2 f = unpack2(acc[b]);
-        pp[(warp * kRowBlock + lane) * B + b] = f.x + f.y;
+      if (tid == 0 && misc->prof_rec && r0 + kRowBlock >= a.nrows) misc->prof_rec[5] = globaltimer();
+      // this warp's partial tile: rows lane/4 and lane/4+8, batch columns (lane%4)*2, +1
+      float *pp = part + pb * kPartHalf + warp * (kRowBlock * kMaxBatch);
+      const int pr = lane >> 2, pc = (lane & 3) * 2;
+      *reinterpret_cast<float2 *>(pp + pr * kMaxBatch + pc) = make_float2(d[0], d[1]);
+      *reinterpret_cast<float2 *>(pp + (pr + 8) * kMaxBatch + pc) = make_float2(d[2], d[3]);
+      if (!rnorm_ready && !chunked) {
+        // statistics are complete after the single staging pass; accs is idle here
+        publish_rnorm(a, misc, accs, ss, B, tid);
+        rnorm_ready = true;
+      } else {
+        consumer_bar();
       }
-      consumer_bar();
+      const float *pall = part + pb * kPartHalf;
       auto summed = [&](int r, int b) {
         float s = 0.f;
 #pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w) s += pp[(w * kRowBlock + r) * B + b];
+        for (int w = 0; w < kConsumerWarps; ++w) s += pall[(w * kRowBlock + r) * kMaxBatch + b];
         return s;
       };
       if (!chunked) {
-        linear_epilogue<F16>(a, misc, r0, nr, b0, B, tid, summed);
+        linear_epilogue<F16>(a, misc, res_s, r0, nr, b0, B, tid, summed);
       } else {
         for (int idx = tid; idx < nr * B; idx += kConsumerThreads) {
           const int b = idx / nr, r = idx - b * nr;
-          accs[(r0 + r) * B + b] += summed(r, b);
+          accs[(r0 + r) * kMaxBatch + b] += summed(r, b);
         }
       }
       pb ^= 1;
     }
   }
   if (chunked) {
-    consumer_bar();
-    auto fromacc = [&](int r, int b) { return accs[r * B + b]; };
-    linear_epilogue<F16>(a, misc, 0, a.nrows, b0, B, tid, fromacc);
-  }
-}
-
-template <bool F16>
-__device__ __forceinline__ void linear_consume_dispatch(WaitCtx &wc, char *smem, Misc *misc,
-                                                        const LinearArgs &a, int b0, int bc,
-                                                        RingPos &pos) {
-  switch (bc) {
-    case 1: linear_consume_group<1, F16>(wc, smem, misc, a, b0, pos); break;
-    case 2: linear_consume_group<2, F16>(wc, smem, misc, a, b0, pos); break;
-    case 3: linear_consume_group<3, F16>(wc, smem, misc, a, b0, pos); break;
-    case 4: linear_consume_group<4, F16>(wc, smem, misc, a, b0, pos); break;
-    case 5: linear_consume_group<5, F16>(wc, smem, misc, a, b0, pos); break;
-    case 6: linear_consume_group<6, F16>(wc, smem, misc, a, b0, pos); break;
-    case 7: linear_consume_group<7, F16>(wc, smem, misc, a, b0, pos); break;
-    default: linear_consume_group<8, F16>(wc, smem, misc, a, b0, pos); break;
+    // statistics cover the whole K only now; the idle half of part is the scratch
+    if (norm) {
+      consumer_bar();
+      publish_rnorm(a, misc, part + pb * kPartHalf, ss, B, tid);
+    } else {
+      consumer_bar();
+    }
+    auto fromacc = [&](int r, int b) { return accs[r * kMaxBatch + b]; };
+    linear_epilogue<F16>(a, misc, res_s, 0, a.nrows, b0, B, tid, fromacc);
   }
 }
 
@@ -315,10 +384,11 @@ __device__ __forceinline__ void linear_consume(WaitCtx &wc, char *smem, Misc *mi
     const int b0 = bg * kMaxBatch;
     const int bc = min(kMaxBatch, batch - b0);
     if (a.flags & YPK_F_F16) {
-      linear_consume_dispatch<true>(wc, smem, misc, a, b0, bc, pos);
+      linear_consume_group<true>(wc, smem, misc, a, b0, bc, pos);
     } else {
-      linear_consume_dispatch<false>(wc, smem, misc, a, b0, bc, pos);
+      linear_consume_group<false>(wc, smem, misc, a, b0, bc, pos);
     }
+    if (bg + 1 < nbg) consumer_bar();  // smem of this group is dead before the next one starts
   }
 }
 

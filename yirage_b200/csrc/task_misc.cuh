@@ -140,7 +140,7 @@ __device__ __forceinline__ void silu_mul_task(const ypk_task &t, int batch) {
 // Continuous batching between iterations, one thread (the reference runs the same
 // logic in scheduler 0: persistent_kernel.cuh:169-322).  Retires finished requests and
 // frees their pages, compacts the active ones, admits new requests, chunks prefill to
-// the token budget (and to kMaxNewTokens per request), copies the iteration's input
+// the token budget (and to rt.max_new_tokens per request), copies the iteration's input
 // tokens and rebuilds qo_indptr / paged_kv_indptr / paged_kv_indices.
 // paged_kv_last_page_len is written in [1, page_size].
 // `first` skips the finalisation of a previous batch.  Returns the number of active
@@ -190,7 +190,7 @@ __device__ __noinline__ int prepare_next_batch(const Runtime &rt, bool first) {
     const int nold = rt.kv_indptr[i + 1] - kv;
     const int step = rt.step[req];
     int nnew = rt.prompt_len[req] - step;
-    nnew = nnew > 0 ? min(min(nnew, MT - ntok), kMaxNewTokens) : min(1, MT - ntok);
+    nnew = nnew > 0 ? min(min(nnew, MT - ntok), rt.max_new_tokens) : min(1, MT - ntok);
     // nreq <= i, so the indptr entries overwritten below have been consumed already.
     for (int j = 0; j < nold; ++j) rt.kv_indices[npages + j] = rt.kv_tmp[kv + j];
     rt.request_ids[nreq] = req;
@@ -213,7 +213,7 @@ __device__ __noinline__ int prepare_next_batch(const Runtime &rt, bool first) {
   while (nreq < MR && ntok < MT) {
     const int req = rt.bstate[0];
     if (req >= rt.total_req) break;
-    int nnew = min(min(rt.prompt_len[req], MT - ntok), kMaxNewTokens);
+    int nnew = min(min(rt.prompt_len[req], MT - ntok), rt.max_new_tokens);
     const int need = (nnew + PS - 1) / PS;
     if (npages + need > MP || (tail - head) < need) break;  // no page budget yet
     rt.request_ids[nreq] = req;

@@ -4,11 +4,14 @@
 // A handle created with cfg.device == -1 is a host-only handle: it validates and
 // resolves graphs exactly like a real one but owns no device memory and cannot launch.
 // It exists so that graph validation can be exercised on a machine without a GPU.
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdarg.h>
+#include <stdlib.h>
 #include <stdio.h>
 #include <string.h>
 
+#include <algorithm>
 #include <string>
 #include <vector>
 
@@ -39,11 +42,14 @@ struct ypk_handle {
   std::vector<int32_t> queue, queue_off;
   int num_events = 0;
   int end_event = -1, end_count = 0;
+  int max_new_tokens = kMaxNewTokens;  // prefill chunk per request the attention tasks allow
   bool graph_loaded = false;
   // device state
   ypk_task *d_tasks = nullptr;
   int *d_queue = nullptr, *d_queue_off = nullptr;
   unsigned long long *d_events = nullptr, *d_ctrl = nullptr;
+  void *d_tmaps = nullptr;       // CUtensorMap[], one per distinct K / V cache tensor
+  std::vector<uint64_t> tmap_keys;  // device address of the cache each map describes
   int *d_request_ids = nullptr, *d_page_queue = nullptr, *d_kv_tmp = nullptr, *d_bstate = nullptr;
   // progress
   long long base_iter = 0;
@@ -176,9 +182,10 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
       if (h->cfg.page_size <= 0 || h->cfg.page_size % kKvTile)
         return fail(h, YPK_ERR_UNSUPPORTED, "ATTENTION needs page_size %% %d == 0 (got %d)",
                     kKvTile, h->cfg.page_size);
-      if (max_rows < G * kMaxNewTokens)
+      if (max_rows < std::min(G * kMaxNewTokens, kMaxAttnRows))
         return fail(h, YPK_ERR_INVALID, "task %d: ATTENTION scratch rows %d < %d", ti, max_rows,
-                    G * kMaxNewTokens);
+                    std::min(G * kMaxNewTokens, kMaxAttnRows));
+      h->max_new_tokens = std::min(h->max_new_tokens, kMaxAttnRows / G);
       if (!h->cfg.qo_indptr || !h->cfg.paged_kv_indptr || !h->cfg.paged_kv_indices ||
           !h->cfg.paged_kv_last_page_len)
         return fail(h, YPK_ERR_INVALID, "ATTENTION needs the paged-KV meta tensors in ypk_config");
@@ -252,7 +259,38 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
   return YPK_OK;
 }
 
+// Rank-3 tiled tensor map over a KV cache [pages*page_size tokens][kv heads][128] bf16:
+// box = 64 dims x 1 head x 64 tokens, 128-byte swizzle.
+int encode_kv_tmap(ypk_handle *h, void *base, int hkv, CUtensorMap *out) {
+  typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                               const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                               const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn fn = nullptr;
+  if (!fn) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !p)
+      return fail(h, YPK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    fn = reinterpret_cast<EncodeFn>(p);
+  }
+  const cuuint64_t tokens = cuuint64_t(h->cfg.max_num_pages) * h->cfg.page_size;
+  const cuuint64_t dims[3] = {cuuint64_t(kHeadDim), cuuint64_t(hkv), tokens};
+  const cuuint64_t strides[2] = {cuuint64_t(kHeadDim) * 2, cuuint64_t(hkv) * kHeadDim * 2};
+  const cuuint32_t box[3] = {64, 1, cuuint32_t(kKvTile)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(h, YPK_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", int(r));
+  return YPK_OK;
+}
+
 void free_graph(ypk_handle *h) {
+  if (!h->host_only && h->d_tmaps) cudaFree(h->d_tmaps);
+  h->d_tmaps = nullptr;
+  h->tmap_keys.clear();
   if (!h->host_only) {
     if (h->d_tasks) cudaFree(h->d_tasks);
     if (h->d_queue) cudaFree(h->d_queue);
@@ -513,6 +551,7 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
       seen[size_t(ti)] = 1;
     }
   }
+  h->max_new_tokens = kMaxNewTokens;
   std::vector<ypk_task> resolved(static_cast<size_t>(num_tasks));
   std::vector<int> trig_count(size_t(num_events), 0), last_trig(size_t(num_events), -1);
   for (int i = 0; i < num_tasks; ++i) {
@@ -535,10 +574,41 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
       return fail(h, YPK_ERR_INVALID, "task %d waits for event %d that task %d triggers", i,
                   t.dep_event, last_trig[size_t(t.dep_event)]);
   }
+  // tensor maps for the K / V caches the attention tasks read (one per distinct tensor)
+  std::vector<uint64_t> keys;
+  std::vector<int> key_hkv;
+  for (int i = 0; i < num_tasks; ++i) {
+    ypk_task &t = resolved[size_t(i)];
+    if (t.type != YPK_TASK_ATTENTION) continue;
+    for (int which = 0; which < 2; ++which) {
+      const uint64_t addr = t.ptr[1 + which];
+      size_t k = 0;
+      while (k < keys.size() && keys[k] != addr) ++k;
+      if (k == keys.size()) {
+        keys.push_back(addr);
+        key_hkv.push_back(t.iarg[5]);
+      } else if (key_hkv[k] != t.iarg[5]) {
+        return fail(h, YPK_ERR_INVALID, "task %d: cache tensor used with two head counts", i);
+      }
+      t.iarg[9 + which] = int(k);
+    }
+  }
   h->end_event = tasks[num_tasks - 1].trig_event;
   h->end_count = h->end_event >= 0 ? trig_count[size_t(h->end_event)] : 0;
 
   free_graph(h);
+  if (!keys.empty() && !h->host_only) {
+    std::vector<CUtensorMap> maps(keys.size());
+    for (size_t k = 0; k < keys.size(); ++k) {
+      int rc = encode_kv_tmap(h, reinterpret_cast<void *>(keys[k]), key_hkv[k], &maps[k]);
+      if (rc) return rc;
+    }
+    CUDA_TRY(h, cudaSetDevice(h->cfg.device));
+    CUDA_TRY(h, cudaMalloc(&h->d_tmaps, sizeof(CUtensorMap) * maps.size()));
+    CUDA_TRY(h, cudaMemcpy(h->d_tmaps, maps.data(), sizeof(CUtensorMap) * maps.size(),
+                           cudaMemcpyHostToDevice));
+  }
+  h->tmap_keys = keys;
   h->tasks.swap(resolved);
   h->queue.assign(queue, queue + num_tasks);
   h->queue_off.assign(queue_off, queue_off + num_queues + 1);
@@ -641,8 +711,23 @@ int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_
   rt.resume_pending = h->resume_pending ? 1 : 0;
   rt.rank = c.rank;
   rt.world = c.world_size;
+  rt.max_new_tokens = h->max_new_tokens;
   rt.end_event = h->end_event;
   rt.end_count = h->end_count;
+  rt.tmaps = h->d_tmaps;
+  rt.prof = nullptr;
+  rt.prof_stride = 0;
+  if (c.profiler_buffer) {
+    int longest = 0;
+    for (size_t w = 0; w + 1 < h->queue_off.size(); ++w)
+      longest = std::max(longest, h->queue_off[w + 1] - h->queue_off[w]);
+    const uint64_t need = uint64_t(h->num_workers) * longest * 64u;
+    if (need > c.profiler_bytes)
+      return fail(h, YPK_ERR_INVALID, "profiler buffer has %llu bytes, the graph needs %llu",
+                  (unsigned long long)c.profiler_bytes, (unsigned long long)need);
+    rt.prof = static_cast<unsigned long long *>(c.profiler_buffer);
+    rt.prof_stride = longest;
+  }
   // The control word a new launch starts from: last completed iteration, stopped, and
   // the size of the batch that is waiting (if any).
   const unsigned long long words[kCtrlWords] = {

@@ -32,6 +32,7 @@ MAX_TASK_ROWS = 256          # kMaxAccRows in device_common.cuh
 KV_TILE = 64
 HEAD_DIM = 128
 MAX_NEW_TOKENS = 8           # kMaxNewTokens
+MAX_ATTN_ROWS = 32           # kMaxAttnRows
 ATTN_ROW_FLOATS = HEAD_DIM + 4   # kAttnRowFloats in task_attention.cuh
 MAX_SPLITS = 16
 
@@ -375,7 +376,7 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                 raise ValueError("packed qkv width does not match the head counts")
             max_tiles = (max_seq_length + KV_TILE - 1) // KV_TILE
             nsplit = max(1, min(W // max(1, max_requests * hkv), max_tiles, MAX_SPLITS))
-            max_rows = G * MAX_NEW_TOKENS
+            max_rows = min(G * MAX_NEW_TOKENS, MAX_ATTN_ROWS)
             if nsplit > 1:
                 need = max_requests * hkv * nsplit * max_rows * ATTN_ROW_FLOATS
                 if attn_scratch is None or attn_scratch.dims[0] < need:

@@ -429,9 +429,24 @@ class PersistentKernel:
             stream = torch.cuda.current_stream()
         sp = stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
         self._handle.launch(sp, int(kwargs.get("max_iterations", 0)), int(kwargs.get("batch", 1)))
-        if self.profiler_tensor is not None and self.trace_name is not None:
+        if self.profiler_tensor is not None and self.trace_name:
             from .profiler_persistent import export_trace
-            export_trace(self.profiler_tensor, self.trace_name or f"yirage_{self.mpi_rank}")
+            g = self.lower()
+            export_trace(self.profiler_tensor, self.trace_name, self._handle.cfg.num_workers,
+                         self.profile_stride(), g.tasks)
+
+    def profile_stride(self):
+        """Records per worker in the profiler buffer (= the longest worker queue)."""
+        g = self.lower()
+        return max(b - a for a, b in zip(g.queue_off[:-1], g.queue_off[1:]))
+
+    def profile_summary(self):
+        """Per-operator timing of the last iteration (needs profiler_tensor)."""
+        from .profiler_persistent import decode_records, summarize
+        g = self.lower()
+        recs = decode_records(self.profiler_tensor, self._handle.cfg.num_workers,
+                              self.profile_stride())
+        return summarize(recs, g.tasks, g.ops)
 
     def read_tensor(self, t: DTensor) -> torch.Tensor:
         """Copy of a tensor of the graph (attached or runtime-owned) as a torch tensor."""
