@@ -73,7 +73,7 @@ enum ypk_task_type {
 /* ypk_task.flags */
 #define YPK_F_NORM 0x1u        /* LINEAR: fold RMSNorm(x)*norm_w in front  */
 #define YPK_F_RESIDUAL 0x2u    /* LINEAR: add residual[b, n]               */
-#define YPK_F_SILU_MUL 0x4u    /* LINEAR: rows come as 8 gate + 8 up       */
+#define YPK_F_SILU_MUL 0x4u    /* LINEAR: rows come as 2 gate + 2 up       */
 #define YPK_F_F16 0x8u         /* operands are fp16 instead of bf16        */
 #define YPK_F_ROPE 0x10u       /* ATTENTION: rotate new q/k                */
 #define YPK_F_NORM_NOWEIGHT 0x40u /* LINEAR: RMSNorm without a weight      */

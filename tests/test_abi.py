@@ -73,7 +73,7 @@ def test_bad_graphs_are_rejected_with_a_message(native_lib):
         "reaches byte": [linear_task(row0=48, nrows=32)],           # rows past the weight
         "unbound tensor slot": [linear_task(w=7)],
         "operand 3 is required": [linear_task(flags=N.F_NORM)],      # norm weight missing
-        "16-row granules": [linear_task(nrows=24, flags=N.F_SILU_MUL)],
+        "4-row granules": [linear_task(nrows=30, flags=N.F_SILU_MUL)],
         "waits for 2 triggers": [linear_task(trig=0), linear_task(dep=0, depc=2, trig=1)],
     }
     for needle, tasks in cases.items():

@@ -34,9 +34,9 @@ def test_demo_layer_sequence_fuses_to_five_operators_per_layer():
     assert gate_up.flags & N.F_NORM and gate_up.flags & N.F_SILU_MUL
     assert gate_up.t["out"].name == "silu_mul_out", "mlp_mid must not be materialised"
     assert down.flags & N.F_RESIDUAL
-    # fused gate/up weights are interleaved in 8-row granules, qkv per kv head
+    # fused gate/up weights are interleaved in 2-row granules, qkv per kv head
     gran = {sh["dst"].name: sh["gran"] for sh in g.shuffles}
-    assert gran["layer_0_gatedup_proj"] == [8, 8]
+    assert gran["layer_0_gatedup_proj"] == [2, 2]
     assert gran["layer_0_qkv_proj"] == [4 * 128, 128, 128]
 
 

@@ -43,6 +43,11 @@ constexpr int kKvBoxBytes = kKvTile * 128;       // 8192
 constexpr int kVOffset = 2 * kKvBoxBytes;        // V boxes follow the K boxes
 constexpr int kMaxNewTokens = 8;                 // new tokens of one request per iteration
 constexpr int kMaxAttnRows = 32;                 // new tokens x q heads per kv head, per task
+// Cached tiles one attention split should hold.  A warp needs ~2.8 us per tile, so a CTA
+// with more tiles than it can overlap runs in rounds; measured on Llama-3-8B at ~600 tokens
+// of context, 2..5 tiles per split all beat one CTA per head by ~4 us per layer.
+constexpr int kAttnTilesPerSplit = 4;
+constexpr int kSiluGran = 2;                     // fused gate/up rows come as 2 gate + 2 up
 
 // Shared-memory map (dynamic shared memory, bytes).
 constexpr int kOffRing = 0;

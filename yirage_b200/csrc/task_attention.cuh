@@ -49,9 +49,7 @@ __device__ __forceinline__ AttnShape attn_shape(const Runtime &rt, const ypk_tas
   s.seq_len = (npages - 1) * rt.page_size + __ldcg(rt.kv_last_len + r);
   s.cached = s.seq_len - s.T;
   const int tiles = (s.cached + kKvTile - 1) / kKvTile;
-  // a split is worth its partial write and its share of the cross-CTA combine only once a
-  // CTA has two tiles per consumer warp; below that one CTA takes the whole sequence
-  const int want = min(nsplit, (tiles + 2 * kConsumerWarps - 1) / (2 * kConsumerWarps));
+  const int want = min(nsplit, (tiles + kAttnTilesPerSplit - 1) / kAttnTilesPerSplit);
   const int tps = max(1, (tiles + max(want, 1) - 1) / max(want, 1));
   s.nact = tiles > 0 ? (tiles + tps - 1) / tps : 1;
   s.active = s.T > 0 && s.T <= kMaxNewTokens && s.T * t.iarg[4] <= kMaxAttnRows && npages > 0 &&

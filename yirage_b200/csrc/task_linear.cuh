@@ -133,11 +133,11 @@ __device__ __forceinline__ void linear_epilogue(const LinearArgs &a, const Misc 
                                                 int bc, int tid, ValFn val) {
   const bool norm = (a.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT)) != 0;
   if (a.flags & YPK_F_SILU_MUL) {
-    const int nout = nr >> 1;  // 16-row granules: 8 gate rows then 8 up rows
+    const int nout = nr >> 1;  // granules of kSiluGran gate rows followed by kSiluGran up rows
     for (int idx = tid; idx < nout * bc; idx += kConsumerThreads) {
       const int b = idx / nout, o = idx - b * nout;
-      const int rg = (o >> 3) * 16 + (o & 7);
-      float g = val(rg, b), u = val(rg + 8, b);
+      const int rg = (o / kSiluGran) * (2 * kSiluGran) + (o % kSiluGran);
+      float g = val(rg, b), u = val(rg + kSiluGran, b);
       if (norm) {
         g *= misc->rnorm[b];
         u *= misc->rnorm[b];

@@ -147,8 +147,9 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
         return fail(h, YPK_ERR_INVALID, "task %d: LINEAR strides (ldx=%d ldw=%d K=%d)", ti, ldx,
                     ldw, K);
       const bool silu = in.flags & YPK_F_SILU_MUL;
-      if (silu && (row0 % 16 || nrows % 16))
-        return fail(h, YPK_ERR_INVALID, "task %d: SILU_MUL rows must come in 16-row granules", ti);
+      if (silu && (row0 % (2 * kSiluGran) || nrows % (2 * kSiluGran)))
+        return fail(h, YPK_ERR_INVALID, "task %d: SILU_MUL rows must come in %d-row granules", ti,
+                    2 * kSiluGran);
       if ((in.flags & YPK_F_NORM) && (in.flags & YPK_F_NORM_NOWEIGHT))
         return fail(h, YPK_ERR_INVALID, "task %d: NORM and NORM_NOWEIGHT together", ti);
       const int ocols0 = silu ? oc0 + row0 / 2 : oc0 + row0;

@@ -35,6 +35,7 @@ MAX_NEW_TOKENS = 8           # kMaxNewTokens
 MAX_ATTN_ROWS = 32           # kMaxAttnRows
 ATTN_ROW_FLOATS = HEAD_DIM + 4   # kAttnRowFloats in task_attention.cuh
 MAX_SPLITS = 16
+SILU_GRAN = 2                # kSiluGran: fused gate/up rows come as 2 gate + 2 up
 
 
 @dataclass
@@ -180,7 +181,7 @@ def fuse(regs: List[RegisteredTask], default_eps: float) -> List[FusedOp]:
             if (res is None and nxt is not None and canonical_name(nxt.name) == "silu_mul"
                     and nxt.operands[0] is y and w.kind == "shuffled" and len(w.sources) == 2
                     and w.sources[0].dims == w.sources[1].dims
-                    and w.sources[0].dims[0] % 8 == 0 and _dead_after(regs, k + 1, y)):
+                    and w.sources[0].dims[0] % SILU_GRAN == 0 and _dead_after(regs, k + 1, y)):
                 flags |= N.F_SILU_MUL
                 t["out"] = nxt.operands[1]
                 srcs.append(nxt)
@@ -318,11 +319,11 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
             if (flags & N.F_RESIDUAL) and world_size > 1 and rank != 0:
                 # partial sums are added across ranks afterwards: the residual goes in once
                 flags &= ~N.F_RESIDUAL
-            gran = 16 if silu else 1
+            gran = 2 * SILU_GRAN if silu else 1
             if w.kind == "shuffled" and id(w) not in shuffled_done:
                 srcs = w.sources
                 if silu:
-                    g = [8, 8]
+                    g = [SILU_GRAN, SILU_GRAN]
                 else:
                     if any(s.dims[0] % w.num_groups for s in srcs):
                         raise ValueError("shuffle_tensors: rows not divisible by num_groups")
@@ -331,14 +332,14 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                       "gran": g, "row_bytes": K * w.dtype.itemsize}
                 shuffles.append(sh)
                 shuffled_done[id(w)] = sh
-            elif w.kind == "shuffled" and silu and shuffled_done[id(w)]["gran"] != [8, 8]:
+            elif w.kind == "shuffled" and silu and shuffled_done[id(w)]["gran"] != [SILU_GRAN, SILU_GRAN]:
                 raise ValueError("a shuffled weight is used both fused and unfused")
             expect_out = Nrows // 2 if silu else Nrows
             if o.dims[1] < expect_out:
                 raise ValueError(f"linear: output width {o.dims[1]} < {expect_out}")
             units = Nrows // gran
             if Nrows % gran:
-                raise ValueError("fused gate/up weight rows must be a multiple of 16")
+                raise ValueError(f"fused gate/up weight rows must be a multiple of {gran}")
             unit_bytes = gran * K * 2
             counts = level_partition(units, unit_bytes, loads)
             r = 0
