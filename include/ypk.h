@@ -218,6 +218,25 @@ int ypk_wait(ypk_handle *h);
 
 int ypk_get_status(ypk_handle *h, ypk_status *out);
 
+/* Greedy sampling for callers that cannot let a library allocate device memory (a host
+ * whose own allocator owns the whole GPU, or a path where the device-wide synchronisation
+ * of cudaMalloc / cudaFree is not acceptable).  No counterpart in the reference: there the
+ * chunk buffers of the two arg-max tasks are cudaMalloc'ed by generated code.
+ *
+ * out_tokens[b] = index of the largest of logits[b, 0:vocab] (bf16, row stride ld
+ * elements), lowest index on ties, for b < batch.  All pointers are device pointers on the
+ * current device; the kernel is enqueued on `stream` and the call does not wait for it.
+ * Needs no handle.  The per-chunk partial results go to a fixed array inside the library
+ * (about 100 KB per GPU, held until the process exits), which is why batch is limited to
+ * 64 rows; larger batches are refused with YPK_ERR_UNSUPPORTED.  The call makes no
+ * cudaMalloc / cudaFree and calls no allocating library routine.
+ * The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress); make that first call outside any stream capture.
+ * All calls share the one array: two calls whose kernels can overlap on the GPU (different
+ * streams, no dependency) race on it - serialise them. */
+int ypk_argmax_noalloc(const void *logits_bf16, int32_t batch, int32_t vocab, int64_t ld,
+                       int64_t *out_tokens, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -105,6 +105,8 @@ SYMBOLS = {
     "ypk_launch_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32]),
     "ypk_wait": (C.c_int, [C.c_void_p]),
     "ypk_get_status": (C.c_int, [C.c_void_p, C.POINTER(Status)]),
+    "ypk_argmax_noalloc": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_void_p,
+                                     C.c_void_p]),
 }
 
 _lib = None

@@ -16,6 +16,7 @@
 #include <vector>
 
 #include "../../include/ypk.h"
+#include "argmax_noalloc.cuh"
 #include "megakernel.cuh"
 
 using namespace ypk;
@@ -795,6 +796,48 @@ int ypk_launch(ypk_handle *h, void *stream, int32_t max_iterations, int32_t batc
   int rc = ypk_launch_async(h, stream, max_iterations, batch);
   if (rc) return rc;
   return ypk_wait(h);
+}
+
+int ypk_argmax_noalloc(const void *logits_bf16, int32_t batch, int32_t vocab, int64_t ld,
+                       int64_t *out_tokens, void *stream) {
+  if (!logits_bf16 || !out_tokens)
+    return fail(nullptr, YPK_ERR_INVALID, "argmax_noalloc: null logits or output");
+  if (batch < 1 || batch > kNoAllocMaxBatch)
+    return fail(nullptr, YPK_ERR_UNSUPPORTED,
+                "argmax_noalloc: batch %d is outside 1..%d (the built-in scratch is fixed)", batch,
+                kNoAllocMaxBatch);
+  if (vocab < 1 || ld < vocab || ld > 0x7fffffff)
+    return fail(nullptr, YPK_ERR_INVALID, "argmax_noalloc: vocab %d / row stride %lld", vocab,
+                (long long)ld);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64)
+    return fail(nullptr, YPK_ERR_CUDA, "argmax_noalloc: no current device (%s)",
+                cudaGetErrorString(e));
+  // Set-up, once per device, with that device current: the device address of the array.
+  static unsigned char *scratch_of[64] = {nullptr};
+  if (!scratch_of[dev]) {
+    void *p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || !p)
+      return fail(nullptr, YPK_ERR_CUDA, "argmax_noalloc: cudaGetSymbolAddress: %s",
+                  cudaGetErrorString(e));
+    scratch_of[dev] = static_cast<unsigned char *>(p);
+  }
+  unsigned char *scratch = scratch_of[dev];
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the arrival counter has to start at zero even if an earlier call was cut short
+  e = cudaMemsetAsync(scratch + kNoAllocCtrOff, 0, 256, st);
+  if (e != cudaSuccess)
+    return fail(nullptr, YPK_ERR_CUDA, "argmax_noalloc: clearing the counter: %s",
+                cudaGetErrorString(e));
+  argmax_noalloc_kernel<<<kNoAllocParts, kConsumerThreads, 0, st>>>(
+      static_cast<const uint16_t *>(logits_bf16), batch, vocab, (long long)ld,
+      reinterpret_cast<long long *>(out_tokens), scratch);
+  e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return fail(nullptr, YPK_ERR_CUDA, "argmax_noalloc: launch: %s", cudaGetErrorString(e));
+  return YPK_OK;
 }
 
 int ypk_get_status(ypk_handle *h, ypk_status *out) {
