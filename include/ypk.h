@@ -103,6 +103,10 @@ enum ypk_task_type {
  * ARGMAX_PARTIAL: ptr = {logits, part_val, part_idx}; iarg = {col0, ncols,
  *                  ldlogits, part, nparts}
  * ARGMAX_REDUCE: ptr = {part_val, part_idx, out(int64)}; iarg = {nparts}
+ * ALLREDUCE: ptr = {in, buf, out, signals} (buf, signals from the symmetric arena;
+ *          buf = [2][world][max_tokens][hidden] 16-bit, signals uint64[])
+ *          iarg = {col0, ncols, ld_in, ld_out, hidden, max_tokens, half, signal index,
+ *                  world, rank}
  * RMSNORM: ptr = {x, w, out}; iarg = {K, row0, nrows, ldx, ldout}; farg = {eps}
  * SILU_MUL: ptr = {in, out}; iarg = {col0, ncols, group, ldin, ldout}
  * The number of batch rows is the active-token count of the iteration (mode 1) or the
@@ -189,6 +193,20 @@ int ypk_shuffle_tensor(ypk_handle *h, int32_t dst_slot, const char *name, int32_
                        const int32_t *src_slots, const int32_t *rows, const int32_t *gran,
                        uint64_t row_bytes);
 int ypk_tensor_ptr(ypk_handle *h, int32_t slot, void **dev_ptr, uint64_t *bytes);
+
+/* Tensor parallelism.  Every rank owns one "symmetric arena" of device memory; tensors
+ * allocated from it sit at the same offset on every rank (allocate them in the same order
+ * everywhere), so a kernel reaches a peer's copy as peer_arena_base + own offset.  Replaces
+ * the NVSHMEM symmetric heap of the reference (nvshmem_malloc for io_category
+ * "nvshmem_tensor", src/kernel/runtime.cc:797; bootstrap persistent_kernel.cuh:1072-1085).
+ * ypk_comm_export writes a 64-byte CUDA IPC handle of the own arena; the caller moves the
+ * handles between the ranks' processes (any transport) and gives each peer's handle to
+ * ypk_comm_import, which maps that peer's arena.  All of this before the first launch. */
+#define YPK_IPC_HANDLE_BYTES 64
+int ypk_comm_init(ypk_handle *h, uint64_t arena_bytes);
+int ypk_alloc_symmetric(ypk_handle *h, int32_t slot, const char *name, uint64_t bytes);
+int ypk_comm_export(ypk_handle *h, void *handle_out);
+int ypk_comm_import(ypk_handle *h, int32_t peer_rank, const void *handle);
 /* Device-to-device copy of `bytes` bytes of a registered tensor, starting at byte_off,
  * into caller memory on the same device (inspection of runtime-owned intermediates;
  * the reference has no counterpart, its intermediates are unreachable from Python). */

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from oracle import decode_oracle as O
-from tests.util import assert_close
+from tests.util import assert_close, oracle_weights, replay_against_oracle
 from yirage_b200 import llama
 
 pytestmark = pytest.mark.gpu
@@ -16,16 +16,6 @@ def tiny_shape(layers=2):
     return llama.LlamaShape(hidden_size=512, intermediate_size=1024, num_hidden_layers=layers,
                             num_attention_heads=8, num_key_value_heads=2, vocab_size=3000,
                             rms_norm_eps=1e-5)
-
-
-def oracle_weights(shape, w):
-    c = lambda t: t.detach().cpu()
-    return O.LlamaWeights(
-        embed=c(w["embed"]),
-        layers=[{k: c(v) for k, v in L.items()} for L in w["layers"]],
-        final_norm=c(w["final_norm"]), lm_head=c(w["lm_head"]),
-        num_q_heads=shape.num_attention_heads, num_kv_heads=shape.num_key_value_heads,
-        head_dim=shape.head_dim, eps=shape.rms_norm_eps, rope_theta=shape.rope_theta)
 
 
 def run_generation(prompt_lens, max_seq, *, max_requests, max_tokens, max_pages, page_size=64,
@@ -55,43 +45,10 @@ def run_generation(prompt_lens, max_seq, *, max_requests, max_tokens, max_pages,
     assert status.error == 0 and status.finished == 1
 
     ow = oracle_weights(shape, w)
-    bs = O.BatchState(total_requests=R, max_requests=max_requests, max_tokens=max_tokens,
-                      max_pages=max_pages, page_size=page_size, max_seq_length=max_seq, eos=-1,
-                      tokens=tokens_ref, prompt_len=list(prompt_lens))
-    kc = [torch.zeros(max_pages, page_size, shape.num_key_value_heads, shape.head_dim,
-                      dtype=torch.bfloat16) for _ in range(layers)]
-    vc = [torch.zeros_like(k) for k in kc]
-    cos, sin = O.rope_tables(shape.head_dim, shape.rope_theta, max(max_seq, 64))
     got = tokens.cpu()
-    # Teacher-forced replay: the oracle sees the device's own token history, so every
-    # iteration is checked on identical inputs and one flipped near-tie cannot cascade.
-    iters, exact, total, out, last_logits = 0, 0, 0, None, None
-    while True:
-        ntok = bs.prepare_next_batch(out)
-        if ntok == 0:
-            break
-        trace = []
-        pred = O.decode_iteration(ow, bs, kc, vc, cos, sin, rounding=None, logits_out=trace)
-        logits = trace[0]
-        out = list(pred)
-        for i in range(max_requests):
-            req = bs.request_ids[i]
-            if req < 0:
-                continue
-            for j in range(bs.qo_indptr[i], bs.qo_indptr[i + 1]):
-                pos = bs.step[req] + (j - bs.qo_indptr[i]) + 1
-                if pos >= prompt_lens[req] and pos < max_seq:
-                    dev_tok = int(got[req, pos])
-                    total += 1
-                    exact += int(dev_tok == pred[j])
-                    gap = float(logits[j].max() - logits[j, dev_tok])
-                    # ids are bit-exact whenever the oracle's top-2 are separable in bf16;
-                    # inside the activation tolerance either of two tied tokens is accepted
-                    assert gap <= O.ATOL + O.RTOL * float(logits[j].max().abs()), \
-                        f"request {req} position {pos}: device token {dev_tok} is {gap:.3f} below the max"
-                    out[j] = dev_tok
-        last_logits = logits
-        iters += 1
+    iters, bs, last_logits, exact, total = replay_against_oracle(
+        shape, ow, got, prompt_lens, max_seq=max_seq, max_requests=max_requests,
+        max_tokens=max_tokens, max_pages=max_pages, page_size=page_size)
     assert status.iterations == iters, "device and oracle disagree on the iteration count"
     assert st["meta"]["step"].cpu().tolist() == bs.step
     # exact agreement is not guaranteed (bf16 near-ties are accepted above); a low rate

@@ -25,3 +25,60 @@ def onepass_kernel(max_tokens, meta=None, max_requests=1, max_pages=1, page_size
 def assert_close(got, want, what=""):
     ok, max_abs, ratio = O.within_tolerance(got.float().cpu(), want.float().cpu())
     assert ok, f"{what}: max abs err {max_abs:.4g}, worst err/bound {ratio:.3g}"
+
+
+def oracle_weights(shape, w):
+    """Device weight dictionary (unsharded) -> oracle LlamaWeights on CPU."""
+    c = lambda t: t.detach().cpu()
+    return O.LlamaWeights(
+        embed=c(w["embed"]), layers=[{k: c(v) for k, v in L.items()} for L in w["layers"]],
+        final_norm=c(w["final_norm"]), lm_head=c(w["lm_head"]),
+        num_q_heads=shape.num_attention_heads, num_kv_heads=shape.num_key_value_heads,
+        head_dim=shape.head_dim, eps=shape.rms_norm_eps, rope_theta=shape.rope_theta)
+
+
+def replay_against_oracle(shape, ow, device_tokens, prompt_lens, *, max_seq, max_requests,
+                          max_tokens, max_pages, page_size, max_new_per_request=8):
+    """Teacher-forced replay: the fp32 oracle runs the same batcher and graph but sees the
+    device's own token history, so every iteration is checked on identical inputs and one
+    flipped near-tie cannot cascade.  Every device token must be the oracle arg-max or tie
+    with it inside the activation tolerance.  Returns (iterations, batch state, logits of
+    the last iteration, exact matches, sampled tokens)."""
+    R = len(prompt_lens)
+    tokens_ref = torch.zeros(R, max_seq, dtype=torch.int64)
+    for r, n in enumerate(prompt_lens):
+        tokens_ref[r, :n] = device_tokens[r, :n]
+    bs = O.BatchState(total_requests=R, max_requests=max_requests, max_tokens=max_tokens,
+                      max_pages=max_pages, page_size=page_size, max_seq_length=max_seq, eos=-1,
+                      tokens=tokens_ref, prompt_len=list(prompt_lens),
+                      max_new_per_request=max_new_per_request)
+    L = len(ow.layers)
+    kc = [torch.zeros(max_pages, page_size, ow.num_kv_heads, ow.head_dim, dtype=torch.bfloat16)
+          for _ in range(L)]
+    vc = [torch.zeros_like(k) for k in kc]
+    cos, sin = O.rope_tables(ow.head_dim, ow.rope_theta, max(max_seq, 64))
+    iters, exact, total, out, last_logits = 0, 0, 0, None, None
+    while True:
+        if bs.prepare_next_batch(out) == 0:
+            break
+        trace = []
+        pred = O.decode_iteration(ow, bs, kc, vc, cos, sin, rounding=None, logits_out=trace)
+        logits = trace[0]
+        out = list(pred)
+        for i in range(max_requests):
+            req = bs.request_ids[i]
+            if req < 0:
+                continue
+            for j in range(bs.qo_indptr[i], bs.qo_indptr[i + 1]):
+                pos = bs.step[req] + (j - bs.qo_indptr[i]) + 1
+                if pos >= prompt_lens[req] and pos < max_seq:
+                    dev_tok = int(device_tokens[req, pos])
+                    total += 1
+                    exact += int(dev_tok == pred[j])
+                    gap = float(logits[j].max() - logits[j, dev_tok])
+                    assert gap <= O.ATOL + O.RTOL * float(logits[j].max().abs()), \
+                        f"request {req} position {pos}: device token {dev_tok} is {gap:.3f} below the max"
+                    out[j] = dev_tok
+        last_logits = logits
+        iters += 1
+    return iters, bs, last_logits, exact, total

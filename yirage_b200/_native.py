@@ -95,6 +95,10 @@ SYMBOLS = {
     "ypk_shuffle_tensor": (C.c_int, [C.c_void_p, C.c_int32, C.c_char_p, C.c_int32,
                                      C.POINTER(C.c_int32), C.POINTER(C.c_int32),
                                      C.POINTER(C.c_int32), C.c_uint64]),
+    "ypk_comm_init": (C.c_int, [C.c_void_p, C.c_uint64]),
+    "ypk_alloc_symmetric": (C.c_int, [C.c_void_p, C.c_int32, C.c_char_p, C.c_uint64]),
+    "ypk_comm_export": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "ypk_comm_import": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
     "ypk_tensor_ptr": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(C.c_void_p),
                                  C.POINTER(C.c_uint64)]),
     "ypk_read_tensor": (C.c_int, [C.c_void_p, C.c_int32, C.c_uint64, C.c_void_p, C.c_uint64]),
@@ -175,6 +179,20 @@ class Handle:
 
     def alloc(self, slot, name, nbytes):
         check(self._h, self.lib.ypk_alloc_tensor(self._h, slot, name.encode(), nbytes))
+
+    def comm_init(self, nbytes):
+        check(self._h, self.lib.ypk_comm_init(self._h, nbytes))
+
+    def alloc_symmetric(self, slot, name, nbytes):
+        check(self._h, self.lib.ypk_alloc_symmetric(self._h, slot, name.encode(), nbytes))
+
+    def comm_export(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        check(self._h, self.lib.ypk_comm_export(self._h, buf))
+        return buf.raw
+
+    def comm_import(self, peer, handle: bytes):
+        check(self._h, self.lib.ypk_comm_import(self._h, peer, C.c_char_p(handle)))
 
     def shuffle(self, dst_slot, name, src_slots, rows, gran, row_bytes):
         n = len(src_slots)

@@ -121,6 +121,7 @@ struct Runtime {
   // iteration: {iteration << 32 | task, t_fetch, t_dependency_met, t_done, t_inputs_staged,
   // t_last_stage_consumed, 0, 0} (globaltimer ns; the last two only for LINEAR tasks)
   const void *tmaps;   // array of 128-byte TMA tensor maps (K/V caches), or null
+  char *arena[8];      // symmetric arena of every tensor-parallel rank as mapped here (own at [rank])
   unsigned long long *prof;
   int prof_stride;  // records per worker
 };
@@ -143,6 +144,14 @@ __device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long
   unsigned long long v;
   asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long *p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add_u64(unsigned long long *p, unsigned long long v) {
+  asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 __device__ __forceinline__ void st_release_u64(unsigned long long *p, unsigned long long v) {
   asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
@@ -295,6 +304,24 @@ __device__ __forceinline__ bool wait_counter(const WaitCtx &w, const unsigned lo
   unsigned long long t0 = globaltimer();
   for (uint32_t it = 1;; ++it) {
     if (ld_acquire_u64(ctr) >= need) return true;
+    __nanosleep(20);
+    if ((it & 63u) == 0u) {
+      if (abort_seen(w)) return false;
+      if (globaltimer() - t0 > w.rt->budget_ns) {
+        raise_abort(w, YPK_ERR_TIMEOUT, event);
+        return false;
+      }
+    }
+  }
+}
+
+// Same for a counter that peer GPUs bump over NVLink (system scope).
+__device__ __forceinline__ bool wait_counter_sys(const WaitCtx &w, const unsigned long long *ctr,
+                                                 unsigned long long need, int event) {
+  if (ld_acquire_sys_u64(ctr) >= need) return true;
+  unsigned long long t0 = globaltimer();
+  for (uint32_t it = 1;; ++it) {
+    if (ld_acquire_sys_u64(ctr) >= need) return true;
     __nanosleep(20);
     if ((it & 63u) == 0u) {
       if (abort_seen(w)) return false;

@@ -7,6 +7,7 @@
 // time) and every SM used as a worker.
 #pragma once
 #include "device_common.cuh"
+#include "task_allreduce.cuh"
 #include "task_attention.cuh"
 #include "task_linear.cuh"
 #include "task_misc.cuh"
@@ -171,6 +172,9 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const Runtime
             case YPK_TASK_ARGMAX_REDUCE: argmax_reduce_task(t, batch); break;
             case YPK_TASK_RMSNORM: rmsnorm_task(t, batch); break;
             case YPK_TASK_SILU_MUL: silu_mul_task(t, batch); break;
+            case YPK_TASK_ALLREDUCE:
+              if (!allreduce_task(wc, misc, rt, t, batch, iter)) wc.failed = true;
+              break;
             default: break;
           }
           // a wait that gave up inside the task is known to one warp only: agree on it.

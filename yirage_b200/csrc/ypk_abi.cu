@@ -49,6 +49,9 @@ struct ypk_handle {
   ypk_task *d_tasks = nullptr;
   int *d_queue = nullptr, *d_queue_off = nullptr;
   unsigned long long *d_events = nullptr, *d_ctrl = nullptr;
+  char *arena = nullptr;         // symmetric arena (tensor parallelism)
+  uint64_t arena_bytes = 0, arena_used = 0;
+  char *peer_arena[8] = {nullptr};   // peers' arenas mapped through CUDA IPC (own at [rank])
   void *d_tmaps = nullptr;       // CUtensorMap[], one per distinct K / V cache tensor
   std::vector<uint64_t> tmap_keys;  // device address of the cache each map describes
   int *d_request_ids = nullptr, *d_page_queue = nullptr, *d_kv_tmp = nullptr, *d_bstate = nullptr;
@@ -226,6 +229,22 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
       need[2] = uint64_t(mb) * 8; align[2] = 8; required[2] = true;
       break;
     }
+    case YPK_TASK_ALLREDUCE: {
+      const int col0 = a[0], ncols = a[1], ldi = a[2], ldo = a[3], hidden = a[4], mt = a[5],
+                half = a[6], sidx = a[7], world = a[8], rank = a[9];
+      if (world != h->cfg.world_size || rank != h->cfg.rank || world < 2 || world > 8)
+        return fail(h, YPK_ERR_INVALID, "task %d: ALLREDUCE for rank %d of %d on a handle of rank %d of %d",
+                    ti, rank, world, h->cfg.rank, h->cfg.world_size);
+      if (ncols <= 0 || ncols % 8 || col0 % 8 || col0 + ncols > hidden || ldi % 8 || ldo % 8 ||
+          hidden % 8 || mt < mb || half < 0 || half > 1 || sidx < 0)
+        return fail(h, YPK_ERR_INVALID, "task %d: ALLREDUCE shape", ti);
+      if (!h->arena) return fail(h, YPK_ERR_STATE, "ALLREDUCE needs ypk_comm_init first");
+      need[0] = rows(ldi, mb, col0 + ncols); align[0] = 16; required[0] = true;
+      need[1] = uint64_t(2) * world * mt * hidden * 2; align[1] = 16; required[1] = true;
+      need[2] = rows(ldo, mb, col0 + ncols); align[2] = 16; required[2] = true;
+      need[3] = uint64_t(sidx + 1) * 8; align[3] = 8; required[3] = true;
+      break;
+    }
     case YPK_TASK_RMSNORM: {
       const int K = a[0], ldx = a[3], ldo = a[4];
       if (K <= 0) return fail(h, YPK_ERR_INVALID, "task %d: RMSNORM K", ti);
@@ -253,6 +272,14 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
       return fail(h, YPK_ERR_INVALID, "task %d (type %d): operand %d is required", ti, in.type, p);
     int rc = resolve(h, ti, p, in.ptr[p], need[p], align[p], &out->ptr[p]);
     if (rc) return rc;
+  }
+  if (in.type == YPK_TASK_ALLREDUCE) {
+    for (int p : {1, 3}) {
+      const uint64_t a0 = reinterpret_cast<uint64_t>(h->arena);
+      if (out->ptr[p] < a0 || out->ptr[p] + need[p] > a0 + h->arena_bytes)
+        return fail(h, YPK_ERR_INVALID, "task %d: ALLREDUCE operand %d is not in the symmetric arena",
+                    ti, p);
+    }
   }
   if (in.dep_event >= h->num_events || in.trig_event >= h->num_events)
     return fail(h, YPK_ERR_INVALID, "task %d: event index out of range", ti);
@@ -413,6 +440,9 @@ int ypk_destroy(ypk_handle *h) {
   free_graph(h);
   for (auto &s : h->slots) release_slot(h, s);
   if (!h->host_only) {
+    for (int p = 0; p < 8; ++p)
+      if (h->peer_arena[p] && p != h->cfg.rank) cudaIpcCloseMemHandle(h->peer_arena[p]);
+    if (h->arena) cudaFree(h->arena);
     if (h->d_ctrl) cudaFree(h->d_ctrl);
     if (h->d_request_ids) cudaFree(h->d_request_ids);
     if (h->d_page_queue) cudaFree(h->d_page_queue);
@@ -497,6 +527,80 @@ int ypk_shuffle_tensor(ypk_handle *h, int32_t dst_slot, const char *name, int32_
                              cudaMemcpyDeviceToDevice));
     row_in_block += gran[i];
   }
+  return YPK_OK;
+}
+
+int ypk_comm_init(ypk_handle *h, uint64_t arena_bytes) {
+  if (!h) return fail(nullptr, YPK_ERR_INVALID, "null handle");
+  if (h->arena) return fail(h, YPK_ERR_STATE, "comm_init called twice");
+  if (h->cfg.world_size < 2 || h->cfg.world_size > 8)
+    return fail(h, YPK_ERR_UNSUPPORTED, "tensor parallelism is built for 2..8 ranks (got %d)",
+                h->cfg.world_size);
+  if (arena_bytes == 0) return fail(h, YPK_ERR_INVALID, "comm_init: empty arena");
+  arena_bytes = (arena_bytes + 255) / 256 * 256;
+  if (h->host_only) {
+    h->arena = reinterpret_cast<char *>(0x7000000000ull);
+  } else {
+    CUDA_TRY(h, cudaSetDevice(h->cfg.device));
+    CUDA_TRY(h, cudaMalloc(&h->arena, arena_bytes));
+    CUDA_TRY(h, cudaMemset(h->arena, 0, arena_bytes));   // counters start at zero
+  }
+  h->arena_bytes = arena_bytes;
+  h->arena_used = 0;
+  h->peer_arena[h->cfg.rank] = h->arena;
+  return YPK_OK;
+}
+
+int ypk_alloc_symmetric(ypk_handle *h, int32_t slot, const char *name, uint64_t bytes) {
+  if (!h) return fail(nullptr, YPK_ERR_INVALID, "null handle");
+  if (!h->arena) return fail(h, YPK_ERR_STATE, "alloc_symmetric before comm_init");
+  if (bytes == 0) return fail(h, YPK_ERR_INVALID, "alloc_symmetric: zero bytes");
+  const uint64_t off = (h->arena_used + 255) / 256 * 256;
+  if (off + bytes > h->arena_bytes)
+    return fail(h, YPK_ERR_INVALID, "alloc_symmetric: arena of %llu bytes is full",
+                (unsigned long long)h->arena_bytes);
+  Slot *s = get_slot(h, slot, true);
+  if (!s) return fail(h, YPK_ERR_INVALID, "alloc_symmetric: bad slot %d", slot);
+  release_slot(h, *s);
+  s->ptr = h->arena + off;
+  s->bytes = bytes;
+  s->used = true;
+  s->owned = false;   // lives and dies with the arena
+  s->name = name ? name : "";
+  h->arena_used = off + bytes;
+  return YPK_OK;
+}
+
+int ypk_comm_export(ypk_handle *h, void *handle_out) {
+  if (!h || !handle_out) return fail(h, YPK_ERR_INVALID, "comm_export: null argument");
+  if (!h->arena) return fail(h, YPK_ERR_STATE, "comm_export before comm_init");
+  static_assert(sizeof(cudaIpcMemHandle_t) == YPK_IPC_HANDLE_BYTES, "IPC handle size");
+  memset(handle_out, 0, YPK_IPC_HANDLE_BYTES);
+  if (h->host_only) return YPK_OK;
+  CUDA_TRY(h, cudaSetDevice(h->cfg.device));
+  cudaIpcMemHandle_t ipc;
+  CUDA_TRY(h, cudaIpcGetMemHandle(&ipc, h->arena));
+  memcpy(handle_out, &ipc, sizeof ipc);
+  return YPK_OK;
+}
+
+int ypk_comm_import(ypk_handle *h, int32_t peer_rank, const void *handle) {
+  if (!h || !handle) return fail(h, YPK_ERR_INVALID, "comm_import: null argument");
+  if (!h->arena) return fail(h, YPK_ERR_STATE, "comm_import before comm_init");
+  if (peer_rank < 0 || peer_rank >= h->cfg.world_size || peer_rank == h->cfg.rank)
+    return fail(h, YPK_ERR_INVALID, "comm_import: peer %d of world %d (own rank %d)", peer_rank,
+                h->cfg.world_size, h->cfg.rank);
+  if (h->peer_arena[peer_rank]) return fail(h, YPK_ERR_STATE, "peer %d imported twice", peer_rank);
+  if (h->host_only) {
+    h->peer_arena[peer_rank] = reinterpret_cast<char *>(0x7100000000ull + (uint64_t(peer_rank) << 32));
+    return YPK_OK;
+  }
+  CUDA_TRY(h, cudaSetDevice(h->cfg.device));
+  cudaIpcMemHandle_t ipc;
+  memcpy(&ipc, handle, sizeof ipc);
+  void *p = nullptr;
+  CUDA_TRY(h, cudaIpcOpenMemHandle(&p, ipc, cudaIpcMemLazyEnablePeerAccess));
+  h->peer_arena[peer_rank] = static_cast<char *>(p);
   return YPK_OK;
 }
 
@@ -717,6 +821,10 @@ int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_
   rt.end_event = h->end_event;
   rt.end_count = h->end_count;
   rt.tmaps = h->d_tmaps;
+  for (int p = 0; p < 8; ++p) rt.arena[p] = h->peer_arena[p];
+  if (h->arena)
+    for (int p = 0; p < c.world_size; ++p)
+      if (!h->peer_arena[p]) return fail(h, YPK_ERR_STATE, "launch before peer %d was imported", p);
   rt.prof = nullptr;
   rt.prof_stride = 0;
   if (c.profiler_buffer) {

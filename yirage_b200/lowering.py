@@ -35,6 +35,7 @@ MAX_NEW_TOKENS = 8           # kMaxNewTokens
 MAX_ATTN_ROWS = 32           # kMaxAttnRows
 ATTN_ROW_FLOATS = HEAD_DIM + 4   # kAttnRowFloats in task_attention.cuh
 MAX_SPLITS = 16
+ALLREDUCE_TILE = 256          # columns per ALLREDUCE task
 SILU_GRAN = 2                # kSiluGran: fused gate/up rows come as 2 gate + 2 up
 
 
@@ -272,12 +273,17 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
     shuffled_done: Dict[int, dict] = {}
     rr = 0  # rotating start for round-robin placed tasks
 
-    def scratch(dims, dt, name):
+    def scratch(dims, dt, name, symmetric=False):
         if new_tensor is None:
             raise RuntimeError("lowering needs a tensor factory for scratch buffers")
-        t = new_tensor(dims, dt, name)
+        t = new_tensor(dims, dt, name, symmetric) if symmetric else new_tensor(dims, dt, name)
         internal.append(t)
         return t
+
+    comm_buf = None
+    num_signals = 0
+    num_allreduce = 0
+    allreduce_tasks: List[TaskSpec] = []
 
     attn_scratch = None
     attn_counters = None
@@ -472,7 +478,34 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                 k += 1
             rr += k
         elif op.kind == "allreduce":
-            raise NotImplementedError("in-graph all-reduce is lowered by the tensor-parallel path")
+            x, o = op.t["in"], op.t["out"]
+            world_a, rank_a = op.attrs["world"], op.attrs["rank"]
+            if world_a != world_size or rank_a != rank:
+                raise ValueError("allreduce_layer was built for another rank / world size")
+            if world_size < 2:
+                raise ValueError("allreduce_layer needs world_size > 1")
+            hidden = x.dims[1]
+            if hidden % ALLREDUCE_TILE or o.dims[1] != hidden:
+                raise NotImplementedError(f"all-reduce width must be a multiple of {ALLREDUCE_TILE}")
+            ntile = hidden // ALLREDUCE_TILE
+            # The caller's buffer tensor ([world, tokens, hidden]) is not used: the runtime keeps
+            # one double-buffered exchange area and one counter per all-reduce tile in the
+            # symmetric arena (identical offsets on every rank).
+            if comm_buf is None or comm_buf.dims[-1] != hidden:
+                comm_buf = scratch((2, world_size, max_tokens, hidden), bfloat16, "allreduce_exchange",
+                                   symmetric=True)
+            sig0 = num_signals
+            num_signals += ntile
+            for k in range(ntile):
+                ts = TaskSpec(N.TASK_ALLREDUCE, op_id=oi)
+                ts.ptr[0], ts.ptr[1], ts.ptr[2] = (x, 0), (comm_buf, 0), (o, 0)
+                ts.iarg[:10] = [k * ALLREDUCE_TILE, ALLREDUCE_TILE, x.dims[1], o.dims[1], hidden,
+                                max_tokens, num_allreduce % 2, sig0 + k, world_size, rank]
+                ts.worker = (rr + k) % W
+                tasks.append(ts)
+                allreduce_tasks.append(ts)
+            rr += ntile
+            num_allreduce += 1
         else:
             raise NotImplementedError(op.kind)
         count = len(tasks) - first
@@ -481,6 +514,11 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
             ts.dep_event = prev_event
             ts.dep_count = prev_count
         prev_event, prev_count = ev, count
+
+    if allreduce_tasks:
+        signals = scratch((num_signals,), int64, "allreduce_signals", symmetric=True)
+        for ts in allreduce_tasks:
+            ts.ptr[3] = (signals, 0)
 
     # queues: tasks of a worker in task (= operator) order
     per_worker: List[List[int]] = [[] for _ in range(W)]
@@ -529,7 +567,7 @@ def simulate(g: LoweredGraph, iterations: int = 2):
 # ------------------------------------------------------------------------------- JSON
 _REF_TASK_TYPE = {  # TaskType numbers of the reference (runtime_header.h:62-124)
     N.TASK_EMBED: 101, N.TASK_LINEAR: 253, N.TASK_ATTENTION: 257, N.TASK_ARGMAX_PARTIAL: 259,
-    N.TASK_ARGMAX_REDUCE: 258, N.TASK_RMSNORM: 154, N.TASK_SILU_MUL: 118, N.TASK_ALLREDUCE: 199,
+    N.TASK_ARGMAX_REDUCE: 258, N.TASK_RMSNORM: 154, N.TASK_SILU_MUL: 118, N.TASK_ALLREDUCE: 107,
 }
 
 

@@ -285,8 +285,9 @@ class PersistentKernel:
     def verify_layer_dispatcher(self, *a, **k): self._not_built("speculative decoding")
 
     # ------------------------------------------------------------------ lowering / compile
-    def _scratch_tensor(self, dims, dt, name):
-        return self.new_tensor(dims=dims, dtype=dt, name=name, io_category="cuda_tensor")
+    def _scratch_tensor(self, dims, dt, name, symmetric=False):
+        return self.new_tensor(dims=dims, dtype=dt, name=name,
+                               io_category="nvshmem_tensor" if symmetric else "cuda_tensor")
 
     def _num_ctas(self):
         if torch.cuda.is_available():
@@ -359,8 +360,6 @@ class PersistentKernel:
         if not dry and not torch.cuda.is_available():
             raise RuntimeError("PersistentKernel.compile needs a CUDA device (sm_100a); "
                                "there is no CPU execution path")
-        if self.world_size > 1 and not dry:
-            from . import tensor_parallel  # noqa: F401  (raises if the TP runtime is missing)
         num_ctas = self._num_ctas()
         g = self.lower(num_ctas)
         if output_dir is not None:
@@ -379,6 +378,11 @@ class PersistentKernel:
             for s in sh["sources"]:
                 used[s.guid] = s
         shuffled = {id(sh["dst"]) for sh in g.shuffles}
+        if self.world_size > 1:
+            # peer-visible tensors come from one symmetric arena, allocated in guid order so
+            # that every rank (same graph, same order) gets the same offsets
+            sym = [t for _, t in sorted(used.items()) if t.kind == "nvshmem"]
+            h.comm_init(sum((t.nbytes + 255) // 256 * 256 for t in sym) + 256)
         for guid, t in sorted(used.items()):
             name = t.name or f"tensor_{guid}"
             if t.kind == "torch":
@@ -386,6 +390,8 @@ class PersistentKernel:
                 if not dry and not tt.is_cuda:
                     raise ValueError(f"attached tensor '{name}' is not on the GPU")
                 h.bind(guid, name, tt.data_ptr(), tt.numel() * tt.element_size())
+            elif t.kind == "nvshmem" and self.world_size > 1:
+                h.alloc_symmetric(guid, name, t.nbytes)
             elif t.kind in ("cuda", "nvshmem"):
                 h.alloc(guid, name, t.nbytes)
             elif t.kind == "shuffled":
@@ -409,6 +415,9 @@ class PersistentKernel:
                 t.farg[i] = v
             tasks.append(t)
         h.load_graph(tasks, g.num_events, g.queue, g.queue_off)
+        if self.world_size > 1 and not kwargs.get("defer_connect", False):
+            from . import tensor_parallel
+            tensor_parallel.connect(h, self.world_size, self.mpi_rank)
         self._handle = h
         self._is_compiled = True
         self._dry = dry
