@@ -45,6 +45,10 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers (invalid as a result)")
+    ap.add_argument("--workload", default="decode",
+                    choices=["decode", "rmsnorm_linear", "gated_mlp", "attention"],
+                    help="decode = BASELINE configs[3] (the headline); the others time one task "
+                         "kernel on BASELINE configs[0..2] as a chain of independent copies")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -363,10 +367,131 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------ task-kernel workloads
+def run_kernel_workload(args):
+    """BASELINE configs[0..2] on one GPU.  One launch of a few microseconds cannot be timed
+    from the host, so a step is a chain of `reps` independent copies of the operator (own
+    weights / own KV cache each, several GB in total, far beyond L2) executed by one
+    persistent-kernel launch; the figure is bytes the chain has to read / time."""
+    import yirage_b200 as yr
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    K, W, B = args.steps, max(args.warmup, 3), args.batch
+    g = torch.Generator(device=dev)
+
+    def rn(shape, std, dtype, mean=0.0):
+        return (torch.randn(*shape, generator=g, device=dev, dtype=torch.float32) * std + mean).to(dtype)
+
+    def pk(max_tokens, meta=None, **kw):
+        return yr.PersistentKernel(
+            mode="onepass", world_size=1, mpi_rank=0, num_workers=128, num_local_schedulers=0,
+            num_remote_schedulers=0, max_seq_length=kw.get("max_seq", 64),
+            max_num_batched_requests=kw.get("max_req", 1), max_num_batched_tokens=max_tokens,
+            max_num_pages=kw.get("max_pages", 1), page_size=64, eos_token_id=-1,
+            meta_tensors=meta or {}, profiler_tensor=None, trace_name="", spec_decode_config=None,
+            use_cutlass_kernel=True)
+
+    keep = []
+    if args.workload == "rmsnorm_linear":
+        g.manual_seed(0)
+        B = B if args.batch != 1 else 8
+        reps, H, dt, ydt = 64, 4096, torch.float16, yr.float16
+        ypk = pk(B)
+        x = ypk.attach_input(rn((B, H), 1.0, dt), "x")
+        alg = 0
+        for i in range(reps):
+            nw, w = rn((H,), 0.1, dt, 1.0), rn((H, H), 0.02, dt)
+            keep += [nw, w]
+            tmp = ypk.new_tensor(dims=(B, H), dtype=ydt, name=f"n{i}")
+            out = ypk.new_tensor(dims=(B, H), dtype=ydt, name=f"o{i}")
+            ypk.rmsnorm_layer(x, ypk.attach_input(nw, f"nw{i}"), tmp, (B, 1, 1), (128, 1, 1), eps=1e-6)
+            ypk.linear_layer(tmp, ypk.attach_input(w, f"w{i}"), out, (64, 1, 1), (128, 1, 1))
+            alg += H * H * 2 + 2 * B * H * 2 + H * 2
+        name = f"RMSNorm->linear, X[{B},4096] fp16, W[4096,4096] (BASELINE configs[0]) x {reps} copies"
+        dtype = "f16"
+    elif args.workload == "gated_mlp":
+        g.manual_seed(1)
+        B = B if args.batch != 1 else 8
+        reps, H, I, dt = 6, 4096, 14336, torch.bfloat16
+        ypk = pk(B)
+        x = ypk.attach_input(rn((B, H), 1.0, dt), "x")
+        alg = 0
+        for i in range(reps):
+            wg, wu, wd = rn((I, H), 0.02, dt), rn((I, H), 0.02, dt), rn((H, I), 0.02, dt)
+            keep += [wg, wu, wd]
+            wgu = ypk.shuffle_tensors([ypk.attach_input(wg, f"g{i}"), ypk.attach_input(wu, f"u{i}")], 0, 32, f"gu{i}")
+            mid = ypk.new_tensor(dims=(B, 2 * I), name=f"mid{i}")
+            act = ypk.new_tensor(dims=(B, I), name=f"act{i}")
+            out = ypk.new_tensor(dims=(B, H), name=f"out{i}")
+            ypk.linear_layer(x, wgu, mid, (64, 1, 1), (128, 1, 1))
+            ypk.silu_mul_layer(mid, act, (32, 1, 1), (128, 1, 1))
+            ypk.linear_layer(act, ypk.attach_input(wd, f"d{i}"), out, (64, 1, 1), (128, 1, 1))
+            alg += 3 * I * H * 2 + B * (2 * H + I * 2) * 2
+        name = f"SiLU-gated MLP, X[{B},4096] bf16, 4096x14336 (BASELINE configs[1]) x {reps} copies"
+        dtype = "bf16"
+    else:
+        g.manual_seed(2)
+        R, HQ, HKV, D, CTX, reps = 8, 32, 8, 128, 4096, 12
+        B = R
+        pages = (CTX + 1 + 63) // 64
+        perm = torch.randperm(R * pages, generator=torch.Generator().manual_seed(2)).tolist()
+        i32 = dict(dtype=torch.int32, device=dev)
+        meta = {"qo_indptr_buffer": torch.arange(R + 1, **i32),
+                "paged_kv_indptr_buffer": torch.arange(R + 1, **i32) * pages,
+                "paged_kv_indices_buffer": torch.tensor(perm, **i32),
+                "paged_kv_last_page_len_buffer": torch.full((R,), (CTX + 1 - 1) % 64 + 1, **i32)}
+        ypk = pk(R, meta, max_req=R, max_pages=R * pages, max_seq=CTX + 1)
+        from yirage_b200 import llama
+        cos, sin = llama.rope_tables(llama.LlamaShape(), CTX + 64, dev)
+        cos_t, sin_t = ypk.attach_input(cos, "cos"), ypk.attach_input(sin, "sin")
+        qkv = ypk.attach_input(rn((R, (HQ + 2 * HKV) * D), 1.0, torch.bfloat16), "qkv")
+        alg = 0
+        for i in range(reps):
+            kc, vc = rn((R * pages, 64, HKV, D), 1.0, torch.bfloat16), rn((R * pages, 64, HKV, D), 1.0, torch.bfloat16)
+            keep += [kc, vc]
+            out = ypk.new_tensor(dims=(R, HQ * D), name=f"o{i}")
+            ypk.paged_attention_layer(qkv, ypk.attach_input(kc, f"k{i}"), ypk.attach_input(vc, f"v{i}"), None,
+                                      None, cos_t, sin_t, out, (R, HKV, 1), (128, 1, 1))
+            alg += R * CTX * HKV * D * 2 * 2
+        name = (f"GQA decode attention, batch 8, 32q/8kv heads, ctx {CTX} in 64-token pages, random page "
+                f"order (BASELINE configs[2]) x {reps} copies")
+        dtype = "bf16"
+    ypk.compile()
+    for _ in range(W):
+        ypk(batch=B)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(K):
+        ypk(batch=B)
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / K
+    clocks = sampler.stop()
+    hbm, src = peaks()
+    achieved = alg / (ms / 1e3) / 1e9
+    print(json.dumps({
+        "metric": "task_kernel_hbm_gbs", "value": achieved, "unit": "GB/s", "n_gpus": 1, "steps": K,
+        "warmup": W, "ms_per_step": ms, "us_per_operator": ms * 1e3 / reps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+        "config": {"workload": name, "batch": B,
+                   "l2": f"{alg / 1e9:.2f} GB read per step, far larger than the 126 MB L2",
+                   "note": "launch overhead of one cooperative launch per step is inside the time"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s",
+                     "frac": achieved / hbm, "frac_of": f"{src} copy bandwidth",
+                     "algorithmic_bytes_per_step": alg, "traffic": None},
+        "clocks": clocks, "gpu_launches": K}), flush=True)
+    ypk.finalize()
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "decode":
+        run_kernel_workload(args)
     else:
         run_ours(args)
 

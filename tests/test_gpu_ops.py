@@ -171,3 +171,40 @@ def test_argmax_is_bit_exact_with_planted_and_tied_maxima():
     assert out[:, 0].cpu().tolist() == want.tolist()
     assert want.tolist()[:5] == [4095, 0, 77, 1024, 0]
     ypk.finalize()
+
+
+def test_kernel_graph_surface_rmsnorm_matmul_config1():
+    """benchmark/rmsnorm.py through yirage.new_kernel_graph(): X [8,4096] fp16 ~N(0,1),
+    W [4096,4096] fp16 ~N(0,0.02) stored [K,N]; rms_norm without weight or epsilon."""
+    import yirage as yr_alias
+    graph = yr_alias.new_kernel_graph()
+    X = graph.new_input(dims=(8, 4096), dtype=yr_alias.float16)
+    W = graph.new_input(dims=(4096, 4096), dtype=yr_alias.float16)
+    graph.mark_output(graph.matmul(graph.rms_norm(X, normalized_shape=(4096,)), W))
+    run = graph.superoptimize(config="mlp", backend="cuda", warmup_iters=1, profile_iters=1)
+    x = randn((8, 4096), 0, 1.0, torch.float16)
+    w = randn((4096, 4096), 1, 0.02, torch.float16)
+    out = run(inputs=[x, w])[0]
+    out2 = run(inputs=[x, w])[0]          # second call reuses the loaded graph
+    torch.cuda.synchronize()
+    want = O.linear(O.rmsnorm(x.cpu(), None, 0.0), w.cpu().t())
+    assert_close(out, want, "kernel-graph rms_norm->matmul")
+    assert out2.data_ptr() == out.data_ptr()
+
+
+@pytest.mark.parametrize("B", [8, 64])
+def test_kernel_graph_surface_gated_mlp_config2(B):
+    """benchmark/gated_mlp.py: mul(silu(X.W1), X.W2) at reduced width, batch 8 and 64."""
+    import yirage as yr_alias
+    H, I = 1024, 1792
+    graph = yr_alias.new_kernel_graph()
+    X = graph.new_input(dims=(B, H), dtype=yr_alias.bfloat16)
+    W1 = graph.new_input(dims=(H, I), dtype=yr_alias.bfloat16)
+    W2 = graph.new_input(dims=(H, I), dtype=yr_alias.bfloat16)
+    graph.mark_output(graph.mul(graph.silu(graph.matmul(X, W1)), graph.matmul(X, W2)))
+    run = graph.superoptimize(config="mlp")
+    x, w1, w2 = randn((B, H), 1), randn((H, I), 2, 0.02), randn((H, I), 3, 0.02)
+    out = run(inputs=[x, w1, w2])[0]
+    torch.cuda.synchronize()
+    want = O.silu_mul(O.linear(x.cpu(), w1.cpu().t()), O.linear(x.cpu(), w2.cpu().t()))
+    assert_close(out, want, f"kernel-graph gated mlp B={B}")

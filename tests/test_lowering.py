@@ -144,3 +144,28 @@ def test_compile_without_a_gpu_fails_loudly():
     _, ypk = small_graph()
     with pytest.raises(RuntimeError, match="no CPU execution path"):
         ypk.compile()
+
+
+def test_kernel_graph_matching():
+    from yirage_b200.micrograph import MicroGraphExecutor
+    g = yr.new_kernel_graph()
+    X = g.new_input(dims=(8, 4096), dtype=yr.float16)
+    W = g.new_input(dims=(4096, 4096), dtype=yr.float16)
+    g.mark_output(g.matmul(g.rms_norm(X, normalized_shape=(4096,)), W))
+    plan = MicroGraphExecutor(g.cygraph).plan
+    assert [p[0] for p in plan] == ["linear"] and plan[0][2] is True      # norm folded in
+    g2 = yr.new_kernel_graph()
+    X = g2.new_input(dims=(8, 4096), dtype=yr.bfloat16)
+    W1 = g2.new_input(dims=(4096, 4096), dtype=yr.bfloat16)
+    W2 = g2.new_input(dims=(4096, 4096), dtype=yr.bfloat16)
+    g2.mark_output(g2.mul(g2.silu(g2.matmul(X, W1)), g2.matmul(X, W2)))
+    assert [p[0] for p in MicroGraphExecutor(g2.cygraph).plan] == ["gated"]
+    g3 = yr.new_kernel_graph()
+    A = g3.new_input(dims=(8, 64), dtype=yr.bfloat16)
+    g3.mark_output(g3.silu(A))
+    with pytest.raises(NotImplementedError):
+        MicroGraphExecutor(g3.cygraph)
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="no CPU execution path"):
+            g.superoptimize()(inputs=[torch.zeros(8, 4096, dtype=torch.float16),
+                                      torch.zeros(4096, 4096, dtype=torch.float16)])

@@ -172,7 +172,7 @@ def fuse(regs: List[RegisteredTask], default_eps: float) -> List[FusedOp]:
             if norm_rt is not None:
                 t["x"] = norm_rt.operands[0]
                 t["norm_w"] = norm_rt.operands[1]
-                flags |= N.F_NORM
+                flags |= N.F_NORM if norm_rt.operands[1] is not None else N.F_NORM_NOWEIGHT
                 attrs["eps"] = norm_rt.attrs.get("eps", default_eps)
                 srcs = [norm_rt, lin]
             if res is not None:
