@@ -170,6 +170,7 @@ typedef struct ypk_status {
   int32_t finished;       /* 1 when every request has retired               */
   int32_t active_tokens;  /* tokens in the batch that is pending            */
   int64_t tasks_executed; /* worker-side task executions, last launch       */
+  int64_t tensor_core_tasks; /* of those, LINEAR tasks run on tcgen05 / TMEM */
 } ypk_status;
 
 /* Library / build information. */

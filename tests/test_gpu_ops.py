@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 
 
 def run_linear(B, K, Nrows, *, norm=False, residual=False, dtype=torch.bfloat16, seed=0,
-               eps=1e-6, max_tokens=8):
+               eps=1e-6, max_tokens=8, tensor_core=None):
     x = randn((max_tokens, K), seed, 1.0, dtype)
     w = randn((Nrows, K), seed + 1, 0.02, dtype)
     nw = randn((K,), seed + 2, 0.1, dtype, mean=1.0)
@@ -24,6 +24,7 @@ def run_linear(B, K, Nrows, *, norm=False, residual=False, dtype=torch.bfloat16,
     out = torch.zeros(max_tokens, Nrows, dtype=dtype, device="cuda")
     ot = ypk.attach_input(out, "out")
     src = xt
+    grid = max(g for g in range(1, Nrows // 64 + 1) if Nrows % g == 0)
     if norm:
         nwt = ypk.attach_input(nw, "nw")
         tmp = ypk.new_tensor(dims=(max_tokens, K), dtype=ydt, name="normed")
@@ -31,12 +32,15 @@ def run_linear(B, K, Nrows, *, norm=False, residual=False, dtype=torch.bfloat16,
         src = tmp
     if residual:
         rt = ypk.attach_input(res, "res")
-        ypk.linear_with_residual_layer(src, wt, rt, ot, (Nrows // 64, 1, 1), (128, 1, 1))
+        ypk.linear_with_residual_layer(src, wt, rt, ot, (grid, 1, 1), (128, 1, 1))
     else:
-        ypk.linear_layer(src, wt, ot, (Nrows // 64, 1, 1), (128, 1, 1))
+        ypk.linear_layer(src, wt, ot, (grid, 1, 1), (128, 1, 1))
     ypk.compile()
     ypk(batch=B)
     torch.cuda.synchronize()
+    if tensor_core is not None:
+        ran = ypk.status().tensor_core_tasks
+        assert (ran > 0) == tensor_core, f"tensor-core LINEAR tasks: {ran}"
     xin = x[:B].cpu()
     if norm:
         xin = O.rmsnorm(xin, nw.cpu(), eps)
@@ -68,14 +72,35 @@ def test_linear_norm_residual(B):
 
 
 def test_linear_batch_above_eight_restreams():
-    run_linear(11, 512, 192, max_tokens=16, seed=9)
+    """K is not a multiple of 256: the batch runs as groups of 8 on the GEMV path."""
+    run_linear(11, 320, 192, max_tokens=16, seed=9, tensor_core=False)
 
 
-@pytest.mark.parametrize("B,H,I", [(1, 512, 1024), (8, 4096, 1792), (3, 1024, 2048)])
+@pytest.mark.parametrize("B,K,N,norm,res,dtype", [
+    (9, 512, 192, False, False, torch.bfloat16),
+    (11, 512, 200, True, False, torch.bfloat16),
+    (16, 4096, 4096, True, False, torch.float16),
+    (33, 1024, 520, True, True, torch.bfloat16),
+    (48, 1792, 256, False, True, torch.bfloat16),
+    (64, 4096, 1000, False, False, torch.bfloat16),
+    (64, 14336, 296, True, True, torch.bfloat16),
+])
+def test_linear_tensor_core_path(B, K, N, norm, res, dtype):
+    """9..64 tokens: tcgen05.mma with TMEM accumulators, TMA-staged weights."""
+    run_linear(B, K, N, norm=norm, residual=res, dtype=dtype, seed=B, eps=1e-5, max_tokens=64,
+               tensor_core=True)
+
+
+def test_linear_small_batch_in_a_large_batch_graph_stays_on_gemv():
+    run_linear(8, 512, 192, max_tokens=64, seed=4, tensor_core=False)
+
+
+@pytest.mark.parametrize("B,H,I", [(1, 512, 1024), (8, 4096, 1792), (3, 1024, 2048),
+                                   (16, 1024, 2048), (40, 512, 1024), (64, 4096, 1792)])
 def test_gated_mlp_fused(B, H, I):
     """rmsnorm -> linear(gate|up) -> silu_mul -> linear(down)+residual, the MLP half of a
-    layer (BASELINE config 2 at reduced width)."""
-    MT = 8
+    layer (BASELINE config 2 at reduced width); more than 8 tokens take the tcgen05 path."""
+    MT = 8 if B <= 8 else 64
     x = randn((MT, H), 1)
     nw = randn((H,), 2, 0.1, mean=1.0)
     wg, wu = randn((I, H), 3, 0.02), randn((I, H), 4, 0.02)
@@ -98,6 +123,7 @@ def test_gated_mlp_fused(B, H, I):
     assert [o.kind for o in ypk.lower().ops] == ["linear", "linear"], "gate/up + silu must fuse"
     ypk(batch=B)
     torch.cuda.synchronize()
+    assert (ypk.status().tensor_core_tasks > 0) == (B > 8)
     xc = x[:B].cpu()
     h = O.rmsnorm(xc, nw.cpu(), 1e-5)
     want = xc.float() + O.gated_mlp(h, wg.cpu(), wu.cpu(), wd.cpu())

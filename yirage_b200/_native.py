@@ -81,6 +81,7 @@ class Status(C.Structure):
         ("error", C.c_int32), ("fail_worker", C.c_int32), ("fail_task", C.c_int32),
         ("fail_event", C.c_int32), ("iterations", C.c_int64), ("finished", C.c_int32),
         ("active_tokens", C.c_int32), ("tasks_executed", C.c_int64),
+        ("tensor_core_tasks", C.c_int64),
     ]
 
 

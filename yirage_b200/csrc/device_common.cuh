@@ -14,6 +14,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <stddef.h>
 #include <stdint.h>
 #include "../../include/ypk.h"
 
@@ -49,6 +50,17 @@ constexpr int kMaxAttnRows = 32;                 // new tokens x q heads per kv 
 constexpr int kAttnTilesPerSplit = 4;
 constexpr int kSiluGran = 2;                     // fused gate/up rows come as 2 gate + 2 up
 
+// Tensor-core LINEAR path (9..64 tokens): weights arrive as 8-row x 4-k-block TMA boxes
+// (a k-block is 64 columns = one 128-byte swizzled row), tokens sit in a ring of 8 KB units.
+constexpr int kUmmaKBlock = 64;
+constexpr int kUmmaStepKBlocks = 4;              // k-blocks per weight stage ("super-step")
+constexpr int kUmmaBoxBytes = 8 * kUmmaStepKBlocks * 128;   // 4096: one TMA box
+constexpr int kUmmaBlockRows = 64;               // weight rows per accumulator block
+constexpr int kUmmaMaxBatch = 64;
+constexpr int kUmmaUnits = 7;                    // token ring: 7 x 8 KB
+constexpr int kUmmaUnitBytes = 8192;
+constexpr int kUmmaTmemCols = 256;               // 4 blocks x 64 fp32 columns
+
 // Shared-memory map (dynamic shared memory, bytes).
 constexpr int kOffRing = 0;
 constexpr int kOffXs = kOffRing + kStages * kStageBytes;   // 174080
@@ -63,6 +75,8 @@ constexpr int kOffMisc = kOffAcc + kAccBytes;              // 231424
 constexpr int kMiscBytes = 1024;
 constexpr int kSmemBytes = kOffMisc + kMiscBytes;          // 232448 = 227 KB, the per-CTA maximum
 constexpr int kScratchSmemBytes = kXsBytes + kPartBytes + kResBytes + kAccBytes;  // 57344 from kOffXs
+static_assert(kUmmaUnits * kUmmaUnitBytes <= kScratchSmemBytes, "token ring does not fit");
+static_assert(8 * kUmmaBoxBytes <= kStageBytes, "a 64-row super-step does not fit a ring stage");
 
 // Layout of the misc area.
 struct __align__(16) Misc {
@@ -73,10 +87,16 @@ struct __align__(16) Misc {
   int flag;                      // generic broadcast slot for the consumers
   unsigned long long *prof_rec;  // timeline record of the current task (thread 0), or null
   int abort_flag;                // set when this CTA has seen an abort
-  ypk_task ctask;                // consumer copy of the current task
-  ypk_task ptask;                // producer copy of the current task
+  uint32_t tmem_base;            // tensor-memory address of the CTA's accumulator columns
+  unsigned long long xfull_bar[kUmmaUnits];   // token ring of the tensor-core LINEAR path
+  unsigned long long xempty_bar[kUmmaUnits];
+  unsigned long long acc_bar;    // every MMA of the current task has completed
+  float rnorm_umma[kUmmaMaxBatch];
+  alignas(16) ypk_task ctask;    // consumer copy of the current task (copied 16 bytes at a time)
+  alignas(16) ypk_task ptask;                // producer copy of the current task
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "misc area too small");
+static_assert(offsetof(Misc, ctask) % 16 == 0 && offsetof(Misc, ptask) % 16 == 0, "task copies");
 static_assert(sizeof(ypk_task) == 176, "ypk_task layout changed");
 
 // Control block in global memory (unsigned long long words).
@@ -86,6 +106,7 @@ enum CtrlWord {
   kCtrlFailInfo = 2,   // worker << 40 | (task & 0xfffff) << 20 | (event & 0xfffff)
   kCtrlTasksDone = 3,
   kCtrlFinished = 4,
+  kCtrlUmmaTasks = 5,  // LINEAR tasks that took the tensor-core path
   kCtrlWords = 8
 };
 constexpr unsigned kStateRun = 0, kStateStop = 1;
@@ -120,7 +141,8 @@ struct Runtime {
   // optional per-task timeline: 8 words per (worker, queue position), overwritten every
   // iteration: {iteration << 32 | task, t_fetch, t_dependency_met, t_done, t_inputs_staged,
   // t_last_stage_consumed, 0, 0} (globaltimer ns; the last two only for LINEAR tasks)
-  const void *tmaps;   // array of 128-byte TMA tensor maps (K/V caches), or null
+  const void *tmaps;   // array of 128-byte TMA tensor maps (K/V caches, LINEAR weights), or null
+  int use_tmem;        // allocate tensor memory: some LINEAR task can take the tcgen05 path
   char *arena[8];      // symmetric arena of every tensor-parallel rank as mapped here (own at [rank])
   unsigned long long *prof;
   int prof_stride;  // records per worker

@@ -10,6 +10,7 @@
 #include "task_allreduce.cuh"
 #include "task_attention.cuh"
 #include "task_linear.cuh"
+#include "task_linear_umma.cuh"
 #include "task_misc.cuh"
 
 namespace ypk {
@@ -61,19 +62,33 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const Runtime
       mbar_init(&misc->full_bar[s], 1);
       mbar_init(&misc->empty_bar[s], kConsumerWarps);
     }
+    for (int s = 0; s < kUmmaUnits; ++s) {
+      mbar_init(&misc->xfull_bar[s], kConsumerWarps - 1);
+      mbar_init(&misc->xempty_bar[s], 1);
+    }
+    mbar_init(&misc->acc_bar, 1);
     misc->flag = 0;
     misc->abort_flag = 0;
+    misc->tmem_base = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  // Accumulator columns of the tensor-core LINEAR path: taken once, for the kernel's lifetime.
+  if (rt.use_tmem) {
+    if (warp == 0) tmem_alloc(misc);
+    tcgen05_before_sync();
+    __syncthreads();
+    tcgen05_after_sync();
+  }
 
   const int q0 = __ldg(rt.queue_off + worker), q1 = __ldg(rt.queue_off + worker + 1);
   WaitCtx wc{&rt, misc, worker, -1, false};
   // swizzled TMA boxes assume ring stages on 1 KB boundaries
   if (tid == 0 && (smem_u32(smem) & 1023u) != 0u) raise_abort(wc, YPK_ERR_STATE, -4);
   RingPos pos;
+  UmmaState ustate;
   long long iter = rt.base_iter;
-  long long tasks_done = 0;
+  long long tasks_done = 0, umma_done = 0;
   unsigned long long policy = 0;
   if (is_producer) policy = policy_evict_first();
 
@@ -131,7 +146,8 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const Runtime
         wc.task = ti;
         const ypk_task &t = misc->ptask;
         if (t.type == YPK_TASK_LINEAR) {
-          ok = linear_produce(wc, smem, misc, t, batch, pos, policy);
+          ok = linear_uses_umma(t, batch) ? linear_produce_umma(wc, smem, misc, rt, t, pos, policy)
+                                          : linear_produce(wc, smem, misc, t, batch, pos, policy);
         } else if (t.type == YPK_TASK_ATTENTION) {
           ok = attention_produce(wc, smem, misc, rt, t, pos);
         }
@@ -165,7 +181,14 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const Runtime
         if (prec) prec[2] = globaltimer();
         if (ok) {
           switch (t.type) {
-            case YPK_TASK_LINEAR: linear_consume(wc, smem, misc, t, batch, pos); break;
+            case YPK_TASK_LINEAR:
+              if (linear_uses_umma(t, batch)) {
+                linear_consume_umma(wc, smem, misc, t, batch, pos, ustate);
+                ++umma_done;
+              } else {
+                linear_consume(wc, smem, misc, t, batch, pos);
+              }
+              break;
             case YPK_TASK_ATTENTION: attention_consume(wc, smem, misc, rt, t, pos); break;
             case YPK_TASK_EMBED: embed_task(t, batch); break;
             case YPK_TASK_ARGMAX_PARTIAL: argmax_partial_task(t, batch); break;
@@ -234,6 +257,21 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const Runtime
     }
   }
   if (tid == 0 && tasks_done) atomicAdd(rt.ctrl + kCtrlTasksDone, (unsigned long long)tasks_done);
+  if (tid == 0 && umma_done) atomicAdd(rt.ctrl + kCtrlUmmaTasks, (unsigned long long)umma_done);
+  if (rt.use_tmem) {
+    // After an abort the issuing thread can leave with MMAs in flight: wait (bounded) for
+    // them before the columns are handed back.  On the normal path every task has waited.
+    if (tid == 0 && ld_relaxed_u64(rt.ctrl + kCtrlAbort) != 0ull) {
+      umma_commit(&misc->acc_bar);
+      const unsigned long long t0 = globaltimer();
+      for (uint32_t it = 0; !mbar_try_wait(&misc->acc_bar, ustate.acc_phase); ++it) {
+        if ((it & 255u) == 255u && globaltimer() - t0 > 1000000ull) break;
+      }
+    }
+    tcgen05_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_free(misc->tmem_base);
+  }
   __syncthreads();
 }
 

@@ -54,6 +54,7 @@ struct ypk_handle {
   char *peer_arena[8] = {nullptr};   // peers' arenas mapped through CUDA IPC (own at [rank])
   void *d_tmaps = nullptr;       // CUtensorMap[], one per distinct K / V cache tensor
   std::vector<uint64_t> tmap_keys;  // device address of the cache each map describes
+  bool use_tmem = false;            // some LINEAR task has a weight tensor map
   int *d_request_ids = nullptr, *d_page_queue = nullptr, *d_kv_tmp = nullptr, *d_bstate = nullptr;
   // progress
   long long base_iter = 0;
@@ -313,6 +314,35 @@ int encode_kv_tmap(ypk_handle *h, void *base, int hkv, CUtensorMap *out) {
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(h, YPK_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", int(r));
+  return YPK_OK;
+}
+
+// Rank-3 view {64 columns, rows, K / 64} of a row-major 16-bit weight [rows][ldw] for the
+// tensor-core LINEAR path: box = one 128-byte k-block x 8 rows x 4 k-blocks, 128-byte swizzle,
+// so that a box lands in shared memory as [k-block][row][128 B].
+int encode_weight_tmap(ypk_handle *h, void *base, int rows, int K, int ldw, CUtensorMap *out) {
+  typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                               const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                               const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn fn = nullptr;
+  if (!fn) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !p)
+      return fail(h, YPK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    fn = reinterpret_cast<EncodeFn>(p);
+  }
+  const cuuint64_t dims[3] = {cuuint64_t(kUmmaKBlock), cuuint64_t(rows), cuuint64_t(K / kUmmaKBlock)};
+  const cuuint64_t strides[2] = {cuuint64_t(ldw) * 2, cuuint64_t(kUmmaKBlock) * 2};
+  const cuuint32_t box[3] = {cuuint32_t(kUmmaKBlock), 8, cuuint32_t(kUmmaStepKBlocks)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, base, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(h, YPK_ERR_CUDA, "cuTensorMapEncodeTiled failed for a weight (%d)", int(r));
   return YPK_OK;
 }
 
@@ -699,14 +729,43 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
       t.iarg[9 + which] = int(k);
     }
   }
+  // tensor maps for the weights of LINEAR tasks that can take the tensor-core path (more
+  // than 8 tokens in flight): one per distinct (weight, K, row pitch)
+  struct WeightKey { uint64_t addr; int K, ldw, rows; };
+  std::vector<WeightKey> wkeys;
+  const bool umma_possible = h->cfg.max_num_batched_tokens > kMaxBatch;
+  for (int i = 0; i < num_tasks; ++i) {
+    ypk_task &t = resolved[size_t(i)];
+    if (t.type != YPK_TASK_LINEAR) continue;
+    t.iarg[9] = -1;
+    const int K = t.iarg[0], nrows = t.iarg[2], ldw = t.iarg[4];
+    const bool silu_ok = !(t.flags & YPK_F_SILU_MUL) || (t.iarg[1] % (2 * kSiluGran) == 0);
+    if (!umma_possible || K % (kUmmaKBlock * kUmmaStepKBlocks) != 0 || nrows > kMaxAccRows ||
+        ldw % 8 != 0 || (t.ptr[1] & 15u) != 0 || t.iarg[3] % 8 != 0 || (t.ptr[0] & 15u) != 0 ||
+        !silu_ok)
+      continue;
+    size_t k = 0;
+    while (k < wkeys.size() &&
+           !(wkeys[k].addr == t.ptr[1] && wkeys[k].K == K && wkeys[k].ldw == ldw))
+      ++k;
+    if (k == wkeys.size()) wkeys.push_back({t.ptr[1], K, ldw, 0});
+    wkeys[k].rows = std::max(wkeys[k].rows, t.iarg[1] + nrows);
+    t.iarg[9] = int(keys.size() + k);
+  }
   h->end_event = tasks[num_tasks - 1].trig_event;
   h->end_count = h->end_event >= 0 ? trig_count[size_t(h->end_event)] : 0;
 
   free_graph(h);
-  if (!keys.empty() && !h->host_only) {
-    std::vector<CUtensorMap> maps(keys.size());
+  h->use_tmem = !wkeys.empty();
+  if (!(keys.empty() && wkeys.empty()) && !h->host_only) {
+    std::vector<CUtensorMap> maps(keys.size() + wkeys.size());
     for (size_t k = 0; k < keys.size(); ++k) {
       int rc = encode_kv_tmap(h, reinterpret_cast<void *>(keys[k]), key_hkv[k], &maps[k]);
+      if (rc) return rc;
+    }
+    for (size_t k = 0; k < wkeys.size(); ++k) {
+      int rc = encode_weight_tmap(h, reinterpret_cast<void *>(wkeys[k].addr), wkeys[k].rows,
+                                  wkeys[k].K, wkeys[k].ldw, &maps[keys.size() + k]);
       if (rc) return rc;
     }
     CUDA_TRY(h, cudaSetDevice(h->cfg.device));
@@ -821,6 +880,7 @@ int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_
   rt.end_event = h->end_event;
   rt.end_count = h->end_count;
   rt.tmaps = h->d_tmaps;
+  rt.use_tmem = h->use_tmem ? 1 : 0;
   for (int p = 0; p < 8; ++p) rt.arena[p] = h->peer_arena[p];
   if (h->arena)
     for (int p = 0; p < c.world_size; ++p)
@@ -869,6 +929,7 @@ int ypk_wait(ypk_handle *h) {
   unsigned long long words[kCtrlWords];
   CUDA_TRY(h, cudaMemcpy(words, h->d_ctrl, sizeof words, cudaMemcpyDeviceToHost));
   h->status.tasks_executed = (int64_t)words[kCtrlTasksDone];
+  h->status.tensor_core_tasks = (int64_t)words[kCtrlUmmaTasks];
   if (words[kCtrlAbort]) {
     const unsigned long long info = words[kCtrlFailInfo];
     h->status.error = -int(words[kCtrlAbort]);
