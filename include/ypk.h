@@ -177,7 +177,10 @@ typedef struct ypk_status {
 int ypk_abi_version(void);
 const char *ypk_last_error(const ypk_handle *h);
 
-/* Lifetime (init_persistent_kernel / finalize_persistent_kernel). */
+/* Lifetime (init_persistent_kernel / finalize_persistent_kernel).
+ * Environment, read by ypk_create: YPK_TENSOR_CORE = "auto" (default: a LINEAR task with
+ * 9..64 tokens takes the tcgen05 path when its estimated time beats the GEMV path),
+ * "always" (whenever the task is eligible) or "never". */
 int ypk_create(const ypk_config *cfg, ypk_handle **out);
 int ypk_destroy(ypk_handle *h);
 

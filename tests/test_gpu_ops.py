@@ -85,8 +85,9 @@ def test_linear_batch_above_eight_restreams():
     (64, 4096, 1000, False, False, torch.bfloat16),
     (64, 14336, 296, True, True, torch.bfloat16),
 ])
-def test_linear_tensor_core_path(B, K, N, norm, res, dtype):
+def test_linear_tensor_core_path(B, K, N, norm, res, dtype, monkeypatch):
     """9..64 tokens: tcgen05.mma with TMEM accumulators, TMA-staged weights."""
+    monkeypatch.setenv("YPK_TENSOR_CORE", "always")   # these slabs are too small to win on cost
     run_linear(B, K, N, norm=norm, residual=res, dtype=dtype, seed=B, eps=1e-5, max_tokens=64,
                tensor_core=True)
 
@@ -97,10 +98,11 @@ def test_linear_small_batch_in_a_large_batch_graph_stays_on_gemv():
 
 @pytest.mark.parametrize("B,H,I", [(1, 512, 1024), (8, 4096, 1792), (3, 1024, 2048),
                                    (16, 1024, 2048), (40, 512, 1024), (64, 4096, 1792)])
-def test_gated_mlp_fused(B, H, I):
+def test_gated_mlp_fused(B, H, I, monkeypatch):
     """rmsnorm -> linear(gate|up) -> silu_mul -> linear(down)+residual, the MLP half of a
     layer (BASELINE config 2 at reduced width); more than 8 tokens take the tcgen05 path."""
     MT = 8 if B <= 8 else 64
+    monkeypatch.setenv("YPK_TENSOR_CORE", "always")
     x = randn((MT, H), 1)
     nw = randn((H,), 2, 0.1, mean=1.0)
     wg, wu = randn((I, H), 3, 0.02), randn((I, H), 4, 0.02)

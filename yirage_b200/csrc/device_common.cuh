@@ -59,7 +59,7 @@ constexpr int kUmmaBlockRows = 64;               // weight rows per accumulator 
 constexpr int kUmmaMaxBatch = 64;
 constexpr int kUmmaUnits = 7;                    // token ring: 7 x 8 KB
 constexpr int kUmmaUnitBytes = 8192;
-constexpr int kUmmaTmemCols = 256;               // 4 blocks x 64 fp32 columns
+constexpr int kUmmaTmemCols = 512;               // all of the SM's tensor memory: 4 blocks x 64 columns x 2 partial sums
 
 // Shared-memory map (dynamic shared memory, bytes).
 constexpr int kOffRing = 0;
@@ -143,6 +143,7 @@ struct Runtime {
   // t_last_stage_consumed, 0, 0} (globaltimer ns; the last two only for LINEAR tasks)
   const void *tmaps;   // array of 128-byte TMA tensor maps (K/V caches, LINEAR weights), or null
   int use_tmem;        // allocate tensor memory: some LINEAR task can take the tcgen05 path
+  int umma_policy;     // 0 = by estimated cost, 1 = whenever eligible, 2 = never
   char *arena[8];      // symmetric arena of every tensor-parallel rank as mapped here (own at [rank])
   unsigned long long *prof;
   int prof_stride;  // records per worker

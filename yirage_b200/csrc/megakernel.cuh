@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const Runtime
         wc.task = ti;
         const ypk_task &t = misc->ptask;
         if (t.type == YPK_TASK_LINEAR) {
-          ok = linear_uses_umma(t, batch) ? linear_produce_umma(wc, smem, misc, rt, t, pos, policy)
+          ok = linear_uses_umma(rt, t, batch) ? linear_produce_umma(wc, smem, misc, rt, t, pos, policy)
                                           : linear_produce(wc, smem, misc, t, batch, pos, policy);
         } else if (t.type == YPK_TASK_ATTENTION) {
           ok = attention_produce(wc, smem, misc, rt, t, pos);
@@ -182,7 +182,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const Runtime
         if (ok) {
           switch (t.type) {
             case YPK_TASK_LINEAR:
-              if (linear_uses_umma(t, batch)) {
+              if (linear_uses_umma(rt, t, batch)) {
                 linear_consume_umma(wc, smem, misc, t, batch, pos, ustate);
                 ++umma_done;
               } else {

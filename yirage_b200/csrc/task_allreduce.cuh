@@ -8,8 +8,8 @@
 // (CUDA IPC over NVLink / NVSwitch) inside one symmetric arena per rank:
 //
 //   1. push: 16-byte stores of this rank's slice into slot `rank` of each peer's buffer;
-//   2. CTA barrier, then one thread does red.release.sys.add on each peer's counter (the
-//      release is cumulative over the other threads' stores);
+//   2. CTA barrier, then one thread per peer does fence.acq_rel.sys + red.relaxed.sys.add on
+//      that peer's counter (the fence is cumulative over the other threads' stores);
 //   3. bounded wait until the own counter has world-1 arrivals for this iteration
 //      (ld.acquire.sys), so the remote tiles are in this GPU's memory before they are read;
 //   4. reduce from local memory only.
@@ -49,12 +49,17 @@ __device__ __forceinline__ bool allreduce_task(WaitCtx &wc, Misc *misc, const Ru
     }
   }
   consumer_bar();
+  // One signalling thread per peer, side by side: each orders the CTA's stores (known to it
+  // through the barrier) with a system-scope fence and bumps its peer's counter.  A single
+  // thread doing the peers in turn would pay one NVLink round trip per peer.
+  if (tid < world && tid != rank) {
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(
+                     reinterpret_cast<unsigned long long *>(rt.arena[tid] + sig_off) + sidx),
+                 "l"(1ull)
+                 : "memory");
+  }
   if (tid == 0) {
-    for (int p = 0; p < world; ++p) {
-      if (p == rank) continue;
-      red_release_sys_add_u64(reinterpret_cast<unsigned long long *>(rt.arena[p] + sig_off) + sidx,
-                              1ull);
-    }
     const unsigned long long need =
         static_cast<unsigned long long>(world - 1) * static_cast<unsigned long long>(iter);
     misc->flag = wait_counter_sys(wc, reinterpret_cast<unsigned long long *>(sig) + sidx, need,

@@ -7,20 +7,22 @@
 //   A (weights)   tiled TMA through a rank-3 view {64 columns, rows, K / 64} of the weight:
 //                 one box is 8 rows x 4 k-blocks (4 KB) and lands as [k-block][row][128 B]
 //                 with the 128-byte swizzle, i.e. as four 8-row core-matrix groups of the
-//                 K-major UMMA layout.  A ring stage holds one "super-step": up to 8 such
-//                 boxes (64 rows) x 4 k-blocks.  Rows past the task's slab are never read
-//                 back; rows past the end of the tensor arrive as zeros.
+//                 K-major UMMA layout.  A ring stage holds one "super-step" of one row
+//                 block: up to 8 such boxes (64 rows) x 4 k-blocks, or, for a task of at
+//                 most 32 rows, 4 boxes x 8 k-blocks.  Rows past the task's slab are never
+//                 read back; rows past the end of the tensor arrive as zeros.
 //   B (tokens)    staged by consumer warps 1..7 with 16-byte cp.async into a second ring of
 //                 seven 8 KB units (64 / N k-blocks each), same swizzled K-major layout, then
 //                 multiplied in place by the norm weight while the RMS statistics are
 //                 taken; several units are in flight so that the L2 latency is hidden.
 //   D             fp32 accumulators in tensor memory, N columns per 64-row block (at most
-//                 four blocks per task).  Lane 0 of consumer warp 0 issues tcgen05.mma
-//                 (cta_group::1, kind::f16, M = 128: TMEM lanes 64..127 take whatever follows
-//                 the block in shared memory and are never read); tcgen05.commit hands weight
-//                 stages and token units back to their producers and signals the end.
-//   epilogue      tcgen05.ld 32x32b (lane = weight row) -> RMS factor, residual or
-//                 SiLU(gate) * up -> 16-bit stores.
+//                 four blocks per task) and per partial sum (up to four, see below).  Lane 0 of consumer warp 0 issues tcgen05.mma
+//                 (cta_group::1, kind::f16, M = 64, so that a block reads only its own 64
+//                 rows of shared memory); tcgen05.commit hands weight stages and token units
+//                 back to their producers and signals the end.
+//   epilogue      tcgen05.ld 32x32b: with M = 64 row r of a block sits in TMEM lane
+//                 32 * (r / 16) + r % 16, i.e. in the lower 16 lanes of warp r / 16 -> RMS
+//                 factor, residual or SiLU(gate) * up -> 16-bit stores.
 //
 // The TMEM columns are allocated once per CTA when the kernel starts and freed when it ends
 // (the reference allocates and frees them inside every task, linear_sm100_mpk.cuh:561,704).
@@ -34,9 +36,28 @@ __device__ __forceinline__ int umma_n(int batch) { return (batch + 15) / 16 * 16
 // k-blocks per token-ring unit (8 KB): 4, 2, 1, 1 for N = 16, 32, 48, 64
 __device__ __forceinline__ int umma_unit_kblocks(int N) { return kUmmaMaxBatch / N; }
 
-// Batches the tensor-core path takes.  Producer and consumers evaluate this identically.
-__device__ __forceinline__ bool linear_uses_umma(const ypk_task &t, int batch) {
-  return batch > kMaxBatch && batch <= kUmmaMaxBatch && t.iarg[9] >= 0;
+// k-blocks per ring stage: 8 for a task of at most 32 rows (one block, <= 4 boxes per
+// k-half), else 4.
+__device__ __forceinline__ int umma_step_kblocks(const LinearArgs &a) {
+  return (a.nrows <= 32 && (a.K / kUmmaKBlock) % (2 * kUmmaStepKBlocks) == 0) ? 2 * kUmmaStepKBlocks
+                                                                             : kUmmaStepKBlocks;
+}
+
+// Does this task take the tensor-core path at this batch?  Producer and consumers evaluate
+// this identically.  A tcgen05.mma costs the issuing SM about 78 ns whatever M and N
+// (measured: 64x16x16 and 128x256x16 alike), and a task issues K / 16 of them per 64-row
+// block; the GEMV path instead streams the weights once per 8 tokens at about 3/4 of the
+// SM's share of HBM (44 bytes / ns).  Take whichever is estimated to finish first.
+__device__ __forceinline__ bool linear_uses_umma(const Runtime &rt, const ypk_task &t, int batch) {
+  if (batch <= kMaxBatch || batch > kUmmaMaxBatch || t.iarg[9] < 0 || rt.umma_policy == 2) return false;
+  if (rt.umma_policy == 1) return true;
+  const long long K = t.iarg[0], nrows = t.iarg[2];
+  const long long wbytes = nrows * K * 2;
+  const long long nblocks = (nrows + kUmmaBlockRows - 1) / kUmmaBlockRows;
+  const long long mma_ns = nblocks * (K / 16) * 78;
+  const long long umma_ns = max(wbytes / 44, mma_ns);
+  const long long gemv_ns = ((batch + kMaxBatch - 1) / kMaxBatch) * (wbytes / 33);
+  return umma_ns < gemv_ns;
 }
 
 __device__ __forceinline__ void tma_load_3d_hint(void *dst, const void *tmap, int x, int y, int z,
@@ -57,18 +78,22 @@ __device__ __noinline__ bool linear_produce_umma(WaitCtx &wc, char *smem, Misc *
   const int lane = threadIdx.x & 31;
   const LinearArgs a = linear_args(t);
   const char *tmap = static_cast<const char *>(rt.tmaps) + size_t(t.iarg[9]) * 128;
-  const int nss = a.K / (kUmmaKBlock * kUmmaStepKBlocks);
+  const int KS = umma_step_kblocks(a);
+  const int halves = KS / kUmmaStepKBlocks;            // TMA boxes per 8-row group
+  const int nss = a.K / (kUmmaKBlock * KS);
   for (int ss = 0; ss < nss; ++ss) {
     for (int r0 = 0; r0 < a.nrows; r0 += kUmmaBlockRows) {
       const int groups = (min(kUmmaBlockRows, a.nrows - r0) + 7) / 8;
       if (!wait_mbar(wc, &misc->empty_bar[pos.slot], pos.phase ^ 1u)) return false;
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       char *stage = smem + kOffRing + pos.slot * kStageBytes;
-      if (lane == 0) mbar_expect_tx(&misc->full_bar[pos.slot], uint32_t(groups) * kUmmaBoxBytes);
+      if (lane == 0)
+        mbar_expect_tx(&misc->full_bar[pos.slot], uint32_t(groups * halves) * kUmmaBoxBytes);
       __syncwarp();
-      if (lane < groups) {
-        tma_load_3d_hint(stage + lane * kUmmaBoxBytes, tmap, 0, a.row0 + r0 + lane * 8,
-                         ss * kUmmaStepKBlocks, &misc->full_bar[pos.slot], policy);
+      if (lane < groups * halves) {
+        const int g = lane / halves, hf = lane - g * halves;
+        tma_load_3d_hint(stage + lane * kUmmaBoxBytes, tmap, 0, a.row0 + r0 + g * 8,
+                         ss * KS + hf * kUmmaStepKBlocks, &misc->full_bar[pos.slot], policy);
       }
       pos.advance();
     }
@@ -158,6 +183,18 @@ struct UmmaState {
   }
 };
 
+// cp.async.wait_group with a run-time count (the instruction takes an immediate).
+__device__ __forceinline__ void cp_async_wait_pending(int n) {
+  switch (n) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+  }
+}
+
 __device__ __forceinline__ void cp_async16_zfill(void *dst, const void *src, bool real) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src),
                "r"(real ? 16u : 0u)
@@ -180,43 +217,63 @@ __device__ __noinline__ void linear_consume_umma_t(WaitCtx &wc, char *smem, Misc
   const int XB = umma_unit_kblocks(N);               // k-blocks per unit
   const int nkb = a.K / kUmmaKBlock;                 // multiple of kUmmaStepKBlocks
   const int nunits = nkb / XB;
-  const int nsteps = nkb / kUmmaStepKBlocks;
+  const int KS = umma_step_kblocks(a);               // k-blocks per weight stage
+  const int nsteps = nkb / KS;
   const int nblocks = (a.nrows + kUmmaBlockRows - 1) / kUmmaBlockRows;
+  // Back-to-back MMAs into one accumulator serialise on its read-modify-write (about 100 ns
+  // each, whatever M and N), so the four 16-wide K steps of a k-block go to up to four
+  // accumulators, summed in the epilogue.
+  const int nacc = min(kUmmaKBlock / 16, kUmmaTmemCols / (nblocks * N));
   const uint32_t tmem = misc->tmem_base;
 
   if (warp == 0) {
     // ------------------------------------------------------------ MMA issuer
-    const uint32_t idesc = umma_instr_desc(128, N, F16);
-    UmmaState xcur = us;
-    const int units_per_step = kUmmaStepKBlocks / XB;
+    const uint32_t idesc = umma_instr_desc(kUmmaBlockRows, N, F16);
+    UmmaState xbase = us;   // unit holding the first k-block of the current step
+    // timeline (lane 0): [4] first stage in hand, [5] last MMA issued, [6] / [7] ns spent
+    // waiting for weight stages / token units
+    unsigned long long *prec = lane == 0 ? misc->prof_rec : nullptr;
+    unsigned long long wait_w = 0, wait_x = 0;
     for (int ss = 0; ss < nsteps; ++ss) {
-      // the token units of this super-step
-      UmmaState xnext = xcur;
-      bool xok = true;
-      for (int u = 0; u < units_per_step; ++u) {
-        xok = wait_mbar(wc, &misc->xfull_bar[xnext.xslot], xnext.xphase) && xok;
-        xnext.advance();
-      }
       for (int blk = 0; blk < nblocks; ++blk) {
-        const bool got = wait_mbar(wc, &misc->full_bar[pos.slot], pos.phase) && xok;
-        if (got) {
-          if (lane == 0) {
-            tcgen05_after_sync();
-            const char *stage = smem + kOffRing + pos.slot * kStageBytes;
-            for (int j = 0; j < kUmmaStepKBlocks; ++j) {
-              uint32_t slot = xcur.xslot + uint32_t(j / XB);
-              if (slot >= uint32_t(kUmmaUnits)) slot -= kUmmaUnits;
-              const unsigned long long ad =
-                  umma_smem_desc(stage + j * 1024, kUmmaStepKBlocks * 1024);
-              const unsigned long long bd =
-                  umma_smem_desc(xring + slot * kUmmaUnitBytes + (j % XB) * N * 128, 1024);
+        unsigned long long tw = prec ? globaltimer() : 0ull;
+        const bool got = wait_mbar(wc, &misc->full_bar[pos.slot], pos.phase);
+        if (prec) {
+          const unsigned long long now = globaltimer();
+          wait_w += now - tw;
+          if (ss == 0 && blk == 0) prec[4] = now;
+        }
+        const char *stage = smem + kOffRing + pos.slot * kStageBytes;
+        if (got && lane == 0) tcgen05_after_sync();
+        UmmaState xu = xbase;
+        for (int j = 0; j < KS; ++j) {
+          const int ju = j % XB;
+          // a token unit is awaited when the first block first touches it ...
+          bool xok = true;
+          if (blk == 0 && ju == 0) {
+            tw = prec ? globaltimer() : 0ull;
+            xok = wait_mbar(wc, &misc->xfull_bar[xu.xslot], xu.xphase);
+            if (prec) wait_x += globaltimer() - tw;
+          }
+          if (got && xok && lane == 0) {
+            if (blk == 0 && ju == 0) tcgen05_after_sync();
+            const unsigned long long ad = umma_smem_desc(stage + j * 1024, uint32_t(KS) * 1024u);
+            const unsigned long long bd =
+                umma_smem_desc(xring + xu.xslot * kUmmaUnitBytes + ju * N * 128, 1024);
 #pragma unroll
-              for (int kk = 0; kk < kUmmaKBlock / 16; ++kk) {
-                // 32 bytes per 16-wide K step inside the swizzle atom: +2 in the address field
-                umma_f16(tmem + uint32_t(blk * N), ad + 2ull * kk, bd + 2ull * kk, idesc,
-                         ss > 0 || j > 0 || kk > 0);
-              }
+            for (int kk = 0; kk < kUmmaKBlock / 16; ++kk) {
+              // 32 bytes per 16-wide K step inside the swizzle atom: +2 in the address field
+              const int acc = kk % nacc;
+              umma_f16(tmem + uint32_t((blk * nacc + acc) * N), ad + 2ull * kk, bd + 2ull * kk,
+                       idesc, ss > 0 || j > 0 || kk >= nacc);
             }
+            // ... and handed back when the last block is done with it
+            if (blk == nblocks - 1 && ju == XB - 1) umma_commit(&misc->xempty_bar[xu.xslot]);
+          }
+          if (ju == XB - 1) xu.advance();
+        }
+        if (got && !wc.failed) {
+          if (lane == 0) {
             umma_commit(&misc->empty_bar[pos.slot]);   // one of the 8 arrivals, when the MMAs are done
           } else if (lane < kConsumerWarps) {
             mbar_arrive(&misc->empty_bar[pos.slot]);   // the other 7: nothing else reads the stage
@@ -224,17 +281,15 @@ __device__ __noinline__ void linear_consume_umma_t(WaitCtx &wc, char *smem, Misc
         }
         __syncwarp();
         pos.advance();
+        if (blk == nblocks - 1) xbase = xu;
       }
-      if (lane == 0 && xok) {
-        UmmaState xr = xcur;
-        for (int u = 0; u < units_per_step; ++u) {
-          umma_commit(&misc->xempty_bar[xr.xslot]);
-          xr.advance();
-        }
-      }
-      xcur = xnext;
     }
     if (lane == 0) umma_commit(&misc->acc_bar);
+    if (prec) {
+      prec[5] = globaltimer();
+      prec[6] = wait_w;
+      prec[7] = wait_x;
+    }
     __syncwarp();
   } else {
     // ------------------------------------------------------------ token stagers (7 warps)
@@ -243,7 +298,11 @@ __device__ __noinline__ void linear_consume_umma_t(WaitCtx &wc, char *smem, Misc
     const int c = lane & 7, rb = (warp - 1) * 4 + (lane >> 3);
     constexpr int kRowsPerPass = (kConsumerWarps - 1) * 4;                         // 28
     constexpr int kMaxPasses = (kUmmaMaxBatch + kRowsPerPass - 1) / kRowsPerPass;  // 3
-    constexpr int kDepth = 3;                                                      // units in flight
+    // Units in flight.  The first block of a multi-block task holds every unit of a step
+    // (KS / XB of the 7) until the last block has used them, so the copies can only run
+    // 7 - KS / XB units ahead of the oldest unit still needed; a one-block task hands its
+    // units back as it goes.
+    const int kDepth = nblocks == 1 ? 5 : min(5, kUmmaUnits - KS / XB);
     float ssq[kMaxPasses] = {0.f, 0.f, 0.f};
     UmmaState xi = us, xf = us;   // issue / finish positions
     for (int u = 0; u < nunits + kDepth; ++u) {
@@ -253,6 +312,8 @@ __device__ __noinline__ void linear_consume_umma_t(WaitCtx &wc, char *smem, Misc
         if (free_ok) {
           for (int j = 0; j < XB; ++j) {
             const int k = (u * XB + j) * kUmmaKBlock + c * 8;
+            // the norm weights of this unit are wanted a few units from now: bring them to L1
+            if (has_nw && rb < B) asm volatile("prefetch.global.L1 [%0];" ::"l"(nw + k));
 #pragma unroll
             for (int p = 0; p < kMaxPasses; ++p) {
               const int b = rb + p * kRowsPerPass;
@@ -269,7 +330,7 @@ __device__ __noinline__ void linear_consume_umma_t(WaitCtx &wc, char *smem, Misc
       asm volatile("cp.async.commit_group;" ::: "memory");
       if (u >= kDepth) {
         const int uf = u - kDepth;
-        asm volatile("cp.async.wait_group %0;" ::"n"(kDepth) : "memory");
+        cp_async_wait_pending(kDepth);
         char *unit = xring + xf.xslot * kUmmaUnitBytes;
         if (norm) {
           for (int j = 0; j < XB; ++j) {
@@ -332,17 +393,24 @@ __device__ __noinline__ void linear_consume_umma_t(WaitCtx &wc, char *smem, Misc
   consumer_bar();   // RMS factors published, every MMA of the task complete
   tcgen05_after_sync();
 
-  // Epilogue.  Warp w reads TMEM lanes 32 * (w % 4) .. + 31 (its weight rows) and half of
-  // the token columns; only lanes 0..63 hold rows of a block.
+  // Epilogue.  With M = 64 row r of a block is TMEM lane 32 * (r / 16) + r % 16: warp w reads
+  // the lane quarter w % 4, whose lower 16 lanes hold rows 16 * (w % 4) .. + 15, and half of
+  // the token columns.
   const int lq = warp & 3, chalf = warp >> 2;
-  if (lq < 2 && !wc.failed) {
+  if (!wc.failed) {
     for (int blk = 0; blk < nblocks; ++blk) {
-      const int r = blk * kUmmaBlockRows + lq * 32 + lane;   // row of the task
-      const bool live = r < a.nrows;
+      const int r = blk * kUmmaBlockRows + lq * 16 + lane;   // row of the task (lanes < 16)
+      const bool live = lane < 16 && r < a.nrows;
       const int p = a.row0 + r;                               // row of the weight
       for (int c0 = chalf * (N / 2); c0 < (chalf + 1) * (N / 2); c0 += 8) {
         float v[8];
-        tmem_ld8(tmem + (uint32_t(lq * 32) << 16) + uint32_t(blk * N + c0), v);
+        tmem_ld8(tmem + (uint32_t(lq * 32) << 16) + uint32_t(blk * nacc * N + c0), v);
+        for (int acc = 1; acc < nacc; ++acc) {
+          float v2[8];
+          tmem_ld8(tmem + (uint32_t(lq * 32) << 16) + uint32_t((blk * nacc + acc) * N + c0), v2);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] += v2[i];
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int b = c0 + i;

@@ -55,6 +55,7 @@ struct ypk_handle {
   void *d_tmaps = nullptr;       // CUtensorMap[], one per distinct K / V cache tensor
   std::vector<uint64_t> tmap_keys;  // device address of the cache each map describes
   bool use_tmem = false;            // some LINEAR task has a weight tensor map
+  int umma_policy = 0;              // YPK_TENSOR_CORE: auto (by estimated cost) / always / never
   int *d_request_ids = nullptr, *d_page_queue = nullptr, *d_kv_tmp = nullptr, *d_bstate = nullptr;
   // progress
   long long base_iter = 0;
@@ -392,6 +393,9 @@ int ypk_create(const ypk_config *cfg, ypk_handle **out) {
   }
   ypk_handle *h = new ypk_handle();
   h->cfg = *cfg;
+  if (const char *pol = getenv("YPK_TENSOR_CORE")) {
+    h->umma_policy = !strcmp(pol, "always") ? 1 : !strcmp(pol, "never") ? 2 : 0;
+  }
   if (h->cfg.wait_budget_ns == 0) h->cfg.wait_budget_ns = 2000000000ull;
   memset(&h->status, 0, sizeof h->status);
   h->status.fail_task = h->status.fail_event = h->status.fail_worker = -1;
@@ -881,6 +885,7 @@ int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_
   rt.end_count = h->end_count;
   rt.tmaps = h->d_tmaps;
   rt.use_tmem = h->use_tmem ? 1 : 0;
+  rt.umma_policy = h->umma_policy;
   for (int p = 0; p < 8; ++p) rt.arena[p] = h->peer_arena[p];
   if (h->arena)
     for (int p = 0; p < c.world_size; ++p)
