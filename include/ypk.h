@@ -77,6 +77,15 @@ enum ypk_task_type {
 #define YPK_F_F16 0x8u         /* operands are fp16 instead of bf16        */
 #define YPK_F_ROPE 0x10u       /* ATTENTION: rotate new q/k                */
 #define YPK_F_NORM_NOWEIGHT 0x40u /* LINEAR: RMSNorm without a weight      */
+/* Flagged-word hand-off between tasks (no event, no fence): a [tokens][ld] tensor of 16-bit
+ * values travels as [max_tokens][ld / 2] 8-byte words {two values, 32-bit tag}; the tag
+ * names the iteration and the producing operator, a reader polls until it sees it. */
+#define YPK_F_LL_IN 0x100u     /* LINEAR: x comes as flagged words (ptr[5]);
+                                  ALLREDUCE: the ranks' partials do (buf)   */
+#define YPK_F_LL_RES 0x200u    /* LINEAR: residual as flagged words (ptr[6]) */
+#define YPK_F_LL_OUT 0x400u    /* result also leaves as flagged words (ptr[7]) */
+#define YPK_F_LL_PUSH 0x800u   /* LINEAR: partial sum: flagged words only, into slot `rank`
+                                  of ptr[7] = [world][max_tokens][ld / 2] on every rank */
 
 #define YPK_TASK_NPTR 8
 #define YPK_TASK_NINT 16
@@ -91,8 +100,10 @@ enum ypk_task_type {
  * (persistent_kernel/runtime_header.h:136-269) with run-time shapes instead
  * of template arguments.  176 bytes, 16-byte aligned.
  *
- * LINEAR:  ptr = {x, W, out, norm_w, residual}
- *          iarg = {K, row0, nrows, ldx, ldw, ldout, ldres, out_col0}
+ * LINEAR:  ptr = {x, W, out, norm_w, residual, ll_x, ll_residual, ll_out}
+ *          iarg = {K, row0, nrows, ldx, ldw, ldout, ldres, out_col0}; iarg[9] is filled in
+ *                  by ypk_load_graph (TMA tensor map of W, or -1); iarg[10..12] = tag ids
+ *                  of the producers of x and of the residual, and this operator's own
  *          farg = {eps}
  * EMBED:   ptr = {ids(int64), table, out}; iarg = {hidden, col0, ncols,
  *                  ldtable, ldout}
@@ -106,7 +117,10 @@ enum ypk_task_type {
  * ALLREDUCE: ptr = {in, buf, out, signals} (buf, signals from the symmetric arena;
  *          buf = [2][world][max_tokens][hidden] 16-bit, signals uint64[])
  *          iarg = {col0, ncols, ld_in, ld_out, hidden, max_tokens, half, signal index,
- *                  world, rank}
+ *                  world, rank}; with YPK_F_LL_IN | YPK_F_LL_OUT: buf = [world][max_tokens]
+ *                  [hidden / 2] flagged words pushed by the producing LINEAR tasks,
+ *                  ptr[7] = flagged-word copy of out, iarg[10] / iarg[12] = tag ids of the
+ *                  producer / of this operator, no signals
  * RMSNORM: ptr = {x, w, out}; iarg = {K, row0, nrows, ldx, ldout}; farg = {eps}
  * SILU_MUL: ptr = {in, out}; iarg = {col0, ncols, group, ldin, ldout}
  * The number of batch rows is the active-token count of the iteration (mode 1) or the

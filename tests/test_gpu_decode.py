@@ -19,7 +19,7 @@ def tiny_shape(layers=2):
 
 
 def run_generation(prompt_lens, max_seq, *, max_requests, max_tokens, max_pages, page_size=64,
-                   seed=3, layers=2, pause_every=0):
+                   seed=3, layers=2, pause_every=0, handoff=None):
     shape = tiny_shape(layers)
     w = llama.init_weights(shape, "cuda", seed, std=0.02)  # BASELINE: weights ~N(0, 0.02)
     g = torch.Generator().manual_seed(seed)
@@ -32,7 +32,8 @@ def run_generation(prompt_lens, max_seq, *, max_requests, max_tokens, max_pages,
     plen = torch.tensor(prompt_lens, dtype=torch.int32, device="cuda")
     ypk, st = llama.build_decode_kernel(
         shape, w, tokens=tokens, prompt_lengths=plen, max_num_batched_requests=max_requests,
-        max_num_batched_tokens=max_tokens, max_num_pages=max_pages, page_size=page_size)
+        max_num_batched_tokens=max_tokens, max_num_pages=max_pages, page_size=page_size,
+        handoff=handoff)
     if pause_every:
         for _ in range(10000):
             ypk(max_iterations=pause_every)
@@ -68,6 +69,35 @@ def test_single_request_prefill_then_decode():
 def test_continuous_batching_more_requests_than_slots():
     # 5 requests through 2 slots: retirement, page recycling, admission mid-run
     run_generation([3, 17, 9, 1, 12], 24, max_requests=2, max_tokens=8, max_pages=4)
+
+
+def test_whole_operator_events_instead_of_flagged_words():
+    """The hand-off every graph with more than 8 tokens uses, forced on a small one."""
+    run_generation([3, 17, 9], 24, max_requests=2, max_tokens=8, max_pages=4, handoff="event")
+
+
+def test_reset_and_rerun_with_flagged_words():
+    """Tags keep growing across ypk_reset: words of the first run never pass for the second."""
+    shape = tiny_shape(2)
+    w = llama.init_weights(shape, "cuda", 7, std=0.02)
+    tokens = torch.zeros(1, 40, dtype=torch.int64)
+    tokens[0, :11] = torch.randint(0, shape.vocab_size, (11,), generator=torch.Generator().manual_seed(7))
+    first = tokens.clone()
+    tokens = tokens.cuda()
+    plen = torch.tensor([11], dtype=torch.int32, device="cuda")
+    ypk, st = llama.build_decode_kernel(shape, w, tokens=tokens, prompt_lengths=plen,
+                                        max_num_batched_requests=1, max_num_batched_tokens=8,
+                                        max_num_pages=1, page_size=64, handoff="ll")
+    ypk()
+    run1 = tokens.cpu().clone()
+    tokens.copy_(first)
+    ypk.reset()
+    ypk(max_iterations=2)
+    ypk()
+    torch.cuda.synchronize()
+    assert ypk.status().error == 0 and ypk.status().finished == 1
+    assert torch.equal(tokens.cpu(), run1)
+    ypk.finalize()
 
 
 def test_sequence_crosses_page_boundaries():

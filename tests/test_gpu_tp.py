@@ -20,7 +20,7 @@ def _free_port():
     return p
 
 
-def _rank_main(rank, port, prompt_lens, max_seq, ret):
+def _rank_main(rank, port, prompt_lens, max_seq, ret, handoff):
     import torch.distributed as dist
     from tests.util import oracle_weights, replay_against_oracle
     from yirage_b200 import llama
@@ -40,7 +40,8 @@ def _rank_main(rank, port, prompt_lens, max_seq, ret):
     plen = torch.tensor(prompt_lens, dtype=torch.int32, device=dev)
     ypk, st = llama.build_decode_kernel(
         shape, w, tokens=tokens, prompt_lengths=plen, max_num_batched_requests=2,
-        max_num_batched_tokens=8, max_num_pages=4, page_size=64, world_size=WORLD, rank=rank)
+        max_num_batched_tokens=8, max_num_pages=4, page_size=64, world_size=WORLD, rank=rank,
+        handoff=handoff)
     dist.barrier()
     ypk()
     torch.cuda.synchronize()
@@ -66,9 +67,10 @@ def _rank_main(rank, port, prompt_lens, max_seq, ret):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < WORLD, reason="needs 2 GPUs")
-def test_tp2_decode_matches_oracle_and_ranks_agree():
+@pytest.mark.parametrize("handoff", ["ll", "event"])
+def test_tp2_decode_matches_oracle_and_ranks_agree(handoff):
     import torch.multiprocessing as mp
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_rank_main, args=(_free_port(), [9, 14, 5], 30, ret), nprocs=WORLD, join=True)
+    mp.spawn(_rank_main, args=(_free_port(), [9, 14, 5], 30, ret, handoff), nprocs=WORLD, join=True)
     assert "ok" in ret, "rank 0 did not finish its checks"

@@ -11,7 +11,7 @@ from yirage_b200 import _native as N
 from yirage_b200 import llama, lowering
 
 
-def small_graph(world_size=1, rank=0, layers=2):
+def small_graph(world_size=1, rank=0, layers=2, handoff="event"):
     shape = llama.LlamaShape(hidden_size=512, intermediate_size=1024, num_hidden_layers=layers,
                              num_attention_heads=8, num_key_value_heads=2, vocab_size=2048)
     w = llama.init_weights(shape, "cpu", 0)
@@ -19,7 +19,8 @@ def small_graph(world_size=1, rank=0, layers=2):
     pl = torch.tensor([5, 7], dtype=torch.int32)
     return shape, llama.build_decode_kernel(
         shape, w, tokens=tokens, prompt_lengths=pl, max_num_batched_requests=2,
-        max_num_batched_tokens=8, max_num_pages=8, page_size=64, compile=False)[0]
+        max_num_batched_tokens=8, max_num_pages=8, page_size=64, compile=False,
+        handoff=handoff)[0]
 
 
 def test_demo_layer_sequence_fuses_to_five_operators_per_layer():
@@ -56,6 +57,45 @@ def test_every_task_runs_once_per_iteration_and_graph_cannot_deadlock():
     # queues are in task order
     for a, b in zip(g.queue_off[:-1], g.queue_off[1:]):
         assert g.queue[a:b] == sorted(g.queue[a:b])
+
+
+def test_flagged_word_handoff_plan():
+    """At most 8 tokens: the residual stream and the MLP activation travel as flagged words.
+    Their readers wait for no event, their producers trigger none; everything else keeps the
+    whole-operator events."""
+    _, ypk = small_graph(handoff="ll")
+    g = ypk.lower(148)
+    assert set(lowering.simulate(g, iterations=3)) == {3}
+    kinds = [o.kind for o in g.ops]
+    by_op = {}
+    for ts in g.tasks:
+        by_op.setdefault(ts.op_id, []).append(ts)
+    LL = N.F_LL_IN | N.F_LL_RES | N.F_LL_OUT | N.F_LL_PUSH
+    # layer 0: qkv (x from the embedding: event), o_proj, gate/up, down; layer 1: qkv ...
+    qkv0, att0, o0, gu0, dn0, qkv1, att1, o1 = (by_op[i][0] for i in range(1, 9))
+    assert qkv0.flags & LL == 0 and qkv0.dep_event == 0 and qkv0.trig_event == 1
+    assert att0.dep_event == 1 and att0.trig_event == 2
+    assert o0.flags & LL == N.F_LL_OUT and o0.dep_event == 2 and o0.trig_event == -1
+    assert gu0.flags & LL == N.F_LL_IN | N.F_LL_OUT and gu0.dep_event == -1 and gu0.trig_event == -1
+    assert dn0.flags & LL == N.F_LL_IN | N.F_LL_RES | N.F_LL_OUT and dn0.dep_event == -1
+    assert qkv1.flags & LL == N.F_LL_IN and qkv1.dep_event == -1 and qkv1.trig_event == 6
+    assert o1.flags & LL == N.F_LL_RES | N.F_LL_OUT and o1.dep_event == 7
+    # tags: a reader polls for the tag its producer writes
+    assert gu0.flagged_deps == [o0.flagged_out] and dn0.flagged_deps == [gu0.flagged_out, o0.flagged_out]
+    assert qkv1.flagged_deps == [dn0.flagged_out] and o1.flagged_deps == [dn0.flagged_out]
+    # flagged results come in pairs of columns: rows of every such slab are even
+    for ts in g.tasks:
+        if ts.type == N.TASK_LINEAR and ts.flags & (N.F_LL_OUT | N.F_LL_RES):
+            assert ts.iarg[1] % 2 == 0 and ts.iarg[2] % 2 == 0
+    # the lm_head reads flagged words and hands its logits to the arg-max through an event
+    lm = by_op[kinds.index("argmax_partial") - 1][0]
+    assert lm.flags & LL == N.F_LL_IN and lm.trig_event >= 0
+    # dropping a producer is caught
+    victim = next(i for i, ts in enumerate(g.tasks) if ts.flagged_out == gu0.flagged_out)
+    g.tasks[victim].flagged_out = -1
+    g.tasks[victim].flagged_deps = [255]
+    with pytest.raises(RuntimeError, match="deadlock"):
+        lowering.simulate(g, iterations=1)
 
 
 def test_a_broken_dependency_is_caught_by_the_simulator():

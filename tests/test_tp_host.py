@@ -15,7 +15,7 @@ def _free_port():
     return p
 
 
-def _rank_main(rank, port, ret):
+def _rank_main(rank, port, ret, handoff):
     import torch.distributed as dist
     from yirage_b200 import _native as N
     from yirage_b200 import llama, lowering
@@ -29,17 +29,27 @@ def _rank_main(rank, port, ret):
     ypk, _ = llama.build_decode_kernel(shape, w, tokens=tokens, prompt_lengths=plen,
                                        max_num_batched_requests=2, max_num_batched_tokens=8,
                                        max_num_pages=4, page_size=64, world_size=2, rank=rank,
-                                       compile=False)
+                                       compile=False, handoff=handoff)
     g = ypk.lower(148)
     kinds = [o.kind for o in g.ops]
     assert kinds.count("allreduce") == 2 * shape.num_hidden_layers
     assert set(lowering.simulate(g, 2)) == {2}
     ar = [t for t in g.tasks if t.type == N.TASK_ALLREDUCE]
-    assert {t.iarg[6] for t in ar} == {0, 1}, "alternate all-reduces use alternate buffer halves"
-    assert sorted(t.iarg[7] for t in ar) == list(range(len(ar))), "one counter per tile"
+    o_proj = [t for t in g.tasks if t.op_id == 3][0]
+    if handoff == "event":
+        assert {t.iarg[6] for t in ar} == {0, 1}, "alternate all-reduces use alternate buffer halves"
+        assert sorted(t.iarg[7] for t in ar) == list(range(len(ar))), "one counter per tile"
+    else:
+        # flagged words: the row-split projections push their partial sums to every rank, the
+        # all-reduce tasks poll them (no event in or out) and pass the sum on the same way
+        assert o_proj.flags & N.F_LL_PUSH and o_proj.flags & N.F_LL_OUT and o_proj.trig_event == -1
+        assert all(t.flags & N.F_LL_IN and t.flags & N.F_LL_OUT for t in ar)
+        assert all(t.dep_event == -1 and t.trig_event == -1 for t in ar)
+        assert all(t.flagged_deps == [o.flagged_out] for t, o in [(ar[0], o_proj)])
+        gate_up = [t for t in g.tasks if t.op_id == 5][0]
+        assert gate_up.flags & N.F_LL_IN and gate_up.flagged_deps == [ar[0].flagged_out]
     assert all(t.iarg[8] == 2 and t.iarg[9] == rank for t in ar)
     # the residual goes in on rank 0 only
-    o_proj = [t for t in g.tasks if t.op_id == 3][0]
     assert bool(o_proj.flags & N.F_RESIDUAL) == (rank == 0)
     # host-only handles: symmetric allocation, validation, handle exchange over gloo
     ypk.compile(dry_run=True)
@@ -55,11 +65,12 @@ def _rank_main(rank, port, ret):
     dist.destroy_process_group()
 
 
-def test_two_cpu_ranks_build_validate_and_connect(native_lib):
+@pytest.mark.parametrize("handoff", ["event", "ll"])
+def test_two_cpu_ranks_build_validate_and_connect(native_lib, handoff):
     import torch.multiprocessing as mp
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_rank_main, args=(_free_port(), ret), nprocs=2, join=True)
+    mp.spawn(_rank_main, args=(_free_port(), ret, handoff), nprocs=2, join=True)
     assert ret.get(0) and ret.get(1)
 
 

@@ -144,6 +144,9 @@ struct Runtime {
   const void *tmaps;   // array of 128-byte TMA tensor maps (K/V caches, LINEAR weights), or null
   int use_tmem;        // allocate tensor memory: some LINEAR task can take the tcgen05 path
   int umma_policy;     // 0 = by estimated cost, 1 = whenever eligible, 2 = never
+  // iterations run before the last reset: flagged-word tags and all-reduce arrival counts
+  // keep growing across resets (ll_epoch also steps over an aborted iteration)
+  unsigned long long ll_epoch, ar_epoch;
   char *arena[8];      // symmetric arena of every tensor-parallel rank as mapped here (own at [rank])
   unsigned long long *prof;
   int prof_stride;  // records per worker

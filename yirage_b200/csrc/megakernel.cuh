@@ -50,7 +50,91 @@ __device__ __forceinline__ unsigned long long make_word(long long iter, unsigned
          (static_cast<unsigned long long>(state) << 16) | static_cast<unsigned long long>(ntok);
 }
 
-__global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const Runtime rt) {
+// ------------------------------------------------------------------ task runners
+// Every task kind runs out of line, with the ring position and the failure state passed and
+// returned by value: each kind gets its own register allocation, and the worker loop keeps
+// its state in registers (a by-reference argument would pin it to local memory for the whole
+// kernel).  The call costs a few tens of nanoseconds per task.
+struct TaskRet {
+  RingPos pos;
+  bool failed;
+};
+struct TaskRetU {
+  RingPos pos;
+  UmmaState us;
+  bool failed;
+};
+
+__device__ __noinline__ TaskRet run_linear(const Runtime *rt, Misc *misc, char *smem, int worker,
+                                           int task, bool failed, int batch, long long iter,
+                                           RingPos pos) {
+  WaitCtx wc{rt, misc, worker, task, failed};
+  linear_consume_groups<false>(wc, smem, misc, *rt, misc->ctask, batch, iter, pos);
+  return TaskRet{pos, wc.failed};
+}
+__device__ __noinline__ TaskRet run_linear_ll(const Runtime *rt, Misc *misc, char *smem, int worker,
+                                              int task, bool failed, int batch, long long iter,
+                                              RingPos pos) {
+  WaitCtx wc{rt, misc, worker, task, failed};
+  linear_consume_groups<true>(wc, smem, misc, *rt, misc->ctask, batch, iter, pos);
+  return TaskRet{pos, wc.failed};
+}
+__device__ __noinline__ TaskRetU run_linear_umma(const Runtime *rt, Misc *misc, char *smem,
+                                                 int worker, int task, bool failed, int batch,
+                                                 RingPos pos, UmmaState us) {
+  WaitCtx wc{rt, misc, worker, task, failed};
+  linear_consume_umma(wc, smem, misc, misc->ctask, batch, pos, us);
+  return TaskRetU{pos, us, wc.failed};
+}
+__device__ __noinline__ TaskRet run_attention(const Runtime *rt, Misc *misc, char *smem, int worker,
+                                              int task, bool failed, RingPos pos) {
+  WaitCtx wc{rt, misc, worker, task, failed};
+  attention_consume(wc, smem, misc, *rt, misc->ctask, pos);
+  return TaskRet{pos, wc.failed};
+}
+__device__ __noinline__ bool run_small(const Runtime *rt, Misc *misc, int worker, int task,
+                                       bool failed, int batch, long long iter) {
+  WaitCtx wc{rt, misc, worker, task, failed};
+  const ypk_task &t = misc->ctask;
+  switch (t.type) {
+    case YPK_TASK_EMBED: embed_task(t, batch); break;
+    case YPK_TASK_ARGMAX_PARTIAL: argmax_partial_task(t, batch); break;
+    case YPK_TASK_ARGMAX_REDUCE: argmax_reduce_task(t, batch); break;
+    case YPK_TASK_RMSNORM: rmsnorm_task(t, batch); break;
+    case YPK_TASK_SILU_MUL: silu_mul_task(t, batch); break;
+    case YPK_TASK_ALLREDUCE:
+      if (t.flags & YPK_F_LL_IN) {
+        if (!allreduce_ll_task(wc, *rt, t, batch, iter)) wc.failed = true;
+      } else if (!allreduce_task(wc, misc, *rt, t, batch, iter)) {
+        wc.failed = true;
+      }
+      break;
+    default: break;
+  }
+  return wc.failed;
+}
+
+// Producer side, same convention; `ok` false = a wait gave up.
+struct ProdRet {
+  RingPos pos;
+  bool ok;
+};
+__device__ __noinline__ ProdRet run_produce(const Runtime *rt, Misc *misc, char *smem, int worker,
+                                            int task, int batch, RingPos pos,
+                                            unsigned long long policy) {
+  WaitCtx wc{rt, misc, worker, task, false};
+  const ypk_task &t = misc->ptask;
+  bool ok = true;
+  if (t.type == YPK_TASK_LINEAR) {
+    ok = linear_uses_umma(*rt, t, batch) ? linear_produce_umma(wc, smem, misc, *rt, t, pos, policy)
+                                         : linear_produce(wc, smem, misc, t, batch, pos, policy);
+  } else if (t.type == YPK_TASK_ATTENTION) {
+    ok = attention_produce(wc, smem, misc, *rt, t, pos);
+  }
+  return ProdRet{pos, ok};
+}
+
+__global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_constant__ Runtime rt) {
   extern __shared__ __align__(1024) char smem[];
   Misc *misc = reinterpret_cast<Misc *>(smem + kOffMisc);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -145,11 +229,10 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const Runtime
         __syncwarp();
         wc.task = ti;
         const ypk_task &t = misc->ptask;
-        if (t.type == YPK_TASK_LINEAR) {
-          ok = linear_uses_umma(rt, t, batch) ? linear_produce_umma(wc, smem, misc, rt, t, pos, policy)
-                                          : linear_produce(wc, smem, misc, t, batch, pos, policy);
-        } else if (t.type == YPK_TASK_ATTENTION) {
-          ok = attention_produce(wc, smem, misc, rt, t, pos);
+        if (t.type == YPK_TASK_LINEAR || t.type == YPK_TASK_ATTENTION) {
+          const ProdRet r = run_produce(&rt, misc, smem, worker, ti, batch, pos, policy);
+          pos = r.pos;
+          ok = r.ok;
         }
         __syncwarp();
       }
@@ -180,25 +263,30 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const Runtime
         }
         if (prec) prec[2] = globaltimer();
         if (ok) {
-          switch (t.type) {
-            case YPK_TASK_LINEAR:
-              if (linear_uses_umma(rt, t, batch)) {
-                linear_consume_umma(wc, smem, misc, t, batch, pos, ustate);
-                ++umma_done;
-              } else {
-                linear_consume(wc, smem, misc, t, batch, pos);
-              }
-              break;
-            case YPK_TASK_ATTENTION: attention_consume(wc, smem, misc, rt, t, pos); break;
-            case YPK_TASK_EMBED: embed_task(t, batch); break;
-            case YPK_TASK_ARGMAX_PARTIAL: argmax_partial_task(t, batch); break;
-            case YPK_TASK_ARGMAX_REDUCE: argmax_reduce_task(t, batch); break;
-            case YPK_TASK_RMSNORM: rmsnorm_task(t, batch); break;
-            case YPK_TASK_SILU_MUL: silu_mul_task(t, batch); break;
-            case YPK_TASK_ALLREDUCE:
-              if (!allreduce_task(wc, misc, rt, t, batch, iter)) wc.failed = true;
-              break;
-            default: break;
+          if (t.type == YPK_TASK_LINEAR) {
+            if (linear_uses_umma(rt, t, batch)) {
+              const TaskRetU r =
+                  run_linear_umma(&rt, misc, smem, worker, ti, wc.failed, batch, pos, ustate);
+              pos = r.pos;
+              ustate = r.us;
+              wc.failed = r.failed;
+              ++umma_done;
+            } else if (t.flags & (YPK_F_LL_IN | YPK_F_LL_RES | YPK_F_LL_OUT)) {
+              const TaskRet r =
+                  run_linear_ll(&rt, misc, smem, worker, ti, wc.failed, batch, iter, pos);
+              pos = r.pos;
+              wc.failed = r.failed;
+            } else {
+              const TaskRet r = run_linear(&rt, misc, smem, worker, ti, wc.failed, batch, iter, pos);
+              pos = r.pos;
+              wc.failed = r.failed;
+            }
+          } else if (t.type == YPK_TASK_ATTENTION) {
+            const TaskRet r = run_attention(&rt, misc, smem, worker, ti, wc.failed, pos);
+            pos = r.pos;
+            wc.failed = r.failed;
+          } else {
+            wc.failed = run_small(&rt, misc, worker, ti, wc.failed, batch, iter);
           }
           // a wait that gave up inside the task is known to one warp only: agree on it.
           if (wc.failed) misc->abort_flag = 1;

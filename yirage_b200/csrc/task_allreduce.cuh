@@ -22,6 +22,7 @@
 // iarg = {col0, ncols, ld_in, ld_out, hidden, max_tokens, half, signal index, world, rank}
 #pragma once
 #include "device_common.cuh"
+#include "ll_handoff.cuh"
 
 namespace ypk {
 
@@ -60,8 +61,9 @@ __device__ __forceinline__ bool allreduce_task(WaitCtx &wc, Misc *misc, const Ru
                  : "memory");
   }
   if (tid == 0) {
-    const unsigned long long need =
-        static_cast<unsigned long long>(world - 1) * static_cast<unsigned long long>(iter);
+    // arrivals are never reset: count the iterations of earlier runs too
+    const unsigned long long need = static_cast<unsigned long long>(world - 1) *
+                                    (rt.ar_epoch + static_cast<unsigned long long>(iter));
     misc->flag = wait_counter_sys(wc, reinterpret_cast<unsigned long long *>(sig) + sidx, need,
                                   -5) ? 1 : 0;
   }
@@ -92,6 +94,48 @@ __device__ __forceinline__ bool allreduce_task(WaitCtx &wc, Misc *misc, const Ru
     *reinterpret_cast<uint4 *>(out + size_t(b) * ld_out + col0 + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
   }
   return true;
+}
+
+// Flagged-word form (YPK_F_LL_IN | YPK_F_LL_OUT): the LINEAR tasks that produce the partial
+// sums have already pushed them, as {two values, tag} words, into slot `rank` of `buf` on
+// every rank (buf = [world][max_tokens][hidden / 2] words, single-buffered: a rank cannot
+// push the next partial of this buffer before it has consumed this one's sum on every rank).
+// This task only polls the world slots of its column slice, adds them in rank order in fp32,
+// rounds once and hands the sum on, again as flagged words (ptr[7]) plus the plain tensor.
+// No signal counters, no fences, no event in or out.
+__device__ __forceinline__ bool allreduce_ll_task(WaitCtx &wc, const Runtime &rt, const ypk_task &t,
+                                                  int batch, long long iter) {
+  const int tid = threadIdx.x;
+  const unsigned long long *buf = reinterpret_cast<const unsigned long long *>(t.ptr[1]);
+  uint16_t *out = reinterpret_cast<uint16_t *>(t.ptr[2]);
+  unsigned long long *ll_out = reinterpret_cast<unsigned long long *>(t.ptr[7]);
+  const int col0 = t.iarg[0], ncols = t.iarg[1], ld_out = t.iarg[3];
+  const int hidden = t.iarg[4], max_tok = t.iarg[5], world = t.iarg[8];
+  const uint32_t tag_in = ll_tag(rt, iter, t.iarg[10]), tag_out = ll_tag(rt, iter, t.iarg[12]);
+  const int nword = ncols >> 1;
+  const size_t slot_words = size_t(max_tok) * size_t(hidden >> 1);
+  LLPoll poll;
+  for (int idx = tid; idx < batch * nword; idx += kConsumerThreads) {
+    const int b = idx / nword, c = idx - b * nword;
+    const unsigned long long *src = buf + size_t(b) * size_t(hidden >> 1) + size_t(col0 >> 1) + c;
+    unsigned long long w[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) w[r] = r < world ? ll_load(src + r * slot_words) : 0ull;
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      if (r < world) {
+        while (!ll_ok(w[r], tag_in) && poll.again(wc)) w[r] = ll_load(src + r * slot_words);
+        const float2 f = unpack2(cvt_pair<false>(static_cast<uint32_t>(w[r])));
+        s0 += f.x;
+        s1 += f.y;
+      }
+    }
+    const uint32_t packed = uint32_t(cvt_out<false>(s0)) | (uint32_t(cvt_out<false>(s1)) << 16);
+    *reinterpret_cast<uint32_t *>(out + size_t(b) * ld_out + col0 + 2 * c) = packed;
+    ll_store(ll_out + size_t(b) * size_t(ld_out >> 1) + size_t(col0 >> 1) + c, ll_word(packed, tag_out));
+  }
+  return !poll.failed;
 }
 
 }  // namespace ypk

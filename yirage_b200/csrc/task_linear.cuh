@@ -19,6 +19,7 @@
 // rows beyond the real batch alias the last real row (their MMA columns are never stored).
 #pragma once
 #include "device_common.cuh"
+#include "ll_handoff.cuh"
 
 namespace ypk {
 
@@ -31,10 +32,25 @@ struct LinearArgs {
   int K, row0, nrows, ldx, ldw, ldout, ldres, out_col0;
   float eps;
   uint32_t flags;
+  // flagged-word hand-off (YPK_F_LL_*): x, residual and result as 8-byte words, and the
+  // tags to expect / to write this iteration
+  const unsigned long long *ll_x, *ll_res;
+  unsigned long long *ll_out;
+  uint32_t tag_x, tag_res, tag_out;
 };
 
-__device__ __forceinline__ LinearArgs linear_args(const ypk_task &t) {
+__device__ __forceinline__ LinearArgs linear_args(const ypk_task &t, const Runtime *rt = nullptr,
+                                                  long long iter = 0) {
   LinearArgs a;
+  a.ll_x = reinterpret_cast<const unsigned long long *>(t.ptr[5]);
+  a.ll_res = reinterpret_cast<const unsigned long long *>(t.ptr[6]);
+  a.ll_out = reinterpret_cast<unsigned long long *>(t.ptr[7]);
+  a.tag_x = a.tag_res = a.tag_out = 0;
+  if (rt != nullptr) {
+    a.tag_x = ll_tag(*rt, iter, t.iarg[10]);
+    a.tag_res = ll_tag(*rt, iter, t.iarg[11]);
+    a.tag_out = ll_tag(*rt, iter, t.iarg[12]);
+  }
   a.x = reinterpret_cast<const char *>(t.ptr[0]);
   a.w = reinterpret_cast<const char *>(t.ptr[1]);
   a.out = reinterpret_cast<char *>(t.ptr[2]);
@@ -127,6 +143,75 @@ __device__ __forceinline__ float silu_mul_ref(float g, float u) {
 // Writes the finished values of `nr` rows starting at task row r0.  val(r, b) returns the
 // fp32 dot product (before the RMS scale); res_s holds the residual slice of the task,
 // [batch][nrows] 16-bit, staged in shared memory when the task started.
+// Result pair (columns col, col + 1 of token b) in flagged-word form: into this GPU's copy,
+// or, for a partial sum (YPK_F_LL_PUSH), into slot `rank` of the copy on every rank; the
+// plain tensor is written too unless the values are partial.
+template <bool F16>
+__device__ __forceinline__ void ll_emit(const LinearArgs &a, const Runtime &rt, int b, int col,
+                                        float v0, float v1) {
+  const uint32_t packed = uint32_t(cvt_out<F16>(v0)) | (uint32_t(cvt_out<F16>(v1)) << 16);
+  const size_t widx = size_t(b) * size_t(a.ldout >> 1) + size_t(col >> 1);
+  const unsigned long long w = ll_word(packed, a.tag_out);
+  if (a.flags & YPK_F_LL_PUSH) {
+    const size_t off = size_t(reinterpret_cast<char *>(a.ll_out) - rt.arena[rt.rank]) +
+                       (size_t(rt.rank) * rt.max_tok * size_t(a.ldout >> 1) + widx) * 8;
+    for (int p = 0; p < rt.world; ++p)
+      ll_store_sys(reinterpret_cast<unsigned long long *>(rt.arena[p] + off), w);
+  } else {
+    *reinterpret_cast<uint32_t *>(reinterpret_cast<uint16_t *>(a.out) + size_t(b) * a.ldout + col) =
+        packed;
+    ll_store(a.ll_out + widx, w);
+  }
+}
+
+// Flagged-word epilogue (YPK_F_LL_OUT).  Values come from the per-warp partial tiles
+// (`pall` = [8 warps][16 rows][8 tokens]) or, for a K-chunked task, from `accs`
+// ([rows][8 tokens]); two neighbouring result columns per thread.
+template <bool F16>
+__device__ __forceinline__ void linear_epilogue_ll(const LinearArgs &a, const Runtime &rt,
+                                                const Misc *misc, const uint16_t *res_s, int r0,
+                                                int nr, int b0, int bc, const float *pall,
+                                                const float *accs) {
+  const int tid = threadIdx.x;
+  const bool norm = (a.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT)) != 0;
+  auto val = [&](int r, int b) {
+    if (pall == nullptr) return accs[r * kMaxBatch + b];
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) s += pall[(w * kRowBlock + r) * kMaxBatch + b];
+    return s;
+  };
+  if (a.flags & YPK_F_SILU_MUL) {
+    const int npair = nr >> 2;   // one 2 gate + 2 up granule = one pair of outputs
+    for (int idx = tid; idx < npair * bc; idx += kConsumerThreads) {
+      const int b = idx / npair, g = idx - b * npair;
+      const int rg = g * (2 * kSiluGran);
+      float g0 = val(rg, b), g1 = val(rg + 1, b), u0 = val(rg + 2, b), u1 = val(rg + 3, b);
+      if (norm) {
+        const float rn = misc->rnorm[b];
+        g0 *= rn; g1 *= rn; u0 *= rn; u1 *= rn;
+      }
+      const int col = a.out_col0 + ((a.row0 + r0) >> 1) + g * kSiluGran;
+      ll_emit<F16>(a, rt, b0 + b, col, silu_mul_ref(g0, u0), silu_mul_ref(g1, u1));
+    }
+  } else {
+    const int npair = nr >> 1;
+    for (int idx = tid; idx < npair * bc; idx += kConsumerThreads) {
+      const int b = idx / npair, r = (idx - b * npair) * 2;
+      float v0 = val(r, b), v1 = val(r + 1, b);
+      if (norm) {
+        v0 *= misc->rnorm[b];
+        v1 *= misc->rnorm[b];
+      }
+      if (a.flags & YPK_F_RESIDUAL) {
+        v0 += cvt_one<F16>(res_s[b * a.nrows + r0 + r]);
+        v1 += cvt_one<F16>(res_s[b * a.nrows + r0 + r + 1]);
+      }
+      ll_emit<F16>(a, rt, b0 + b, a.out_col0 + a.row0 + r0 + r, v0, v1);
+    }
+  }
+}
+
 template <bool F16, typename ValFn>
 __device__ __forceinline__ void linear_epilogue(const LinearArgs &a, const Misc *misc,
                                                 const uint16_t *res_s, int r0, int nr, int b0,
@@ -176,10 +261,97 @@ __device__ __forceinline__ void publish_rnorm(const LinearArgs &a, Misc *misc, f
   consumer_bar();
 }
 
+// Residual slice of a task from flagged words (YPK_F_LL_RES): pairs of columns, polled until
+// this iteration's producer has written them.  Returns true if a poll gave up.
+__device__ __forceinline__ bool linear_stage_residual_ll(WaitCtx &wc, const LinearArgs &a,
+                                                      uint16_t *res_s, int b0, int B) {
+  LLPoll poll;
+  const int npair = a.nrows >> 1;
+  for (int i = threadIdx.x; i < npair * B; i += kConsumerThreads) {
+    const int b = i / npair, rp = i - b * npair;
+    const unsigned long long *src = a.ll_res + size_t(b0 + b) * size_t(a.ldres >> 1) +
+                                    size_t((a.out_col0 + a.row0) >> 1) + rp;
+    unsigned long long w = ll_load(src);
+    while (!ll_ok(w, a.tag_res) && poll.again(wc)) w = ll_load(src);
+    *reinterpret_cast<uint32_t *>(res_s + b * a.nrows + 2 * rp) = static_cast<uint32_t>(w);
+  }
+  return poll.failed;
+}
+
+// x[b0 .. b0 + B, k0 .. k0 + klen) from flagged words (YPK_F_LL_IN) into xs, multiplied by the
+// norm weight, with the sums of squares added to ss[].  A thread takes 4 columns (two words,
+// one 16-byte load) per step and has the loads of four steps in flight; words that are not
+// there yet are polled again, all stragglers of the four steps in one round, so that a round
+// costs one trip to L2 however many words are late.  Returns true if a poll gave up.
 template <bool F16>
+__device__ __forceinline__ bool linear_stage_x_ll(WaitCtx &wc, const LinearArgs &a, uint16_t *xs,
+                                               int xpitch, int b0, int B, int k0, int klen,
+                                               float *ss) {
+  const int tid = threadIdx.x;
+  const uint16_t *nw = reinterpret_cast<const uint16_t *>(a.norm_w);
+  const bool has_nw = (a.flags & YPK_F_NORM) != 0;
+  LLPoll poll;
+  constexpr int kU = 4;
+  for (int kb = tid * 4; kb < klen; kb += kConsumerThreads * 4 * kU) {
+    uint2 wnv[kU];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int k = kb + u * kConsumerThreads * 4;
+      wnv[u] = make_uint2(0u, 0u);
+      if (has_nw && k < klen) wnv[u] = __ldg(reinterpret_cast<const uint2 *>(nw + k0 + k));
+    }
+    for (int b = 0; b < B; ++b) {
+      const unsigned long long *row = a.ll_x + size_t(b0 + b) * size_t(a.ldx >> 1);
+      unsigned long long w0[kU], w1[kU];
+      bool late[kU];
+#pragma unroll
+      for (int u = 0; u < kU; ++u) late[u] = kb + u * kConsumerThreads * 4 < klen;
+      for (;;) {
+#pragma unroll
+        for (int u = 0; u < kU; ++u)
+          if (late[u]) ll_load2(row + ((k0 + kb + u * kConsumerThreads * 4) >> 1), w0[u], w1[u]);
+        bool any = false;
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          if (late[u]) late[u] = !(ll_ok(w0[u], a.tag_x) && ll_ok(w1[u], a.tag_x));
+          any |= late[u];
+        }
+        if (!any || !poll.again(wc)) break;
+      }
+      float s = 0.f;
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const int k = kb + u * kConsumerThreads * 4;
+        if (k < klen) {
+          const uint32_t p[2] = {static_cast<uint32_t>(w0[u]), static_cast<uint32_t>(w1[u])};
+          const uint32_t q[2] = {wnv[u].x, wnv[u].y};
+          uint32_t o[2];
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const float2 f = unpack2(cvt_pair<F16>(p[i]));
+            s += f.x * f.x + f.y * f.y;
+            if (has_nw) {
+              const float2 g = unpack2(cvt_pair<F16>(q[i]));
+              o[i] = uint32_t(cvt_out<F16>(f.x * g.x)) | (uint32_t(cvt_out<F16>(f.y * g.y)) << 16);
+            } else {
+              o[i] = p[i];
+            }
+          }
+          *reinterpret_cast<uint2 *>(xs + b * xpitch + k) = make_uint2(o[0], o[1]);
+        }
+      }
+      ss[b] += s;
+    }
+  }
+  return poll.failed;
+}
+
+// LL = the task uses the flagged-word hand-off somewhere (YPK_F_LL_*); the two instantiations
+// are separate out-of-line functions, so the event path compiles as if the other did not exist.
+template <bool F16, bool LL>
 __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Misc *misc,
-                                                     const LinearArgs &a, int b0, int B,
-                                                     RingPos &pos) {
+                                                     const Runtime &rt, const LinearArgs &a,
+                                                     int b0, int B, RingPos &pos) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint16_t *xs = reinterpret_cast<uint16_t *>(smem + kOffXs);
   float *part = reinterpret_cast<float *>(smem + kOffPart);          // [2][8 warps][16][8]
@@ -197,7 +369,10 @@ __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Mi
   if (chunked) {
     for (int i = tid; i < a.nrows * kMaxBatch; i += kConsumerThreads) accs[i] = 0.f;
   }
-  if (a.flags & YPK_F_RESIDUAL) {
+  bool poll_failed = false;
+  if (LL && (a.flags & YPK_F_RESIDUAL) && (a.flags & YPK_F_LL_RES)) {
+    if constexpr (LL) poll_failed = linear_stage_residual_ll(wc, a, res_s, b0, B);
+  } else if (a.flags & YPK_F_RESIDUAL) {
     for (int i = tid; i < a.nrows * B; i += kConsumerThreads) {
       const int b = i / a.nrows, r = i - b * a.nrows;
       res_s[i] = __ldcg(reinterpret_cast<const uint16_t *>(a.res) + size_t(b0 + b) * a.ldres +
@@ -224,7 +399,9 @@ __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Mi
     // K).  With a norm the values pass through registers: multiplied by the norm weight and
     // squared into the RMS statistics (fp32, as rmsnorm_hopper.cuh); the loads of four
     // iterations are issued before the first is used.
-    if (!norm) {
+    if (LL && (a.flags & YPK_F_LL_IN)) {
+      if constexpr (LL) poll_failed |= linear_stage_x_ll<F16>(wc, a, xs, xpitch, b0, B, k0, klen, ss);
+    } else if (!norm) {
       for (int k = tid * 8; k < klen; k += kConsumerThreads * 8) {
 #pragma unroll
         for (int b = 0; b < kMaxBatch; ++b) {
@@ -284,6 +461,9 @@ __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Mi
         }
       }
     }
+    // a poll that gave up is known to one thread: the mbarrier waits below need the
+    // failure state to be the same across the warp
+    if constexpr (LL) wc.failed = __any_sync(0xffffffffu, poll_failed || wc.failed);
     consumer_bar();
     if (tid == 0 && misc->prof_rec && k0 == 0) misc->prof_rec[4] = globaltimer();
 
@@ -353,7 +533,11 @@ __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Mi
         return s;
       };
       if (!chunked) {
-        linear_epilogue<F16>(a, misc, res_s, r0, nr, b0, B, tid, summed);
+        if (LL && (a.flags & YPK_F_LL_OUT)) {
+          if constexpr (LL) linear_epilogue_ll<F16>(a, rt, misc, res_s, r0, nr, b0, B, pall, nullptr);
+        } else {
+          linear_epilogue<F16>(a, misc, res_s, r0, nr, b0, B, tid, summed);
+        }
       } else {
         for (int idx = tid; idx < nr * B; idx += kConsumerThreads) {
           const int b = idx / nr, r = idx - b * nr;
@@ -372,21 +556,27 @@ __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Mi
       consumer_bar();
     }
     auto fromacc = [&](int r, int b) { return accs[r * kMaxBatch + b]; };
-    linear_epilogue<F16>(a, misc, res_s, 0, a.nrows, b0, B, tid, fromacc);
+    if (LL && (a.flags & YPK_F_LL_OUT)) {
+      if constexpr (LL) linear_epilogue_ll<F16>(a, rt, misc, res_s, 0, a.nrows, b0, B, nullptr, accs);
+    } else {
+      linear_epilogue<F16>(a, misc, res_s, 0, a.nrows, b0, B, tid, fromacc);
+    }
   }
 }
 
-__device__ __forceinline__ void linear_consume(WaitCtx &wc, char *smem, Misc *misc,
-                                               const ypk_task &t, int batch, RingPos &pos) {
-  const LinearArgs a = linear_args(t);
+template <bool LL>
+__device__ __forceinline__ void linear_consume_groups(WaitCtx &wc, char *smem, Misc *misc,
+                                                      const Runtime &rt, const ypk_task &t,
+                                                      int batch, long long iter, RingPos &pos) {
+  const LinearArgs a = linear_args(t, LL ? &rt : nullptr, iter);
   const int nbg = (batch + kMaxBatch - 1) / kMaxBatch;
   for (int bg = 0; bg < nbg; ++bg) {
     const int b0 = bg * kMaxBatch;
     const int bc = min(kMaxBatch, batch - b0);
     if (a.flags & YPK_F_F16) {
-      linear_consume_group<true>(wc, smem, misc, a, b0, bc, pos);
+      linear_consume_group<true, LL>(wc, smem, misc, rt, a, b0, bc, pos);
     } else {
-      linear_consume_group<false>(wc, smem, misc, a, b0, bc, pos);
+      linear_consume_group<false, LL>(wc, smem, misc, rt, a, b0, bc, pos);
     }
     if (bg + 1 < nbg) consumer_bar();  // smem of this group is dead before the next one starts
   }

@@ -49,7 +49,9 @@ __device__ __forceinline__ int umma_step_kblocks(const LinearArgs &a) {
 // block; the GEMV path instead streams the weights once per 8 tokens at about 3/4 of the
 // SM's share of HBM (44 bytes / ns).  Take whichever is estimated to finish first.
 __device__ __forceinline__ bool linear_uses_umma(const Runtime &rt, const ypk_task &t, int batch) {
-  if (batch <= kMaxBatch || batch > kUmmaMaxBatch || t.iarg[9] < 0 || rt.umma_policy == 2) return false;
+  if (batch <= kMaxBatch || batch > kUmmaMaxBatch || t.iarg[9] < 0 || rt.umma_policy == 2 ||
+      (t.flags & (YPK_F_LL_IN | YPK_F_LL_RES | YPK_F_LL_OUT)))
+    return false;
   if (rt.umma_policy == 1) return true;
   const long long K = t.iarg[0], nrows = t.iarg[2];
   const long long wbytes = nrows * K * 2;
@@ -72,7 +74,7 @@ __device__ __forceinline__ void tma_load_3d_hint(void *dst, const void *tmap, in
 // ------------------------------------------------------------------ producer
 // Traversal (must match the issuer in linear_consume_umma): super-steps of 4 k-blocks ->
 // row blocks of <= 64 rows; one ring stage each.
-__device__ __noinline__ bool linear_produce_umma(WaitCtx &wc, char *smem, Misc *misc,
+__device__ __forceinline__ bool linear_produce_umma(WaitCtx &wc, char *smem, Misc *misc,
                                                     const Runtime &rt, const ypk_task &t,
                                                     RingPos &pos, unsigned long long policy) {
   const int lane = threadIdx.x & 31;
@@ -203,7 +205,7 @@ __device__ __forceinline__ void cp_async16_zfill(void *dst, const void *src, boo
 
 // ------------------------------------------------------------------ consumer
 template <bool F16>
-__device__ __noinline__ void linear_consume_umma_t(WaitCtx &wc, char *smem, Misc *misc,
+__device__ __forceinline__ void linear_consume_umma_t(WaitCtx &wc, char *smem, Misc *misc,
                                                       const LinearArgs &a, int B, RingPos &pos,
                                                       UmmaState &us) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;

@@ -59,6 +59,8 @@ struct ypk_handle {
   int *d_request_ids = nullptr, *d_page_queue = nullptr, *d_kv_tmp = nullptr, *d_bstate = nullptr;
   // progress
   long long base_iter = 0;
+  // iterations of earlier runs (see Runtime::ll_epoch / ar_epoch)
+  unsigned long long ll_epoch = 0, ar_epoch = 0;
   int pending_tokens = 0;
   bool resume_pending = false;
   bool finished = false;
@@ -167,6 +169,33 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
       if (in.flags & YPK_F_RESIDUAL) {
         need[4] = rows(ldr, mb, ocols0 + ocols); align[4] = 2; required[4] = true;
       }
+      // flagged-word copies: 4 bytes per value ([max_tokens][ld / 2] 8-byte words)
+      const uint32_t ll = in.flags & (YPK_F_LL_IN | YPK_F_LL_RES | YPK_F_LL_OUT | YPK_F_LL_PUSH);
+      if (ll) {
+        if (mb > kMaxBatch)
+          return fail(h, YPK_ERR_UNSUPPORTED,
+                      "task %d: flagged-word hand-off is built for at most %d tokens", ti, kMaxBatch);
+        if ((in.flags & YPK_F_LL_PUSH) && !(in.flags & YPK_F_LL_OUT))
+          return fail(h, YPK_ERR_INVALID, "task %d: LL_PUSH without LL_OUT", ti);
+        if ((in.flags & YPK_F_LL_RES) && !(in.flags & YPK_F_RESIDUAL))
+          return fail(h, YPK_ERR_INVALID, "task %d: LL_RES without RESIDUAL", ti);
+        if (in.flags & YPK_F_LL_IN) {
+          if (ldx % 4) return fail(h, YPK_ERR_INVALID, "task %d: LL_IN needs ldx %% 4 == 0", ti);
+          need[5] = uint64_t(mb) * ldx * 4; align[5] = 16; required[5] = true;
+        }
+        if (in.flags & YPK_F_LL_RES) {
+          if (ldr % 2 || (oc0 + row0) % 2 || nrows % 2)
+            return fail(h, YPK_ERR_INVALID, "task %d: LL_RES needs even rows and columns", ti);
+          need[6] = uint64_t(mb) * ldr * 4; align[6] = 8; required[6] = true;
+        }
+        if (in.flags & YPK_F_LL_OUT) {
+          const int gran = silu ? 2 * kSiluGran : 2;
+          if (ldo % 2 || oc0 % 2 || row0 % gran || nrows % gran)
+            return fail(h, YPK_ERR_INVALID, "task %d: LL_OUT needs rows in granules of %d", ti, gran);
+          const uint64_t copies = (in.flags & YPK_F_LL_PUSH) ? uint64_t(h->cfg.world_size) : 1u;
+          need[7] = copies * mb * ldo * 4; align[7] = 8; required[7] = true;
+        }
+      }
       break;
     }
     case YPK_TASK_EMBED: {
@@ -241,9 +270,17 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
           hidden % 8 || mt < mb || half < 0 || half > 1 || sidx < 0)
         return fail(h, YPK_ERR_INVALID, "task %d: ALLREDUCE shape", ti);
       if (!h->arena) return fail(h, YPK_ERR_STATE, "ALLREDUCE needs ypk_comm_init first");
+      need[2] = rows(ldo, mb, col0 + ncols); align[2] = 16; required[2] = true;
+      if (in.flags & YPK_F_LL_IN) {
+        // partials arrive as flagged words pushed by the producing LINEAR tasks
+        if (!(in.flags & YPK_F_LL_OUT) || mt != h->cfg.max_num_batched_tokens || ldo != hidden)
+          return fail(h, YPK_ERR_INVALID, "task %d: flagged-word ALLREDUCE shape", ti);
+        need[1] = uint64_t(world) * mt * hidden * 4; align[1] = 16; required[1] = true;
+        need[7] = uint64_t(mt) * ldo * 4; align[7] = 8; required[7] = true;
+        break;
+      }
       need[0] = rows(ldi, mb, col0 + ncols); align[0] = 16; required[0] = true;
       need[1] = uint64_t(2) * world * mt * hidden * 2; align[1] = 16; required[1] = true;
-      need[2] = rows(ldo, mb, col0 + ncols); align[2] = 16; required[2] = true;
       need[3] = uint64_t(sidx + 1) * 8; align[3] = 8; required[3] = true;
       break;
     }
@@ -275,7 +312,14 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
     int rc = resolve(h, ti, p, in.ptr[p], need[p], align[p], &out->ptr[p]);
     if (rc) return rc;
   }
-  if (in.type == YPK_TASK_ALLREDUCE) {
+  if ((in.type == YPK_TASK_LINEAR && (in.flags & YPK_F_LL_PUSH)) ||
+      (in.type == YPK_TASK_ALLREDUCE && (in.flags & YPK_F_LL_IN))) {
+    const int p = in.type == YPK_TASK_LINEAR ? 7 : 1;
+    const uint64_t a0 = reinterpret_cast<uint64_t>(h->arena);
+    if (!h->arena || out->ptr[p] < a0 || out->ptr[p] + need[p] > a0 + h->arena_bytes)
+      return fail(h, YPK_ERR_INVALID, "task %d: the pushed flagged-word buffer is not in the symmetric arena",
+                  ti);
+  } else if (in.type == YPK_TASK_ALLREDUCE) {
     for (int p : {1, 3}) {
       const uint64_t a0 = reinterpret_cast<uint64_t>(h->arena);
       if (out->ptr[p] < a0 || out->ptr[p] + need[p] > a0 + h->arena_bytes)
@@ -797,6 +841,8 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
                            cudaMemcpyHostToDevice));
     CUDA_TRY(h, cudaMemset(h->d_events, 0, 8 * size_t(num_events + 1)));
   }
+  h->ar_epoch += static_cast<unsigned long long>(h->base_iter);
+  h->ll_epoch += static_cast<unsigned long long>(h->base_iter) + 1;
   h->base_iter = 0;
   h->resume_pending = false;
   h->pending_tokens = 0;
@@ -807,6 +853,8 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
 int ypk_reset(ypk_handle *h) {
   if (!h) return fail(nullptr, YPK_ERR_INVALID, "null handle");
   if (h->in_flight) return fail(h, YPK_ERR_STATE, "reset while a launch is in flight");
+  h->ar_epoch += static_cast<unsigned long long>(h->base_iter);
+  h->ll_epoch += static_cast<unsigned long long>(h->base_iter) + 1;
   h->base_iter = 0;
   h->resume_pending = false;
   h->pending_tokens = 0;
@@ -886,6 +934,8 @@ int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_
   rt.tmaps = h->d_tmaps;
   rt.use_tmem = h->use_tmem ? 1 : 0;
   rt.umma_policy = h->umma_policy;
+  rt.ll_epoch = h->ll_epoch;
+  rt.ar_epoch = h->ar_epoch;
   for (int p = 0; p < 8; ++p) rt.arena[p] = h->peer_arena[p];
   if (h->arena)
     for (int p = 0; p < c.world_size; ++p)

@@ -124,7 +124,7 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
                         num_workers: int = 128, use_model_eps: bool = True,
                         k_cache: Optional[torch.Tensor] = None,
                         v_cache: Optional[torch.Tensor] = None, compile: bool = True,
-                        dry_run: bool = False, profiler_tensor: Optional[torch.Tensor] = None):
+                        dry_run: bool = False, profiler_tensor: Optional[torch.Tensor] = None, handoff: Optional[str] = None):
     """Build (and compile) the decode megakernel for `weights`.  Returns (ypk, state) where
     state holds the meta tensors, caches and rope tables the kernel works on."""
     dev = tokens.device
@@ -162,6 +162,8 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
         page_size=page_size, eos_token_id=eos_token_id, meta_tensors=meta,
         profiler_tensor=profiler_tensor, trace_name="", spec_decode_config=None,
         use_cutlass_kernel=True)
+    if handoff is not None:
+        ypk.handoff = handoff   # "event" | "ll" | "auto" (see lowering.lower)
     if use_model_eps:
         ypk.rms_norm_eps = shape.rms_norm_eps
 

@@ -16,7 +16,13 @@ B200 design:
     per worker stay level across operators, and the queues are fixed ahead of time;
   * dependencies are whole-operator events (every task of operator i waits for all tasks
     of operator i-1), which is what the reference's chain of consecutive operators
-    degenerates to for these graphs (runtime.cc:446-503).
+    degenerates to for these graphs (runtime.cc:446-503);
+  * with at most 8 tokens in flight, a tensor that a linear operator produces and only
+    linear operators read (the residual stream, the MLP activation) is not handed over
+    through an event at all: it travels as flagged 8-byte words {two values, tag} that the
+    readers poll (`plan_handoff`).  Under tensor parallelism the row-split projections push
+    their partial sums straight into every rank's exchange buffer in that form and the
+    ALLREDUCE tasks only poll, add and pass the sum on.
 
 Nothing here touches the GPU; it is plain Python and is unit-tested on CPU.
 """
@@ -73,6 +79,8 @@ class TaskSpec:
     trig_event: int = -1
     worker: int = 0
     weight_bytes: int = 0
+    flagged_deps: List[int] = field(default_factory=list)   # tag ids this task polls for
+    flagged_out: int = -1                                   # tag id it writes
 
 
 @dataclass
@@ -222,6 +230,90 @@ def fuse(regs: List[RegisteredTask], default_eps: float) -> List[FusedOp]:
     return out
 
 
+# --------------------------------------------------------------------- flagged hand-off
+_OUTPUT_KEYS = {"embed": ("out",), "linear": ("out",), "attention": ("out",), "rmsnorm": ("out",),
+                "silu_mul": ("out",), "argmax_partial": ("val", "idx"), "argmax_reduce": ("out",),
+                "allreduce": ("out",)}
+# operands that are not activations produced inside the iteration
+_STATIC_KEYS = {"w", "norm_w", "table", "ids", "k_cache", "v_cache", "cos", "sin", "buf"}
+
+
+def _op_outputs(op):
+    return [op.t[k] for k in _OUTPUT_KEYS[op.kind] if op.t.get(k) is not None]
+
+
+def _op_inputs(op):
+    """(role, tensor) of the activations an operator reads."""
+    outs = _OUTPUT_KEYS[op.kind]
+    return [(k, t) for k, t in op.t.items()
+            if t is not None and k not in outs and k not in _STATIC_KEYS]
+
+
+def _readers(ops, i, T):
+    """Operators that read what operator i wrote into T, as (index, role), and whether the
+    value is also read across the iteration boundary (by an operator at or before i)."""
+    found, wraps = [], False
+    n = len(ops)
+    for step in range(1, n + 1):
+        j = (i + step) % n
+        if j == i:
+            break
+        for role, t in _op_inputs(ops[j]):
+            if t is T:
+                found.append((j, role))
+                wraps = wraps or j < i
+        if any(t is T for t in _op_outputs(ops[j])):
+            break
+    return found, wraps
+
+
+def plan_handoff(ops, world_size: int):
+    """Which tensors leave their producer as flagged words.  Returns per operator index a
+    dict with optional entries
+        "out":  (key, tag id, push)   producer side (linear, or allreduce passing its sum on)
+        "x" / "res" / "in": (key, tag id)   consumer side
+    where `key` names the flagged-word buffer (one per tensor, shared by all layers)."""
+    plan = {i: {} for i in range(len(ops))}
+    next_id = 0
+    for i, op in enumerate(ops):
+        if op.kind != "linear":
+            continue
+        T = op.t["out"]
+        readers, wraps = _readers(ops, i, T)
+        if not readers or wraps:
+            continue
+        ar = None
+        if (len(readers) == 1 and ops[readers[0][0]].kind == "allreduce" and world_size > 1
+                and readers[0][0] == i + 1):
+            ar = readers[0][0]
+            T2 = ops[ar].t["out"]
+            readers2, wraps2 = _readers(ops, ar, T2)
+            if not readers2 or wraps2 or T.dims[1] % ALLREDUCE_TILE:
+                continue
+            final = readers2
+        else:
+            final = readers
+        if not all(ops[j].kind == "linear" and role in ("x", "res") for j, role in final):
+            continue
+        if any(role == "res" and (ops[j].flags & N.F_SILU_MUL) for j, role in final):
+            continue
+        if ar is None:
+            pid = next_id % 256
+            next_id += 1
+            plan[i]["out"] = (("ll", id(T)), pid, False, T)
+            for j, role in final:
+                plan[j][role] = (("ll", id(T)), pid)
+        else:
+            pid, aid = next_id % 256, (next_id + 1) % 256
+            next_id += 2
+            plan[i]["out"] = (("push", id(T)), pid, True, T)
+            plan[ar]["in"] = (("push", id(T)), pid)
+            plan[ar]["out"] = (("ll", id(T2)), aid, False, T2)
+            for j, role in final:
+                plan[j][role] = (("ll", id(T2)), aid)
+    return plan
+
+
 # ------------------------------------------------------------------------- balancing
 def level_partition(n_units: int, unit_bytes: int, loads: List[float]) -> List[int]:
     """Split n_units equal units over the workers so that load[i] + count[i]*unit_bytes is
@@ -255,16 +347,56 @@ def level_partition(n_units: int, unit_bytes: int, loads: List[float]) -> List[i
 
 
 # --------------------------------------------------------------------------- lowering
+def _all_flagged(plan, ops, oi):
+    """True if every activation operator `oi` reads arrives as flagged words."""
+    ins = _op_inputs(ops[oi])
+    return bool(ins) and all(role in plan[oi] for role, _ in ins)
+
+
+def _link(tasks, first, ev, plan, ops, oi, prev_event, prev_count):
+    """Events of the tasks of operator `oi` (tasks[first:]).  An operator waits for its
+    predecessor's event unless all its activations come as flagged words, and triggers its
+    own unless the next operator does not wait for it."""
+    waits = not _all_flagged(plan, ops, oi)
+    last = oi == len(ops) - 1
+    triggers = last or not _all_flagged(plan, ops, oi + 1)
+    for ts in tasks[first:]:
+        ts.trig_event = ev if triggers else -1
+        ts.dep_event = prev_event if waits else -1
+        ts.dep_count = prev_count if waits else 0
+        ts.flagged_deps = [plan[oi][r][1] for r in ("x", "res", "in") if r in plan[oi]]
+        ts.flagged_out = plan[oi]["out"][1] if "out" in plan[oi] else -1
+
+
 def _is16(t: DTensor):
     return t.dtype in (bfloat16, float16)
 
 
 def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_requests: int,
           max_seq_length: int, page_size: int, world_size: int = 1, rank: int = 0,
-          default_eps: float = 1e-6, new_tensor=None) -> LoweredGraph:
+          default_eps: float = 1e-6, new_tensor=None, handoff: str = "auto") -> LoweredGraph:
     """Fuse, cut into tasks, assign to workers.  `new_tensor(dims, dtype, name)` creates
-    runtime-owned scratch tensors (attention split partials and arrival counters)."""
+    runtime-owned scratch tensors (attention split partials and arrival counters).
+    `handoff`: "event" = every operator waits for its predecessor's event; "ll" = flagged
+    words where possible (at most 8 tokens); "auto" = "ll" when max_tokens <= 8."""
     ops = fuse(regs, default_eps)
+    if handoff == "auto":
+        handoff = "ll" if max_tokens <= 8 else "event"
+    if handoff == "ll" and max_tokens > 8:
+        raise ValueError("the flagged-word hand-off is built for at most 8 tokens in flight")
+    plan = plan_handoff(ops, world_size) if handoff == "ll" else {i: {} for i in range(len(ops))}
+    ll_bufs: Dict[tuple, DTensor] = {}
+
+    def ll_buffer(key, T, push):
+        if key not in ll_bufs:
+            base = (T.name or f"tensor_{T.guid}")
+            if push:
+                ll_bufs[key] = scratch((world_size, max_tokens, T.dims[1]), int32,
+                                       f"flagged_push_{base}", symmetric=True)
+            else:
+                ll_bufs[key] = scratch((max_tokens, T.dims[1]), int32, f"flagged_{base}")
+        return ll_bufs[key]
+
     W = num_workers
     loads = [0.0] * W
     tasks: List[TaskSpec] = []
@@ -325,7 +457,14 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
             if (flags & N.F_RESIDUAL) and world_size > 1 and rank != 0:
                 # partial sums are added across ranks afterwards: the residual goes in once
                 flags &= ~N.F_RESIDUAL
-            gran = 2 * SILU_GRAN if silu else 1
+            ll = plan[oi]
+            if "x" in ll:
+                flags |= N.F_LL_IN
+            if "res" in ll and (flags & N.F_RESIDUAL):
+                flags |= N.F_LL_RES
+            if "out" in ll:
+                flags |= N.F_LL_OUT | (N.F_LL_PUSH if ll["out"][2] else 0)
+            gran = 2 * SILU_GRAN if silu else (2 if (flags & (N.F_LL_OUT | N.F_LL_RES)) else 1)
             if w.kind == "shuffled" and id(w) not in shuffled_done:
                 srcs = w.sources
                 if silu:
@@ -362,6 +501,16 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                         ts.ptr[4] = (res, 0)
                     ts.iarg[:8] = [K, r, take, x.dims[1], w.dims[1], o.dims[1],
                                    res.dims[1] if res is not None else 0, 0]
+                    if flags & N.F_LL_IN:
+                        ts.ptr[5] = (ll_bufs[ll["x"][0]], 0)
+                        ts.iarg[10] = ll["x"][1]
+                    if flags & N.F_LL_RES:
+                        ts.ptr[6] = (ll_bufs[ll["res"][0]], 0)
+                        ts.iarg[11] = ll["res"][1]
+                    if flags & N.F_LL_OUT:
+                        key, pid, push, T = ll["out"]
+                        ts.ptr[7] = (ll_buffer(key, T, push), 0)
+                        ts.iarg[12] = pid
                     ts.farg[0] = float(op.attrs.get("eps", default_eps))
                     ts.worker = wk
                     ts.weight_bytes = take * K * 2
@@ -488,6 +637,24 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
             if hidden % ALLREDUCE_TILE or o.dims[1] != hidden:
                 raise NotImplementedError(f"all-reduce width must be a multiple of {ALLREDUCE_TILE}")
             ntile = hidden // ALLREDUCE_TILE
+            if "in" in plan[oi]:
+                # flagged-word form: the producing LINEAR tasks have pushed their partial sums
+                # into every rank's exchange buffer; these tasks poll, add and pass the sum on
+                key_o, aid, _, T2 = plan[oi]["out"]
+                for k in range(ntile):
+                    ts = TaskSpec(N.TASK_ALLREDUCE, op_id=oi, flags=N.F_LL_IN | N.F_LL_OUT)
+                    ts.ptr[0], ts.ptr[1], ts.ptr[2] = (x, 0), (ll_bufs[plan[oi]["in"][0]], 0), (o, 0)
+                    ts.ptr[7] = (ll_buffer(key_o, T2, False), 0)
+                    ts.iarg[:10] = [k * ALLREDUCE_TILE, ALLREDUCE_TILE, x.dims[1], o.dims[1], hidden,
+                                    max_tokens, 0, 0, world_size, rank]
+                    ts.iarg[10], ts.iarg[12] = plan[oi]["in"][1], aid
+                    ts.worker = (rr + k) % W
+                    tasks.append(ts)
+                rr += ntile
+                count = len(tasks) - first
+                _link(tasks, first, ev, plan, ops, oi, prev_event, prev_count)
+                prev_event, prev_count = ev, count
+                continue
             # The caller's buffer tensor ([world, tokens, hidden]) is not used: the runtime keeps
             # one double-buffered exchange area and one counter per all-reduce tile in the
             # symmetric arena (identical offsets on every rank).
@@ -509,10 +676,7 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
         else:
             raise NotImplementedError(op.kind)
         count = len(tasks) - first
-        for ts in tasks[first:]:
-            ts.trig_event = ev
-            ts.dep_event = prev_event
-            ts.dep_count = prev_count
+        _link(tasks, first, ev, plan, ops, oi, prev_event, prev_count)
         prev_event, prev_count = ev, count
 
     if allreduce_tasks:
@@ -543,9 +707,15 @@ def simulate(g: LoweredGraph, iterations: int = 2):
     ntask = len(g.tasks)
     counters = [0] * g.num_events
     executed = [0] * ntask
+    # flagged words: a reader needs every task that writes the tag to have run this iteration
+    writers: Dict[int, int] = {}
+    for ts in g.tasks:
+        if ts.flagged_out >= 0:
+            writers[ts.flagged_out] = writers.get(ts.flagged_out, 0) + 1
     for it in range(1, iterations + 1):
         heads = [g.queue_off[w] for w in range(len(g.queue_off) - 1)]
         remaining = ntask
+        written: Dict[int, int] = {}
         while remaining:
             progressed = False
             for w in range(len(heads)):
@@ -553,8 +723,12 @@ def simulate(g: LoweredGraph, iterations: int = 2):
                     ts = g.tasks[g.queue[heads[w]]]
                     if ts.dep_event >= 0 and counters[ts.dep_event] < ts.dep_count * it:
                         break
+                    if any(written.get(d, 0) < writers.get(d, 1) for d in ts.flagged_deps):
+                        break
                     if ts.trig_event >= 0:
                         counters[ts.trig_event] += 1
+                    if ts.flagged_out >= 0:
+                        written[ts.flagged_out] = written.get(ts.flagged_out, 0) + 1
                     executed[g.queue[heads[w]]] += 1
                     heads[w] += 1
                     remaining -= 1
@@ -595,6 +769,8 @@ def to_json(g: LoweredGraph) -> str:
             "dependent_count": ts.dep_count,
             "worker": ts.worker,
             "op_id": ts.op_id,
+            "flagged_inputs": list(ts.flagged_deps),
+            "flagged_output": ts.flagged_out,
             "iarg": list(ts.iarg),
             "request_id": ts.iarg[0] if ts.type == N.TASK_ATTENTION else -1,
         })

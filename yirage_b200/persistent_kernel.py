@@ -305,7 +305,8 @@ class PersistentKernel:
                 page_size=self.page_size,
                 world_size=self.world_size, rank=self.mpi_rank,
                 default_eps=self.rms_norm_eps,
-                new_tensor=self._scratch_tensor)
+                new_tensor=self._scratch_tensor,
+                handoff=getattr(self, "handoff", None) or os.environ.get("YPK_HANDOFF", "auto"))
         return self._lowered
 
     def _generate_task_graph(self, num_gpus: int, my_gpu_id: int):
