@@ -24,6 +24,7 @@
 // ldmatrix.trans.  Warps own stages round-robin, so up to five tiles are in flight.
 #pragma once
 #include "device_common.cuh"
+#include <type_traits>
 #include "task_linear.cuh"  // ldmatrix_x4, mma_16816
 
 namespace ypk {
@@ -294,11 +295,180 @@ __device__ __forceinline__ void attn_store_state(float *dst, const AttnAcc &acc,
   }
 }
 
-__device__ __forceinline__ void attention_consume(WaitCtx &wc, char *smem, Misc *misc,
-                                                  const Runtime &rt, const ypk_task &t,
-                                                  RingPos &pos) {
-  const AttnShape s = attn_shape(rt, t);
-  if (!s.active) return;
+// ---- decode form: at most 8 query rows --------------------------------------------------
+// With one new token per request the query tile has G <= 8 rows, and a 16-row MMA tile of
+// queries is half empty.  The products are taken transposed instead: S^T = K Q^T (the 64
+// cached tokens are the M side, the 8 query rows the N side) and O^T = V^T P^T (head dims on
+// the M side), 32 + 32 MMAs per tile instead of 64 + 64, and a third of the accumulator
+// registers.  P^T leaves the first product in the accumulator layout and enters the second
+// as a B operand, which is that layout transposed: movmatrix does it in registers.
+//
+// A lane holds, for query rows q0 = (lane % 4) * 2 and q0 + 1: their running max and its
+// share of their running sum, and for each 16-dim block of the head the outputs
+// {[d][q0], [d][q0 + 1], [d + 8][q0], [d + 8][q0 + 1]} with d = lane / 4.
+struct AttnAccT {
+  float o[kHeadDim / 16][4];
+  float m[2];
+  float l[2];
+};
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+  return r;
+}
+
+template <bool SWZ>
+__device__ __forceinline__ void attn_tile_mma_t(const char *qsm, const char *ksm, char *vsm,
+                                                int ntok, bool causal, int G, int lane,
+                                                AttnAccT &acc) {
+  const float qscale = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
+  const int nk16 = (ntok + 15) >> 4;       // 16-token blocks with at least one valid token
+  if (ntok < nk16 * 16) {
+    // P is zero for the padding tokens of the last block, but 0 * (stale Inf/NaN) would
+    // poison the output: clear those V rows (see attn_tile_mma).
+    for (int i = lane; i < (nk16 * 16 - ntok) * (kHeadDim / 8); i += 32) {
+      const int row = ntok + i / (kHeadDim / 8), c = i % (kHeadDim / 8);
+      char *dst = SWZ ? vsm + (c >> 3) * kKvBoxBytes + row * 128 + (c & 7) * 16
+                      : vsm + row * kKPitch + c * 16;
+      *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+  }
+  const int sw = lane & 7;
+  // Q^T as the B operand: the 8 query rows, 32 head dims per ldmatrix.x4
+  uint32_t qf[kHeadDim / 32][4];
+#pragma unroll
+  for (int p = 0; p < kHeadDim / 32; ++p)
+    ldmatrix_x4(qf[p], qsm + sw * kKPitch + (p * 32 + (lane >> 3) * 8) * 2);
+
+  float st[kKvTile / 16][4];
+#pragma unroll
+  for (int mt = 0; mt < kKvTile / 16; ++mt) st[mt][0] = st[mt][1] = st[mt][2] = st[mt][3] = 0.f;
+#pragma unroll
+  for (int mt = 0; mt < kKvTile / 16; ++mt) {
+    if (mt < nk16) {
+      const int row = mt * 16 + ((lane >> 3) & 1) * 8 + sw;   // token of this lane's ldmatrix row
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {                   // 64 head dims at a time
+        uint32_t kf[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int cg = (half * 4 + j) * 2 + (lane >> 4);     // 16-byte chunk of the 256-byte row
+          if constexpr (SWZ) {
+            ldmatrix_x4(kf[j], ksm + (cg >> 3) * kKvBoxBytes + row * 128 + (((cg & 7) ^ sw) << 4));
+          } else {
+            ldmatrix_x4(kf[j], ksm + row * kKPitch + cg * 16);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int ks = half * 4 + j;                         // 16-dim step
+          mma_16816<false>(st[mt], kf[j], qf[ks >> 1][(ks & 1) * 2], qf[ks >> 1][(ks & 1) * 2 + 1]);
+        }
+      }
+    }
+  }
+  // scale, mask, column max (a column = one query row)
+  const int q0 = (lane & 3) * 2;
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int mt = 0; mt < kKvTile / 16; ++mt) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int tok = mt * 16 + (lane >> 2) + ((e & 2) ? 8 : 0);
+      const int tq = (q0 + (e & 1)) / G;
+      const bool vis = mt < nk16 && tok < ntok && (!causal || tok <= tq);
+      st[mt][e] = vis ? st[mt][e] * qscale : -INFINITY;
+      mx[e & 1] = fmaxf(mx[e & 1], st[mt][e]);
+    }
+  }
+  float corr[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 4));
+    mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 8));
+    mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 16));
+    const float m_new = fmaxf(acc.m[j], mx[j]);
+    const float base = m_new == -INFINITY ? 0.f : m_new;   // nothing seen yet: exponent base 0
+    corr[j] = exp2f(acc.m[j] - base);
+    acc.m[j] = m_new;
+    mx[j] = base;
+    acc.l[j] *= corr[j];
+  }
+  // p = exp2(s - m), rounded to bf16, transposed into B fragments of the second product
+  uint32_t pb[kKvTile / 16][2];
+#pragma unroll
+  for (int mt = 0; mt < kKvTile / 16; ++mt) {
+    float pv[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) pv[e] = exp2f(st[mt][e] - mx[e & 1]);
+    acc.l[0] += pv[0] + pv[2];
+    acc.l[1] += pv[1] + pv[3];
+    pb[mt][0] = movmatrix_trans(pack_bf16(pv[0], pv[1]));   // tokens mt*16 + 0..7
+    pb[mt][1] = movmatrix_trans(pack_bf16(pv[2], pv[3]));   // tokens mt*16 + 8..15
+  }
+#pragma unroll
+  for (int md = 0; md < kHeadDim / 16; ++md) {
+    acc.o[md][0] *= corr[0];
+    acc.o[md][1] *= corr[1];
+    acc.o[md][2] *= corr[0];
+    acc.o[md][3] *= corr[1];
+  }
+  // O^T += V^T P^T: V rows are the k dimension of an A operand, so they come transposed
+#pragma unroll
+  for (int kk = 0; kk < kKvTile / 16; ++kk) {
+    if (kk < nk16) {
+      const int row = kk * 16 + sw + ((lane >> 4) & 1) * 8;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t vf[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int cg = (half * 4 + j) * 2 + ((lane >> 3) & 1);
+          if constexpr (SWZ) {
+            ldmatrix_x4_trans(vf[j], vsm + (cg >> 3) * kKvBoxBytes + row * 128 + (((cg & 7) ^ sw) << 4));
+          } else {
+            ldmatrix_x4_trans(vf[j], vsm + row * kKPitch + cg * 16);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_16816<false>(acc.o[half * 4 + j], vf[j], pb[kk][0], pb[kk][1]);
+      }
+    }
+  }
+}
+
+// A warp's transposed state -> shared memory [8 rows][kAttnRowFloats].
+__device__ __forceinline__ void attn_store_state_t(float *dst, const AttnAccT &acc, int lane) {
+  const int q0 = (lane & 3) * 2, d0 = lane >> 2;
+  float l0 = acc.l[0], l1 = acc.l[1];
+#pragma unroll
+  for (int o = 4; o <= 16; o <<= 1) {
+    l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+  }
+#pragma unroll
+  for (int md = 0; md < kHeadDim / 16; ++md) {
+    dst[q0 * kAttnRowFloats + md * 16 + d0] = acc.o[md][0];
+    dst[(q0 + 1) * kAttnRowFloats + md * 16 + d0] = acc.o[md][1];
+    dst[q0 * kAttnRowFloats + md * 16 + d0 + 8] = acc.o[md][2];
+    dst[(q0 + 1) * kAttnRowFloats + md * 16 + d0 + 8] = acc.o[md][3];
+  }
+  if (lane < 4) {
+    dst[q0 * kAttnRowFloats + kHeadDim] = acc.m[0];
+    dst[q0 * kAttnRowFloats + kHeadDim + 1] = l0;
+    dst[(q0 + 1) * kAttnRowFloats + kHeadDim] = acc.m[1];
+    dst[(q0 + 1) * kAttnRowFloats + kHeadDim + 1] = l1;
+  }
+}
+
+// DECODE: the request has at most 8 query rows this iteration (transposed products).
+template <bool DECODE>
+__device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, Misc *misc,
+                                                       const Runtime &rt, const ypk_task &t,
+                                                       const AttnShape &s, RingPos &pos) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int r = t.iarg[0], h = t.iarg[1], split = t.iarg[2], nsplit = t.iarg[3];
   const int G = t.iarg[4], hkv = t.iarg[5], ld_qkv = t.iarg[6], ld_out = t.iarg[7];
@@ -376,9 +546,10 @@ __device__ __forceinline__ void attention_consume(WaitCtx &wc, char *smem, Misc 
   consumer_bar();
   if (tid == 0 && misc->prof_rec) misc->prof_rec[4] = globaltimer();
 
-  AttnAcc acc;
+  using Acc = typename std::conditional<DECODE, AttnAccT, AttnAcc>::type;
+  Acc acc;
 #pragma unroll
-  for (int nb = 0; nb < kHeadDim / 8; ++nb) acc.o[nb][0] = acc.o[nb][1] = acc.o[nb][2] = acc.o[nb][3] = 0.f;
+  for (int i = 0; i < int(sizeof(acc.o) / sizeof(acc.o[0])); ++i) acc.o[i][0] = acc.o[i][1] = acc.o[i][2] = acc.o[i][3] = 0.f;
   acc.m[0] = acc.m[1] = -INFINITY;
   acc.l[0] = acc.l[1] = 0.f;
 
@@ -389,7 +560,11 @@ __device__ __forceinline__ void attention_consume(WaitCtx &wc, char *smem, Misc 
     const bool got = wait_mbar(wc, &misc->full_bar[pos.slot], pos.phase);
     if (got && (tile - s.tile0) % nslots == slot) {
       char *stage = smem + kOffRing + pos.slot * kStageBytes;
-      attn_tile_mma<true>(qsm, stage, stage + kVOffset, ntok, false, G, mt * 16, lane, acc);
+      if constexpr (DECODE) {
+        attn_tile_mma_t<true>(qsm, stage, stage + kVOffset, ntok, false, G, lane, acc);
+      } else {
+        attn_tile_mma<true>(qsm, stage, stage + kVOffset, ntok, false, G, mt * 16, lane, acc);
+      }
     }
     __syncwarp();
     if (lane == 0 && got) mbar_arrive(&misc->empty_bar[pos.slot]);
@@ -397,8 +572,13 @@ __device__ __forceinline__ void attention_consume(WaitCtx &wc, char *smem, Misc 
   }
   // the new tokens: causal among themselves; the last slot of the group is the one with
   // the fewest cached tiles
-  if (s.handles_new && slot == nslots - 1)
-    attn_tile_mma<false>(qsm, knew, vnew, T, true, G, mt * 16, lane, acc);
+  if (s.handles_new && slot == nslots - 1) {
+    if constexpr (DECODE) {
+      attn_tile_mma_t<false>(qsm, knew, vnew, T, true, G, lane, acc);
+    } else {
+      attn_tile_mma<false>(qsm, knew, vnew, T, true, G, mt * 16, lane, acc);
+    }
+  }
   consumer_bar();  // q / knew / vnew are dead from here on; the area becomes the merge buffer
   if (tid == 0 && misc->prof_rec) misc->prof_rec[5] = globaltimer();
 
@@ -436,9 +616,9 @@ __device__ __forceinline__ void attention_consume(WaitCtx &wc, char *smem, Misc 
       }
     }
   };
-  if (rows <= 8) {
+  if constexpr (DECODE) {
     // decode: eight 8-row states fit the buffer at once
-    attn_store_state(mrg + warp * kStateFloats, acc, lane, false);
+    attn_store_state_t(mrg + warp * kStateFloats, acc, lane);
     consumer_bar();
     finalize(0, kConsumerWarps);
   } else if (nm == 1) {
@@ -517,6 +697,33 @@ __device__ __forceinline__ void attention_consume(WaitCtx &wc, char *smem, Misc 
     }
     if (tid == 0) counters[r * hkv + h] = 0u;
   }
+}
+
+// The two forms are separate out-of-line functions: the 16-row form needs twice the
+// accumulator registers and must not weigh on the decode form's allocation.
+struct AttnRet {
+  RingPos pos;
+  bool failed;
+};
+template <bool DECODE>
+__device__ __noinline__ AttnRet attention_consume_out(const Runtime *rt, Misc *misc, char *smem,
+                                                      int worker, int task, bool failed,
+                                                      AttnShape s, RingPos pos) {
+  WaitCtx wc{rt, misc, worker, task, failed};
+  attention_consume_impl<DECODE>(wc, smem, misc, *rt, misc->ctask, s, pos);
+  return AttnRet{pos, wc.failed};
+}
+
+__device__ __forceinline__ void attention_consume(WaitCtx &wc, char *smem, Misc *misc,
+                                                  const Runtime &rt, const ypk_task &t,
+                                                  RingPos &pos) {
+  const AttnShape s = attn_shape(rt, t);
+  if (!s.active) return;
+  const AttnRet r = s.T * t.iarg[4] <= 8
+      ? attention_consume_out<true>(&rt, misc, smem, wc.worker, wc.task, wc.failed, s, pos)
+      : attention_consume_out<false>(&rt, misc, smem, wc.worker, wc.task, wc.failed, s, pos);
+  pos = r.pos;
+  wc.failed = r.failed;
 }
 
 }  // namespace ypk
