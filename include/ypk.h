@@ -81,9 +81,11 @@ enum ypk_task_type {
  * values travels as [max_tokens][ld / 2] 8-byte words {two values, 32-bit tag}; the tag
  * names the iteration and the producing operator, a reader polls until it sees it. */
 #define YPK_F_LL_IN 0x100u     /* LINEAR: x comes as flagged words (ptr[5]);
-                                  ALLREDUCE: the ranks' partials do (buf)   */
+                                  ALLREDUCE: the ranks' partials do (buf);
+                                  ATTENTION: the packed q/k/v do (ptr[0])    */
 #define YPK_F_LL_RES 0x200u    /* LINEAR: residual as flagged words (ptr[6]) */
-#define YPK_F_LL_OUT 0x400u    /* result also leaves as flagged words (ptr[7]) */
+#define YPK_F_LL_OUT 0x400u    /* result also leaves as flagged words (ptr[7]);
+                                  ATTENTION: only as flagged words (ptr[3])  */
 #define YPK_F_LL_PUSH 0x800u   /* LINEAR: partial sum: flagged words only, into slot `rank`
                                   of ptr[7] = [world][max_tokens][ld / 2] on every rank */
 
@@ -110,7 +112,9 @@ enum ypk_task_type {
  * ATTENTION: ptr = {qkv, k_cache, v_cache, out, cos, sin, scratch, counters}
  *          iarg = {request, kv_head, split, nsplit, q_per_kv, num_kv_heads,
  *                  ld_qkv, ld_out, max_rows}; iarg[9], iarg[10] are filled in by
- *                  ypk_load_graph (TMA tensor maps of the two caches)
+ *                  ypk_load_graph (TMA tensor maps of the two caches); with YPK_F_LL_IN
+ *                  qkv is the flagged-word form and iarg[11] its producer's tag id, with
+ *                  YPK_F_LL_OUT out is written as flagged words under tag id iarg[12]
  * ARGMAX_PARTIAL: ptr = {logits, part_val, part_idx}; iarg = {col0, ncols,
  *                  ldlogits, part, nparts}
  * ARGMAX_REDUCE: ptr = {part_val, part_idx, out(int64)}; iarg = {nparts}

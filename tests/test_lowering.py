@@ -71,18 +71,34 @@ def test_flagged_word_handoff_plan():
     for ts in g.tasks:
         by_op.setdefault(ts.op_id, []).append(ts)
     LL = N.F_LL_IN | N.F_LL_RES | N.F_LL_OUT | N.F_LL_PUSH
-    # layer 0: qkv (x from the embedding: event), o_proj, gate/up, down; layer 1: qkv ...
+    # layer 0: qkv (x from the embedding: event), attention, o_proj (residual from the
+    # embedding: event), gate/up, down; layer 1: everything flagged
     qkv0, att0, o0, gu0, dn0, qkv1, att1, o1 = (by_op[i][0] for i in range(1, 9))
-    assert qkv0.flags & LL == 0 and qkv0.dep_event == 0 and qkv0.trig_event == 1
-    assert att0.dep_event == 1 and att0.trig_event == 2
-    assert o0.flags & LL == N.F_LL_OUT and o0.dep_event == 2 and o0.trig_event == -1
+    assert qkv0.flags & LL == N.F_LL_OUT and qkv0.dep_event == 0 and qkv0.trig_event == -1
+    assert att0.flags & LL == N.F_LL_IN | N.F_LL_OUT and att0.dep_event == -1 and att0.trig_event == 2
+    assert o0.flags & LL == N.F_LL_IN | N.F_LL_OUT and o0.dep_event == 2 and o0.trig_event == -1
     assert gu0.flags & LL == N.F_LL_IN | N.F_LL_OUT and gu0.dep_event == -1 and gu0.trig_event == -1
     assert dn0.flags & LL == N.F_LL_IN | N.F_LL_RES | N.F_LL_OUT and dn0.dep_event == -1
-    assert qkv1.flags & LL == N.F_LL_IN and qkv1.dep_event == -1 and qkv1.trig_event == 6
-    assert o1.flags & LL == N.F_LL_RES | N.F_LL_OUT and o1.dep_event == 7
+    assert qkv1.flags & LL == N.F_LL_IN | N.F_LL_OUT and qkv1.dep_event == -1 and qkv1.trig_event == -1
+    assert att1.dep_event == -1 and att1.trig_event == -1
+    assert o1.flags & LL == N.F_LL_IN | N.F_LL_RES | N.F_LL_OUT and o1.dep_event == -1
     # tags: a reader polls for the tag its producer writes
+    assert att0.flagged_deps == [qkv0.flagged_out] and o0.flagged_deps == [att0.flagged_out]
     assert gu0.flagged_deps == [o0.flagged_out] and dn0.flagged_deps == [gu0.flagged_out, o0.flagged_out]
-    assert qkv1.flagged_deps == [dn0.flagged_out] and o1.flagged_deps == [dn0.flagged_out]
+    assert qkv1.flagged_deps == [dn0.flagged_out]
+    assert o1.flagged_deps == [att1.flagged_out, dn0.flagged_out]
+    # a tensor wider than MAX_FLAGGED_COLS keeps its event
+    wide = lowering.MAX_FLAGGED_COLS
+    lowering.MAX_FLAGGED_COLS = 512
+    try:
+        _, ypk2 = small_graph(handoff="ll")
+        g2 = ypk2.lower(148)
+        dn = [ts for ts in g2.tasks if ts.op_id == 5][0]
+        gu = [ts for ts in g2.tasks if ts.op_id == 4][0]
+        assert not dn.flags & N.F_LL_IN and dn.dep_event == 4 and gu.trig_event == 4
+        assert set(lowering.simulate(g2, iterations=2)) == {2}
+    finally:
+        lowering.MAX_FLAGGED_COLS = wide
     # flagged results come in pairs of columns: rows of every such slab are even
     for ts in g.tasks:
         if ts.type == N.TASK_LINEAR and ts.flags & (N.F_LL_OUT | N.F_LL_RES):

@@ -87,9 +87,9 @@ __device__ __noinline__ TaskRetU run_linear_umma(const Runtime *rt, Misc *misc, 
   return TaskRetU{pos, us, wc.failed};
 }
 __device__ __noinline__ TaskRet run_attention(const Runtime *rt, Misc *misc, char *smem, int worker,
-                                              int task, bool failed, RingPos pos) {
+                                              int task, bool failed, long long iter, RingPos pos) {
   WaitCtx wc{rt, misc, worker, task, failed};
-  attention_consume(wc, smem, misc, *rt, misc->ctask, pos);
+  attention_consume(wc, smem, misc, *rt, misc->ctask, iter, pos);
   return TaskRet{pos, wc.failed};
 }
 __device__ __noinline__ bool run_small(const Runtime *rt, Misc *misc, int worker, int task,
@@ -282,7 +282,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_
               wc.failed = r.failed;
             }
           } else if (t.type == YPK_TASK_ATTENTION) {
-            const TaskRet r = run_attention(&rt, misc, smem, worker, ti, wc.failed, pos);
+            const TaskRet r = run_attention(&rt, misc, smem, worker, ti, wc.failed, iter, pos);
             pos = r.pos;
             wc.failed = r.failed;
           } else {

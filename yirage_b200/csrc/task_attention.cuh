@@ -25,6 +25,7 @@
 #pragma once
 #include "device_common.cuh"
 #include <type_traits>
+#include "ll_handoff.cuh"
 #include "task_linear.cuh"  // ldmatrix_x4, mma_16816
 
 namespace ypk {
@@ -468,7 +469,8 @@ __device__ __forceinline__ void attn_store_state_t(float *dst, const AttnAccT &a
 template <bool DECODE>
 __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, Misc *misc,
                                                        const Runtime &rt, const ypk_task &t,
-                                                       const AttnShape &s, RingPos &pos) {
+                                                       const AttnShape &s, long long iter,
+                                                       RingPos &pos) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int r = t.iarg[0], h = t.iarg[1], split = t.iarg[2], nsplit = t.iarg[3];
   const int G = t.iarg[4], hkv = t.iarg[5], ld_qkv = t.iarg[6], ld_out = t.iarg[7];
@@ -482,6 +484,13 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
   float *scratch = reinterpret_cast<float *>(t.ptr[6]);
   unsigned int *counters = reinterpret_cast<unsigned int *>(t.ptr[7]);
   const bool rope = (t.flags & YPK_F_ROPE) != 0;
+  // flagged-word hand-off: with YPK_F_LL_IN ptr[0] holds the packed q/k/v as {two values,
+  // tag} words ([max_tokens][ld_qkv / 2]), with YPK_F_LL_OUT ptr[3] takes the result that way
+  const bool ll_in = (t.flags & YPK_F_LL_IN) != 0, ll_out = (t.flags & YPK_F_LL_OUT) != 0;
+  const uint32_t tag_in = ll_tag(rt, iter, t.iarg[11]), tag_out = ll_tag(rt, iter, t.iarg[12]);
+  const unsigned long long *qkv_ll = reinterpret_cast<const unsigned long long *>(t.ptr[0]);
+  unsigned long long *out_ll = reinterpret_cast<unsigned long long *>(t.ptr[3]);
+  LLPoll poll;
   const int T = s.T, rows = T * G;
   const int nm = (rows + 15) >> 4;            // 16-row query tiles: 1 or 2
   const int nslots = kConsumerWarps / nm;     // warps that share the tiles of one query tile
@@ -509,11 +518,38 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
     const int tk = idx / (heads_to_stage * 16);
     const int d0 = c * 8;
     const int pos_t = s.seq_len - T + tk;
-    const uint16_t *src = qkv + size_t(s.qo0 + tk) * ld_qkv + size_t(h) * (G + 2) * kHeadDim +
-                          hh * kHeadDim;
-    uint4 pk = __ldcg(reinterpret_cast<const uint4 *>(src + d0));
-    if (rope && hh <= G) {  // q heads and k, not v
-      const uint4 ov = __ldcg(reinterpret_cast<const uint4 *>(src + (d0 ^ 64)));
+    const size_t col = size_t(h) * (G + 2) * kHeadDim + hh * kHeadDim;
+    const uint16_t *src = qkv + size_t(s.qo0 + tk) * ld_qkv + col;
+    const bool rot = rope && hh <= G;   // q heads and k, not v
+    // the page of the new token (k and v only): asked for ahead of the values it goes with
+    int page = 0;
+    if (hh >= G) page = __ldcg(rt.kv_indices + s.kv0 + pos_t / rt.page_size);
+    uint4 pk, ov = make_uint4(0u, 0u, 0u, 0u);
+    if (ll_in) {
+      // 8 dims = four words; the rotate-half partner's four with them, polled together
+      const unsigned long long *wsrc = qkv_ll + size_t(s.qo0 + tk) * size_t(ld_qkv >> 1) + (col >> 1);
+      unsigned long long w[8];
+      for (;;) {
+        ll_load2(wsrc + (d0 >> 1), w[0], w[1]);
+        ll_load2(wsrc + (d0 >> 1) + 2, w[2], w[3]);
+        bool ok = true;
+        if (rot) {
+          ll_load2(wsrc + ((d0 ^ 64) >> 1), w[4], w[5]);
+          ll_load2(wsrc + ((d0 ^ 64) >> 1) + 2, w[6], w[7]);
+#pragma unroll
+          for (int i = 4; i < 8; ++i) ok = ok && ll_ok(w[i], tag_in);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ok = ok && ll_ok(w[i], tag_in);
+        if (ok || !poll.again(wc)) break;
+      }
+      pk = make_uint4(uint32_t(w[0]), uint32_t(w[1]), uint32_t(w[2]), uint32_t(w[3]));
+      if (rot) ov = make_uint4(uint32_t(w[4]), uint32_t(w[5]), uint32_t(w[6]), uint32_t(w[7]));
+    } else {
+      pk = __ldcg(reinterpret_cast<const uint4 *>(src + d0));
+      if (rot) ov = __ldcg(reinterpret_cast<const uint4 *>(src + (d0 ^ 64)));
+    }
+    if (rot) {
       const uint4 cv = __ldcg(reinterpret_cast<const uint4 *>(cosp + size_t(pos_t) * kHeadDim + d0));
       const uint4 sv = __ldcg(reinterpret_cast<const uint4 *>(sinp + size_t(pos_t) * kHeadDim + d0));
       const uint32_t pv[4] = {pk.x, pk.y, pk.z, pk.w}, po[4] = {ov.x, ov.y, ov.z, ov.w},
@@ -531,7 +567,6 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
     if (hh < G) {
       *reinterpret_cast<uint4 *>(qsm + (tk * G + hh) * kKPitch + d0 * 2) = pk;
     } else {
-      const int page = __ldcg(rt.kv_indices + s.kv0 + pos_t / rt.page_size);
       const size_t off =
           ((size_t(page) * rt.page_size + (pos_t % rt.page_size)) * hkv + h) * kHeadDim + d0;
       if (hh == G) {
@@ -543,6 +578,8 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
       }
     }
   }
+  // a poll that gave up is known to one thread; the mbarrier waits need a warp-uniform state
+  if (ll_in) wc.failed = __any_sync(0xffffffffu, poll.failed || wc.failed);
   consumer_bar();
   if (tid == 0 && misc->prof_rec) misc->prof_rec[4] = globaltimer();
 
@@ -588,27 +625,39 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
   // merge states are [16 rows][132] per warp, or [8 rows][132] when only 8 rows are live
   const int kStateFloats = (rows <= 8 ? 8 : 16) * kAttnRowFloats;
   // Merge the warps of a query tile, four states at a time, then finish rows [mt*16, ..).
+  // Two neighbouring head dims of a finished query row: plain bf16, or one flagged word.
+  auto emit = [&](int row, int d, float v0, float v1) {
+    const int tk = row / G, g = row - tk * G;
+    const size_t col = size_t(h * G + g) * kHeadDim + d;
+    const uint32_t packed = pack_bf16(v0, v1);
+    if (ll_out) {
+      ll_store(out_ll + size_t(s.qo0 + tk) * size_t(ld_out >> 1) + (col >> 1), ll_word(packed, tag_out));
+    } else {
+      *reinterpret_cast<uint32_t *>(out + size_t(s.qo0 + tk) * ld_out + col) = packed;
+    }
+  };
   auto finalize = [&](int mtile, int nstates) {
     const int row_lo = mtile * 16, nrow = min(16, rows - row_lo);
-    for (int idx = tid; idx < nrow * kHeadDim; idx += kConsumerThreads) {
-      const int d = idx & (kHeadDim - 1), rr = idx >> 7;
+    for (int idx = tid; idx < nrow * (kHeadDim / 2); idx += kConsumerThreads) {
+      const int d = (idx & (kHeadDim / 2 - 1)) * 2, rr = idx >> 6;
       float m = -INFINITY;
       for (int w = 0; w < nstates; ++w)
         m = fmaxf(m, mrg[w * kStateFloats + rr * kAttnRowFloats + kHeadDim]);
-      float l = 0.f, o = 0.f;
+      float l = 0.f, o0 = 0.f, o1 = 0.f;
       for (int w = 0; w < nstates; ++w) {
         const float *pr = mrg + w * kStateFloats + rr * kAttnRowFloats;
         const float c = pr[kHeadDim] == -INFINITY ? 0.f : exp2f(pr[kHeadDim] - m);
+        const float2 po = *reinterpret_cast<const float2 *>(pr + d);
         l += pr[kHeadDim + 1] * c;
-        o += pr[d] * c;
+        o0 += po.x * c;
+        o1 += po.y * c;
       }
-      const int row = row_lo + rr, tk = row / G, g = row - tk * G;
+      const int row = row_lo + rr;
       if (single) {
-        out[size_t(s.qo0 + tk) * ld_out + size_t(h * G + g) * kHeadDim + d] =
-            __bfloat16_as_ushort(__float2bfloat16_rn(o / l));
+        emit(row, d, o0 / l, o1 / l);
       } else {
         float *dst = my_scr + row * kAttnRowFloats;
-        dst[d] = o;
+        *reinterpret_cast<float2 *>(dst + d) = make_float2(o0, o1);
         if (d == 0) {
           dst[kHeadDim] = m;
           dst[kHeadDim + 1] = l;
@@ -676,24 +725,37 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
   consumer_bar();
   if (tid == 0 && misc->prof_rec) misc->prof_rec[6] = globaltimer();
   if (misc->flag) {
+    // Last arriver: fold the splits' partial rows together in split order.  One running
+    // (max, sum, outputs) per thread, so the loads of all splits are independent of each
+    // other and go out together.
     const float *base = scratch + (size_t(r) * hkv + h) * nsplit * size_t(max_rows) * kAttnRowFloats;
-    for (int idx = tid; idx < rows * kHeadDim; idx += kConsumerThreads) {
-      const int d = idx & (kHeadDim - 1);
-      const int row = idx >> 7;
-      const int tk = row / G, g = row - tk * G;
-      float m = -INFINITY;
-      for (int sp = 0; sp < s.nact; ++sp)
-        m = fmaxf(m, __ldcg(base + (size_t(sp) * max_rows + row) * kAttnRowFloats + kHeadDim));
-      float l = 0.f, o = 0.f;
-      for (int sp = 0; sp < s.nact; ++sp) {
-        const float *pr = base + (size_t(sp) * max_rows + row) * kAttnRowFloats;
-        const float ms = __ldcg(pr + kHeadDim);
-        const float c = ms == -INFINITY ? 0.f : exp2f(ms - m);
-        l += __ldcg(pr + kHeadDim + 1) * c;
-        o += __ldcg(pr + d) * c;
+    for (int idx = tid; idx < rows * (kHeadDim / 2); idx += kConsumerThreads) {
+      const int d = (idx & (kHeadDim / 2 - 1)) * 2;
+      const int row = idx >> 6;
+      float m = -INFINITY, l = 0.f, o0 = 0.f, o1 = 0.f;
+      for (int sp0 = 0; sp0 < s.nact; sp0 += 4) {
+        float ms[4], ls[4];
+        float2 os[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float *pr = base + (size_t(min(sp0 + j, s.nact - 1)) * max_rows + row) * kAttnRowFloats;
+          ms[j] = __ldcg(pr + kHeadDim);
+          ls[j] = __ldcg(pr + kHeadDim + 1);
+          os[j] = __ldcg(reinterpret_cast<const float2 *>(pr + d));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (sp0 + j < s.nact && ms[j] != -INFINITY) {
+            const float m_new = fmaxf(m, ms[j]);
+            const float c_old = exp2f(m - m_new), c_new = exp2f(ms[j] - m_new);   // exp2f(-inf) = 0
+            l = l * c_old + ls[j] * c_new;
+            o0 = o0 * c_old + os[j].x * c_new;
+            o1 = o1 * c_old + os[j].y * c_new;
+            m = m_new;
+          }
+        }
       }
-      out[size_t(s.qo0 + tk) * ld_out + size_t(h * G + g) * kHeadDim + d] =
-          __bfloat16_as_ushort(__float2bfloat16_rn(o / l));
+      emit(row, d, o0 / l, o1 / l);
     }
     if (tid == 0) counters[r * hkv + h] = 0u;
   }
@@ -708,20 +770,20 @@ struct AttnRet {
 template <bool DECODE>
 __device__ __noinline__ AttnRet attention_consume_out(const Runtime *rt, Misc *misc, char *smem,
                                                       int worker, int task, bool failed,
-                                                      AttnShape s, RingPos pos) {
+                                                      AttnShape s, long long iter, RingPos pos) {
   WaitCtx wc{rt, misc, worker, task, failed};
-  attention_consume_impl<DECODE>(wc, smem, misc, *rt, misc->ctask, s, pos);
+  attention_consume_impl<DECODE>(wc, smem, misc, *rt, misc->ctask, s, iter, pos);
   return AttnRet{pos, wc.failed};
 }
 
 __device__ __forceinline__ void attention_consume(WaitCtx &wc, char *smem, Misc *misc,
                                                   const Runtime &rt, const ypk_task &t,
-                                                  RingPos &pos) {
+                                                  long long iter, RingPos &pos) {
   const AttnShape s = attn_shape(rt, t);
   if (!s.active) return;
   const AttnRet r = s.T * t.iarg[4] <= 8
-      ? attention_consume_out<true>(&rt, misc, smem, wc.worker, wc.task, wc.failed, s, pos)
-      : attention_consume_out<false>(&rt, misc, smem, wc.worker, wc.task, wc.failed, s, pos);
+      ? attention_consume_out<true>(&rt, misc, smem, wc.worker, wc.task, wc.failed, s, iter, pos)
+      : attention_consume_out<false>(&rt, misc, smem, wc.worker, wc.task, wc.failed, s, iter, pos);
   pos = r.pos;
   wc.failed = r.failed;
 }

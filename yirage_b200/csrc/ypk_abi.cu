@@ -230,7 +230,12 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
       need[0] = rows(ldq, mb, hkv * (G + 2) * kHeadDim); align[0] = 16; required[0] = true;
       need[1] = cache_bytes; align[1] = 16; required[1] = true;
       need[2] = cache_bytes; align[2] = 16; required[2] = true;
-      need[3] = rows(ldo, mb, hkv * G * kHeadDim); align[3] = 2; required[3] = true;
+      need[3] = rows(ldo, mb, hkv * G * kHeadDim); align[3] = 4; required[3] = true;
+      // flagged-word forms of the packed q/k/v and of the result: 4 bytes per value
+      if (in.flags & YPK_F_LL_IN) { need[0] = uint64_t(mb) * ldq * 4; align[0] = 16; }
+      if (in.flags & YPK_F_LL_OUT) { need[3] = uint64_t(mb) * ldo * 4; align[3] = 8; }
+      if ((in.flags & (YPK_F_LL_IN | YPK_F_LL_OUT)) && (mb > kMaxBatch || ldq % 4 || ldo % 2))
+        return fail(h, YPK_ERR_UNSUPPORTED, "task %d: flagged-word ATTENTION shape", ti);
       if (in.flags & YPK_F_ROPE) {
         need[4] = need[5] = uint64_t(kHeadDim) * 2; align[4] = align[5] = 2;
         required[4] = required[5] = true;

@@ -43,6 +43,10 @@ ATTN_ROW_FLOATS = HEAD_DIM + 4   # kAttnRowFloats in task_attention.cuh
 MAX_SPLITS = 16
 ALLREDUCE_TILE = 256          # columns per ALLREDUCE task
 SILU_GRAN = 2                # kSiluGran: fused gate/up rows come as 2 gate + 2 up
+# Widest tensor handed over as flagged words: a reader polls 2x the bytes, four 16-byte loads
+# in flight per thread, so a 14336-wide MLP activation would take four trips to L2 against
+# the one of a plain copy.
+MAX_FLAGGED_COLS = 8192
 
 
 @dataclass
@@ -275,16 +279,22 @@ def plan_handoff(ops, world_size: int):
     where `key` names the flagged-word buffer (one per tensor, shared by all layers)."""
     plan = {i: {} for i in range(len(ops))}
     next_id = 0
+    def reader_ok(j, role):
+        return (ops[j].kind == "linear" and role in ("x", "res")) or \
+               (ops[j].kind == "attention" and role == "qkv")
+
     for i, op in enumerate(ops):
-        if op.kind != "linear":
+        if op.kind not in ("linear", "attention"):
             continue
         T = op.t["out"]
+        if T.dims[1] > MAX_FLAGGED_COLS:
+            continue
         readers, wraps = _readers(ops, i, T)
         if not readers or wraps:
             continue
         ar = None
-        if (len(readers) == 1 and ops[readers[0][0]].kind == "allreduce" and world_size > 1
-                and readers[0][0] == i + 1):
+        if (op.kind == "linear" and len(readers) == 1 and ops[readers[0][0]].kind == "allreduce"
+                and world_size > 1 and readers[0][0] == i + 1):
             ar = readers[0][0]
             T2 = ops[ar].t["out"]
             readers2, wraps2 = _readers(ops, ar, T2)
@@ -293,7 +303,7 @@ def plan_handoff(ops, world_size: int):
             final = readers2
         else:
             final = readers
-        if not all(ops[j].kind == "linear" and role in ("x", "res") for j, role in final):
+        if not all(reader_ok(j, role) for j, role in final):
             continue
         if any(role == "res" and (ops[j].flags & N.F_SILU_MUL) for j, role in final):
             continue
@@ -364,7 +374,7 @@ def _link(tasks, first, ev, plan, ops, oi, prev_event, prev_count):
         ts.trig_event = ev if triggers else -1
         ts.dep_event = prev_event if waits else -1
         ts.dep_count = prev_count if waits else 0
-        ts.flagged_deps = [plan[oi][r][1] for r in ("x", "res", "in") if r in plan[oi]]
+        ts.flagged_deps = [plan[oi][r][1] for r in ("x", "res", "in", "qkv") if r in plan[oi]]
         ts.flagged_out = plan[oi]["out"][1] if "out" in plan[oi] else -1
 
 
@@ -549,6 +559,15 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                         if nsplit > 1:
                             ts.ptr[6], ts.ptr[7] = (attn_scratch, 0), (attn_counters, 0)
                         ts.iarg[:9] = [r, h, s, nsplit, G, hkv, qkv.dims[1], o.dims[1], max_rows]
+                        if "qkv" in plan[oi]:    # packed q/k/v arrive as flagged words
+                            ts.flags |= N.F_LL_IN
+                            ts.ptr[0] = (ll_bufs[plan[oi]["qkv"][0]], 0)
+                            ts.iarg[11] = plan[oi]["qkv"][1]
+                        if "out" in plan[oi]:    # and the result leaves the same way
+                            key, pid, _, Tout = plan[oi]["out"]
+                            ts.flags |= N.F_LL_OUT
+                            ts.ptr[3] = (ll_buffer(key, Tout, False), 0)
+                            ts.iarg[12] = pid
                         # splits of one (request, head) go to different workers
                         ts.worker = (rr + k) % W
                         tasks.append(ts)
