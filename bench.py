@@ -225,10 +225,13 @@ def run_ours(args):
     shape = llama.LlamaShape.llama3_8b()
     if args.layers:
         shape.num_hidden_layers = args.layers
+    # 8 prompt tokens per request and iteration: all requests prefill in lockstep and reach
+    # the decode phase together (with fewer token slots the first requests would already be
+    # hundreds of tokens into their generation when the last one finishes its prompt)
+    MT = 8 * B
     max_seq = PROMPT_LEN + W + K + 2
     page = 64
     pages_per_req = (max_seq + page - 1) // page
-    MT = max(8, B)
 
     def fresh_tokens():
         g = torch.Generator().manual_seed(SEED)
@@ -242,7 +245,8 @@ def run_ours(args):
     plen = host_plen.to(dev)
     # N > 1: tensor parallelism over the N GPUs (column-split qkv / gate / up, row-split
     # o_proj / down_proj, in-kernel all-reduce over NVLink after each row-split projection;
-    # lm_head replicated).  The total work is fixed, so the scaling is "strong".
+    # lm_head split by vocabulary rows, arg-max winners exchanged).  The total work is fixed,
+    # so the scaling is "strong".
     if world > 1:
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     weights = llama.init_weights(shape, dev, SEED, world_size=world, rank=rank)
@@ -254,7 +258,7 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
 
-    prefill_iters = (PROMPT_LEN + 7) // 8 if B == 1 else None
+    prefill_iters = (PROMPT_LEN + 7) // 8   # every request advances 8 prompt tokens per iteration
 
     def run_to_decode():
         """Prefill the prompts (untimed): iterate until every request is decoding."""
@@ -329,9 +333,8 @@ def run_ours(args):
         return
     hbm, src = peaks()
     vpad = llama.padded_vocab(shape.vocab_size)
-    # per GPU: its shard of the layer weights + the replicated lm_head + its kv heads
-    wbytes = (shape.decode_weight_bytes(1, vpad) - vpad * shape.hidden_size * 2) / world \
-        + vpad * shape.hidden_size * 2
+    # per GPU: its shard of every weight (the lm_head by vocabulary rows) + its kv heads
+    wbytes = shape.decode_weight_bytes(1, vpad) / world
     ctx_mid = PROMPT_LEN + W + K / 2.0
     kv_bytes = B * ctx_mid * shape.num_hidden_layers * shape.num_key_value_heads * shape.head_dim * 2 * 2 / world
     alg = wbytes + kv_bytes

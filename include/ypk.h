@@ -87,7 +87,8 @@ enum ypk_task_type {
 #define YPK_F_LL_OUT 0x400u    /* result also leaves as flagged words (ptr[7]);
                                   ATTENTION: only as flagged words (ptr[3])  */
 #define YPK_F_LL_PUSH 0x800u   /* LINEAR: partial sum: flagged words only, into slot `rank`
-                                  of ptr[7] = [world][max_tokens][ld / 2] on every rank */
+                                  of ptr[7] = [world][max_tokens][ld / 2] on every rank;
+                                  ARGMAX_REDUCE: exchange the slice winners (ptr[3]) */
 
 #define YPK_TASK_NPTR 8
 #define YPK_TASK_NINT 16
@@ -117,7 +118,10 @@ enum ypk_task_type {
  *                  YPK_F_LL_OUT out is written as flagged words under tag id iarg[12]
  * ARGMAX_PARTIAL: ptr = {logits, part_val, part_idx}; iarg = {col0, ncols,
  *                  ldlogits, part, nparts}
- * ARGMAX_REDUCE: ptr = {part_val, part_idx, out(int64)}; iarg = {nparts}
+ * ARGMAX_REDUCE: ptr = {part_val, part_idx, out(int64)}; iarg = {nparts}; with
+ *          YPK_F_LL_PUSH (vocabulary split over the ranks) ptr[3] = exchange buffer
+ *          [world][max_tokens][2] flagged words in the symmetric arena, iarg = {nparts,
+ *          first vocabulary row of this rank's slice, world, rank}, iarg[12] = tag id
  * ALLREDUCE: ptr = {in, buf, out, signals} (buf, signals from the symmetric arena;
  *          buf = [2][world][max_tokens][hidden] 16-bit, signals uint64[])
  *          iarg = {col0, ncols, ld_in, ld_out, hidden, max_tokens, half, signal index,

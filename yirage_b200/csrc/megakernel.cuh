@@ -99,7 +99,9 @@ __device__ __noinline__ bool run_small(const Runtime *rt, Misc *misc, int worker
   switch (t.type) {
     case YPK_TASK_EMBED: embed_task(t, batch); break;
     case YPK_TASK_ARGMAX_PARTIAL: argmax_partial_task(t, batch); break;
-    case YPK_TASK_ARGMAX_REDUCE: argmax_reduce_task(t, batch); break;
+    case YPK_TASK_ARGMAX_REDUCE:
+      if (!argmax_reduce_task(wc, rt, t, batch, iter)) wc.failed = true;
+      break;
     case YPK_TASK_RMSNORM: rmsnorm_task(t, batch); break;
     case YPK_TASK_SILU_MUL: silu_mul_task(t, batch); break;
     case YPK_TASK_ALLREDUCE:

@@ -3,6 +3,7 @@
 // on-device continuous batcher that runs between iterations.
 #pragma once
 #include "device_common.cuh"
+#include "ll_handoff.cuh"
 
 namespace ypk {
 
@@ -60,12 +61,19 @@ __device__ __forceinline__ void argmax_partial_task(const ypk_task &t, int batch
 }
 
 // Final reduction over the chunks (argmax_sm100.cuh:116-167), token id as int64.
-__device__ __forceinline__ void argmax_reduce_task(const ypk_task &t, int batch) {
+// With YPK_F_LL_PUSH the logits are one rank's slice of a vocabulary split over the
+// tensor-parallel ranks (iarg = {nparts, first vocabulary row of the slice, world, rank}):
+// the slice's winner goes to every rank as two flagged words {value bits, tag}, {index, tag}
+// into slot `rank` of ptr[3] = [world][max_tokens][2] words (symmetric arena), and every rank
+// takes the best of the world slots, lowest index on ties, so all ranks sample the same token.
+__device__ __forceinline__ bool argmax_reduce_task(WaitCtx &wc, const Runtime *rt, const ypk_task &t,
+                                                   int batch, long long iter) {
   const uint16_t *pval = reinterpret_cast<const uint16_t *>(t.ptr[0]);
   const long long *pidx = reinterpret_cast<const long long *>(t.ptr[1]);
   long long *out = reinterpret_cast<long long *>(t.ptr[2]);
   const int nparts = t.iarg[0];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  LLPoll poll;
   for (int b = warp; b < batch; b += kConsumerWarps) {
     float best = -INFINITY;
     long long bidx = 0x7fffffffffffffffll;
@@ -86,8 +94,41 @@ __device__ __forceinline__ void argmax_reduce_task(const ypk_task &t, int batch)
         bidx = oi;
       }
     }
+    if (t.flags & YPK_F_LL_PUSH) {
+      const int world = t.iarg[2], rank = t.iarg[3];
+      const uint32_t tag = ll_tag(*rt, iter, t.iarg[12]);
+      const size_t off = size_t(reinterpret_cast<char *>(t.ptr[3]) - rt->arena[rank]);
+      bidx += t.iarg[1];
+      if (lane < world) {   // lane p tells rank p
+        unsigned long long *dst = reinterpret_cast<unsigned long long *>(rt->arena[lane] + off) +
+                                  (size_t(rank) * rt->max_tok + b) * 2;
+        ll_store_sys(dst, ll_word(__float_as_uint(best), tag));
+        ll_store_sys(dst + 1, ll_word(static_cast<uint32_t>(bidx), tag));
+      }
+      best = -INFINITY;
+      bidx = 0x7fffffffffffffffll;
+      if (lane < world) {   // and reads what rank p found
+        const unsigned long long *src =
+            reinterpret_cast<const unsigned long long *>(t.ptr[3]) + (size_t(lane) * rt->max_tok + b) * 2;
+        unsigned long long wv, wi;
+        ll_load2(src, wv, wi);
+        while (!(ll_ok(wv, tag) && ll_ok(wi, tag)) && poll.again(wc)) ll_load2(src, wv, wi);
+        best = __uint_as_float(static_cast<uint32_t>(wv));
+        bidx = static_cast<long long>(static_cast<uint32_t>(wi));
+      }
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) {   // world <= 8
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const long long oi = __shfl_xor_sync(0xffffffffu, bidx, o);
+        if (ov > best || (ov == best && oi < bidx)) {
+          best = ov;
+          bidx = oi;
+        }
+      }
+    }
     if (lane == 0) out[b] = bidx;
   }
+  return !__any_sync(0xffffffffu, poll.failed);
 }
 
 // out[b, :] = bf16(x * rsqrt(mean(x^2) + eps) * w) for rows [row0, row0+nrows) of the batch

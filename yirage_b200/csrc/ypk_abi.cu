@@ -263,6 +263,11 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
       need[0] = uint64_t(mb) * nparts * 2; align[0] = 2; required[0] = true;
       need[1] = uint64_t(mb) * nparts * 8; align[1] = 8; required[1] = true;
       need[2] = uint64_t(mb) * 8; align[2] = 8; required[2] = true;
+      if (in.flags & YPK_F_LL_PUSH) {   // vocabulary split over the ranks: winners are exchanged
+        if (a[2] != h->cfg.world_size || a[3] != h->cfg.rank || a[2] < 2 || a[2] > 8 || a[1] < 0)
+          return fail(h, YPK_ERR_INVALID, "task %d: ARGMAX_REDUCE exchange for rank %d of %d", ti, a[3], a[2]);
+        need[3] = uint64_t(a[2]) * mb * 16; align[3] = 16; required[3] = true;
+      }
       break;
     }
     case YPK_TASK_ALLREDUCE: {
@@ -318,8 +323,9 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
     if (rc) return rc;
   }
   if ((in.type == YPK_TASK_LINEAR && (in.flags & YPK_F_LL_PUSH)) ||
+      (in.type == YPK_TASK_ARGMAX_REDUCE && (in.flags & YPK_F_LL_PUSH)) ||
       (in.type == YPK_TASK_ALLREDUCE && (in.flags & YPK_F_LL_IN))) {
-    const int p = in.type == YPK_TASK_LINEAR ? 7 : 1;
+    const int p = in.type == YPK_TASK_LINEAR ? 7 : in.type == YPK_TASK_ARGMAX_REDUCE ? 3 : 1;
     const uint64_t a0 = reinterpret_cast<uint64_t>(h->arena);
     if (!h->arena || out->ptr[p] < a0 || out->ptr[p] + need[p] > a0 + h->arena_bytes)
       return fail(h, YPK_ERR_INVALID, "task %d: the pushed flagged-word buffer is not in the symmetric arena",

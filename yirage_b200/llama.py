@@ -124,7 +124,8 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
                         num_workers: int = 128, use_model_eps: bool = True,
                         k_cache: Optional[torch.Tensor] = None,
                         v_cache: Optional[torch.Tensor] = None, compile: bool = True,
-                        dry_run: bool = False, profiler_tensor: Optional[torch.Tensor] = None, handoff: Optional[str] = None):
+                        dry_run: bool = False, profiler_tensor: Optional[torch.Tensor] = None, handoff: Optional[str] = None,
+                        vocab_parallel: Optional[bool] = None):
     """Build (and compile) the decode megakernel for `weights`.  Returns (ypk, state) where
     state holds the meta tensors, caches and rope tables the kernel works on."""
     dev = tokens.device
@@ -154,6 +155,16 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
     cos, sin = rope_tables(shape, max(max_seq_length, 64), dev)
     lm_head = torch.cat((weights["lm_head"],
                          torch.zeros(vpad - shape.vocab_size, h, dtype=torch.bfloat16, device=dev)), 0)
+    # Tensor parallelism: every rank keeps one slice of the vocabulary rows and the ranks
+    # exchange their arg-max winners (vocab_parallel=False replicates the lm_head instead).
+    if vocab_parallel is None:
+        vocab_parallel = world_size > 1
+    vocab_parallel = bool(vocab_parallel) and world_size > 1
+    vslice = vpad // world_size if vocab_parallel else vpad
+    if vocab_parallel:
+        if vpad % world_size or vslice % num_workers:
+            raise ValueError("the padded vocabulary does not split evenly over the ranks and workers")
+        lm_head = lm_head[rank * vslice:(rank + 1) * vslice].contiguous()
 
     ypk = PersistentKernel(
         mode="offline", world_size=world_size, mpi_rank=rank, num_workers=num_workers,
@@ -189,7 +200,7 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
     silu_mul_out = tmp("silu_mul_out", inter)
     mlp_out = tmp("mlp_out", h, shared=True)
     mlp_final = tmp("mlp_final", h, shared=True)
-    argmax_in = tmp("argmax_in", vpad)
+    argmax_in = tmp("argmax_in", vslice)
     argmax_part_value = tmp("argmax_part_value", num_workers)
     argmax_part_index = tmp("argmax_part_index", num_workers, dt=core.int64)
     argmax_out = ypk.attach_input(meta["output_tokens"], name="output_token")
@@ -247,13 +258,15 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
     ypk.rmsnorm_layer(input=x, weight=w_fn, output=rmsnorm_out, grid_dim=(MT, 1, 1),
                       block_dim=(128, 1, 1))
     ypk.linear_layer(input=rmsnorm_out, weight=w_lm, output=argmax_in,
-                     grid_dim=(vpad // 256, 1, 1), block_dim=(128, 1, 1))
+                     grid_dim=(vslice // 256 if vslice % 256 == 0 else 1, 1, 1), block_dim=(128, 1, 1))
     ypk.argmax_partial_layer(input=argmax_in, output=(argmax_part_value, argmax_part_index),
                              grid_dim=(num_workers, 1, 1), block_dim=(128, 1, 1))
     ypk.argmax_reduce_layer(input=(argmax_part_value, argmax_part_index), output=argmax_out,
-                            grid_dim=(1, 1, 1), block_dim=(128, 1, 1))
+                            grid_dim=(1, 1, 1), block_dim=(128, 1, 1),
+                            vocab_offset=rank * vslice if vocab_parallel else 0, exchange=vocab_parallel)
     state = {"meta": meta, "k_cache": k_cache, "v_cache": v_cache, "cos": cos, "sin": sin,
-             "lm_head": lm_head, "tensors": {"argmax_in": argmax_in, "attn_out": attn_out}}
+             "lm_head": lm_head, "vocab_slice": (rank * vslice if vocab_parallel else 0, vslice),
+             "tensors": {"argmax_in": argmax_in, "attn_out": attn_out}}
     if compile:
         ypk.compile(dry_run=dry_run)
     return ypk, state

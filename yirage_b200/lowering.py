@@ -47,6 +47,7 @@ SILU_GRAN = 2                # kSiluGran: fused gate/up rows come as 2 gate + 2 
 # in flight per thread, so a 14336-wide MLP activation would take four trips to L2 against
 # the one of a plain copy.
 MAX_FLAGGED_COLS = 8192
+ARGMAX_TAG_ID = 255           # tag id of the cross-rank arg-max exchange (operators use 0..253)
 
 
 @dataclass
@@ -222,7 +223,9 @@ def fuse(regs: List[RegisteredTask], default_eps: float) -> List[FusedOp]:
             i += 1
         elif name == "argmax_reduce":
             pv, pi, o = rt.operands
-            out.append(FusedOp("argmax_reduce", [rt], {"val": pv, "idx": pi, "out": o}))
+            out.append(FusedOp("argmax_reduce", [rt], {"val": pv, "idx": pi, "out": o},
+                               attrs={"vocab_offset": rt.attrs.get("vocab_offset", 0),
+                                      "exchange": rt.attrs.get("exchange", False)}))
             i += 1
         elif name == "allreduce":
             x, buf, o = rt.operands
@@ -308,13 +311,13 @@ def plan_handoff(ops, world_size: int):
         if any(role == "res" and (ops[j].flags & N.F_SILU_MUL) for j, role in final):
             continue
         if ar is None:
-            pid = next_id % 256
+            pid = next_id % 254
             next_id += 1
             plan[i]["out"] = (("ll", id(T)), pid, False, T)
             for j, role in final:
                 plan[j][role] = (("ll", id(T)), pid)
         else:
-            pid, aid = next_id % 256, (next_id + 1) % 256
+            pid, aid = next_id % 254, (next_id + 1) % 254
             next_id += 2
             plan[i]["out"] = (("push", id(T)), pid, True, T)
             plan[ar]["in"] = (("push", id(T)), pid)
@@ -607,6 +610,12 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
             ts = TaskSpec(N.TASK_ARGMAX_REDUCE, op_id=oi)
             ts.ptr[0], ts.ptr[1], ts.ptr[2] = (pv, 0), (pi, 0), (o, 0)
             ts.iarg[0] = nparts
+            if op.attrs.get("exchange") and world_size > 1:
+                xbuf = scratch((world_size, max_tokens, 2), int64, "argmax_exchange", symmetric=True)
+                ts.flags |= N.F_LL_PUSH
+                ts.ptr[3] = (xbuf, 0)
+                ts.iarg[1:4] = [op.attrs["vocab_offset"], world_size, rank]
+                ts.iarg[12] = ARGMAX_TAG_ID
             ts.worker = 0
             tasks.append(ts)
         elif op.kind == "rmsnorm":

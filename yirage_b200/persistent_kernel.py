@@ -253,7 +253,10 @@ class PersistentKernel:
                               (output_index, (1, 0, -1), -1)], grid_dim, block_dim, [num_tasks])
 
     def argmax_reduce_layer(self, input: tuple, output: DTensor, grid_dim: tuple,
-                            block_dim: tuple):
+                            block_dim: tuple, vocab_offset: int = 0, exchange: bool = False):
+        """`exchange=True` (not in the reference): the logits are this rank's slice of a
+        vocabulary split over the tensor-parallel ranks, starting at row `vocab_offset`; the
+        ranks exchange their winners and all write the same token."""
         assert len(input) == 2
         input_value, input_index = input
         assert input_value.num_dims == 2 and input_index.num_dims == 2
@@ -261,7 +264,8 @@ class PersistentKernel:
         name = "argmax_reduce_sm100" if self.target_cc == 100 else "argmax_reduce"
         self._register(name, [(input_value, (1, 0, -1), -1), (input_index, (1, 0, -1), -1),
                               (output, (0, 1, -1), -1)], grid_dim, block_dim,
-                       [getattr(self, "argmax_partial_output_size", 0)])
+                       [getattr(self, "argmax_partial_output_size", 0)],
+                       vocab_offset=int(vocab_offset), exchange=bool(exchange))
 
     # builders of the reference that lie outside the decode hot path
     def _not_built(self, what):
