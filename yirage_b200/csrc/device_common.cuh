@@ -147,6 +147,7 @@ struct Runtime {
   // iterations run before the last reset: flagged-word tags and all-reduce arrival counts
   // keep growing across resets (ll_epoch also steps over an aborted iteration)
   unsigned long long ll_epoch, ar_epoch;
+  int ll_push_fence;   // diagnostic (YPK_LL_PUSH_FENCE=1): system-scope fence after a task's pushes
   char *arena[8];      // symmetric arena of every tensor-parallel rank as mapped here (own at [rank])
   unsigned long long *prof;
   int prof_stride;  // records per worker

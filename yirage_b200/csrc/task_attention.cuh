@@ -482,7 +482,6 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
   const uint16_t *cosp = reinterpret_cast<const uint16_t *>(t.ptr[4]);
   const uint16_t *sinp = reinterpret_cast<const uint16_t *>(t.ptr[5]);
   float *scratch = reinterpret_cast<float *>(t.ptr[6]);
-  unsigned int *counters = reinterpret_cast<unsigned int *>(t.ptr[7]);
   const bool rope = (t.flags & YPK_F_ROPE) != 0;
   // flagged-word hand-off: with YPK_F_LL_IN ptr[0] holds the packed q/k/v as {two values,
   // tag} words ([max_tokens][ld_qkv / 2]), with YPK_F_LL_OUT ptr[3] takes the result that way
@@ -619,9 +618,16 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
   consumer_bar();  // q / knew / vnew are dead from here on; the area becomes the merge buffer
   if (tid == 0 && misc->prof_rec) misc->prof_rec[5] = globaltimer();
 
+  // Split-KV partials travel as flagged words {fp32 bits, tag}: the split that owns the new
+  // tokens (the last one) folds the others' rows into its own as they show up, the others
+  // just write.  No arrival counter, no fence, no second pass.
   const bool single = s.nact == 1;
-  float *my_scr =
-      scratch + ((size_t(r) * hkv + h) * nsplit + split) * size_t(max_rows) * kAttnRowFloats;
+  const bool combiner = s.handles_new;
+  const uint32_t tag_sp = ll_tag(rt, iter, t.iarg[13]);
+  unsigned long long *scr_w = reinterpret_cast<unsigned long long *>(scratch);
+  const size_t split_words = size_t(max_rows) * kAttnRowFloats;
+  unsigned long long *head_scr = scr_w + (size_t(r) * hkv + h) * nsplit * split_words;
+  unsigned long long *my_scr = head_scr + size_t(split) * split_words;
   // merge states are [16 rows][132] per warp, or [8 rows][132] when only 8 rows are live
   const int kStateFloats = (rows <= 8 ? 8 : 16) * kAttnRowFloats;
   // Merge the warps of a query tile, four states at a time, then finish rows [mt*16, ..).
@@ -655,13 +661,41 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
       const int row = row_lo + rr;
       if (single) {
         emit(row, d, o0 / l, o1 / l);
-      } else {
-        float *dst = my_scr + row * kAttnRowFloats;
-        *reinterpret_cast<float2 *>(dst + d) = make_float2(o0, o1);
+      } else if (!combiner) {
+        unsigned long long *dst = my_scr + row * kAttnRowFloats;
+        ll_store(dst + d, ll_word(__float_as_uint(o0), tag_sp));
+        ll_store(dst + d + 1, ll_word(__float_as_uint(o1), tag_sp));
         if (d == 0) {
-          dst[kHeadDim] = m;
-          dst[kHeadDim + 1] = l;
+          ll_store(dst + kHeadDim, ll_word(__float_as_uint(m), tag_sp));
+          ll_store(dst + kHeadDim + 1, ll_word(__float_as_uint(l), tag_sp));
         }
+      } else {
+        // fold in the other splits in split order, this split's own row last
+        float mr = -INFINITY, lr = 0.f, a0 = 0.f, a1 = 0.f;
+        auto fold = [&](float ms, float ls, float x0, float x1) {
+          if (ms == -INFINITY) return;
+          const float m_new = fmaxf(mr, ms);
+          const float c_old = exp2f(mr - m_new), c_new = exp2f(ms - m_new);   // exp2f(-inf) = 0
+          lr = lr * c_old + ls * c_new;
+          a0 = a0 * c_old + x0 * c_new;
+          a1 = a1 * c_old + x1 * c_new;
+          mr = m_new;
+        };
+        for (int sp = 0; sp < s.nact - 1; ++sp) {
+          const unsigned long long *pr = head_scr + size_t(sp) * split_words + row * kAttnRowFloats;
+          unsigned long long w0, w1, w2, w3;
+          for (;;) {
+            ll_load2(pr + d, w0, w1);
+            ll_load2(pr + kHeadDim, w2, w3);
+            if ((ll_ok(w0, tag_sp) && ll_ok(w1, tag_sp) && ll_ok(w2, tag_sp) && ll_ok(w3, tag_sp)) ||
+                !poll.again(wc))
+              break;
+          }
+          fold(__uint_as_float(uint32_t(w2)), __uint_as_float(uint32_t(w3)),
+               __uint_as_float(uint32_t(w0)), __uint_as_float(uint32_t(w1)));
+        }
+        fold(m, l, o0, o1);
+        emit(row, d, a0 / lr, a1 / lr);
       }
     }
   };
@@ -708,57 +742,7 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
     consumer_bar();
     finalize(1, 4);
   }
-  if (single) return;
-
-  // Arrival: the barrier orders every thread's partial before thread 0, whose acq_rel
-  // increment publishes it (release) and, for the last arriver, makes the other splits'
-  // partials visible (acquire); the second barrier passes that on to the whole CTA.
-  consumer_bar();
-  if (tid == 0) {
-    unsigned old;
-    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;"
-                 : "=r"(old)
-                 : "l"(counters + r * hkv + h)
-                 : "memory");
-    misc->flag = (old == unsigned(s.nact - 1)) ? 1 : 0;
-  }
-  consumer_bar();
-  if (tid == 0 && misc->prof_rec) misc->prof_rec[6] = globaltimer();
-  if (misc->flag) {
-    // Last arriver: fold the splits' partial rows together in split order.  One running
-    // (max, sum, outputs) per thread, so the loads of all splits are independent of each
-    // other and go out together.
-    const float *base = scratch + (size_t(r) * hkv + h) * nsplit * size_t(max_rows) * kAttnRowFloats;
-    for (int idx = tid; idx < rows * (kHeadDim / 2); idx += kConsumerThreads) {
-      const int d = (idx & (kHeadDim / 2 - 1)) * 2;
-      const int row = idx >> 6;
-      float m = -INFINITY, l = 0.f, o0 = 0.f, o1 = 0.f;
-      for (int sp0 = 0; sp0 < s.nact; sp0 += 4) {
-        float ms[4], ls[4];
-        float2 os[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float *pr = base + (size_t(min(sp0 + j, s.nact - 1)) * max_rows + row) * kAttnRowFloats;
-          ms[j] = __ldcg(pr + kHeadDim);
-          ls[j] = __ldcg(pr + kHeadDim + 1);
-          os[j] = __ldcg(reinterpret_cast<const float2 *>(pr + d));
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (sp0 + j < s.nact && ms[j] != -INFINITY) {
-            const float m_new = fmaxf(m, ms[j]);
-            const float c_old = exp2f(m - m_new), c_new = exp2f(ms[j] - m_new);   // exp2f(-inf) = 0
-            l = l * c_old + ls[j] * c_new;
-            o0 = o0 * c_old + os[j].x * c_new;
-            o1 = o1 * c_old + os[j].y * c_new;
-            m = m_new;
-          }
-        }
-      }
-      emit(row, d, o0 / l, o1 / l);
-    }
-    if (tid == 0) counters[r * hkv + h] = 0u;
-  }
+  if (poll.failed) wc.failed = true;
 }
 
 // The two forms are separate out-of-line functions: the 16-row form needs twice the

@@ -143,20 +143,22 @@ __device__ __forceinline__ float silu_mul_ref(float g, float u) {
 // Writes the finished values of `nr` rows starting at task row r0.  val(r, b) returns the
 // fp32 dot product (before the RMS scale); res_s holds the residual slice of the task,
 // [batch][nrows] 16-bit, staged in shared memory when the task started.
-// Result pair (columns col, col + 1 of token b) in flagged-word form: into this GPU's copy,
-// or, for a partial sum (YPK_F_LL_PUSH), into slot `rank` of the copy on every rank; the
-// plain tensor is written too unless the values are partial.
+// Result pair (columns col, col + 1 of token b) in flagged-word form: into this GPU's copy
+// (and the plain tensor), or, for a partial sum (YPK_F_LL_PUSH), into slot `rank` of the copy
+// on rank `peer`.  The copies for the different peers are made by different threads (the
+// epilogue loops run over peer x pair): one thread storing to the peers in turn pays the
+// address translation of each peer's mapping one after the other, about a microsecond each,
+// and the last peer in everybody's loop then runs that far behind the first.
 template <bool F16>
 __device__ __forceinline__ void ll_emit(const LinearArgs &a, const Runtime &rt, int b, int col,
-                                        float v0, float v1) {
+                                        float v0, float v1, int peer) {
   const uint32_t packed = uint32_t(cvt_out<F16>(v0)) | (uint32_t(cvt_out<F16>(v1)) << 16);
   const size_t widx = size_t(b) * size_t(a.ldout >> 1) + size_t(col >> 1);
   const unsigned long long w = ll_word(packed, a.tag_out);
   if (a.flags & YPK_F_LL_PUSH) {
     const size_t off = size_t(reinterpret_cast<char *>(a.ll_out) - rt.arena[rt.rank]) +
                        (size_t(rt.rank) * rt.max_tok * size_t(a.ldout >> 1) + widx) * 8;
-    for (int p = 0; p < rt.world; ++p)
-      ll_store_sys(reinterpret_cast<unsigned long long *>(rt.arena[p] + off), w);
+    ll_store_sys(reinterpret_cast<unsigned long long *>(rt.arena[peer] + off), w);
   } else {
     *reinterpret_cast<uint32_t *>(reinterpret_cast<uint16_t *>(a.out) + size_t(b) * a.ldout + col) =
         packed;
@@ -181,9 +183,11 @@ __device__ __forceinline__ void linear_epilogue_ll(const LinearArgs &a, const Ru
     for (int w = 0; w < kConsumerWarps; ++w) s += pall[(w * kRowBlock + r) * kMaxBatch + b];
     return s;
   };
+  const int ncopy = (a.flags & YPK_F_LL_PUSH) ? rt.world : 1;
   if (a.flags & YPK_F_SILU_MUL) {
     const int npair = nr >> 2;   // one 2 gate + 2 up granule = one pair of outputs
-    for (int idx = tid; idx < npair * bc; idx += kConsumerThreads) {
+    for (int idx0 = tid; idx0 < npair * bc * ncopy; idx0 += kConsumerThreads) {
+      const int peer = idx0 / (npair * bc), idx = idx0 - peer * (npair * bc);
       const int b = idx / npair, g = idx - b * npair;
       const int rg = g * (2 * kSiluGran);
       float g0 = val(rg, b), g1 = val(rg + 1, b), u0 = val(rg + 2, b), u1 = val(rg + 3, b);
@@ -192,11 +196,12 @@ __device__ __forceinline__ void linear_epilogue_ll(const LinearArgs &a, const Ru
         g0 *= rn; g1 *= rn; u0 *= rn; u1 *= rn;
       }
       const int col = a.out_col0 + ((a.row0 + r0) >> 1) + g * kSiluGran;
-      ll_emit<F16>(a, rt, b0 + b, col, silu_mul_ref(g0, u0), silu_mul_ref(g1, u1));
+      ll_emit<F16>(a, rt, b0 + b, col, silu_mul_ref(g0, u0), silu_mul_ref(g1, u1), peer);
     }
   } else {
     const int npair = nr >> 1;
-    for (int idx = tid; idx < npair * bc; idx += kConsumerThreads) {
+    for (int idx0 = tid; idx0 < npair * bc * ncopy; idx0 += kConsumerThreads) {
+      const int peer = idx0 / (npair * bc), idx = idx0 - peer * (npair * bc);
       const int b = idx / npair, r = (idx - b * npair) * 2;
       float v0 = val(r, b), v1 = val(r + 1, b);
       if (norm) {
@@ -207,9 +212,10 @@ __device__ __forceinline__ void linear_epilogue_ll(const LinearArgs &a, const Ru
         v0 += cvt_one<F16>(res_s[b * a.nrows + r0 + r]);
         v1 += cvt_one<F16>(res_s[b * a.nrows + r0 + r + 1]);
       }
-      ll_emit<F16>(a, rt, b0 + b, a.out_col0 + a.row0 + r0 + r, v0, v1);
+      ll_emit<F16>(a, rt, b0 + b, a.out_col0 + a.row0 + r0 + r, v0, v1, peer);
     }
   }
+  if (rt.ll_push_fence && (a.flags & YPK_F_LL_PUSH)) asm volatile("fence.acq_rel.sys;" ::: "memory");
 }
 
 template <bool F16, typename ValFn>

@@ -242,7 +242,7 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
       }
       if (nsplit > 1) {
         need[6] = uint64_t(h->cfg.max_num_batched_requests) * hkv * nsplit * max_rows *
-                  kAttnRowFloats * 4u;
+                  kAttnRowFloats * 8u;   // flagged words {fp32 bits, tag}
         need[7] = uint64_t(h->cfg.max_num_batched_requests) * hkv * 4u;
         align[6] = 16; align[7] = 4; required[6] = required[7] = true;
       }
@@ -946,6 +946,7 @@ int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_
   rt.use_tmem = h->use_tmem ? 1 : 0;
   rt.umma_policy = h->umma_policy;
   rt.ll_epoch = h->ll_epoch;
+  { const char *pf = getenv("YPK_LL_PUSH_FENCE"); rt.ll_push_fence = (pf && pf[0] == '1') ? 1 : 0; }
   rt.ar_epoch = h->ar_epoch;
   for (int p = 0; p < 8; ++p) rt.arena[p] = h->peer_arena[p];
   if (h->arena)

@@ -547,7 +547,8 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
             nsplit = max(1, min(W // max(1, max_requests * hkv), max_tiles, MAX_SPLITS))
             max_rows = min(G * MAX_NEW_TOKENS, MAX_ATTN_ROWS)
             if nsplit > 1:
-                need = max_requests * hkv * nsplit * max_rows * ATTN_ROW_FLOATS
+                # partial rows travel as 8-byte flagged words {fp32 bits, tag}: two floats each
+                need = 2 * max_requests * hkv * nsplit * max_rows * ATTN_ROW_FLOATS
                 if attn_scratch is None or attn_scratch.dims[0] < need:
                     attn_scratch = scratch((need,), float32, "attn_split_scratch")
                     attn_counters = scratch((max_requests * hkv,), int32, "attn_split_counters")
@@ -562,6 +563,7 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                         if nsplit > 1:
                             ts.ptr[6], ts.ptr[7] = (attn_scratch, 0), (attn_counters, 0)
                         ts.iarg[:9] = [r, h, s, nsplit, G, hkv, qkv.dims[1], o.dims[1], max_rows]
+                        ts.iarg[13] = oi % 254     # tag id of the split-KV partials
                         if "qkv" in plan[oi]:    # packed q/k/v arrive as flagged words
                             ts.flags |= N.F_LL_IN
                             ts.ptr[0] = (ll_bufs[plan[oi]["qkv"][0]], 0)
