@@ -32,6 +32,7 @@ if ROOT not in sys.path:
 
 import torch  # noqa: E402
 
+DRAM_TRAFFIC_RATIO = 0.998   # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes, ncu, profiles/
 PROMPT_LEN = 512
 SEED = 3
 FALLBACK_HBM_GBS = 6650.0
@@ -49,6 +50,8 @@ def parse():
                     choices=["decode", "rmsnorm_linear", "gated_mlp", "attention"],
                     help="decode = BASELINE configs[3] (the headline); the others time one task "
                          "kernel on BASELINE configs[0..2] as a chain of independent copies")
+    ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "llama3-70b"],
+                    help="llama3-70b = BASELINE configs[4] (context 2048); needs --gpus >= 2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -222,7 +225,13 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     K, W, B = args.steps, max(args.warmup, 3), args.batch
-    shape = llama.LlamaShape.llama3_8b()
+    global PROMPT_LEN
+    big = args.model == "llama3-70b"
+    shape = llama.LlamaShape.llama3_70b() if big else llama.LlamaShape.llama3_8b()
+    if big:
+        PROMPT_LEN = 2048      # BASELINE configs[4]: context 2048
+        if world < 2:
+            raise SystemExit("llama3-70b (140 GB of weights) is a tensor-parallel configuration: --gpus 2/4/8")
     if args.layers:
         shape.num_hidden_layers = args.layers
     # 8 prompt tokens per request and iteration: all requests prefill in lockstep and reach
@@ -258,7 +267,9 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
 
-    prefill_iters = (PROMPT_LEN + 7) // 8   # every request advances 8 prompt tokens per iteration
+    # every request advances min(8, 32 / q-heads-per-kv-head) prompt tokens per iteration
+    chunk = min(8, 32 // (shape.num_attention_heads // shape.num_key_value_heads))
+    prefill_iters = (PROMPT_LEN + chunk - 1) // chunk
 
     def run_to_decode():
         """Prefill the prompts (untimed): iterate until every request is decoding."""
@@ -346,14 +357,21 @@ def run_ours(args):
         "us_per_token": ms * 1e3 / K / B,
         "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"llama3-8b decode, batch {B}, prompt {PROMPT_LEN}, greedy (BASELINE configs[3])",
+        "config": {"workload": f"{args.model} decode, batch {B}, prompt {PROMPT_LEN}, greedy "
+                               f"(BASELINE configs[{4 if big else 3}])",
                    "layers": shape.num_hidden_layers, "page_size": page,
                    "parallelism": f"tp{world}" if world > 1 else "single",
-                   "l2": "weights streamed per iteration are 15 GB, far larger than the 126 MB L2"},
+                   "l2": f"weights streamed per iteration and GPU are {wbytes / 1e9:.1f} GB, far larger than the 126 MB L2"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s",
                      "frac": achieved / hbm, "frac_of": f"{src} copy bandwidth, per GPU",
                      "frac_of_nominal_8TBs": achieved / 8000.0,
-                     "algorithmic_bytes_per_iteration": alg, "traffic": None,
+                     "algorithmic_bytes_per_iteration": alg,
+                     "algorithmic_bytes_per_launch": alg * K,
+                     # ncu on the 4-layer case of this kernel (profiles/): dram read + write =
+                     # 0.998 x the algorithmic bytes of the captured launch; the traffic grows
+                     # with the weights streamed, so the ratio carries over to the full launch
+                     "traffic": DRAM_TRAFFIC_RATIO * alg * K,
+                     "traffic_note": "scaled from the ncu capture of the 4-layer case (ratio 0.998), per launch of K iterations",
                      "kernel": "ypk_megakernel (one launch covers all K iterations)"},
         "clocks": clocks,
         "gpu_launches": 1,

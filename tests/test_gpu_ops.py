@@ -72,8 +72,24 @@ def test_linear_norm_residual(B):
 
 
 def test_linear_batch_above_eight_restreams():
-    """K is not a multiple of 256: the batch runs as groups of 8 on the GEMV path."""
+    """K is not a multiple of 256: the batch stays on the GEMV path (one pass of 16 tokens)."""
     run_linear(11, 320, 192, max_tokens=16, seed=9, tensor_core=False)
+
+
+@pytest.mark.parametrize("B,K,N,norm,res,dtype", [
+    (9, 512, 192, False, False, torch.bfloat16),
+    (16, 4096, 4096, True, False, torch.float16),
+    (17, 1024, 520, True, True, torch.bfloat16),      # 16 + 1
+    (40, 1792, 250, False, True, torch.bfloat16),     # 16 + 16 + 8, odd row slabs
+    (64, 14336, 296, True, True, torch.bfloat16),     # 14 chunks of K
+    (12, 64, 64, True, False, torch.bfloat16),        # K below one stage
+])
+def test_linear_sixteen_tokens_per_pass(B, K, N, norm, res, dtype, monkeypatch):
+    """More than 8 tokens on the GEMV path: 16 per pass, K in chunks of a ring stage, running
+    sums in registers."""
+    monkeypatch.setenv("YPK_TENSOR_CORE", "never")
+    run_linear(B, K, N, norm=norm, residual=res, dtype=dtype, seed=B, eps=1e-5, max_tokens=64,
+               tensor_core=False)
 
 
 @pytest.mark.parametrize("B,K,N,norm,res,dtype", [
@@ -96,13 +112,15 @@ def test_linear_small_batch_in_a_large_batch_graph_stays_on_gemv():
     run_linear(8, 512, 192, max_tokens=64, seed=4, tensor_core=False)
 
 
-@pytest.mark.parametrize("B,H,I", [(1, 512, 1024), (8, 4096, 1792), (3, 1024, 2048),
-                                   (16, 1024, 2048), (40, 512, 1024), (64, 4096, 1792)])
-def test_gated_mlp_fused(B, H, I, monkeypatch):
+@pytest.mark.parametrize("B,H,I,tc", [(1, 512, 1024, "always"), (8, 4096, 1792, "always"),
+                                      (3, 1024, 2048, "always"), (16, 1024, 2048, "always"),
+                                      (40, 512, 1024, "always"), (64, 4096, 1792, "always"),
+                                      (16, 1024, 2048, "never"), (33, 4096, 1792, "never")])
+def test_gated_mlp_fused(B, H, I, tc, monkeypatch):
     """rmsnorm -> linear(gate|up) -> silu_mul -> linear(down)+residual, the MLP half of a
     layer (BASELINE config 2 at reduced width); more than 8 tokens take the tcgen05 path."""
     MT = 8 if B <= 8 else 64
-    monkeypatch.setenv("YPK_TENSOR_CORE", "always")
+    monkeypatch.setenv("YPK_TENSOR_CORE", tc)
     x = randn((MT, H), 1)
     nw = randn((H,), 2, 0.1, mean=1.0)
     wg, wu = randn((I, H), 3, 0.02), randn((I, H), 4, 0.02)
@@ -125,7 +143,7 @@ def test_gated_mlp_fused(B, H, I, monkeypatch):
     assert [o.kind for o in ypk.lower().ops] == ["linear", "linear"], "gate/up + silu must fuse"
     ypk(batch=B)
     torch.cuda.synchronize()
-    assert (ypk.status().tensor_core_tasks > 0) == (B > 8)
+    assert (ypk.status().tensor_core_tasks > 0) == (B > 8 and tc == "always")
     xc = x[:B].cpu()
     h = O.rmsnorm(xc, nw.cpu(), 1e-5)
     want = xc.float() + O.gated_mlp(h, wg.cpu(), wu.cpu(), wd.cpu())

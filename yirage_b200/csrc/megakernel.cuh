@@ -72,6 +72,12 @@ __device__ __noinline__ TaskRet run_linear(const Runtime *rt, Misc *misc, char *
   linear_consume_groups<false>(wc, smem, misc, *rt, misc->ctask, batch, iter, pos);
   return TaskRet{pos, wc.failed};
 }
+__device__ __noinline__ TaskRet run_linear16(const Runtime *rt, Misc *misc, char *smem, int worker,
+                                             int task, bool failed, int batch, RingPos pos) {
+  WaitCtx wc{rt, misc, worker, task, failed};
+  linear_consume_groups16(wc, smem, misc, misc->ctask, batch, pos);
+  return TaskRet{pos, wc.failed};
+}
 __device__ __noinline__ TaskRet run_linear_ll(const Runtime *rt, Misc *misc, char *smem, int worker,
                                               int task, bool failed, int batch, long long iter,
                                               RingPos pos) {
@@ -276,6 +282,10 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_
             } else if (t.flags & (YPK_F_LL_IN | YPK_F_LL_RES | YPK_F_LL_OUT)) {
               const TaskRet r =
                   run_linear_ll(&rt, misc, smem, worker, ti, wc.failed, batch, iter, pos);
+              pos = r.pos;
+              wc.failed = r.failed;
+            } else if (batch > kMaxBatch) {
+              const TaskRet r = run_linear16(&rt, misc, smem, worker, ti, wc.failed, batch, pos);
               pos = r.pos;
               wc.failed = r.failed;
             } else {

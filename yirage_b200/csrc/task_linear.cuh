@@ -69,6 +69,13 @@ __device__ __forceinline__ LinearArgs linear_args(const ypk_task &t, const Runti
   return a;
 }
 
+// Tokens per pass over the weights: 8 (one n-tile of the MMA) up to batch 8, else 16 (two
+// n-tiles per weight fragment, see linear_consume_group16).
+constexpr int kWideBatch = 16;
+__device__ __forceinline__ int linear_group_size(int batch) {
+  return batch > kMaxBatch ? kWideBatch : kMaxBatch;
+}
+
 // ------------------------------------------------------------------ producer
 // Traversal (must match linear_consume): batch groups -> K chunks -> 16-row blocks
 // -> 1024-column stages.
@@ -77,10 +84,11 @@ __device__ __forceinline__ bool linear_produce(WaitCtx &wc, char *smem, Misc *mi
                                                unsigned long long policy) {
   const int lane = threadIdx.x & 31;
   const LinearArgs a = linear_args(t);
-  const int nbg = (batch + kMaxBatch - 1) / kMaxBatch;
+  const int gsz = linear_group_size(batch);
+  const int nbg = (batch + gsz - 1) / gsz;
   for (int bg = 0; bg < nbg; ++bg) {
-    const int bc = min(kMaxBatch, batch - bg * kMaxBatch);
-    const int KC = chunk_cols(bc, a.K);
+    const int bc = min(gsz, batch - bg * gsz);
+    const int KC = gsz == kWideBatch ? min(a.K, kStageCols) : chunk_cols(bc, a.K);
     for (int k0 = 0; k0 < a.K; k0 += KC) {
       const int klen = min(KC, a.K - k0);
       for (int r0 = 0; r0 < a.nrows; r0 += kRowBlock) {
@@ -570,15 +578,241 @@ __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Mi
   }
 }
 
+// ------------------------------------------------------------------ 16 tokens per pass
+// More than 8 tokens: the weights are streamed once per 16 tokens.  Every weight fragment
+// (ldmatrix of 16 rows x 16 columns) feeds two m16n8k16 MMAs, tokens 0..7 and 8..15, so
+// the extra tokens cost tensor-pipe issue slots (a few per cent in use) and no HBM bytes.
+// The activations of 16 tokens do not fit shared memory for a whole K, so K goes in chunks
+// of one ring stage (1024 columns) and the running sums live in registers: a thread owns
+// up to four (4-row quad, token) items, i.e. 16 fp32 accumulators, and adds to them, after
+// every stage, the eight warps' partial tiles.  The residual is read in the epilogue.
+template <bool F16>
+__device__ __forceinline__ void linear_consume_group16(WaitCtx &wc, char *smem, Misc *misc,
+                                                       const LinearArgs &a, int b0, int B,
+                                                       RingPos &pos) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint16_t *xs = reinterpret_cast<uint16_t *>(smem + kOffXs);
+  float *part = reinterpret_cast<float *>(smem + kOffPart);   // [2][8 warps][16 rows][16 tokens]
+  const uint16_t *x = reinterpret_cast<const uint16_t *>(a.x) + size_t(b0) * a.ldx;
+  const uint16_t *nw = reinterpret_cast<const uint16_t *>(a.norm_w);
+  const bool norm = (a.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT)) != 0;
+  const bool has_nw = (a.flags & YPK_F_NORM) != 0;
+  const bool silu = (a.flags & YPK_F_SILU_MUL) != 0;
+  constexpr int kTok = kWideBatch;
+  constexpr int kPartHalf16 = kConsumerWarps * kRowBlock * kTok;   // floats
+  static_assert(2 * kPartHalf16 * 4 <= kPartBytes + kResBytes + kAccBytes, "partial tiles do not fit");
+  const int KC = min(a.K, kStageCols);
+  const int xpitch = KC + 8;
+  static_assert(kTok * (kStageCols + 8) * 2 <= kXsBytes, "16 token rows of a stage do not fit");
+
+  // items of this thread: item = token * nquads + quad (quad = 4 consecutive rows)
+  constexpr int kItems = 4;
+  const int nquads = (a.nrows + 3) >> 2;
+  const int nitems = nquads * B;
+  float racc[kItems][4];
+  int iq[kItems], ib[kItems];
+#pragma unroll
+  for (int j = 0; j < kItems; ++j) {
+    const int it = tid + j * kConsumerThreads;
+    ib[j] = it < nitems ? it / nquads : -1;
+    iq[j] = it < nitems ? it - ib[j] * nquads : -1;
+    racc[j][0] = racc[j][1] = racc[j][2] = racc[j][3] = 0.f;
+  }
+  float ss[kTok];
+#pragma unroll
+  for (int b = 0; b < kTok; ++b) ss[b] = 0.f;
+
+  const int a_row = ((lane >> 3) & 1) * 8 + (lane & 7);
+  const int a_kof = ((lane >> 4) & 1) * 8;
+  const int b_row0 = min(lane & 7, B - 1), b_row1 = min(8 + (lane & 7), B - 1);
+  const int b_kof = (lane >> 3) * 8;
+
+  int pb = 0;
+  for (int k0 = 0; k0 < a.K; k0 += KC) {
+    const int klen = min(KC, a.K - k0);
+    consumer_bar();  // the previous chunk is done with xs
+    if (!norm) {
+      for (int k = tid * 8; k < klen; k += kConsumerThreads * 8) {
+#pragma unroll
+        for (int b = 0; b < kTok; ++b) {
+          if (b < B) {
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(xs + b * xpitch + k)),
+                         "l"(x + size_t(b) * a.ldx + k0 + k)
+                         : "memory");
+          }
+        }
+      }
+      asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+    } else {
+      // a chunk is at most 1024 columns: 128 threads x 8 columns; the other 128 threads take
+      // the upper half of the tokens
+      const int half = tid >> 7, k = (tid & 127) * 8;
+      if (k < klen) {
+        uint4 wnv = make_uint4(0u, 0u, 0u, 0u);
+        if (has_nw) wnv = __ldcg(reinterpret_cast<const uint4 *>(nw + k0 + k));
+        const uint32_t q[4] = {wnv.x, wnv.y, wnv.z, wnv.w};
+        uint4 xv[kTok / 2];
+#pragma unroll
+        for (int i = 0; i < kTok / 2; ++i) {
+          const int b = half * (kTok / 2) + i;
+          xv[i] = make_uint4(0u, 0u, 0u, 0u);
+          if (b < B) xv[i] = __ldcg(reinterpret_cast<const uint4 *>(x + size_t(b) * a.ldx + k0 + k));
+        }
+#pragma unroll
+        for (int i = 0; i < kTok / 2; ++i) {
+          const int b = half * (kTok / 2) + i;
+          if (b < B) {
+            const uint32_t p[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w};
+            uint32_t o[4];
+            float s2 = 0.f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = unpack2(cvt_pair<F16>(p[e]));
+              s2 += f.x * f.x + f.y * f.y;
+              if (has_nw) {
+                const float2 g = unpack2(cvt_pair<F16>(q[e]));
+                o[e] = uint32_t(cvt_out<F16>(f.x * g.x)) | (uint32_t(cvt_out<F16>(f.y * g.y)) << 16);
+              } else {
+                o[e] = p[e];
+              }
+            }
+            // ss[] is indexed by the token's position in this thread's half
+            ss[i] += s2;
+            *reinterpret_cast<uint4 *>(xs + b * xpitch + k) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+      }
+    }
+    consumer_bar();
+
+    for (int r0 = 0; r0 < a.nrows; r0 += kRowBlock) {
+      float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
+      {
+        const int ncols = klen;   // one stage per (chunk, row block)
+        const bool got = wait_mbar(wc, &misc->full_bar[pos.slot], pos.phase);
+        const int c0 = warp * kWarpCols;
+        if (got && c0 < ncols) {
+          const char *stage = smem + kOffRing + pos.slot * kStageBytes;
+          const char *ap = stage + a_row * kRowPitch + (c0 + a_kof) * 2;
+          const uint16_t *bp0 = xs + b_row0 * xpitch + c0 + b_kof;
+          const uint16_t *bp1 = xs + b_row1 * xpitch + c0 + b_kof;
+          const int nsteps = min(kWarpCols, ncols - c0) / 32;
+          for (int s = 0; s < nsteps; ++s) {
+            uint32_t f0[4], f1[4], a0[4], a1[4];
+            ldmatrix_x4(f0, bp0 + s * 32);
+            ldmatrix_x4(f1, bp1 + s * 32);
+            ldmatrix_x4(a0, ap + s * 64);
+            ldmatrix_x4(a1, ap + s * 64 + 32);
+            mma_16816<F16>(d0, a0, f0[0], f0[1]);
+            mma_16816<F16>(d1, a0, f1[0], f1[1]);
+            mma_16816<F16>(d0, a1, f0[2], f0[3]);
+            mma_16816<F16>(d1, a1, f1[2], f1[3]);
+          }
+        }
+        __syncwarp();
+        if (lane == 0 && got) mbar_arrive(&misc->empty_bar[pos.slot]);
+        pos.advance();
+      }
+      // partial tile of this warp: rows lane/4 and +8, tokens (lane%4)*2, +1 and those + 8
+      float *pp = part + pb * kPartHalf16 + warp * (kRowBlock * kTok);
+      const int pr = lane >> 2, pc = (lane & 3) * 2;
+      *reinterpret_cast<float2 *>(pp + pr * kTok + pc) = make_float2(d0[0], d0[1]);
+      *reinterpret_cast<float2 *>(pp + (pr + 8) * kTok + pc) = make_float2(d0[2], d0[3]);
+      *reinterpret_cast<float2 *>(pp + pr * kTok + 8 + pc) = make_float2(d1[0], d1[1]);
+      *reinterpret_cast<float2 *>(pp + (pr + 8) * kTok + 8 + pc) = make_float2(d1[2], d1[3]);
+      consumer_bar();
+      const float *pall = part + pb * kPartHalf16;
+#pragma unroll
+      for (int j = 0; j < kItems; ++j) {
+        const int rq = iq[j] * 4 - r0;   // first row of the quad inside this block
+        if (iq[j] >= 0 && rq >= 0 && rq < kRowBlock) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) sum += pall[(w * kRowBlock + rq + i) * kTok + ib[j]];
+            racc[j][i] += sum;
+          }
+        }
+      }
+      pb ^= 1;
+    }
+  }
+  // RMS factors: the two halves of the block hold the statistics of their own 8 tokens
+  if (norm) {
+    float *red = part + pb * kPartHalf16;   // idle half: [8 warps][8]
+#pragma unroll
+    for (int i = 0; i < kTok / 2; ++i) {
+      const float sred = warp_sum(ss[i]);
+      if (lane == 0) red[warp * (kTok / 2) + i] = sred;
+    }
+    consumer_bar();
+    if (tid < B) {
+      const int half = tid / (kTok / 2), i = tid % (kTok / 2);
+      float sred = 0.f;
+      for (int w = half * 4; w < half * 4 + 4; ++w) sred += red[w * (kTok / 2) + i];
+      misc->rnorm_umma[tid] = rsqrtf(sred / float(a.K) + a.eps);
+    }
+    consumer_bar();
+  }
+  // epilogue from the register accumulators
+#pragma unroll
+  for (int j = 0; j < kItems; ++j) {
+    if (iq[j] < 0) continue;
+    const int b = ib[j], r = iq[j] * 4;
+    float v[4] = {racc[j][0], racc[j][1], racc[j][2], racc[j][3]};
+    if (norm) {
+      const float rn = misc->rnorm_umma[b];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] *= rn;
+    }
+    uint16_t *orow = reinterpret_cast<uint16_t *>(a.out) + size_t(b0 + b) * a.ldout;
+    if (silu) {
+      const int col = a.out_col0 + ((a.row0 + r) >> 1);
+      orow[col] = cvt_out<F16>(silu_mul_ref(v[0], v[2]));
+      orow[col + 1] = cvt_out<F16>(silu_mul_ref(v[1], v[3]));
+    } else {
+      const int col = a.out_col0 + a.row0 + r;
+      const uint16_t *rrow = reinterpret_cast<const uint16_t *>(a.res) + size_t(b0 + b) * a.ldres;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (r + i < a.nrows) {
+          float o = v[i];
+          if (a.flags & YPK_F_RESIDUAL) o += cvt_one<F16>(__ldcg(rrow + col + i));
+          orow[col + i] = cvt_out<F16>(o);
+        }
+      }
+    }
+  }
+}
+
+// More than 8 tokens on the GEMV path: groups of 16.
+__device__ __forceinline__ void linear_consume_groups16(WaitCtx &wc, char *smem, Misc *misc,
+                                                        const ypk_task &t, int batch, RingPos &pos) {
+  const LinearArgs a = linear_args(t);
+  const int nbg = (batch + kWideBatch - 1) / kWideBatch;
+  for (int bg = 0; bg < nbg; ++bg) {
+    const int b0 = bg * kWideBatch;
+    const int bc = min(kWideBatch, batch - b0);
+    if (a.flags & YPK_F_F16) {
+      linear_consume_group16<true>(wc, smem, misc, a, b0, bc, pos);
+    } else {
+      linear_consume_group16<false>(wc, smem, misc, a, b0, bc, pos);
+    }
+    if (bg + 1 < nbg) consumer_bar();  // smem of this group is dead before the next one starts
+  }
+}
+
 template <bool LL>
 __device__ __forceinline__ void linear_consume_groups(WaitCtx &wc, char *smem, Misc *misc,
                                                       const Runtime &rt, const ypk_task &t,
                                                       int batch, long long iter, RingPos &pos) {
   const LinearArgs a = linear_args(t, LL ? &rt : nullptr, iter);
-  const int nbg = (batch + kMaxBatch - 1) / kMaxBatch;
+  const int gsz = linear_group_size(batch);
+  const int nbg = (batch + gsz - 1) / gsz;
   for (int bg = 0; bg < nbg; ++bg) {
-    const int b0 = bg * kMaxBatch;
-    const int bc = min(kMaxBatch, batch - b0);
+    const int b0 = bg * gsz;
+    const int bc = min(gsz, batch - b0);
     if (a.flags & YPK_F_F16) {
       linear_consume_group<true, LL>(wc, smem, misc, rt, a, b0, bc, pos);
     } else {

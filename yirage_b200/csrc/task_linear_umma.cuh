@@ -47,9 +47,10 @@ __device__ __forceinline__ int umma_step_kblocks(const LinearArgs &a) {
 // this identically.  A tcgen05.mma occupies the SM's tensor pipe for about 78 ns whatever M
 // and N (measured back to back: 64x16x16 and 128x256x16 alike; about 130 ns each inside this
 // task, with its waits and commits), and a task issues K / 16 of them per 64-row block; the
-// GEMV path instead streams the weights once per 8 tokens at about 3/4 of the SM's share of
-// HBM (44 bytes / ns).  Take whichever is estimated to finish first: with these slabs that is
-// the GEMV path up to about 24 tokens and the tensor-core path beyond.
+// GEMV path instead streams the weights once per 16 tokens at about 3/4 of the SM's share of
+// HBM (44 bytes / ns).  Take whichever is estimated to finish first: with the slabs of an 8B
+// model that is the GEMV path up to 32 tokens and, for the wider slabs, the tensor-core path
+// beyond.
 __device__ __forceinline__ bool linear_uses_umma(const Runtime &rt, const ypk_task &t, int batch) {
   if (batch <= kMaxBatch || batch > kUmmaMaxBatch || t.iarg[9] < 0 || rt.umma_policy == 2 ||
       (t.flags & (YPK_F_LL_IN | YPK_F_LL_RES | YPK_F_LL_OUT)))
@@ -60,7 +61,7 @@ __device__ __forceinline__ bool linear_uses_umma(const Runtime &rt, const ypk_ta
   const long long nblocks = (nrows + kUmmaBlockRows - 1) / kUmmaBlockRows;
   const long long mma_ns = nblocks * (K / 16) * 130;
   const long long umma_ns = max(wbytes / 44, mma_ns);
-  const long long gemv_ns = ((batch + kMaxBatch - 1) / kMaxBatch) * (wbytes / 33);
+  const long long gemv_ns = ((batch + kWideBatch - 1) / kWideBatch) * (wbytes / 33);
   return umma_ns < gemv_ns;
 }
 
