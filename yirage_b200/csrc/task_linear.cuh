@@ -84,11 +84,46 @@ __device__ __forceinline__ bool linear_produce(WaitCtx &wc, char *smem, Misc *mi
                                                unsigned long long policy) {
   const int lane = threadIdx.x & 31;
   const LinearArgs a = linear_args(t);
-  const int gsz = linear_group_size(batch);
-  const int nbg = (batch + gsz - 1) / gsz;
+  const int nbg = (batch + kMaxBatch - 1) / kMaxBatch;
   for (int bg = 0; bg < nbg; ++bg) {
-    const int bc = min(gsz, batch - bg * gsz);
-    const int KC = gsz == kWideBatch ? min(a.K, kStageCols) : chunk_cols(bc, a.K);
+    const int bc = min(kMaxBatch, batch - bg * kMaxBatch);
+    const int KC = chunk_cols(bc, a.K);
+    for (int k0 = 0; k0 < a.K; k0 += KC) {
+      const int klen = min(KC, a.K - k0);
+      for (int r0 = 0; r0 < a.nrows; r0 += kRowBlock) {
+        const int nr = min(kRowBlock, a.nrows - r0);
+        for (int ks = 0; ks < klen; ks += kStageCols) {
+          const int ncols = min(kStageCols, klen - ks);
+          if (!wait_mbar(wc, &misc->empty_bar[pos.slot], pos.phase ^ 1u)) return false;
+          // the slot may last have been written through the generic proxy (attention tiles
+          // arrive by cp.async, partial tiles are zero-padded by the consumers)
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          char *stage = smem + kOffRing + pos.slot * kStageBytes;
+          if (lane == 0) mbar_expect_tx(&misc->full_bar[pos.slot], uint32_t(nr) * ncols * 2u);
+          __syncwarp();
+          if (lane < nr) {
+            const char *src =
+                a.w + (size_t(a.row0 + r0 + lane) * a.ldw + size_t(k0 + ks)) * 2u;
+            bulk_g2s_hint(stage + lane * kRowPitch, src, uint32_t(ncols) * 2u,
+                          &misc->full_bar[pos.slot], policy);
+          }
+          pos.advance();
+        }
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ bool linear_produce16(WaitCtx &wc, char *smem, Misc *misc,
+                                               const ypk_task &t, int batch, RingPos &pos,
+                                               unsigned long long policy) {
+  const int lane = threadIdx.x & 31;
+  const LinearArgs a = linear_args(t);
+  // groups of 16 tokens, K in chunks of one stage (see linear_consume_group16)
+  const int nbg = (batch + kWideBatch - 1) / kWideBatch;
+  for (int bg = 0; bg < nbg; ++bg) {
+    const int KC = min(a.K, kStageCols);
     for (int k0 = 0; k0 < a.K; k0 += KC) {
       const int klen = min(KC, a.K - k0);
       for (int r0 = 0; r0 < a.nrows; r0 += kRowBlock) {
@@ -583,54 +618,43 @@ __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Mi
 // (ldmatrix of 16 rows x 16 columns) feeds two m16n8k16 MMAs, tokens 0..7 and 8..15, so
 // the extra tokens cost tensor-pipe issue slots (a few per cent in use) and no HBM bytes.
 // The activations of 16 tokens do not fit shared memory for a whole K, so K goes in chunks
-// of one ring stage (1024 columns) and the running sums live in registers: a thread owns
-// up to four (4-row quad, token) items, i.e. 16 fp32 accumulators, and adds to them, after
-// every stage, the eight warps' partial tiles.  The residual is read in the epilogue.
+// of one ring stage (1024 columns), one stage per (chunk, 16-row block).  A barrier and a
+// cross-warp sum after every stage would cost as much as the stage's HBM time, so each warp
+// adds its partial tile straight into a shared fp32 accumulator [rows][16] with
+// red.shared.add.f32 and the warps only meet at chunk boundaries.  (The order of those eight
+// additions is not fixed: results of this path can differ in the last fp32 bit between runs,
+// unlike the 8-token path.)  The residual is read in the epilogue.
 template <bool F16>
 __device__ __forceinline__ void linear_consume_group16(WaitCtx &wc, char *smem, Misc *misc,
                                                        const LinearArgs &a, int b0, int B,
                                                        RingPos &pos) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr int kTok = kWideBatch;
+  constexpr int kXs16Bytes = kTok * (kStageCols + 8) * 2;                  // 33024
+  static_assert(kXs16Bytes + kMaxAccRows * kTok * 4 <= kScratchSmemBytes, "accumulators do not fit");
   uint16_t *xs = reinterpret_cast<uint16_t *>(smem + kOffXs);
-  float *part = reinterpret_cast<float *>(smem + kOffPart);   // [2][8 warps][16 rows][16 tokens]
+  float *accs = reinterpret_cast<float *>(smem + kOffXs + kXs16Bytes);     // [nrows][16]
   const uint16_t *x = reinterpret_cast<const uint16_t *>(a.x) + size_t(b0) * a.ldx;
   const uint16_t *nw = reinterpret_cast<const uint16_t *>(a.norm_w);
   const bool norm = (a.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT)) != 0;
   const bool has_nw = (a.flags & YPK_F_NORM) != 0;
   const bool silu = (a.flags & YPK_F_SILU_MUL) != 0;
-  constexpr int kTok = kWideBatch;
-  constexpr int kPartHalf16 = kConsumerWarps * kRowBlock * kTok;   // floats
-  static_assert(2 * kPartHalf16 * 4 <= kPartBytes + kResBytes + kAccBytes, "partial tiles do not fit");
   const int KC = min(a.K, kStageCols);
   const int xpitch = KC + 8;
-  static_assert(kTok * (kStageCols + 8) * 2 <= kXsBytes, "16 token rows of a stage do not fit");
 
-  // items of this thread: item = token * nquads + quad (quad = 4 consecutive rows)
-  constexpr int kItems = 4;
-  const int nquads = (a.nrows + 3) >> 2;
-  const int nitems = nquads * B;
-  float racc[kItems][4];
-  int iq[kItems], ib[kItems];
+  for (int i = tid; i < a.nrows * kTok; i += kConsumerThreads) accs[i] = 0.f;
+  float ss[kTok / 2];
 #pragma unroll
-  for (int j = 0; j < kItems; ++j) {
-    const int it = tid + j * kConsumerThreads;
-    ib[j] = it < nitems ? it / nquads : -1;
-    iq[j] = it < nitems ? it - ib[j] * nquads : -1;
-    racc[j][0] = racc[j][1] = racc[j][2] = racc[j][3] = 0.f;
-  }
-  float ss[kTok];
-#pragma unroll
-  for (int b = 0; b < kTok; ++b) ss[b] = 0.f;
+  for (int i = 0; i < kTok / 2; ++i) ss[i] = 0.f;
 
   const int a_row = ((lane >> 3) & 1) * 8 + (lane & 7);
   const int a_kof = ((lane >> 4) & 1) * 8;
   const int b_row0 = min(lane & 7, B - 1), b_row1 = min(8 + (lane & 7), B - 1);
   const int b_kof = (lane >> 3) * 8;
 
-  int pb = 0;
   for (int k0 = 0; k0 < a.K; k0 += KC) {
     const int klen = min(KC, a.K - k0);
-    consumer_bar();  // the previous chunk is done with xs
+    consumer_bar();  // the previous chunk is done with xs (and the accumulators are zeroed)
     if (!norm) {
       for (int k = tid * 8; k < klen; k += kConsumerThreads * 8) {
 #pragma unroll
@@ -644,9 +668,9 @@ __device__ __forceinline__ void linear_consume_group16(WaitCtx &wc, char *smem, 
       }
       asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
     } else {
-      // a chunk is at most 1024 columns: 128 threads x 8 columns; the other 128 threads take
-      // the upper half of the tokens
-      const int half = tid >> 7, k = (tid & 127) * 8;
+      // a chunk is at most 1024 columns: 128 threads x 8 columns; each half of the block takes
+      // the tokens of one parity
+      const int par = tid >> 7, k = (tid & 127) * 8;
       if (k < klen) {
         uint4 wnv = make_uint4(0u, 0u, 0u, 0u);
         if (has_nw) wnv = __ldcg(reinterpret_cast<const uint4 *>(nw + k0 + k));
@@ -654,13 +678,13 @@ __device__ __forceinline__ void linear_consume_group16(WaitCtx &wc, char *smem, 
         uint4 xv[kTok / 2];
 #pragma unroll
         for (int i = 0; i < kTok / 2; ++i) {
-          const int b = half * (kTok / 2) + i;
+          const int b = par + 2 * i;
           xv[i] = make_uint4(0u, 0u, 0u, 0u);
           if (b < B) xv[i] = __ldcg(reinterpret_cast<const uint4 *>(x + size_t(b) * a.ldx + k0 + k));
         }
 #pragma unroll
         for (int i = 0; i < kTok / 2; ++i) {
-          const int b = half * (kTok / 2) + i;
+          const int b = par + 2 * i;
           if (b < B) {
             const uint32_t p[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w};
             uint32_t o[4];
@@ -676,8 +700,7 @@ __device__ __forceinline__ void linear_consume_group16(WaitCtx &wc, char *smem, 
                 o[e] = p[e];
               }
             }
-            // ss[] is indexed by the token's position in this thread's half
-            ss[i] += s2;
+            ss[i] += s2;   // token par + 2 * i
             *reinterpret_cast<uint4 *>(xs + b * xpitch + k) = make_uint4(o[0], o[1], o[2], o[3]);
           }
         }
@@ -687,16 +710,40 @@ __device__ __forceinline__ void linear_consume_group16(WaitCtx &wc, char *smem, 
 
     for (int r0 = 0; r0 < a.nrows; r0 += kRowBlock) {
       float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
-      {
-        const int ncols = klen;   // one stage per (chunk, row block)
-        const bool got = wait_mbar(wc, &misc->full_bar[pos.slot], pos.phase);
-        const int c0 = warp * kWarpCols;
-        if (got && c0 < ncols) {
-          const char *stage = smem + kOffRing + pos.slot * kStageBytes;
-          const char *ap = stage + a_row * kRowPitch + (c0 + a_kof) * 2;
-          const uint16_t *bp0 = xs + b_row0 * xpitch + c0 + b_kof;
-          const uint16_t *bp1 = xs + b_row1 * xpitch + c0 + b_kof;
-          const int nsteps = min(kWarpCols, ncols - c0) / 32;
+      const bool got = wait_mbar(wc, &misc->full_bar[pos.slot], pos.phase);
+      const int c0 = warp * kWarpCols;
+      const bool mine = got && c0 < klen;
+      if (mine) {
+        const char *stage = smem + kOffRing + pos.slot * kStageBytes;
+        const char *ap = stage + a_row * kRowPitch + (c0 + a_kof) * 2;
+        const uint16_t *bp0 = xs + b_row0 * xpitch + c0 + b_kof;
+        const uint16_t *bp1 = xs + b_row1 * xpitch + c0 + b_kof;
+        const int nsteps = min(kWarpCols, klen - c0) / 32;
+        if (nsteps == kWarpCols / 32) {
+          // full slice: the sixteen fragment loads first (the asm statements keep program
+          // order and a warp issues in order), then the sixteen MMAs on four accumulators
+          uint32_t f0[4][4], f1[4][4], a0[4][4], a1[4][4];
+#pragma unroll
+          for (int s = 0; s < 4; ++s) {
+            ldmatrix_x4(f0[s], bp0 + s * 32);
+            ldmatrix_x4(f1[s], bp1 + s * 32);
+            ldmatrix_x4(a0[s], ap + s * 64);
+            ldmatrix_x4(a1[s], ap + s * 64 + 32);
+          }
+          float e0[4] = {0.f, 0.f, 0.f, 0.f}, e1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int s = 0; s < 4; ++s) {
+            mma_16816<F16>(d0, a0[s], f0[s][0], f0[s][1]);
+            mma_16816<F16>(d1, a0[s], f1[s][0], f1[s][1]);
+            mma_16816<F16>(e0, a1[s], f0[s][2], f0[s][3]);
+            mma_16816<F16>(e1, a1[s], f1[s][2], f1[s][3]);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            d0[i] += e0[i];
+            d1[i] += e1[i];
+          }
+        } else {
           for (int s = 0; s < nsteps; ++s) {
             uint32_t f0[4], f1[4], a0[4], a1[4];
             ldmatrix_x4(f0, bp0 + s * 32);
@@ -709,58 +756,55 @@ __device__ __forceinline__ void linear_consume_group16(WaitCtx &wc, char *smem, 
             mma_16816<F16>(d1, a1, f1[2], f1[3]);
           }
         }
-        __syncwarp();
-        if (lane == 0 && got) mbar_arrive(&misc->empty_bar[pos.slot]);
-        pos.advance();
       }
-      // partial tile of this warp: rows lane/4 and +8, tokens (lane%4)*2, +1 and those + 8
-      float *pp = part + pb * kPartHalf16 + warp * (kRowBlock * kTok);
-      const int pr = lane >> 2, pc = (lane & 3) * 2;
-      *reinterpret_cast<float2 *>(pp + pr * kTok + pc) = make_float2(d0[0], d0[1]);
-      *reinterpret_cast<float2 *>(pp + (pr + 8) * kTok + pc) = make_float2(d0[2], d0[3]);
-      *reinterpret_cast<float2 *>(pp + pr * kTok + 8 + pc) = make_float2(d1[0], d1[1]);
-      *reinterpret_cast<float2 *>(pp + (pr + 8) * kTok + 8 + pc) = make_float2(d1[2], d1[3]);
-      consumer_bar();
-      const float *pall = part + pb * kPartHalf16;
-#pragma unroll
-      for (int j = 0; j < kItems; ++j) {
-        const int rq = iq[j] * 4 - r0;   // first row of the quad inside this block
-        if (iq[j] >= 0 && rq >= 0 && rq < kRowBlock) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float sum = 0.f;
-#pragma unroll
-            for (int w = 0; w < kConsumerWarps; ++w) sum += pall[(w * kRowBlock + rq + i) * kTok + ib[j]];
-            racc[j][i] += sum;
-          }
+      __syncwarp();
+      if (lane == 0 && got) mbar_arrive(&misc->empty_bar[pos.slot]);
+      pos.advance();
+      if (mine) {
+        // this warp's partial tile: rows lane/4 and +8, tokens (lane%4)*2, +1 and those + 8
+        const int pr = r0 + (lane >> 2), pc = (lane & 3) * 2;
+        if (pr < a.nrows) {
+          atomicAdd(accs + pr * kTok + pc, d0[0]);
+          atomicAdd(accs + pr * kTok + pc + 1, d0[1]);
+          atomicAdd(accs + pr * kTok + 8 + pc, d1[0]);
+          atomicAdd(accs + pr * kTok + 8 + pc + 1, d1[1]);
+        }
+        if (pr + 8 < a.nrows) {
+          atomicAdd(accs + (pr + 8) * kTok + pc, d0[2]);
+          atomicAdd(accs + (pr + 8) * kTok + pc + 1, d0[3]);
+          atomicAdd(accs + (pr + 8) * kTok + 8 + pc, d1[2]);
+          atomicAdd(accs + (pr + 8) * kTok + 8 + pc + 1, d1[3]);
         }
       }
-      pb ^= 1;
     }
   }
-  // RMS factors: the two halves of the block hold the statistics of their own 8 tokens
+  consumer_bar();   // every warp's last additions are in
+  // RMS factors: each half of the block holds the statistics of the tokens of its parity
   if (norm) {
-    float *red = part + pb * kPartHalf16;   // idle half: [8 warps][8]
+    float rs[kTok / 2];
 #pragma unroll
-    for (int i = 0; i < kTok / 2; ++i) {
-      const float sred = warp_sum(ss[i]);
-      if (lane == 0) red[warp * (kTok / 2) + i] = sred;
+    for (int i = 0; i < kTok / 2; ++i) rs[i] = warp_sum(ss[i]);
+    float *mred = reinterpret_cast<float *>(xs);   // [8 warps][8]; the activations are dead by now
+    if (lane == 0) {
+#pragma unroll
+      for (int i = 0; i < kTok / 2; ++i) mred[warp * (kTok / 2) + i] = rs[i];
     }
     consumer_bar();
     if (tid < B) {
-      const int half = tid / (kTok / 2), i = tid % (kTok / 2);
+      const int half = tid & 1, i = tid >> 1;   // warps 0..3 hold the even tokens, 4..7 the odd ones
       float sred = 0.f;
-      for (int w = half * 4; w < half * 4 + 4; ++w) sred += red[w * (kTok / 2) + i];
+      for (int w = half * 4; w < half * 4 + 4; ++w) sred += mred[w * (kTok / 2) + i];
       misc->rnorm_umma[tid] = rsqrtf(sred / float(a.K) + a.eps);
     }
     consumer_bar();
   }
-  // epilogue from the register accumulators
+  // epilogue: item = token * nquads + quad (4 consecutive rows)
+  const int nquads = (a.nrows + 3) >> 2;
+  for (int it = tid; it < nquads * B; it += kConsumerThreads) {
+    const int b = it / nquads, r = (it - b * nquads) * 4;
+    float v[4];
 #pragma unroll
-  for (int j = 0; j < kItems; ++j) {
-    if (iq[j] < 0) continue;
-    const int b = ib[j], r = iq[j] * 4;
-    float v[4] = {racc[j][0], racc[j][1], racc[j][2], racc[j][3]};
+    for (int i = 0; i < 4; ++i) v[i] = r + i < a.nrows ? accs[(r + i) * kTok + b] : 0.f;
     if (norm) {
       const float rn = misc->rnorm_umma[b];
 #pragma unroll
@@ -808,11 +852,10 @@ __device__ __forceinline__ void linear_consume_groups(WaitCtx &wc, char *smem, M
                                                       const Runtime &rt, const ypk_task &t,
                                                       int batch, long long iter, RingPos &pos) {
   const LinearArgs a = linear_args(t, LL ? &rt : nullptr, iter);
-  const int gsz = linear_group_size(batch);
-  const int nbg = (batch + gsz - 1) / gsz;
+  const int nbg = (batch + kMaxBatch - 1) / kMaxBatch;
   for (int bg = 0; bg < nbg; ++bg) {
-    const int b0 = bg * gsz;
-    const int bc = min(gsz, batch - b0);
+    const int b0 = bg * kMaxBatch;
+    const int bc = min(kMaxBatch, batch - b0);
     if (a.flags & YPK_F_F16) {
       linear_consume_group<true, LL>(wc, smem, misc, rt, a, b0, bc, pos);
     } else {
