@@ -100,6 +100,12 @@ def test_reset_and_rerun_with_flagged_words():
     ypk.finalize()
 
 
+def test_more_than_eight_tokens_per_iteration():
+    """16 token slots: whole-operator events, the 16-token GEMV pass, several requests
+    prefilling and decoding in one iteration."""
+    run_generation([19, 7, 12, 3, 9], 30, max_requests=4, max_tokens=16, max_pages=4)
+
+
 def test_sequence_crosses_page_boundaries():
     run_generation([60], 140, max_requests=1, max_tokens=8, max_pages=3)
 
