@@ -118,14 +118,28 @@ __device__ __forceinline__ bool allreduce_ll_task(WaitCtx &wc, const Runtime &rt
   for (int idx = tid; idx < batch * nword; idx += kConsumerThreads) {
     const int b = idx / nword, c = idx - b * nword;
     const unsigned long long *src = buf + size_t(b) * size_t(hidden >> 1) + size_t(col0 >> 1) + c;
+    // every rank's word in flight at once; the late ones are asked for again together, so a
+    // round costs one trip to L2 however many ranks are late
     unsigned long long w[8];
+    bool late[8];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) w[r] = r < world ? ll_load(src + r * slot_words) : 0ull;
+    for (int r = 0; r < 8; ++r) late[r] = r < world;
+    for (;;) {
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        if (late[r]) w[r] = ll_load(src + r * slot_words);
+      bool any = false;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (late[r]) late[r] = !ll_ok(w[r], tag_in);
+        any |= late[r];
+      }
+      if (!any || !poll.again(wc)) break;
+    }
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (int r = 0; r < 8; ++r) {
       if (r < world) {
-        while (!ll_ok(w[r], tag_in) && poll.again(wc)) w[r] = ll_load(src + r * slot_words);
         const float2 f = unpack2(cvt_pair<false>(static_cast<uint32_t>(w[r])));
         s0 += f.x;
         s1 += f.y;
