@@ -104,6 +104,11 @@ def init_weights(shape: LlamaShape, device, seed: int, world_size: int = 1, rank
     return w
 
 
+def _divisor(n: int, want: int) -> int:
+    """Largest divisor of n that is <= want (grid hints must divide the tiled dimension)."""
+    return max(g for g in range(1, max(1, want) + 1) if n % g == 0)
+
+
 def _gate_up_groups(rows: int) -> int:
     """Number of (gate|up) groups the demo asks shuffle_tensors for: half the task count
     its grid heuristic picks for the fused gate/up projection (demo/llama3/demo.py:120-130,
@@ -217,7 +222,8 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
                                     name=f"layer_{li}_qkv_proj")
         ypk.rmsnorm_layer(input=x, weight=w_norm, output=rmsnorm_out, grid_dim=(MT, 1, 1),
                           block_dim=(128, 1, 1))
-        ypk.linear_layer(input=rmsnorm_out, weight=w_qkv, output=attn_in, grid_dim=(96, 1, 1),
+        ypk.linear_layer(input=rmsnorm_out, weight=w_qkv, output=attn_in,
+                         grid_dim=(_divisor(w_qkv.dims[0], 96), 1, 1),
                          block_dim=(128, 1, 1))
         kc = ypk.attach_input(k_cache[li], name=f"layer_{li}_k_cache")
         vc = ypk.attach_input(v_cache[li], name=f"layer_{li}_v_cache")
