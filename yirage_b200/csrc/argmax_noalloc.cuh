@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(kConsumerThreads) argmax_noalloc_kernel(
   r.iarg[0] = kNoAllocParts;
   r.flags = 0;   // no cross-rank exchange: the wait context and the runtime are never touched
   WaitCtx none{nullptr, nullptr, 0, -1, false};
-  argmax_reduce_task(none, nullptr, r, batch, 0);
+  argmax_reduce_task<false>(none, nullptr, r, batch, 0);
   if (threadIdx.x == 0) *counter = 0u;   // the next call starts from zero again
 }
 

@@ -69,7 +69,7 @@ __device__ __noinline__ TaskRet run_linear(const Runtime *rt, Misc *misc, char *
                                            int task, bool failed, int batch, long long iter,
                                            RingPos pos) {
   WaitCtx wc{rt, misc, worker, task, failed};
-  linear_consume_groups<false>(wc, smem, misc, *rt, misc->ctask, batch, iter, pos);
+  linear_consume_groups<false, false>(wc, smem, misc, *rt, misc->ctask, batch, iter, pos);
   return TaskRet{pos, wc.failed};
 }
 __device__ __noinline__ TaskRet run_linear16(const Runtime *rt, Misc *misc, char *smem, int worker,
@@ -78,11 +78,12 @@ __device__ __noinline__ TaskRet run_linear16(const Runtime *rt, Misc *misc, char
   linear_consume_groups16(wc, smem, misc, misc->ctask, batch, pos);
   return TaskRet{pos, wc.failed};
 }
+template <bool TP>
 __device__ __noinline__ TaskRet run_linear_ll(const Runtime *rt, Misc *misc, char *smem, int worker,
                                               int task, bool failed, int batch, long long iter,
                                               RingPos pos) {
   WaitCtx wc{rt, misc, worker, task, failed};
-  linear_consume_groups<true>(wc, smem, misc, *rt, misc->ctask, batch, iter, pos);
+  linear_consume_groups<true, TP>(wc, smem, misc, *rt, misc->ctask, batch, iter, pos);
   return TaskRet{pos, wc.failed};
 }
 __device__ __noinline__ TaskRetU run_linear_umma(const Runtime *rt, Misc *misc, char *smem,
@@ -98,6 +99,7 @@ __device__ __noinline__ TaskRet run_attention(const Runtime *rt, Misc *misc, cha
   attention_consume(wc, smem, misc, *rt, misc->ctask, iter, pos);
   return TaskRet{pos, wc.failed};
 }
+template <bool FULL>
 __device__ __noinline__ bool run_small(const Runtime *rt, Misc *misc, int worker, int task,
                                        bool failed, int batch, long long iter) {
   WaitCtx wc{rt, misc, worker, task, failed};
@@ -106,12 +108,14 @@ __device__ __noinline__ bool run_small(const Runtime *rt, Misc *misc, int worker
     case YPK_TASK_EMBED: embed_task(t, batch); break;
     case YPK_TASK_ARGMAX_PARTIAL: argmax_partial_task(t, batch); break;
     case YPK_TASK_ARGMAX_REDUCE:
-      if (!argmax_reduce_task(wc, rt, t, batch, iter)) wc.failed = true;
+      if (!argmax_reduce_task<FULL>(wc, rt, t, batch, iter)) wc.failed = true;
       break;
     case YPK_TASK_RMSNORM: rmsnorm_task(t, batch); break;
     case YPK_TASK_SILU_MUL: silu_mul_task(t, batch); break;
     case YPK_TASK_ALLREDUCE:
-      if (t.flags & YPK_F_LL_IN) {
+      if constexpr (!FULL) {
+        wc.failed = true;   // the single-GPU decode variant has no all-reduce (the host never picks it then)
+      } else if (t.flags & YPK_F_LL_IN) {
         if (!allreduce_ll_task(wc, *rt, t, batch, iter)) wc.failed = true;
       } else if (!allreduce_task(wc, misc, *rt, t, batch, iter)) {
         wc.failed = true;
@@ -127,6 +131,7 @@ struct ProdRet {
   RingPos pos;
   bool ok;
 };
+template <bool FULL>
 __device__ __noinline__ ProdRet run_produce(const Runtime *rt, Misc *misc, char *smem, int worker,
                                             int task, int batch, RingPos pos,
                                             unsigned long long policy) {
@@ -134,15 +139,24 @@ __device__ __noinline__ ProdRet run_produce(const Runtime *rt, Misc *misc, char 
   const ypk_task &t = misc->ptask;
   bool ok = true;
   if (t.type == YPK_TASK_LINEAR) {
-    ok = linear_uses_umma(*rt, t, batch) ? linear_produce_umma(wc, smem, misc, *rt, t, pos, policy)
-         : batch > kMaxBatch             ? linear_produce16(wc, smem, misc, t, batch, pos, policy)
-                                         : linear_produce(wc, smem, misc, t, batch, pos, policy);
+    if constexpr (FULL) {
+      ok = linear_uses_umma(*rt, t, batch) ? linear_produce_umma(wc, smem, misc, *rt, t, pos, policy)
+           : batch > kMaxBatch             ? linear_produce16(wc, smem, misc, t, batch, pos, policy)
+                                           : linear_produce(wc, smem, misc, t, batch, pos, policy);
+    } else {
+      ok = linear_produce(wc, smem, misc, t, batch, pos, policy);
+    }
   } else if (t.type == YPK_TASK_ATTENTION) {
     ok = attention_produce(wc, smem, misc, *rt, t, pos);
   }
   return ProdRet{pos, ok};
 }
 
+// FULL = false: the variant for one GPU and at most 8 tokens per iteration (the decode
+// headline): no all-reduce, no arg-max exchange, no pushes to peers, no 16-token or tcgen05
+// LINEAR paths, no TMEM.  Code generation at the 168-register cap is sensitive to every
+// function in the kernel, so what that configuration never runs is not compiled into it.
+template <bool FULL>
 __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_constant__ Runtime rt) {
   extern __shared__ __align__(1024) char smem[];
   Misc *misc = reinterpret_cast<Misc *>(smem + kOffMisc);
@@ -167,7 +181,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_
   }
   __syncthreads();
   // Accumulator columns of the tensor-core LINEAR path: taken once, for the kernel's lifetime.
-  if (rt.use_tmem) {
+  if (FULL && rt.use_tmem) {
     if (warp == 0) tmem_alloc(misc);
     tcgen05_before_sync();
     __syncthreads();
@@ -239,7 +253,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_
         wc.task = ti;
         const ypk_task &t = misc->ptask;
         if (t.type == YPK_TASK_LINEAR || t.type == YPK_TASK_ATTENTION) {
-          const ProdRet r = run_produce(&rt, misc, smem, worker, ti, batch, pos, policy);
+          const ProdRet r = run_produce<FULL>(&rt, misc, smem, worker, ti, batch, pos, policy);
           pos = r.pos;
           ok = r.ok;
         }
@@ -273,7 +287,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_
         if (prec) prec[2] = globaltimer();
         if (ok) {
           if (t.type == YPK_TASK_LINEAR) {
-            if (linear_uses_umma(rt, t, batch)) {
+            if (FULL && linear_uses_umma(rt, t, batch)) {
               const TaskRetU r =
                   run_linear_umma(&rt, misc, smem, worker, ti, wc.failed, batch, pos, ustate);
               pos = r.pos;
@@ -282,10 +296,10 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_
               ++umma_done;
             } else if (t.flags & (YPK_F_LL_IN | YPK_F_LL_RES | YPK_F_LL_OUT)) {
               const TaskRet r =
-                  run_linear_ll(&rt, misc, smem, worker, ti, wc.failed, batch, iter, pos);
+                  run_linear_ll<FULL>(&rt, misc, smem, worker, ti, wc.failed, batch, iter, pos);
               pos = r.pos;
               wc.failed = r.failed;
-            } else if (batch > kMaxBatch) {
+            } else if (FULL && batch > kMaxBatch) {
               const TaskRet r = run_linear16(&rt, misc, smem, worker, ti, wc.failed, batch, pos);
               pos = r.pos;
               wc.failed = r.failed;
@@ -299,7 +313,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_
             pos = r.pos;
             wc.failed = r.failed;
           } else {
-            wc.failed = run_small(&rt, misc, worker, ti, wc.failed, batch, iter);
+            wc.failed = run_small<FULL>(&rt, misc, worker, ti, wc.failed, batch, iter);
           }
           // a wait that gave up inside the task is known to one warp only: agree on it.
           if (wc.failed) misc->abort_flag = 1;
@@ -359,7 +373,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_
   }
   if (tid == 0 && tasks_done) atomicAdd(rt.ctrl + kCtrlTasksDone, (unsigned long long)tasks_done);
   if (tid == 0 && umma_done) atomicAdd(rt.ctrl + kCtrlUmmaTasks, (unsigned long long)umma_done);
-  if (rt.use_tmem) {
+  if (FULL && rt.use_tmem) {
     // After an abort the issuing thread can leave with MMAs in flight: wait (bounded) for
     // them before the columns are handed back.  On the normal path every task has waited.
     if (tid == 0 && ld_relaxed_u64(rt.ctrl + kCtrlAbort) != 0ull) {

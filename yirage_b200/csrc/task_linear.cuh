@@ -192,13 +192,13 @@ __device__ __forceinline__ float silu_mul_ref(float g, float u) {
 // epilogue loops run over peer x pair): one thread storing to the peers in turn pays the
 // address translation of each peer's mapping one after the other, about a microsecond each,
 // and the last peer in everybody's loop then runs that far behind the first.
-template <bool F16>
+template <bool F16, bool TP>
 __device__ __forceinline__ void ll_emit(const LinearArgs &a, const Runtime &rt, int b, int col,
                                         float v0, float v1, int peer) {
   const uint32_t packed = uint32_t(cvt_out<F16>(v0)) | (uint32_t(cvt_out<F16>(v1)) << 16);
   const size_t widx = size_t(b) * size_t(a.ldout >> 1) + size_t(col >> 1);
   const unsigned long long w = ll_word(packed, a.tag_out);
-  if (a.flags & YPK_F_LL_PUSH) {
+  if (TP && (a.flags & YPK_F_LL_PUSH)) {
     const size_t off = size_t(reinterpret_cast<char *>(a.ll_out) - rt.arena[rt.rank]) +
                        (size_t(rt.rank) * rt.max_tok * size_t(a.ldout >> 1) + widx) * 8;
     ll_store_sys(reinterpret_cast<unsigned long long *>(rt.arena[peer] + off), w);
@@ -212,7 +212,7 @@ __device__ __forceinline__ void ll_emit(const LinearArgs &a, const Runtime &rt, 
 // Flagged-word epilogue (YPK_F_LL_OUT).  Values come from the per-warp partial tiles
 // (`pall` = [8 warps][16 rows][8 tokens]) or, for a K-chunked task, from `accs`
 // ([rows][8 tokens]); two neighbouring result columns per thread.
-template <bool F16>
+template <bool F16, bool TP>
 __device__ __forceinline__ void linear_epilogue_ll(const LinearArgs &a, const Runtime &rt,
                                                 const Misc *misc, const uint16_t *res_s, int r0,
                                                 int nr, int b0, int bc, const float *pall,
@@ -226,7 +226,7 @@ __device__ __forceinline__ void linear_epilogue_ll(const LinearArgs &a, const Ru
     for (int w = 0; w < kConsumerWarps; ++w) s += pall[(w * kRowBlock + r) * kMaxBatch + b];
     return s;
   };
-  const int ncopy = (a.flags & YPK_F_LL_PUSH) ? rt.world : 1;
+  const int ncopy = (TP && (a.flags & YPK_F_LL_PUSH)) ? rt.world : 1;
   if (a.flags & YPK_F_SILU_MUL) {
     const int npair = nr >> 2;   // one 2 gate + 2 up granule = one pair of outputs
     for (int idx0 = tid; idx0 < npair * bc * ncopy; idx0 += kConsumerThreads) {
@@ -239,7 +239,7 @@ __device__ __forceinline__ void linear_epilogue_ll(const LinearArgs &a, const Ru
         g0 *= rn; g1 *= rn; u0 *= rn; u1 *= rn;
       }
       const int col = a.out_col0 + ((a.row0 + r0) >> 1) + g * kSiluGran;
-      ll_emit<F16>(a, rt, b0 + b, col, silu_mul_ref(g0, u0), silu_mul_ref(g1, u1), peer);
+      ll_emit<F16, TP>(a, rt, b0 + b, col, silu_mul_ref(g0, u0), silu_mul_ref(g1, u1), peer);
     }
   } else {
     const int npair = nr >> 1;
@@ -255,10 +255,10 @@ __device__ __forceinline__ void linear_epilogue_ll(const LinearArgs &a, const Ru
         v0 += cvt_one<F16>(res_s[b * a.nrows + r0 + r]);
         v1 += cvt_one<F16>(res_s[b * a.nrows + r0 + r + 1]);
       }
-      ll_emit<F16>(a, rt, b0 + b, a.out_col0 + a.row0 + r0 + r, v0, v1, peer);
+      ll_emit<F16, TP>(a, rt, b0 + b, a.out_col0 + a.row0 + r0 + r, v0, v1, peer);
     }
   }
-  if (rt.ll_push_fence && (a.flags & YPK_F_LL_PUSH)) asm volatile("fence.acq_rel.sys;" ::: "memory");
+  if (TP && rt.ll_push_fence && (a.flags & YPK_F_LL_PUSH)) asm volatile("fence.acq_rel.sys;" ::: "memory");
 }
 
 template <bool F16, typename ValFn>
@@ -397,7 +397,8 @@ __device__ __forceinline__ bool linear_stage_x_ll(WaitCtx &wc, const LinearArgs 
 
 // LL = the task uses the flagged-word hand-off somewhere (YPK_F_LL_*); the two instantiations
 // are separate out-of-line functions, so the event path compiles as if the other did not exist.
-template <bool F16, bool LL>
+// TP = the kernel variant that can push partial sums to peer GPUs (YPK_F_LL_PUSH).
+template <bool F16, bool LL, bool TP>
 __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Misc *misc,
                                                      const Runtime &rt, const LinearArgs &a,
                                                      int b0, int B, RingPos &pos) {
@@ -583,7 +584,7 @@ __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Mi
       };
       if (!chunked) {
         if (LL && (a.flags & YPK_F_LL_OUT)) {
-          if constexpr (LL) linear_epilogue_ll<F16>(a, rt, misc, res_s, r0, nr, b0, B, pall, nullptr);
+          if constexpr (LL) linear_epilogue_ll<F16, TP>(a, rt, misc, res_s, r0, nr, b0, B, pall, nullptr);
         } else {
           linear_epilogue<F16>(a, misc, res_s, r0, nr, b0, B, tid, summed);
         }
@@ -606,7 +607,7 @@ __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Mi
     }
     auto fromacc = [&](int r, int b) { return accs[r * kMaxBatch + b]; };
     if (LL && (a.flags & YPK_F_LL_OUT)) {
-      if constexpr (LL) linear_epilogue_ll<F16>(a, rt, misc, res_s, 0, a.nrows, b0, B, nullptr, accs);
+      if constexpr (LL) linear_epilogue_ll<F16, TP>(a, rt, misc, res_s, 0, a.nrows, b0, B, nullptr, accs);
     } else {
       linear_epilogue<F16>(a, misc, res_s, 0, a.nrows, b0, B, tid, fromacc);
     }
@@ -847,7 +848,7 @@ __device__ __forceinline__ void linear_consume_groups16(WaitCtx &wc, char *smem,
   }
 }
 
-template <bool LL>
+template <bool LL, bool TP>
 __device__ __forceinline__ void linear_consume_groups(WaitCtx &wc, char *smem, Misc *misc,
                                                       const Runtime &rt, const ypk_task &t,
                                                       int batch, long long iter, RingPos &pos) {
@@ -857,9 +858,9 @@ __device__ __forceinline__ void linear_consume_groups(WaitCtx &wc, char *smem, M
     const int b0 = bg * kMaxBatch;
     const int bc = min(kMaxBatch, batch - b0);
     if (a.flags & YPK_F_F16) {
-      linear_consume_group<true, LL>(wc, smem, misc, rt, a, b0, bc, pos);
+      linear_consume_group<true, LL, TP>(wc, smem, misc, rt, a, b0, bc, pos);
     } else {
-      linear_consume_group<false, LL>(wc, smem, misc, rt, a, b0, bc, pos);
+      linear_consume_group<false, LL, TP>(wc, smem, misc, rt, a, b0, bc, pos);
     }
     if (bg + 1 < nbg) consumer_bar();  // smem of this group is dead before the next one starts
   }

@@ -66,6 +66,7 @@ __device__ __forceinline__ void argmax_partial_task(const ypk_task &t, int batch
 // the slice's winner goes to every rank as two flagged words {value bits, tag}, {index, tag}
 // into slot `rank` of ptr[3] = [world][max_tokens][2] words (symmetric arena), and every rank
 // takes the best of the world slots, lowest index on ties, so all ranks sample the same token.
+template <bool TP>
 __device__ __forceinline__ bool argmax_reduce_task(WaitCtx &wc, const Runtime *rt, const ypk_task &t,
                                                    int batch, long long iter) {
   const uint16_t *pval = reinterpret_cast<const uint16_t *>(t.ptr[0]);
@@ -94,7 +95,7 @@ __device__ __forceinline__ bool argmax_reduce_task(WaitCtx &wc, const Runtime *r
         bidx = oi;
       }
     }
-    if (t.flags & YPK_F_LL_PUSH) {
+    if (TP && (t.flags & YPK_F_LL_PUSH)) {
       const int world = t.iarg[2], rank = t.iarg[3];
       const uint32_t tag = ll_tag(*rt, iter, t.iarg[12]);
       const size_t off = size_t(reinterpret_cast<char *>(t.ptr[3]) - rt->arena[rank]);
