@@ -99,7 +99,7 @@ __device__ __noinline__ TaskRet run_attention(const Runtime *rt, Misc *misc, cha
   attention_consume(wc, smem, misc, *rt, misc->ctask, iter, pos);
   return TaskRet{pos, wc.failed};
 }
-template <bool FULL>
+template <bool TP>
 __device__ __noinline__ bool run_small(const Runtime *rt, Misc *misc, int worker, int task,
                                        bool failed, int batch, long long iter) {
   WaitCtx wc{rt, misc, worker, task, failed};
@@ -108,13 +108,13 @@ __device__ __noinline__ bool run_small(const Runtime *rt, Misc *misc, int worker
     case YPK_TASK_EMBED: embed_task(t, batch); break;
     case YPK_TASK_ARGMAX_PARTIAL: argmax_partial_task(t, batch); break;
     case YPK_TASK_ARGMAX_REDUCE:
-      if (!argmax_reduce_task<FULL>(wc, rt, t, batch, iter)) wc.failed = true;
+      if (!argmax_reduce_task<TP>(wc, rt, t, batch, iter)) wc.failed = true;
       break;
     case YPK_TASK_RMSNORM: rmsnorm_task(t, batch); break;
     case YPK_TASK_SILU_MUL: silu_mul_task(t, batch); break;
     case YPK_TASK_ALLREDUCE:
-      if constexpr (!FULL) {
-        wc.failed = true;   // the single-GPU decode variant has no all-reduce (the host never picks it then)
+      if constexpr (!TP) {
+        wc.failed = true;   // single-GPU variants have no all-reduce (the host never picks them then)
       } else if (t.flags & YPK_F_LL_IN) {
         if (!allreduce_ll_task(wc, *rt, t, batch, iter)) wc.failed = true;
       } else if (!allreduce_task(wc, misc, *rt, t, batch, iter)) {
@@ -131,7 +131,7 @@ struct ProdRet {
   RingPos pos;
   bool ok;
 };
-template <bool FULL>
+template <bool WIDE>
 __device__ __noinline__ ProdRet run_produce(const Runtime *rt, Misc *misc, char *smem, int worker,
                                             int task, int batch, RingPos pos,
                                             unsigned long long policy) {
@@ -139,7 +139,7 @@ __device__ __noinline__ ProdRet run_produce(const Runtime *rt, Misc *misc, char 
   const ypk_task &t = misc->ptask;
   bool ok = true;
   if (t.type == YPK_TASK_LINEAR) {
-    if constexpr (FULL) {
+    if constexpr (WIDE) {
       ok = linear_uses_umma(*rt, t, batch) ? linear_produce_umma(wc, smem, misc, *rt, t, pos, policy)
            : batch > kMaxBatch             ? linear_produce16(wc, smem, misc, t, batch, pos, policy)
                                            : linear_produce(wc, smem, misc, t, batch, pos, policy);
@@ -152,11 +152,13 @@ __device__ __noinline__ ProdRet run_produce(const Runtime *rt, Misc *misc, char 
   return ProdRet{pos, ok};
 }
 
-// FULL = false: the variant for one GPU and at most 8 tokens per iteration (the decode
-// headline): no all-reduce, no arg-max exchange, no pushes to peers, no 16-token or tcgen05
-// LINEAR paths, no TMEM.  Code generation at the 168-register cap is sensitive to every
-// function in the kernel, so what that configuration never runs is not compiled into it.
-template <bool FULL>
+// Kernel variants.  TP: tensor-parallel code (all-reduce tasks, arg-max exchange, pushes of
+// partial sums to peers).  WIDE: more than 8 tokens per iteration (16-token and tcgen05
+// LINEAR paths, TMEM).  Code generation at the 168-register cap is sensitive to every
+// function in the kernel (an edit to a path that a configuration never runs moved batch-1
+// decode by 2-4 %), so what a configuration cannot run is not compiled into its variant:
+// <false, false> one GPU decode, <true, false> tensor-parallel decode, <true, true> the rest.
+template <bool TP, bool WIDE>
 __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_constant__ Runtime rt) {
   extern __shared__ __align__(1024) char smem[];
   Misc *misc = reinterpret_cast<Misc *>(smem + kOffMisc);
@@ -181,7 +183,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_
   }
   __syncthreads();
   // Accumulator columns of the tensor-core LINEAR path: taken once, for the kernel's lifetime.
-  if (FULL && rt.use_tmem) {
+  if (WIDE && rt.use_tmem) {
     if (warp == 0) tmem_alloc(misc);
     tcgen05_before_sync();
     __syncthreads();
@@ -253,7 +255,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_
         wc.task = ti;
         const ypk_task &t = misc->ptask;
         if (t.type == YPK_TASK_LINEAR || t.type == YPK_TASK_ATTENTION) {
-          const ProdRet r = run_produce<FULL>(&rt, misc, smem, worker, ti, batch, pos, policy);
+          const ProdRet r = run_produce<WIDE>(&rt, misc, smem, worker, ti, batch, pos, policy);
           pos = r.pos;
           ok = r.ok;
         }
@@ -287,7 +289,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_
         if (prec) prec[2] = globaltimer();
         if (ok) {
           if (t.type == YPK_TASK_LINEAR) {
-            if (FULL && linear_uses_umma(rt, t, batch)) {
+            if (WIDE && linear_uses_umma(rt, t, batch)) {
               const TaskRetU r =
                   run_linear_umma(&rt, misc, smem, worker, ti, wc.failed, batch, pos, ustate);
               pos = r.pos;
@@ -296,10 +298,10 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_
               ++umma_done;
             } else if (t.flags & (YPK_F_LL_IN | YPK_F_LL_RES | YPK_F_LL_OUT)) {
               const TaskRet r =
-                  run_linear_ll<FULL>(&rt, misc, smem, worker, ti, wc.failed, batch, iter, pos);
+                  run_linear_ll<TP>(&rt, misc, smem, worker, ti, wc.failed, batch, iter, pos);
               pos = r.pos;
               wc.failed = r.failed;
-            } else if (FULL && batch > kMaxBatch) {
+            } else if (WIDE && batch > kMaxBatch) {
               const TaskRet r = run_linear16(&rt, misc, smem, worker, ti, wc.failed, batch, pos);
               pos = r.pos;
               wc.failed = r.failed;
@@ -313,7 +315,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_
             pos = r.pos;
             wc.failed = r.failed;
           } else {
-            wc.failed = run_small<FULL>(&rt, misc, worker, ti, wc.failed, batch, iter);
+            wc.failed = run_small<TP>(&rt, misc, worker, ti, wc.failed, batch, iter);
           }
           // a wait that gave up inside the task is known to one warp only: agree on it.
           if (wc.failed) misc->abort_flag = 1;
@@ -373,7 +375,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_
   }
   if (tid == 0 && tasks_done) atomicAdd(rt.ctrl + kCtrlTasksDone, (unsigned long long)tasks_done);
   if (tid == 0 && umma_done) atomicAdd(rt.ctrl + kCtrlUmmaTasks, (unsigned long long)umma_done);
-  if (FULL && rt.use_tmem) {
+  if (WIDE && rt.use_tmem) {
     // After an abort the issuing thread can leave with MMAs in flight: wait (bounded) for
     // them before the columns are handed back.  On the normal path every task has waited.
     if (tid == 0 && ld_relaxed_u64(rt.ctrl + kCtrlAbort) != 0ull) {

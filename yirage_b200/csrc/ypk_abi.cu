@@ -477,20 +477,18 @@ int ypk_create(const ypk_config *cfg, ypk_handle **out) {
     delete h;
     return rc;
   }
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(ypk_megakernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemBytes);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(ypk_megakernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemBytes);
-  int per_sm = 0, per_sm_decode = 0;
-  if (e == cudaSuccess)
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ypk_megakernel<true>, kBlockThreads,
-                                                      kSmemBytes);
-  if (e == cudaSuccess)
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_decode, ypk_megakernel<false>,
-                                                      kBlockThreads, kSmemBytes);
-  per_sm = std::min(per_sm, per_sm_decode);
+  const void *variants[3] = {(const void *)ypk_megakernel<false, false>,
+                             (const void *)ypk_megakernel<true, false>,
+                             (const void *)ypk_megakernel<true, true>};
+  int per_sm = 1 << 30;
+  for (const void *k : variants) {
+    int n = 0;
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k, kBlockThreads, kSmemBytes);
+    per_sm = std::min(per_sm, n);
+  }
   if (e != cudaSuccess || per_sm < 1) {
     int rc = fail(nullptr, YPK_ERR_CUDA, "megakernel cannot be made resident: %s",
                   e != cudaSuccess ? cudaGetErrorString(e) : "0 blocks per SM");
@@ -983,10 +981,11 @@ int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_
   void *args[] = {&rt};
   // Workers wait on each other, so they must all be resident: a cooperative launch
   // refuses to start otherwise instead of deadlocking.
-  // One GPU and at most 8 tokens per iteration: the decode variant, which carries none of the
-  // tensor-parallel, 16-token and tcgen05 code.
-  const bool full = c.world_size > 1 || c.max_num_batched_tokens > kMaxBatch;
-  const void *kernel = full ? (const void *)ypk_megakernel<true> : (const void *)ypk_megakernel<false>;
+  // The variant that carries no code this configuration cannot run (see ypk_megakernel).
+  const bool wide = c.max_num_batched_tokens > kMaxBatch, tp = c.world_size > 1;
+  const void *kernel = wide ? (const void *)ypk_megakernel<true, true>
+                       : tp ? (const void *)ypk_megakernel<true, false>
+                            : (const void *)ypk_megakernel<false, false>;
   CUDA_TRY(h, cudaLaunchCooperativeKernel(kernel, dim3(h->num_workers),
                                           dim3(kBlockThreads), args, kSmemBytes, st));
   h->stream = st;
