@@ -225,3 +225,31 @@ def test_kernel_graph_matching():
         with pytest.raises(RuntimeError, match="no CPU execution path"):
             g.superoptimize()(inputs=[torch.zeros(8, 4096, dtype=torch.float16),
                                       torch.zeros(4096, 4096, dtype=torch.float16)])
+
+
+def test_70b_shape_lowers_and_validates_under_tp8():
+    """BASELINE's 70B shape (hidden 8192, 64 q / 8 kv heads, FFN 28672) sharded 8 ways, one
+    layer and a small vocabulary: grid hints divide the sharded dimensions, the residual
+    stream (8192 wide) still travels as flagged words, one kv head per rank, and the native
+    library accepts the graph on a host-only handle."""
+    shape = llama.LlamaShape(hidden_size=8192, intermediate_size=28672, num_hidden_layers=1,
+                             num_attention_heads=64, num_key_value_heads=8, vocab_size=16384)
+    w = llama.init_weights(shape, "cpu", 0, world_size=8, rank=3)
+    tokens = torch.zeros(1, 128, dtype=torch.int64)
+    pl = torch.tensor([40], dtype=torch.int32)
+    ypk, _ = llama.build_decode_kernel(shape, w, tokens=tokens, prompt_lengths=pl,
+                                       max_num_batched_requests=1, max_num_batched_tokens=8,
+                                       max_num_pages=2, page_size=64, world_size=8, rank=3,
+                                       compile=False)
+    g = ypk.lower(148)
+    assert set(lowering.simulate(g, 2)) == {2}
+    kinds = [o.kind for o in g.ops]
+    assert kinds.count("allreduce") == 2 and kinds.count("attention") == 1
+    att = [t for t in g.tasks if t.type == N.TASK_ATTENTION]
+    assert {t.iarg[4] for t in att} == {8} and {t.iarg[5] for t in att} == {1}
+    gate_up = [t for t in g.tasks if t.op_id == kinds.index("allreduce") + 1][0]
+    assert gate_up.flags & N.F_LL_IN and gate_up.iarg[0] == 8192
+    red = [t for t in g.tasks if t.type == N.TASK_ARGMAX_REDUCE][0]
+    assert red.flags & N.F_LL_PUSH and red.iarg[1] == 3 * (llama.padded_vocab(16384) // 8)
+    ypk.compile(dry_run=True, defer_connect=True)
+    ypk.finalize()
