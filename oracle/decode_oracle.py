@@ -11,10 +11,14 @@ What can run here is the reference's PyTorch model code
 (demo/llama3/models/modeling_llama3.py): Llama3RMSNorm, Llama3MLP, naive_attention,
 Llama3RotaryEmbedding.  tests/golden/make_golden.py imports those from the reference tree,
 runs them on seeded inputs and stores inputs+outputs under tests/golden/; the tests check
-this oracle against those fixtures.  Pieces with no runnable reference counterpart on a
-CPU - the rotate-half RoPE application (a triton kernel in the reference), the paged-KV
-indexing and the continuous batcher (CUDA only) - are "parity unpinned": they follow the
-cited source by reading only.
+this oracle against those fixtures.  The same script also covers what has a counterpart on a
+CPU: the rotate-half RoPE application, the paged-KV indexing with its in-place K update, the
+causal window among several new tokens and the q/k RMSNorm inside attention are pinned by
+the torch functions the reference's own kernel tests compare against
+(tests/runtime_python/test_paged_attention.py, test_multitoken_paged_attention.py,
+test_decoding_w_norm.py), whose definitions make_golden.py takes out of those scripts and
+runs on CPU.  Still "parity unpinned" (CUDA-only in the reference, followed by reading): the
+continuous batcher, the all-reduce order and the arg-max tie order.
 
 `rounding="bf16"` reproduces the rounding points of the reference's bf16 pipeline (every
 operator output rounded to bf16); `rounding=None` keeps fp32 throughout and is the fp32
@@ -290,17 +294,24 @@ class LlamaWeights:
 
 
 def paged_attention_step(q, k_new, v_new, k_cache, v_cache, pages, seq_len, page_size,
-                         num_q_heads, num_kv_heads, cos, sin, rounding="bf16"):
+                         num_q_heads, num_kv_heads, cos, sin, rounding="bf16",
+                         q_norm_w=None, k_norm_w=None, qk_eps=1e-6):
     """Attention of T new tokens of one request against its paged cache, updating the cache
     in place.  q: [T, Hq, d]; k_new, v_new: [T, Hkv, d]; caches: [pages, page_size, Hkv, d];
     `pages` the request's page list; seq_len counts the new tokens
     (tests/runtime_python/test_multitoken_paged_attention.py:51-122 for the in-place update
-    and causal windows; attention_sm100.cuh:86-102,254-269,412-427 for the indexing)."""
+    and causal windows; attention_sm100.cuh:86-102,254-269,412-427 for the indexing).
+    q_norm_w / k_norm_w [d]: RMSNorm over the head dimension of every new q head and of the
+    new k before the rotation, its result rounded like an operator output (Qwen3;
+    attention_sm100.cuh:349-379, norm_sm100.cuh; test_decoding_w_norm.py:38-72)."""
     T = q.shape[0]
     G = num_q_heads // num_kv_heads
     pos0 = seq_len - T
     out = torch.zeros(T, num_q_heads, q.shape[-1])
     positions = torch.arange(pos0, seq_len)
+    if q_norm_w is not None:
+        q = rmsnorm(q, q_norm_w.reshape(-1), qk_eps, rounding)
+        k_new = rmsnorm(k_new, k_norm_w.reshape(-1), qk_eps, rounding)
     if cos is not None:
         c, s = cos[positions][:, None, :], sin[positions][:, None, :]
         q = apply_rope(q, c, s, rounding)
@@ -353,7 +364,9 @@ def decode_iteration(w: LlamaWeights, bs: BatchState, k_caches, v_caches, cos, s
             seq_len = (kv1 - kv0 - 1) * bs.page_size + bs.kv_last_len[i]
             attn[a:b] = paged_attention_step(q[a:b], k[a:b], v[a:b], k_caches[li], v_caches[li],
                                              pages, seq_len, bs.page_size, w.num_q_heads,
-                                             w.num_kv_heads, cos, sin, rounding)
+                                             w.num_kv_heads, cos, sin, rounding,
+                                             q_norm_w=L.get("q_norm"), k_norm_w=L.get("k_norm"),
+                                             qk_eps=w.eps)
         x = linear(attn.reshape(ntok, -1), L["o"], residual=x, rounding=rounding)
         h = rmsnorm(x, L["post_norm"], w.eps, rounding)
         g = linear(h, L["gate"], rounding=rounding)

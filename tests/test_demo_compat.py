@@ -12,7 +12,9 @@ import types
 import pytest
 import torch
 
-REF = "/root/reference"
+# where the reference tree is mounted: YIRAGE_REFERENCE_ROOT, else <parent of the repo>/reference
+REF = os.environ.get("YIRAGE_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 DEMO = os.path.join(REF, "demo", "llama3", "demo.py")
 
 pytestmark = pytest.mark.skipif(not os.path.exists(DEMO), reason="reference tree not mounted")

@@ -64,9 +64,90 @@ def test_prefill_attention_causal_window_matches_reference_sdpa():
         assert O.within_tolerance(out, g["out"][:, h * 4:(h + 1) * 4].float())[0]
 
 
+def test_rope_application_matches_reference_test_function():
+    """apply_rotary_pos_emb of the reference's kernel tests (test_paged_attention.py:18-34)
+    on random cos/sin rows whose halves differ: same values after the one bf16 rounding."""
+    g = load("rope_apply.pt")
+    c, s = g["cos"][:, None, :], g["sin"][:, None, :]
+    assert torch.equal(O.apply_rope(g["q"], c, s, "bf16").to(torch.bfloat16), g["q_out"])
+    assert torch.equal(O.apply_rope(g["k"], c, s, "bf16").to(torch.bfloat16), g["k_out"])
+
+
+def _scatter(rows, pages, page_size, num_pages):
+    """Position-ordered rows [seq, d] -> a paged cache [pages, page_size, 1, d]."""
+    cache = torch.zeros(num_pages, page_size, 1, rows.shape[-1], dtype=rows.dtype)
+    for p in range(rows.shape[0]):
+        cache[int(pages[p // page_size]), p % page_size, 0] = rows[p]
+    return cache
+
+
+def test_paged_attention_matches_reference_test_function():
+    """torch_paged_attention (test_paged_attention.py:48-94): one new token against a cache
+    in a permuted page order, lengths on either side of a page boundary and a last page that
+    is exactly full; with the q/k RMSNorm of Qwen3 in three of the cases.  The rotated
+    (normed) K that lands in the page is compared bit for bit, the output within tolerance
+    (the reference function multiplies and normalises in bf16)."""
+    g = load("paged_attention_decode.pt")
+    PS, pages = g["page_size"], g["pages"].tolist()
+    assert {c["seq_len"] for c in g["cases"]} >= {63, 64, 65, 128}
+    for c in g["cases"]:
+        L = c["seq_len"]
+        kc = _scatter(c["k_rows"], pages, PS, 16)
+        vc = _scatter(c["v_rows"], pages, PS, 16)
+        qkv = c["qkv"].float()
+        cos = torch.zeros(L, 128, dtype=torch.bfloat16)
+        sin = torch.zeros(L, 128, dtype=torch.bfloat16)
+        cos[L - 1], sin[L - 1] = c["cos_row"], c["sin_row"]
+        norm = dict(q_norm_w=c["q_norm_w"], k_norm_w=c["k_norm_w"], qk_eps=c["eps"]) if c["qk_norm"] else {}
+        out = O.paged_attention_step(qkv[None, :4], qkv[None, 4:5], qkv[None, 5:6], kc, vc,
+                                     pages[:(L + PS - 1) // PS], L, PS, 4, 1, cos, sin, "bf16", **norm)
+        slot = kc[pages[(L - 1) // PS], (L - 1) % PS, 0]
+        assert torch.equal(slot, c["k_new_after"]), f"seq_len {L}: appended K differs"
+        ok, max_abs, _ = O.within_tolerance(out[0], c["out"].float())
+        assert ok, f"seq_len {L} qk_norm {c['qk_norm']}: max abs err {max_abs}"
+
+
+def test_multitoken_paged_attention_matches_reference_test_function():
+    """torch_multitoken_paged_attention (test_multitoken_paged_attention.py:51-122): several
+    new tokens of one request, K updated in place in the page, causal among the new tokens."""
+    g = load("paged_attention_multitoken.pt")
+    PS = g["page_size"]
+    for c in g["cases"]:
+        T, cached = c["num_tokens"], c["cached"]
+        L = T + cached
+        pages = c["pages"].tolist()
+        kc = _scatter(c["k_rows"], pages, PS, 16)
+        vc = _scatter(c["v_rows"], pages, PS, 16)
+        qkv = c["qkv"].float().view(T, 6, 128)
+        norm = dict(q_norm_w=c["q_norm_w"], k_norm_w=c["k_norm_w"], qk_eps=c["eps"]) if c["qk_norm"] else {}
+        out = O.paged_attention_step(qkv[:, :4], qkv[:, 4:5], qkv[:, 5:6], kc, vc, pages, L, PS, 4, 1,
+                                     c["cos"], c["sin"], "bf16", **norm)
+        want_k = _scatter(c["k_rows_after"], pages, PS, 16)
+        assert torch.equal(kc, want_k), f"cached {cached} + {T}: K cache after the update differs"
+        ok, max_abs, _ = O.within_tolerance(out, c["out"].float())
+        assert ok, f"cached {cached} + {T} qk_norm {c['qk_norm']}: max abs err {max_abs}"
+
+
+def test_decode_attention_with_qk_norm_matches_reference_test_function():
+    """attention_decode (test_decoding_w_norm.py:55-72): RMSNorm of q and of the new k over the
+    head dimension, then the rotation, contiguous cache."""
+    g = load("decode_attention_qknorm.pt")
+    for c in g["cases"]:
+        L = c["valid_len"]
+        kc, vc = c["k_cache"][None, :, None, :].clone(), c["v_cache"][None, :, None, :].clone()
+        PS = kc.shape[1]
+        cos = torch.zeros(L, 128, dtype=torch.bfloat16)
+        sin = torch.zeros(L, 128, dtype=torch.bfloat16)
+        cos[L - 1], sin[L - 1] = c["cos"], c["sin"]
+        out = O.paged_attention_step(c["q"].float()[None], kc[0, L - 1:L, :, :].float(),
+                                     vc[0, L - 1:L, :, :].float(), kc, vc, [0], L, PS, 4, 1, cos, sin,
+                                     "bf16", q_norm_w=c["q_norm_w"], k_norm_w=c["k_norm_w"], qk_eps=c["eps"])
+        assert torch.equal(kc[0, L - 1, 0], c["k_new_after"])
+        assert O.within_tolerance(out[0], c["out"].float())[0]
+
+
 def test_paged_attention_step_equals_contiguous_attention():
-    """Paged indexing + in-place append against the contiguous formulation on the same data
-    (no reference fixture exists for the paged path: parity unpinned, consistency only)."""
+    """Paged indexing + in-place append against the contiguous formulation on the same data."""
     gen = torch.Generator().manual_seed(7)
     hq, hkv, d, page, L, T = 8, 2, 128, 64, 150, 3
     pages = [5, 1, 3]
