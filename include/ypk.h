@@ -76,6 +76,8 @@ enum ypk_task_type {
 #define YPK_F_SILU_MUL 0x4u    /* LINEAR: rows come as 2 gate + 2 up       */
 #define YPK_F_F16 0x8u         /* operands are fp16 instead of bf16        */
 #define YPK_F_ROPE 0x10u       /* ATTENTION: rotate new q/k                */
+#define YPK_F_QK_NORM 0x20u    /* ATTENTION: RMSNorm of every new q head and of the new k over
+                                  the head dimension, before the rotation (Qwen3)          */
 #define YPK_F_NORM_NOWEIGHT 0x40u /* LINEAR: RMSNorm without a weight      */
 /* Flagged-word hand-off between tasks (no event, no fence): a [tokens][ld] tensor of 16-bit
  * values travels as [max_tokens][ld / 2] 8-byte words {two values, 32-bit tag}; the tag
@@ -109,23 +111,28 @@ enum ypk_task_type {
  *                  of the producers of x and of the residual, and this operator's own
  *          farg = {eps}
  * EMBED:   ptr = {ids(int64), table, out}; iarg = {hidden, col0, ncols,
- *                  ldtable, ldout}
- * ATTENTION: ptr = {qkv, k_cache, v_cache, out, cos, sin, scratch, counters}
+ *                  ldtable, ldout, rows of the table}; an id outside [0, rows) gives zeros
+ * ATTENTION: ptr = {qkv, k_cache, v_cache, out, cos, sin, split scratch, qk-norm weights};
+ *          with YPK_F_QK_NORM ptr[7] = [2][128] 16-bit weights (q heads, then k) and
+ *          farg = {eps}
  *          iarg = {request, kv_head, split, nsplit, q_per_kv, num_kv_heads,
  *                  ld_qkv, ld_out, max_rows}; iarg[9], iarg[10] are filled in by
  *                  ypk_load_graph (TMA tensor maps of the two caches); with YPK_F_LL_IN
  *                  qkv is the flagged-word form and iarg[11] its producer's tag id, with
  *                  YPK_F_LL_OUT out is written as flagged words under tag id iarg[12]
  * ARGMAX_PARTIAL: ptr = {logits, part_val, part_idx}; iarg = {col0, ncols,
- *                  ldlogits, part, nparts}
+ *                  ldlogits, part, nparts, valid}; valid != 0: only columns [0, valid) of a
+ *                  logits row can be sampled (the rest pads the lm_head; negative: none)
  * ARGMAX_REDUCE: ptr = {part_val, part_idx, out(int64)}; iarg = {nparts}; with
  *          YPK_F_LL_PUSH (vocabulary split over the ranks) ptr[3] = exchange buffer
  *          [world][max_tokens][2] flagged words in the symmetric arena, iarg = {nparts,
  *          first vocabulary row of this rank's slice, world, rank}, iarg[12] = tag id
  * ALLREDUCE: ptr = {in, buf, out, signals} (buf, signals from the symmetric arena;
  *          buf = [2][world][max_tokens][hidden] 16-bit, signals uint64[])
- *          iarg = {col0, ncols, ld_in, ld_out, hidden, max_tokens, half, signal index,
- *                  world, rank}; with YPK_F_LL_IN | YPK_F_LL_OUT: buf = [world][max_tokens]
+ *          iarg = {col0, ncols, ld_in, ld_out, hidden, max_tokens, index of this all-reduce
+ *                  among those of the iteration, signal index, world, rank, all-reduces per
+ *                  iteration} (the half of buf is the parity of the running all-reduce
+ *                  number); with YPK_F_LL_IN | YPK_F_LL_OUT: buf = [world][max_tokens]
  *                  [hidden / 2] flagged words pushed by the producing LINEAR tasks,
  *                  ptr[7] = flagged-word copy of out, iarg[10] / iarg[12] = tag ids of the
  *                  producer / of this operator, no signals
@@ -187,7 +194,10 @@ typedef struct ypk_status {
   int32_t error;          /* 0 or a ypk_error raised on the device          */
   int32_t fail_worker;    /* CTA that gave up                               */
   int32_t fail_task;      /* task index it was on (-1 if none)              */
-  int32_t fail_event;     /* event it waited for (-1 if none)               */
+  int32_t fail_event;     /* event it waited for (-1 if none); negative codes:
+                             -2 shared-memory ring barrier, -3 iteration word,
+                             -5 all-reduce arrivals, -6 flagged word,
+                             -7 (error YPK_ERR_STATE) the KV page pool ran out */
   int64_t iterations;     /* iterations completed since create/reset        */
   int32_t finished;       /* 1 when every request has retired               */
   int32_t active_tokens;  /* tokens in the batch that is pending            */
@@ -247,7 +257,9 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks,
                    int32_t num_queues);
 
 /* init_kernel (persistent_kernel.cuh:107-132): zero step[], request slots,
- * refill the free-page queue. */
+ * refill the free-page queue.  Also clears a device error (ypk_status.error) of a
+ * single-GPU handle; a tensor-parallel handle that has seen a device error cannot be
+ * reset (YPK_ERR_STATE): destroy the handles of all ranks and create them again. */
 int ypk_reset(ypk_handle *h);
 
 /* launch_persistent_kernel: run the megakernel on `stream` (a cudaStream_t,

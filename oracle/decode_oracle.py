@@ -242,6 +242,8 @@ class BatchState:
                 self.input_tokens[ntok + j] = int(self.tokens[req, step + j])
             total = step + nnew
             need = (total + PS - 1) // PS
+            if need > nold and (self.tail - self.head < need - nold or npages + need > MP):
+                raise RuntimeError("KV page pool exhausted")   # the device raises YPK_ERR_STATE
             for j in range(nold, need):
                 self.kv_indices[npages + j] = self.page_queue[self.head % MP]
                 self.head += 1

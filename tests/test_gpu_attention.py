@@ -14,7 +14,7 @@ D = 128
 
 
 def run_attention(seq_lens, new_tokens, *, hq=8, hkv=2, page_size=64, max_seq=None, seed=0,
-                  theta=500000.0):
+                  theta=500000.0, qk_norm=False, eps=1e-6):
     R = len(seq_lens)
     G = hq // hkv
     MT = max(8, sum(new_tokens))
@@ -46,9 +46,14 @@ def run_attention(seq_lens, new_tokens, *, hq=8, hkv=2, page_size=64, max_seq=No
 
     ypk = onepass_kernel(MT, meta, max_requests=R, max_pages=max_pages, page_size=page_size,
                          max_seq_length=max_seq)
+    qn = kn = qn_t = kn_t = None
+    if qk_norm:
+        qn, kn = randn((D,), seed + 4, 0.2, mean=1.0), randn((D,), seed + 5, 0.2, mean=1.0)
+        qn_t, kn_t = ypk.attach_input(qn, "q_norm"), ypk.attach_input(kn, "k_norm")
+        ypk.rms_norm_eps = eps
     ypk.paged_attention_layer(
         ypk.attach_input(qkv, "qkv"), ypk.attach_input(kc, "kc"), ypk.attach_input(vc, "vc"),
-        None, None, ypk.attach_input(cos, "cos"), ypk.attach_input(sin, "sin"),
+        qn_t, kn_t, ypk.attach_input(cos, "cos"), ypk.attach_input(sin, "sin"),
         ypk.attach_input(out, "out"), (R, hkv, 1), (128, 1, 1))
     ypk.compile()
     ypk(batch=qo[-1])
@@ -65,8 +70,9 @@ def run_attention(seq_lens, new_tokens, *, hq=8, hkv=2, page_size=64, max_seq=No
         q = qkv_c[a:b, :, :G].reshape(b - a, hq, D)
         k = qkv_c[a:b, :, G]
         v = qkv_c[a:b, :, G + 1]
+        norm = dict(q_norm_w=qn.cpu(), k_norm_w=kn.cpu(), qk_eps=eps) if qk_norm else {}
         want = O.paged_attention_step(q, k, v, kref, vref, idx[kvp[r]:kvp[r + 1]], seq_lens[r],
-                                      page_size, hq, hkv, cos.cpu(), sin.cpu(), rounding="bf16")
+                                      page_size, hq, hkv, cos.cpu(), sin.cpu(), rounding="bf16", **norm)
         assert_close(out[a:b].view(b - a, hq, D), want, f"request {r} (len {seq_lens[r]})")
     # new V rows land bit-exactly in their slots, new K within tolerance, nothing else moves
     assert torch.equal(vc.cpu(), vref), "V cache: paged indexing of the append is wrong"
@@ -105,3 +111,118 @@ def test_config3_shape_reduced_context():
     # BASELINE config 3 layout (batch 8, 32 q / 8 kv heads, 64-token pages, theta 5e5) at a
     # context the CPU oracle finishes quickly
     run_attention([513] * 8, [1] * 8, hq=32, hkv=8, seed=2)
+
+
+def test_config3_full_context_4096():
+    """BASELINE config 3 as stated: batch 8, 32 q / 8 kv heads, KV length 4096 in 64-token pages
+    in a seeded random page order, RoPE theta 5e5 on the new token at position 4096."""
+    nsplit = run_attention([4097] * 8, [1] * 8, hq=32, hkv=8, seed=2, max_seq=4098)
+    assert nsplit >= 2
+
+
+def test_qk_norm_decode_and_prefill_chunks():
+    """q/k RMSNorm inside attention (Qwen3): decode rows and multi-token chunks, page
+    boundaries, split-KV."""
+    run_attention([1, 64, 65, 200], [1, 1, 1, 1], hq=8, hkv=2, seed=10, qk_norm=True)
+    run_attention([9, 70, 133], [8, 6, 5], hq=8, hkv=2, seed=11, qk_norm=True, eps=1e-5)
+    run_attention([900], [1], hq=16, hkv=2, seed=12, qk_norm=True, max_seq=1024)
+
+
+# ---- against outputs of the reference's own torch functions (tests/golden, written by
+# ---- tests/golden/make_golden.py from tests/runtime_python/test_*paged_attention.py)
+def _golden(name):
+    import os
+    return torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", name))
+
+
+def _run_fixture_case(qkv_rows, k_rows, v_rows, pages, seq_len, T, cos_tab, sin_tab, qw, kw, eps,
+                      page_size=64, num_pages=16):
+    """One request of the fixture layout (4 q heads, 1 kv head) through the attention task.
+    Returns (out [T, 4, 128], K cache after the call [pages, page, 1, 128])."""
+    MT = 8
+    kc = torch.zeros(num_pages, page_size, 1, D, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    for p in range(seq_len):
+        kc[int(pages[p // page_size]), p % page_size, 0] = k_rows[p]
+        vc[int(pages[p // page_size]), p % page_size, 0] = v_rows[p]
+    kc, vc = kc.cuda(), vc.cuda()
+    npages = (seq_len + page_size - 1) // page_size
+    i32 = dict(dtype=torch.int32, device="cuda")
+    meta = {"qo_indptr_buffer": torch.tensor([0, T], **i32),
+            "paged_kv_indptr_buffer": torch.tensor([0, npages], **i32),
+            "paged_kv_indices_buffer": torch.tensor([int(p) for p in pages[:npages]] + [0] * (num_pages - npages), **i32),
+            "paged_kv_last_page_len_buffer": torch.tensor([(seq_len - 1) % page_size + 1], **i32)}
+    qkv = torch.zeros(MT, 6 * D, dtype=torch.bfloat16)
+    qkv[:T] = qkv_rows.reshape(T, 6 * D)
+    qkv = qkv.cuda()
+    out = torch.zeros(MT, 4 * D, dtype=torch.bfloat16, device="cuda")
+    ypk = onepass_kernel(MT, meta, max_requests=1, max_pages=num_pages, page_size=page_size,
+                         max_seq_length=max(seq_len + 1, 64))
+    qn_t = kn_t = None
+    if qw is not None:
+        qn_t = ypk.attach_input(qw.reshape(-1).cuda(), "q_norm")
+        kn_t = ypk.attach_input(kw.reshape(-1).cuda(), "k_norm")
+        ypk.rms_norm_eps = eps
+    ypk.paged_attention_layer(
+        ypk.attach_input(qkv, "qkv"), ypk.attach_input(kc, "kc"), ypk.attach_input(vc, "vc"),
+        qn_t, kn_t, ypk.attach_input(cos_tab.cuda(), "cos"), ypk.attach_input(sin_tab.cuda(), "sin"),
+        ypk.attach_input(out, "out"), (1, 1, 1), (128, 1, 1))
+    ypk.compile()
+    ypk(batch=T)
+    torch.cuda.synchronize()
+    res = out[:T].view(T, 4, D).cpu(), kc.cpu()
+    ypk.finalize()
+    return res
+
+
+def _same_k(got, want, normed, what):
+    """The K written to the page against the reference function's.  Rotation alone is three
+    fp32 operations with the same rounding points on both sides: bit for bit.  With the
+    RMSNorm in front the reciprocal square root and the order of the 128-term sum differ in
+    the last fp32 bit, which can move a value across a bf16 rounding boundary: one bf16 step."""
+    if not normed:
+        assert torch.equal(got, want), f"{what}: appended K differs from the reference's"
+        return
+    g, w = got.float(), want.float()
+    step = torch.maximum(w.abs(), torch.tensor(1e-30)).log2().floor().exp2() * 2.0 ** -7
+    assert bool(((g - w).abs() <= step).all()), f"{what}: appended K more than one bf16 step off"
+    assert float((g != w).float().mean()) < 0.05, f"{what}: too many K values differ"
+
+
+def test_decode_matches_reference_torch_paged_attention():
+    """torch_paged_attention (test_paged_attention.py:48-94) on the committed inputs: the
+    appended K bit for bit, the output within tolerance; lengths 63/64/65, a full last page,
+    a permuted page list, with and without q/k RMSNorm."""
+    g = _golden("paged_attention_decode.pt")
+    pages = g["pages"].tolist()
+    for c in g["cases"]:
+        L = c["seq_len"]
+        cos = torch.zeros(max(L, 64), D, dtype=torch.bfloat16)
+        sin = torch.zeros_like(cos)
+        cos[L - 1], sin[L - 1] = c["cos_row"], c["sin_row"]
+        qw, kw = (c["q_norm_w"], c["k_norm_w"]) if c["qk_norm"] else (None, None)
+        out, kc = _run_fixture_case(c["qkv"][None], c["k_rows"], c["v_rows"], pages, L, 1, cos, sin,
+                                    qw, kw, c["eps"])
+        slot = kc[pages[(L - 1) // 64], (L - 1) % 64, 0]
+        _same_k(slot, c["k_new_after"], c["qk_norm"], f"seq_len {L}")
+        assert_close(out[0], c["out"][0], f"seq_len {L} qk_norm {c['qk_norm']}")
+
+
+def test_chunks_match_reference_torch_multitoken_paged_attention():
+    """torch_multitoken_paged_attention (test_multitoken_paged_attention.py:51-122): several new
+    tokens, K updated in place in the page, causal among the new tokens."""
+    g = _golden("paged_attention_multitoken.pt")
+    for c in g["cases"]:
+        T, L = c["num_tokens"], c["num_tokens"] + c["cached"]
+        pages = c["pages"].tolist() + [0] * 16
+        cos = torch.zeros(max(L + 1, 64), D, dtype=torch.bfloat16)
+        sin = torch.zeros_like(cos)
+        cos[:L + 1], sin[:L + 1] = c["cos"], c["sin"]
+        qw, kw = (c["q_norm_w"], c["k_norm_w"]) if c["qk_norm"] else (None, None)
+        out, kc = _run_fixture_case(c["qkv"], c["k_rows"], c["v_rows"], pages, L, T, cos, sin, qw, kw,
+                                    c["eps"])
+        got_rows = torch.stack([kc[pages[p // 64], p % 64, 0] for p in range(L)])
+        assert torch.equal(got_rows[:c["cached"]], c["k_rows_after"][:c["cached"]]), "cached K rows moved"
+        _same_k(got_rows[c["cached"]:], c["k_rows_after"][c["cached"]:], c["qk_norm"],
+                f"cached {c['cached']} + {T}")
+        assert_close(out, c["out"], f"cached {c['cached']} + {T} tokens qk_norm {c['qk_norm']}")

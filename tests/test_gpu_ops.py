@@ -115,10 +115,15 @@ def test_linear_small_batch_in_a_large_batch_graph_stays_on_gemv():
 @pytest.mark.parametrize("B,H,I,tc", [(1, 512, 1024, "always"), (8, 4096, 1792, "always"),
                                       (3, 1024, 2048, "always"), (16, 1024, 2048, "always"),
                                       (40, 512, 1024, "always"), (64, 4096, 1792, "always"),
-                                      (16, 1024, 2048, "never"), (33, 4096, 1792, "never")])
+                                      (16, 1024, 2048, "never"), (33, 4096, 1792, "never"),
+                                      # BASELINE config 2 at its stated size, batch 8 and 64,
+                                      # both LINEAR paths for the 64-token case
+                                      (8, 4096, 14336, "auto"), (64, 4096, 14336, "always"),
+                                      (64, 4096, 14336, "never"), (16, 4096, 14336, "auto")])
 def test_gated_mlp_fused(B, H, I, tc, monkeypatch):
     """rmsnorm -> linear(gate|up) -> silu_mul -> linear(down)+residual, the MLP half of a
-    layer (BASELINE config 2 at reduced width); more than 8 tokens take the tcgen05 path."""
+    layer (BASELINE config 2, at reduced width and at its full 4096 x 14336); more than 8
+    tokens can take the tcgen05 path."""
     MT = 8 if B <= 8 else 64
     monkeypatch.setenv("YPK_TENSOR_CORE", tc)
     x = randn((MT, H), 1)
@@ -143,7 +148,8 @@ def test_gated_mlp_fused(B, H, I, tc, monkeypatch):
     assert [o.kind for o in ypk.lower().ops] == ["linear", "linear"], "gate/up + silu must fuse"
     ypk(batch=B)
     torch.cuda.synchronize()
-    assert (ypk.status().tensor_core_tasks > 0) == (B > 8 and tc == "always")
+    if tc != "auto":
+        assert (ypk.status().tensor_core_tasks > 0) == (B > 8 and tc == "always")
     xc = x[:B].cpu()
     h = O.rmsnorm(xc, nw.cpu(), 1e-5)
     want = xc.float() + O.gated_mlp(h, wg.cpu(), wu.cpu(), wd.cpu())
@@ -254,3 +260,72 @@ def test_kernel_graph_surface_gated_mlp_config2(B):
     torch.cuda.synchronize()
     want = O.silu_mul(O.linear(x.cpu(), w1.cpu().t()), O.linear(x.cpu(), w2.cpu().t()))
     assert_close(out, want, f"kernel-graph gated mlp B={B}")
+
+
+def test_embedding_id_beyond_the_table_gives_zeros():
+    """A sampled id can lie in the zero-padded tail of the lm_head, past the last row of the
+    embedding table: the gather must not read there."""
+    MT, V, H = 8, 1000, 1024
+    table = randn((V, H), 21, 0.02)
+    ids = torch.tensor([[999], [1000], [1 << 40], [0], [5000], [7], [0], [0]], dtype=torch.int64, device="cuda")
+    out = torch.full((MT, H), 7.0, dtype=torch.bfloat16, device="cuda")
+    ypk = onepass_kernel(MT)
+    ypk.embed_layer(ypk.attach_input(ids, "ids"), ypk.attach_input(table, "table"),
+                    ypk.attach_input(out, "out"), (1, 1, 1), (128, 1, 1), input_source=1)
+    ypk.compile()
+    ypk(batch=6)
+    torch.cuda.synchronize()
+    want = torch.zeros(6, H, dtype=torch.bfloat16, device="cuda")
+    for b, i in enumerate([999, None, None, 0, None, 7]):
+        if i is not None:
+            want[b] = table[i]
+    assert torch.equal(out[:6], want)
+    ypk.finalize()
+
+
+def test_argmax_ignores_the_padded_vocabulary_tail():
+    """All real logits negative, the padded columns hold 0.0 (zero rows of the lm_head): the
+    sampled id must be the arg-max over the real vocabulary (torch.argmax on the unpadded
+    columns), not a padded column."""
+    MT, V, VPAD, parts = 8, 3000, 4096, 128
+    logits = -(randn((MT, VPAD), 41).abs()) - 0.5
+    logits[:, V:] = 0.0
+    logits[5, V - 1] = -0.01           # the last real column wins in one row
+    pv = torch.zeros(MT, parts, dtype=torch.bfloat16, device="cuda")
+    pi = torch.zeros(MT, parts, dtype=torch.int64, device="cuda")
+    out = torch.full((MT, 1), -1, dtype=torch.int64, device="cuda")
+    ypk = onepass_kernel(MT)
+    lt, pvt, pit = ypk.attach_input(logits, "logits"), ypk.attach_input(pv, "pv"), ypk.attach_input(pi, "pi")
+    ypk.argmax_partial_layer(lt, (pvt, pit), (parts, 1, 1), (128, 1, 1), valid_cols=V)
+    ypk.argmax_reduce_layer((pvt, pit), ypk.attach_input(out, "out"), (1, 1, 1), (128, 1, 1))
+    ypk.compile()
+    ypk(batch=MT)
+    torch.cuda.synchronize()
+    want = torch.argmax(logits[:, :V].float().cpu(), dim=-1)
+    assert out[:, 0].cpu().tolist() == want.tolist()
+    assert int(out[5, 0]) == V - 1 and int(out.max()) < V
+    ypk.finalize()
+
+
+def test_argmax_planted_maximum_as_the_reference_test_does():
+    """tests/runtime_python/test_argmax.py of the reference: 6 rows of 153600 bf16 logits, 96
+    chunks, the largest bf16 planted at a known column per row; the ids must match exactly."""
+    rows, V, parts = 6, 153600, 96
+    logits = randn((8, V), 51)
+    g = torch.Generator().manual_seed(51)
+    planted = torch.randint(0, V, (rows,), generator=g).tolist()
+    for r, c in enumerate(planted):
+        logits[r, c] = 65504.0
+    pv = torch.zeros(8, parts, dtype=torch.bfloat16, device="cuda")
+    pi = torch.zeros(8, parts, dtype=torch.int64, device="cuda")
+    out = torch.full((8, 1), -1, dtype=torch.int64, device="cuda")
+    ypk = onepass_kernel(8)
+    ypk.argmax_partial_layer(ypk.attach_input(logits, "logits"),
+                             (ypk.attach_input(pv, "pv"), ypk.attach_input(pi, "pi")), (parts, 1, 1), (128, 1, 1))
+    ypk.argmax_reduce_layer((ypk.kn_graph.cygraph.tensors[1], ypk.kn_graph.cygraph.tensors[2]),
+                            ypk.attach_input(out, "out"), (1, 1, 1), (128, 1, 1))
+    ypk.compile()
+    ypk(batch=rows)
+    torch.cuda.synchronize()
+    assert out[:rows, 0].cpu().tolist() == planted
+    ypk.finalize()

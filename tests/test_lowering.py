@@ -174,16 +174,242 @@ def test_out_of_scope_builders_say_so():
                             page_size=64, eos_token_id=0, meta_tensors={})
 
 
-def test_task_graph_json_follows_the_reference_layout():
-    _, ypk = small_graph()
+# TaskType / EventType numbers of the reference (persistent_kernel/runtime_header.h:62-134) and
+# the element types its tools accept (scripts/display_task_graph.py:34-38)
+REF_TASK_TYPES = {101, 107, 118, 154, 252, 253, 257, 258, 259}
+REF_EVENT_TYPES = {900, 901, 902, 903, 910, 911, 999}
+EVENT_INVALID_ID = 0x7ffffffffffffffe
+
+
+@pytest.mark.parametrize("handoff", ["event", "ll"])
+def test_task_graph_json_follows_the_reference_layout(handoff):
+    """Every key scripts/display_task_graph.py and the reference's JSON loader
+    (runtime.cc:650-745) read is there with the reference's types and conventions."""
+    _, ypk = small_graph(handoff=handoff)
     res = ypk.kn_graph.generate_task_graph(num_gpus=1, my_gpu_id=0)
     assert set(res) == {"json_file", "cuda_code"}
     j = json.loads(res["json_file"])
     assert {"all_tasks", "all_events", "first_tasks"} <= set(j)
-    t = j["all_tasks"][10]
-    assert {"task_type", "variant_id", "inputs", "outputs", "trigger_event", "dependent_event"} <= set(t)
-    assert t["inputs"][0]["base_ptr"] and t["inputs"][0]["data_type"] in (940, 941, 955, 965)
-    assert sum(e["num_triggers"] for e in j["all_events"]) == len(j["all_tasks"])
+    for t in j["all_tasks"]:
+        assert {"task_type", "variant_id", "inputs", "outputs", "trigger_event", "dependent_event",
+                "request_id", "expert_offset"} <= set(t)
+        assert t["task_type"] in REF_TASK_TYPES and isinstance(t["variant_id"], int)
+        for ev in (t["trigger_event"], t["dependent_event"]):
+            assert ev == EVENT_INVALID_ID or 0 <= ev < len(j["all_events"])
+        for o in t["inputs"] + t["outputs"]:
+            assert set(o) == {"base_ptr", "offset", "dims", "strides", "data_type"}
+            assert isinstance(o["base_ptr"], str) and o["base_ptr"]
+            assert o["data_type"] in (940, 941, 965) and o["offset"] >= 0
+            assert len(o["dims"]) == len(o["strides"])
+        assert t["outputs"], "every task names what it writes"
+    for e in j["all_events"]:
+        assert set(e) == {"event_type", "num_triggers", "first_task_id", "last_task_id"}
+        assert e["event_type"] in REF_EVENT_TYPES
+    triggering = [t for t in j["all_tasks"] if t["trigger_event"] != EVENT_INVALID_ID]
+    assert sum(e["num_triggers"] for e in j["all_events"]) == len(triggering)
+    assert all(j["all_tasks"][i]["dependent_event"] == EVENT_INVALID_ID for i in j["first_tasks"])
+
+
+def test_reference_display_script_reads_the_emitted_task_graph(tmp_path, monkeypatch):
+    """scripts/display_task_graph.py of the reference, run unchanged on a task_graph.json this
+    build emitted.  graphviz and matplotlib are not installed here, so the two names the
+    script takes from them are stood in for by recorders; everything else (the enum parsing
+    from the reference headers, the walk over tasks, events and operands) is its own code."""
+    import os, sys, types, importlib.util
+    ref = os.environ.get("YIRAGE_REFERENCE_ROOT") or os.path.join(
+        os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
+    script = os.path.join(ref, "scripts", "display_task_graph.py")
+    if not os.path.exists(script):
+        pytest.skip("reference tree not mounted")
+    nodes, edges = [], []
+
+    class Digraph:
+        def attr(self, *a, **k): pass
+        def node(self, name, label=None): nodes.append(name)
+        def edge(self, a, b): edges.append((a, b))
+        def save(self, path): open(path, "w").write("digraph {}")
+
+    gv = types.ModuleType("graphviz"); gv.Digraph = Digraph
+    mpl = types.ModuleType("matplotlib"); colors = types.ModuleType("matplotlib.colors")
+    colors.CSS4_COLORS = {f"colour{i}": "#000000" for i in range(400)}
+    mpl.colors = colors
+    for name, mod in (("graphviz", gv), ("matplotlib", mpl), ("matplotlib.colors", colors)):
+        monkeypatch.setitem(sys.modules, name, mod)
+    monkeypatch.setenv("YIRAGE_HOME", ref)
+    _, ypk = small_graph()
+    path = tmp_path / "task_graph.json"
+    path.write_text(ypk.kn_graph.generate_task_graph(num_gpus=1, my_gpu_id=0)["json_file"])
+    spec = importlib.util.spec_from_file_location("ref_display_task_graph", script)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.display_task_graph(str(path), False)
+    g = ypk.lower()
+    assert sum(n.startswith("task_") for n in nodes) == g.num_tasks
+    assert sum(n.startswith("event_") for n in nodes) == g.num_events + 1   # + the base event
+    assert len(edges) == 2 * g.num_tasks
+    assert (tmp_path / "task_graph.dot").exists()
+
+
+def test_events_follow_tensors_so_independent_chains_do_not_wait_for_each_other():
+    """Two chains that share only a graph input: x -> A1 -> A2 and x -> B1 -> B2.  An
+    operator waits for the producer of what it reads (src/kernel/runtime.cc:446-503), not for
+    whatever was registered before it."""
+    ypk = yr.PersistentKernel(
+        mode="onepass", world_size=1, mpi_rank=0, num_workers=128, num_local_schedulers=0,
+        num_remote_schedulers=0, max_seq_length=64, max_num_batched_requests=1,
+        max_num_batched_tokens=16, max_num_pages=1, page_size=64, eos_token_id=-1, meta_tensors={})
+    x = ypk.attach_input(torch.zeros(16, 512, dtype=torch.bfloat16), "x")
+    def chain(tag):
+        w1 = ypk.attach_input(torch.zeros(512, 512, dtype=torch.bfloat16), f"{tag}w1")
+        w2 = ypk.attach_input(torch.zeros(512, 512, dtype=torch.bfloat16), f"{tag}w2")
+        h = ypk.new_tensor(dims=(16, 512), name=f"{tag}h")
+        y = ypk.new_tensor(dims=(16, 512), name=f"{tag}y")
+        ypk.linear_layer(x, w1, h, (8, 1, 1), (128, 1, 1))
+        ypk.linear_layer(h, w2, y, (8, 1, 1), (128, 1, 1))
+    chain("a")
+    chain("b")
+    g = ypk.lower(148)
+    assert [o.kind for o in g.ops] == ["linear"] * 4
+    assert lowering.tensor_dependencies(g.ops, serving=False) == [-1, 0, -1, 2]
+    dep = {ts.op_id: ts.dep_event for ts in g.tasks}
+    assert dep == {0: -1, 1: 0, 2: -1, 3: 2}
+    trig = {ts.op_id: ts.trig_event for ts in g.tasks}
+    assert trig == {0: 0, 1: -1, 2: 2, 3: 3}, "only awaited operators (and the last) publish an event"
+    assert set(lowering.simulate(g, 1)) == {1}
+    ypk.compile(dry_run=True)       # the native validation accepts it
+    ypk.finalize()
+    # a buffer reused by the second chain orders it after the first chain's reader
+    ypk2 = yr.PersistentKernel(
+        mode="onepass", world_size=1, mpi_rank=0, num_workers=128, num_local_schedulers=0,
+        num_remote_schedulers=0, max_seq_length=64, max_num_batched_requests=1,
+        max_num_batched_tokens=16, max_num_pages=1, page_size=64, eos_token_id=-1, meta_tensors={})
+    x = ypk2.attach_input(torch.zeros(16, 512, dtype=torch.bfloat16), "x")
+    h = ypk2.new_tensor(dims=(16, 512), name="h")
+    ws = [ypk2.attach_input(torch.zeros(512, 512, dtype=torch.bfloat16), f"w{i}") for i in range(4)]
+    ys = [ypk2.new_tensor(dims=(16, 512), name=f"y{i}") for i in range(2)]
+    ypk2.linear_layer(x, ws[0], h, (8, 1, 1), (128, 1, 1))
+    ypk2.linear_layer(h, ws[1], ys[0], (8, 1, 1), (128, 1, 1))
+    ypk2.linear_layer(x, ws[2], h, (8, 1, 1), (128, 1, 1))      # overwrites h: after its reader
+    ypk2.linear_layer(h, ws[3], ys[1], (8, 1, 1), (128, 1, 1))
+    assert lowering.tensor_dependencies(ypk2.lower(148).ops, serving=False) == [-1, 0, 1, 2]
+    # serving graphs end every iteration on the last operator: the chain is kept when the last
+    # operator's completion would not imply everybody's
+    assert lowering.tensor_dependencies(g.ops, serving=True) is None
+
+
+def test_embedding_and_argmax_tasks_carry_the_real_table_and_vocabulary_sizes():
+    shape, ypk = small_graph()
+    g = ypk.lower(148)
+    emb = [t for t in g.tasks if t.type == N.TASK_EMBED]
+    assert emb and all(t.iarg[5] == shape.vocab_size for t in emb)
+    part = [t for t in g.tasks if t.type == N.TASK_ARGMAX_PARTIAL]
+    assert part and all(t.iarg[5] == shape.vocab_size for t in part)
+
+
+def test_embed_task_without_a_row_count_is_refused(native_lib):
+    from tests.test_abi import host_handle
+    h = host_handle()
+    h.alloc(0, "ids", 8 * 8)
+    h.alloc(1, "table", 100 * 512 * 2)
+    h.alloc(2, "out", 8 * 512 * 2)
+    t = N.Task()
+    t.type, t.dep_event, t.trig_event = N.TASK_EMBED, -1, 0
+    t.ptr[0], t.ptr[1], t.ptr[2] = N.ref(0), N.ref(1), N.ref(2)
+    for i, v in enumerate([512, 0, 512, 512, 512, 0]):
+        t.iarg[i] = v
+    with pytest.raises(N.YpkError, match="row count"):
+        h.load_graph([t], 1, [0], [0, 1])
+    t.iarg[5] = 101                                  # one row more than the table holds
+    with pytest.raises(N.YpkError, match="reaches byte"):
+        h.load_graph([t], 1, [0], [0, 1])
+    t.iarg[5] = 100
+    h.load_graph([t], 1, [0], [0, 1])
+    h.close()
+
+
+def _tp_graph(n_allreduce_layers, handoff, world=2):
+    """A tensor-parallel graph with `n` all-reduces per iteration: x -> (linear -> allreduce) x n."""
+    ypk = yr.PersistentKernel(
+        mode="onepass", world_size=world, mpi_rank=0, num_workers=128, num_local_schedulers=0,
+        num_remote_schedulers=0, max_seq_length=64, max_num_batched_requests=1,
+        max_num_batched_tokens=8, max_num_pages=1, page_size=64, eos_token_id=-1, meta_tensors={})
+    ypk.handoff = handoff
+    x = ypk.attach_input(torch.zeros(8, 512, dtype=torch.bfloat16), "x")
+    buf = ypk.new_tensor(dims=(world, 8, 512), name="buf", io_category="nvshmem_tensor")
+    for i in range(n_allreduce_layers):
+        w = ypk.attach_input(torch.zeros(512, 512, dtype=torch.bfloat16), f"w{i}")
+        part = ypk.new_tensor(dims=(8, 512), name=f"part{i % 2}_{i}", io_category="nvshmem_tensor")
+        out = ypk.new_tensor(dims=(8, 512), name=f"sum{i}", io_category="nvshmem_tensor")
+        ypk.linear_layer(x, w, part, (8, 1, 1), (128, 1, 1))
+        ypk.allreduce_layer(part, buf, out, (8, 1, 1), (128, 1, 1))
+        x = out
+    wl = ypk.attach_input(torch.zeros(512, 512, dtype=torch.bfloat16), "w_last")
+    y = ypk.new_tensor(dims=(8, 512), name="y")
+    ypk.linear_layer(x, wl, y, (8, 1, 1), (128, 1, 1))
+    return ypk
+
+
+@pytest.mark.parametrize("n", [1, 2, 3])
+def test_allreduce_buffer_halves_alternate_for_any_count_per_iteration(n):
+    """Event form: the half is the parity of the running all-reduce number, so with an odd
+    count per iteration the last all-reduce of one iteration and the first of the next still
+    differ (the task carries index and count, the device adds iterations * count)."""
+    g = _tp_graph(n, "event").lower(148)
+    ar = [t for t in g.tasks if t.type == N.TASK_ALLREDUCE]
+    assert {t.iarg[6] for t in ar} == set(range(n)) and {t.iarg[10] for t in ar} == {n}
+    halves = [((it * n + k) & 1) for it in range(4) for k in range(n)]
+    assert all(a != b for a, b in zip(halves, halves[1:]))
+
+
+def test_single_buffered_pushes_are_used_only_where_consecutive_allreduces_differ():
+    """Flagged-word form: a peer's slot may be overwritten once that peer has pushed the next
+    all-reduce.  With one all-reduce per iteration the next one is the same buffer: such
+    a graph keeps the event form."""
+    one = _tp_graph(1, "ll").lower(148)
+    assert not any(t.flags & N.F_LL_PUSH for t in one.tasks)
+    assert all(not (t.flags & N.F_LL_IN) for t in one.tasks if t.type == N.TASK_ALLREDUCE)
+    two = _tp_graph(2, "ll").lower(148)
+    assert any(t.flags & N.F_LL_PUSH for t in two.tasks)
+    for g in (one, two):
+        assert set(lowering.simulate(g, 2)) == {2}
+
+
+def test_more_flagged_producers_than_tag_ids_do_not_confuse_the_simulator():
+    """40 layers under 2-way tensor parallelism have 284 flagged producers for 254 tag ids:
+    the ids repeat on the device (never twice on one buffer within an iteration), the plan
+    and the simulator tell the producers apart."""
+    shape = llama.LlamaShape(hidden_size=512, intermediate_size=1024, num_hidden_layers=40,
+                             num_attention_heads=8, num_key_value_heads=2, vocab_size=2048)
+    w = llama.init_weights(shape, "cpu", 0, world_size=2, rank=0)
+    tokens = torch.zeros(1, 64, dtype=torch.int64)
+    ypk, _ = llama.build_decode_kernel(shape, w, tokens=tokens, prompt_lengths=torch.tensor([5], dtype=torch.int32),
+                                       max_num_batched_requests=1, max_num_batched_tokens=8, max_num_pages=1,
+                                       page_size=64, world_size=2, rank=0, compile=False, handoff="ll")
+    g = ypk.lower(148)
+    outs = {t.flagged_out for t in g.tasks if t.flagged_out >= 0}
+    assert len(outs) > 254
+    assert set(lowering.simulate(g, 2)) == {2}
+
+
+def test_qk_norm_attention_lowers_with_packed_weights(native_lib):
+    """Dense Qwen3 form: q/k RMSNorm inside the attention task (demo/qwen3/demo.py:444-476)."""
+    shape = llama.LlamaShape(hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                             num_attention_heads=8, num_key_value_heads=2, vocab_size=2048,
+                             rms_norm_eps=1e-6, qk_norm=True)
+    w = llama.init_weights(shape, "cpu", 0)
+    tokens = torch.zeros(1, 64, dtype=torch.int64)
+    ypk, _ = llama.build_decode_kernel(shape, w, tokens=tokens, prompt_lengths=torch.tensor([5], dtype=torch.int32),
+                                       max_num_batched_requests=1, max_num_batched_tokens=8, max_num_pages=1,
+                                       page_size=64, compile=False)
+    g = ypk.lower(148)
+    att = [t for t in g.tasks if t.type == N.TASK_ATTENTION]
+    assert att and all(t.flags & N.F_QK_NORM and t.ptr[7] is not None for t in att)
+    assert all(abs(t.farg[0] - 1e-6) < 1e-12 for t in att)
+    packed = [sh for sh in g.shuffles if sh["rows"] == [1, 1]]
+    assert len(packed) == 2 and packed[0]["row_bytes"] == 256
+    assert [s.name for s in packed[0]["sources"]] == ["layer_0_q_norm", "layer_0_k_norm"]
+    ypk.compile(dry_run=True)
+    ypk.finalize()
 
 
 def test_native_library_accepts_the_lowered_llama_graph(native_lib):

@@ -37,7 +37,10 @@ def _rank_main(rank, port, ret, handoff):
     ar = [t for t in g.tasks if t.type == N.TASK_ALLREDUCE]
     o_proj = [t for t in g.tasks if t.op_id == 3][0]
     if handoff == "event":
-        assert {t.iarg[6] for t in ar} == {0, 1}, "alternate all-reduces use alternate buffer halves"
+        # the buffer half is the parity of the running all-reduce number, derived on the device
+        # from (index in the iteration, all-reduces per iteration)
+        nar = 2 * shape.num_hidden_layers
+        assert {t.iarg[6] for t in ar} == set(range(nar)) and {t.iarg[10] for t in ar} == {nar}
         assert sorted(t.iarg[7] for t in ar) == list(range(len(ar))), "one counter per tile"
     else:
         # flagged words: the row-split projections push their partial sums to every rank, the

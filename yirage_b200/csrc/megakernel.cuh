@@ -210,10 +210,14 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_
     } else {
       ntok = prepare_next_batch(rt, false);
     }
-    if (ntok == 0) rt.ctrl[kCtrlFinished] = 1ull;
-    __threadfence();
-    st_release_u64(rt.ctrl + kCtrlPublished,
-                   make_word(iter + 1, ntok > 0 ? kStateRun : kStateStop, ntok));
+    if (ntok < 0) {
+      raise_abort(wc, YPK_ERR_STATE, -7);   // KV page pool exhausted
+    } else {
+      if (ntok == 0) rt.ctrl[kCtrlFinished] = 1ull;
+      __threadfence();
+      st_release_u64(rt.ctrl + kCtrlPublished,
+                     make_word(iter + 1, ntok > 0 ? kStateRun : kStateStop, ntok));
+    }
   }
 
   bool ok = true;
@@ -351,10 +355,14 @@ __global__ void __launch_bounds__(kBlockThreads, 1) ypk_megakernel(const __grid_
       if (good) {
         const int ntok = prepare_next_batch(rt, false);
         const bool pause = rt.max_iters > 0 && iters_here >= rt.max_iters;
-        if (ntok == 0) rt.ctrl[kCtrlFinished] = 1ull;
-        __threadfence();
-        st_release_u64(rt.ctrl + kCtrlPublished,
-                       make_word(iter + 1, (ntok == 0 || pause) ? kStateStop : kStateRun, ntok));
+        if (ntok < 0) {
+          raise_abort(wc, YPK_ERR_STATE, -7);   // KV page pool exhausted: every waiter leaves
+        } else {
+          if (ntok == 0) rt.ctrl[kCtrlFinished] = 1ull;
+          __threadfence();
+          st_release_u64(rt.ctrl + kCtrlPublished,
+                         make_word(iter + 1, (ntok == 0 || pause) ? kStateStop : kStateRun, ntok));
+        }
       }
     }
   }

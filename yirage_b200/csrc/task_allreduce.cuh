@@ -16,10 +16,15 @@
 //
 // The buffer has two halves used by alternate all-reduces: a fast rank writing all-reduce
 // k+1 cannot touch what a slow rank still reads for k, and it cannot reach k+2 before the
-// slow rank has pushed k+1, i.e. finished reading k.  No TMA and no multicast are involved.
+// slow rank has pushed k+1, i.e. finished reading k.  "Alternate" counts across iteration
+// boundaries, so the half is the parity of the running all-reduce number
+// (iterations so far * all-reduces per iteration + index in the iteration): a graph with an
+// odd number of all-reduces still never uses one half twice in a row.  No TMA and no
+// multicast are involved.
 //
 // ptr  = {in, buf, out, signals};  buf = [2][world][max_tokens][hidden] 16-bit, symmetric
-// iarg = {col0, ncols, ld_in, ld_out, hidden, max_tokens, half, signal index, world, rank}
+// iarg = {col0, ncols, ld_in, ld_out, hidden, max_tokens, index of this all-reduce in the
+//         iteration, signal index, world, rank, all-reduces per iteration}
 #pragma once
 #include "device_common.cuh"
 #include "ll_handoff.cuh"
@@ -34,8 +39,11 @@ __device__ __forceinline__ bool allreduce_task(WaitCtx &wc, Misc *misc, const Ru
   uint16_t *out = reinterpret_cast<uint16_t *>(t.ptr[2]);
   char *sig = reinterpret_cast<char *>(t.ptr[3]);
   const int col0 = t.iarg[0], ncols = t.iarg[1], ld_in = t.iarg[2], ld_out = t.iarg[3];
-  const int hidden = t.iarg[4], max_tok = t.iarg[5], half = t.iarg[6], sidx = t.iarg[7];
+  const int hidden = t.iarg[4], max_tok = t.iarg[5], sidx = t.iarg[7];
   const int world = t.iarg[8], rank = t.iarg[9];
+  const int half = int(((rt.ar_epoch + static_cast<unsigned long long>(iter)) *
+                            static_cast<unsigned long long>(t.iarg[10]) +
+                        static_cast<unsigned long long>(t.iarg[6])) & 1ull);
   const size_t buf_off = size_t(buf - rt.arena[rank]), sig_off = size_t(sig - rt.arena[rank]);
   const int nvec = ncols / 8;
   auto slot = [&](int r, int b) -> size_t {   // byte offset of row b of rank r's slot in the half

@@ -465,6 +465,47 @@ __device__ __forceinline__ void attn_store_state_t(float *dst, const AttnAccT &a
   }
 }
 
+// q/k RMSNorm inside attention (YPK_F_QK_NORM; Qwen3: attention_sm100.cuh:349-379,
+// norm_sm100.cuh): every new q head and the new k are normalised over the 128 head dims and
+// scaled by a weight before the rotation, the result rounded to bf16 as an operator output
+// would be.  Called by the 16 neighbouring lanes that hold the 16 8-dim chunks of one
+// (token, head); `pk` are the lane's own 8 values, `ov` their rotate-half partners (the
+// chunk 64 dims away, same head, hence the same RMS), w the 128 weights of the head kind.
+struct QkPair {
+  uint4 pk, ov;
+};
+__device__ __noinline__ QkPair qk_norm_chunk(uint4 pk, uint4 ov, const uint16_t *w, int d0,
+                                             float eps, bool partner, unsigned lanes) {
+  const uint32_t pv[4] = {pk.x, pk.y, pk.z, pk.w}, po[4] = {ov.x, ov.y, ov.z, ov.w};
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = unpack2(cvt_pair<false>(pv[i]));
+    ss += f.x * f.x + f.y * f.y;
+  }
+#pragma unroll
+  for (int o = 1; o < 16; o <<= 1) ss += __shfl_xor_sync(lanes, ss, o);
+  const float rn = rsqrtf(ss * (1.0f / kHeadDim) + eps);
+  const uint4 wv = __ldg(reinterpret_cast<const uint4 *>(w + d0));
+  const uint32_t pw[4] = {wv.x, wv.y, wv.z, wv.w};
+  uint32_t o1[4], o2[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = unpack2(cvt_pair<false>(pv[i])), g = unpack2(cvt_pair<false>(pw[i]));
+    o1[i] = pack_bf16((f.x * rn) * g.x, (f.y * rn) * g.y);
+  }
+  if (partner) {
+    const uint4 wo = __ldg(reinterpret_cast<const uint4 *>(w + (d0 ^ 64)));
+    const uint32_t qw[4] = {wo.x, wo.y, wo.z, wo.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = unpack2(cvt_pair<false>(po[i])), g = unpack2(cvt_pair<false>(qw[i]));
+      o2[i] = pack_bf16((f.x * rn) * g.x, (f.y * rn) * g.y);
+    }
+  }
+  return QkPair{make_uint4(o1[0], o1[1], o1[2], o1[3]), make_uint4(o2[0], o2[1], o2[2], o2[3])};
+}
+
 // DECODE: the request has at most 8 query rows this iteration (transposed products).
 template <bool DECODE>
 __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, Misc *misc,
@@ -483,6 +524,9 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
   const uint16_t *sinp = reinterpret_cast<const uint16_t *>(t.ptr[5]);
   float *scratch = reinterpret_cast<float *>(t.ptr[6]);
   const bool rope = (t.flags & YPK_F_ROPE) != 0;
+  // q/k RMSNorm: ptr[7] = [2][128] weights (q heads, then k), farg[0] = epsilon
+  const bool qk_norm = (t.flags & YPK_F_QK_NORM) != 0;
+  const uint16_t *qk_w = reinterpret_cast<const uint16_t *>(t.ptr[7]);
   // flagged-word hand-off: with YPK_F_LL_IN ptr[0] holds the packed q/k/v as {two values,
   // tag} words ([max_tokens][ld_qkv / 2]), with YPK_F_LL_OUT ptr[3] takes the result that way
   const bool ll_in = (t.flags & YPK_F_LL_IN) != 0, ll_out = (t.flags & YPK_F_LL_OUT) != 0;
@@ -548,6 +592,13 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
       pk = __ldcg(reinterpret_cast<const uint4 *>(src + d0));
       if (rot) ov = __ldcg(reinterpret_cast<const uint4 *>(src + (d0 ^ 64)));
     }
+    if (qk_norm && hh <= G) {
+      // the 16 chunks of a (token, head) sit in 16 neighbouring lanes (idx & 15 = chunk)
+      const QkPair n = qk_norm_chunk(pk, ov, qk_w + (hh == G ? kHeadDim : 0), d0, t.farg[0], rot,
+                                     (lane & 16) ? 0xffff0000u : 0x0000ffffu);
+      pk = n.pk;
+      ov = n.ov;
+    }
     if (rot) {
       const uint4 cv = __ldcg(reinterpret_cast<const uint4 *>(cosp + size_t(pos_t) * kHeadDim + d0));
       const uint4 sv = __ldcg(reinterpret_cast<const uint4 *>(sinp + size_t(pos_t) * kHeadDim + d0));
@@ -559,7 +610,10 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
         const float2 v2 = unpack2(cvt_pair<false>(pv[i])), o2 = unpack2(cvt_pair<false>(po[i])),
                      c2 = unpack2(cvt_pair<false>(pc[i])), s2 = unpack2(cvt_pair<false>(ps[i]));
         const float sgn = d0 < 64 ? -1.f : 1.f;
-        o[i] = pack_bf16(v2.x * c2.x + sgn * (o2.x * s2.x), v2.y * c2.y + sgn * (o2.y * s2.y));
+        // two products and a sum, each rounded to fp32 (no fused multiply-add): the rounding
+        // points of x * cos + rotate_half(x) * sin evaluated in fp32
+        o[i] = pack_bf16(__fadd_rn(__fmul_rn(v2.x, c2.x), sgn * __fmul_rn(o2.x, s2.x)),
+                         __fadd_rn(__fmul_rn(v2.y, c2.y), sgn * __fmul_rn(o2.y, s2.y)));
       }
       pk = make_uint4(o[0], o[1], o[2], o[3]);
     }

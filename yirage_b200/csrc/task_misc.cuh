@@ -7,19 +7,21 @@
 
 namespace ypk {
 
-// out[b, col0:col0+ncols] = table[ids[b], col0:col0+ncols]; a negative id gives zeros
-// (tasks/ampere/embedding.cuh:42-70).
+// out[b, col0:col0+ncols] = table[ids[b], col0:col0+ncols]; an id outside [0, rows) gives
+// zeros (tasks/ampere/embedding.cuh:42-70 reads whatever row the id names; a sampled id can
+// lie in the zero-padded tail of the lm_head, beyond the embedding table).
 __device__ __forceinline__ void embed_task(const ypk_task &t, int batch) {
   const long long *ids = reinterpret_cast<const long long *>(t.ptr[0]);
   const uint16_t *table = reinterpret_cast<const uint16_t *>(t.ptr[1]);
   uint16_t *out = reinterpret_cast<uint16_t *>(t.ptr[2]);
   const int col0 = t.iarg[1], ncols = t.iarg[2], ldt = t.iarg[3], ldo = t.iarg[4];
+  const long long rows = t.iarg[5];
   const int vec = ncols / 8;
   for (int idx = threadIdx.x; idx < batch * vec; idx += kConsumerThreads) {
     const int b = idx / vec, c = (idx - b * vec) * 8 + col0;
     const long long id = __ldcg(ids + b);
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (id >= 0) v = __ldg(reinterpret_cast<const uint4 *>(table + size_t(id) * ldt + c));
+    if (id >= 0 && id < rows) v = __ldg(reinterpret_cast<const uint4 *>(table + size_t(id) * ldt + c));
     *reinterpret_cast<uint4 *>(out + size_t(b) * ldo + c) = v;
   }
 }
@@ -30,8 +32,10 @@ __device__ __forceinline__ void argmax_partial_task(const ypk_task &t, int batch
   const uint16_t *logits = reinterpret_cast<const uint16_t *>(t.ptr[0]);
   uint16_t *pval = reinterpret_cast<uint16_t *>(t.ptr[1]);
   long long *pidx = reinterpret_cast<long long *>(t.ptr[2]);
-  const int col0 = t.iarg[0], ncols = t.iarg[1], ld = t.iarg[2], part = t.iarg[3],
-            nparts = t.iarg[4];
+  const int col0 = t.iarg[0], ld = t.iarg[2], part = t.iarg[3], nparts = t.iarg[4];
+  // iarg[5] != 0: only the first iarg[5] columns of a logits row are real vocabulary (the
+  // rest is padding of the lm_head and must not be sampled); negative = none of them
+  const int ncols = t.iarg[5] != 0 ? max(0, min(t.iarg[1], t.iarg[5] - col0)) : t.iarg[1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int b = warp; b < batch; b += kConsumerWarps) {
     const uint16_t *row = logits + size_t(b) * ld + col0;
@@ -186,7 +190,9 @@ __device__ __forceinline__ void silu_mul_task(const ypk_task &t, int batch) {
 // tokens and rebuilds qo_indptr / paged_kv_indptr / paged_kv_indices.
 // paged_kv_last_page_len is written in [1, page_size].
 // `first` skips the finalisation of a previous batch.  Returns the number of active
-// tokens of the next iteration (0 = everything retired).
+// tokens of the next iteration (0 = everything retired), or -1 when a request that is
+// already running needs a page and the pool has none left (the reference hands out pages
+// without looking, persistent_kernel.cuh:262-270, and two requests then share one).
 __device__ __noinline__ int prepare_next_batch(const Runtime &rt, bool first) {
   const int MR = rt.max_req, MT = rt.max_tok, MP = rt.max_pages, PS = rt.page_size;
   int head = rt.bstate[1], tail = rt.bstate[2];
@@ -242,6 +248,7 @@ __device__ __noinline__ int prepare_next_batch(const Runtime &rt, bool first) {
       rt.input_tokens[ntok + j] = rt.tokens[size_t(req) * rt.max_seq + step + j];
     const int total = step + nnew;
     const int need = (total + PS - 1) / PS;
+    if (need > nold && (tail - head < need - nold || npages + need > MP)) return -1;
     for (int j = nold; j < need; ++j) {
       rt.kv_indices[npages + j] = rt.page_queue[head % MP];
       ++head;

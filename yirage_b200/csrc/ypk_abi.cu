@@ -61,6 +61,7 @@ struct ypk_handle {
   long long base_iter = 0;
   // iterations of earlier runs (see Runtime::ll_epoch / ar_epoch)
   unsigned long long ll_epoch = 0, ar_epoch = 0;
+  long long abort_iters = 0;   // last iteration an aborted launch had published
   int pending_tokens = 0;
   bool resume_pending = false;
   bool finished = false;
@@ -203,7 +204,9 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
       if (ncols <= 0 || ncols % 8 || col0 % 8 || ldt % 8 || ldo % 8)
         return fail(h, YPK_ERR_INVALID, "task %d: EMBED columns must be multiples of 8", ti);
       need[0] = uint64_t(mb) * 8; align[0] = 8; required[0] = true;
-      need[1] = uint64_t(col0 + ncols) * 2; align[1] = 16; required[1] = true;
+      if (a[5] <= 0)
+        return fail(h, YPK_ERR_INVALID, "task %d: EMBED needs the row count of its table (iarg[5])", ti);
+      need[1] = rows(ldt, a[5], col0 + ncols); align[1] = 16; required[1] = true;
       need[2] = rows(ldo, mb, col0 + ncols); align[2] = 16; required[2] = true;
       break;
     }
@@ -243,8 +246,10 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
       if (nsplit > 1) {
         need[6] = uint64_t(h->cfg.max_num_batched_requests) * hkv * nsplit * max_rows *
                   kAttnRowFloats * 8u;   // flagged words {fp32 bits, tag}
-        need[7] = uint64_t(h->cfg.max_num_batched_requests) * hkv * 4u;
-        align[6] = 16; align[7] = 4; required[6] = required[7] = true;
+        align[6] = 16; required[6] = true;
+      }
+      if (in.flags & YPK_F_QK_NORM) {
+        need[7] = 2u * kHeadDim * 2u; align[7] = 16; required[7] = true;
       }
       break;
     }
@@ -272,12 +277,12 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
     }
     case YPK_TASK_ALLREDUCE: {
       const int col0 = a[0], ncols = a[1], ldi = a[2], ldo = a[3], hidden = a[4], mt = a[5],
-                half = a[6], sidx = a[7], world = a[8], rank = a[9];
+                sidx = a[7], world = a[8], rank = a[9];
       if (world != h->cfg.world_size || rank != h->cfg.rank || world < 2 || world > 8)
         return fail(h, YPK_ERR_INVALID, "task %d: ALLREDUCE for rank %d of %d on a handle of rank %d of %d",
                     ti, rank, world, h->cfg.rank, h->cfg.world_size);
       if (ncols <= 0 || ncols % 8 || col0 % 8 || col0 + ncols > hidden || ldi % 8 || ldo % 8 ||
-          hidden % 8 || mt < mb || half < 0 || half > 1 || sidx < 0)
+          hidden % 8 || mt < mb || sidx < 0)
         return fail(h, YPK_ERR_INVALID, "task %d: ALLREDUCE shape", ti);
       if (!h->arena) return fail(h, YPK_ERR_STATE, "ALLREDUCE needs ypk_comm_init first");
       need[2] = rows(ldo, mb, col0 + ncols); align[2] = 16; required[2] = true;
@@ -289,6 +294,9 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
         need[7] = uint64_t(mt) * ldo * 4; align[7] = 8; required[7] = true;
         break;
       }
+      if (a[10] < 1 || a[6] < 0 || a[6] >= a[10])
+        return fail(h, YPK_ERR_INVALID, "task %d: ALLREDUCE is number %d of %d in the iteration", ti,
+                    a[6], a[10]);
       need[0] = rows(ldi, mb, col0 + ncols); align[0] = 16; required[0] = true;
       need[1] = uint64_t(2) * world * mt * hidden * 2; align[1] = 16; required[1] = true;
       need[3] = uint64_t(sidx + 1) * 8; align[3] = 8; required[3] = true;
@@ -869,8 +877,17 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
 int ypk_reset(ypk_handle *h) {
   if (!h) return fail(nullptr, YPK_ERR_INVALID, "null handle");
   if (h->in_flight) return fail(h, YPK_ERR_STATE, "reset while a launch is in flight");
+  if (h->status.error && h->arena)
+    // After an abort the ranks have stopped in different places: arrival counters in the
+    // peers' arenas hold part of the aborted iteration and the ranks' tag epochs no longer
+    // agree.  Nothing on one rank can repair that.
+    return fail(h, YPK_ERR_STATE,
+                "a tensor-parallel handle cannot be reset after a device error: destroy the "
+                "handles of all ranks and create them again");
   h->ar_epoch += static_cast<unsigned long long>(h->base_iter);
-  h->ll_epoch += static_cast<unsigned long long>(h->base_iter) + 1;
+  // step over every iteration an aborted launch may have written tags for
+  h->ll_epoch += static_cast<unsigned long long>(std::max(h->base_iter, h->abort_iters)) + 1;
+  h->abort_iters = 0;
   h->base_iter = 0;
   h->resume_pending = false;
   h->pending_tokens = 0;
@@ -1015,9 +1032,16 @@ int ypk_wait(ypk_handle *h) {
     int ev = int(info & 0xfffff);
     if (ev & 0x80000) ev |= ~0xfffff;  // sign-extend the 20-bit field
     h->status.fail_event = ev;
+    // how far the aborted launch got: tags of flagged words up to there may sit in buffers
+    h->abort_iters = (long long)(words[kCtrlPublished] >> 32);
+    if (ev == -7)
+      return fail(h, h->status.error,
+                  "the KV page pool ran out: a running request needs a page and none of the %d "
+                  "is free (max_num_pages is too small for max_num_batched_requests x "
+                  "max_seq_length)", h->cfg.max_num_pages);
     return fail(h, h->status.error,
                 "device wait timed out: worker %d, task %d, event %d (negative: -2 ring "
-                "barrier, -3 iteration word)",
+                "barrier, -3 iteration word, -5 all-reduce arrivals, -6 flagged word)",
                 h->status.fail_worker, h->status.fail_task, h->status.fail_event);
   }
   if (h->cfg.mode == 0) {

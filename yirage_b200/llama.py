@@ -27,10 +27,19 @@ class LlamaShape:
     vocab_size: int = 128256
     rms_norm_eps: float = 1e-5
     rope_theta: float = 500000.0
+    qk_norm: bool = False          # RMSNorm of q and k heads inside attention (Qwen3)
 
     @staticmethod
     def llama3_8b():
         return LlamaShape()
+
+    @staticmethod
+    def qwen3_8b():
+        """Dense Qwen3-8B: the Llama graph plus q/k RMSNorm in attention
+        (demo/qwen3/demo.py:402-575)."""
+        return LlamaShape(hidden_size=4096, intermediate_size=12288, num_hidden_layers=36,
+                          num_attention_heads=32, num_key_value_heads=8, vocab_size=151936,
+                          rms_norm_eps=1e-6, rope_theta=1000000.0, qk_norm=True)
 
     @staticmethod
     def llama3_70b():
@@ -98,6 +107,9 @@ def init_weights(shape: LlamaShape, device, seed: int, world_size: int = 1, rank
             "up": rows_shard(full(f, h)),
             "down": cols_shard(full(h, f)),
         }
+        if shape.qk_norm:
+            L["q_norm"] = (1.0 + 0.1 * torch.randn(d, generator=g, device=device)).to(dtype)
+            L["k_norm"] = (1.0 + 0.1 * torch.randn(d, generator=g, device=device)).to(dtype)
         w["layers"].append(L)
     w["final_norm"] = torch.ones(h, device=device, dtype=dtype)
     w["lm_head"] = full(shape.vocab_size, h)
@@ -227,7 +239,11 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
                          block_dim=(128, 1, 1))
         kc = ypk.attach_input(k_cache[li], name=f"layer_{li}_k_cache")
         vc = ypk.attach_input(v_cache[li], name=f"layer_{li}_v_cache")
-        ypk.paged_attention_layer(input=attn_in, k_cache=kc, v_cache=vc, q_norm=None, k_norm=None,
+        qn = kn = None
+        if "q_norm" in L:
+            qn = ypk.attach_input(L["q_norm"], name=f"layer_{li}_q_norm")
+            kn = ypk.attach_input(L["k_norm"], name=f"layer_{li}_k_norm")
+        ypk.paged_attention_layer(input=attn_in, k_cache=kc, v_cache=vc, q_norm=qn, k_norm=kn,
                                   cos_pos_embed=cos_t, sin_pos_embed=sin_t, output=attn_out,
                                   grid_dim=(MR, hkv, 1), block_dim=(128, 1, 1))
         w_o = ypk.attach_input(L["o"], name=f"layer_{li}_o_proj")
@@ -265,8 +281,13 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
                       block_dim=(128, 1, 1))
     ypk.linear_layer(input=rmsnorm_out, weight=w_lm, output=argmax_in,
                      grid_dim=(vslice // 256 if vslice % 256 == 0 else 1, 1, 1), block_dim=(128, 1, 1))
+    # real vocabulary columns of this rank's logits (the lm_head is padded with zero rows,
+    # whose logit 0.0 would win whenever every real logit is negative)
+    v0 = rank * vslice if vocab_parallel else 0
+    valid = max(0, min(vslice, shape.vocab_size - v0))
     ypk.argmax_partial_layer(input=argmax_in, output=(argmax_part_value, argmax_part_index),
-                             grid_dim=(num_workers, 1, 1), block_dim=(128, 1, 1))
+                             grid_dim=(num_workers, 1, 1), block_dim=(128, 1, 1),
+                             valid_cols=valid if valid > 0 else -1)
     ypk.argmax_reduce_layer(input=(argmax_part_value, argmax_part_index), output=argmax_out,
                             grid_dim=(1, 1, 1), block_dim=(128, 1, 1),
                             vocab_offset=rank * vslice if vocab_parallel else 0, exchange=vocab_parallel)

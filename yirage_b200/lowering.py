@@ -88,6 +88,10 @@ class TaskSpec:
     weight_bytes: int = 0
     flagged_deps: List[int] = field(default_factory=list)   # tag ids this task polls for
     flagged_out: int = -1                                   # tag id it writes
+    # tensors of the graph that the task reads / writes only in flagged-word form (their plain
+    # copies are not touched); listed in the JSON so that the data flow stays readable
+    logical_in: List[Tuple[DTensor, int]] = field(default_factory=list)
+    logical_out: List[Tuple[DTensor, int]] = field(default_factory=list)
 
 
 @dataclass
@@ -206,12 +210,18 @@ def fuse(regs: List[RegisteredTask], default_eps: float) -> List[FusedOp]:
             i = k
         elif name == "paged_attention":
             qkv, kc, vc, qn, kn, cos, sin, o = rt.operands
-            if qn is not None or kn is not None:
-                raise NotImplementedError("q/k RMSNorm inside attention (Qwen3) is not built yet")
             flags = N.F_ROPE if (cos is not None and sin is not None) else 0
+            attrs = {"num_q_heads": rt.params[0], "num_kv_heads": rt.params[1]}
+            if qn is not None or kn is not None:
+                # q/k RMSNorm of Qwen3 (demo/qwen3/demo.py:444-476): the two weight vectors are
+                # packed into one [2, 128] tensor when the graph is compiled
+                if qn is None or kn is None or rt.attrs.get("qk_norm_packed") is None:
+                    raise ValueError("paged attention needs both q_norm and k_norm, or neither")
+                flags |= N.F_QK_NORM
+                attrs.update(q_norm=qn, k_norm=kn, qk_norm_packed=rt.attrs["qk_norm_packed"],
+                             eps=rt.attrs.get("eps", default_eps))
             out.append(FusedOp("attention", [rt], {"qkv": qkv, "k_cache": kc, "v_cache": vc,
-                                                    "cos": cos, "sin": sin, "out": o}, flags,
-                               {"num_q_heads": rt.params[0], "num_kv_heads": rt.params[1]}))
+                                                    "cos": cos, "sin": sin, "out": o}, flags, attrs))
             i += 1
         elif name == "silu_mul":
             x, o = rt.operands
@@ -221,7 +231,8 @@ def fuse(regs: List[RegisteredTask], default_eps: float) -> List[FusedOp]:
         elif name == "argmax_partial":
             x, pv, pi = rt.operands
             out.append(FusedOp("argmax_partial", [rt], {"in": x, "val": pv, "idx": pi},
-                               attrs={"nparts": rt.grid_dim[0]}))
+                               attrs={"nparts": rt.grid_dim[0],
+                                      "valid_cols": rt.attrs.get("valid_cols")}))
             i += 1
         elif name == "argmax_reduce":
             pv, pi, o = rt.operands
@@ -281,9 +292,26 @@ def plan_handoff(ops, world_size: int):
     dict with optional entries
         "out":  (key, tag id, push)   producer side (linear, or allreduce passing its sum on)
         "x" / "res" / "in": (key, tag id)   consumer side
-    where `key` names the flagged-word buffer (one per tensor, shared by all layers)."""
+    where `key` names the flagged-word buffer (one per tensor, shared by all layers).
+
+    Tag ids in the plan are unique per producer; the device sees them modulo 254
+    (`device_tag`).  Two producers whose ids agree modulo 254 must not write the same buffer
+    in one iteration (a reader could take one for the other): checked here.
+
+    The exchange buffers of pushed partial sums are single-buffered, which is safe only if
+    consecutive all-reduces (cyclically, across the iteration boundary) use different
+    buffers: a rank can then overwrite a peer's slot only after that peer has pushed the
+    next all-reduce, i.e. has finished reading this one.  A graph where that does not hold
+    (one all-reduce per iteration, or an odd number alternating between two tensors) keeps
+    its all-reduces on the event path, whose buffer halves alternate on the device."""
     plan = {i: {} for i in range(len(ops))}
     next_id = 0
+    if world_size > 1:
+        ar_inputs = [id(op.t["in"]) for op in ops if op.kind == "allreduce"]
+        push_safe = len(ar_inputs) >= 2 and all(
+            ar_inputs[k] != ar_inputs[(k + 1) % len(ar_inputs)] for k in range(len(ar_inputs)))
+    else:
+        push_safe = False
     def reader_ok(j, role):
         return (ops[j].kind == "linear" and role in ("x", "res")) or \
                (ops[j].kind == "attention" and role == "qkv")
@@ -300,6 +328,8 @@ def plan_handoff(ops, world_size: int):
         ar = None
         if (op.kind == "linear" and len(readers) == 1 and ops[readers[0][0]].kind == "allreduce"
                 and world_size > 1 and readers[0][0] == i + 1):
+            if not push_safe:
+                continue
             ar = readers[0][0]
             T2 = ops[ar].t["out"]
             readers2, wraps2 = _readers(ops, ar, T2)
@@ -313,20 +343,33 @@ def plan_handoff(ops, world_size: int):
         if any(role == "res" and (ops[j].flags & N.F_SILU_MUL) for j, role in final):
             continue
         if ar is None:
-            pid = next_id % 254
+            pid = next_id
             next_id += 1
             plan[i]["out"] = (("ll", id(T)), pid, False, T)
             for j, role in final:
                 plan[j][role] = (("ll", id(T)), pid)
         else:
-            pid, aid = next_id % 254, (next_id + 1) % 254
+            pid, aid = next_id, next_id + 1
             next_id += 2
             plan[i]["out"] = (("push", id(T)), pid, True, T)
             plan[ar]["in"] = (("push", id(T)), pid)
             plan[ar]["out"] = (("ll", id(T2)), aid, False, T2)
             for j, role in final:
                 plan[j][role] = (("ll", id(T2)), aid)
+    seen = set()
+    for i in plan:
+        if "out" in plan[i]:
+            key, pid = plan[i]["out"][0], plan[i]["out"][1]
+            if (key, device_tag(pid)) in seen:
+                raise NotImplementedError(
+                    "more than 254 flagged-word producers alias on one buffer; use handoff='event'")
+            seen.add((key, device_tag(pid)))
     return plan
+
+
+def device_tag(pid: int) -> int:
+    """Tag id as the device sees it (8 bits; 254 and 255 are reserved)."""
+    return pid % 254
 
 
 # ------------------------------------------------------------------------- balancing
@@ -383,17 +426,76 @@ def _link(tasks, first, ev, plan, ops, oi, prev_event, prev_count):
         ts.flagged_out = plan[oi]["out"][1] if "out" in plan[oi] else -1
 
 
+def tensor_dependencies(ops, serving: bool):
+    """Which operator each operator has to wait for, derived from the tensors they read and
+    write (the reference derives its events the same way, src/kernel/runtime.cc:446-503),
+    instead of chaining every operator to its predecessor.  Operator j must run after the
+    last writer of everything it reads (read after write), after the readers of what it
+    overwrites and after its previous writer.  A task carries one dependency event, so j
+    waits for the latest of those operators, m, provided m's completion implies the others'
+    (they are among the operators m itself, transitively, waited for).  Returns the list of
+    operator indices (-1: none), or None when one event per task cannot express the graph,
+    or when, in serving mode, completion of the last operator would not imply completion of
+    all (the iteration boundary waits for the last operator only); the caller then keeps the
+    chain."""
+    n = len(ops)
+    last_writer, readers_since = {}, {}
+    dep, anc = [-1] * n, [None] * n
+    for j, op in enumerate(ops):
+        reads = [id(t) for _, t in _op_inputs(op)]
+        writes = [id(t) for t in _op_outputs(op)]
+        if op.kind == "attention":
+            # appends to the caches it reads; all attention operators share the split scratch
+            reads += [id(op.t["k_cache"]), id(op.t["v_cache"]), "attn_split_scratch"]
+            writes += [id(op.t["k_cache"]), id(op.t["v_cache"]), "attn_split_scratch"]
+        if op.kind == "allreduce":
+            reads.append("allreduce_exchange")
+            writes.append("allreduce_exchange")
+        need = set()
+        for t in reads:
+            if t in last_writer:
+                need.add(last_writer[t])
+        for t in writes:
+            if t in last_writer:
+                need.add(last_writer[t])
+            need |= readers_since.get(t, set())
+        need.discard(j)
+        if need:
+            m = max(need)
+            if need <= anc[m]:
+                dep[j] = m
+            elif need <= anc[j - 1]:
+                dep[j] = j - 1
+            else:
+                return None
+            anc[j] = {j} | anc[dep[j]]
+        else:
+            anc[j] = {j}
+        for t in reads:
+            readers_since.setdefault(t, set()).add(j)
+        for t in writes:
+            last_writer[t] = j
+            readers_since[t] = set()
+    if serving and anc[n - 1] != set(range(n)):
+        return None
+    return dep
+
+
 def _is16(t: DTensor):
     return t.dtype in (bfloat16, float16)
 
 
 def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_requests: int,
           max_seq_length: int, page_size: int, world_size: int = 1, rank: int = 0,
-          default_eps: float = 1e-6, new_tensor=None, handoff: str = "auto") -> LoweredGraph:
+          default_eps: float = 1e-6, new_tensor=None, handoff: str = "auto",
+          serving: bool = True) -> LoweredGraph:
     """Fuse, cut into tasks, assign to workers.  `new_tensor(dims, dtype, name)` creates
-    runtime-owned scratch tensors (attention split partials and arrival counters).
-    `handoff`: "event" = every operator waits for its predecessor's event; "ll" = flagged
-    words where possible (at most 8 tokens); "auto" = "ll" when max_tokens <= 8."""
+    runtime-owned scratch tensors (attention split partials, flagged-word buffers).
+    `handoff`: "event" = operators wait for events; "ll" = flagged words where possible (at
+    most 8 tokens); "auto" = "ll" when max_tokens <= 8.  `serving`: the graph runs iteration
+    after iteration with the batcher in between (offline mode) rather than once per launch.
+    Where no tensor travels as flagged words the events follow the tensors
+    (`tensor_dependencies`): independent operators do not wait for each other."""
     ops = fuse(regs, default_eps)
     if handoff == "auto":
         handoff = "ll" if max_tokens <= 8 else "event"
@@ -433,7 +535,7 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
     allreduce_tasks: List[TaskSpec] = []
 
     attn_scratch = None
-    attn_counters = None
+    attn_tag_ids = set()
     prev_event, prev_count = -1, 0
 
     for oi, op in enumerate(ops):
@@ -451,7 +553,7 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                 nc = cols if k < ntask - 1 else hidden - c
                 ts = TaskSpec(N.TASK_EMBED, op_id=oi)
                 ts.ptr[0], ts.ptr[1], ts.ptr[2] = (ids, 0), (table, 0), (o, 0)
-                ts.iarg[:5] = [hidden, c, nc, table.dims[1], o.dims[1]]
+                ts.iarg[:6] = [hidden, c, nc, table.dims[1], o.dims[1], table.dims[0]]
                 ts.worker = (rr + k) % W
                 tasks.append(ts)
                 c += nc
@@ -518,14 +620,14 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                                    res.dims[1] if res is not None else 0, 0]
                     if flags & N.F_LL_IN:
                         ts.ptr[5] = (ll_bufs[ll["x"][0]], 0)
-                        ts.iarg[10] = ll["x"][1]
+                        ts.iarg[10] = device_tag(ll["x"][1])
                     if flags & N.F_LL_RES:
                         ts.ptr[6] = (ll_bufs[ll["res"][0]], 0)
-                        ts.iarg[11] = ll["res"][1]
+                        ts.iarg[11] = device_tag(ll["res"][1])
                     if flags & N.F_LL_OUT:
                         key, pid, push, T = ll["out"]
                         ts.ptr[7] = (ll_buffer(key, T, push), 0)
-                        ts.iarg[12] = pid
+                        ts.iarg[12] = device_tag(pid)
                     ts.farg[0] = float(op.attrs.get("eps", default_eps))
                     ts.worker = wk
                     ts.weight_bytes = take * K * 2
@@ -553,7 +655,23 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                 need = 2 * max_requests * hkv * nsplit * max_rows * ATTN_ROW_FLOATS
                 if attn_scratch is None or attn_scratch.dims[0] < need:
                     attn_scratch = scratch((need,), float32, "attn_split_scratch")
-                    attn_counters = scratch((max_requests * hkv,), int32, "attn_split_counters")
+                # all layers share the scratch: the tags of two attention operators must differ
+                if oi % 254 in attn_tag_ids:
+                    raise NotImplementedError("two attention operators 254 operators apart share "
+                                              "a split-KV tag; reduce the graph or the splits")
+                attn_tag_ids.add(oi % 254)
+            qk_packed = None
+            if op.flags & N.F_QK_NORM:
+                qk_packed = op.attrs["qk_norm_packed"]
+                if id(qk_packed) not in shuffled_done:
+                    qn_t, kn_t = op.attrs["q_norm"], op.attrs["k_norm"]
+                    if not (qn_t.dims == kn_t.dims == (HEAD_DIM,) and _is16(qn_t) and qn_t.dtype == kn_t.dtype
+                            and qn_t.dtype == qkv.dtype):
+                        raise ValueError("q_norm / k_norm must be 16-bit vectors of head_dim entries")
+                    sh = {"dst": qk_packed, "sources": [qn_t, kn_t], "rows": [1, 1], "gran": [1, 1],
+                          "row_bytes": HEAD_DIM * 2}
+                    shuffles.append(sh)
+                    shuffled_done[id(qk_packed)] = sh
             k = 0
             for r in range(max_requests):
                 for h in range(hkv):
@@ -563,18 +681,23 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                         if op.flags & N.F_ROPE:
                             ts.ptr[4], ts.ptr[5] = (op.t["cos"], 0), (op.t["sin"], 0)
                         if nsplit > 1:
-                            ts.ptr[6], ts.ptr[7] = (attn_scratch, 0), (attn_counters, 0)
+                            ts.ptr[6] = (attn_scratch, 0)
+                        if qk_packed is not None:
+                            ts.ptr[7] = (qk_packed, 0)
+                            ts.farg[0] = float(op.attrs["eps"])
                         ts.iarg[:9] = [r, h, s, nsplit, G, hkv, qkv.dims[1], o.dims[1], max_rows]
                         ts.iarg[13] = oi % 254     # tag id of the split-KV partials
                         if "qkv" in plan[oi]:    # packed q/k/v arrive as flagged words
                             ts.flags |= N.F_LL_IN
+                            ts.logical_in.append((qkv, 0))
                             ts.ptr[0] = (ll_bufs[plan[oi]["qkv"][0]], 0)
-                            ts.iarg[11] = plan[oi]["qkv"][1]
+                            ts.iarg[11] = device_tag(plan[oi]["qkv"][1])
                         if "out" in plan[oi]:    # and the result leaves the same way
                             key, pid, _, Tout = plan[oi]["out"]
                             ts.flags |= N.F_LL_OUT
+                            ts.logical_out.append((o, 0))
                             ts.ptr[3] = (ll_buffer(key, Tout, False), 0)
-                            ts.iarg[12] = pid
+                            ts.iarg[12] = device_tag(pid)
                         # splits of one (request, head) go to different workers
                         ts.worker = (rr + k) % W
                         tasks.append(ts)
@@ -592,7 +715,8 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
             for p in range(nparts):
                 ts = TaskSpec(N.TASK_ARGMAX_PARTIAL, op_id=oi)
                 ts.ptr[0], ts.ptr[1], ts.ptr[2] = (x, 0), (pv, 0), (pi, 0)
-                ts.iarg[:5] = [p * per, per, x.dims[1], p, pv.dims[1]]
+                ts.iarg[:6] = [p * per, per, x.dims[1], p, pv.dims[1],
+                               int(op.attrs.get("valid_cols") or 0)]
                 ts.worker = (rr + p) % W
                 tasks.append(ts)
             rr += nparts
@@ -679,7 +803,7 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                     ts.ptr[7] = (ll_buffer(key_o, T2, False), 0)
                     ts.iarg[:10] = [k * ALLREDUCE_TILE, ALLREDUCE_TILE, x.dims[1], o.dims[1], hidden,
                                     max_tokens, 0, 0, world_size, rank]
-                    ts.iarg[10], ts.iarg[12] = plan[oi]["in"][1], aid
+                    ts.iarg[10], ts.iarg[12] = device_tag(plan[oi]["in"][1]), device_tag(aid)
                     ts.worker = (rr + k) % W
                     tasks.append(ts)
                 rr += ntile
@@ -698,8 +822,10 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
             for k in range(ntile):
                 ts = TaskSpec(N.TASK_ALLREDUCE, op_id=oi)
                 ts.ptr[0], ts.ptr[1], ts.ptr[2] = (x, 0), (comm_buf, 0), (o, 0)
+                # iarg[6] = index among the iteration's all-reduces, iarg[10] (filled in below)
+                # their number: the device derives the buffer half from the running count
                 ts.iarg[:10] = [k * ALLREDUCE_TILE, ALLREDUCE_TILE, x.dims[1], o.dims[1], hidden,
-                                max_tokens, num_allreduce % 2, sig0 + k, world_size, rank]
+                                max_tokens, num_allreduce, sig0 + k, world_size, rank]
                 ts.worker = (rr + k) % W
                 tasks.append(ts)
                 allreduce_tasks.append(ts)
@@ -711,10 +837,24 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
         _link(tasks, first, ev, plan, ops, oi, prev_event, prev_count)
         prev_event, prev_count = ev, count
 
+    if all(not p for p in plan.values()):
+        dep = tensor_dependencies(ops, serving)
+        if dep is not None:
+            by_op: Dict[int, List[TaskSpec]] = {}
+            for ts in tasks:
+                by_op.setdefault(ts.op_id, []).append(ts)
+            awaited = {d for d in dep if d >= 0}
+            for j in range(len(ops)):
+                for ts in by_op[j]:
+                    ts.dep_event = dep[j]
+                    ts.dep_count = len(by_op[dep[j]]) if dep[j] >= 0 else 0
+                    ts.trig_event = j if (j in awaited or j == len(ops) - 1) else -1
+
     if allreduce_tasks:
         signals = scratch((num_signals,), int64, "allreduce_signals", symmetric=True)
         for ts in allreduce_tasks:
             ts.ptr[3] = (signals, 0)
+            ts.iarg[10] = num_allreduce
 
     # queues: tasks of a worker in task (= operator) order
     per_worker: List[List[int]] = [[] for _ in range(W)]
@@ -775,44 +915,91 @@ _REF_TASK_TYPE = {  # TaskType numbers of the reference (runtime_header.h:62-124
     N.TASK_EMBED: 101, N.TASK_LINEAR: 253, N.TASK_ATTENTION: 257, N.TASK_ARGMAX_PARTIAL: 259,
     N.TASK_ARGMAX_REDUCE: 258, N.TASK_RMSNORM: 154, N.TASK_SILU_MUL: 118, N.TASK_ALLREDUCE: 107,
 }
+REF_TASK_NAMES = {101: "TASK_EMBEDDING", 253: "TASK_LINEAR_SM100", 252: "TASK_LINEAR_WITH_RESIDUAL_SM100",
+                  257: "TASK_ATTN_SM100", 259: "TASK_ARGMAX_PARTIAL_SM100",
+                  258: "TASK_ARGMAX_REDUCE_SM100", 154: "TASK_RMS_NORM_HOPPER", 118: "TASK_SILU_MUL",
+                  107: "TASK_REDUCE"}
+EVENT_INVALID_ID = 0x7ffffffffffffffe     # runtime_header.h:55: "no event"
+EVENT_LAUNCH_DEPENDENT_TASKS = 903        # runtime_header.h:126-134
+EVENT_END_OF_TASK_GRAPH = 910
+_JSON_DTYPES = (940, 941, 965)            # fp16, bf16, int64: what the reference's tools accept
+# pointer slots of ypk_task that a task writes, by task type (the rest are inputs)
+_OUTPUT_SLOTS = {N.TASK_EMBED: (2,), N.TASK_LINEAR: (2,), N.TASK_ATTENTION: (3,),
+                 N.TASK_ARGMAX_PARTIAL: (1, 2), N.TASK_ARGMAX_REDUCE: (2,), N.TASK_RMSNORM: (2,),
+                 N.TASK_SILU_MUL: (1,), N.TASK_ALLREDUCE: (2,)}
+
+
+# pointer slots that hold runtime-internal buffers (flagged-word copies, exchange areas, scratch)
+_INTERNAL_SLOTS = {N.TASK_LINEAR: (5, 6, 7), N.TASK_ALLREDUCE: (1, 3, 7), N.TASK_ATTENTION: (6,),
+                   N.TASK_ARGMAX_REDUCE: (3,)}
+
+
+def ref_task_type(ts: TaskSpec) -> int:
+    """TaskType number of the reference task this task stands for (runtime_header.h:62-124)."""
+    if ts.type == N.TASK_LINEAR and (ts.flags & N.F_RESIDUAL):
+        return 252
+    return _REF_TASK_TYPE.get(ts.type, ts.type)
 
 
 def to_json(g: LoweredGraph) -> str:
-    """Task graph in the layout of the reference's task_graph.json (runtime.cc:847-1318):
-    all_tasks / all_events / first_tasks, operands named by the name given at
-    attach_input / new_tensor, offsets in bytes."""
+    """Task graph in the layout of the reference's task_graph.json (src/kernel/runtime.cc:
+    847-1318), so that its tools (scripts/display_task_graph.py) read it: all_tasks with
+    task_type / variant_id / inputs / outputs / trigger_event / dependent_event / request_id /
+    expert_offset, operands as {base_ptr = the name given at attach_input / new_tensor, offset
+    in bytes, data_type, dims, strides}, all_events with event_type / num_triggers /
+    first_task_id / last_task_id, and first_tasks.  "No event" is EVENT_INVALID_ID as there.
+    What the reference has no field for sits under each task's "ypk" key (and the worker
+    queues under the top-level "ypk_queues"): worker, operator, the task's integer
+    arguments, flagged-word tags, and the runtime-internal operands (flagged-word buffers,
+    split scratch), whose element types the reference's tools do not know."""
     def operand(ref):
-        if ref is None:
-            return {"base_ptr": "nullptr", "offset": 0, "dims": [], "strides": [], "data_type": 999}
         t, off = ref
         return {"base_ptr": t.name or f"tensor_{t.guid}", "offset": off, "dims": list(t.dims),
                 "strides": list(t.strides), "data_type": t.dtype.code}
 
+    def event_id(e):
+        return e if e >= 0 else EVENT_INVALID_ID
+
     tasks = []
     for ti, ts in enumerate(g.tasks):
+        outs = _OUTPUT_SLOTS.get(ts.type, ())
+        inputs, outputs, internal = [], [], []
+        for slot, p in enumerate(ts.ptr):
+            if p is None:
+                continue
+            o = operand(p)
+            if o["data_type"] not in _JSON_DTYPES or slot in _INTERNAL_SLOTS.get(ts.type, ()):
+                o["slot"] = slot
+                internal.append(o)
+            elif slot in outs:
+                outputs.append(o)
+            else:
+                inputs.append(o)
+        inputs += [operand(p) for p in ts.logical_in]
+        outputs += [operand(p) for p in ts.logical_out]
         tasks.append({
-            "task_type": _REF_TASK_TYPE.get(ts.type, ts.type),
-            "ypk_task_type": N.TASK_NAMES[ts.type],
-            "variant_id": ts.flags,
-            "inputs": [operand(p) for p in ts.ptr if p is not None],
-            "outputs": [],
-            "trigger_event": ts.trig_event,
-            "dependent_event": ts.dep_event,
-            "dependent_count": ts.dep_count,
-            "worker": ts.worker,
-            "op_id": ts.op_id,
-            "flagged_inputs": list(ts.flagged_deps),
-            "flagged_output": ts.flagged_out,
-            "iarg": list(ts.iarg),
+            "task_type": ref_task_type(ts),
+            "variant_id": 0,
+            "inputs": inputs,
+            "outputs": outputs,
+            "trigger_event": event_id(ts.trig_event),
+            "dependent_event": event_id(ts.dep_event),
             "request_id": ts.iarg[0] if ts.type == N.TASK_ATTENTION else -1,
+            "expert_offset": -1,
+            "ypk": {"task_type": N.TASK_NAMES[ts.type], "flags": ts.flags, "worker": ts.worker,
+                    "op_id": ts.op_id, "dependent_count": ts.dep_count, "iarg": list(ts.iarg),
+                    "farg": list(ts.farg), "flagged_inputs": list(ts.flagged_deps),
+                    "flagged_output": ts.flagged_out, "internal_operands": internal},
         })
     events = []
+    last_event = max((ts.trig_event for ts in g.tasks), default=-1)
     for e in range(g.num_events):
         ids = [i for i, ts in enumerate(g.tasks) if ts.dep_event == e]
-        events.append({"event_type": 902,  # EVENT_EMPTY: consumers poll the counter
+        events.append({"event_type": EVENT_END_OF_TASK_GRAPH if (e == last_event and not ids)
+                       else EVENT_LAUNCH_DEPENDENT_TASKS,
                        "num_triggers": sum(1 for ts in g.tasks if ts.trig_event == e),
                        "first_task_id": ids[0] if ids else 0,
                        "last_task_id": ids[-1] + 1 if ids else 0})
     first = [i for i, ts in enumerate(g.tasks) if ts.dep_event < 0]
     return json.dumps({"all_tasks": tasks, "all_events": events, "first_tasks": first,
-                       "queues": {"queue": g.queue, "queue_off": g.queue_off}})
+                       "ypk_queues": {"queue": g.queue, "queue_off": g.queue_off}})

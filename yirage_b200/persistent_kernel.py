@@ -201,11 +201,19 @@ class PersistentKernel:
         assert grid_dim[1] == num_kv_heads
         name = {90: "paged_attention_hopper", 100: "paged_attention_sm100"}.get(
             self.target_cc, "paged_attention")
+        attrs = {}
+        if qk_norm:
+            # the two weight vectors are packed into one runtime-owned [2, head_dim] tensor when
+            # the graph is compiled (one pointer operand of the task)
+            packed = self.kn_graph.cygraph.new_input((2, head_dim), None, q_norm.dtype)
+            packed.kind, packed.name = "shuffled", f"{q_norm.name or 'q_norm'}+{k_norm.name or 'k_norm'}"
+            packed.sources, packed.num_groups = [q_norm, k_norm], 1
+            attrs = {"qk_norm_packed": packed, "eps": self.rms_norm_eps}
         self._register(name, [(input, (-1, 1, -1), -1), (k_cache, (-1, 2, -1), 1),
                               (v_cache, (-1, 2, -1), 1), (q_norm, (-1, -1, -1), -1),
                               (k_norm, (-1, -1, -1), -1), (cos_pos_embed, (-1, -1, -1), -1),
                               (sin_pos_embed, (-1, -1, -1), -1), (output, (-1, 1, -1), -1)],
-                       grid_dim, block_dim, params)
+                       grid_dim, block_dim, params, **attrs)
 
     def linear_layer(self, input: DTensor, weight: DTensor, output: DTensor, grid_dim: tuple,
                      block_dim: tuple):
@@ -241,7 +249,9 @@ class PersistentKernel:
                        grid_dim, block_dim)
 
     def argmax_partial_layer(self, input: DTensor, output: tuple, grid_dim: tuple,
-                             block_dim: tuple):
+                             block_dim: tuple, valid_cols: int = None):
+        """`valid_cols` (not in the reference): only logits columns [0, valid_cols) are real
+        vocabulary; the zero-padded tail of the lm_head is never sampled."""
         assert input.num_dims == 2
         assert len(output) == 2
         output_value, output_index = output
@@ -250,7 +260,8 @@ class PersistentKernel:
         self.argmax_partial_output_size = input.dim(1) // num_tasks
         name = "argmax_partial_sm100" if self.target_cc in (90, 100) else "argmax_partial"
         self._register(name, [(input, (1, 0, -1), -1), (output_value, (1, 0, -1), -1),
-                              (output_index, (1, 0, -1), -1)], grid_dim, block_dim, [num_tasks])
+                              (output_index, (1, 0, -1), -1)], grid_dim, block_dim, [num_tasks],
+                       valid_cols=None if valid_cols is None else int(valid_cols))
 
     def argmax_reduce_layer(self, input: tuple, output: DTensor, grid_dim: tuple,
                             block_dim: tuple, vocab_offset: int = 0, exchange: bool = False):
@@ -309,7 +320,7 @@ class PersistentKernel:
                 page_size=self.page_size,
                 world_size=self.world_size, rank=self.mpi_rank,
                 default_eps=self.rms_norm_eps,
-                new_tensor=self._scratch_tensor,
+                new_tensor=self._scratch_tensor, serving=self.mode == "offline",
                 handoff=getattr(self, "handoff", None) or os.environ.get("YPK_HANDOFF", "auto"))
         return self._lowered
 

@@ -73,7 +73,14 @@ def export_trace(profiler_tensor: torch.Tensor, file_name: str, num_workers: int
         raise ValueError("export_trace needs the worker count and the records per worker")
     events = []
     for r in decode_records(profiler_tensor, num_workers, stride):
-        name = f"task {r['task']}" if tasks is None else f"op{tasks[r['task']].op_id}"
+        if tasks is None:
+            name = f"task {r['task']}"
+        else:
+            # event names as the reference's trace has them (python/yirage/profiler_persistent.py:
+            # 12-78: "<task type name>_<number>")
+            from .lowering import REF_TASK_NAMES, ref_task_type
+            ts = tasks[r["task"]]
+            name = f"{REF_TASK_NAMES.get(ref_task_type(ts), 'TASK')}_{ts.op_id}"
         events.append({"name": "wait", "ph": "X", "ts": r["fetch"] / 1e3,
                        "dur": (r["ready"] - r["fetch"]) / 1e3, "pid": 0, "tid": r["worker"]})
         events.append({"name": name, "ph": "X", "ts": r["ready"] / 1e3,
