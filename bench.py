@@ -2,18 +2,25 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE.json configs[3]): random-init Llama-3-8B, bf16, batch 1, a 512-token
-prompt of uniform-random ids, greedy decode; seed 3.  One "step" is one decode iteration
-of the megakernel (one new token per sequence): the prompt is prefilled untimed, W decode
-iterations warm up, then exactly K iterations are timed with CUDA events around one
-persistent-kernel launch.  Prints one JSON line (rank 0).
+Headline workload (BASELINE.json configs[3]): random-init Llama-3-8B, bf16, batch 1, a
+512-token prompt of uniform-random ids, greedy decode; seed 3.  One "step" is one decode
+iteration of the megakernel (one new token per sequence): the prompt is prefilled untimed, W
+decode iterations warm up, then exactly K iterations are timed with CUDA events around one
+persistent-kernel launch.  With N > 1 the same model runs under N-way tensor parallelism
+(strong scaling).  Prints one JSON line (rank 0).
 
  value      tokens/s over the K timed iterations, inputs resident in HBM
- e2e        tokens/s of a whole generation through PersistentKernel.__call__ with the
-            prompt starting in pinned host memory and the generated ids read back to the
-            host, prefill included in the time
+ e2e        tokens/s of a whole generation through PersistentKernel.__call__: the prompt starts
+            in pinned host memory, 256 tokens are generated (BASELINE's count, whatever
+            --steps is), the ids are read back to the host; prefill inside the time, with
+            prefill_ms / decode_ms and the decode-only rate beside it
  roofline   weight + KV bytes one iteration has to read / time per iteration, against the
             measured copy bandwidth in MEASURED_PEAKS.json
+ kernels    (N = 1) the task kernels on BASELINE configs[0..2]: achieved GB/s and fraction
+ batch16    (N = 1) configs[3] at batch 16
+ parity     (N > 1) a small model generated under N-way tensor parallelism just before the
+            timed runs: the ranks' tokens bit-equal, rank 0's replayed against the CPU oracle
+ llama3_70b (N > 1) configs[4]: the 70B shape at batch 1 / 8 / 64, context 2048
  cpu_baseline / --impl reference
             the CPU oracle (port of the reference's PyTorch model code) timed on the host
             cores on a bounded sample of the same workload
@@ -34,6 +41,7 @@ import torch  # noqa: E402
 
 DRAM_TRAFFIC_RATIO = 0.998   # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes, ncu, profiles/
 PROMPT_LEN = 512
+E2E_NEW_TOKENS = 256         # BASELINE configs[3]: 256 greedy decode steps
 SEED = 3
 FALLBACK_HBM_GBS = 6650.0
 
@@ -41,7 +49,7 @@ FALLBACK_HBM_GBS = 6650.0
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1)
@@ -54,6 +62,8 @@ def parse():
                     help="llama3-70b = BASELINE configs[4] (context 2048); needs --gpus >= 2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="headline line only: no kernels / batch16 / llama3_70b / parity sub-results")
     return ap.parse_args()
 
 
@@ -180,6 +190,35 @@ def cpu_decode_sample(shape, ctx, budget_s=20.0):
     return per_token, desc
 
 
+def cpu_prefill_sample(shape, prompt_len, chunk=64):
+    """Host time to prefill `prompt_len` tokens with the same arithmetic: the projections of
+    one layer on a chunk of tokens (causal attention inside the chunk left out: under 2 % of
+    the flops at these lengths), scaled to all chunks and layers.  Returns seconds."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(SEED)
+    h, f, d = shape.hidden_size, shape.intermediate_size, shape.head_dim
+    hq, hkv = shape.num_attention_heads, shape.num_key_value_heads
+    mk = lambda r, c: (torch.randn(r, c, generator=g) * 0.02).to(torch.bfloat16)
+    ws = [mk((hq + 2 * hkv) * d, h), mk(h, hq * d), mk(2 * f, h), mk(h, f)]
+    x = torch.randn(chunk, h, generator=g).to(torch.bfloat16)
+    a = torch.randn(chunk, f, generator=g).to(torch.bfloat16)
+
+    def layer():
+        torch.nn.functional.linear(x, ws[0])
+        torch.nn.functional.linear(x, ws[1])
+        torch.nn.functional.linear(x, ws[2])
+        torch.nn.functional.linear(a, ws[3])
+
+    layer()
+    t0 = time.perf_counter()
+    reps = 0
+    while time.perf_counter() - t0 < 3.0 and reps < 8:
+        layer()
+        reps += 1
+    t_layer = (time.perf_counter() - t0) / reps
+    return t_layer * shape.num_hidden_layers * ((prompt_len + chunk - 1) // chunk)
+
+
 # ------------------------------------------------------------------ reference arm
 def run_reference(args):
     from yirage_b200 import llama
@@ -191,73 +230,185 @@ def run_reference(args):
     # each "step" is a bounded sample of a decode token; keep the whole run to ~a minute
     budget = max(2.0, min(20.0, 60.0 / (K + W)))
     per = []
-    for i in range(min(K + W, 3)):
+    nsamples = min(K + W, 3)
+    for i in range(nsamples):
         t, desc = cpu_decode_sample(shape, PROMPT_LEN, budget_s=budget)
         per.append(t)
     t_tok = sorted(per)[len(per) // 2]
+    t_prefill = cpu_prefill_sample(shape, PROMPT_LEN)
     val = args.batch / t_tok
+    e2e_val = E2E_NEW_TOKENS / (t_prefill + E2E_NEW_TOKENS * t_tok)
     line = {
         "impl": "reference", "metric": "decode_tokens_per_second", "value": val, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": t_tok * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": "llama3-8b decode, batch 1, prompt 512 (BASELINE configs[3])",
-                   "note": "CPU port of the reference's PyTorch model code; the reference's native "
-                           "library cannot be built here and its model code needs a GPU"},
+        "scaled_from_sample": True,
+        "config": {"workload": "llama3-8b decode, batch 1, prompt 512, greedy (BASELINE configs[3])",
+                   "note": "CPU port of the reference's PyTorch model code (the reference's native "
+                           "library cannot be built here and its model code needs a GPU); the value "
+                           f"is the median of {nsamples} samples, each one layer timed and scaled to "
+                           "a token, not K full steps"},
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
                          "sample": desc},
-        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                "prefill_ms": t_prefill * 1e3, "decode_ms": E2E_NEW_TOKENS * t_tok * 1e3,
+                "new_tokens": E2E_NEW_TOKENS,
+                "note": f"{E2E_NEW_TOKENS} tokens after a {PROMPT_LEN}-token prompt: prefill estimated "
+                        "from one layer's projections on a 64-token chunk, decode from the sample above"},
+        "e2e_decode_only": {"value": val, "unit": "tokens/s"},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
 # ------------------------------------------------------------------ our arm
-def run_ours(args):
+def _dist():
     import torch.distributed as dist
-    from yirage_b200 import llama
+    return dist
 
+
+def max_over_ranks(value, dev, world):
+    if world == 1:
+        return value
+    t = torch.tensor([value], device=dev, dtype=torch.float64)
+    _dist().all_reduce(t, op=_dist().ReduceOp.MAX)
+    return float(t)
+
+
+def tp_parity_prelude(world, rank, dev):
+    """Correct tokens under N-way tensor parallelism, checked right here because the GPU test
+    box has one GPU: a 2-layer 512-wide model (16 q / 8 kv heads so that it shards 8 ways)
+    generates from three prompts through two request slots; every rank's token matrix must be
+    bit-equal, and rank 0's is replayed iteration by iteration against the CPU oracle on the
+    unsharded weights (each sampled token the oracle arg-max or inside the tolerance of it)."""
+    dist = _dist()
+    from yirage_b200 import llama
+    shape = llama.LlamaShape(hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                             num_attention_heads=16, num_key_value_heads=8, vocab_size=3000)
+    w = llama.init_weights(shape, dev, 3, world_size=world, rank=rank)
+    prompt_lens, max_seq = [9, 14, 5], 30
+    g = torch.Generator().manual_seed(3)
+    tokens = torch.zeros(len(prompt_lens), max_seq, dtype=torch.int64)
+    for r, n in enumerate(prompt_lens):
+        tokens[r, :n] = torch.randint(0, shape.vocab_size, (n,), generator=g)
+    tokens = tokens.to(dev)
+    plen = torch.tensor(prompt_lens, dtype=torch.int32, device=dev)
+    ypk, st = llama.build_decode_kernel(
+        shape, w, tokens=tokens, prompt_lengths=plen, max_num_batched_requests=2,
+        max_num_batched_tokens=8, max_num_pages=4, page_size=64, world_size=world, rank=rank)
+    dist.barrier()
+    ypk()
+    torch.cuda.synchronize()
+    status = ypk.status()
+    every = [torch.empty_like(tokens) for _ in range(world)]
+    dist.all_gather(every, tokens)
+    agree = all(torch.equal(every[0], t) for t in every[1:])
+    res = {"ranks_agree": bool(agree), "device_error": int(status.error), "world": world}
+    if rank == 0:
+        from tests.util import oracle_weights, replay_against_oracle
+        full = llama.init_weights(shape, dev, 3)
+        try:
+            iters, bs, _, exact, total = replay_against_oracle(
+                shape, oracle_weights(shape, full), tokens.cpu(), prompt_lens, max_seq=max_seq,
+                max_requests=2, max_tokens=8, max_pages=4, page_size=64)
+            ok = status.iterations == iters and st["meta"]["step"].cpu().tolist() == bs.step
+            res.update(oracle_ok=bool(ok and status.error == 0), tokens=int(total),
+                       exact_argmax_matches=int(exact), iterations=int(iters))
+        except AssertionError as e:
+            res.update(oracle_ok=False, tokens=0, failure=str(e)[:200])
+        del full
+    dist.barrier()
+    ypk.finalize()
+    del w, ypk, st
+    torch.cuda.empty_cache()
+    return res
+
+
+def time_decode(ypk, st, K, W, B, prompt_len, shape, dev, world, rank, sample_clocks=False,
+                synthetic_context=False):
+    """Bring every request to the decode phase (untimed), W warm-up iterations, then exactly K
+    iterations in one launch between two CUDA events; max over ranks.  Returns (ms, clocks)."""
+    dist = _dist()
+    ypk.reset()
+    if synthetic_context:
+        # the requests enter with `prompt_len` tokens taken as cached: their pages keep
+        # whatever the cache tensors hold (random values), no prefill is run
+        st["meta"]["step"].fill_(prompt_len - 1)
+    else:
+        chunk = min(8, 32 // (shape.num_attention_heads // shape.num_key_value_heads))
+        ypk(max_iterations=(prompt_len + chunk - 1) // chunk)
+    ypk(max_iterations=W)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(dev.index) if (sample_clocks and rank == 0) else None
+    if sampler:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    before = st["meta"]["step"].clone()
+    torch.cuda.synchronize()
+    ev0.record()
+    ypk(max_iterations=K)
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if sampler else None
+    done = int((st["meta"]["step"] - before).sum())
+    assert done == K * B, f"timed region ran {done} token-steps, expected {K * B}"
+    assert ypk.status().error == 0
+    return max_over_ranks(ms, dev, world), clocks
+
+
+def decode_bytes(shape, world, B, ctx):
+    """Algorithmic HBM bytes of one decode iteration on one GPU: its shard of every weight
+    (lm_head padded and split by vocabulary rows) + the K/V of its kv heads over `ctx` tokens."""
+    from yirage_b200 import llama
+    wbytes = shape.decode_weight_bytes(1, llama.padded_vocab(shape.vocab_size)) / world
+    kv = B * ctx * shape.num_hidden_layers * shape.num_key_value_heads * shape.head_dim * 2 * 2 / world
+    return wbytes, kv
+
+
+def run_ours(args):
+    from yirage_b200 import llama
+    dist = _dist()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
     K, W, B = args.steps, max(args.warmup, 3), args.batch
-    global PROMPT_LEN
     big = args.model == "llama3-70b"
     shape = llama.LlamaShape.llama3_70b() if big else llama.LlamaShape.llama3_8b()
-    if big:
-        PROMPT_LEN = 2048      # BASELINE configs[4]: context 2048
-        if world < 2:
-            raise SystemExit("llama3-70b (140 GB of weights) is a tensor-parallel configuration: --gpus 2/4/8")
+    prompt_len = 2048 if big else PROMPT_LEN
+    if big and world < 2:
+        raise SystemExit("llama3-70b (140 GB of weights) is a tensor-parallel configuration: --gpus 2/4/8")
     if args.layers:
         shape.num_hidden_layers = args.layers
-    # 8 prompt tokens per request and iteration: all requests prefill in lockstep and reach
-    # the decode phase together (with fewer token slots the first requests would already be
-    # hundreds of tokens into their generation when the last one finishes its prompt)
+    extras = not args.no_extras and not args.layers and not big
+
+    parity = tp_parity_prelude(world, rank, dev) if (world > 1 and not args.no_extras) else None
+
+    # ---- headline: 8 prompt tokens per request and iteration; all requests prefill in lockstep
     MT = 8 * B
-    max_seq = PROMPT_LEN + W + K + 2
+    # a request retires at max_seq_length - 1 tokens: with this length the end-to-end run
+    # below generates exactly E2E_NEW_TOKENS per request on the same kernel
+    gen_seq = prompt_len + E2E_NEW_TOKENS + 1
+    max_seq = gen_seq if W + K + 2 <= E2E_NEW_TOKENS else prompt_len + W + K + 2
     page = 64
     pages_per_req = (max_seq + page - 1) // page
-
-    def fresh_tokens():
-        g = torch.Generator().manual_seed(SEED)
-        t = torch.zeros(B, max_seq, dtype=torch.int64)
-        t[:, :PROMPT_LEN] = torch.randint(0, shape.vocab_size, (B, PROMPT_LEN), generator=g)
-        return t
-
-    host_tokens = fresh_tokens().pin_memory()
-    host_plen = torch.full((B,), PROMPT_LEN, dtype=torch.int32).pin_memory()
-    tokens = host_tokens.to(dev)
-    plen = host_plen.to(dev)
+    g = torch.Generator().manual_seed(SEED)
+    host_tokens = torch.zeros(B, max_seq, dtype=torch.int64)
+    host_tokens[:, :prompt_len] = torch.randint(0, shape.vocab_size, (B, prompt_len), generator=g)
+    host_tokens = host_tokens.pin_memory()
+    host_plen = torch.full((B,), prompt_len, dtype=torch.int32).pin_memory()
+    tokens, plen = host_tokens.to(dev), host_plen.to(dev)
     # N > 1: tensor parallelism over the N GPUs (column-split qkv / gate / up, row-split
     # o_proj / down_proj, in-kernel all-reduce over NVLink after each row-split projection;
-    # lm_head split by vocabulary rows, arg-max winners exchanged).  The total work is fixed,
-    # so the scaling is "strong".
-    if world > 1:
-        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    # lm_head split by vocabulary rows, arg-max winners exchanged).  Total work is fixed.
     weights = llama.init_weights(shape, dev, SEED, world_size=world, rank=rank)
     ypk, st = llama.build_decode_kernel(
         shape, weights, tokens=tokens, prompt_lengths=plen, max_num_batched_requests=B,
@@ -266,88 +417,121 @@ def run_ours(args):
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
+    ms, clocks = time_decode(ypk, st, K, W, B, prompt_len, shape, dev, world, rank, sample_clocks=True)
 
-    # every request advances min(8, 32 / q-heads-per-kv-head) prompt tokens per iteration
-    chunk = min(8, 32 // (shape.num_attention_heads // shape.num_key_value_heads))
-    prefill_iters = (PROMPT_LEN + chunk - 1) // chunk
-
-    def run_to_decode():
-        """Prefill the prompts (untimed): iterate until every request is decoding."""
-        ypk.reset()
-        if prefill_iters is not None:
-            ypk(max_iterations=prefill_iters)
-        else:
-            for _ in range(100000):
-                ypk(max_iterations=1)
-                if int(st["meta"]["step"].min()) >= PROMPT_LEN:
-                    break
-
-    if world > 1:
-        dist.barrier()
-    run_to_decode()
-    ypk(max_iterations=W)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    step_before = st["meta"]["step"].clone()
-    torch.cuda.synchronize()
-    ev0.record()
-    ypk(max_iterations=K)
-    ev1.record()
-    torch.cuda.synchronize()
-    ms = ev0.elapsed_time(ev1)
-    clocks = sampler.stop() if rank == 0 else None
-    done = int((st["meta"]["step"] - step_before).sum())
-    assert done == K * B, f"timed region ran {done} token-steps, expected {K * B}"
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t)
-
-    # ---- end-to-end: whole generation through the public call, host buffers in and out
-    e2e = None
+    # ---- end to end: one whole generation through the public call, host buffers in and out,
+    # always E2E_NEW_TOKENS new tokens per request (max_seq_length ends the generation)
+    e2e = e2e_decode_only = None
     if not args.no_e2e:
-        host_out = torch.empty_like(host_tokens).pin_memory()
+        chunk = min(8, 32 // (shape.num_attention_heads // shape.num_key_value_heads))
+        prefill_iters = (prompt_len + chunk - 1) // chunk
+        if max_seq == gen_seq:
+            ypk2, st2, e_tokens, e_host = ypk, st, tokens, host_tokens
+        else:       # more timed steps than the generation is long: a second kernel of the right length
+            e_tokens = torch.zeros(B, gen_seq, dtype=torch.int64, device=dev)
+            e_host = torch.zeros(B, gen_seq, dtype=torch.int64)
+            e_host[:, :prompt_len] = host_tokens[:, :prompt_len]
+            e_host = e_host.pin_memory()
+            ypk2, st2 = llama.build_decode_kernel(
+                shape, weights, tokens=e_tokens, prompt_lengths=plen, max_num_batched_requests=B,
+                max_num_batched_tokens=MT, max_num_pages=((gen_seq + page - 1) // page) * B,
+                page_size=page, world_size=world, rank=rank)
+        host_out = torch.empty_like(e_host).pin_memory()
         host_step = torch.empty(B, dtype=torch.int32).pin_memory()
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         t0 = time.perf_counter()
-        tokens.copy_(host_tokens, non_blocking=True)
+        e_tokens.copy_(e_host, non_blocking=True)
         plen.copy_(host_plen, non_blocking=True)
-        ypk.reset()
-        ypk()
-        host_out.copy_(tokens, non_blocking=True)
-        host_step.copy_(st["meta"]["step"], non_blocking=True)
+        ypk2.reset()
+        ypk2(max_iterations=prefill_iters)      # the launch returns when the prompt is in
         torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
-        gen = int((host_step.to(torch.int64) + 1 - PROMPT_LEN).sum())
-        iters = int(ypk.status().iterations)
-        if world > 1:
-            t = torch.tensor([dt], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            dt = float(t)
-        h2d = host_tokens.numel() * 8 + host_plen.numel() * 4
+        t1 = time.perf_counter()
+        ypk2()                                   # decode until every request has retired
+        host_out.copy_(e_tokens, non_blocking=True)
+        host_step.copy_(st2["meta"]["step"], non_blocking=True)
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        gen = int((host_step.to(torch.int64) + 1 - prompt_len).sum())
+        iters = int(ypk2.status().iterations)
+        dt = max_over_ranks(t2 - t0, dev, world)
+        t_pre = max_over_ranks(t1 - t0, dev, world)
+        h2d = e_host.numel() * 8 + host_plen.numel() * 4
         d2h = host_out.numel() * 8 + host_step.numel() * 4
         e2e = {"value": gen / dt, "unit": "tokens/s",
                "h2d_bytes_per_step": h2d / max(1, iters), "d2h_bytes_per_step": d2h / max(1, iters),
-               "note": f"{gen} generated tokens, {iters} iterations incl. chunked prefill of the "
-                       f"{PROMPT_LEN}-token prompt, host->device prompt copy and device->host token read-back inside the time"}
+               "new_tokens": gen, "iterations": iters,
+               "prefill_ms": t_pre * 1e3, "decode_ms": (dt - t_pre) * 1e3,
+               "note": f"{gen} generated tokens after a {prompt_len}-token prompt ({prefill_iters} chunked-"
+                       "prefill iterations), prompt copied from pinned host memory, token matrix and step "
+                       "counters read back; independent of --steps"}
+        e2e_decode_only = {"value": gen / max(1e-9, dt - t_pre), "unit": "tokens/s",
+                           "note": "same run, prefill time taken out (the device->host read-back stays in)"}
+        if ypk2 is not ypk:
+            ypk2.finalize()
+        del ypk2, st2, e_tokens
+
+    sub = {}
+    if extras and world == 1:
+        # ---- BASELINE configs[3] at batch 16 (same weights): 16 requests, 8 token slots each
+        try:
+            B16, K16 = 16, max(8, min(K, 48))
+            mseq = prompt_len + W + K16 + 2
+            tk = torch.zeros(B16, mseq, dtype=torch.int64)
+            tk[:, :prompt_len] = torch.randint(0, shape.vocab_size, (B16, prompt_len), generator=g)
+            tk = tk.to(dev)
+            pl16 = torch.full((B16,), prompt_len, dtype=torch.int32, device=dev)
+            y16, s16 = llama.build_decode_kernel(
+                shape, weights, tokens=tk, prompt_lengths=pl16, max_num_batched_requests=B16,
+                max_num_batched_tokens=8 * B16, max_num_pages=((mseq + page - 1) // page) * B16,
+                page_size=page)
+            ms16, _ = time_decode(y16, s16, K16, W, B16, prompt_len, shape, dev, 1, 0)
+            wb, kvb = decode_bytes(shape, 1, B16, prompt_len + W + K16 / 2.0)
+            hbm, src = peaks()
+            ach = (wb + kvb) / (ms16 / 1e3 / K16) / 1e9
+            sub["batch16"] = {"ms_per_step": ms16 / K16, "tokens_per_s": K16 * B16 / (ms16 / 1e3),
+                              "steps": K16, "achieved_gbs": ach, "frac": ach / hbm,
+                              "frac_of": f"{src} copy bandwidth",
+                              "tensor_core_tasks": int(y16.status().tensor_core_tasks),
+                              "workload": "llama3-8b decode, batch 16, prompt 512 (BASELINE configs[3])"}
+            y16.finalize()
+            del y16, s16, tk
+        except Exception as e:   # a sub-result must not take the headline down
+            sub["batch16"] = {"error": str(e)[:300]}
+    ypk.finalize()
+    del ypk, st, weights
+    torch.cuda.empty_cache()
+
+    if extras and world == 1:
+        ks = {}
+        for key, wl, b in (("rmsnorm_linear", "rmsnorm_linear", 8), ("gated_mlp_b8", "gated_mlp", 8),
+                           ("gated_mlp_b16", "gated_mlp", 16), ("gated_mlp_b64", "gated_mlp", 64),
+                           ("attention", "attention", 8)):
+            try:
+                r = measure_kernel(wl, b, steps=20, warmup=3)
+                ks[key] = {"gbs": r["achieved"], "frac": r["frac"], "us_per_operator": r["us_per_operator"],
+                           "ms_per_step": r["ms"], "tensor_core_tasks": r["tensor_core_tasks"],
+                           "workload": r["name"]}
+            except Exception as e:
+                ks[key] = {"error": str(e)[:300]}
+            torch.cuda.empty_cache()
+        sub["kernels"] = ks
+
+    if extras and world > 1:
+        # ---- BASELINE configs[4]: Llama-3-70B shape, context 2048, batch 1 / 8 / 64
+        try:
+            sub["llama3_70b"] = run_70b(world, rank, dev, steps=max(4, min(K, 16)), warmup=3)
+        except Exception as e:
+            sub["llama3_70b"] = {"error": str(e)[:300]}
 
     if rank != 0:
         if world > 1:
+            dist.barrier()
             dist.destroy_process_group()
         return
     hbm, src = peaks()
-    vpad = llama.padded_vocab(shape.vocab_size)
-    # per GPU: its shard of every weight (the lm_head by vocabulary rows) + its kv heads
-    wbytes = shape.decode_weight_bytes(1, vpad) / world
-    ctx_mid = PROMPT_LEN + W + K / 2.0
-    kv_bytes = B * ctx_mid * shape.num_hidden_layers * shape.num_key_value_heads * shape.head_dim * 2 * 2 / world
+    wbytes, kv_bytes = decode_bytes(shape, world, B, prompt_len + W + K / 2.0)
     alg = wbytes + kv_bytes
     per_iter_s = ms / 1e3 / K
     achieved = alg / per_iter_s / 1e9
@@ -355,9 +539,9 @@ def run_ours(args):
         "metric": "decode_tokens_per_second", "value": K * B / (ms / 1e3), "unit": "tokens/s",
         "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
         "us_per_token": ms * 1e3 / K / B,
-        "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{args.model} decode, batch {B}, prompt {PROMPT_LEN}, greedy "
+        "config": {"workload": f"{args.model} decode, batch {B}, prompt {prompt_len}, greedy "
                                f"(BASELINE configs[{4 if big else 3}])",
                    "layers": shape.num_hidden_layers, "page_size": page,
                    "parallelism": f"tp{world}" if world > 1 else "single",
@@ -378,18 +562,82 @@ def run_ours(args):
     }
     if e2e is not None:
         line["e2e"] = e2e
-    if not args.no_cpu_baseline:
-        t_tok, desc = cpu_decode_sample(shape, PROMPT_LEN, budget_s=15.0)
+        line["e2e_decode_only"] = e2e_decode_only
+    if parity is not None:
+        line["parity"] = parity
+    line.update(sub)
+    if not args.no_cpu_baseline and world == 1:
+        t_tok, desc = cpu_decode_sample(shape, prompt_len, budget_s=15.0)
         line["cpu_baseline"] = {"value": 1.0 / t_tok, "unit": "tokens/s", "cores": os.cpu_count(),
                                 "kind": "port", "sample": desc}
     print(json.dumps(line), flush=True)
-    ypk.finalize()
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
+def run_70b(world, rank, dev, steps, warmup):
+    """BASELINE configs[4] on the N GPUs of this run: Llama-3-70B shape (weights generated on
+    the device per shard, ~139 GB / N per GPU), context 2048, batch 1, 8 and 64.  The context
+    is synthetic: the requests enter the batcher with 2048 tokens taken as cached and the
+    cache tensors hold random values, so no prefill of 2048 x batch tokens is run (at batch
+    64 it would take minutes); the timed iterations read weights and 2048 tokens of K/V per
+    request exactly as after a real prefill."""
+    from yirage_b200 import llama
+    dist = _dist()
+    shape = llama.LlamaShape.llama3_70b()
+    ctx, page = 2048, 64
+    weights = llama.init_weights(shape, dev, 4, world_size=world, rank=rank)
+    hbm, src = peaks()
+    out = {"workload": "llama3-70b shape decode, context 2048 (BASELINE configs[4]), synthetic context",
+           "parallelism": f"tp{world}", "steps": steps, "batch": {}}
+    free_b, _ = torch.cuda.mem_get_info()
+    for B in (1, 8, 64):
+        try:
+            mseq = ctx + warmup + steps + 2
+            pages = ((mseq + page - 1) // page) * B
+            hkv = shape.num_key_value_heads // world
+            kv_need = 2 * shape.num_hidden_layers * pages * page * hkv * shape.head_dim * 2
+            free_b, _ = torch.cuda.mem_get_info()
+            if kv_need > 0.9 * free_b:
+                out["batch"][str(B)] = {"skipped": f"KV cache of {kv_need / 1e9:.0f} GB does not fit beside the weights"}
+                continue
+            g = torch.Generator().manual_seed(4)
+            tk = torch.zeros(B, mseq, dtype=torch.int64)
+            tk[:, :ctx] = torch.randint(0, shape.vocab_size, (B, ctx), generator=g)
+            tk = tk.to(dev)
+            pl = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+            kc = torch.empty(shape.num_hidden_layers, pages, page, hkv, shape.head_dim,
+                             dtype=torch.bfloat16, device=dev).normal_()
+            vc = torch.empty_like(kc).normal_()
+            ypk, st = llama.build_decode_kernel(
+                shape, weights, tokens=tk, prompt_lengths=pl, max_num_batched_requests=B,
+                max_num_batched_tokens=max(8, B), max_num_pages=pages, page_size=page,
+                world_size=world, rank=rank, k_cache=kc, v_cache=vc)
+            dist.barrier()
+            ms, _ = time_decode(ypk, st, steps, warmup, B, ctx, shape, dev, world, rank,
+                                synthetic_context=True)
+            wb, kvb = decode_bytes(shape, world, B, ctx + warmup + steps / 2.0)
+            ach = (wb + kvb) / (ms / 1e3 / steps) / 1e9
+            out["batch"][str(B)] = {"ms_per_step": ms / steps, "tokens_per_s": steps * B / (ms / 1e3),
+                                    "us_per_token": ms * 1e3 / steps / B,
+                                    "achieved_gbs_per_gpu": ach, "frac": ach / hbm,
+                                    "frac_of": f"{src} copy bandwidth, per GPU",
+                                    "tensor_core_tasks": int(ypk.status().tensor_core_tasks)}
+            ypk.finalize()
+            del ypk, st, kc, vc, tk
+            torch.cuda.empty_cache()
+        except Exception as e:
+            out["batch"][str(B)] = {"error": str(e)[:300]}
+            # every rank must take the same path afterwards: stop here
+            break
+    del weights
+    torch.cuda.empty_cache()
+    return out
+
+
 # ------------------------------------------------------------------ task-kernel workloads
-def run_kernel_workload(args):
+def measure_kernel(workload, batch, steps, warmup):
     """BASELINE configs[0..2] on one GPU.  One launch of a few microseconds cannot be timed
     from the host, so a step is a chain of `reps` independent copies of the operator (own
     weights / own KV cache each, several GB in total, far beyond L2) executed by one
@@ -397,7 +645,7 @@ def run_kernel_workload(args):
     import yirage_b200 as yr
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
-    K, W, B = args.steps, max(args.warmup, 3), args.batch
+    K, W, B = steps, max(warmup, 3), batch
     g = torch.Generator(device=dev)
 
     def rn(shape, std, dtype, mean=0.0):
@@ -413,9 +661,8 @@ def run_kernel_workload(args):
             use_cutlass_kernel=True)
 
     keep = []
-    if args.workload == "rmsnorm_linear":
+    if workload == "rmsnorm_linear":
         g.manual_seed(0)
-        B = B if args.batch != 1 else 8
         reps, H, dt, ydt = 64, 4096, torch.float16, yr.float16
         ypk = pk(B)
         x = ypk.attach_input(rn((B, H), 1.0, dt), "x")
@@ -428,11 +675,10 @@ def run_kernel_workload(args):
             ypk.rmsnorm_layer(x, ypk.attach_input(nw, f"nw{i}"), tmp, (B, 1, 1), (128, 1, 1), eps=1e-6)
             ypk.linear_layer(tmp, ypk.attach_input(w, f"w{i}"), out, (64, 1, 1), (128, 1, 1))
             alg += H * H * 2 + 2 * B * H * 2 + H * 2
-        name = f"RMSNorm->linear, X[{B},4096] fp16, W[4096,4096] (BASELINE configs[0]) x {reps} copies"
+        name = f"RMSNorm->linear, X[{B},4096] fp16, W[4096,4096] (BASELINE configs[0]) x {reps} independent copies"
         dtype = "f16"
-    elif args.workload == "gated_mlp":
+    elif workload == "gated_mlp":
         g.manual_seed(1)
-        B = B if args.batch != 1 else 8
         reps, H, I, dt = 6, 4096, 14336, torch.bfloat16
         ypk = pk(B)
         x = ypk.attach_input(rn((B, H), 1.0, dt), "x")
@@ -493,18 +739,30 @@ def run_kernel_workload(args):
     clocks = sampler.stop()
     hbm, src = peaks()
     achieved = alg / (ms / 1e3) / 1e9
-    print(json.dumps({
-        "metric": "task_kernel_hbm_gbs", "value": achieved, "unit": "GB/s", "n_gpus": 1, "steps": K,
-        "warmup": W, "ms_per_step": ms, "us_per_operator": ms * 1e3 / reps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
-        "config": {"workload": name, "batch": B,
-                   "l2": f"{alg / 1e9:.2f} GB read per step, far larger than the 126 MB L2",
-                   "note": "launch overhead of one cooperative launch per step is inside the time"},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s",
-                     "frac": achieved / hbm, "frac_of": f"{src} copy bandwidth",
-                     "algorithmic_bytes_per_step": alg, "traffic": None},
-        "clocks": clocks, "gpu_launches": K}), flush=True)
+    res = {"name": name, "dtype": dtype, "batch": B, "ms": ms, "us_per_operator": ms * 1e3 / reps,
+           "alg": alg, "achieved": achieved, "frac": achieved / hbm, "src": src, "hbm": hbm,
+           "clocks": clocks, "tensor_core_tasks": int(ypk.status().tensor_core_tasks)}
     ypk.finalize()
+    del keep
+    return res
+
+
+def run_kernel_workload(args):
+    B = args.batch if args.batch != 1 else 8
+    r = measure_kernel(args.workload, B, args.steps, args.warmup)
+    print(json.dumps({
+        "metric": "task_kernel_hbm_gbs", "value": r["achieved"], "unit": "GB/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": r["ms"],
+        "us_per_operator": r["us_per_operator"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": r["dtype"], "data": "synthetic",
+        "config": {"workload": r["name"], "batch": r["batch"],
+                   "l2": f"{r['alg'] / 1e9:.2f} GB read per step, far larger than the 126 MB L2",
+                   "note": "launch overhead of one cooperative launch per step is inside the time"},
+        "roofline": {"bound": "hbm", "achieved": r["achieved"], "peak": r["hbm"], "unit": "GB/s",
+                     "frac": r["frac"], "frac_of": f"{r['src']} copy bandwidth",
+                     "algorithmic_bytes_per_step": r["alg"], "traffic": None},
+        "tensor_core_tasks": r["tensor_core_tasks"],
+        "clocks": r["clocks"], "gpu_launches": args.steps}), flush=True)
 
 
 def main():

@@ -259,7 +259,12 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks,
 /* init_kernel (persistent_kernel.cuh:107-132): zero step[], request slots,
  * refill the free-page queue.  Also clears a device error (ypk_status.error) of a
  * single-GPU handle; a tensor-parallel handle that has seen a device error cannot be
- * reset (YPK_ERR_STATE): destroy the handles of all ranks and create them again. */
+ * reset (YPK_ERR_STATE): destroy the handles of all ranks and create them again.
+ * Extension: a caller may write step[r] = s0 > 0 after the reset and before the first
+ * launch; request r then enters with its first s0 tokens taken as already cached (it is
+ * given the pages for them, in free-queue order, and starts at position s0).  What those
+ * pages hold is up to the caller (a benchmark that wants a long context without running the
+ * prefill leaves them as they are). */
 int ypk_reset(ypk_handle *h);
 
 /* launch_persistent_kernel: run the megakernel on `stream` (a cudaStream_t,

@@ -256,19 +256,21 @@ class BatchState:
             req = self.next_request
             if req >= self.total_requests:
                 break
-            nnew = min(self.prompt_len[req], MT - ntok, self.max_new_per_request)
-            need = (nnew + PS - 1) // PS
+            s0 = max(0, min(self.step[req], self.max_seq_length - 2))   # tokens taken as cached
+            left = self.prompt_len[req] - s0
+            nnew = min(left, MT - ntok, self.max_new_per_request) if left > 0 else min(1, MT - ntok)
+            need = (s0 + nnew + PS - 1) // PS
             if npages + need > MP or (self.tail - self.head) < need:
                 break
             self.request_ids[nreq] = req
             self.qo_indptr[nreq] = ntok
             self.kv_indptr[nreq] = npages
             for j in range(nnew):
-                self.input_tokens[ntok + j] = int(self.tokens[req, j])
+                self.input_tokens[ntok + j] = int(self.tokens[req, s0 + j])
             for j in range(need):
                 self.kv_indices[npages + j] = self.page_queue[self.head % MP]
                 self.head += 1
-            self.kv_last_len[nreq] = (nnew - 1) % PS + 1 if nnew > 0 else 0
+            self.kv_last_len[nreq] = (s0 + nnew - 1) % PS + 1 if s0 + nnew > 0 else 0
             npages += need
             ntok += nnew
             nreq += 1

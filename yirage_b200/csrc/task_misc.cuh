@@ -262,19 +262,24 @@ __device__ __noinline__ int prepare_next_batch(const Runtime &rt, bool first) {
   while (nreq < MR && ntok < MT) {
     const int req = rt.bstate[0];
     if (req >= rt.total_req) break;
-    int nnew = min(min(rt.prompt_len[req], MT - ntok), rt.max_new_tokens);
-    const int need = (nnew + PS - 1) / PS;
+    // A request normally enters at step 0.  If the caller set step[req] = s0 after the reset,
+    // its first s0 tokens count as already cached: the request gets the pages for them and
+    // starts at position s0 (what those pages hold is the caller's business).
+    const int s0 = max(0, min(rt.step[req], rt.max_seq - 2));
+    const int left = rt.prompt_len[req] - s0;
+    int nnew = left > 0 ? min(min(left, MT - ntok), rt.max_new_tokens) : min(1, MT - ntok);
+    const int need = (s0 + nnew + PS - 1) / PS;
     if (npages + need > MP || (tail - head) < need) break;  // no page budget yet
     rt.request_ids[nreq] = req;
     rt.qo_indptr[nreq] = ntok;
     rt.kv_indptr[nreq] = npages;
     for (int j = 0; j < nnew; ++j)
-      rt.input_tokens[ntok + j] = rt.tokens[size_t(req) * rt.max_seq + j];
+      rt.input_tokens[ntok + j] = rt.tokens[size_t(req) * rt.max_seq + s0 + j];
     for (int j = 0; j < need; ++j) {
       rt.kv_indices[npages + j] = rt.page_queue[head % MP];
       ++head;
     }
-    rt.kv_last_len[nreq] = nnew > 0 ? (nnew - 1) % PS + 1 : 0;
+    rt.kv_last_len[nreq] = s0 + nnew > 0 ? (s0 + nnew - 1) % PS + 1 : 0;
     npages += need;
     ntok += nnew;
     ++nreq;
