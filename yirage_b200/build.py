@@ -1,9 +1,11 @@
 """Ahead-of-time build of the native library (sm_100a only, in-tree).
 
-`python -m yirage_b200.build` compiles csrc/ypk_abi.cu (which includes every kernel)
-into yirage_b200/libypk.so with nvcc.  There is no per-model JIT: shapes travel in the
-task table at run time, unlike the reference which runs nvcc for every graph
-(python/yirage/persistent_kernel.py:1138-1318).
+`python -m yirage_b200.build` compiles every csrc/*.cu into yirage_b200/libypk.so with nvcc:
+the host side of the C ABI (ypk_abi.cu), the kernels (megakernel.cu) and one translation unit
+per task runner (run_*.cu), as relocatable device code linked at the end, so that each
+runner's register allocation depends on its own source only.  There is no per-model JIT:
+shapes travel in the task table at run time, unlike the reference which runs nvcc for every
+graph (python/yirage/persistent_kernel.py:1138-1318).
 """
 import os
 import shutil
@@ -17,6 +19,10 @@ LIB = os.path.join(HERE, "libypk.so")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",
+    "-rdc=true", "--threads", "0",
+    # every runner is called from a kernel of 288 threads (one CTA per SM): 168 registers per
+    # thread is what such a kernel can have, and a callee may not use more than its caller
+    "-maxrregcount", "168",
     "-Xcompiler", "-fPIC", "-shared",
     "--expt-relaxed-constexpr",
     "-Xptxas", "-v",
@@ -24,7 +30,7 @@ NVCC_FLAGS = [
 
 
 def sources():
-    return [os.path.join(CSRC, "ypk_abi.cu")]
+    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
 
 
 def _stale():

@@ -47,6 +47,7 @@ __global__ void __launch_bounds__(kConsumerThreads) argmax_noalloc_kernel(
   t.iarg[2] = int(ld);
   t.iarg[3] = blockIdx.x;
   t.iarg[4] = kNoAllocParts;
+  t.iarg[5] = 0;   // every column of [0, vocab) is real vocabulary
   argmax_partial_task(t, batch);   // an empty chunk yields (-inf, col0) and never wins
   __threadfence();
   __syncthreads();

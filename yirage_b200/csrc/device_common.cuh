@@ -312,7 +312,7 @@ struct WaitCtx {
 __device__ __forceinline__ bool abort_seen(const WaitCtx &w) {
   return ld_relaxed_u64(w.rt->ctrl + kCtrlAbort) != 0ull;
 }
-__device__ __noinline__ void raise_abort(const WaitCtx &w, int code, int event) {
+static __device__ __noinline__ void raise_abort(const WaitCtx &w, int code, int event) {
   unsigned long long info = (static_cast<unsigned long long>(w.worker) << 40) |
                             ((static_cast<unsigned long long>(w.task) & 0xfffffull) << 20) |
                             (static_cast<unsigned long long>(event) & 0xfffffull);
@@ -393,6 +393,18 @@ struct RingPos {
     if (++slot == kStages) {
       slot = 0;
       phase ^= 1u;
+    }
+  }
+};
+
+// Per-thread position in the token ring and phase of the accumulator barrier; every
+// consumer thread keeps one and advances it identically.
+struct UmmaState {
+  uint32_t xslot = 0, xphase = 0, acc_phase = 0;
+  __device__ __forceinline__ void advance() {
+    if (++xslot == uint32_t(kUmmaUnits)) {
+      xslot = 0;
+      xphase ^= 1u;
     }
   }
 };

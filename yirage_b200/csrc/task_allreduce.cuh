@@ -111,7 +111,7 @@ __device__ __forceinline__ bool allreduce_task(WaitCtx &wc, Misc *misc, const Ru
 // This task only polls the world slots of its column slice, adds them in rank order in fp32,
 // rounds once and hands the sum on, again as flagged words (ptr[7]) plus the plain tensor.
 // No signal counters, no fences, no event in or out.
-__device__ __noinline__ bool allreduce_ll_task(WaitCtx &wc, const Runtime &rt, const ypk_task &t,
+static __device__ __noinline__ bool allreduce_ll_task(WaitCtx &wc, const Runtime &rt, const ypk_task &t,
                                                   int batch, long long iter) {
   const int tid = threadIdx.x;
   const unsigned long long *buf = reinterpret_cast<const unsigned long long *>(t.ptr[1]);

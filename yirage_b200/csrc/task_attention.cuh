@@ -474,7 +474,7 @@ __device__ __forceinline__ void attn_store_state_t(float *dst, const AttnAccT &a
 struct QkPair {
   uint4 pk, ov;
 };
-__device__ __noinline__ QkPair qk_norm_chunk(uint4 pk, uint4 ov, const uint16_t *w, int d0,
+static __device__ __noinline__ QkPair qk_norm_chunk(uint4 pk, uint4 ov, const uint16_t *w, int d0,
                                              float eps, bool partner, unsigned lanes) {
   const uint32_t pv[4] = {pk.x, pk.y, pk.z, pk.w}, po[4] = {ov.x, ov.y, ov.z, ov.w};
   float ss = 0.f;

@@ -395,10 +395,136 @@ __device__ __forceinline__ bool linear_stage_x_ll(WaitCtx &wc, const LinearArgs 
   return poll.failed;
 }
 
+// ---- staging for more than two tokens ---------------------------------------------------
+// The loops above keep the loads of several K steps of ONE token in flight, which is right
+// for one or two tokens.  With more tokens they would take the tokens one after the other,
+// one trip to L2 each (8 tokens: 8 trips, ~4.5 us per 2048-column chunk against ~5 us of
+// weight streaming for the whole task).  Here a token row belongs to one warp (to two warps
+// for up to 4 tokens), which keeps 8 loads of its row in flight and needs no per-token
+// register arrays: one running sum of squares, added to the slot of the warp's token.
+// Compiled only into the MANY instantiation of the consumer (3..8 tokens), so the one- and
+// two-token path keeps its code and register allocation.
+template <bool F16>
+__device__ __forceinline__ void stage_x_norm_rows(const uint16_t *x, int ldx, const uint16_t *nw,
+                                                  bool has_nw, uint16_t *xs, int xpitch, int B,
+                                                  int k0, int klen, float (&ss)[kMaxBatch]) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wpr = B <= 4 ? 2 : 1;               // warps per token row
+  const int b = warp / wpr, ph = warp - b * wpr;
+  constexpr int KU = 8;
+  const int step = 32 * wpr * 8;                // columns one pass of the row's warps covers
+  float s = 0.f;
+  if (b < B) {
+    const uint16_t *row = x + size_t(b) * ldx + k0;
+    for (int kb = (ph * 32 + lane) * 8; kb < klen; kb += step * KU) {
+      uint4 xv[KU], wv[KU];
+#pragma unroll
+      for (int u = 0; u < KU; ++u) {
+        const int k = kb + u * step;
+        xv[u] = wv[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (k < klen) {
+          xv[u] = __ldcg(reinterpret_cast<const uint4 *>(row + k));
+          if (has_nw) wv[u] = __ldg(reinterpret_cast<const uint4 *>(nw + k0 + k));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < KU; ++u) {
+        const int k = kb + u * step;
+        if (k < klen) {
+          const uint32_t p[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
+          const uint32_t q[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+          uint32_t o[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = unpack2(cvt_pair<F16>(p[i]));
+            s += f.x * f.x + f.y * f.y;
+            if (has_nw) {
+              const float2 g = unpack2(cvt_pair<F16>(q[i]));
+              o[i] = uint32_t(cvt_out<F16>(f.x * g.x)) | (uint32_t(cvt_out<F16>(f.y * g.y)) << 16);
+            } else {
+              o[i] = p[i];
+            }
+          }
+          *reinterpret_cast<uint4 *>(xs + b * xpitch + k) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int bb = 0; bb < kMaxBatch; ++bb)
+    if (bb == b) ss[bb] += s;
+}
+
+// The same from flagged words: 4 columns (two words, one 16-byte load) per step; words that
+// are not there yet are asked for again, all stragglers of the 8 steps in one round.
+template <bool F16>
+__device__ __forceinline__ void stage_x_ll_rows(const WaitCtx &wc, LLPoll &poll,
+                                                const unsigned long long *ll_x, int ldx, uint32_t tag,
+                                                const uint16_t *nw, bool has_nw, uint16_t *xs,
+                                                int xpitch, int b0, int B, int k0, int klen,
+                                                float (&ss)[kMaxBatch]) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wpr = B <= 4 ? 2 : 1;
+  const int b = warp / wpr, ph = warp - b * wpr;
+  constexpr int KU = 8;
+  const int step = 32 * wpr * 4;
+  float s = 0.f;
+  if (b < B) {
+    const unsigned long long *row = ll_x + size_t(b0 + b) * size_t(ldx >> 1) + (k0 >> 1);
+    for (int kb = (ph * 32 + lane) * 4; kb < klen; kb += step * KU) {
+      unsigned long long w0[KU], w1[KU];
+      bool late[KU];
+#pragma unroll
+      for (int u = 0; u < KU; ++u) late[u] = kb + u * step < klen;
+      for (;;) {
+#pragma unroll
+        for (int u = 0; u < KU; ++u)
+          if (late[u]) ll_load2(row + ((kb + u * step) >> 1), w0[u], w1[u]);
+        bool any = false;
+#pragma unroll
+        for (int u = 0; u < KU; ++u) {
+          if (late[u]) late[u] = !(ll_ok(w0[u], tag) && ll_ok(w1[u], tag));
+          any |= late[u];
+        }
+        if (!any || !poll.again(wc)) break;
+      }
+#pragma unroll
+      for (int u = 0; u < KU; ++u) {
+        const int k = kb + u * step;
+        if (k < klen) {
+          const uint32_t p[2] = {static_cast<uint32_t>(w0[u]), static_cast<uint32_t>(w1[u])};
+          // the norm weights (a few KB, hot in L1) are fetched here rather than before the
+          // poll: held across it they cost 16 registers that this function does not have
+          uint2 wn = make_uint2(0u, 0u);
+          if (has_nw) wn = __ldg(reinterpret_cast<const uint2 *>(nw + k0 + k));
+          const uint32_t q[2] = {wn.x, wn.y};
+          uint32_t o[2];
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const float2 f = unpack2(cvt_pair<F16>(p[i]));
+            s += f.x * f.x + f.y * f.y;
+            if (has_nw) {
+              const float2 g = unpack2(cvt_pair<F16>(q[i]));
+              o[i] = uint32_t(cvt_out<F16>(f.x * g.x)) | (uint32_t(cvt_out<F16>(f.y * g.y)) << 16);
+            } else {
+              o[i] = p[i];
+            }
+          }
+          *reinterpret_cast<uint2 *>(xs + b * xpitch + k) = make_uint2(o[0], o[1]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int bb = 0; bb < kMaxBatch; ++bb)
+    if (bb == b) ss[bb] += s;
+}
+
 // LL = the task uses the flagged-word hand-off somewhere (YPK_F_LL_*); the two instantiations
 // are separate out-of-line functions, so the event path compiles as if the other did not exist.
 // TP = the kernel variant that can push partial sums to peer GPUs (YPK_F_LL_PUSH).
-template <bool F16, bool LL, bool TP>
+// MANY = the instantiation for 3..8 tokens (batched staging, see above).
+template <bool F16, bool LL, bool TP, bool MANY>
 __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Misc *misc,
                                                      const Runtime &rt, const LinearArgs &a,
                                                      int b0, int B, RingPos &pos) {
@@ -450,7 +576,13 @@ __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Mi
     // squared into the RMS statistics (fp32, as rmsnorm_hopper.cuh); the loads of four
     // iterations are issued before the first is used.
     if (LL && (a.flags & YPK_F_LL_IN)) {
-      if constexpr (LL) poll_failed |= linear_stage_x_ll<F16>(wc, a, xs, xpitch, b0, B, k0, klen, ss);
+      if constexpr (LL && MANY) {
+        LLPoll poll;
+        stage_x_ll_rows<F16>(wc, poll, a.ll_x, a.ldx, a.tag_x, nw, has_nw, xs, xpitch, b0, B, k0, klen, ss);
+        poll_failed |= poll.failed;
+      } else if constexpr (LL) {
+        poll_failed |= linear_stage_x_ll<F16>(wc, a, xs, xpitch, b0, B, k0, klen, ss);
+      }
     } else if (!norm) {
       for (int k = tid * 8; k < klen; k += kConsumerThreads * 8) {
 #pragma unroll
@@ -464,6 +596,8 @@ __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Mi
         }
       }
       asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+    } else if constexpr (MANY) {
+      stage_x_norm_rows<F16>(x, a.ldx, nw, has_nw, xs, xpitch, B, k0, klen, ss);
     } else {
       constexpr int kU = 4;
       for (int kb = tid * 8; kb < klen; kb += kConsumerThreads * 8 * kU) {
@@ -848,7 +982,7 @@ __device__ __forceinline__ void linear_consume_groups16(WaitCtx &wc, char *smem,
   }
 }
 
-template <bool LL, bool TP>
+template <bool LL, bool TP, bool MANY>
 __device__ __forceinline__ void linear_consume_groups(WaitCtx &wc, char *smem, Misc *misc,
                                                       const Runtime &rt, const ypk_task &t,
                                                       int batch, long long iter, RingPos &pos) {
@@ -858,9 +992,9 @@ __device__ __forceinline__ void linear_consume_groups(WaitCtx &wc, char *smem, M
     const int b0 = bg * kMaxBatch;
     const int bc = min(kMaxBatch, batch - b0);
     if (a.flags & YPK_F_F16) {
-      linear_consume_group<true, LL, TP>(wc, smem, misc, rt, a, b0, bc, pos);
+      linear_consume_group<true, LL, TP, MANY>(wc, smem, misc, rt, a, b0, bc, pos);
     } else {
-      linear_consume_group<false, LL, TP>(wc, smem, misc, rt, a, b0, bc, pos);
+      linear_consume_group<false, LL, TP, MANY>(wc, smem, misc, rt, a, b0, bc, pos);
     }
     if (bg + 1 < nbg) consumer_bar();  // smem of this group is dead before the next one starts
   }

@@ -176,18 +176,6 @@ __device__ __forceinline__ void tmem_free(uint32_t base) {
                : "memory");
 }
 
-// Per-thread position in the token ring and phase of the accumulator barrier; every
-// consumer thread keeps one and advances it identically.
-struct UmmaState {
-  uint32_t xslot = 0, xphase = 0, acc_phase = 0;
-  __device__ __forceinline__ void advance() {
-    if (++xslot == uint32_t(kUmmaUnits)) {
-      xslot = 0;
-      xphase ^= 1u;
-    }
-  }
-};
-
 // cp.async.wait_group with a run-time count (the instruction takes an immediate).
 __device__ __forceinline__ void cp_async_wait_pending(int n) {
   switch (n) {

@@ -193,7 +193,7 @@ __device__ __forceinline__ void silu_mul_task(const ypk_task &t, int batch) {
 // tokens of the next iteration (0 = everything retired), or -1 when a request that is
 // already running needs a page and the pool has none left (the reference hands out pages
 // without looking, persistent_kernel.cuh:262-270, and two requests then share one).
-__device__ __noinline__ int prepare_next_batch(const Runtime &rt, bool first) {
+static __device__ __noinline__ int prepare_next_batch(const Runtime &rt, bool first) {
   const int MR = rt.max_req, MT = rt.max_tok, MP = rt.max_pages, PS = rt.page_size;
   int head = rt.bstate[1], tail = rt.bstate[2];
   if (!first) {

@@ -18,6 +18,7 @@
 #include "../../include/ypk.h"
 #include "argmax_noalloc.cuh"
 #include "megakernel.cuh"
+#include "task_attention.cuh"   // kAttnRowFloats
 
 using namespace ypk;
 
@@ -485,9 +486,9 @@ int ypk_create(const ypk_config *cfg, ypk_handle **out) {
     delete h;
     return rc;
   }
-  const void *variants[3] = {(const void *)ypk_megakernel<false, false>,
-                             (const void *)ypk_megakernel<true, false>,
-                             (const void *)ypk_megakernel<true, true>};
+  const void *variants[3] = {(const void *)ypk_megakernel_decode,
+                             (const void *)ypk_megakernel_decode_tp,
+                             (const void *)ypk_megakernel_wide};
   int per_sm = 1 << 30;
   for (const void *k : variants) {
     int n = 0;
@@ -1000,9 +1001,9 @@ int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_
   // refuses to start otherwise instead of deadlocking.
   // The variant that carries no code this configuration cannot run (see ypk_megakernel).
   const bool wide = c.max_num_batched_tokens > kMaxBatch, tp = c.world_size > 1;
-  const void *kernel = wide ? (const void *)ypk_megakernel<true, true>
-                       : tp ? (const void *)ypk_megakernel<true, false>
-                            : (const void *)ypk_megakernel<false, false>;
+  const void *kernel = wide ? (const void *)ypk_megakernel_wide
+                       : tp ? (const void *)ypk_megakernel_decode_tp
+                            : (const void *)ypk_megakernel_decode;
   CUDA_TRY(h, cudaLaunchCooperativeKernel(kernel, dim3(h->num_workers),
                                           dim3(kBlockThreads), args, kSmemBytes, st));
   h->stream = st;

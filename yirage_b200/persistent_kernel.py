@@ -460,6 +460,19 @@ class PersistentKernel:
             export_trace(self.profiler_tensor, self.trace_name, self._handle.cfg.num_workers,
                          self.profile_stride(), g.tasks)
 
+    def launch_async(self, **kwargs):
+        """Enqueue the megakernel on the stream and return; `wait()` collects the outcome.
+        (The reference's launch_func is synchronous; this is for callers that time the launch
+        with events or overlap host work.)"""
+        if not self._is_compiled or self._dry:
+            raise RuntimeError("PersistentKernel is not compiled for a device")
+        stream = kwargs.get("stream", None) or torch.cuda.current_stream()
+        sp = stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+        self._handle.launch_async(sp, int(kwargs.get("max_iterations", 0)), int(kwargs.get("batch", 1)))
+
+    def wait(self):
+        self._handle.wait()
+
     def profile_stride(self):
         """Records per worker in the profiler buffer (= the longest worker queue)."""
         g = self.lower()
