@@ -110,6 +110,14 @@ enum ypk_task_type {
  *                  by ypk_load_graph (TMA tensor map of W, or -1); iarg[10..12] = tag ids
  *                  of the producers of x and of the residual, and this operator's own
  *          farg = {eps}
+ *          Split along K (graphs of more than 8 tokens only; no flagged words there):
+ *          iarg[13] = first column k0 and iarg[14] = number of columns of the task's K range
+ *          (0: up to K), iarg[15] = split | nsplit << 8 | workspace tokens << 16, iarg[8] =
+ *          row pitch of the workspace, iarg[10] = index of the row block's arrival counter;
+ *          ptr[5] = workspace fp32 [nsplit][tokens][pitch], ptr[6] = partial sums of squares
+ *          fp32 [blocks][nsplit][tokens], ptr[7] = counters uint32 [blocks][ceil(tokens / 16)].
+ *          Every split of a row block leaves its partial sums there; the last to arrive adds
+ *          them in split order and writes the rows.
  * EMBED:   ptr = {ids(int64), table, out}; iarg = {hidden, col0, ncols,
  *                  ldtable, ldout, rows of the table}; an id outside [0, rows) gives zeros
  * ATTENTION: ptr = {qkv, k_cache, v_cache, out, cos, sin, split scratch, qk-norm weights};

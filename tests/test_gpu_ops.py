@@ -71,8 +71,11 @@ def test_linear_norm_residual(B):
     run_linear(B, 1024, 512, norm=True, residual=True, seed=5, eps=1e-5)
 
 
-def test_linear_batch_above_eight_restreams():
-    """K is not a multiple of 256: the batch stays on the GEMV path (one pass of 16 tokens)."""
+def test_linear_batch_above_eight_odd_k_blocks(monkeypatch):
+    """K of five 64-column k-blocks, split along K unevenly: on the tensor cores and, with
+    them switched off, as one pass of 16 tokens."""
+    run_linear(11, 320, 192, max_tokens=16, seed=9, tensor_core=True)
+    monkeypatch.setenv("YPK_TENSOR_CORE", "never")
     run_linear(11, 320, 192, max_tokens=16, seed=9, tensor_core=False)
 
 

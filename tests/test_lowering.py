@@ -257,7 +257,8 @@ def test_events_follow_tensors_so_independent_chains_do_not_wait_for_each_other(
     ypk = yr.PersistentKernel(
         mode="onepass", world_size=1, mpi_rank=0, num_workers=128, num_local_schedulers=0,
         num_remote_schedulers=0, max_seq_length=64, max_num_batched_requests=1,
-        max_num_batched_tokens=16, max_num_pages=1, page_size=64, eos_token_id=-1, meta_tensors={})
+        max_num_batched_tokens=8, max_num_pages=1, page_size=64, eos_token_id=-1, meta_tensors={})
+    ypk.handoff = "event"
     x = ypk.attach_input(torch.zeros(16, 512, dtype=torch.bfloat16), "x")
     def chain(tag):
         w1 = ypk.attach_input(torch.zeros(512, 512, dtype=torch.bfloat16), f"{tag}w1")
@@ -282,7 +283,8 @@ def test_events_follow_tensors_so_independent_chains_do_not_wait_for_each_other(
     ypk2 = yr.PersistentKernel(
         mode="onepass", world_size=1, mpi_rank=0, num_workers=128, num_local_schedulers=0,
         num_remote_schedulers=0, max_seq_length=64, max_num_batched_requests=1,
-        max_num_batched_tokens=16, max_num_pages=1, page_size=64, eos_token_id=-1, meta_tensors={})
+        max_num_batched_tokens=8, max_num_pages=1, page_size=64, eos_token_id=-1, meta_tensors={})
+    ypk2.handoff = "event"
     x = ypk2.attach_input(torch.zeros(16, 512, dtype=torch.bfloat16), "x")
     h = ypk2.new_tensor(dims=(16, 512), name="h")
     ws = [ypk2.attach_input(torch.zeros(512, 512, dtype=torch.bfloat16), f"w{i}") for i in range(4)]
@@ -478,4 +480,41 @@ def test_70b_shape_lowers_and_validates_under_tp8():
     red = [t for t in g.tasks if t.type == N.TASK_ARGMAX_REDUCE][0]
     assert red.flags & N.F_LL_PUSH and red.iarg[1] == 3 * (llama.padded_vocab(16384) // 8)
     ypk.compile(dry_run=True, defer_connect=True)
+    ypk.finalize()
+
+
+def test_wide_graphs_split_narrow_operators_along_k(native_lib):
+    """More than 8 tokens: an operator with few rows per worker becomes row blocks x K ranges
+    (about one task per worker, 100+ rows each) whose partial sums meet in a workspace; wide
+    operators keep plain row slabs.  The native validation accepts the graph."""
+    assert lowering.splitk_plan(4096, 4096, 1, 148) == (112, 4)        # o_proj of Llama-3-8B
+    assert lowering.splitk_plan(6144, 4096, 1, 148) == (128, 3)        # qkv
+    assert lowering.splitk_plan(28672, 4096, 4, 148) is None           # gate/up: 194 rows per worker
+    shape = llama.LlamaShape(hidden_size=1024, intermediate_size=2048, num_hidden_layers=1,
+                             num_attention_heads=8, num_key_value_heads=2, vocab_size=2048)
+    w = llama.init_weights(shape, "cpu", 0)
+    tokens = torch.zeros(4, 64, dtype=torch.int64)
+    ypk, _ = llama.build_decode_kernel(shape, w, tokens=tokens, prompt_lengths=torch.full((4,), 9, dtype=torch.int32),
+                                       max_num_batched_requests=4, max_num_batched_tokens=32, max_num_pages=4,
+                                       page_size=64, compile=False)
+    g = ypk.lower(148)
+    lin = [t for t in g.tasks if t.type == N.TASK_LINEAR]
+    split = [t for t in lin if (t.iarg[15] >> 8) & 0xff > 1]
+    assert split
+    by_block = {}
+    for t in split:
+        by_block.setdefault((t.op_id, t.iarg[10]), []).append(t)
+    for (op, blk), ts in by_block.items():
+        S = (ts[0].iarg[15] >> 8) & 0xff
+        assert sorted(t.iarg[15] & 0xff for t in ts) == list(range(S)), "every split of a block once"
+        assert len({(t.iarg[1], t.iarg[2]) for t in ts}) == 1, "the splits of a block share its rows"
+        assert sum(t.iarg[14] for t in ts) == ts[0].iarg[0], "the K ranges tile K"
+        assert all(t.iarg[13] % 64 == 0 and t.iarg[14] % 64 == 0 for t in ts)
+        assert len({t.worker for t in ts}) == S, "on different workers"
+    # rows of every operator are covered exactly once per split
+    for op in {t.op_id for t in split}:
+        rows = sorted((t.iarg[1], t.iarg[2]) for t in split if t.op_id == op and (t.iarg[15] & 0xff) == 0)
+        assert rows[0][0] == 0 and all(a[0] + a[1] == b[0] for a, b in zip(rows, rows[1:]))
+    assert set(lowering.simulate(g, 2)) == {2}
+    ypk.compile(dry_run=True)
     ypk.finalize()

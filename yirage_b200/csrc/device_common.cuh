@@ -50,16 +50,16 @@ constexpr int kMaxAttnRows = 32;                 // new tokens x q heads per kv 
 constexpr int kAttnTilesPerSplit = 4;
 constexpr int kSiluGran = 2;                     // fused gate/up rows come as 2 gate + 2 up
 
-// Tensor-core LINEAR path (9..64 tokens): weights arrive as 8-row x 4-k-block TMA boxes
-// (a k-block is 64 columns = one 128-byte swizzled row), tokens sit in a ring of 8 KB units.
+// Tensor-core LINEAR path (more than 16 tokens): weights arrive as TMA boxes of 64 rows x one
+// k-block (a k-block is 64 columns = one 128-byte swizzled row), tokens sit in a ring of 8 KB
+// units (one k-block of up to 64 tokens).
 constexpr int kUmmaKBlock = 64;
-constexpr int kUmmaStepKBlocks = 4;              // k-blocks per weight stage ("super-step")
-constexpr int kUmmaBoxBytes = 8 * kUmmaStepKBlocks * 128;   // 4096: one TMA box
-constexpr int kUmmaBlockRows = 64;               // weight rows per accumulator block
-constexpr int kUmmaMaxBatch = 64;
+constexpr int kUmmaBoxRows = 64;                 // weight rows per TMA box
+constexpr int kUmmaBoxBytes = kUmmaBoxRows * 128;   // 8192
+constexpr int kUmmaMaxBatch = 64;                // tokens per pass (M of the MMA)
 constexpr int kUmmaUnits = 7;                    // token ring: 7 x 8 KB
 constexpr int kUmmaUnitBytes = 8192;
-constexpr int kUmmaTmemCols = 512;               // all of the SM's tensor memory: 4 blocks x 64 columns x 2 partial sums
+constexpr int kUmmaTmemCols = 512;               // all of the SM's tensor memory (a task uses <= 256 columns)
 
 // Shared-memory map (dynamic shared memory, bytes).
 constexpr int kOffRing = 0;
@@ -76,7 +76,7 @@ constexpr int kMiscBytes = 1024;
 constexpr int kSmemBytes = kOffMisc + kMiscBytes;          // 232448 = 227 KB, the per-CTA maximum
 constexpr int kScratchSmemBytes = kXsBytes + kPartBytes + kResBytes + kAccBytes;  // 57344 from kOffXs
 static_assert(kUmmaUnits * kUmmaUnitBytes <= kScratchSmemBytes, "token ring does not fit");
-static_assert(8 * kUmmaBoxBytes <= kStageBytes, "a 64-row super-step does not fit a ring stage");
+static_assert(4 * kUmmaBoxBytes <= kStageBytes, "a 256-row k-block does not fit a ring stage");
 
 // Layout of the misc area.
 struct __align__(16) Misc {
@@ -143,7 +143,8 @@ struct Runtime {
   // t_last_stage_consumed, 0, 0} (globaltimer ns; the last two only for LINEAR tasks)
   const void *tmaps;   // array of 128-byte TMA tensor maps (K/V caches, LINEAR weights), or null
   int use_tmem;        // allocate tensor memory: some LINEAR task can take the tcgen05 path
-  int umma_policy;     // 0 = by estimated cost, 1 = whenever eligible, 2 = never
+  int umma_policy;     // 0 / 1 = whenever eligible, 2 = never
+  int umma_depth;      // token units the stagers keep in flight (YPK_UMMA_DEPTH, default 4)
   // iterations run before the last reset: flagged-word tags and all-reduce arrival counts
   // keep growing across resets (ll_epoch also steps over an aborted iteration)
   unsigned long long ll_epoch, ar_epoch;

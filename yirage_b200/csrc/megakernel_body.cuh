@@ -198,7 +198,9 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
                             : run_linear<true, TP, false>(&rt, misc, smem, worker, ti, wc.failed, batch, iter, pos);
               pos = r.pos;
               wc.failed = r.failed;
-            } else if (WIDE && batch > kMaxBatch) {
+            } else if (WIDE && (batch > kMaxBatch || t.iarg[15] != 0)) {
+              // more than 8 tokens, or a task that covers a K range only (the 16-token pass
+              // is the GEMV path that can leave partial sums for the split along K)
               const TaskRet r = run_linear16(&rt, misc, smem, worker, ti, wc.failed, batch, pos);
               pos = r.pos;
               wc.failed = r.failed;

@@ -106,9 +106,10 @@ __device__ __noinline__ ProdRet run_produce(const Runtime *rt, Misc *misc, char 
   bool ok = true;
   if (t.type == YPK_TASK_LINEAR) {
     if constexpr (WIDE) {
-      ok = linear_uses_umma(*rt, t, batch) ? linear_produce_umma(wc, smem, misc, *rt, t, pos, policy)
-           : batch > kMaxBatch             ? linear_produce16(wc, smem, misc, t, batch, pos, policy)
-                                           : linear_produce(wc, smem, misc, t, batch, pos, policy);
+      ok = linear_uses_umma(*rt, t, batch) ? linear_produce_umma(wc, smem, misc, *rt, t, batch, pos, policy)
+           : (batch > kMaxBatch || t.iarg[15] != 0)
+               ? linear_produce16(wc, smem, misc, t, batch, pos, policy)
+               : linear_produce(wc, smem, misc, t, batch, pos, policy);
     } else {
       ok = linear_produce(wc, smem, misc, t, batch, pos, policy);
     }

@@ -23,6 +23,14 @@
 
 namespace ypk {
 
+__device__ __forceinline__ float silu_mul_ref(float g, float u) {
+  // Rounding points of the unfused reference: linear output in bf16, silu in fp32
+  // rounded to bf16, product in bf16 (tasks/ampere/silu_mul.cuh:33-40).
+  const float gr = bf16_round(g), ur = bf16_round(u);
+  const float s = bf16_round(gr / (1.0f + __expf(-gr)));
+  return s * ur;
+}
+
 struct LinearArgs {
   const char *x;
   const char *w;
@@ -37,6 +45,12 @@ struct LinearArgs {
   const unsigned long long *ll_x, *ll_res;
   unsigned long long *ll_out;
   uint32_t tag_x, tag_res, tag_out;
+  // K range of the task (graphs of more than 8 tokens may split an operator along K): the
+  // task covers columns [k0, k0 + klen) of K; with nsplit > 1 it is split `split` of
+  // `nsplit` of its row block, whose partial sums meet in the workspace `ws`
+  int k0, klen, split, nsplit, ws_ld, ws_tok, cnt_idx;
+  float *ws, *ws_ss;
+  unsigned int *ws_cnt;
 };
 
 __device__ __forceinline__ LinearArgs linear_args(const ypk_task &t, const Runtime *rt = nullptr,
@@ -66,7 +80,98 @@ __device__ __forceinline__ LinearArgs linear_args(const ypk_task &t, const Runti
   a.out_col0 = t.iarg[7];
   a.eps = t.farg[0];
   a.flags = t.flags;
+  a.k0 = t.iarg[13];
+  a.klen = t.iarg[14] > 0 ? t.iarg[14] : a.K - a.k0;
+  a.split = t.iarg[15] & 0xff;
+  a.nsplit = max(1, (t.iarg[15] >> 8) & 0xff);
+  a.ws_tok = t.iarg[15] >> 16;      // tokens per split slot of the workspace
+  a.ws_ld = t.iarg[8];              // its row pitch (weight rows of the operator)
+  a.cnt_idx = t.iarg[10];           // row block's counter (the tag fields are free in wide graphs)
+  a.ws = a.ws_ss = nullptr;
+  a.ws_cnt = nullptr;
+  if (a.nsplit > 1) {
+    a.ws = reinterpret_cast<float *>(t.ptr[5]);
+    a.ws_ss = reinterpret_cast<float *>(t.ptr[6]);
+    a.ws_cnt = reinterpret_cast<unsigned int *>(t.ptr[7]);
+  }
   return a;
+}
+
+// ---- split along K ------------------------------------------------------------------------
+// An operator whose rows per worker would be too few for the tensor cores (o_proj, down_proj,
+// qkv of a wide graph) is cut into row blocks x K ranges.  Each task leaves the fp32 partial
+// dot products of its range, [tokens][rows of the block], in its slot of the workspace
+// (ws[split][token][row], L2 resident) together with its partial sums of squares, then
+// arrives on the block's counter; the task that arrives last adds the slots in split order
+// (so the result does not depend on who was last) and runs the epilogue.  The counter is
+// never reset: the nsplit-th, 2*nsplit-th, ... arrival is the last of its iteration.
+// `accs(r, b)` = this task's own partial for row r of the block and token b.
+// STORE_OWN false: the caller has written its partials to its slot already.
+template <bool F16, bool STORE_OWN, typename AccFn>
+__device__ __forceinline__ void linear_splitk_finish(const LinearArgs &a, Misc *misc, int b0, int B,
+                                                     const float *ss_part, AccFn accs) {
+  const int tid = threadIdx.x;
+  const bool norm = (a.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT)) != 0;
+  const size_t slot = size_t(a.ws_tok) * size_t(a.ws_ld);
+  if constexpr (STORE_OWN) {
+    float *mine = a.ws + size_t(a.split) * slot;
+    for (int idx = tid; idx < a.nrows * B; idx += kConsumerThreads) {
+      const int b = idx / a.nrows, r = idx - b * a.nrows;
+      __stcg(mine + size_t(b0 + b) * a.ws_ld + a.row0 + r, accs(r, b));
+    }
+  }
+  // partial sums of squares: [block][split][token]
+  float *ssb = a.ws_ss + (size_t(a.cnt_idx) * a.nsplit) * a.ws_tok;
+  if (norm && tid < B) __stcg(ssb + size_t(a.split) * a.ws_tok + b0 + tid, ss_part[tid]);
+  __threadfence();
+  consumer_bar();
+  if (tid == 0) {
+    // one counter per (row block, group of 16 tokens): a task passes here once per group
+    unsigned int *ctr = a.ws_cnt + size_t(a.cnt_idx) * size_t((a.ws_tok + 15) >> 4) + (b0 >> 4);
+    const unsigned old = atomicAdd(ctr, 1u);
+    misc->flag = ((old + 1u) % unsigned(a.nsplit)) == 0u ? 1 : 0;
+  }
+  consumer_bar();
+  const bool last = misc->flag != 0;
+  consumer_bar();   // flag is read by everybody before anyone can rewrite it
+  if (!last) return;
+  __threadfence();
+  if (norm && tid < B) {
+    float s = 0.f;
+    for (int sp = 0; sp < a.nsplit; ++sp) s += __ldcg(ssb + size_t(sp) * a.ws_tok + b0 + tid);
+    misc->rnorm_umma[tid] = rsqrtf(s / float(a.K) + a.eps);
+  }
+  consumer_bar();
+  auto total = [&](int r, int b) {
+    float s = 0.f;
+    for (int sp = 0; sp < a.nsplit; ++sp)
+      s += __ldcg(a.ws + size_t(sp) * slot + size_t(b0 + b) * a.ws_ld + a.row0 + r);
+    return s;
+  };
+  uint16_t *out = reinterpret_cast<uint16_t *>(a.out);
+  if (a.flags & YPK_F_SILU_MUL) {
+    const int ngr = a.nrows >> 2;   // granules of 2 gate + 2 up rows -> 2 outputs
+    for (int idx = tid; idx < ngr * B; idx += kConsumerThreads) {
+      const int b = idx / ngr, g = idx - b * ngr;
+      float v[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] = total(g * 4 + i, b) * (norm ? misc->rnorm_umma[b] : 1.f);
+      const int col = a.out_col0 + ((a.row0 + g * 4) >> 1);
+      uint16_t *orow = out + size_t(b0 + b) * a.ldout;
+      orow[col] = cvt_out<F16>(silu_mul_ref(v[0], v[2]));
+      orow[col + 1] = cvt_out<F16>(silu_mul_ref(v[1], v[3]));
+    }
+  } else {
+    for (int idx = tid; idx < a.nrows * B; idx += kConsumerThreads) {
+      const int b = idx / a.nrows, r = idx - b * a.nrows;
+      float v = total(r, b);
+      if (norm) v *= misc->rnorm_umma[b];
+      const int col = a.out_col0 + a.row0 + r;
+      if (a.flags & YPK_F_RESIDUAL)
+        v += cvt_one<F16>(__ldcg(reinterpret_cast<const uint16_t *>(a.res) + size_t(b0 + b) * a.ldres + col));
+      out[size_t(b0 + b) * a.ldout + col] = cvt_out<F16>(v);
+    }
+  }
 }
 
 // Tokens per pass over the weights: 8 (one n-tile of the MMA) up to batch 8, else 16 (two
@@ -123,9 +228,9 @@ __device__ __forceinline__ bool linear_produce16(WaitCtx &wc, char *smem, Misc *
   // groups of 16 tokens, K in chunks of one stage (see linear_consume_group16)
   const int nbg = (batch + kWideBatch - 1) / kWideBatch;
   for (int bg = 0; bg < nbg; ++bg) {
-    const int KC = min(a.K, kStageCols);
-    for (int k0 = 0; k0 < a.K; k0 += KC) {
-      const int klen = min(KC, a.K - k0);
+    const int KC = min(a.klen, kStageCols);
+    for (int k0 = a.k0; k0 < a.k0 + a.klen; k0 += KC) {
+      const int klen = min(KC, a.k0 + a.klen - k0);
       for (int r0 = 0; r0 < a.nrows; r0 += kRowBlock) {
         const int nr = min(kRowBlock, a.nrows - r0);
         for (int ks = 0; ks < klen; ks += kStageCols) {
@@ -173,14 +278,6 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   }
-}
-
-__device__ __forceinline__ float silu_mul_ref(float g, float u) {
-  // Rounding points of the unfused reference: linear output in bf16, silu in fp32
-  // rounded to bf16, product in bf16 (tasks/ampere/silu_mul.cuh:33-40).
-  const float gr = bf16_round(g), ur = bf16_round(u);
-  const float s = bf16_round(gr / (1.0f + __expf(-gr)));
-  return s * ur;
 }
 
 // Writes the finished values of `nr` rows starting at task row r0.  val(r, b) returns the
@@ -774,7 +871,7 @@ __device__ __forceinline__ void linear_consume_group16(WaitCtx &wc, char *smem, 
   const bool norm = (a.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT)) != 0;
   const bool has_nw = (a.flags & YPK_F_NORM) != 0;
   const bool silu = (a.flags & YPK_F_SILU_MUL) != 0;
-  const int KC = min(a.K, kStageCols);
+  const int KC = min(a.klen, kStageCols);
   const int xpitch = KC + 8;
 
   for (int i = tid; i < a.nrows * kTok; i += kConsumerThreads) accs[i] = 0.f;
@@ -787,8 +884,8 @@ __device__ __forceinline__ void linear_consume_group16(WaitCtx &wc, char *smem, 
   const int b_row0 = min(lane & 7, B - 1), b_row1 = min(8 + (lane & 7), B - 1);
   const int b_kof = (lane >> 3) * 8;
 
-  for (int k0 = 0; k0 < a.K; k0 += KC) {
-    const int klen = min(KC, a.K - k0);
+  for (int k0 = a.k0; k0 < a.k0 + a.klen; k0 += KC) {
+    const int klen = min(KC, a.k0 + a.klen - k0);
     consumer_bar();  // the previous chunk is done with xs (and the accumulators are zeroed)
     if (!norm) {
       for (int k = tid * 8; k < klen; k += kConsumerThreads * 8) {
@@ -914,6 +1011,29 @@ __device__ __forceinline__ void linear_consume_group16(WaitCtx &wc, char *smem, 
     }
   }
   consumer_bar();   // every warp's last additions are in
+  if (a.nsplit > 1) {
+    // this task covered a K range only: its partial sums (and partial statistics) go to the
+    // block's workspace, the last split to arrive finishes the rows
+    float *mred = reinterpret_cast<float *>(xs);   // [8 warps][8]; the activations are dead by now
+    float *sstok = mred + kConsumerWarps * (kTok / 2);   // [16] per-token partial sums of squares
+    if (norm) {
+#pragma unroll
+      for (int i = 0; i < kTok / 2; ++i) {
+        const float r = warp_sum(ss[i]);
+        if (lane == 0) mred[warp * (kTok / 2) + i] = r;
+      }
+      consumer_bar();
+      if (tid < kTok) {
+        const int half = tid & 1, i = tid >> 1;
+        float sred = 0.f;
+        for (int w = half * 4; w < half * 4 + 4; ++w) sred += mred[w * (kTok / 2) + i];
+        sstok[tid] = sred;
+      }
+      consumer_bar();
+    }
+    linear_splitk_finish<F16, true>(a, misc, b0, B, sstok, [&](int r, int b) { return accs[r * kTok + b]; });
+    return;
+  }
   // RMS factors: each half of the block holds the statistics of the tokens of its parity
   if (norm) {
     float rs[kTok / 2];

@@ -1,28 +1,40 @@
-// LINEAR task for 9..64 tokens: the fused operator of task_linear.cuh on the 5th-generation
-// tensor cores.  With more than 8 tokens the projection is a real dense contraction,
-// out^T[rows, batch] = W[rows, K] . x^T[K, batch].  As in the reference's Blackwell linear
-// task (tasks/blackwell/linear_sm100_mpk.cuh:31-707) the weights are the M side of the MMA
-// and the batch, padded to a multiple of 16, is N.
+// LINEAR task for more than 16 tokens on the 5th-generation tensor cores (tcgen05.mma with
+// accumulators in tensor memory).  out[tokens, rows] = x[tokens, K] . W[rows, K]^T for the
+// row block and K range of the task, up to 64 tokens per pass.
 //
-//   A (weights)   tiled TMA through a rank-3 view {64 columns, rows, K / 64} of the weight:
-//                 one box is 8 rows x 4 k-blocks (4 KB) and lands as [k-block][row][128 B]
-//                 with the 128-byte swizzle, i.e. as four 8-row core-matrix groups of the
-//                 K-major UMMA layout.  A ring stage holds one "super-step" of one row
-//                 block: up to 8 such boxes (64 rows) x 4 k-blocks, or, for a task of at
-//                 most 32 rows, 4 boxes x 8 k-blocks.  Rows past the task's slab are never
-//                 read back; rows past the end of the tensor arrive as zeros.
-//   B (tokens)    staged by consumer warps 1..7 with 16-byte cp.async into a second ring of
-//                 seven 8 KB units (64 / N k-blocks each), same swizzled K-major layout, then
-//                 multiplied in place by the norm weight while the RMS statistics are
-//                 taken; several units are in flight so that the L2 latency is hidden.
-//   D             fp32 accumulators in tensor memory, N columns per 64-row block (at most
-//                 four blocks per task) and per partial sum (up to four, see below).  Lane 0 of consumer warp 0 issues tcgen05.mma
-//                 (cta_group::1, kind::f16, M = 64, so that a block reads only its own 64
-//                 rows of shared memory); tcgen05.commit hands weight stages and token units
-//                 back to their producers and signals the end.
-//   epilogue      tcgen05.ld 32x32b: with M = 64 row r of a block sits in TMEM lane
-//                 32 * (r / 16) + r % 16, i.e. in the lower 16 lanes of warp r / 16 -> RMS
-//                 factor, residual or SiLU(gate) * up -> 16-bit stores.
+// Operand roles.  The tokens are the M side of the MMA (padded to 64) and the WEIGHT ROWS are
+// the N side, up to 256 of them per instruction.  A tcgen05.mma occupies the tensor pipe for
+// about 78 ns whatever its shape on this part, so what an instruction consumes decides
+// whether the task can follow HBM: with the weights on M (as in the reference's Blackwell
+// linear task, tasks/blackwell/linear_sm100_mpk.cuh:31-707: M = 128 weight rows, N = 16
+// tokens) an instruction covers at most 4 KB of weights, about what 78 ns of one SM's share of
+// HBM delivers, and in practice less; with 128..256 weight rows on N it covers 4..8 KB at
+// M = 64.  Operators whose row slab per worker would be narrow (o_proj, down_proj, qkv) are
+// cut by the host into row blocks x K ranges instead (split along K, see
+// linear_splitk_finish), which also cuts the token bytes each CTA has to fetch.
+//
+//   B (weights)   tiled TMA through a rank-3 view {64 columns, rows, K / 64} of the weight
+//                 with the 128-byte swizzle: one box is 64 rows x one 64-column k-block (8 KB)
+//                 and lands as [row][128 B], i.e. as eight 8-row core-matrix groups of the
+//                 K-major UMMA layout, 1024 bytes apart.  A ring stage holds `kbs` k-blocks
+//                 of the task's whole row block: [k-block][box][64 rows][128 B].  Rows past
+//                 the task's block belong to a neighbour (their columns of the accumulator
+//                 are never read); rows past the end of the tensor arrive as zeros.
+//   A (tokens)    staged by consumer warps 1..7 with 16-byte cp.async into a second ring of
+//                 seven 8 KB units (one k-block of up to 64 tokens each), same swizzled
+//                 K-major layout, then multiplied in place by the norm weight while the RMS
+//                 statistics are taken.  Rows past the batch are never written: they hold
+//                 stale bytes, which only reach accumulator rows that nobody reads.
+//   D             fp32 in tensor memory: 64 rows (tokens) x Npad columns (weight rows of the
+//                 block, padded to 8).  Lane 0 of consumer warp 0 issues four
+//                 tcgen05.mma.cta_group::1.kind::f16 (M = 64, N = Npad, K = 16) per k-block;
+//                 tcgen05.commit hands weight stages and token units back to their producers
+//                 and signals the end.
+//   epilogue      tcgen05.ld 32x32b: with M = 64, token t sits in TMEM lane 32 * (t / 16) + t % 16,
+//                 so a thread holds one token and reads 8 neighbouring weight rows at a time:
+//                 RMS factor, residual or SiLU(gate) * up (the 2 + 2 granules lie inside the
+//                 8), stores.  A task that covers only a K range leaves its partial sums in
+//                 the workspace instead and the last split finishes the rows.
 //
 // The TMEM columns are allocated once per CTA when the kernel starts and freed when it ends
 // (the reference allocates and frees them inside every task, linear_sm100_mpk.cuh:561,704).
@@ -32,37 +44,20 @@
 
 namespace ypk {
 
-__device__ __forceinline__ int umma_n(int batch) { return (batch + 15) / 16 * 16; }
-// k-blocks per token-ring unit (8 KB): 4, 2, 1, 1 for N = 16, 32, 48, 64
-__device__ __forceinline__ int umma_unit_kblocks(int N) { return kUmmaMaxBatch / N; }
-
-// k-blocks per ring stage: 8 for a task of at most 32 rows (one block, <= 4 boxes per
-// k-half), else 4.
-__device__ __forceinline__ int umma_step_kblocks(const LinearArgs &a) {
-  return (a.nrows <= 32 && (a.K / kUmmaKBlock) % (2 * kUmmaStepKBlocks) == 0) ? 2 * kUmmaStepKBlocks
-                                                                             : kUmmaStepKBlocks;
+__device__ __forceinline__ int umma_npad(int nrows) { return (nrows + 7) & ~7; }
+// 64-row TMA boxes per k-block of the task's row block, and k-blocks per ring stage
+__device__ __forceinline__ int umma_nbox(int nrows) { return (nrows + kUmmaBoxRows - 1) / kUmmaBoxRows; }
+__device__ __forceinline__ int umma_stage_kblocks(int nrows) {
+  return kStageBytes / (umma_nbox(nrows) * kUmmaBoxBytes);
 }
 
 // Does this task take the tensor-core path at this batch?  Producer and consumers evaluate
-// this identically.  A tcgen05.mma occupies the SM's tensor pipe for about 78 ns whatever M
-// and N (measured back to back: 64x16x16 and 128x256x16 alike; about 130 ns each inside this
-// task, with its waits and commits), and a task issues K / 16 of them per 64-row block; the
-// GEMV path instead streams the weights once per 16 tokens at about 3/4 of the SM's share of
-// HBM (44 bytes / ns).  Take whichever is estimated to finish first: with the slabs of an 8B
-// model that is the GEMV path up to 32 tokens and, for the wider slabs, the tensor-core path
-// beyond.
+// this identically.  Every eligible task with more than 8 tokens does (measured on the gated
+// MLP of Llama-3-8B: 16 tokens 0.58 ms against 0.64 ms for one 16-token GEMV pass, 64 tokens
+// 0.70 ms against 2.36 ms for four passes); YPK_TENSOR_CORE=never keeps the GEMV passes.
 __device__ __forceinline__ bool linear_uses_umma(const Runtime &rt, const ypk_task &t, int batch) {
-  if (batch <= kMaxBatch || batch > kUmmaMaxBatch || t.iarg[9] < 0 || rt.umma_policy == 2 ||
-      (t.flags & (YPK_F_LL_IN | YPK_F_LL_RES | YPK_F_LL_OUT)))
-    return false;
-  if (rt.umma_policy == 1) return true;
-  const long long K = t.iarg[0], nrows = t.iarg[2];
-  const long long wbytes = nrows * K * 2;
-  const long long nblocks = (nrows + kUmmaBlockRows - 1) / kUmmaBlockRows;
-  const long long mma_ns = nblocks * (K / 16) * 130;
-  const long long umma_ns = max(wbytes / 44, mma_ns);
-  const long long gemv_ns = ((batch + kWideBatch - 1) / kWideBatch) * (wbytes / 33);
-  return umma_ns < gemv_ns;
+  if (batch <= kMaxBatch || t.iarg[9] < 0 || rt.umma_policy == 2) return false;
+  return true;
 }
 
 __device__ __forceinline__ void tma_load_3d_hint(void *dst, const void *tmap, int x, int y, int z,
@@ -75,30 +70,29 @@ __device__ __forceinline__ void tma_load_3d_hint(void *dst, const void *tmap, in
 }
 
 // ------------------------------------------------------------------ producer
-// Traversal (must match the issuer in linear_consume_umma): super-steps of 4 k-blocks ->
-// row blocks of <= 64 rows; one ring stage each.
+// Traversal (must match the issuer in linear_consume_umma_group): groups of 64 tokens ->
+// stages of `kbs` k-blocks over the task's K range.
 __device__ __forceinline__ bool linear_produce_umma(WaitCtx &wc, char *smem, Misc *misc,
-                                                    const Runtime &rt, const ypk_task &t,
+                                                    const Runtime &rt, const ypk_task &t, int batch,
                                                     RingPos &pos, unsigned long long policy) {
   const int lane = threadIdx.x & 31;
   const LinearArgs a = linear_args(t);
   const char *tmap = static_cast<const char *>(rt.tmaps) + size_t(t.iarg[9]) * 128;
-  const int KS = umma_step_kblocks(a);
-  const int halves = KS / kUmmaStepKBlocks;            // TMA boxes per 8-row group
-  const int nss = a.K / (kUmmaKBlock * KS);
-  for (int ss = 0; ss < nss; ++ss) {
-    for (int r0 = 0; r0 < a.nrows; r0 += kUmmaBlockRows) {
-      const int groups = (min(kUmmaBlockRows, a.nrows - r0) + 7) / 8;
+  const int nbox = umma_nbox(a.nrows), kbs = umma_stage_kblocks(a.nrows);
+  const int kb0 = a.k0 / kUmmaKBlock, nkb = a.klen / kUmmaKBlock;
+  const int ngroups = (batch + kUmmaMaxBatch - 1) / kUmmaMaxBatch;
+  for (int grp = 0; grp < ngroups; ++grp) {
+    for (int kb = 0; kb < nkb; kb += kbs) {
+      const int nk = min(kbs, nkb - kb);
       if (!wait_mbar(wc, &misc->empty_bar[pos.slot], pos.phase ^ 1u)) return false;
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       char *stage = smem + kOffRing + pos.slot * kStageBytes;
-      if (lane == 0)
-        mbar_expect_tx(&misc->full_bar[pos.slot], uint32_t(groups * halves) * kUmmaBoxBytes);
+      if (lane == 0) mbar_expect_tx(&misc->full_bar[pos.slot], uint32_t(nk * nbox) * kUmmaBoxBytes);
       __syncwarp();
-      if (lane < groups * halves) {
-        const int g = lane / halves, hf = lane - g * halves;
-        tma_load_3d_hint(stage + lane * kUmmaBoxBytes, tmap, 0, a.row0 + r0 + g * 8,
-                         ss * KS + hf * kUmmaStepKBlocks, &misc->full_bar[pos.slot], policy);
+      if (lane < nk * nbox) {
+        const int j = lane / nbox, bx = lane - j * nbox;
+        tma_load_3d_hint(stage + lane * kUmmaBoxBytes, tmap, 0, a.row0 + bx * kUmmaBoxRows, kb0 + kb + j,
+                         &misc->full_bar[pos.slot], policy);
       }
       pos.advance();
     }
@@ -188,94 +182,70 @@ __device__ __forceinline__ void cp_async_wait_pending(int n) {
   }
 }
 
-__device__ __forceinline__ void cp_async16_zfill(void *dst, const void *src, bool real) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src),
-               "r"(real ? 16u : 0u)
-               : "memory");
-}
-
 // ------------------------------------------------------------------ consumer
+// One group of B <= 64 tokens starting at token b0.
 template <bool F16>
-__device__ __forceinline__ void linear_consume_umma_t(WaitCtx &wc, char *smem, Misc *misc,
-                                                      const LinearArgs &a, int B, RingPos &pos,
-                                                      UmmaState &us) {
+__device__ __forceinline__ void linear_consume_umma_group(WaitCtx &wc, char *smem, Misc *misc,
+                                                          const LinearArgs &a, int b0, int B,
+                                                          RingPos &pos, UmmaState &us) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   char *xring = smem + kOffXs;                       // kUmmaUnits x 8 KB
-  const uint16_t *x = reinterpret_cast<const uint16_t *>(a.x);
+  const uint16_t *x = reinterpret_cast<const uint16_t *>(a.x) + size_t(b0) * a.ldx;
   const uint16_t *nw = reinterpret_cast<const uint16_t *>(a.norm_w);
   const bool norm = (a.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT)) != 0;
   const bool has_nw = (a.flags & YPK_F_NORM) != 0;
   const bool silu = (a.flags & YPK_F_SILU_MUL) != 0;
-  const int N = umma_n(B);
-  const int XB = umma_unit_kblocks(N);               // k-blocks per unit
-  const int nkb = a.K / kUmmaKBlock;                 // multiple of kUmmaStepKBlocks
-  const int nunits = nkb / XB;
-  const int KS = umma_step_kblocks(a);               // k-blocks per weight stage
-  const int nsteps = nkb / KS;
-  const int nblocks = (a.nrows + kUmmaBlockRows - 1) / kUmmaBlockRows;
-  // Back-to-back MMAs into one accumulator serialise on its read-modify-write (about 100 ns
-  // each, whatever M and N), so the four 16-wide K steps of a k-block go to up to four
-  // accumulators, summed in the epilogue.
-  const int nacc = min(kUmmaKBlock / 16, kUmmaTmemCols / (nblocks * N));
+  const int Npad = umma_npad(a.nrows);
+  const int nbox = umma_nbox(a.nrows), kbs = umma_stage_kblocks(a.nrows);
+  const int nkb = a.klen / kUmmaKBlock;              // k-blocks of the task = token units
   const uint32_t tmem = misc->tmem_base;
+  // sums of squares over this task's K range, turned into the RMS factors in place
+  float *ssum = misc->rnorm_umma;
 
   if (warp == 0) {
     // ------------------------------------------------------------ MMA issuer
-    const uint32_t idesc = umma_instr_desc(kUmmaBlockRows, N, F16);
-    UmmaState xbase = us;   // unit holding the first k-block of the current step
+    const uint32_t idesc = umma_instr_desc(kUmmaMaxBatch, Npad, F16);
     // timeline (lane 0): [4] first stage in hand, [5] last MMA issued, [6] / [7] ns spent
     // waiting for weight stages / token units
     unsigned long long *prec = lane == 0 ? misc->prof_rec : nullptr;
     unsigned long long wait_w = 0, wait_x = 0;
-    for (int ss = 0; ss < nsteps; ++ss) {
-      for (int blk = 0; blk < nblocks; ++blk) {
-        unsigned long long tw = prec ? globaltimer() : 0ull;
-        const bool got = wait_mbar(wc, &misc->full_bar[pos.slot], pos.phase);
-        if (prec) {
-          const unsigned long long now = globaltimer();
-          wait_w += now - tw;
-          if (ss == 0 && blk == 0) prec[4] = now;
-        }
-        const char *stage = smem + kOffRing + pos.slot * kStageBytes;
-        if (got && lane == 0) tcgen05_after_sync();
-        UmmaState xu = xbase;
-        for (int j = 0; j < KS; ++j) {
-          const int ju = j % XB;
-          // a token unit is awaited when the first block first touches it ...
-          bool xok = true;
-          if (blk == 0 && ju == 0) {
-            tw = prec ? globaltimer() : 0ull;
-            xok = wait_mbar(wc, &misc->xfull_bar[xu.xslot], xu.xphase);
-            if (prec) wait_x += globaltimer() - tw;
-          }
-          if (got && xok && lane == 0) {
-            if (blk == 0 && ju == 0) tcgen05_after_sync();
-            const unsigned long long ad = umma_smem_desc(stage + j * 1024, uint32_t(KS) * 1024u);
-            const unsigned long long bd =
-                umma_smem_desc(xring + xu.xslot * kUmmaUnitBytes + ju * N * 128, 1024);
-#pragma unroll
-            for (int kk = 0; kk < kUmmaKBlock / 16; ++kk) {
-              // 32 bytes per 16-wide K step inside the swizzle atom: +2 in the address field
-              const int acc = kk % nacc;
-              umma_f16(tmem + uint32_t((blk * nacc + acc) * N), ad + 2ull * kk, bd + 2ull * kk,
-                       idesc, ss > 0 || j > 0 || kk >= nacc);
-            }
-            // ... and handed back when the last block is done with it
-            if (blk == nblocks - 1 && ju == XB - 1) umma_commit(&misc->xempty_bar[xu.xslot]);
-          }
-          if (ju == XB - 1) xu.advance();
-        }
-        if (got && !wc.failed) {
-          if (lane == 0) {
-            umma_commit(&misc->empty_bar[pos.slot]);   // one of the 8 arrivals, when the MMAs are done
-          } else if (lane < kConsumerWarps) {
-            mbar_arrive(&misc->empty_bar[pos.slot]);   // the other 7: nothing else reads the stage
-          }
-        }
-        __syncwarp();
-        pos.advance();
-        if (blk == nblocks - 1) xbase = xu;
+    UmmaState xu = us;
+    for (int kb = 0; kb < nkb; kb += kbs) {
+      const int nk = min(kbs, nkb - kb);
+      unsigned long long tw = prec ? globaltimer() : 0ull;
+      const bool got = wait_mbar(wc, &misc->full_bar[pos.slot], pos.phase);
+      if (prec) {
+        const unsigned long long now = globaltimer();
+        wait_w += now - tw;
+        if (kb == 0) prec[4] = now;
       }
+      const char *stage = smem + kOffRing + pos.slot * kStageBytes;
+      for (int j = 0; j < nk; ++j) {
+        tw = prec ? globaltimer() : 0ull;
+        const bool xok = wait_mbar(wc, &misc->xfull_bar[xu.xslot], xu.xphase);
+        if (prec) wait_x += globaltimer() - tw;
+        if (got && xok && lane == 0) {
+          tcgen05_after_sync();
+          const unsigned long long ad = umma_smem_desc(xring + xu.xslot * kUmmaUnitBytes, 1024);
+          const unsigned long long bd = umma_smem_desc(stage + j * nbox * kUmmaBoxBytes, 1024);
+#pragma unroll
+          for (int kk = 0; kk < kUmmaKBlock / 16; ++kk) {
+            // 32 bytes per 16-wide K step inside the swizzle atom: +2 in the address field
+            umma_f16(tmem, ad + 2ull * kk, bd + 2ull * kk, idesc, kb + j > 0 || kk > 0);
+          }
+          umma_commit(&misc->xempty_bar[xu.xslot]);   // the unit is free once these have run
+        }
+        xu.advance();
+      }
+      if (got && !wc.failed) {
+        if (lane == 0) {
+          umma_commit(&misc->empty_bar[pos.slot]);   // one of the 8 arrivals, when the MMAs are done
+        } else if (lane < kConsumerWarps) {
+          mbar_arrive(&misc->empty_bar[pos.slot]);   // the other 7: nothing else reads the stage
+        }
+      }
+      __syncwarp();
+      pos.advance();
     }
     if (lane == 0) umma_commit(&misc->acc_bar);
     if (prec) {
@@ -291,30 +261,25 @@ __device__ __forceinline__ void linear_consume_umma_t(WaitCtx &wc, char *smem, M
     const int c = lane & 7, rb = (warp - 1) * 4 + (lane >> 3);
     constexpr int kRowsPerPass = (kConsumerWarps - 1) * 4;                         // 28
     constexpr int kMaxPasses = (kUmmaMaxBatch + kRowsPerPass - 1) / kRowsPerPass;  // 3
-    // Units in flight.  The first block of a multi-block task holds every unit of a step
-    // (KS / XB of the 7) until the last block has used them, so the copies can only run
-    // 7 - KS / XB units ahead of the oldest unit still needed; a one-block task hands its
-    // units back as it goes.
-    const int kDepth = nblocks == 1 ? 5 : min(5, kUmmaUnits - KS / XB);
+    const int kDepth = wc.rt->umma_depth;     // units in flight (1..5)
     float ssq[kMaxPasses] = {0.f, 0.f, 0.f};
     UmmaState xi = us, xf = us;   // issue / finish positions
-    for (int u = 0; u < nunits + kDepth; ++u) {
-      if (u < nunits) {
+    for (int u = 0; u < nkb + kDepth; ++u) {
+      if (u < nkb) {
         const bool free_ok = wait_mbar(wc, &misc->xempty_bar[xi.xslot], xi.xphase ^ 1u);
         char *unit = xring + xi.xslot * kUmmaUnitBytes;
         if (free_ok) {
-          for (int j = 0; j < XB; ++j) {
-            const int k = (u * XB + j) * kUmmaKBlock + c * 8;
-            // the norm weights of this unit are wanted a few units from now: bring them to L1
-            if (has_nw && rb < B) asm volatile("prefetch.global.L1 [%0];" ::"l"(nw + k));
+          const int k = a.k0 + u * kUmmaKBlock + c * 8;
+          // the norm weights of this unit are wanted a few units from now: bring them to L1
+          if (has_nw && rb < B) asm volatile("prefetch.global.L1 [%0];" ::"l"(nw + k));
 #pragma unroll
-            for (int p = 0; p < kMaxPasses; ++p) {
-              const int b = rb + p * kRowsPerPass;
-              if (b < N) {
-                const int bs = b < B ? b : 0;
-                cp_async16_zfill(unit + j * N * 128 + b * 128 + ((c ^ (b & 7)) << 4),
-                                 x + size_t(bs) * a.ldx + k, b < B);
-              }
+          for (int p = 0; p < kMaxPasses; ++p) {
+            const int b = rb + p * kRowsPerPass;
+            if (b < B) {
+              asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                               smem_u32(unit + b * 128 + ((c ^ (b & 7)) << 4))),
+                           "l"(x + size_t(b) * a.ldx + k)
+                           : "memory");
             }
           }
         }
@@ -326,34 +291,30 @@ __device__ __forceinline__ void linear_consume_umma_t(WaitCtx &wc, char *smem, M
         cp_async_wait_pending(kDepth);
         char *unit = xring + xf.xslot * kUmmaUnitBytes;
         if (norm) {
-          for (int j = 0; j < XB; ++j) {
-            const int k = (uf * XB + j) * kUmmaKBlock + c * 8;
-            uint4 wv = make_uint4(0u, 0u, 0u, 0u);
-            if (has_nw) wv = __ldg(reinterpret_cast<const uint4 *>(nw + k));
-            const uint32_t q[4] = {wv.x, wv.y, wv.z, wv.w};
+          const int k = a.k0 + uf * kUmmaKBlock + c * 8;
+          uint4 wv = make_uint4(0u, 0u, 0u, 0u);
+          if (has_nw) wv = __ldg(reinterpret_cast<const uint4 *>(nw + k));
+          const uint32_t q[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
-            for (int p = 0; p < kMaxPasses; ++p) {
-              const int b = rb + p * kRowsPerPass;
-              if (b < B) {
-                uint4 *cell = reinterpret_cast<uint4 *>(unit + j * N * 128 + b * 128 +
-                                                        ((c ^ (b & 7)) << 4));
-                const uint4 v = *cell;
-                const uint32_t pv[4] = {v.x, v.y, v.z, v.w};
-                uint32_t o[4];
+          for (int p = 0; p < kMaxPasses; ++p) {
+            const int b = rb + p * kRowsPerPass;
+            if (b < B) {
+              uint4 *cell = reinterpret_cast<uint4 *>(unit + b * 128 + ((c ^ (b & 7)) << 4));
+              const uint4 v = *cell;
+              const uint32_t pv[4] = {v.x, v.y, v.z, v.w};
+              uint32_t o[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const float2 f = unpack2(cvt_pair<F16>(pv[i]));
-                  ssq[p] += f.x * f.x + f.y * f.y;
-                  if (has_nw) {
-                    const float2 g = unpack2(cvt_pair<F16>(q[i]));
-                    o[i] = uint32_t(cvt_out<F16>(f.x * g.x)) |
-                           (uint32_t(cvt_out<F16>(f.y * g.y)) << 16);
-                  } else {
-                    o[i] = pv[i];
-                  }
+              for (int i = 0; i < 4; ++i) {
+                const float2 f = unpack2(cvt_pair<F16>(pv[i]));
+                ssq[p] += f.x * f.x + f.y * f.y;
+                if (has_nw) {
+                  const float2 g = unpack2(cvt_pair<F16>(q[i]));
+                  o[i] = uint32_t(cvt_out<F16>(f.x * g.x)) | (uint32_t(cvt_out<F16>(f.y * g.y)) << 16);
+                } else {
+                  o[i] = pv[i];
                 }
-                if (has_nw) *cell = make_uint4(o[0], o[1], o[2], o[3]);
               }
+              if (has_nw) *cell = make_uint4(o[0], o[1], o[2], o[3]);
             }
           }
         }
@@ -373,74 +334,128 @@ __device__ __forceinline__ void linear_consume_umma_t(WaitCtx &wc, char *smem, M
         s += __shfl_xor_sync(0xffffffffu, s, 2);
         s += __shfl_xor_sync(0xffffffffu, s, 4);
         const int b = rb + p * kRowsPerPass;
-        if (c == 0 && b < B) misc->rnorm_umma[b] = rsqrtf(s / float(a.K) + a.eps);
+        if (c == 0 && b < B) ssum[b] = s;
       }
     }
     // keep the weight-ring position in step with the issuer
-    for (int i = 0; i < nsteps * nblocks; ++i) pos.advance();
+    for (int kb = 0; kb < nkb; kb += kbs) pos.advance();
   }
-  for (int u = 0; u < nunits; ++u) us.advance();
+  for (int u = 0; u < nkb; ++u) us.advance();
 
   wait_mbar(wc, &misc->acc_bar, us.acc_phase);
   us.acc_phase ^= 1u;
-  consumer_bar();   // RMS factors published, every MMA of the task complete
+  consumer_bar();   // statistics published, every MMA of the group complete
   tcgen05_after_sync();
+  if (norm && a.nsplit == 1) {
+    if (tid < B) ssum[tid] = rsqrtf(ssum[tid] / float(a.K) + a.eps);
+    consumer_bar();
+  }
 
-  // Epilogue.  With M = 64 row r of a block is TMEM lane 32 * (r / 16) + r % 16: warp w reads
-  // the lane quarter w % 4, whose lower 16 lanes hold rows 16 * (w % 4) .. + 15, and half of
-  // the token columns.
+  // Epilogue.  With M = 64, token t is TMEM lane 32 * (t / 16) + t % 16: warp w reads the lane
+  // quarter w % 4, whose lower 16 lanes hold tokens 16 * (w % 4) .. + 15, and half of the
+  // 8-column groups (8 neighbouring weight rows).
   const int lq = warp & 3, chalf = warp >> 2;
+  const int tok = lq * 16 + lane;                 // token of this thread (lanes < 16)
+  const bool live = lane < 16 && tok < B;
+  const int ncol8 = Npad >> 3;
+  const int gmid = (ncol8 + 1) >> 1;
+  const int g0 = chalf == 0 ? 0 : gmid, g1 = chalf == 0 ? gmid : ncol8;
   if (!wc.failed) {
-    for (int blk = 0; blk < nblocks; ++blk) {
-      const int r = blk * kUmmaBlockRows + lq * 16 + lane;   // row of the task (lanes < 16)
-      const bool live = lane < 16 && r < a.nrows;
-      const int p = a.row0 + r;                               // row of the weight
-      for (int c0 = chalf * (N / 2); c0 < (chalf + 1) * (N / 2); c0 += 8) {
+    if (a.nsplit > 1) {
+      // partial sums of this K range -> the block's workspace slot, [token][row]
+      float *mine = a.ws + size_t(a.split) * size_t(a.ws_tok) * size_t(a.ws_ld);
+      for (int g = g0; g < g1; ++g) {
         float v[8];
-        tmem_ld8(tmem + (uint32_t(lq * 32) << 16) + uint32_t(blk * nacc * N + c0), v);
-        for (int acc = 1; acc < nacc; ++acc) {
-          float v2[8];
-          tmem_ld8(tmem + (uint32_t(lq * 32) << 16) + uint32_t((blk * nacc + acc) * N + c0), v2);
+        tmem_ld8(tmem + (uint32_t(lq * 32) << 16) + uint32_t(g * 8), v);
+        if (live) {
+          float *dst = mine + size_t(b0 + tok) * a.ws_ld + a.row0 + g * 8;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) v[i] += v2[i];
+          for (int i = 0; i < 8; ++i)
+            if (g * 8 + i < a.nrows) __stcg(dst + i, v[i]);
         }
+      }
+    } else {
+      const float rn = (norm && live) ? ssum[tok] : 1.f;
+      uint16_t *orow = reinterpret_cast<uint16_t *>(a.out) + size_t(b0 + (live ? tok : 0)) * a.ldout;
+      const uint16_t *rrow =
+          reinterpret_cast<const uint16_t *>(a.res) + size_t(b0 + (live ? tok : 0)) * a.ldres;
+      for (int g = g0; g < g1; ++g) {
+        float v[8];
+        tmem_ld8(tmem + (uint32_t(lq * 32) << 16) + uint32_t(g * 8), v);
+        if (!live) continue;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int b = c0 + i;
-          float val = v[i];
-          if (norm) val *= misc->rnorm_umma[b < B ? b : 0];
-          if (silu) {
-            // granules of kSiluGran gate rows then kSiluGran up rows: the partner is 2 lanes on
-            const float up = __shfl_down_sync(0xffffffffu, val, kSiluGran);
-            if (live && b < B && (p % (2 * kSiluGran)) < kSiluGran) {
-              const int col = a.out_col0 + (p / (2 * kSiluGran)) * kSiluGran + p % kSiluGran;
-              reinterpret_cast<uint16_t *>(a.out)[size_t(b) * a.ldout + col] =
-                  cvt_out<F16>(silu_mul_ref(val, up));
+        for (int i = 0; i < 8; ++i) v[i] *= rn;
+        const int r = g * 8;                       // first row of the group inside the block
+        if (silu) {
+          // rows come as 2 gate + 2 up: {g0 g1 u0 u1 g2 g3 u2 u3} -> 4 outputs
+          const int col = a.out_col0 + ((a.row0 + r) >> 1);
+          const uint16_t o[4] = {
+              cvt_out<F16>(silu_mul_ref(v[0], v[2])), cvt_out<F16>(silu_mul_ref(v[1], v[3])),
+              cvt_out<F16>(silu_mul_ref(v[4], v[6])), cvt_out<F16>(silu_mul_ref(v[5], v[7]))};
+          const int nout = min(4, (a.nrows - r) >> 1);
+          if (nout == 4 && (col & 3) == 0) {
+            *reinterpret_cast<uint2 *>(orow + col) =
+                make_uint2(uint32_t(o[0]) | (uint32_t(o[1]) << 16), uint32_t(o[2]) | (uint32_t(o[3]) << 16));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (i < nout) orow[col + i] = o[i];
+          }
+        } else {
+          const int col = a.out_col0 + a.row0 + r;
+          const int nout = min(8, a.nrows - r);
+          const bool res = (a.flags & YPK_F_RESIDUAL) != 0;
+          if (nout == 8 && (col & 7) == 0) {
+            if (res) {
+              const uint4 rv = __ldcg(reinterpret_cast<const uint4 *>(rrow + col));
+              const uint32_t rp[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 f = unpack2(cvt_pair<F16>(rp[i]));
+                v[2 * i] += f.x;
+                v[2 * i + 1] += f.y;
+              }
             }
-          } else if (live && b < B) {
-            const int col = a.out_col0 + p;
-            if (a.flags & YPK_F_RESIDUAL) {
-              val += cvt_one<F16>(
-                  __ldcg(reinterpret_cast<const uint16_t *>(a.res) + size_t(b) * a.ldres + col));
+            uint32_t o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              o[i] = uint32_t(cvt_out<F16>(v[2 * i])) | (uint32_t(cvt_out<F16>(v[2 * i + 1])) << 16);
+            *reinterpret_cast<uint4 *>(orow + col) = make_uint4(o[0], o[1], o[2], o[3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              if (i < nout) {
+                float val = v[i];
+                if (res) val += cvt_one<F16>(__ldcg(rrow + col + i));
+                orow[col + i] = cvt_out<F16>(val);
+              }
             }
-            reinterpret_cast<uint16_t *>(a.out)[size_t(b) * a.ldout + col] = cvt_out<F16>(val);
           }
         }
       }
     }
   }
-  // the next task's first MMA overwrites the accumulators: order these reads before it
+  // the next group's first MMA overwrites the accumulators: order these reads before it
   tcgen05_before_sync();
+  if (a.nsplit > 1 && !wc.failed) {
+    consumer_bar();
+    // own partials are in the workspace already: the finish only needs the arrival protocol
+    linear_splitk_finish<F16, false>(a, misc, b0, B, ssum, [](int, int) { return 0.f; });
+  }
 }
 
 __device__ __forceinline__ void linear_consume_umma(WaitCtx &wc, char *smem, Misc *misc,
                                                     const ypk_task &t, int batch, RingPos &pos,
                                                     UmmaState &us) {
   const LinearArgs a = linear_args(t);
-  if (a.flags & YPK_F_F16) {
-    linear_consume_umma_t<true>(wc, smem, misc, a, batch, pos, us);
-  } else {
-    linear_consume_umma_t<false>(wc, smem, misc, a, batch, pos, us);
+  for (int b0 = 0; b0 < batch; b0 += kUmmaMaxBatch) {
+    const int B = min(kUmmaMaxBatch, batch - b0);
+    if (a.flags & YPK_F_F16) {
+      linear_consume_umma_group<true>(wc, smem, misc, a, b0, B, pos, us);
+    } else {
+      linear_consume_umma_group<false>(wc, smem, misc, a, b0, B, pos, us);
+    }
+    consumer_bar();   // the group's shared-memory scratch is dead before the next one starts
   }
 }
 

@@ -171,6 +171,25 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
       if (in.flags & YPK_F_RESIDUAL) {
         need[4] = rows(ldr, mb, ocols0 + ocols); align[4] = 2; required[4] = true;
       }
+      // K range / split along K (graphs of more than 8 tokens)
+      const int k0 = a[13], klen = a[14] > 0 ? a[14] : K - a[13];
+      const int split = a[15] & 0xff, nsplit = (a[15] >> 8) & 0xff, ws_tok = a[15] >> 16;
+      if (k0 < 0 || k0 % 64 || klen <= 0 || klen % 64 || k0 + klen > K)
+        return fail(h, YPK_ERR_INVALID, "task %d: LINEAR K range [%d, %d) of %d", ti, k0, k0 + klen, K);
+      if (nsplit > 1) {
+        const int ws_ld = a[8], cnt = a[10];
+        if (mb <= kMaxBatch || (in.flags & (YPK_F_LL_IN | YPK_F_LL_RES | YPK_F_LL_OUT | YPK_F_LL_PUSH)))
+          return fail(h, YPK_ERR_UNSUPPORTED,
+                      "task %d: the split along K is built for graphs of more than %d tokens", ti, kMaxBatch);
+        if (split >= nsplit || ws_tok < mb || ws_ld < row0 + nrows || cnt < 0)
+          return fail(h, YPK_ERR_INVALID, "task %d: split %d of %d, workspace [%d tokens][%d rows]", ti,
+                      split, nsplit, ws_tok, ws_ld);
+        need[5] = uint64_t(nsplit) * ws_tok * ws_ld * 4; align[5] = 16; required[5] = true;
+        need[6] = uint64_t(cnt + 1) * nsplit * ws_tok * 4; align[6] = 4; required[6] = true;
+        need[7] = uint64_t(cnt + 1) * ((ws_tok + 15) / 16) * 4; align[7] = 4; required[7] = true;
+      } else if (klen != K) {
+        return fail(h, YPK_ERR_INVALID, "task %d: a K range needs a split count", ti);
+      }
       // flagged-word copies: 4 bytes per value ([max_tokens][ld / 2] 8-byte words)
       const uint32_t ll = in.flags & (YPK_F_LL_IN | YPK_F_LL_RES | YPK_F_LL_OUT | YPK_F_LL_PUSH);
       if (ll) {
@@ -383,8 +402,8 @@ int encode_kv_tmap(ypk_handle *h, void *base, int hkv, CUtensorMap *out) {
 }
 
 // Rank-3 view {64 columns, rows, K / 64} of a row-major 16-bit weight [rows][ldw] for the
-// tensor-core LINEAR path: box = one 128-byte k-block x 8 rows x 4 k-blocks, 128-byte swizzle,
-// so that a box lands in shared memory as [k-block][row][128 B].
+// tensor-core LINEAR path: box = one 128-byte k-block x 64 rows, 128-byte swizzle, so that a
+// box lands in shared memory as [row][128 B] (eight 8-row core-matrix groups).
 int encode_weight_tmap(ypk_handle *h, void *base, int rows, int K, int ldw, CUtensorMap *out) {
   typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
                                const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
@@ -401,7 +420,7 @@ int encode_weight_tmap(ypk_handle *h, void *base, int rows, int K, int ldw, CUte
   }
   const cuuint64_t dims[3] = {cuuint64_t(kUmmaKBlock), cuuint64_t(rows), cuuint64_t(K / kUmmaKBlock)};
   const cuuint64_t strides[2] = {cuuint64_t(ldw) * 2, cuuint64_t(kUmmaKBlock) * 2};
-  const cuuint32_t box[3] = {cuuint32_t(kUmmaKBlock), 8, cuuint32_t(kUmmaStepKBlocks)};
+  const cuuint32_t box[3] = {cuuint32_t(kUmmaKBlock), cuuint32_t(kUmmaBoxRows), 1};
   const cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, base, dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -813,9 +832,8 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
     t.iarg[9] = -1;
     const int K = t.iarg[0], nrows = t.iarg[2], ldw = t.iarg[4];
     const bool silu_ok = !(t.flags & YPK_F_SILU_MUL) || (t.iarg[1] % (2 * kSiluGran) == 0);
-    if (!umma_possible || K % (kUmmaKBlock * kUmmaStepKBlocks) != 0 || nrows > kMaxAccRows ||
-        ldw % 8 != 0 || (t.ptr[1] & 15u) != 0 || t.iarg[3] % 8 != 0 || (t.ptr[0] & 15u) != 0 ||
-        !silu_ok)
+    if (!umma_possible || K % kUmmaKBlock != 0 || nrows > kMaxAccRows || ldw % 8 != 0 ||
+        (t.ptr[1] & 15u) != 0 || t.iarg[3] % 8 != 0 || (t.ptr[0] & 15u) != 0 || !silu_ok)
       continue;
     size_t k = 0;
     while (k < wkeys.size() &&
@@ -968,6 +986,7 @@ int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_
   rt.tmaps = h->d_tmaps;
   rt.use_tmem = h->use_tmem ? 1 : 0;
   rt.umma_policy = h->umma_policy;
+  { const char *d = getenv("YPK_UMMA_DEPTH"); rt.umma_depth = d ? std::min(5, std::max(1, atoi(d))) : 4; }
   rt.ll_epoch = h->ll_epoch;
   { const char *pf = getenv("YPK_LL_PUSH_FENCE"); rt.ll_push_fence = (pf && pf[0] == '1') ? 1 : 0; }
   rt.ar_epoch = h->ar_epoch;

@@ -404,6 +404,29 @@ def level_partition(n_units: int, unit_bytes: int, loads: List[float]) -> List[i
     return counts
 
 
+def splitk_plan(nrows: int, K: int, gran: int, W: int):
+    """Row blocks x K ranges for a linear operator of a graph with more than 8 tokens, or None
+    to keep plain row slabs.  The tensor-core LINEAR path wants 100+ weight rows per task (an
+    instruction then covers enough weight bytes to follow HBM); an operator with fewer rows
+    per worker than that (o_proj, down_proj, qkv) is cut along K as well, so that it still
+    makes about one task per worker.  Returns (rows per block, number of splits)."""
+    if nrows >= 96 * W or K % 64:
+        return None
+    nkb = K // 64
+    for S in range(2, 17):
+        if nkb < 4 * S:
+            break
+        nb = max(1, W // S)
+        unit = 8 if gran in (1, 2, 4, 8) else gran
+        rows = -(-nrows // nb)
+        rows = -(-rows // unit) * unit
+        if rows > MAX_TASK_ROWS:
+            continue
+        if rows >= 100 or S == 16 or nkb < 4 * (S + 1):
+            return rows, S
+    return None
+
+
 # --------------------------------------------------------------------------- lowering
 def _all_flagged(plan, ops, oi):
     """True if every activation operator `oi` reads arrives as flagged words."""
@@ -451,6 +474,10 @@ def tensor_dependencies(ops, serving: bool):
         if op.kind == "allreduce":
             reads.append("allreduce_exchange")
             writes.append("allreduce_exchange")
+        if op.attrs.get("splitk_key") is not None:
+            # operators of one shape share the workspace of their split along K
+            reads.append(("splitk", op.attrs["splitk_key"]))
+            writes.append(("splitk", op.attrs["splitk_key"]))
         need = set()
         for t in reads:
             if t in last_writer:
@@ -536,6 +563,7 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
 
     attn_scratch = None
     attn_tag_ids = set()
+    splitk_bufs: Dict[tuple, tuple] = {}
     prev_event, prev_count = -1, 0
 
     for oi, op in enumerate(ops):
@@ -603,6 +631,50 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
             if Nrows % gran:
                 raise ValueError(f"fused gate/up weight rows must be a multiple of {gran}")
             unit_bytes = gran * K * 2
+            sk = splitk_plan(Nrows, K, gran, W) if max_tokens > 8 else None
+            if sk is not None:
+                # row blocks x K ranges: every task leaves fp32 partial sums in a workspace,
+                # the last split of a block to arrive adds them and writes the rows
+                rows_blk, S = sk
+                key = (Nrows, S)
+                if key not in splitk_bufs:
+                    nb_max = -(-Nrows // rows_blk)
+                    splitk_bufs[key] = (
+                        scratch((S * max_tokens * Nrows,), float32, f"splitk_ws_{Nrows}x{S}"),
+                        scratch((nb_max * S * max_tokens,), float32, f"splitk_ss_{Nrows}x{S}"),
+                        scratch((nb_max * ((max_tokens + 15) // 16),), int32, f"splitk_cnt_{Nrows}x{S}"))
+                ws, ws_ss, ws_cnt = splitk_bufs[key]
+                op.attrs["splitk_key"] = key
+                nkb = K // 64
+                kb_edges = [nkb * s // S for s in range(S + 1)]
+                order = sorted(range(W), key=lambda w_: loads[w_])
+                ti_local = 0
+                for blk, r in enumerate(range(0, Nrows, rows_blk)):
+                    take = min(rows_blk, Nrows - r)
+                    for s_ in range(S):
+                        k0, k1 = kb_edges[s_] * 64, kb_edges[s_ + 1] * 64
+                        ts = TaskSpec(N.TASK_LINEAR, flags=flags, op_id=oi)
+                        ts.ptr[0], ts.ptr[1], ts.ptr[2] = (x, 0), (w, 0), (o, 0)
+                        if nw is not None:
+                            ts.ptr[3] = (nw, 0)
+                        if flags & N.F_RESIDUAL:
+                            ts.ptr[4] = (res, 0)
+                        ts.ptr[5], ts.ptr[6], ts.ptr[7] = (ws, 0), (ws_ss, 0), (ws_cnt, 0)
+                        ts.iarg[:9] = [K, r, take, x.dims[1], w.dims[1], o.dims[1],
+                                       res.dims[1] if res is not None else 0, 0, Nrows]
+                        ts.iarg[10] = blk
+                        ts.iarg[13], ts.iarg[14] = k0, k1 - k0
+                        ts.iarg[15] = s_ | (S << 8) | (max_tokens << 16)
+                        ts.farg[0] = float(op.attrs.get("eps", default_eps))
+                        ts.worker = order[ti_local % W]
+                        ts.weight_bytes = take * (k1 - k0) * 2
+                        loads[ts.worker] += ts.weight_bytes
+                        tasks.append(ts)
+                        ti_local += 1
+                count = len(tasks) - first
+                _link(tasks, first, ev, plan, ops, oi, prev_event, prev_count)
+                prev_event, prev_count = ev, count
+                continue
             counts = level_partition(units, unit_bytes, loads)
             r = 0
             for wk in range(W):
