@@ -148,7 +148,10 @@ def test_gated_mlp_fused(B, H, I, tc, monkeypatch):
     ypk.silu_mul_layer(mid, act, (groups, 1, 1), (128, 1, 1))
     ypk.linear_with_residual_layer(act, wdt, xt, ot, (H // 64, 1, 1), (128, 1, 1))
     ypk.compile()
-    assert [o.kind for o in ypk.lower().ops] == ["linear", "linear"], "gate/up + silu must fuse"
+    # gate/up + silu fuse; the norm folds into the projection in graphs of at most 8 tokens
+    # and stays an operator of its own beyond (the tensor-core path takes its tokens by TMA)
+    assert [o.kind for o in ypk.lower().ops] == (["linear", "linear"] if MT <= 8 else
+                                                 ["rmsnorm", "linear", "linear"])
     ypk(batch=B)
     torch.cuda.synchronize()
     if tc != "auto":

@@ -64,7 +64,7 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
       mbar_init(&misc->empty_bar[s], kConsumerWarps);
     }
     for (int s = 0; s < kUmmaUnits; ++s) {
-      mbar_init(&misc->xfull_bar[s], kConsumerWarps - 1);
+      mbar_init(&misc->xfull_bar[s], 1);
       mbar_init(&misc->xempty_bar[s], 1);
     }
     mbar_init(&misc->acc_bar, 1);

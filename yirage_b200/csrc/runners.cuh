@@ -80,7 +80,7 @@ __device__ __noinline__ bool run_small(const Runtime *rt, Misc *misc, int worker
     case YPK_TASK_ARGMAX_REDUCE:
       if (!argmax_reduce_task<TP>(wc, rt, t, batch, iter)) wc.failed = true;
       break;
-    case YPK_TASK_RMSNORM: rmsnorm_task(t, batch); break;
+    case YPK_TASK_RMSNORM: rmsnorm_task(t, batch, misc->rnorm); break;
     case YPK_TASK_SILU_MUL: silu_mul_task(t, batch); break;
     case YPK_TASK_ALLREDUCE:
       if constexpr (!TP) {

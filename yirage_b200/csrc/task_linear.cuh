@@ -49,6 +49,7 @@ struct LinearArgs {
   // task covers columns [k0, k0 + klen) of K; with nsplit > 1 it is split `split` of
   // `nsplit` of its row block, whose partial sums meet in the workspace `ws`
   int k0, klen, split, nsplit, ws_ld, ws_tok, cnt_idx;
+  int x_tmap;   // tensor map of x for the tensor-core path (graphs of more than 8 tokens), or -1
   float *ws, *ws_ss;
   unsigned int *ws_cnt;
 };
@@ -86,6 +87,7 @@ __device__ __forceinline__ LinearArgs linear_args(const ypk_task &t, const Runti
   a.nsplit = max(1, (t.iarg[15] >> 8) & 0xff);
   a.ws_tok = t.iarg[15] >> 16;      // tokens per split slot of the workspace
   a.ws_ld = t.iarg[8];              // its row pitch (weight rows of the operator)
+  a.x_tmap = t.iarg[11];
   a.cnt_idx = t.iarg[10];           // row block's counter (the tag fields are free in wide graphs)
   a.ws = a.ws_ss = nullptr;
   a.ws_cnt = nullptr;
@@ -845,6 +847,44 @@ __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Mi
   }
 }
 
+// Epilogue from fp32 sums held somewhere addressable (shared memory): acc(r, b) = sum for row r
+// of the task and token b of the group; four consecutive rows per thread and step.  RMS
+// factors, if any, are in misc->rnorm_umma.
+template <bool F16, typename AccFn>
+__device__ __forceinline__ void linear_epilogue_quads(const LinearArgs &a, const Misc *misc, int b0,
+                                                      int B, bool norm, AccFn acc) {
+  const bool silu = (a.flags & YPK_F_SILU_MUL) != 0;
+  const int nquads = (a.nrows + 3) >> 2;
+  for (int it = threadIdx.x; it < nquads * B; it += kConsumerThreads) {
+    const int b = it / nquads, r = (it - b * nquads) * 4;
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = r + i < a.nrows ? acc(r + i, b) : 0.f;
+    if (norm) {
+      const float rn = misc->rnorm_umma[b];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] *= rn;
+    }
+    uint16_t *orow = reinterpret_cast<uint16_t *>(a.out) + size_t(b0 + b) * a.ldout;
+    if (silu) {
+      const int col = a.out_col0 + ((a.row0 + r) >> 1);
+      *reinterpret_cast<uint32_t *>(orow + col) =
+          uint32_t(cvt_out<F16>(silu_mul_ref(v[0], v[2]))) | (uint32_t(cvt_out<F16>(silu_mul_ref(v[1], v[3]))) << 16);
+    } else {
+      const int col = a.out_col0 + a.row0 + r;
+      const uint16_t *rrow = reinterpret_cast<const uint16_t *>(a.res) + size_t(b0 + b) * a.ldres;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (r + i < a.nrows) {
+          float o = v[i];
+          if (a.flags & YPK_F_RESIDUAL) o += cvt_one<F16>(__ldcg(rrow + col + i));
+          orow[col + i] = cvt_out<F16>(o);
+        }
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------ 16 tokens per pass
 // More than 8 tokens: the weights are streamed once per 16 tokens.  Every weight fragment
 // (ldmatrix of 16 rows x 16 columns) feeds two m16n8k16 MMAs, tokens 0..7 and 8..15, so
@@ -870,7 +910,6 @@ __device__ __forceinline__ void linear_consume_group16(WaitCtx &wc, char *smem, 
   const uint16_t *nw = reinterpret_cast<const uint16_t *>(a.norm_w);
   const bool norm = (a.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT)) != 0;
   const bool has_nw = (a.flags & YPK_F_NORM) != 0;
-  const bool silu = (a.flags & YPK_F_SILU_MUL) != 0;
   const int KC = min(a.klen, kStageCols);
   const int xpitch = KC + 8;
 
@@ -1053,36 +1092,7 @@ __device__ __forceinline__ void linear_consume_group16(WaitCtx &wc, char *smem, 
     }
     consumer_bar();
   }
-  // epilogue: item = token * nquads + quad (4 consecutive rows)
-  const int nquads = (a.nrows + 3) >> 2;
-  for (int it = tid; it < nquads * B; it += kConsumerThreads) {
-    const int b = it / nquads, r = (it - b * nquads) * 4;
-    float v[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = r + i < a.nrows ? accs[(r + i) * kTok + b] : 0.f;
-    if (norm) {
-      const float rn = misc->rnorm_umma[b];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] *= rn;
-    }
-    uint16_t *orow = reinterpret_cast<uint16_t *>(a.out) + size_t(b0 + b) * a.ldout;
-    if (silu) {
-      const int col = a.out_col0 + ((a.row0 + r) >> 1);
-      orow[col] = cvt_out<F16>(silu_mul_ref(v[0], v[2]));
-      orow[col + 1] = cvt_out<F16>(silu_mul_ref(v[1], v[3]));
-    } else {
-      const int col = a.out_col0 + a.row0 + r;
-      const uint16_t *rrow = reinterpret_cast<const uint16_t *>(a.res) + size_t(b0 + b) * a.ldres;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        if (r + i < a.nrows) {
-          float o = v[i];
-          if (a.flags & YPK_F_RESIDUAL) o += cvt_one<F16>(__ldcg(rrow + col + i));
-          orow[col + i] = cvt_out<F16>(o);
-        }
-      }
-    }
-  }
+  linear_epilogue_quads<F16>(a, misc, b0, B, norm, [&](int r, int b) { return accs[r * kTok + b]; });
 }
 
 // More than 8 tokens on the GEMV path: groups of 16.

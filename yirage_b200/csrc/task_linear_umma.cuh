@@ -20,11 +20,14 @@
 //                 of the task's whole row block: [k-block][box][64 rows][128 B].  Rows past
 //                 the task's block belong to a neighbour (their columns of the accumulator
 //                 are never read); rows past the end of the tensor arrive as zeros.
-//   A (tokens)    staged by consumer warps 1..7 with 16-byte cp.async into a second ring of
-//                 seven 8 KB units (one k-block of up to 64 tokens each), same swizzled
-//                 K-major layout, then multiplied in place by the norm weight while the RMS
-//                 statistics are taken.  Rows past the batch are never written: they hold
-//                 stale bytes, which only reach accumulator rows that nobody reads.
+//   A (tokens)    tiled TMA as well, through the same kind of view of the activation tensor:
+//                 one box of 64 token rows x one k-block per unit of a second ring of seven
+//                 8 KB units, issued by lane 0 of consumer warp 1.  The task must not carry a
+//                 fused RMSNorm: graphs of more than 8 tokens keep the norm as an operator of
+//                 its own (as the reference does), so the tokens need no arithmetic on their
+//                 way in.  (A first version staged them with cp.async and multiplied the norm
+//                 weight in place: the generic-to-async proxy fence that every unit then
+//                 needs cost about 0.4 us per unit, more than the MMAs of the unit.)
 //   D             fp32 in tensor memory: 64 rows (tokens) x Npad columns (weight rows of the
 //                 block, padded to 8).  Lane 0 of consumer warp 0 issues four
 //                 tcgen05.mma.cta_group::1.kind::f16 (M = 64, N = Npad, K = 16) per k-block;
@@ -51,13 +54,33 @@ __device__ __forceinline__ int umma_stage_kblocks(int nrows) {
   return kStageBytes / (umma_nbox(nrows) * kUmmaBoxBytes);
 }
 
+// Order in which a worker walks the stages of its K range.  Every task of an operator reads
+// the same token rows; if all workers walked K in the same order they would all ask L2 for the
+// same 8 KB of tokens at the same moment (measured: the token ring then delivers a k-block per
+// microsecond, the tensor pipe could take three).  Each worker therefore starts at its own
+// stage and wraps around; the fp32 sum over K is taken in that rotated order.
+struct UmmaWalk {
+  int nkb, kbs, stages, rot;
+  __device__ __forceinline__ UmmaWalk(int nkb_, int kbs_, int worker) : nkb(nkb_), kbs(kbs_) {
+    stages = (nkb + kbs - 1) / kbs;
+    rot = int((unsigned(worker) * 37u) % unsigned(stages));
+  }
+  // stage visited at position si: its first k-block and its number of k-blocks
+  __device__ __forceinline__ void stage(int si, int &kb, int &nk) const {
+    int s = si + rot;
+    if (s >= stages) s -= stages;
+    kb = s * kbs;
+    nk = min(kbs, nkb - kb);
+  }
+};
+
 // Does this task take the tensor-core path at this batch?  Producer and consumers evaluate
 // this identically.  Every eligible task with more than 8 tokens does (measured on the gated
 // MLP of Llama-3-8B: 16 tokens 0.58 ms against 0.64 ms for one 16-token GEMV pass, 64 tokens
 // 0.70 ms against 2.36 ms for four passes); YPK_TENSOR_CORE=never keeps the GEMV passes.
 __device__ __forceinline__ bool linear_uses_umma(const Runtime &rt, const ypk_task &t, int batch) {
-  if (batch <= kMaxBatch || t.iarg[9] < 0 || rt.umma_policy == 2) return false;
-  return true;
+  if (batch <= kMaxBatch || t.iarg[9] < 0 || t.iarg[11] < 0 || rt.umma_policy == 2) return false;
+  return (t.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT)) == 0;
 }
 
 __device__ __forceinline__ void tma_load_3d_hint(void *dst, const void *tmap, int x, int y, int z,
@@ -81,9 +104,11 @@ __device__ __forceinline__ bool linear_produce_umma(WaitCtx &wc, char *smem, Mis
   const int nbox = umma_nbox(a.nrows), kbs = umma_stage_kblocks(a.nrows);
   const int kb0 = a.k0 / kUmmaKBlock, nkb = a.klen / kUmmaKBlock;
   const int ngroups = (batch + kUmmaMaxBatch - 1) / kUmmaMaxBatch;
+  const UmmaWalk walk(nkb, kbs, wc.worker);
   for (int grp = 0; grp < ngroups; ++grp) {
-    for (int kb = 0; kb < nkb; kb += kbs) {
-      const int nk = min(kbs, nkb - kb);
+    for (int si = 0; si < walk.stages; ++si) {
+      int kb, nk;
+      walk.stage(si, kb, nk);
       if (!wait_mbar(wc, &misc->empty_bar[pos.slot], pos.phase ^ 1u)) return false;
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       char *stage = smem + kOffRing + pos.slot * kStageBytes;
@@ -149,6 +174,20 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, "
+      "%13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
 __device__ __forceinline__ void tcgen05_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
@@ -190,14 +229,12 @@ __device__ __forceinline__ void linear_consume_umma_group(WaitCtx &wc, char *sme
                                                           RingPos &pos, UmmaState &us) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   char *xring = smem + kOffXs;                       // kUmmaUnits x 8 KB
-  const uint16_t *x = reinterpret_cast<const uint16_t *>(a.x) + size_t(b0) * a.ldx;
-  const uint16_t *nw = reinterpret_cast<const uint16_t *>(a.norm_w);
-  const bool norm = (a.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT)) != 0;
-  const bool has_nw = (a.flags & YPK_F_NORM) != 0;
+  constexpr bool norm = false;   // a fused norm keeps the task on the GEMV path (linear_uses_umma)
   const bool silu = (a.flags & YPK_F_SILU_MUL) != 0;
   const int Npad = umma_npad(a.nrows);
   const int nbox = umma_nbox(a.nrows), kbs = umma_stage_kblocks(a.nrows);
   const int nkb = a.klen / kUmmaKBlock;              // k-blocks of the task = token units
+  const UmmaWalk walk(nkb, kbs, wc.worker);
   const uint32_t tmem = misc->tmem_base;
   // sums of squares over this task's K range, turned into the RMS factors in place
   float *ssum = misc->rnorm_umma;
@@ -210,14 +247,15 @@ __device__ __forceinline__ void linear_consume_umma_group(WaitCtx &wc, char *sme
     unsigned long long *prec = lane == 0 ? misc->prof_rec : nullptr;
     unsigned long long wait_w = 0, wait_x = 0;
     UmmaState xu = us;
-    for (int kb = 0; kb < nkb; kb += kbs) {
-      const int nk = min(kbs, nkb - kb);
+    for (int si = 0; si < walk.stages; ++si) {
+      int kb, nk;
+      walk.stage(si, kb, nk);
       unsigned long long tw = prec ? globaltimer() : 0ull;
       const bool got = wait_mbar(wc, &misc->full_bar[pos.slot], pos.phase);
       if (prec) {
         const unsigned long long now = globaltimer();
         wait_w += now - tw;
-        if (kb == 0) prec[4] = now;
+        if (si == 0) prec[4] = now;
       }
       const char *stage = smem + kOffRing + pos.slot * kStageBytes;
       for (int j = 0; j < nk; ++j) {
@@ -231,7 +269,7 @@ __device__ __forceinline__ void linear_consume_umma_group(WaitCtx &wc, char *sme
 #pragma unroll
           for (int kk = 0; kk < kUmmaKBlock / 16; ++kk) {
             // 32 bytes per 16-wide K step inside the swizzle atom: +2 in the address field
-            umma_f16(tmem, ad + 2ull * kk, bd + 2ull * kk, idesc, kb + j > 0 || kk > 0);
+            umma_f16(tmem, ad + 2ull * kk, bd + 2ull * kk, idesc, si + j > 0 || kk > 0);
           }
           umma_commit(&misc->xempty_bar[xu.xslot]);   // the unit is free once these have run
         }
@@ -254,91 +292,32 @@ __device__ __forceinline__ void linear_consume_umma_group(WaitCtx &wc, char *sme
       prec[7] = wait_x;
     }
     __syncwarp();
-  } else {
-    // ------------------------------------------------------------ token stagers (7 warps)
-    // Thread -> (16-byte chunk c, row b): a warp covers 4 rows x 8 chunks per pass and the
-    // 7 warps 28 rows, so a thread sees the same <= 3 rows in every unit.
-    const int c = lane & 7, rb = (warp - 1) * 4 + (lane >> 3);
-    constexpr int kRowsPerPass = (kConsumerWarps - 1) * 4;                         // 28
-    constexpr int kMaxPasses = (kUmmaMaxBatch + kRowsPerPass - 1) / kRowsPerPass;  // 3
-    const int kDepth = wc.rt->umma_depth;     // units in flight (1..5)
-    float ssq[kMaxPasses] = {0.f, 0.f, 0.f};
-    UmmaState xi = us, xf = us;   // issue / finish positions
-    for (int u = 0; u < nkb + kDepth; ++u) {
-      if (u < nkb) {
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ token loader
+    // One tiled-TMA box of 64 token rows x one k-block per unit, in the issuer's order.  The
+    // bytes arrive through the async proxy, as the tensor core reads them: no fence, no
+    // thread touches them.  (Rows past the batch are rows of the activation buffer that this
+    // iteration did not write, or zero fill past its end: they only reach accumulator rows
+    // that nobody reads.)
+    const char *xmap = static_cast<const char *>(wc.rt->tmaps) + size_t(a.x_tmap) * 128;
+    UmmaState xi = us;
+    for (int si = 0; si < walk.stages; ++si) {
+      int kb, nk;
+      walk.stage(si, kb, nk);
+      for (int j = 0; j < nk; ++j) {
         const bool free_ok = wait_mbar(wc, &misc->xempty_bar[xi.xslot], xi.xphase ^ 1u);
-        char *unit = xring + xi.xslot * kUmmaUnitBytes;
-        if (free_ok) {
-          const int k = a.k0 + u * kUmmaKBlock + c * 8;
-          // the norm weights of this unit are wanted a few units from now: bring them to L1
-          if (has_nw && rb < B) asm volatile("prefetch.global.L1 [%0];" ::"l"(nw + k));
-#pragma unroll
-          for (int p = 0; p < kMaxPasses; ++p) {
-            const int b = rb + p * kRowsPerPass;
-            if (b < B) {
-              asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
-                               smem_u32(unit + b * 128 + ((c ^ (b & 7)) << 4))),
-                           "l"(x + size_t(b) * a.ldx + k)
-                           : "memory");
-            }
-          }
+        if (free_ok && lane == 0) {
+          mbar_expect_tx(&misc->xfull_bar[xi.xslot], kUmmaUnitBytes);
+          tma_load_3d(xring + xi.xslot * kUmmaUnitBytes, xmap, 0, b0, a.k0 / kUmmaKBlock + kb + j,
+                      &misc->xfull_bar[xi.xslot]);
         }
+        __syncwarp();
         xi.advance();
       }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      if (u >= kDepth) {
-        const int uf = u - kDepth;
-        cp_async_wait_pending(kDepth);
-        char *unit = xring + xf.xslot * kUmmaUnitBytes;
-        if (norm) {
-          const int k = a.k0 + uf * kUmmaKBlock + c * 8;
-          uint4 wv = make_uint4(0u, 0u, 0u, 0u);
-          if (has_nw) wv = __ldg(reinterpret_cast<const uint4 *>(nw + k));
-          const uint32_t q[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-          for (int p = 0; p < kMaxPasses; ++p) {
-            const int b = rb + p * kRowsPerPass;
-            if (b < B) {
-              uint4 *cell = reinterpret_cast<uint4 *>(unit + b * 128 + ((c ^ (b & 7)) << 4));
-              const uint4 v = *cell;
-              const uint32_t pv[4] = {v.x, v.y, v.z, v.w};
-              uint32_t o[4];
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float2 f = unpack2(cvt_pair<F16>(pv[i]));
-                ssq[p] += f.x * f.x + f.y * f.y;
-                if (has_nw) {
-                  const float2 g = unpack2(cvt_pair<F16>(q[i]));
-                  o[i] = uint32_t(cvt_out<F16>(f.x * g.x)) | (uint32_t(cvt_out<F16>(f.y * g.y)) << 16);
-                } else {
-                  o[i] = pv[i];
-                }
-              }
-              if (has_nw) *cell = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-          }
-        }
-        // generic-proxy writes (cp.async, the fix-up) -> visible to the tensor core
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0 && !wc.failed) mbar_arrive(&misc->xfull_bar[xf.xslot]);
-        xf.advance();
-      }
+      pos.advance();   // keep the weight-ring position in step with the issuer
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    if (norm) {
-#pragma unroll
-      for (int p = 0; p < kMaxPasses; ++p) {
-        float s = ssq[p];
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        const int b = rb + p * kRowsPerPass;
-        if (c == 0 && b < B) ssum[b] = s;
-      }
-    }
-    // keep the weight-ring position in step with the issuer
-    for (int kb = 0; kb < nkb; kb += kbs) pos.advance();
+  } else {
+    for (int si = 0; si < walk.stages; ++si) pos.advance();
   }
   for (int u = 0; u < nkb; ++u) us.advance();
 
@@ -360,6 +339,44 @@ __device__ __forceinline__ void linear_consume_umma_group(WaitCtx &wc, char *sme
   const int ncol8 = Npad >> 3;
   const int gmid = (ncol8 + 1) >> 1;
   const int g0 = chalf == 0 ? 0 : gmid, g1 = chalf == 0 ? gmid : ncol8;
+  if (!wc.failed && B <= 32) {
+    // Few tokens: only the warps of the first one or two lane quarters can reach them (a warp
+    // reads its own quarter of the TMEM lanes), 16 threads each.  They move the accumulator
+    // to shared memory (the token ring is idle by now) and all 256 threads run the epilogue
+    // from there.
+    const int pitch = Npad + 4;                   // floats; rows stay 16-byte aligned
+    float *acc_s = reinterpret_cast<float *>(smem + kOffXs);   // [B][pitch] <= 32 x 260 x 4 B
+    if (lq * 16 < B) {                            // warp-uniform
+      for (int g = g0; g < g1; g += 2) {
+        if (g + 1 < g1) {
+          float v[16];
+          tmem_ld16(tmem + (uint32_t(lq * 32) << 16) + uint32_t(g * 8), v);
+          if (live) {
+            float4 *dst = reinterpret_cast<float4 *>(acc_s + tok * pitch + g * 8);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          }
+        } else {
+          float v[8];
+          tmem_ld8(tmem + (uint32_t(lq * 32) << 16) + uint32_t(g * 8), v);
+          if (live) {
+            float4 *dst = reinterpret_cast<float4 *>(acc_s + tok * pitch + g * 8);
+            dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+            dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+          }
+        }
+      }
+    }
+    tcgen05_before_sync();
+    consumer_bar();
+    auto acc = [&](int r, int b) { return acc_s[b * pitch + r]; };
+    if (a.nsplit > 1) {
+      linear_splitk_finish<F16, true>(a, misc, b0, B, ssum, acc);
+    } else {
+      linear_epilogue_quads<F16>(a, misc, b0, B, false, acc);
+    }
+    return;
+  }
   if (!wc.failed) {
     if (a.nsplit > 1) {
       // partial sums of this K range -> the block's workspace slot, [token][row]

@@ -138,30 +138,89 @@ __device__ __forceinline__ bool argmax_reduce_task(WaitCtx &wc, const Runtime *r
 
 // out[b, :] = bf16(x * rsqrt(mean(x^2) + eps) * w) for rows [row0, row0+nrows) of the batch
 // (tasks/hopper/rmsnorm_hopper.cuh:20-155).  ptr = {x, w, out}; iarg = {K, row0, nrows, ldx, ldout}.
-__device__ __forceinline__ void rmsnorm_task(const ypk_task &t, int batch) {
+// The CTA takes the rows one after the other: 16-byte loads, the row kept in registers
+// between the two passes (K <= 16384), statistics summed across the 8 warps through `red`
+// ([8] floats of shared memory).
+template <bool F16>
+__device__ __forceinline__ void rmsnorm_rows(const ypk_task &t, int batch, float *red) {
   const uint16_t *x = reinterpret_cast<const uint16_t *>(t.ptr[0]);
   const uint16_t *w = reinterpret_cast<const uint16_t *>(t.ptr[1]);
   uint16_t *out = reinterpret_cast<uint16_t *>(t.ptr[2]);
   const int K = t.iarg[0], row0 = t.iarg[1], ldx = t.iarg[3], ldo = t.iarg[4];
   const int row1 = min(batch, row0 + t.iarg[2]);
   const float eps = t.farg[0];
-  const bool f16 = (t.flags & YPK_F_F16) != 0;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int b = row0 + warp; b < row1; b += kConsumerWarps) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr int kV = 8;   // 16-byte chunks per thread: 8 x 8 x 256 = 16384 columns
+  const bool vec = (K % 8) == 0 && K <= kV * 8 * kConsumerThreads && (ldx % 8) == 0 && (ldo % 8) == 0;
+  for (int b = row0; b < row1; ++b) {
+    const uint16_t *xr = x + size_t(b) * ldx;
+    uint16_t *orow = out + size_t(b) * ldo;
     float ss = 0.f;
-    for (int k = lane; k < K; k += 32) {
-      const uint16_t v = __ldcg(x + size_t(b) * ldx + k);
-      const float f = f16 ? cvt_one<true>(v) : cvt_one<false>(v);
-      ss += f * f;
+    uint4 xv[kV];
+    if (vec) {
+#pragma unroll
+      for (int u = 0; u < kV; ++u) {
+        const int k = (u * kConsumerThreads + tid) * 8;
+        xv[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (k < K) xv[u] = __ldcg(reinterpret_cast<const uint4 *>(xr + k));
+      }
+#pragma unroll
+      for (int u = 0; u < kV; ++u) {
+        const uint32_t p[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = unpack2(cvt_pair<F16>(p[i]));
+          ss += f.x * f.x + f.y * f.y;
+        }
+      }
+    } else {
+      for (int k = tid; k < K; k += kConsumerThreads) {
+        const float f = cvt_one<F16>(__ldcg(xr + k));
+        ss += f * f;
+      }
     }
-    const float rn = rsqrtf(warp_sum(ss) / float(K) + eps);
-    for (int k = lane; k < K; k += 32) {
-      const uint16_t v = __ldcg(x + size_t(b) * ldx + k);
-      const float f = f16 ? cvt_one<true>(v) : cvt_one<false>(v);
-      const float wf = w ? (f16 ? cvt_one<true>(__ldg(w + k)) : cvt_one<false>(__ldg(w + k))) : 1.f;
-      const float y = f * rn * wf;
-      out[size_t(b) * ldo + k] = f16 ? cvt_out<true>(y) : cvt_out<false>(y);
+    ss = warp_sum(ss);
+    consumer_bar();               // the previous row is done with `red`
+    if (lane == 0) red[warp] = ss;
+    consumer_bar();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < kConsumerWarps; ++i) tot += red[i];
+    const float rn = rsqrtf(tot / float(K) + eps);
+    if (vec) {
+#pragma unroll
+      for (int u = 0; u < kV; ++u) {
+        const int k = (u * kConsumerThreads + tid) * 8;
+        if (k < K) {
+          uint4 wv = make_uint4(0u, 0u, 0u, 0u);
+          if (w) wv = __ldg(reinterpret_cast<const uint4 *>(w + k));
+          const uint32_t p[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
+          const uint32_t q[4] = {wv.x, wv.y, wv.z, wv.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = unpack2(cvt_pair<F16>(p[i]));
+            float2 g = make_float2(1.f, 1.f);
+            if (w) g = unpack2(cvt_pair<F16>(q[i]));
+            o[i] = uint32_t(cvt_out<F16>(f.x * rn * g.x)) | (uint32_t(cvt_out<F16>(f.y * rn * g.y)) << 16);
+          }
+          *reinterpret_cast<uint4 *>(orow + k) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+    } else {
+      for (int k = tid; k < K; k += kConsumerThreads) {
+        const float f = cvt_one<F16>(__ldcg(xr + k));
+        const float wf = w ? cvt_one<F16>(__ldg(w + k)) : 1.f;
+        orow[k] = cvt_out<F16>(f * rn * wf);
+      }
     }
+  }
+}
+__device__ __forceinline__ void rmsnorm_task(const ypk_task &t, int batch, float *red) {
+  if (t.flags & YPK_F_F16) {
+    rmsnorm_rows<true>(t, batch, red);
+  } else {
+    rmsnorm_rows<false>(t, batch, red);
   }
 }
 

@@ -843,13 +843,28 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
     wkeys[k].rows = std::max(wkeys[k].rows, t.iarg[1] + nrows);
     t.iarg[9] = int(keys.size() + k);
   }
+  // ... and for their activations (same kind of view; every row the graph can see).  The
+  // index goes where narrow graphs keep a flagged-word tag, which wide graphs do not have.
+  std::vector<WeightKey> xkeys;
+  for (int i = 0; i < num_tasks && umma_possible; ++i) {
+    ypk_task &t = resolved[size_t(i)];
+    if (t.type != YPK_TASK_LINEAR) continue;
+    t.iarg[11] = -1;
+    if (t.iarg[9] < 0 || (t.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT))) continue;
+    const int K = t.iarg[0], ldx = t.iarg[3];
+    size_t k = 0;
+    while (k < xkeys.size() && !(xkeys[k].addr == t.ptr[0] && xkeys[k].K == K && xkeys[k].ldw == ldx))
+      ++k;
+    if (k == xkeys.size()) xkeys.push_back({t.ptr[0], K, ldx, h->cfg.max_num_batched_tokens});
+    t.iarg[11] = int(keys.size() + wkeys.size() + k);
+  }
   h->end_event = tasks[num_tasks - 1].trig_event;
   h->end_count = h->end_event >= 0 ? trig_count[size_t(h->end_event)] : 0;
 
   free_graph(h);
   h->use_tmem = !wkeys.empty();
   if (!(keys.empty() && wkeys.empty()) && !h->host_only) {
-    std::vector<CUtensorMap> maps(keys.size() + wkeys.size());
+    std::vector<CUtensorMap> maps(keys.size() + wkeys.size() + xkeys.size());
     for (size_t k = 0; k < keys.size(); ++k) {
       int rc = encode_kv_tmap(h, reinterpret_cast<void *>(keys[k]), key_hkv[k], &maps[k]);
       if (rc) return rc;
@@ -857,6 +872,11 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
     for (size_t k = 0; k < wkeys.size(); ++k) {
       int rc = encode_weight_tmap(h, reinterpret_cast<void *>(wkeys[k].addr), wkeys[k].rows,
                                   wkeys[k].K, wkeys[k].ldw, &maps[keys.size() + k]);
+      if (rc) return rc;
+    }
+    for (size_t k = 0; k < xkeys.size(); ++k) {
+      int rc = encode_weight_tmap(h, reinterpret_cast<void *>(xkeys[k].addr), xkeys[k].rows, xkeys[k].K,
+                                  xkeys[k].ldw, &maps[keys.size() + wkeys.size() + k]);
       if (rc) return rc;
     }
     CUDA_TRY(h, cudaSetDevice(h->cfg.device));

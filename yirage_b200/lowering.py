@@ -151,7 +151,10 @@ def _dead_after(regs: List[RegisteredTask], start: int, t: DTensor) -> bool:
     return True
 
 
-def fuse(regs: List[RegisteredTask], default_eps: float) -> List[FusedOp]:
+def fuse(regs: List[RegisteredTask], default_eps: float, fuse_norm: bool = True) -> List[FusedOp]:
+    """`fuse_norm` False keeps every RMSNorm an operator of its own (graphs of more than 8
+    tokens: the tensor-core LINEAR path takes its tokens by TMA and cannot scale them on the
+    way in; a norm over 16..128 rows as a separate operator costs a few microseconds)."""
     out: List[FusedOp] = []
     i = 0
     n = len(regs)
@@ -168,7 +171,8 @@ def fuse(regs: List[RegisteredTask], default_eps: float) -> List[FusedOp]:
             if name == "rmsnorm":
                 x, nw, y = rt.operands
                 nxt = regs[i + 1] if i + 1 < n else None
-                if (nxt is not None and canonical_name(nxt.name) in ("linear", "linear_with_residual")
+                if (fuse_norm and nxt is not None
+                        and canonical_name(nxt.name) in ("linear", "linear_with_residual")
                         and nxt.operands[0] is y and _dead_after(regs, i + 2, y)):
                     norm_rt = rt
                     j = i + 1
@@ -523,7 +527,7 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
     after iteration with the batcher in between (offline mode) rather than once per launch.
     Where no tensor travels as flagged words the events follow the tensors
     (`tensor_dependencies`): independent operators do not wait for each other."""
-    ops = fuse(regs, default_eps)
+    ops = fuse(regs, default_eps, fuse_norm=max_tokens <= 8)
     if handoff == "auto":
         handoff = "ll" if max_tokens <= 8 else "event"
     if handoff == "ll" and max_tokens > 8:
