@@ -588,19 +588,33 @@ def run_70b(world, rank, dev, steps, warmup):
     shape = llama.LlamaShape.llama3_70b()
     ctx, page = 2048, 64
     weights = llama.init_weights(shape, dev, 4, world_size=world, rank=rank)
+    torch.cuda.empty_cache()      # the library allocates with cudaMalloc, outside torch's cache
     hbm, src = peaks()
     out = {"workload": "llama3-70b shape decode, context 2048 (BASELINE configs[4]), synthetic context",
            "parallelism": f"tp{world}", "steps": steps, "batch": {}}
     free_b, _ = torch.cuda.mem_get_info()
+    def all_ok(flag):
+        """Every rank must take the same path: the minimum of the ranks' flags."""
+        t = torch.tensor([1 if flag else 0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(int(t))
+
+    # the fused qkv / gate-up copies the library makes of the shard's weights
+    h_, f_, d_ = shape.hidden_size, shape.intermediate_size, shape.head_dim
+    copies = 2 * shape.num_hidden_layers * h_ * ((shape.num_attention_heads + 2 * shape.num_key_value_heads) * d_
+                                                   + 2 * f_) // world
     for B in (1, 8, 64):
+        ypk = None
         try:
             mseq = ctx + warmup + steps + 2
             pages = ((mseq + page - 1) // page) * B
             hkv = shape.num_key_value_heads // world
             kv_need = 2 * shape.num_hidden_layers * pages * page * hkv * shape.head_dim * 2
+            torch.cuda.empty_cache()
             free_b, _ = torch.cuda.mem_get_info()
-            if kv_need > 0.9 * free_b:
-                out["batch"][str(B)] = {"skipped": f"KV cache of {kv_need / 1e9:.0f} GB does not fit beside the weights"}
+            if not all_ok(kv_need + copies < 0.92 * free_b):
+                out["batch"][str(B)] = {"skipped": f"KV cache of {kv_need / 1e9:.0f} GB and {copies / 1e9:.0f} GB of fused "
+                                                   f"weight copies do not fit in the {free_b / 1e9:.0f} GB left beside the weights"}
                 continue
             g = torch.Generator().manual_seed(4)
             tk = torch.zeros(B, mseq, dtype=torch.int64)
@@ -610,10 +624,22 @@ def run_70b(world, rank, dev, steps, warmup):
             kc = torch.empty(shape.num_hidden_layers, pages, page, hkv, shape.head_dim,
                              dtype=torch.bfloat16, device=dev).normal_()
             vc = torch.empty_like(kc).normal_()
-            ypk, st = llama.build_decode_kernel(
-                shape, weights, tokens=tk, prompt_lengths=pl, max_num_batched_requests=B,
-                max_num_batched_tokens=max(8, B), max_num_pages=pages, page_size=page,
-                world_size=world, rank=rank, k_cache=kc, v_cache=vc)
+            try:
+                ypk, st = llama.build_decode_kernel(
+                    shape, weights, tokens=tk, prompt_lengths=pl, max_num_batched_requests=B,
+                    max_num_batched_tokens=max(8, B), max_num_pages=pages, page_size=page,
+                    world_size=world, rank=rank, k_cache=kc, v_cache=vc, defer_connect=True)
+                built = True
+            except Exception as e:
+                built, why = False, str(e)[:200]
+            if not all_ok(built):
+                out["batch"][str(B)] = {"error": "the kernel could not be built on every rank" +
+                                                 ("" if built else f": {why}")}
+                if ypk is not None:
+                    ypk.finalize()
+                continue
+            from yirage_b200 import tensor_parallel
+            tensor_parallel.connect(ypk._handle, world, rank)
             dist.barrier()
             ms, _ = time_decode(ypk, st, steps, warmup, B, ctx, shape, dev, world, rank,
                                 synthetic_context=True)

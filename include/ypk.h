@@ -92,6 +92,14 @@ enum ypk_task_type {
                                   of ptr[7] = [world][max_tokens][ld / 2] on every rank;
                                   ARGMAX_REDUCE: exchange the slice winners (ptr[3]) */
 
+#define YPK_F_LL_OPT 0x1000u   /* LINEAR with YPK_F_LL_IN: take x as flagged words only in
+                                  iterations of one or two tokens; otherwise wait for
+                                  dep_event and read the plain tensor (ptr[0])             */
+
+#define YPK_F_TRIG_WIDE 0x2000u /* publish trig_event only in iterations of more than two tokens:
+                                  its only waiters carry YPK_F_LL_OPT (they count those
+                                  iterations, not all, towards the event's value)          */
+
 #define YPK_TASK_NPTR 8
 #define YPK_TASK_NINT 16
 #define YPK_TASK_NFLT 4

@@ -111,8 +111,13 @@ def test_linear_tensor_core_path(B, K, N, norm, res, dtype, monkeypatch):
                tensor_core=True)
 
 
-def test_linear_small_batch_in_a_large_batch_graph_stays_on_gemv():
-    run_linear(8, 512, 192, max_tokens=64, seed=4, tensor_core=False)
+def test_linear_small_batches_in_a_large_batch_graph():
+    """A graph of up to 64 tokens run with few: 3..8 tokens still take the tensor cores (its
+    operators are cut for them), one or two tokens the GEMV passes."""
+    run_linear(8, 512, 192, max_tokens=64, seed=4, tensor_core=True)
+    run_linear(3, 1024, 520, max_tokens=64, seed=5, norm=True, residual=True, tensor_core=True)
+    run_linear(2, 512, 192, max_tokens=64, seed=6, tensor_core=False)
+    run_linear(1, 4096, 4096, max_tokens=64, seed=7, residual=True, tensor_core=False)
 
 
 @pytest.mark.parametrize("B,H,I,tc", [(1, 512, 1024, "always"), (8, 4096, 1792, "always"),

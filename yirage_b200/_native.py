@@ -34,7 +34,8 @@ TASK_NAMES = {
 
 F_NORM, F_RESIDUAL, F_SILU_MUL, F_F16, F_ROPE, F_NORM_NOWEIGHT = 0x1, 0x2, 0x4, 0x8, 0x10, 0x40
 F_QK_NORM = 0x20
-F_LL_IN, F_LL_RES, F_LL_OUT, F_LL_PUSH = 0x100, 0x200, 0x400, 0x800
+F_LL_IN, F_LL_RES, F_LL_OUT, F_LL_PUSH, F_LL_OPT = 0x100, 0x200, 0x400, 0x800, 0x1000
+F_TRIG_WIDE = 0x2000
 
 NPTR, NINT, NFLT = 8, 16, 4
 

@@ -107,6 +107,7 @@ enum CtrlWord {
   kCtrlTasksDone = 3,
   kCtrlFinished = 4,
   kCtrlUmmaTasks = 5,  // LINEAR tasks that took the tensor-core path
+  kCtrlWideIters = 6,  // iterations of more than two tokens since the last reset
   kCtrlWords = 8
 };
 constexpr unsigned kStateRun = 0, kStateStop = 1;
@@ -133,6 +134,7 @@ struct Runtime {
   int *bstate;        // [0] next request id, [1] page queue head, [2] tail
   long long eos;
   long long base_iter;
+  long long base_wide;   // iterations of more than two tokens before this launch (see YPK_F_TRIG_WIDE)
   unsigned long long budget_ns;
   int mode, max_seq, max_req, max_tok, max_pages, page_size, total_req;
   int max_iters, fixed_batch, resume_pending, rank, world;

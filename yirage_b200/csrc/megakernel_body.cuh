@@ -89,6 +89,7 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
   RingPos pos;
   UmmaState ustate;
   long long iter = rt.base_iter;
+  long long wide_iter = rt.base_wide;   // iterations of more than two tokens so far
   long long tasks_done = 0, umma_done = 0;
   unsigned long long policy = 0;
   if (is_producer) policy = policy_evict_first();
@@ -142,6 +143,7 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
       batch = int(word & 0xffffull);
     }
 
+    if (batch > 2) ++wide_iter;
     if (is_producer) {
       // ---------------------------------------------------------------- producer
       for (int q = q0; q < q1 && ok; ++q) {
@@ -173,10 +175,14 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
           prec[4] = prec[5] = prec[6] = prec[7] = 0ull;
         }
         if (tid == 0) misc->prof_rec = prec;
-        if (t.dep_event >= 0) {
+        // (a LINEAR task whose flagged input is optional polls it instead in small iterations)
+        if (t.dep_event >= 0 && !((t.flags & YPK_F_LL_OPT) && batch <= 2)) {
           if (tid == 0) {
+            // an event that is published in iterations of more than two tokens only
+            // (YPK_F_TRIG_WIDE on its producers) is counted in those iterations
             const unsigned long long need =
-                static_cast<unsigned long long>(t.dep_count) * static_cast<unsigned long long>(iter);
+                static_cast<unsigned long long>(t.dep_count) *
+                static_cast<unsigned long long>((t.flags & YPK_F_LL_OPT) ? wide_iter : iter);
             misc->flag = wait_counter(wc, rt.events + t.dep_event, need, t.dep_event) ? 1 : 0;
           }
           consumer_bar();
@@ -225,7 +231,7 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
           // The barrier orders every thread's global writes before thread 0; its gpu-scope
           // release on the counter is cumulative over them, so a waiter that acquires the
           // counter sees the task's output.
-          if (ok && t.trig_event >= 0 && tid == 0) {
+          if (ok && t.trig_event >= 0 && tid == 0 && !((t.flags & YPK_F_TRIG_WIDE) && batch <= 2)) {
             red_release_add_u64(rt.events + t.trig_event, 1ull);
           }
         }
@@ -278,6 +284,7 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
       }
     }
   }
+  if (tid == 0 && worker == 0 && !is_producer) rt.ctrl[kCtrlWideIters] = (unsigned long long)wide_iter;
   if (tid == 0 && tasks_done) atomicAdd(rt.ctrl + kCtrlTasksDone, (unsigned long long)tasks_done);
   if (tid == 0 && umma_done) atomicAdd(rt.ctrl + kCtrlUmmaTasks, (unsigned long long)umma_done);
   if (WIDE && rt.use_tmem) {

@@ -674,7 +674,7 @@ __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Mi
     // K).  With a norm the values pass through registers: multiplied by the norm weight and
     // squared into the RMS statistics (fp32, as rmsnorm_hopper.cuh); the loads of four
     // iterations are issued before the first is used.
-    if (LL && (a.flags & YPK_F_LL_IN)) {
+    if (LL && (a.flags & YPK_F_LL_IN) && !(MANY && (a.flags & YPK_F_LL_OPT))) {
       if constexpr (LL && MANY) {
         LLPoll poll;
         stage_x_ll_rows<F16>(wc, poll, a.ll_x, a.ldx, a.tag_x, nw, has_nw, xs, xpitch, b0, B, k0, klen, ss);

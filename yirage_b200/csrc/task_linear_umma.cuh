@@ -75,11 +75,12 @@ struct UmmaWalk {
 };
 
 // Does this task take the tensor-core path at this batch?  Producer and consumers evaluate
-// this identically.  Every eligible task with more than 8 tokens does (measured on the gated
-// MLP of Llama-3-8B: 16 tokens 0.58 ms against 0.64 ms for one 16-token GEMV pass, 64 tokens
-// 0.70 ms against 2.36 ms for four passes); YPK_TENSOR_CORE=never keeps the GEMV passes.
+// this identically.  In a graph of more than 8 tokens every eligible task with more than 2
+// tokens does (measured on the gated MLP of Llama-3-8B: 16 tokens 0.52 ms against 0.64 ms for
+// one 16-token GEMV pass, 64 tokens 0.67 ms against 2.36 ms for four passes);
+// YPK_TENSOR_CORE=never keeps the GEMV passes.
 __device__ __forceinline__ bool linear_uses_umma(const Runtime &rt, const ypk_task &t, int batch) {
-  if (batch <= kMaxBatch || t.iarg[9] < 0 || t.iarg[11] < 0 || rt.umma_policy == 2) return false;
+  if (batch <= 2 || t.iarg[9] < 0 || t.iarg[11] < 0 || rt.umma_policy == 2) return false;
   return (t.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT)) == 0;
 }
 

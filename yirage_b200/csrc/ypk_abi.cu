@@ -63,6 +63,7 @@ struct ypk_handle {
   // iterations of earlier runs (see Runtime::ll_epoch / ar_epoch)
   unsigned long long ll_epoch = 0, ar_epoch = 0;
   long long abort_iters = 0;   // last iteration an aborted launch had published
+  long long wide_iters = 0;    // iterations of more than two tokens since the last reset
   int pending_tokens = 0;
   bool resume_pending = false;
   bool finished = false;
@@ -907,6 +908,7 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
   h->ar_epoch += static_cast<unsigned long long>(h->base_iter);
   h->ll_epoch += static_cast<unsigned long long>(h->base_iter) + 1;
   h->base_iter = 0;
+  h->wide_iters = 0;
   h->resume_pending = false;
   h->pending_tokens = 0;
   h->graph_loaded = true;
@@ -928,6 +930,7 @@ int ypk_reset(ypk_handle *h) {
   h->ll_epoch += static_cast<unsigned long long>(std::max(h->base_iter, h->abort_iters)) + 1;
   h->abort_iters = 0;
   h->base_iter = 0;
+  h->wide_iters = 0;
   h->resume_pending = false;
   h->pending_tokens = 0;
   h->finished = false;
@@ -987,6 +990,7 @@ int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_
   rt.bstate = h->d_bstate;
   rt.eos = c.eos_token_id;
   rt.base_iter = h->base_iter;
+  rt.base_wide = h->wide_iters;
   rt.budget_ns = c.wait_budget_ns;
   rt.mode = c.mode;
   rt.max_seq = c.max_seq_length;
@@ -1063,6 +1067,7 @@ int ypk_wait(ypk_handle *h) {
   unsigned long long words[kCtrlWords];
   CUDA_TRY(h, cudaMemcpy(words, h->d_ctrl, sizeof words, cudaMemcpyDeviceToHost));
   h->status.tasks_executed = (int64_t)words[kCtrlTasksDone];
+  h->wide_iters = (long long)words[kCtrlWideIters];
   h->status.tensor_core_tasks = (int64_t)words[kCtrlUmmaTasks];
   if (words[kCtrlAbort]) {
     const unsigned long long info = words[kCtrlFailInfo];

@@ -142,7 +142,7 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
                         k_cache: Optional[torch.Tensor] = None,
                         v_cache: Optional[torch.Tensor] = None, compile: bool = True,
                         dry_run: bool = False, profiler_tensor: Optional[torch.Tensor] = None, handoff: Optional[str] = None,
-                        vocab_parallel: Optional[bool] = None):
+                        vocab_parallel: Optional[bool] = None, defer_connect: bool = False):
     """Build (and compile) the decode megakernel for `weights`.  Returns (ypk, state) where
     state holds the meta tensors, caches and rope tables the kernel works on."""
     dev = tokens.device
@@ -295,5 +295,7 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
              "lm_head": lm_head, "vocab_slice": (rank * vslice if vocab_parallel else 0, vslice),
              "tensors": {"argmax_in": argmax_in, "attn_out": attn_out}}
     if compile:
-        ypk.compile(dry_run=dry_run)
+        # defer_connect: the caller exchanges the ranks' arena handles itself
+        # (tensor_parallel.connect), e.g. after checking that every rank could build
+        ypk.compile(dry_run=dry_run, defer_connect=defer_connect)
     return ypk, state

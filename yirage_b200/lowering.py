@@ -49,6 +49,12 @@ SILU_GRAN = 2                # kSiluGran: fused gate/up rows come as 2 gate + 2 
 # against the one of a plain copy: measured on Llama-3-8B, the 14336-wide MLP activation is
 # still 0.7 % faster per token as flagged words than behind an event.
 MAX_FLAGGED_COLS = int(os.environ.get("YPK_MAX_FLAGGED_COLS", "16384"))
+# Above this width a tensor is taken as flagged words only by iterations of one or two tokens:
+# with more tokens the reader has to poll tokens x width words chunk by chunk (measured on the
+# 14336-wide MLP activation of Llama-3-8B at 8 tokens: the down projection takes 1.3x as long
+# as behind an event), so the producer also publishes its event and the reader decides per
+# iteration (YPK_F_LL_OPT).
+WIDE_FLAGGED_COLS = 8192
 ARGMAX_TAG_ID = 255           # tag id of the cross-rank arg-max exchange (operators use 0..253)
 
 
@@ -346,12 +352,18 @@ def plan_handoff(ops, world_size: int):
             continue
         if any(role == "res" and (ops[j].flags & N.F_SILU_MUL) for j, role in final):
             continue
+        wide = T.dims[1] > WIDE_FLAGGED_COLS
+        if wide and not (ar is None and len(final) == 1 and final[0] == (i + 1, "x")
+                         and ops[i + 1].kind == "linear"):
+            continue        # the per-iteration choice is built for "next operator reads it as x"
         if ar is None:
             pid = next_id
             next_id += 1
             plan[i]["out"] = (("ll", id(T)), pid, False, T)
             for j, role in final:
                 plan[j][role] = (("ll", id(T)), pid)
+                if wide:
+                    plan[j]["x_opt"] = True
         else:
             pid, aid = next_id, next_id + 1
             next_id += 2
@@ -435,17 +447,25 @@ def splitk_plan(nrows: int, K: int, gran: int, W: int):
 def _all_flagged(plan, ops, oi):
     """True if every activation operator `oi` reads arrives as flagged words."""
     ins = _op_inputs(ops[oi])
-    return bool(ins) and all(role in plan[oi] for role, _ in ins)
+    return bool(ins) and all(role in plan[oi] for role, _ in ins)   # ("x_opt" is not a role)
 
 
 def _link(tasks, first, ev, plan, ops, oi, prev_event, prev_count):
     """Events of the tasks of operator `oi` (tasks[first:]).  An operator waits for its
     predecessor's event unless all its activations come as flagged words, and triggers its
     own unless the next operator does not wait for it."""
-    waits = not _all_flagged(plan, ops, oi)
+    # an operator whose flagged input is optional (x_opt) also waits for the event of the
+    # operator before it, which therefore publishes it; the device skips that wait in
+    # iterations of one or two tokens
+    waits = not _all_flagged(plan, ops, oi) or bool(plan[oi].get("x_opt"))
     last = oi == len(ops) - 1
-    triggers = last or not _all_flagged(plan, ops, oi + 1)
+    next_opt = not last and bool(plan[oi + 1].get("x_opt"))
+    triggers = last or not _all_flagged(plan, ops, oi + 1) or next_opt
+    # published for the sake of an optional reader only: not in iterations of one or two tokens
+    wide_only = next_opt and not last and _all_flagged(plan, ops, oi + 1)
     for ts in tasks[first:]:
+        if wide_only:
+            ts.flags |= N.F_TRIG_WIDE
         ts.trig_event = ev if triggers else -1
         ts.dep_event = prev_event if waits else -1
         ts.dep_count = prev_count if waits else 0
@@ -608,7 +628,7 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                 flags &= ~N.F_RESIDUAL
             ll = plan[oi]
             if "x" in ll:
-                flags |= N.F_LL_IN
+                flags |= N.F_LL_IN | (N.F_LL_OPT if ll.get("x_opt") else 0)
             if "res" in ll and (flags & N.F_RESIDUAL):
                 flags |= N.F_LL_RES
             if "out" in ll:
