@@ -64,9 +64,6 @@ enum ypk_task_type {
   YPK_TASK_RMSNORM = 6,       /* stand-alone norm (unfused graphs)        */
   YPK_TASK_SILU_MUL = 7,      /* stand-alone silu(g)*u                    */
   YPK_TASK_ALLREDUCE = 8,     /* push partial to peers + local reduce     */
-  YPK_TASK_LINEAR_KN = 9,     /* x.W with W stored [K,N] (graph surface)  */
-  YPK_TASK_LINEAR_UMMA = 10,  /* tcgen05/TMEM tile linear, batch > 8      */
-  YPK_TASK_ELEMENTWISE = 11,  /* silu / mul / add on the graph surface    */
   YPK_TASK_TYPE_COUNT
 };
 
@@ -294,6 +291,13 @@ int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_
 int ypk_wait(ypk_handle *h);
 
 int ypk_get_status(ypk_handle *h, ypk_status *out);
+
+/* dst[c, r] = src[r, c] for a row-major [rows, cols] matrix of 16-bit elements (device
+ * pointers on the current device, 16-byte aligned, rows and cols multiples of 8; enqueued on
+ * `stream`, no handle needed).  The kernel-graph surface stores a matmul weight as [K, N]
+ * (src/kernel/matmul.cc), the LINEAR task streams [N, K]: the weight is turned once, the
+ * first time it is seen. */
+int ypk_transpose_16bit(const void *src, void *dst, int32_t rows, int32_t cols, void *stream);
 
 /* Greedy sampling for callers that cannot let a library allocate device memory (a host
  * whose own allocator owns the whole GPU, or a path where the device-wide synchronisation

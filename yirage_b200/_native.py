@@ -22,14 +22,12 @@ F16, BF16, F32, I32, I64 = 940, 941, 942, 955, 965
 
 # enum ypk_task_type
 (TASK_NOP, TASK_EMBED, TASK_LINEAR, TASK_ATTENTION, TASK_ARGMAX_PARTIAL, TASK_ARGMAX_REDUCE,
- TASK_RMSNORM, TASK_SILU_MUL, TASK_ALLREDUCE, TASK_LINEAR_KN, TASK_LINEAR_UMMA,
- TASK_ELEMENTWISE) = range(12)
+ TASK_RMSNORM, TASK_SILU_MUL, TASK_ALLREDUCE) = range(9)
 
 TASK_NAMES = {
     TASK_NOP: "nop", TASK_EMBED: "embedding", TASK_LINEAR: "linear", TASK_ATTENTION: "attention",
     TASK_ARGMAX_PARTIAL: "argmax_partial", TASK_ARGMAX_REDUCE: "argmax_reduce",
     TASK_RMSNORM: "rmsnorm", TASK_SILU_MUL: "silu_mul", TASK_ALLREDUCE: "allreduce",
-    TASK_LINEAR_KN: "linear_kn", TASK_LINEAR_UMMA: "linear_umma", TASK_ELEMENTWISE: "elementwise",
 }
 
 F_NORM, F_RESIDUAL, F_SILU_MUL, F_F16, F_ROPE, F_NORM_NOWEIGHT = 0x1, 0x2, 0x4, 0x8, 0x10, 0x40
@@ -115,6 +113,7 @@ SYMBOLS = {
     "ypk_get_status": (C.c_int, [C.c_void_p, C.POINTER(Status)]),
     "ypk_argmax_noalloc": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_void_p,
                                      C.c_void_p]),
+    "ypk_transpose_16bit": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
 }
 
 _lib = None

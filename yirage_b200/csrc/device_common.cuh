@@ -7,7 +7,7 @@
 //               activations, do the arithmetic, publish the trigger event;
 //   warp  8     producer: walks the same per-worker task queue on its own and
 //               streams the bytes that do not depend on activations (weight
-//               rows, cached K/V tiles) into a 4-stage shared-memory ring with
+//               rows, cached K/V tiles) into a 5-stage shared-memory ring with
 //               cp.async.bulk + mbarrier, so HBM stays busy while the consumers
 //               sit on an event.
 #pragma once

@@ -24,6 +24,21 @@ using namespace ypk;
 
 namespace {
 
+// dst[c][r] = src[r][c], 16-bit elements, 32 x 32 tiles through shared memory
+__global__ void transpose16_kernel(const uint16_t *src, uint16_t *dst, int rows, int cols) {
+  __shared__ uint16_t tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int r = r0 + i, c = c0 + threadIdx.x;
+    if (r < rows && c < cols) tile[i][threadIdx.x] = src[size_t(r) * cols + c];
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int c = c0 + i, r = r0 + threadIdx.x;
+    if (r < rows && c < cols) dst[size_t(c) * rows + r] = tile[threadIdx.x][i];
+  }
+}
+
 struct Slot {
   void *ptr = nullptr;
   uint64_t bytes = 0;
@@ -1152,6 +1167,17 @@ int ypk_argmax_noalloc(const void *logits_bf16, int32_t batch, int32_t vocab, in
   e = cudaGetLastError();
   if (e != cudaSuccess)
     return fail(nullptr, YPK_ERR_CUDA, "argmax_noalloc: launch: %s", cudaGetErrorString(e));
+  return YPK_OK;
+}
+
+int ypk_transpose_16bit(const void *src, void *dst, int32_t rows, int32_t cols, void *stream) {
+  if (!src || !dst || rows <= 0 || cols <= 0 || rows % 8 || cols % 8)
+    return fail(nullptr, YPK_ERR_INVALID, "transpose: %d x %d (multiples of 8, non-null)", rows, cols);
+  dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
+  transpose16_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t *>(src), static_cast<uint16_t *>(dst), rows, cols);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(nullptr, YPK_ERR_CUDA, "transpose: %s", cudaGetErrorString(e));
   return YPK_OK;
 }
 

@@ -100,7 +100,17 @@ class MicroGraphExecutor:
         key = (w.data_ptr(), w._version, tuple(w.shape), w.dtype)
         if key not in self._wt_cache:
             self._wt_cache = {k: v for k, v in self._wt_cache.items() if k[0] != key[0]}
-            self._wt_cache[key] = w.t().contiguous()
+            # turned by the library's own kernel (torch only provides the memory)
+            from . import _native as N
+            import ctypes as C
+            K, Nc = w.shape
+            if not w.is_contiguous() or w.element_size() != 2:
+                raise NotImplementedError("matmul weights must be contiguous 16-bit tensors")
+            wt = torch.empty((Nc, K), dtype=w.dtype, device=w.device)
+            N.check(None, N.load().ypk_transpose_16bit(
+                C.c_void_p(w.data_ptr()), C.c_void_p(wt.data_ptr()), K, Nc,
+                C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+            self._wt_cache[key] = wt
         return self._wt_cache[key]
 
     def _build(self, feed: Dict[int, torch.Tensor]):
