@@ -39,7 +39,7 @@ if ROOT not in sys.path:
 
 import torch  # noqa: E402
 
-DRAM_TRAFFIC_RATIO = 0.998   # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes, ncu, profiles/
+DRAM_TRAFFIC_RATIO = 1.000   # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes, ncu, profiles/
 PROMPT_LEN = 512
 E2E_NEW_TOKENS = 256         # BASELINE configs[3]: 256 greedy decode steps
 SEED = 3
