@@ -75,6 +75,16 @@ enum ypk_task_type {
 #define YPK_F_ROPE 0x10u       /* ATTENTION: rotate new q/k                */
 #define YPK_F_QK_NORM 0x20u    /* ATTENTION: RMSNorm of every new q head and of the new k over
                                   the head dimension, before the rotation (Qwen3)          */
+#define YPK_F_QTILES 0x80u     /* ATTENTION: iarg[0] names an entry of the iteration's query-tile
+                                  list instead of a request slot: a request that brings more
+                                  new tokens than one task takes (8, or 32 / q-heads-per-kv-
+                                  head) is spread over several tasks, each of which also
+                                  stages the k / v of the request's earlier new tokens.  All
+                                  ATTENTION tasks of a graph carry it or none; with it a
+                                  request may take up to 64 new tokens per iteration.
+                                  iarg[14] = entries of the list the graph has tasks for (the
+                                  most an iteration can need: n + (max_tokens - n) / tile
+                                  tokens with n = min(max_requests, max_tokens)) */
 #define YPK_F_NORM_NOWEIGHT 0x40u /* LINEAR: RMSNorm without a weight      */
 /* Flagged-word hand-off between tasks (no event, no fence): a [tokens][ld] tensor of 16-bit
  * values travels as [max_tokens][ld / 2] 8-byte words {two values, 32-bit tag}; the tag
@@ -291,6 +301,20 @@ int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_
 int ypk_wait(ypk_handle *h);
 
 int ypk_get_status(ypk_handle *h, ypk_status *out);
+
+/* Two graphs over one set of requests: a graph built for many tokens per iteration runs the
+ * prompts, a graph built for a few tokens the decoding (the reference builds one graph for
+ * max_num_batched_tokens and runs everything on it, persistent_kernel.cuh:231-239; here the
+ * task kernels for at most 8 tokens and those for up to 64 differ).
+ * ypk_set_pause_below(h, n): launches of h return, with the batch left waiting, as soon as
+ * the batcher forms a batch of at most n tokens (0 switches this off).
+ * ypk_adopt_batch(dst, src): dst takes over the requests of src where src stopped: the
+ * request slots, the free-page queue and the waiting batch.  Both handles must have been
+ * created over the same meta tensors, page pool and limits except max_num_batched_tokens,
+ * and the K/V caches of their graphs must be the same memory.  dst must be able to run the
+ * waiting batch (YPK_ERR_STATE otherwise); src is finished afterwards until it is reset. */
+int ypk_set_pause_below(ypk_handle *h, int32_t tokens);
+int ypk_adopt_batch(ypk_handle *dst, ypk_handle *src);
 
 /* dst[c, r] = src[r, c] for a row-major [rows, cols] matrix of 16-bit elements (device
  * pointers on the current device, 16-byte aligned, rows and cols multiples of 8; enqueued on

@@ -99,6 +99,17 @@ def test_chunked_prefill_causal_window():
     run_attention([8, 70, 5], [8, 6, 5], hq=8, hkv=2, seed=4)
 
 
+def test_prefill_over_query_tiles():
+    """More new tokens per request than one task takes: the request is spread over tasks of 8
+    new tokens (4 with 8 q heads per kv head), each staging the earlier new tokens' k / v
+    itself.  From an empty cache, on top of a cached context that ends inside a tile, with a
+    short last tile, and next to a request that only decodes."""
+    run_attention([50, 14], [50, 14], hq=8, hkv=2, seed=11)
+    run_attention([300, 65], [63, 1], hq=8, hkv=2, seed=12, max_seq=320)
+    run_attention([40], [40], hq=16, hkv=2, seed=13)          # tiles of 4 tokens
+    run_attention([64, 200], [27, 37], hq=8, hkv=2, seed=14, qk_norm=True)
+
+
 def test_gqa_group_of_eight_heads():
     run_attention([200, 90], [1, 3], hq=16, hkv=2, seed=6)
 

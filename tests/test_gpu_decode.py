@@ -127,6 +127,56 @@ def test_more_than_eight_tokens_per_iteration():
     run_generation([19, 7, 12, 3, 9], 30, max_requests=4, max_tokens=16, max_pages=4)
 
 
+def test_long_prompts_take_up_to_64_tokens_per_iteration():
+    """A graph of 64 token slots: a request brings up to 64 prompt tokens per iteration (the
+    reference chunks by max_num_batched_tokens only), the attention runs over query tiles."""
+    st = run_generation([150, 40, 9], 170, max_requests=2, max_tokens=64, max_pages=6)
+    # the longest request: 3 iterations for its 150 prompt tokens, one per token after that;
+    # the third request waits for a slot until the second has retired
+    assert st.iterations < 150 // 8 + 170
+
+
+def test_prefill_graph_hands_over_to_decode_graph():
+    """Prompts on a 64-token graph, decoding on an 8-token graph over the same requests, pages
+    and caches (ypk_set_pause_below / ypk_adopt_batch), against one oracle run whose batcher
+    changes limits at the same point."""
+    shape = tiny_shape(2)
+    w = llama.init_weights(shape, "cuda", 9, std=0.02)
+    prompt_lens, max_seq = [130, 20, 77], 150
+    g = torch.Generator().manual_seed(9)
+    tokens = torch.zeros(3, max_seq, dtype=torch.int64)
+    for r, n in enumerate(prompt_lens):
+        tokens[r, :n] = torch.randint(0, shape.vocab_size, (n,), generator=g)
+    tokens = tokens.cuda()
+    plen = torch.tensor(prompt_lens, dtype=torch.int32, device="cuda")
+    pair = llama.build_prefill_decode_pair(shape, w, tokens=tokens, prompt_lengths=plen,
+                                           max_num_batched_requests=2, max_num_pages=6,
+                                           page_size=64, prefill_tokens=64, decode_tokens=8)
+    it_p, it_d = pair.run()
+    torch.cuda.synchronize()
+    sd = pair.decode.status()
+    assert sd.error == 0 and sd.finished == 1 and pair.prefill.status().error == 0
+    assert 0 < it_p < 10 and it_d > 0
+    ow = oracle_weights(shape, w)
+    iters, bs, last_logits, exact, total = replay_against_oracle(
+        shape, ow, tokens.cpu(), prompt_lens, max_seq=max_seq, max_requests=2, max_tokens=64,
+        max_pages=6, page_size=64, decode_tokens=8)
+    assert it_p + it_d == iters, (it_p, it_d, iters)
+    assert pair.state["meta"]["step"].cpu().tolist() == bs.step
+    assert exact >= 0.75 * total
+    dev_logits = pair.decode.read_tensor(pair.state["decode_tensors"]["argmax_in"])
+    assert_close(dev_logits[: last_logits.shape[0], : shape.vocab_size], last_logits,
+                 "logits of the last iteration")
+    # a second run after a reset gives the same tokens
+    first = tokens.cpu().clone()
+    for r, n in enumerate(prompt_lens):
+        tokens[r, n:] = 0
+    pair.reset()
+    assert pair.run() == (it_p, it_d)
+    assert torch.equal(tokens.cpu(), first)
+    pair.finalize()
+
+
 def test_sequence_crosses_page_boundaries():
     run_generation([60], 140, max_requests=1, max_tokens=8, max_pages=3)
 

@@ -38,13 +38,23 @@ def oracle_weights(shape, w):
 
 
 def replay_against_oracle(shape, ow, device_tokens, prompt_lens, *, max_seq, max_requests,
-                          max_tokens, max_pages, page_size, max_new_per_request=8, rounding=None,
-                          check_tokens=True):
+                          max_tokens, max_pages, page_size, max_new_per_request=None, rounding=None,
+                          check_tokens=True, decode_tokens=None):
     """Teacher-forced replay: the fp32 oracle runs the same batcher and graph but sees the
     device's own token history, so every iteration is checked on identical inputs and one
     flipped near-tie cannot cascade.  Every device token must be the oracle arg-max or tie
     with it inside the activation tolerance.  Returns (iterations, batch state, logits of
-    the last iteration, exact matches, sampled tokens)."""
+    the last iteration, exact matches, sampled tokens).
+
+    A request brings at most `max_new_per_request` new tokens per iteration: by default what one
+    attention task takes (8, or 32 // q-heads-per-kv-head) in graphs of at most 8 tokens and
+    min(64, max_tokens) in larger ones.  `decode_tokens`: the run is a prefill/decode pair: once
+    a batch of at most that many tokens has been formed (not the first), the batcher goes on
+    under the small graph's limits."""
+    G = ow.num_q_heads // ow.num_kv_heads
+    small = min(8, 32 // G)
+    if max_new_per_request is None:
+        max_new_per_request = small if max_tokens <= 8 else min(64, max_tokens)
     R = len(prompt_lens)
     tokens_ref = torch.zeros(R, max_seq, dtype=torch.int64)
     for r, n in enumerate(prompt_lens):
@@ -60,8 +70,12 @@ def replay_against_oracle(shape, ow, device_tokens, prompt_lens, *, max_seq, max
     cos, sin = O.rope_tables(ow.head_dim, ow.rope_theta, max(max_seq, 64))
     iters, exact, total, out, last_logits = 0, 0, 0, None, None
     while True:
-        if bs.prepare_next_batch(out) == 0:
+        ntok = bs.prepare_next_batch(out)
+        if ntok == 0:
             break
+        if decode_tokens is not None and iters > 0 and ntok <= decode_tokens:
+            bs.max_tokens, bs.max_new_per_request = decode_tokens, small
+            decode_tokens = None
         trace = []
         pred = O.decode_iteration(ow, bs, kc, vc, cos, sin, rounding=rounding, logits_out=trace)
         logits = trace[0]

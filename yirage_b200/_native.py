@@ -32,6 +32,7 @@ TASK_NAMES = {
 
 F_NORM, F_RESIDUAL, F_SILU_MUL, F_F16, F_ROPE, F_NORM_NOWEIGHT = 0x1, 0x2, 0x4, 0x8, 0x10, 0x40
 F_QK_NORM = 0x20
+F_QTILES = 0x80
 F_LL_IN, F_LL_RES, F_LL_OUT, F_LL_PUSH, F_LL_OPT = 0x100, 0x200, 0x400, 0x800, 0x1000
 F_TRIG_WIDE = 0x2000
 
@@ -111,6 +112,8 @@ SYMBOLS = {
     "ypk_launch_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32]),
     "ypk_wait": (C.c_int, [C.c_void_p]),
     "ypk_get_status": (C.c_int, [C.c_void_p, C.POINTER(Status)]),
+    "ypk_set_pause_below": (C.c_int, [C.c_void_p, C.c_int32]),
+    "ypk_adopt_batch": (C.c_int, [C.c_void_p, C.c_void_p]),
     "ypk_argmax_noalloc": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_void_p,
                                      C.c_void_p]),
     "ypk_transpose_16bit": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
@@ -231,6 +234,12 @@ class Handle:
 
     def wait(self):
         check(self._h, self.lib.ypk_wait(self._h))
+
+    def set_pause_below(self, tokens: int):
+        check(self._h, self.lib.ypk_set_pause_below(self._h, tokens))
+
+    def adopt_batch(self, src: "Handle"):
+        check(self._h, self.lib.ypk_adopt_batch(self._h, src._h))
 
     def status(self):
         st = Status()

@@ -42,7 +42,9 @@ constexpr int kKPitch = kHeadDim * 2 + 16;       // 272 B per row of the q / new
 // swizzle): K dims 0..63, K dims 64..127, V dims 0..63, V dims 64..127.
 constexpr int kKvBoxBytes = kKvTile * 128;       // 8192
 constexpr int kVOffset = 2 * kKvBoxBytes;        // V boxes follow the K boxes
-constexpr int kMaxNewTokens = 8;                 // new tokens of one request per iteration
+constexpr int kMaxNewTokens = 8;                 // new tokens one ATTENTION task takes (a query tile)
+constexpr int kMaxNewKeys = 64;                  // new tokens of one request per iteration when its
+                                                 // queries are spread over several tasks (YPK_F_QTILES)
 constexpr int kMaxAttnRows = 32;                 // new tokens x q heads per kv head, per task
 // Cached tiles one attention split should hold.  A warp needs ~2.8 us per tile, so a CTA
 // with more tiles than it can overlap runs in rounds; measured on Llama-3-8B at ~600 tokens
@@ -131,6 +133,10 @@ struct Runtime {
   int *request_ids;   // [max_req]
   int *page_queue;    // [max_pages]
   int *kv_tmp;        // [max_pages] scratch copy of kv_indices for the batcher
+  // Query tiles of the iteration (YPK_F_QTILES): entry i = request slot | first new token of
+  // the tile << 12 | tokens of the tile << 20, or -1.  A request with more new tokens than one
+  // ATTENTION task takes contributes one tile per rt.attn_chunk tokens.
+  int *qtiles;        // [max_tok]
   int *bstate;        // [0] next request id, [1] page queue head, [2] tail
   long long eos;
   long long base_iter;
@@ -138,7 +144,11 @@ struct Runtime {
   unsigned long long budget_ns;
   int mode, max_seq, max_req, max_tok, max_pages, page_size, total_req;
   int max_iters, fixed_batch, resume_pending, rank, world;
-  int max_new_tokens;  // prefill chunk of one request per iteration (<= kMaxNewTokens)
+  int max_new_tokens;  // prefill chunk of one request per iteration (<= kMaxNewTokens, or
+                       // <= kMaxNewKeys when every ATTENTION task reads the query-tile list)
+  int attn_chunk;      // new tokens per query tile
+  int pause_below;     // > 0: stop (batch pending) once the next batch has at most this many
+                       // tokens: the caller continues with a graph built for small batches
   int end_event, end_count;  // event every task of the last operator triggers
   // optional per-task timeline: 8 words per (worker, queue position), overwritten every
   // iteration: {iteration << 32 | task, t_fetch, t_dependency_met, t_done, t_inputs_staged,

@@ -100,6 +100,7 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
     int ntok;
     if (rt.resume_pending) {
       ntok = int(rt.ctrl[kCtrlPublished] & 0xffffull);
+      build_query_tiles(rt);   // the batch may have been formed by a launch of another graph
     } else {
       ntok = prepare_next_batch(rt, false);
     }
@@ -257,7 +258,8 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
       }
       if (good) {
         const int ntok = prepare_next_batch(rt, false);
-        const bool pause = rt.max_iters > 0 && iters_here >= rt.max_iters;
+        const bool pause = (rt.max_iters > 0 && iters_here >= rt.max_iters) ||
+                           (rt.pause_below > 0 && ntok <= rt.pause_below);
         if (ntok < 0) {
           raise_abort(wc, YPK_ERR_STATE, -7);   // KV page pool exhausted: every waiter leaves
         } else {

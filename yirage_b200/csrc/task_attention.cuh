@@ -31,11 +31,12 @@
 namespace ypk {
 
 struct AttnShape {
-  int T;         // new tokens of this request in this iteration
-  int qo0;       // first row of the request in the packed qkv / output
+  int T;         // new tokens this task takes (all of the request's, or one query tile of them)
+  int pre;       // new tokens of the request in this iteration that come before those
+  int qo0;       // row of the task's first token in the packed qkv / output
   int kv0;       // first entry of the request in kv_indices
-  int seq_len;   // tokens including the new ones
-  int cached;    // seq_len - T
+  int seq_len;   // tokens up to and including the task's own
+  int cached;    // tokens the pages held before this iteration = seq_len - pre - T
   int tile0, tile1;  // cached 64-token tiles of this split
   int nact;      // active splits of this (request, head)
   bool active, handles_new;
@@ -43,19 +44,29 @@ struct AttnShape {
 
 __device__ __forceinline__ AttnShape attn_shape(const Runtime &rt, const ypk_task &t) {
   AttnShape s;
-  const int r = t.iarg[0], split = t.iarg[2], nsplit = t.iarg[3];
-  s.qo0 = __ldcg(rt.qo_indptr + r);
-  s.T = __ldcg(rt.qo_indptr + r + 1) - s.qo0;
+  int r = t.iarg[0];
+  const int split = t.iarg[2], nsplit = t.iarg[3];
+  int tile = 0;
+  if (t.flags & YPK_F_QTILES) {
+    // iarg[0] names an entry of the iteration's query-tile list instead of a request slot
+    tile = __ldcg(rt.qtiles + r);
+    r = tile < 0 ? 0 : (tile & 0xfff);
+  }
+  const int qo = __ldcg(rt.qo_indptr + r);
+  const int treq = __ldcg(rt.qo_indptr + r + 1) - qo;
+  s.pre = (t.flags & YPK_F_QTILES) ? ((tile >> 12) & 0xff) : 0;
+  s.T = (t.flags & YPK_F_QTILES) ? (tile < 0 ? 0 : (tile >> 20)) : treq;
+  s.qo0 = qo + s.pre;
   s.kv0 = __ldcg(rt.kv_indptr + r);
   const int npages = __ldcg(rt.kv_indptr + r + 1) - s.kv0;
-  s.seq_len = (npages - 1) * rt.page_size + __ldcg(rt.kv_last_len + r);
-  s.cached = s.seq_len - s.T;
+  s.cached = (npages - 1) * rt.page_size + __ldcg(rt.kv_last_len + r) - treq;
+  s.seq_len = s.cached + s.pre + s.T;
   const int tiles = (s.cached + kKvTile - 1) / kKvTile;
   const int want = min(nsplit, (tiles + kAttnTilesPerSplit - 1) / kAttnTilesPerSplit);
   const int tps = max(1, (tiles + max(want, 1) - 1) / max(want, 1));
   s.nact = tiles > 0 ? (tiles + tps - 1) / tps : 1;
-  s.active = s.T > 0 && s.T <= kMaxNewTokens && s.T * t.iarg[4] <= kMaxAttnRows && npages > 0 &&
-             split < s.nact;
+  s.active = s.T > 0 && s.T <= kMaxNewTokens && s.T * t.iarg[4] <= kMaxAttnRows &&
+             s.pre + s.T <= kMaxNewKeys && npages > 0 && split < s.nact;
   s.tile0 = min(tiles, split * tps);
   s.tile1 = min(tiles, s.tile0 + tps);
   s.handles_new = split == s.nact - 1;
@@ -120,13 +131,14 @@ struct AttnAcc {
 
 // One 64-token tile (or the new-token mini tile): S = Q K^T, online softmax, O += P V.
 // ksm / vsm: rows of 128 bf16 at kKPitch.  `ntok` valid tokens; when `causal`, token j is
-// visible to query row (t, g) only if j <= t (rows are numbered t * G + g).
+// visible to query row (t, g) only if j <= t + pre (rows are numbered t * G + g; `pre` new
+// tokens of the same request precede the query rows' own).
 // SWZ: ksm / vsm are TMA stages (two 64x128-byte boxes each, 128-byte swizzle: the 16-byte
 // chunk c of row r sits at chunk c ^ (r & 7)); otherwise plain rows at kKPitch.
 template <bool SWZ>
 __device__ __forceinline__ void attn_tile_mma(const char *qsm, const char *ksm, char *vsm,
                                               int ntok, bool causal, int G, int row_base,
-                                              int lane, AttnAcc &acc) {
+                                              int lane, AttnAcc &acc, int pre = 0) {
   // 1/sqrt(128) * log2(e): scores live in the log2 domain so exp2f can be used
   const float qscale = 0.08838834764831845f * 1.4426950408889634f;
   const int nblk = (ntok + 7) >> 3;        // 8-token blocks with at least one valid token
@@ -193,7 +205,7 @@ __device__ __forceinline__ void attn_tile_mma(const char *qsm, const char *ksm, 
     for (int e = 0; e < 4; ++e) {
       const int tok = nb * 8 + (lane & 3) * 2 + (e & 1);
       const int tq = (e & 2) ? t_hi : t_lo;
-      const bool vis = nb < nblk && tok < ntok && (!causal || tok <= tq);
+      const bool vis = nb < nblk && tok < ntok && (!causal || tok <= tq + pre);
       s[nb][e] = vis ? s[nb][e] * qscale : -INFINITY;
       mx[e >> 1] = fmaxf(mx[e >> 1], s[nb][e]);
     }
@@ -506,6 +518,28 @@ static __device__ __noinline__ QkPair qk_norm_chunk(uint4 pk, uint4 ov, const ui
   return QkPair{make_uint4(o1[0], o1[1], o1[2], o1[3]), make_uint4(o2[0], o2[1], o2[2], o2[3])};
 }
 
+// Rotate-half RoPE of 8 neighbouring head dims: `pk` the values at dims d0.., `ov` their
+// partners 64 dims away, cos / sin rows of [positions][128] 16-bit values.
+__device__ __forceinline__ uint4 rope_chunk(uint4 pk, uint4 ov, const uint16_t *cosp,
+                                            const uint16_t *sinp, int pos_t, int d0) {
+  const uint4 cv = __ldcg(reinterpret_cast<const uint4 *>(cosp + size_t(pos_t) * kHeadDim + d0));
+  const uint4 sv = __ldcg(reinterpret_cast<const uint4 *>(sinp + size_t(pos_t) * kHeadDim + d0));
+  const uint32_t pv[4] = {pk.x, pk.y, pk.z, pk.w}, po[4] = {ov.x, ov.y, ov.z, ov.w},
+                 pc[4] = {cv.x, cv.y, cv.z, cv.w}, ps[4] = {sv.x, sv.y, sv.z, sv.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 v2 = unpack2(cvt_pair<false>(pv[i])), o2 = unpack2(cvt_pair<false>(po[i])),
+                 c2 = unpack2(cvt_pair<false>(pc[i])), s2 = unpack2(cvt_pair<false>(ps[i]));
+    const float sgn = d0 < 64 ? -1.f : 1.f;
+    // two products and a sum, each rounded to fp32 (no fused multiply-add): the rounding
+    // points of x * cos + rotate_half(x) * sin evaluated in fp32
+    o[i] = pack_bf16(__fadd_rn(__fmul_rn(v2.x, c2.x), sgn * __fmul_rn(o2.x, s2.x)),
+                     __fadd_rn(__fmul_rn(v2.y, c2.y), sgn * __fmul_rn(o2.y, s2.y)));
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 // DECODE: the request has at most 8 query rows this iteration (transposed products).
 template <bool DECODE>
 __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, Misc *misc,
@@ -513,7 +547,7 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
                                                        const AttnShape &s, long long iter,
                                                        RingPos &pos) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int r = t.iarg[0], h = t.iarg[1], split = t.iarg[2], nsplit = t.iarg[3];
+  const int h = t.iarg[1], split = t.iarg[2], nsplit = t.iarg[3];
   const int G = t.iarg[4], hkv = t.iarg[5], ld_qkv = t.iarg[6], ld_out = t.iarg[7];
   const int max_rows = t.iarg[8];
   const uint16_t *qkv = reinterpret_cast<const uint16_t *>(t.ptr[0]);
@@ -541,8 +575,13 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
 
   // shared-memory scratch of the task (everything from kOffXs up to the misc area)
   char *qsm = smem + kOffXs;                                    // [32][272 B] bf16 q rows
-  char *knew = qsm + kMaxAttnRows * kKPitch;                    // [16][272 B]
-  char *vnew = knew + 16 * kKPitch;                             // [16][272 B]
+  // the new tokens' k and v: 16 rows, or kMaxNewKeys when earlier query tiles of the same
+  // request precede this one (never in the decode form)
+  constexpr int kNewRows = DECODE ? 16 : kMaxNewKeys;
+  char *knew = qsm + kMaxAttnRows * kKPitch;                    // [kNewRows][272 B]
+  char *vnew = knew + kNewRows * kKPitch;                       // [kNewRows][272 B]
+  static_assert(kMaxAttnRows * kKPitch + 2 * kMaxNewKeys * kKPitch <= kScratchSmemBytes, "attention scratch");
+  const int pre = DECODE ? 0 : s.pre;
   float *mrg = reinterpret_cast<float *>(smem + kOffXs);        // merge: [4 warps][16][132] fp32
 
   // Stage q (rotated, rounded to bf16) and, in the split that owns the new tokens, the
@@ -551,7 +590,7 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
   if (s.handles_new) {
     for (int i = tid; i < 16 * (kHeadDim / 8); i += kConsumerThreads) {   // clear rows T..15 of v
       const int row = i >> 4;
-      if (row >= T) *reinterpret_cast<uint4 *>(vnew + row * kKPitch + (i & 15) * 16) = make_uint4(0u, 0u, 0u, 0u);
+      if (row >= pre + T) *reinterpret_cast<uint4 *>(vnew + row * kKPitch + (i & 15) * 16) = make_uint4(0u, 0u, 0u, 0u);
     }
   }
   const int heads_to_stage = G + (s.handles_new ? 2 : 0);
@@ -599,35 +638,44 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
       pk = n.pk;
       ov = n.ov;
     }
-    if (rot) {
-      const uint4 cv = __ldcg(reinterpret_cast<const uint4 *>(cosp + size_t(pos_t) * kHeadDim + d0));
-      const uint4 sv = __ldcg(reinterpret_cast<const uint4 *>(sinp + size_t(pos_t) * kHeadDim + d0));
-      const uint32_t pv[4] = {pk.x, pk.y, pk.z, pk.w}, po[4] = {ov.x, ov.y, ov.z, ov.w},
-                     pc[4] = {cv.x, cv.y, cv.z, cv.w}, ps[4] = {sv.x, sv.y, sv.z, sv.w};
-      uint32_t o[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 v2 = unpack2(cvt_pair<false>(pv[i])), o2 = unpack2(cvt_pair<false>(po[i])),
-                     c2 = unpack2(cvt_pair<false>(pc[i])), s2 = unpack2(cvt_pair<false>(ps[i]));
-        const float sgn = d0 < 64 ? -1.f : 1.f;
-        // two products and a sum, each rounded to fp32 (no fused multiply-add): the rounding
-        // points of x * cos + rotate_half(x) * sin evaluated in fp32
-        o[i] = pack_bf16(__fadd_rn(__fmul_rn(v2.x, c2.x), sgn * __fmul_rn(o2.x, s2.x)),
-                         __fadd_rn(__fmul_rn(v2.y, c2.y), sgn * __fmul_rn(o2.y, s2.y)));
-      }
-      pk = make_uint4(o[0], o[1], o[2], o[3]);
-    }
+    if (rot) pk = rope_chunk(pk, ov, cosp, sinp, pos_t, d0);
     if (hh < G) {
       *reinterpret_cast<uint4 *>(qsm + (tk * G + hh) * kKPitch + d0 * 2) = pk;
     } else {
       const size_t off =
           ((size_t(page) * rt.page_size + (pos_t % rt.page_size)) * hkv + h) * kHeadDim + d0;
       if (hh == G) {
-        *reinterpret_cast<uint4 *>(knew + tk * kKPitch + d0 * 2) = pk;
+        *reinterpret_cast<uint4 *>(knew + (pre + tk) * kKPitch + d0 * 2) = pk;
         *reinterpret_cast<uint4 *>(kcache + off) = pk;
       } else {
-        *reinterpret_cast<uint4 *>(vnew + tk * kKPitch + d0 * 2) = pk;
+        *reinterpret_cast<uint4 *>(vnew + (pre + tk) * kKPitch + d0 * 2) = pk;
         *reinterpret_cast<uint4 *>(vcache + off) = pk;
+      }
+    }
+  }
+  if constexpr (!DECODE) {
+    // The request's new tokens ahead of this query tile: their k (normalised, rotated) and v
+    // are staged from the packed rows as well: the tasks of one iteration do not wait for one
+    // another's appends.  The append itself is left to the task that owns those tokens.
+    if (s.handles_new && pre > 0) {
+      for (int idx = tid; idx < pre * 2 * (kHeadDim / 8); idx += kConsumerThreads) {
+        const int c = idx & 15, hh = G + ((idx >> 4) & 1), tk = idx >> 5;
+        const int d0 = c * 8;
+        const int pos_t = s.cached + tk;
+        const uint16_t *src = qkv + size_t(s.qo0 - pre + tk) * ld_qkv +
+                              size_t(h) * (G + 2) * kHeadDim + hh * kHeadDim;
+        const bool rot = rope && hh == G;
+        uint4 pk = __ldcg(reinterpret_cast<const uint4 *>(src + d0));
+        uint4 ov = make_uint4(0u, 0u, 0u, 0u);
+        if (rot) ov = __ldcg(reinterpret_cast<const uint4 *>(src + (d0 ^ 64)));
+        if (qk_norm && hh == G) {
+          const QkPair n = qk_norm_chunk(pk, ov, qk_w + kHeadDim, d0, t.farg[0], rot,
+                                         (lane & 16) ? 0xffff0000u : 0x0000ffffu);
+          pk = n.pk;
+          ov = n.ov;
+        }
+        if (rot) pk = rope_chunk(pk, ov, cosp, sinp, pos_t, d0);
+        *reinterpret_cast<uint4 *>((hh == G ? knew : vnew) + tk * kKPitch + d0 * 2) = pk;
       }
     }
   }
@@ -666,7 +714,7 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
     if constexpr (DECODE) {
       attn_tile_mma_t<false>(qsm, knew, vnew, T, true, G, lane, acc);
     } else {
-      attn_tile_mma<false>(qsm, knew, vnew, T, true, G, mt * 16, lane, acc);
+      attn_tile_mma<false>(qsm, knew, vnew, pre + T, true, G, mt * 16, lane, acc, pre);
     }
   }
   consumer_bar();  // q / knew / vnew are dead from here on; the area becomes the merge buffer
@@ -680,10 +728,10 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
   const uint32_t tag_sp = ll_tag(rt, iter, t.iarg[13]);
   unsigned long long *scr_w = reinterpret_cast<unsigned long long *>(scratch);
   const size_t split_words = size_t(max_rows) * kAttnRowFloats;
-  unsigned long long *head_scr = scr_w + (size_t(r) * hkv + h) * nsplit * split_words;
+  unsigned long long *head_scr = scr_w + (size_t(t.iarg[0]) * hkv + h) * nsplit * split_words;
   unsigned long long *my_scr = head_scr + size_t(split) * split_words;
-  // merge states are [16 rows][132] per warp, or [8 rows][132] when only 8 rows are live
-  const int kStateFloats = (rows <= 8 ? 8 : 16) * kAttnRowFloats;
+  // merge states are [16 rows][132] per warp, [8 rows][132] in the decode form
+  constexpr int kStateFloats = (DECODE ? 8 : 16) * kAttnRowFloats;
   // Merge the warps of a query tile, four states at a time, then finish rows [mt*16, ..).
   // Two neighbouring head dims of a finished query row: plain bf16, or one flagged word.
   auto emit = [&](int row, int d, float v0, float v1) {
@@ -819,7 +867,7 @@ __device__ __forceinline__ void attention_consume(WaitCtx &wc, char *smem, Misc 
                                                   long long iter, RingPos &pos) {
   const AttnShape s = attn_shape(rt, t);
   if (!s.active) return;
-  const AttnRet r = s.T * t.iarg[4] <= 8
+  const AttnRet r = s.T * t.iarg[4] <= 8 && s.pre == 0
       ? attention_consume_out<true>(&rt, misc, smem, wc.worker, wc.task, wc.failed, s, iter, pos)
       : attention_consume_out<false>(&rt, misc, smem, wc.worker, wc.task, wc.failed, s, iter, pos);
   pos = r.pos;

@@ -252,7 +252,27 @@ __device__ __forceinline__ void silu_mul_task(const ypk_task &t, int batch) {
 // tokens of the next iteration (0 = everything retired), or -1 when a request that is
 // already running needs a page and the pool has none left (the reference hands out pages
 // without looking, persistent_kernel.cuh:262-270, and two requests then share one).
-static __device__ __noinline__ int prepare_next_batch(const Runtime &rt, bool first) {
+// The query-tile list of the batch in qo_indptr (see Runtime::qtiles).
+static __device__ __noinline__ void build_query_tiles(const Runtime &rt) {
+  if (rt.qtiles == nullptr) return;
+  const int ch = max(1, rt.attn_chunk);
+  int n = 0;
+  for (int i = 0; i < rt.max_req && n < rt.max_tok; ++i) {
+    if (rt.request_ids[i] < 0) continue;
+    const int T = rt.qo_indptr[i + 1] - rt.qo_indptr[i];
+    for (int t0 = 0; t0 < T && n < rt.max_tok; t0 += ch)
+      rt.qtiles[n++] = i | (t0 << 12) | (min(ch, T - t0) << 20);
+  }
+  for (; n < rt.max_tok; ++n) rt.qtiles[n] = -1;
+}
+
+static __device__ __noinline__ int prepare_next_batch_impl(const Runtime &rt, bool first);
+static __device__ __forceinline__ int prepare_next_batch(const Runtime &rt, bool first) {
+  const int ntok = prepare_next_batch_impl(rt, first);
+  if (ntok > 0) build_query_tiles(rt);
+  return ntok;
+}
+static __device__ __noinline__ int prepare_next_batch_impl(const Runtime &rt, bool first) {
   const int MR = rt.max_req, MT = rt.max_tok, MP = rt.max_pages, PS = rt.page_size;
   int head = rt.bstate[1], tail = rt.bstate[2];
   if (!first) {

@@ -60,6 +60,9 @@ struct ypk_handle {
   int num_events = 0;
   int end_event = -1, end_count = 0;
   int max_new_tokens = kMaxNewTokens;  // prefill chunk per request the attention tasks allow
+  int attn_chunk = kMaxNewTokens;      // new tokens per query tile (YPK_F_QTILES)
+  bool attn_plain = false, attn_qtiles = false;   // kinds of ATTENTION task in the graph
+  int pause_below = 0;
   bool graph_loaded = false;
   // device state
   ypk_task *d_tasks = nullptr;
@@ -73,6 +76,7 @@ struct ypk_handle {
   bool use_tmem = false;            // some LINEAR task has a weight tensor map
   int umma_policy = 0;              // YPK_TENSOR_CORE: auto (by estimated cost) / always / never
   int *d_request_ids = nullptr, *d_page_queue = nullptr, *d_kv_tmp = nullptr, *d_bstate = nullptr;
+  int *d_qtiles = nullptr;
   // progress
   long long base_iter = 0;
   // iterations of earlier runs (see Runtime::ll_epoch / ar_epoch)
@@ -249,8 +253,20 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
     case YPK_TASK_ATTENTION: {
       const int r = a[0], kvh = a[1], split = a[2], nsplit = a[3], G = a[4], hkv = a[5],
                 ldq = a[6], ldo = a[7], max_rows = a[8];
+      const bool qtiles = (in.flags & YPK_F_QTILES) != 0;
+      // iarg[0] is a request slot, or with YPK_F_QTILES an entry of the query-tile list
+      // (iarg[14] = length of that list as the graph was built for it)
+      const int nslots = qtiles ? a[14] : h->cfg.max_num_batched_requests;
+      if (qtiles && (a[14] < 1 || a[14] > h->cfg.max_num_batched_tokens))
+        return fail(h, YPK_ERR_INVALID, "task %d: ATTENTION over %d query tiles, the graph has %d token slots",
+                    ti, a[14], h->cfg.max_num_batched_tokens);
+      if (qtiles && ((in.flags & (YPK_F_LL_IN | YPK_F_LL_OUT)) ||
+                     h->cfg.max_num_batched_requests > 4096))
+        return fail(h, YPK_ERR_UNSUPPORTED,
+                    "task %d: ATTENTION over query tiles needs plain 16-bit rows on both sides "
+                    "and at most 4096 request slots", ti);
       if (G < 1 || G > 8 || hkv < 1 || kvh < 0 || kvh >= hkv || nsplit < 1 || split < 0 ||
-          split >= nsplit || r < 0 || r >= h->cfg.max_num_batched_requests)
+          split >= nsplit || r < 0 || r >= nslots)
         return fail(h, YPK_ERR_UNSUPPORTED,
                     "task %d: ATTENTION needs 1..8 q heads per kv head (got %d), head_dim 128", ti,
                     G);
@@ -260,7 +276,8 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
       if (max_rows < std::min(G * kMaxNewTokens, kMaxAttnRows))
         return fail(h, YPK_ERR_INVALID, "task %d: ATTENTION scratch rows %d < %d", ti, max_rows,
                     std::min(G * kMaxNewTokens, kMaxAttnRows));
-      h->max_new_tokens = std::min(h->max_new_tokens, kMaxAttnRows / G);
+      h->attn_chunk = std::min(h->attn_chunk, kMaxAttnRows / G);
+      (qtiles ? h->attn_qtiles : h->attn_plain) = true;
       if (!h->cfg.qo_indptr || !h->cfg.paged_kv_indptr || !h->cfg.paged_kv_indices ||
           !h->cfg.paged_kv_last_page_len)
         return fail(h, YPK_ERR_INVALID, "ATTENTION needs the paged-KV meta tensors in ypk_config");
@@ -280,7 +297,7 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
         required[4] = required[5] = true;
       }
       if (nsplit > 1) {
-        need[6] = uint64_t(h->cfg.max_num_batched_requests) * hkv * nsplit * max_rows *
+        need[6] = uint64_t(nslots) * hkv * nsplit * max_rows *
                   kAttnRowFloats * 8u;   // flagged words {fp32 bits, tag}
         align[6] = 16; required[6] = true;
       }
@@ -548,11 +565,17 @@ int ypk_create(const ypk_config *cfg, ypk_handle **out) {
     delete h;
     return rc;
   }
+  if (cudaMalloc(&h->d_qtiles, std::max(1, cfg->max_num_batched_tokens) * 4) != cudaSuccess) {
+    int rc = fail(nullptr, YPK_ERR_CUDA, "query-tile list allocation failed");
+    ypk_destroy(h);
+    return rc;
+  }
   if (cfg->mode == 1) {
     const int MR = cfg->max_num_batched_requests, MP = cfg->max_num_pages;
     if (cudaMalloc(&h->d_request_ids, MR * 4) != cudaSuccess ||
         cudaMalloc(&h->d_page_queue, MP * 4) != cudaSuccess ||
         cudaMalloc(&h->d_kv_tmp, MP * 4) != cudaSuccess ||
+
         cudaMalloc(&h->d_bstate, 16) != cudaSuccess) {
       int rc = fail(nullptr, YPK_ERR_CUDA, "batcher state allocation failed");
       ypk_destroy(h);
@@ -585,6 +608,7 @@ int ypk_destroy(ypk_handle *h) {
     if (h->d_request_ids) cudaFree(h->d_request_ids);
     if (h->d_page_queue) cudaFree(h->d_page_queue);
     if (h->d_kv_tmp) cudaFree(h->d_kv_tmp);
+    if (h->d_qtiles) cudaFree(h->d_qtiles);
     if (h->d_bstate) cudaFree(h->d_bstate);
   }
   delete h;
@@ -795,7 +819,8 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
       seen[size_t(ti)] = 1;
     }
   }
-  h->max_new_tokens = kMaxNewTokens;
+  h->max_new_tokens = h->attn_chunk = kMaxNewTokens;
+  h->attn_plain = h->attn_qtiles = false;
   std::vector<ypk_task> resolved(static_cast<size_t>(num_tasks));
   std::vector<int> trig_count(size_t(num_events), 0), last_trig(size_t(num_events), -1);
   for (int i = 0; i < num_tasks; ++i) {
@@ -806,6 +831,13 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
       last_trig[size_t(tasks[i].trig_event)] = i;
     }
   }
+  if (h->attn_plain && h->attn_qtiles)
+    return fail(h, YPK_ERR_INVALID,
+                "ATTENTION tasks over request slots and over query tiles in one graph");
+  // A request may bring more new tokens than one ATTENTION task takes only if every such task
+  // reads the query-tile list.
+  h->max_new_tokens = h->attn_qtiles ? std::min(kMaxNewKeys, h->cfg.max_num_batched_tokens)
+                                     : h->attn_chunk;
   for (int i = 0; i < num_tasks; ++i) {
     const ypk_task &t = tasks[i];
     if (t.dep_event < 0) continue;
@@ -1002,6 +1034,9 @@ int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_
   rt.request_ids = h->d_request_ids;
   rt.page_queue = h->d_page_queue;
   rt.kv_tmp = h->d_kv_tmp;
+  rt.qtiles = h->attn_qtiles ? h->d_qtiles : nullptr;
+  rt.attn_chunk = h->attn_chunk;
+  rt.pause_below = h->pause_below;
   rt.bstate = h->d_bstate;
   rt.eos = c.eos_token_id;
   rt.base_iter = h->base_iter;
@@ -1045,6 +1080,19 @@ int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_
                   (unsigned long long)c.profiler_bytes, (unsigned long long)need);
     rt.prof = static_cast<unsigned long long *>(c.profiler_buffer);
     rt.prof_stride = longest;
+  }
+  if (c.mode == 0 && h->attn_qtiles) {
+    // One-pass graphs have no batcher: the query-tile list is made here from the caller's
+    // qo_indptr (a blocking read of max_requests + 1 integers; serving launches never do this).
+    const int MR = c.max_num_batched_requests, MT = c.max_num_batched_tokens;
+    std::vector<int> qo(size_t(MR) + 1), tiles(size_t(std::max(1, MT)), -1);
+    CUDA_TRY(h, cudaStreamSynchronize(st));
+    CUDA_TRY(h, cudaMemcpy(qo.data(), c.qo_indptr, 4 * qo.size(), cudaMemcpyDeviceToHost));
+    int n = 0;
+    for (int i = 0; i < MR && n < MT; ++i)
+      for (int t0 = 0, T = qo[size_t(i) + 1] - qo[size_t(i)]; t0 < T && n < MT; t0 += h->attn_chunk)
+        tiles[size_t(n++)] = i | (t0 << 12) | (std::min(h->attn_chunk, T - t0) << 20);
+    CUDA_TRY(h, cudaMemcpy(h->d_qtiles, tiles.data(), 4 * tiles.size(), cudaMemcpyHostToDevice));
   }
   // The control word a new launch starts from: last completed iteration, stopped, and
   // the size of the batch that is waiting (if any).
@@ -1119,6 +1167,70 @@ int ypk_wait(ypk_handle *h) {
   h->status.iterations = h->base_iter;
   h->status.finished = h->finished ? 1 : 0;
   h->status.active_tokens = ntok;
+  return YPK_OK;
+}
+
+int ypk_set_pause_below(ypk_handle *h, int32_t tokens) {
+  if (!h) return fail(nullptr, YPK_ERR_INVALID, "null handle");
+  if (h->in_flight) return fail(h, YPK_ERR_STATE, "set_pause_below while a launch is in flight");
+  if (tokens < 0) return fail(h, YPK_ERR_INVALID, "set_pause_below: negative token count");
+  h->pause_below = tokens;
+  return YPK_OK;
+}
+
+int ypk_adopt_batch(ypk_handle *dst, ypk_handle *src) {
+  if (!dst || !src) return fail(nullptr, YPK_ERR_INVALID, "null handle");
+  if (dst == src) return fail(dst, YPK_ERR_INVALID, "adopt_batch: source and destination are one handle");
+  if (dst->host_only || src->host_only) return fail(dst, YPK_ERR_STATE, "adopt_batch on a host-only handle");
+  if (dst->in_flight || src->in_flight) return fail(dst, YPK_ERR_STATE, "adopt_batch while a launch is in flight");
+  if (dst->status.error || src->status.error)
+    return fail(dst, YPK_ERR_STATE, "adopt_batch: a handle is in a failed state");
+  if (!dst->graph_loaded) return fail(dst, YPK_ERR_STATE, "adopt_batch before load_graph");
+  const ypk_config &a = dst->cfg, &b = src->cfg;
+  if (a.mode != 1 || b.mode != 1 || a.device != b.device ||
+      a.max_num_batched_requests != b.max_num_batched_requests ||
+      a.max_num_pages != b.max_num_pages || a.page_size != b.page_size ||
+      a.max_seq_length != b.max_seq_length || a.total_num_requests != b.total_num_requests ||
+      a.eos_token_id != b.eos_token_id || a.step != b.step || a.tokens != b.tokens ||
+      a.input_tokens != b.input_tokens || a.output_tokens != b.output_tokens ||
+      a.prompt_lengths != b.prompt_lengths || a.qo_indptr != b.qo_indptr ||
+      a.paged_kv_indptr != b.paged_kv_indptr || a.paged_kv_indices != b.paged_kv_indices ||
+      a.paged_kv_last_page_len != b.paged_kv_last_page_len)
+    return fail(dst, YPK_ERR_INVALID,
+                "adopt_batch: the two handles must serve the same requests through the same "
+                "meta tensors, page pool and request slots");
+  if (src->finished || !src->resume_pending) {
+    // nothing is waiting: every request has retired
+    dst->finished = true;
+    dst->resume_pending = false;
+    dst->pending_tokens = 0;
+    dst->status.finished = 1;
+    dst->status.active_tokens = 0;
+    return YPK_OK;
+  }
+  // The waiting batch was formed under the source's limits; the destination's tasks must be
+  // able to take it.  The token count bounds every request's share too.
+  if (src->pending_tokens > a.max_num_batched_tokens ||
+      (src->pending_tokens > dst->max_new_tokens && src->max_new_tokens > dst->max_new_tokens))
+    return fail(dst, YPK_ERR_STATE,
+                "adopt_batch: the waiting batch has %d tokens, this graph takes %d per "
+                "iteration and %d per request", src->pending_tokens, a.max_num_batched_tokens,
+                dst->max_new_tokens);
+  CUDA_TRY(dst, cudaSetDevice(a.device));
+  const size_t MR = size_t(a.max_num_batched_requests), MP = size_t(a.max_num_pages);
+  CUDA_TRY(dst, cudaMemcpy(dst->d_request_ids, src->d_request_ids, 4 * MR, cudaMemcpyDeviceToDevice));
+  CUDA_TRY(dst, cudaMemcpy(dst->d_page_queue, src->d_page_queue, 4 * MP, cudaMemcpyDeviceToDevice));
+  CUDA_TRY(dst, cudaMemcpy(dst->d_bstate, src->d_bstate, 16, cudaMemcpyDeviceToDevice));
+  dst->pending_tokens = src->pending_tokens;
+  dst->resume_pending = true;
+  dst->finished = false;
+  dst->status.finished = 0;
+  dst->status.active_tokens = src->pending_tokens;
+  // the source has given its batch away: it runs again only after a reset
+  src->resume_pending = false;
+  src->pending_tokens = 0;
+  src->finished = true;
+  src->status.finished = 1;
   return YPK_OK;
 }
 

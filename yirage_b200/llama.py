@@ -142,9 +142,13 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
                         k_cache: Optional[torch.Tensor] = None,
                         v_cache: Optional[torch.Tensor] = None, compile: bool = True,
                         dry_run: bool = False, profiler_tensor: Optional[torch.Tensor] = None, handoff: Optional[str] = None,
-                        vocab_parallel: Optional[bool] = None, defer_connect: bool = False):
+                        vocab_parallel: Optional[bool] = None, defer_connect: bool = False,
+                        meta: Optional[Dict] = None):
     """Build (and compile) the decode megakernel for `weights`.  Returns (ypk, state) where
-    state holds the meta tensors, caches and rope tables the kernel works on."""
+    state holds the meta tensors, caches and rope tables the kernel works on.  `meta`, `k_cache`
+    and `v_cache` of an earlier build may be passed in: the two kernels then serve the same
+    requests (PersistentKernel.adopt); the token buffers of `meta` must hold at least
+    max_num_batched_tokens entries."""
     dev = tokens.device
     total_requests, max_seq_length = tokens.shape
     h, d = shape.hidden_size, shape.head_dim
@@ -153,18 +157,23 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
     vpad = padded_vocab(shape.vocab_size)
     MT, MR = max_num_batched_tokens, max_num_batched_requests
     i32 = dict(dtype=torch.int32, device=dev)
-    meta = {
-        "step": torch.zeros(total_requests, **i32),
-        "tokens": tokens,
-        "input_tokens": torch.zeros(MT, 1, dtype=torch.int64, device=dev),
-        "output_tokens": torch.zeros(MT, 1, dtype=torch.int64, device=dev),
-        "num_new_tokens": torch.ones(total_requests, **i32),
-        "prompt_lengths": prompt_lengths,
-        "qo_indptr_buffer": torch.zeros(MR + 1, **i32),
-        "paged_kv_indptr_buffer": torch.zeros(MR + 1, **i32),
-        "paged_kv_indices_buffer": torch.zeros(max_num_pages, **i32),
-        "paged_kv_last_page_len_buffer": torch.zeros(MR, **i32),
-    }
+    if meta is not None:
+        # same memory, this graph's token budget
+        meta = dict(meta, input_tokens=meta["input_tokens"][:MT],
+                    output_tokens=meta["output_tokens"][:MT])
+    else:
+        meta = {
+            "step": torch.zeros(total_requests, **i32),
+            "tokens": tokens,
+            "input_tokens": torch.zeros(MT, 1, dtype=torch.int64, device=dev),
+            "output_tokens": torch.zeros(MT, 1, dtype=torch.int64, device=dev),
+            "num_new_tokens": torch.ones(total_requests, **i32),
+            "prompt_lengths": prompt_lengths,
+            "qo_indptr_buffer": torch.zeros(MR + 1, **i32),
+            "paged_kv_indptr_buffer": torch.zeros(MR + 1, **i32),
+            "paged_kv_indices_buffer": torch.zeros(max_num_pages, **i32),
+            "paged_kv_last_page_len_buffer": torch.zeros(MR, **i32),
+        }
     if k_cache is None:
         k_cache = torch.zeros(shape.num_hidden_layers, max_num_pages, page_size, hkv, d,
                               dtype=torch.bfloat16, device=dev)
@@ -299,3 +308,58 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
         # (tensor_parallel.connect), e.g. after checking that every rank could build
         ypk.compile(dry_run=dry_run, defer_connect=defer_connect)
     return ypk, state
+
+
+class PrefillDecodePair:
+    """Two megakernels over one set of requests, K/V caches and meta tensors: `prefill` is
+    built for `prefill_tokens` tokens per iteration (a request brings up to 64 new tokens,
+    the LINEAR operators run on the tensor-core path), `decode` for at most 8 (flagged-word
+    hand-off, GEMV path).  The reference runs prompts and decoding on one graph sized by
+    max_num_batched_tokens (persistent_kernel.cuh:231-239); here the task kernels of the two
+    regimes differ, so a run starts on `prefill`, which stops once the batcher forms a batch
+    of at most 8 tokens, and `decode` takes the requests over from there.
+
+    run() is the offline mode of the reference's launch_func: until every request has retired."""
+
+    def __init__(self, prefill: PersistentKernel, decode: PersistentKernel, state: Dict,
+                 decode_tokens: int):
+        self.prefill, self.decode, self.state = prefill, decode, state
+        self.decode_tokens = decode_tokens
+        self.prefill.set_pause_below(decode_tokens)
+
+    def reset(self):
+        self.prefill.reset()
+        self.decode.reset()
+
+    def run(self, stream=None, max_iterations: int = 0):
+        """Prompts on the wide graph, the rest on the narrow one.  Returns the iterations each
+        ran.  `max_iterations` bounds the decode graph's launch (0: to the end)."""
+        self.prefill(stream=stream)
+        it_p = int(self.prefill.status().iterations)
+        self.decode.adopt(self.prefill)
+        self.decode(stream=stream, max_iterations=max_iterations)
+        return it_p, int(self.decode.status().iterations)
+
+    def finalize(self):
+        self.prefill.finalize()
+        self.decode.finalize()
+
+
+def build_prefill_decode_pair(shape: LlamaShape, weights: Dict, *, tokens: torch.Tensor,
+                              prompt_lengths: torch.Tensor, max_num_batched_requests: int,
+                              max_num_pages: int, page_size: int, prefill_tokens: int = 64,
+                              decode_tokens: int = 8, **kw) -> PrefillDecodePair:
+    """build_decode_kernel twice over shared meta tensors and caches (single GPU)."""
+    if kw.get("world_size", 1) != 1:
+        raise NotImplementedError("the prefill/decode pair is built for one GPU")
+    if not (decode_tokens <= 8 < prefill_tokens <= 64):
+        raise ValueError("decode_tokens <= 8 < prefill_tokens <= 64")
+    common = dict(tokens=tokens, prompt_lengths=prompt_lengths,
+                  max_num_batched_requests=max_num_batched_requests,
+                  max_num_pages=max_num_pages, page_size=page_size, **kw)
+    pre, st = build_decode_kernel(shape, weights, max_num_batched_tokens=prefill_tokens, **common)
+    dec, st2 = build_decode_kernel(shape, weights, max_num_batched_tokens=decode_tokens,
+                                   meta=st["meta"], k_cache=st["k_cache"], v_cache=st["v_cache"],
+                                   **common)
+    st = dict(st, decode_tensors=st2["tensors"])
+    return PrefillDecodePair(pre, dec, st, decode_tokens)

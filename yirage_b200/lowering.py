@@ -38,7 +38,8 @@ from .core import DTensor, bfloat16, float16, float32, int32, int64
 MAX_TASK_ROWS = 256          # kMaxAccRows in device_common.cuh
 KV_TILE = 64
 HEAD_DIM = 128
-MAX_NEW_TOKENS = 8           # kMaxNewTokens
+MAX_NEW_TOKENS = 8           # kMaxNewTokens: new tokens one ATTENTION task takes
+MAX_NEW_KEYS = 64            # kMaxNewKeys: new tokens of a request per iteration over query tiles
 MAX_ATTN_ROWS = 32           # kMaxAttnRows
 ATTN_ROW_FLOATS = HEAD_DIM + 4   # kAttnRowFloats in task_attention.cuh
 MAX_SPLITS = 16
@@ -381,6 +382,14 @@ def plan_handoff(ops, world_size: int):
                     "more than 254 flagged-word producers alias on one buffer; use handoff='event'")
             seen.add((key, device_tag(pid)))
     return plan
+
+
+def query_tile_slots(max_requests: int, max_tokens: int, chunk: int) -> int:
+    """Most query tiles one iteration can hold: every request contributes one tile per
+    `chunk` new tokens, the last one possibly short.  With n requests sharing max_tokens
+    tokens that is n + (max_tokens - n) // chunk, largest for the most requests."""
+    n = min(max_requests, max_tokens)
+    return n + (max_tokens - n) // chunk
 
 
 def device_tag(pid: int) -> int:
@@ -744,11 +753,17 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
             if qkv.dims[1] != hkv * (G + 2) * HEAD_DIM:
                 raise ValueError("packed qkv width does not match the head counts")
             max_tiles = (max_seq_length + KV_TILE - 1) // KV_TILE
-            nsplit = max(1, min(W // max(1, max_requests * hkv), max_tiles, MAX_SPLITS))
+            # Graphs of more than 8 tokens let a request bring more new tokens than one task
+            # takes: the tasks are made per entry of the iteration's query-tile list (one
+            # entry per `chunk` new tokens of a request) instead of per request slot.
+            qtiles = max_tokens > MAX_NEW_TOKENS
+            chunk = min(MAX_NEW_TOKENS, MAX_ATTN_ROWS // G)
+            nslots = query_tile_slots(max_requests, max_tokens, chunk) if qtiles else max_requests
+            nsplit = max(1, min(W // max(1, nslots * hkv), max_tiles, MAX_SPLITS))
             max_rows = min(G * MAX_NEW_TOKENS, MAX_ATTN_ROWS)
             if nsplit > 1:
                 # partial rows travel as 8-byte flagged words {fp32 bits, tag}: two floats each
-                need = 2 * max_requests * hkv * nsplit * max_rows * ATTN_ROW_FLOATS
+                need = 2 * nslots * hkv * nsplit * max_rows * ATTN_ROW_FLOATS
                 if attn_scratch is None or attn_scratch.dims[0] < need:
                     attn_scratch = scratch((need,), float32, "attn_split_scratch")
                 # all layers share the scratch: the tags of two attention operators must differ
@@ -769,10 +784,11 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                     shuffles.append(sh)
                     shuffled_done[id(qk_packed)] = sh
             k = 0
-            for r in range(max_requests):
+            for r in range(nslots):
                 for h in range(hkv):
                     for s in range(nsplit):
-                        ts = TaskSpec(N.TASK_ATTENTION, flags=op.flags, op_id=oi)
+                        ts = TaskSpec(N.TASK_ATTENTION, flags=op.flags | (N.F_QTILES if qtiles else 0),
+                                      op_id=oi)
                         ts.ptr[0], ts.ptr[1], ts.ptr[2], ts.ptr[3] = (qkv, 0), (kc, 0), (vc, 0), (o, 0)
                         if op.flags & N.F_ROPE:
                             ts.ptr[4], ts.ptr[5] = (op.t["cos"], 0), (op.t["sin"], 0)
@@ -783,6 +799,8 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                             ts.farg[0] = float(op.attrs["eps"])
                         ts.iarg[:9] = [r, h, s, nsplit, G, hkv, qkv.dims[1], o.dims[1], max_rows]
                         ts.iarg[13] = oi % 254     # tag id of the split-KV partials
+                        if qtiles:
+                            ts.iarg[14] = nslots
                         if "qkv" in plan[oi]:    # packed q/k/v arrive as flagged words
                             ts.flags |= N.F_LL_IN
                             ts.logical_in.append((qkv, 0))

@@ -500,6 +500,18 @@ class PersistentKernel:
     def status(self):
         return self._handle.status()
 
+    # Two graphs over one set of requests (see ypk_adopt_batch): a graph built for many tokens
+    # per iteration runs the prompts, one built for at most 8 tokens the decoding.
+    def set_pause_below(self, tokens: int):
+        """Launches return, with the batch left waiting, once the batcher forms a batch of at
+        most `tokens` tokens (0: off)."""
+        self._handle.set_pause_below(int(tokens))
+
+    def adopt(self, other: "PersistentKernel"):
+        """Take over the requests of `other` where it stopped.  Both kernels must have been
+        built over the same meta tensors and K/V caches."""
+        self._handle.adopt_batch(other._handle)
+
     def __del__(self):
         if sys is None or sys.is_finalizing():
             return
