@@ -336,8 +336,10 @@ def time_decode(ypk, st, K, W, B, prompt_len, shape, dev, world, rank, sample_cl
         # whatever the cache tensors hold (random values), no prefill is run
         st["meta"]["step"].fill_(prompt_len - 1)
     else:
-        chunk = min(8, 32 // (shape.num_attention_heads // shape.num_key_value_heads))
-        ypk(max_iterations=(prompt_len + chunk - 1) // chunk)
+        # run the prompts: the launch returns once a batch of B tokens (one per request) waits
+        ypk.set_pause_below(B)
+        ypk()
+        ypk.set_pause_below(0)
     ypk(max_iterations=W)
     torch.cuda.synchronize()
     if world > 1:
@@ -347,6 +349,7 @@ def time_decode(ypk, st, K, W, B, prompt_len, shape, dev, world, rank, sample_cl
         sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     before = st["meta"]["step"].clone()
+    time_decode.mean_context = float(before.float().mean()) + K / 2.0   # over the timed steps
     torch.cuda.synchronize()
     ev0.record()
     ypk(max_iterations=K)
@@ -410,10 +413,20 @@ def run_ours(args):
     # o_proj / down_proj, in-kernel all-reduce over NVLink after each row-split projection;
     # lm_head split by vocabulary rows, arg-max winners exchanged).  Total work is fixed.
     weights = llama.init_weights(shape, dev, SEED, world_size=world, rank=rank)
-    ypk, st = llama.build_decode_kernel(
-        shape, weights, tokens=tokens, prompt_lengths=plen, max_num_batched_requests=B,
-        max_num_batched_tokens=MT, max_num_pages=pages_per_req * B, page_size=page,
-        world_size=world, rank=rank)
+    # One GPU, at most 8 token slots: the decode graph is paired with a 64-token graph over the
+    # same requests and caches, which runs the prompt in the end-to-end measurement below.
+    pair = None
+    use_pair = world == 1 and MT <= 8 and not args.no_e2e
+    if use_pair and max_seq == gen_seq:
+        pair = llama.build_prefill_decode_pair(
+            shape, weights, tokens=tokens, prompt_lengths=plen, max_num_batched_requests=B,
+            max_num_pages=pages_per_req * B, page_size=page, prefill_tokens=64, decode_tokens=MT)
+        ypk, st = pair.decode, pair.state
+    else:
+        ypk, st = llama.build_decode_kernel(
+            shape, weights, tokens=tokens, prompt_lengths=plen, max_num_batched_requests=B,
+            max_num_batched_tokens=MT, max_num_pages=pages_per_req * B, page_size=page,
+            world_size=world, rank=rank)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -423,19 +436,23 @@ def run_ours(args):
     # always E2E_NEW_TOKENS new tokens per request (max_seq_length ends the generation)
     e2e = e2e_decode_only = None
     if not args.no_e2e:
-        chunk = min(8, 32 // (shape.num_attention_heads // shape.num_key_value_heads))
-        prefill_iters = (prompt_len + chunk - 1) // chunk
         if max_seq == gen_seq:
-            ypk2, st2, e_tokens, e_host = ypk, st, tokens, host_tokens
+            ypk2, st2, pair2, e_tokens, e_host = ypk, st, pair, tokens, host_tokens
         else:       # more timed steps than the generation is long: a second kernel of the right length
             e_tokens = torch.zeros(B, gen_seq, dtype=torch.int64, device=dev)
             e_host = torch.zeros(B, gen_seq, dtype=torch.int64)
             e_host[:, :prompt_len] = host_tokens[:, :prompt_len]
             e_host = e_host.pin_memory()
-            ypk2, st2 = llama.build_decode_kernel(
-                shape, weights, tokens=e_tokens, prompt_lengths=plen, max_num_batched_requests=B,
-                max_num_batched_tokens=MT, max_num_pages=((gen_seq + page - 1) // page) * B,
-                page_size=page, world_size=world, rank=rank)
+            pair2 = None
+            kw2 = dict(tokens=e_tokens, prompt_lengths=plen, max_num_batched_requests=B,
+                       max_num_pages=((gen_seq + page - 1) // page) * B, page_size=page)
+            if use_pair:
+                pair2 = llama.build_prefill_decode_pair(shape, weights, prefill_tokens=64,
+                                                        decode_tokens=MT, **kw2)
+                ypk2, st2 = pair2.decode, pair2.state
+            else:
+                ypk2, st2 = llama.build_decode_kernel(shape, weights, max_num_batched_tokens=MT,
+                                                      world_size=world, rank=rank, **kw2)
         host_out = torch.empty_like(e_host).pin_memory()
         host_step = torch.empty(B, dtype=torch.int32).pin_memory()
         torch.cuda.synchronize()
@@ -444,17 +461,33 @@ def run_ours(args):
         t0 = time.perf_counter()
         e_tokens.copy_(e_host, non_blocking=True)
         plen.copy_(host_plen, non_blocking=True)
-        ypk2.reset()
-        ypk2(max_iterations=prefill_iters)      # the launch returns when the prompt is in
-        torch.cuda.synchronize()
-        t1 = time.perf_counter()
-        ypk2()                                   # decode until every request has retired
+        if pair2 is not None:
+            # the prompt on the 64-token graph (a launch that returns once a batch of at most
+            # MT tokens waits), the rest on the decode graph
+            pair2.reset()
+            pair2.prefill()
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            pair2.decode.adopt(pair2.prefill)
+            pair2.decode()
+            prefill_iters = int(pair2.prefill.status().iterations)
+            launches = 2
+        else:
+            ypk2.reset()
+            ypk2.set_pause_below(B)                  # returns when every request is past its prompt
+            ypk2()
+            ypk2.set_pause_below(0)
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            prefill_iters = int(ypk2.status().iterations)
+            ypk2()                                   # decode until every request has retired
+            launches = 2
         host_out.copy_(e_tokens, non_blocking=True)
         host_step.copy_(st2["meta"]["step"], non_blocking=True)
         torch.cuda.synchronize()
         t2 = time.perf_counter()
         gen = int((host_step.to(torch.int64) + 1 - prompt_len).sum())
-        iters = int(ypk2.status().iterations)
+        iters = int(ypk2.status().iterations) + (prefill_iters if pair2 is not None else 0)
         dt = max_over_ranks(t2 - t0, dev, world)
         t_pre = max_over_ranks(t1 - t0, dev, world)
         h2d = e_host.numel() * 8 + host_plen.numel() * 4
@@ -463,44 +496,50 @@ def run_ours(args):
                "h2d_bytes_per_step": h2d / max(1, iters), "d2h_bytes_per_step": d2h / max(1, iters),
                "new_tokens": gen, "iterations": iters,
                "prefill_ms": t_pre * 1e3, "decode_ms": (dt - t_pre) * 1e3,
+               "prefill_iterations": prefill_iters, "gpu_launches": launches,
+               "prefill_graph": ("64 token slots, attention over query tiles, LINEAR on tcgen05"
+                                 if pair2 is not None else f"the decode graph itself, {MT} token slots"),
                "note": f"{gen} generated tokens after a {prompt_len}-token prompt ({prefill_iters} chunked-"
                        "prefill iterations), prompt copied from pinned host memory, token matrix and step "
                        "counters read back; independent of --steps"}
         e2e_decode_only = {"value": gen / max(1e-9, dt - t_pre), "unit": "tokens/s",
                            "note": "same run, prefill time taken out (the device->host read-back stays in)"}
         if ypk2 is not ypk:
-            ypk2.finalize()
-        del ypk2, st2, e_tokens
+            (pair2 or ypk2).finalize()
+        del ypk2, st2, e_tokens, pair2
 
     sub = {}
     if extras and world == 1:
-        # ---- BASELINE configs[3] at batch 16 (same weights): 16 requests, 8 token slots each
+        # ---- BASELINE configs[3] at batch 16 (same weights): 16 requests over 64 token slots
         try:
             B16, K16 = 16, max(8, min(K, 48))
-            mseq = prompt_len + W + K16 + 2
+            # the requests run their prompts one after the other (64 tokens per iteration), so
+            # the first ones have decoded ~9 tokens per later request before the timing starts
+            mseq = prompt_len + 12 * B16 + W + K16 + 8
             tk = torch.zeros(B16, mseq, dtype=torch.int64)
             tk[:, :prompt_len] = torch.randint(0, shape.vocab_size, (B16, prompt_len), generator=g)
             tk = tk.to(dev)
             pl16 = torch.full((B16,), prompt_len, dtype=torch.int32, device=dev)
             y16, s16 = llama.build_decode_kernel(
                 shape, weights, tokens=tk, prompt_lengths=pl16, max_num_batched_requests=B16,
-                max_num_batched_tokens=8 * B16, max_num_pages=((mseq + page - 1) // page) * B16,
+                max_num_batched_tokens=64, max_num_pages=((mseq + page - 1) // page) * B16,
                 page_size=page)
             ms16, _ = time_decode(y16, s16, K16, W, B16, prompt_len, shape, dev, 1, 0)
-            wb, kvb = decode_bytes(shape, 1, B16, prompt_len + W + K16 / 2.0)
+            wb, kvb = decode_bytes(shape, 1, B16, time_decode.mean_context)
             hbm, src = peaks()
             ach = (wb + kvb) / (ms16 / 1e3 / K16) / 1e9
             sub["batch16"] = {"ms_per_step": ms16 / K16, "tokens_per_s": K16 * B16 / (ms16 / 1e3),
                               "steps": K16, "achieved_gbs": ach, "frac": ach / hbm,
                               "frac_of": f"{src} copy bandwidth",
                               "tensor_core_tasks": int(y16.status().tensor_core_tasks),
+                              "mean_context": time_decode.mean_context,
                               "workload": "llama3-8b decode, batch 16, prompt 512 (BASELINE configs[3])"}
             y16.finalize()
             del y16, s16, tk
         except Exception as e:   # a sub-result must not take the headline down
             sub["batch16"] = {"error": str(e)[:300]}
-    ypk.finalize()
-    del ypk, st, weights
+    (pair or ypk).finalize()
+    del ypk, st, weights, pair
     torch.cuda.empty_cache()
 
     if extras and world == 1:
