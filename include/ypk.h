@@ -64,6 +64,9 @@ enum ypk_task_type {
   YPK_TASK_RMSNORM = 6,       /* stand-alone norm (unfused graphs)        */
   YPK_TASK_SILU_MUL = 7,      /* stand-alone silu(g)*u                    */
   YPK_TASK_ALLREDUCE = 8,     /* push partial to peers + local reduce     */
+  YPK_TASK_NGRAM_PARTIAL = 9, /* prompt lookup: earliest match per slice  */
+  YPK_TASK_NGRAM_GLOBAL = 10, /* prompt lookup: drafts into the input ids */
+  YPK_TASK_VERIFY = 11,       /* greedy verification of the drafts        */
   YPK_TASK_TYPE_COUNT
 };
 
@@ -146,6 +149,19 @@ enum ypk_task_type {
  * ARGMAX_PARTIAL: ptr = {logits, part_val, part_idx}; iarg = {col0, ncols,
  *                  ldlogits, part, nparts, valid}; valid != 0: only columns [0, valid) of a
  *                  logits row can be sampled (the rest pads the lm_head; negative: none)
+ * NGRAM_PARTIAL / NGRAM_GLOBAL / VERIFY: speculative decoding by prompt lookup (serving mode;
+ *          the reference's find_ngram_partial / find_ngram_global / target_verify_greedy,
+ *          tasks/speculative_decoding/prompt_lookup.cuh, target_verify.cuh).  With a VERIFY task
+ *          in the graph (iarg = {draft tokens S, 1..7}) a request that is past its prompt
+ *          brings its last token plus S draft slots per iteration when the token budget
+ *          allows.  NGRAM_PARTIAL: ptr = {partial int32 [max_requests][nparts]}, iarg = {part,
+ *          nparts, n-gram length}: lowest position in its share of every slot's history where
+ *          the history's last n-gram occurs earlier.  NGRAM_GLOBAL: ptr = {partial, ids int64
+ *          [max_tokens]}, iarg = {nparts, n-gram length}: ids = the iteration's input tokens
+ *          with the draft slots filled by the tokens that followed the earliest match (-1:
+ *          none); the embedding reads ids.  VERIFY: ptr = {ids, model outputs int64
+ *          [max_tokens]}: num_new_tokens[request] = accepted drafts + 1; the batcher advances
+ *          the request by that many tokens.
  * ARGMAX_REDUCE: ptr = {part_val, part_idx, out(int64)}; iarg = {nparts}; with
  *          YPK_F_LL_PUSH (vocabulary split over the ranks) ptr[3] = exchange buffer
  *          [world][max_tokens][2] flagged words in the symmetric arena, iarg = {nparts,

@@ -169,6 +169,13 @@ class BatchState:
     tokens: torch.Tensor            # [total_requests, max_seq_length] int64
     prompt_len: List[int]
     max_new_per_request: int = 8
+    # prompt-lookup speculative decoding: a request that is past its prompt brings its last
+    # token plus `spec_length` draft tokens per iteration (0: off); `num_new_tokens[req]` is
+    # what the verification accepted (target_verify.cuh:20-60), read by the next
+    # prepare_next_batch as the reference's online batcher does (persistent_kernel.cuh:325-352)
+    spec_length: int = 0
+    ngram_size: int = 3
+    num_new_tokens: List[int] = field(default_factory=list)
     step: List[int] = field(default_factory=list)
     request_ids: List[int] = field(default_factory=list)
     qo_indptr: List[int] = field(default_factory=list)
@@ -183,6 +190,7 @@ class BatchState:
 
     def __post_init__(self):
         self.step = [0] * self.total_requests
+        self.num_new_tokens = [1] * self.total_requests
         self.request_ids = [-1] * self.max_requests
         self.qo_indptr = [0] * (self.max_requests + 1)
         self.kv_indptr = [0] * (self.max_requests + 1)
@@ -203,6 +211,9 @@ class BatchState:
             qo = self.qo_indptr[i]
             ntok = self.qo_indptr[i + 1] - qo
             plen = self.prompt_len[req]
+            if self.spec_length > 0 and step >= plen and ntok > 1:
+                # drafts were verified: only the accepted outputs count
+                ntok = max(1, min(ntok, self.num_new_tokens[req]))
             for j in range(ntok):
                 if step + j + 1 >= plen and step + j + 1 < self.max_seq_length:
                     self.tokens[req, step + j + 1] = output_tokens[qo + j]
@@ -233,13 +244,18 @@ class BatchState:
                 nnew = min(nnew, MT - ntok, self.max_new_per_request)
             else:
                 nnew = min(1, MT - ntok)
+                want = 1 + self.spec_length
+                if (self.spec_length > 0 and MT - ntok >= want and want <= self.max_new_per_request
+                        and step + want < self.max_seq_length):
+                    nnew = want      # the last token and the draft slots (filled by fill_drafts)
             self.request_ids[nreq] = req
             self.qo_indptr[nreq] = ntok
             self.kv_indptr[nreq] = npages
             for j in range(nold):
                 self.kv_indices[npages + j] = old_indices[kv + j]
             for j in range(nnew):
-                self.input_tokens[ntok + j] = int(self.tokens[req, step + j])
+                past_prompt = self.prompt_len[req] - step <= 0
+                self.input_tokens[ntok + j] = int(self.tokens[req, step + j]) if not (past_prompt and j > 0) else -1
             total = step + nnew
             need = (total + PS - 1) // PS
             if need > nold and (self.tail - self.head < need - nold or npages + need > MP):
@@ -281,6 +297,60 @@ class BatchState:
             self.qo_indptr[i] = ntok
             self.kv_indptr[i] = npages
         return ntok
+
+
+def prompt_lookup(tokens_row, step: int, ngram_size: int, spec_length: int) -> List[int]:
+    """Draft tokens of prompt-lookup decoding (find_ngram_partial_kernel +
+    find_ngram_global_kernel, tasks/speculative_decoding/prompt_lookup.cuh:22-132): the last
+    `ngram_size` tokens of the history tokens[0..step] are searched in the history before them;
+    the tokens after the earliest match are the drafts, -1 where there is no match or the
+    history ends."""
+    n_in = step + 1
+    drafts = [-1] * spec_length
+    if n_in <= ngram_size:
+        return drafts
+    row = [int(t) for t in tokens_row[:n_in]]
+    ngram = row[n_in - ngram_size:]
+    for idx in range(n_in - ngram_size):
+        if row[idx:idx + ngram_size] == ngram:
+            for t in range(spec_length):
+                j = idx + ngram_size + t
+                drafts[t] = row[j] if j <= step else -1
+            break
+    return drafts
+
+
+def fill_drafts(bs: BatchState):
+    """The draft slots of every request that is past its prompt (the batcher left -1 there)."""
+    for i in range(bs.max_requests):
+        req = bs.request_ids[i]
+        if req < 0:
+            continue
+        a, b = bs.qo_indptr[i], bs.qo_indptr[i + 1]
+        if bs.spec_length > 0 and bs.step[req] >= bs.prompt_len[req] and b - a > 1:
+            d = prompt_lookup(bs.tokens[req], bs.step[req], bs.ngram_size, b - a - 1)
+            bs.input_tokens[a + 1:b] = d
+
+
+def verify_greedy(bs: BatchState, output_tokens: List[int]):
+    """target_verify_greedy_kernel (tasks/speculative_decoding/target_verify.cuh:20-60): draft
+    i + 1 is accepted while it equals the model's output for position i; the count of new
+    tokens is the accepted drafts plus the model's own next token."""
+    for i in range(bs.max_requests):
+        req = bs.request_ids[i]
+        if req < 0:
+            continue
+        a, b = bs.qo_indptr[i], bs.qo_indptr[i + 1]
+        n = b - a
+        if bs.spec_length > 0 and bs.step[req] >= bs.prompt_len[req] and n > 1:
+            acc = n - 1
+            for k in range(n - 1):
+                if bs.input_tokens[a + k + 1] != output_tokens[a + k]:
+                    acc = k
+                    break
+            bs.num_new_tokens[req] = acc + 1
+        else:
+            bs.num_new_tokens[req] = n
 
 
 @dataclass
@@ -349,7 +419,8 @@ def decode_iteration(w: LlamaWeights, bs: BatchState, k_caches, v_caches, cos, s
     projections; partial sums are reduced with allreduce_sum."""
     ntok = bs.qo_indptr[bs.max_requests] if num_tokens is None else num_tokens
     ids = torch.tensor(bs.input_tokens[:ntok])
-    x = w.embed[ids].float()
+    valid = (ids >= 0) & (ids < w.embed.shape[0])        # an id outside the table embeds as zeros
+    x = w.embed[ids.clamp(0, w.embed.shape[0] - 1)].float() * valid[:, None]
     d = w.head_dim
     for li, L in enumerate(w.layers):
         h = rmsnorm(x, L["input_norm"], w.eps, rounding)
@@ -395,7 +466,9 @@ def generate(w: LlamaWeights, bs: BatchState, k_caches, v_caches, cos, sin, roun
             break
         if max_iterations is not None and it >= max_iterations:
             break
+        fill_drafts(bs)
         out = decode_iteration(w, bs, k_caches, v_caches, cos, sin, rounding,
                                logits_out=logits_trace)
+        verify_greedy(bs, out)
         it += 1
     return it

@@ -7,7 +7,7 @@ import torch
 
 from oracle import decode_oracle as O
 from tests.util import assert_close, oracle_weights, replay_against_oracle
-from yirage_b200 import llama
+from yirage_b200 import llama, speculative
 
 pytestmark = pytest.mark.gpu
 
@@ -20,9 +20,9 @@ def tiny_shape(layers=2):
 
 def run_generation(prompt_lens, max_seq, *, max_requests, max_tokens, max_pages, page_size=64,
                    seed=3, layers=2, pause_every=0, handoff=None, shape=None, min_exact=0.75,
-                   full_width=False):
+                   full_width=False, spec=None, std=0.02):
     shape = shape or tiny_shape(layers)
-    w = llama.init_weights(shape, "cuda", seed, std=0.02)  # BASELINE: weights ~N(0, 0.02)
+    w = llama.init_weights(shape, "cuda", seed, std=std)  # BASELINE: weights ~N(0, 0.02)
     g = torch.Generator().manual_seed(seed)
     R = len(prompt_lens)
     tokens = torch.zeros(R, max_seq, dtype=torch.int64)
@@ -34,7 +34,9 @@ def run_generation(prompt_lens, max_seq, *, max_requests, max_tokens, max_pages,
     ypk, st = llama.build_decode_kernel(
         shape, w, tokens=tokens, prompt_lengths=plen, max_num_batched_requests=max_requests,
         max_num_batched_tokens=max_tokens, max_num_pages=max_pages, page_size=page_size,
-        handoff=handoff)
+        handoff=handoff,
+        spec_decode_config=speculative.PromptLookupConfig(ngram_size=spec[0], spec_length=spec[1])
+        if spec else None)
     if pause_every:
         for _ in range(10000):
             ypk(max_iterations=pause_every)
@@ -50,7 +52,7 @@ def run_generation(prompt_lens, max_seq, *, max_requests, max_tokens, max_pages,
     got = tokens.cpu()
     iters, bs, last_logits, exact, total = replay_against_oracle(
         shape, ow, got, prompt_lens, max_seq=max_seq, max_requests=max_requests,
-        max_tokens=max_tokens, max_pages=max_pages, page_size=page_size)
+        max_tokens=max_tokens, max_pages=max_pages, page_size=page_size, spec=spec)
     assert status.iterations == iters, "device and oracle disagree on the iteration count"
     assert st["meta"]["step"].cpu().tolist() == bs.step
     # exact agreement is not guaranteed (bf16 near-ties are accepted above); a low rate
@@ -80,6 +82,7 @@ def run_generation(prompt_lens, max_seq, *, max_requests, max_tokens, max_pages,
         assert pipe_ratio <= 1.25 * max(ref_ratio, 1.0), \
             f"device logits {pipe_ratio:.2f}x the tolerance from the bf16 pipeline"
     ypk.finalize()
+    status.tokens = got
     return status
 
 
@@ -175,6 +178,24 @@ def test_prefill_graph_hands_over_to_decode_graph():
     assert pair.run() == (it_p, it_d)
     assert torch.equal(tokens.cpu(), first)
     pair.finalize()
+
+
+def test_prompt_lookup_speculative_decoding():
+    """Prompt-lookup drafts verified greedily (the reference's find_ngram / target_verify tasks,
+    here for every request of the batch): the tokens are those of plain greedy decoding, the
+    oracle replay accepts the same drafts, and a model that falls into repeating itself needs
+    far fewer iterations than tokens."""
+    shape = llama.LlamaShape(hidden_size=256, intermediate_size=512, num_hidden_layers=1,
+                             num_attention_heads=2, num_key_value_heads=1, vocab_size=64,
+                             rms_norm_eps=1e-5)
+    kw = dict(max_requests=1, max_tokens=8, max_pages=2, shape=shape, seed=2, std=0.05, min_exact=0.6)
+    plain = run_generation([9], 70, **kw)
+    spec = run_generation([9], 70, spec=(2, 5), **kw)
+    assert plain.iterations == 62 and spec.iterations < 50, (plain.iterations, spec.iterations)
+    assert torch.equal(plain.tokens, spec.tokens)
+    # several requests in flight, drafts only where the token budget allows
+    run_generation([9, 4, 12], 50, max_requests=2, max_tokens=8, max_pages=2, shape=shape, seed=0,
+                   std=0.05, min_exact=0.6, spec=(2, 3))
 
 
 def test_sequence_crosses_page_boundaries():

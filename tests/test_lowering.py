@@ -518,3 +518,36 @@ def test_wide_graphs_split_narrow_operators_along_k(native_lib):
     assert set(lowering.simulate(g, 2)) == {2}
     ypk.compile(dry_run=True)
     ypk.finalize()
+
+
+def test_prompt_lookup_graph_lowers_and_validates(native_lib):
+    """Speculative decoding by prompt lookup (demo/qwen3/demo.py:377-384,457-470,625-632): the
+    draft operators sit in front of the embedding, which reads the draft ids; the verification
+    is the last operator; the reference's task types are in the JSON."""
+    from yirage_b200 import speculative
+    shape = llama.LlamaShape(hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                             num_attention_heads=8, num_key_value_heads=2, vocab_size=2048)
+    w = llama.init_weights(shape, "cpu", 0)
+    tokens = torch.zeros(2, 128, dtype=torch.int64)
+    cfg = speculative.spec_decode_class("promptlookup", ngram_size=3, spec_length=5)
+    ypk, _ = llama.build_decode_kernel(
+        shape, w, tokens=tokens, prompt_lengths=torch.tensor([5, 7], dtype=torch.int32),
+        max_num_batched_requests=2, max_num_batched_tokens=8, max_num_pages=8, page_size=64,
+        compile=False, spec_decode_config=cfg)
+    g = ypk.lower(148)
+    kinds = [o.kind for o in g.ops]
+    assert kinds[:3] == ["ngram_partial", "ngram_global", "embed"] and kinds[-1] == "verify"
+    glob = [t for t in g.tasks if t.type == N.TASK_NGRAM_GLOBAL]
+    emb = [t for t in g.tasks if t.type == N.TASK_EMBED]
+    assert len(glob) == 1 and all(e.ptr[0][0] is glob[0].ptr[1][0] for e in emb), \
+        "the embedding reads the ids the draft operator writes"
+    parts = [t for t in g.tasks if t.type == N.TASK_NGRAM_PARTIAL]
+    assert [t.iarg[0] for t in parts] == list(range(parts[0].iarg[1])) and parts[0].iarg[2] == 3
+    ver = [t for t in g.tasks if t.type == N.TASK_VERIFY]
+    assert len(ver) == 1 and ver[0].iarg[0] == 5 and ver[0] is g.tasks[-1]
+    counts = lowering.simulate(g, iterations=3)
+    assert set(counts) == {3}
+    doc = json.loads(lowering.to_json(g))
+    assert {112, 113, 114} <= {t["task_type"] for t in doc["all_tasks"]}
+    ypk.compile(dry_run=True)          # the native library checks the new task kinds
+    ypk.finalize()

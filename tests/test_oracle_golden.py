@@ -195,3 +195,51 @@ def test_batcher_model_chunks_prefill_and_recycles_pages():
     # every request retires at max_seq_length - 1 tokens processed
     assert bs.step == [11, 11, 11]
     assert bs.tail - bs.head == 2, "all pages returned to the free queue"
+
+
+def test_prompt_lookup_drafts_follow_the_reference_kernel():
+    """find_ngram_partial / find_ngram_global (tasks/speculative_decoding/prompt_lookup.cuh:
+    22-132) by hand: the history's last n-gram is searched in the history before it (earliest
+    match), the drafts are the tokens after the match, -1 past the history's end or without
+    a match; a history no longer than the n-gram gives no drafts."""
+    #           0  1  2  3  4  5  6  7  8  9 10 11
+    history = [5, 6, 7, 8, 5, 6, 7, 9, 1, 5, 6, 7]
+    assert O.prompt_lookup(history, 11, 3, 4) == [8, 5, 6, 7]          # match at 0, not at 4
+    assert O.prompt_lookup(history, 11, 3, 12)[:9] == [8, 5, 6, 7, 9, 1, 5, 6, 7]
+    assert O.prompt_lookup(history, 11, 3, 12)[9:] == [-1, -1, -1]     # index > step
+    assert O.prompt_lookup(history, 7, 2, 3) == [-1, -1, -1]           # (7, 9) never seen before
+    assert O.prompt_lookup([5, 6, 7], 2, 3, 4) == [-1] * 4             # history == n-gram
+    assert O.prompt_lookup([1, 2, 3, 1, 2, 3], 5, 3, 5) == [1, 2, 3, -1, -1]
+
+
+def test_speculative_greedy_decoding_gives_the_tokens_of_plain_greedy_decoding():
+    """target_verify_greedy (target_verify.cuh:20-60) accepts a draft only if it is the model's
+    own arg-max, so the sequence is unchanged and only the iteration count drops."""
+    g = torch.Generator().manual_seed(4)
+    hidden, inter, hq, hkv, vocab = 64, 128, 4, 2, 50
+    d = hidden // hq
+    r = lambda *s: (torch.randn(*s, generator=g) * 0.2).to(torch.bfloat16)
+    one = torch.ones(hidden, dtype=torch.bfloat16)
+    layer = dict(input_norm=one, q=r(hq * d, hidden), k=r(hkv * d, hidden), v=r(hkv * d, hidden),
+                 o=r(hidden, hq * d), post_norm=one, gate=r(inter, hidden), up=r(inter, hidden),
+                 down=r(hidden, inter))
+    w = O.LlamaWeights(embed=r(vocab, hidden), layers=[layer], final_norm=one, lm_head=r(vocab, hidden),
+                       num_q_heads=hq, num_kv_heads=hkv, head_dim=d, eps=1e-5, rope_theta=10000.0)
+
+    def run(spec):
+        tokens = torch.zeros(2, 48, dtype=torch.int64)
+        tokens[0, :5] = torch.tensor([3, 7, 11, 2, 9])
+        tokens[1, :3] = torch.tensor([4, 4, 8])
+        bs = O.BatchState(total_requests=2, max_requests=2, max_tokens=8, max_pages=4, page_size=64,
+                          max_seq_length=48, eos=-1, tokens=tokens, prompt_len=[5, 3],
+                          spec_length=spec, ngram_size=2)
+        kc = [torch.zeros(4, 64, hkv, d, dtype=torch.bfloat16)]
+        vc = [torch.zeros_like(kc[0])]
+        cos, sin = O.rope_tables(d, 10000.0, 64)
+        return O.generate(w, bs, kc, vc, cos, sin, rounding=None), tokens, bs
+
+    it0, t0, _ = run(0)
+    it3, t3, bs = run(3)
+    assert torch.equal(t0, t3)
+    assert it3 < it0, "some drafts must have been accepted on this seed"
+    assert bs.step == [47, 47] and bs.tail - bs.head == 4

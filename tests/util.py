@@ -39,7 +39,7 @@ def oracle_weights(shape, w):
 
 def replay_against_oracle(shape, ow, device_tokens, prompt_lens, *, max_seq, max_requests,
                           max_tokens, max_pages, page_size, max_new_per_request=None, rounding=None,
-                          check_tokens=True, decode_tokens=None):
+                          check_tokens=True, decode_tokens=None, spec=None):
     """Teacher-forced replay: the fp32 oracle runs the same batcher and graph but sees the
     device's own token history, so every iteration is checked on identical inputs and one
     flipped near-tie cannot cascade.  Every device token must be the oracle arg-max or tie
@@ -50,7 +50,10 @@ def replay_against_oracle(shape, ow, device_tokens, prompt_lens, *, max_seq, max
     attention task takes (8, or 32 // q-heads-per-kv-head) in graphs of at most 8 tokens and
     min(64, max_tokens) in larger ones.  `decode_tokens`: the run is a prefill/decode pair: once
     a batch of at most that many tokens has been formed (not the first), the batcher goes on
-    under the small graph's limits."""
+    under the small graph's limits.  `spec` = (ngram_size, spec_length): prompt-lookup
+    speculative decoding; the drafts are looked up in the (device's) token history, the
+    verification runs on the device's tokens, and the rows behind the first rejected draft are
+    not compared (the device wrote nothing for them)."""
     G = ow.num_q_heads // ow.num_kv_heads
     small = min(8, 32 // G)
     if max_new_per_request is None:
@@ -62,7 +65,8 @@ def replay_against_oracle(shape, ow, device_tokens, prompt_lens, *, max_seq, max
     bs = O.BatchState(total_requests=R, max_requests=max_requests, max_tokens=max_tokens,
                       max_pages=max_pages, page_size=page_size, max_seq_length=max_seq, eos=-1,
                       tokens=tokens_ref, prompt_len=list(prompt_lens),
-                      max_new_per_request=max_new_per_request)
+                      max_new_per_request=max_new_per_request,
+                      ngram_size=spec[0] if spec else 3, spec_length=spec[1] if spec else 0)
     L = len(ow.layers)
     kc = [torch.zeros(max_pages, page_size, ow.num_kv_heads, ow.head_dim, dtype=torch.bfloat16)
           for _ in range(L)]
@@ -77,6 +81,7 @@ def replay_against_oracle(shape, ow, device_tokens, prompt_lens, *, max_seq, max
             bs.max_tokens, bs.max_new_per_request = decode_tokens, small
             decode_tokens = None
         trace = []
+        O.fill_drafts(bs)
         pred = O.decode_iteration(ow, bs, kc, vc, cos, sin, rounding=rounding, logits_out=trace)
         logits = trace[0]
         out = list(pred)
@@ -84,8 +89,10 @@ def replay_against_oracle(shape, ow, device_tokens, prompt_lens, *, max_seq, max
             req = bs.request_ids[i]
             if req < 0:
                 continue
-            for j in range(bs.qo_indptr[i], bs.qo_indptr[i + 1]):
-                pos = bs.step[req] + (j - bs.qo_indptr[i]) + 1
+            a, b = bs.qo_indptr[i], bs.qo_indptr[i + 1]
+            drafts = bs.spec_length > 0 and bs.step[req] >= prompt_lens[req] and b - a > 1
+            for j in range(a, b):
+                pos = bs.step[req] + (j - a) + 1
                 if pos >= prompt_lens[req] and pos < max_seq:
                     dev_tok = int(device_tokens[req, pos])
                     total += 1
@@ -94,6 +101,9 @@ def replay_against_oracle(shape, ow, device_tokens, prompt_lens, *, max_seq, max
                     assert not check_tokens or gap <= O.ATOL + O.RTOL * float(logits[j].max().abs()), \
                         f"request {req} position {pos}: device token {dev_tok} is {gap:.3f} below the max"
                     out[j] = dev_tok
+                if drafts and j + 1 < b and bs.input_tokens[j + 1] != out[j]:
+                    break       # draft rejected: the device's iteration ended here for this request
+        O.verify_greedy(bs, out)
         last_logits = logits
         iters += 1
     return iters, bs, last_logits, exact, total

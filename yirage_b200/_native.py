@@ -22,12 +22,15 @@ F16, BF16, F32, I32, I64 = 940, 941, 942, 955, 965
 
 # enum ypk_task_type
 (TASK_NOP, TASK_EMBED, TASK_LINEAR, TASK_ATTENTION, TASK_ARGMAX_PARTIAL, TASK_ARGMAX_REDUCE,
- TASK_RMSNORM, TASK_SILU_MUL, TASK_ALLREDUCE) = range(9)
+ TASK_RMSNORM, TASK_SILU_MUL, TASK_ALLREDUCE, TASK_NGRAM_PARTIAL, TASK_NGRAM_GLOBAL,
+ TASK_VERIFY) = range(12)
 
 TASK_NAMES = {
     TASK_NOP: "nop", TASK_EMBED: "embedding", TASK_LINEAR: "linear", TASK_ATTENTION: "attention",
     TASK_ARGMAX_PARTIAL: "argmax_partial", TASK_ARGMAX_REDUCE: "argmax_reduce",
     TASK_RMSNORM: "rmsnorm", TASK_SILU_MUL: "silu_mul", TASK_ALLREDUCE: "allreduce",
+    TASK_NGRAM_PARTIAL: "find_ngram_partial", TASK_NGRAM_GLOBAL: "find_ngram_global",
+    TASK_VERIFY: "target_verify_greedy",
 }
 
 F_NORM, F_RESIDUAL, F_SILU_MUL, F_F16, F_ROPE, F_NORM_NOWEIGHT = 0x1, 0x2, 0x4, 0x8, 0x10, 0x40

@@ -126,6 +126,7 @@ struct Runtime {
   long long *input_tokens;
   long long *output_tokens;
   int *prompt_len;
+  int *num_new;       // [total_req] tokens the last iteration gave each request (VERIFY task)
   int *qo_indptr;
   int *kv_indptr;
   int *kv_indices;
@@ -146,6 +147,7 @@ struct Runtime {
   int max_iters, fixed_batch, resume_pending, rank, world;
   int max_new_tokens;  // prefill chunk of one request per iteration (<= kMaxNewTokens, or
                        // <= kMaxNewKeys when every ATTENTION task reads the query-tile list)
+  int spec_len;        // draft tokens per decoding request and iteration (0: no speculation)
   int attn_chunk;      // new tokens per query tile
   int pause_below;     // > 0: stop (batch pending) once the next batch has at most this many
                        // tokens: the caller continues with a graph built for small batches

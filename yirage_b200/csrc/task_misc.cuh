@@ -241,6 +241,106 @@ __device__ __forceinline__ void silu_mul_task(const ypk_task &t, int batch) {
   }
 }
 
+// ------------------------------------------------------------ prompt-lookup drafts
+// Speculative decoding by prompt lookup (the reference's find_ngram_partial / find_ngram_global
+// / target_verify_greedy tasks, tasks/speculative_decoding/prompt_lookup.cuh:22-132 and
+// target_verify.cuh:20-60, which serve one request; here every request slot of the batch).
+// A request that is past its prompt brings its last token plus draft slots (the batcher
+// leaves -1 in them).  The drafts are the tokens that followed the earliest earlier
+// occurrence of the history's last `ngram` tokens.
+//
+// NGRAM_PARTIAL: ptr = {partial int32 [max_requests][nparts]}; iarg = {part, nparts, ngram}.
+// Part p looks at its share of the candidate positions of every slot and leaves the lowest
+// matching position (or INT_MAX).
+__device__ __forceinline__ void ngram_partial_task(const Runtime &rt, const ypk_task &t, int *red) {
+  int *partial = reinterpret_cast<int *>(t.ptr[0]);
+  const int part = t.iarg[0], nparts = t.iarg[1], N = t.iarg[2];
+  const int tid = threadIdx.x;
+  for (int i = 0; i < rt.max_req; ++i) {
+    const int req = __ldcg(rt.request_ids + i);
+    int best = 0x7fffffff;
+    if (req >= 0) {
+      const int T = __ldcg(rt.qo_indptr + i + 1) - __ldcg(rt.qo_indptr + i);
+      const int step = __ldcg(rt.step + req);
+      const int total = step + 1 - N;          // candidate positions: 0 .. total - 1
+      if (T > 1 && step >= __ldcg(rt.prompt_len + req) && total > 0) {
+        const long long *row = rt.tokens + size_t(req) * rt.max_seq;
+        const int per = (total + nparts - 1) / nparts;
+        const int lo = part * per, hi = min(total, lo + per);
+        for (int idx = lo + tid; idx < hi && best == 0x7fffffff; idx += kConsumerThreads) {
+          bool same = true;
+          for (int k = 0; k < N && same; ++k)
+            same = __ldcg(row + idx + k) == __ldcg(row + total + k);
+          if (same) best = idx;
+        }
+      }
+    }
+    if (tid == 0) *red = 0x7fffffff;
+    consumer_bar();
+    if (best != 0x7fffffff) atomicMin(red, best);
+    consumer_bar();
+    if (tid == 0) partial[size_t(i) * nparts + part] = *red;
+    consumer_bar();
+  }
+}
+
+// NGRAM_GLOBAL: ptr = {partial, ids out int64 [max_tokens]}; iarg = {nparts, ngram}.  Copies
+// the iteration's input tokens to `ids` (what the embedding reads) and fills the draft slots.
+__device__ __forceinline__ void ngram_global_task(const Runtime &rt, const ypk_task &t, int batch) {
+  const int *partial = reinterpret_cast<const int *>(t.ptr[0]);
+  long long *ids = reinterpret_cast<long long *>(t.ptr[1]);
+  const int nparts = t.iarg[0], N = t.iarg[1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = warp; i < rt.max_req; i += kConsumerWarps) {
+    const int req = __ldcg(rt.request_ids + i);
+    if (req < 0) continue;
+    const int qo = __ldcg(rt.qo_indptr + i), T = __ldcg(rt.qo_indptr + i + 1) - qo;
+    const int step = __ldcg(rt.step + req);
+    const bool drafts = T > 1 && step >= __ldcg(rt.prompt_len + req);
+    int m = 0x7fffffff;
+    if (drafts) {
+      for (int p = lane; p < nparts; p += 32) m = min(m, __ldcg(partial + size_t(i) * nparts + p));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = min(m, __shfl_xor_sync(0xffffffffu, m, o));
+    }
+    const long long *row = rt.tokens + size_t(req) * rt.max_seq;
+    for (int j = lane; j < T; j += 32) {
+      long long v = __ldcg(rt.input_tokens + qo + j);
+      if (drafts && j > 0) {
+        const long long src = static_cast<long long>(m) + N + (j - 1);
+        v = (m != 0x7fffffff && src <= step) ? __ldcg(row + src) : -1ll;
+      }
+      ids[qo + j] = v;
+    }
+  }
+  (void)batch;
+}
+
+// VERIFY: ptr = {ids (with the drafts), model outputs int64 [max_tokens]}; iarg = {spec length}.
+// num_new_tokens[request] = accepted drafts + 1 (the model's own next token), or the number
+// of tokens the slot brought when it carried no drafts.  The batcher reads it.
+__device__ __forceinline__ void verify_greedy_task(const Runtime &rt, const ypk_task &t) {
+  const long long *ids = reinterpret_cast<const long long *>(t.ptr[0]);
+  const long long *target = reinterpret_cast<const long long *>(t.ptr[1]);
+  for (int i = threadIdx.x; i < rt.max_req; i += kConsumerThreads) {
+    const int req = __ldcg(rt.request_ids + i);
+    if (req < 0) continue;
+    const int qo = __ldcg(rt.qo_indptr + i), T = __ldcg(rt.qo_indptr + i + 1) - qo;
+    int n = T;
+    if (T > 1 && __ldcg(rt.step + req) >= __ldcg(rt.prompt_len + req)) {
+      int acc = T - 1;
+      for (int k = 0; k < T - 1; ++k) {
+        if (__ldcg(ids + qo + k + 1) != __ldcg(target + qo + k)) {
+          acc = k;
+          break;
+        }
+      }
+      n = acc + 1;
+    }
+    rt.num_new[req] = n;
+  }
+}
+
 // ------------------------------------------------------------ batcher
 // Continuous batching between iterations, one thread (the reference runs the same
 // logic in scheduler 0: persistent_kernel.cuh:169-322).  Retires finished requests and
@@ -281,8 +381,10 @@ static __device__ __noinline__ int prepare_next_batch_impl(const Runtime &rt, bo
       if (req < 0) continue;
       const int step = rt.step[req];
       const int qo = rt.qo_indptr[i];
-      const int ntok = rt.qo_indptr[i + 1] - qo;
+      int ntok = rt.qo_indptr[i + 1] - qo;
       const int plen = rt.prompt_len[req];
+      // drafts were verified: only the accepted outputs count
+      if (rt.spec_len > 0 && step >= plen && ntok > 1) ntok = max(1, min(ntok, __ldcg(rt.num_new + req)));
       for (int j = 0; j < ntok; ++j) {
         if (step + j + 1 >= plen && step + j + 1 < rt.max_seq) {
           rt.tokens[size_t(req) * rt.max_seq + step + j + 1] = __ldcg(rt.output_tokens + qo + j);
@@ -317,14 +419,21 @@ static __device__ __noinline__ int prepare_next_batch_impl(const Runtime &rt, bo
     const int nold = rt.kv_indptr[i + 1] - kv;
     const int step = rt.step[req];
     int nnew = rt.prompt_len[req] - step;
+    const bool past_prompt = nnew <= 0;
     nnew = nnew > 0 ? min(min(nnew, MT - ntok), rt.max_new_tokens) : min(1, MT - ntok);
+    if (past_prompt && rt.spec_len > 0) {
+      // the last token and the draft slots (filled by the NGRAM_GLOBAL task)
+      const int want = 1 + rt.spec_len;
+      if (MT - ntok >= want && want <= rt.max_new_tokens && step + want < rt.max_seq) nnew = want;
+    }
     // nreq <= i, so the indptr entries overwritten below have been consumed already.
     for (int j = 0; j < nold; ++j) rt.kv_indices[npages + j] = rt.kv_tmp[kv + j];
     rt.request_ids[nreq] = req;
     rt.qo_indptr[nreq] = ntok;
     rt.kv_indptr[nreq] = npages;
     for (int j = 0; j < nnew; ++j)
-      rt.input_tokens[ntok + j] = rt.tokens[size_t(req) * rt.max_seq + step + j];
+      rt.input_tokens[ntok + j] =
+          (past_prompt && j > 0) ? -1ll : rt.tokens[size_t(req) * rt.max_seq + step + j];
     const int total = step + nnew;
     const int need = (total + PS - 1) / PS;
     if (need > nold && (tail - head < need - nold || npages + need > MP)) return -1;

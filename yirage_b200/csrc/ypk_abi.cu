@@ -63,6 +63,7 @@ struct ypk_handle {
   int attn_chunk = kMaxNewTokens;      // new tokens per query tile (YPK_F_QTILES)
   bool attn_plain = false, attn_qtiles = false;   // kinds of ATTENTION task in the graph
   int pause_below = 0;
+  int spec_len = 0;                    // draft tokens per decoding request (a VERIFY task sets it)
   bool graph_loaded = false;
   // device state
   ypk_task *d_tasks = nullptr;
@@ -326,6 +327,37 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
           return fail(h, YPK_ERR_INVALID, "task %d: ARGMAX_REDUCE exchange for rank %d of %d", ti, a[3], a[2]);
         need[3] = uint64_t(a[2]) * mb * 16; align[3] = 16; required[3] = true;
       }
+      break;
+    }
+    case YPK_TASK_NGRAM_PARTIAL: {
+      const int part = a[0], nparts = a[1], ngram = a[2];
+      if (h->cfg.mode != 1 || !h->cfg.num_new_tokens)
+        return fail(h, YPK_ERR_INVALID, "task %d: prompt lookup needs the serving mode and num_new_tokens", ti);
+      if (nparts < 1 || part < 0 || part >= nparts || ngram < 1 || ngram > 8)
+        return fail(h, YPK_ERR_INVALID, "task %d: NGRAM_PARTIAL part %d of %d, n-gram of %d", ti, part, nparts, ngram);
+      need[0] = uint64_t(h->cfg.max_num_batched_requests) * nparts * 4; align[0] = 4; required[0] = true;
+      break;
+    }
+    case YPK_TASK_NGRAM_GLOBAL: {
+      const int nparts = a[0], ngram = a[1];
+      if (h->cfg.mode != 1 || !h->cfg.num_new_tokens)
+        return fail(h, YPK_ERR_INVALID, "task %d: prompt lookup needs the serving mode and num_new_tokens", ti);
+      if (nparts < 1 || ngram < 1 || ngram > 8)
+        return fail(h, YPK_ERR_INVALID, "task %d: NGRAM_GLOBAL over %d parts, n-gram of %d", ti, nparts, ngram);
+      need[0] = uint64_t(h->cfg.max_num_batched_requests) * nparts * 4; align[0] = 4; required[0] = true;
+      need[1] = uint64_t(mb) * 8; align[1] = 8; required[1] = true;
+      break;
+    }
+    case YPK_TASK_VERIFY: {
+      if (h->cfg.mode != 1 || !h->cfg.num_new_tokens)
+        return fail(h, YPK_ERR_INVALID, "task %d: VERIFY needs the serving mode and num_new_tokens", ti);
+      if (a[0] < 1 || a[0] + 1 > kMaxNewTokens)
+        return fail(h, YPK_ERR_UNSUPPORTED, "task %d: %d draft tokens (1..%d)", ti, a[0], kMaxNewTokens - 1);
+      if (h->spec_len && h->spec_len != a[0])
+        return fail(h, YPK_ERR_INVALID, "task %d: two VERIFY tasks with different draft lengths", ti);
+      h->spec_len = a[0];
+      need[0] = uint64_t(mb) * 8; align[0] = 8; required[0] = true;
+      need[1] = uint64_t(mb) * 8; align[1] = 8; required[1] = true;
       break;
     }
     case YPK_TASK_ALLREDUCE: {
@@ -821,6 +853,7 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
   }
   h->max_new_tokens = h->attn_chunk = kMaxNewTokens;
   h->attn_plain = h->attn_qtiles = false;
+  h->spec_len = 0;
   std::vector<ypk_task> resolved(static_cast<size_t>(num_tasks));
   std::vector<int> trig_count(size_t(num_events), 0), last_trig(size_t(num_events), -1);
   for (int i = 0; i < num_tasks; ++i) {
@@ -1027,6 +1060,8 @@ int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_
   rt.input_tokens = static_cast<long long *>(c.input_tokens);
   rt.output_tokens = static_cast<long long *>(c.output_tokens);
   rt.prompt_len = static_cast<int *>(c.prompt_lengths);
+  rt.num_new = static_cast<int *>(c.num_new_tokens);
+  rt.spec_len = h->spec_len;
   rt.qo_indptr = static_cast<int *>(c.qo_indptr);
   rt.kv_indptr = static_cast<int *>(c.paged_kv_indptr);
   rt.kv_indices = static_cast<int *>(c.paged_kv_indices);

@@ -143,12 +143,14 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
                         v_cache: Optional[torch.Tensor] = None, compile: bool = True,
                         dry_run: bool = False, profiler_tensor: Optional[torch.Tensor] = None, handoff: Optional[str] = None,
                         vocab_parallel: Optional[bool] = None, defer_connect: bool = False,
-                        meta: Optional[Dict] = None):
+                        meta: Optional[Dict] = None, spec_decode_config=None):
     """Build (and compile) the decode megakernel for `weights`.  Returns (ypk, state) where
     state holds the meta tensors, caches and rope tables the kernel works on.  `meta`, `k_cache`
     and `v_cache` of an earlier build may be passed in: the two kernels then serve the same
     requests (PersistentKernel.adopt); the token buffers of `meta` must hold at least
-    max_num_batched_tokens entries."""
+    max_num_batched_tokens entries.  `spec_decode_config` (speculative.PromptLookupConfig)
+    adds the prompt-lookup draft and verification operators the way demo/qwen3/demo.py:377-384,
+    457-470,625-632 does."""
     dev = tokens.device
     total_requests, max_seq_length = tokens.shape
     h, d = shape.hidden_size, shape.head_dim
@@ -197,7 +199,7 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
         num_local_schedulers=0, num_remote_schedulers=0, max_seq_length=max_seq_length,
         max_num_batched_requests=MR, max_num_batched_tokens=MT, max_num_pages=max_num_pages,
         page_size=page_size, eos_token_id=eos_token_id, meta_tensors=meta,
-        profiler_tensor=profiler_tensor, trace_name="", spec_decode_config=None,
+        profiler_tensor=profiler_tensor, trace_name="", spec_decode_config=spec_decode_config,
         use_cutlass_kernel=True)
     if handoff is not None:
         ypk.handoff = handoff   # "event" | "ll" | "auto" (see lowering.lower)
@@ -205,6 +207,13 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
         ypk.rms_norm_eps = shape.rms_norm_eps
 
     x_tok = ypk.attach_input(meta["input_tokens"], name="input_token")
+    spec_tokens = None
+    if spec_decode_config is not None:
+        all_tokens = ypk.attach_input(meta["tokens"], name="all_tokens")
+        spec_tokens = ypk.draft_forward_layer_dispatcher(
+            spec_decode_config=spec_decode_config, tokens=all_tokens, grid_dim=(96, 1, 1),
+            block_dim=(128, 1, 1))
+        x_tok = spec_tokens
     cos_t = ypk.attach_input(cos, name="cos_position_embedding")
     sin_t = ypk.attach_input(sin, name="sin_position_embedding")
     embed_w = ypk.attach_input(weights["embed"], name="embed_tokens")
@@ -252,9 +261,11 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
         if "q_norm" in L:
             qn = ypk.attach_input(L["q_norm"], name=f"layer_{li}_q_norm")
             kn = ypk.attach_input(L["k_norm"], name=f"layer_{li}_k_norm")
-        ypk.paged_attention_layer(input=attn_in, k_cache=kc, v_cache=vc, q_norm=qn, k_norm=kn,
-                                  cos_pos_embed=cos_t, sin_pos_embed=sin_t, output=attn_out,
-                                  grid_dim=(MR, hkv, 1), block_dim=(128, 1, 1))
+        attention = (ypk.single_batch_extend_attention_layer if spec_decode_config is not None
+                     else ypk.paged_attention_layer)
+        attention(input=attn_in, k_cache=kc, v_cache=vc, q_norm=qn, k_norm=kn,
+                  cos_pos_embed=cos_t, sin_pos_embed=sin_t, output=attn_out,
+                  grid_dim=(MR, hkv, 1), block_dim=(128, 1, 1))
         w_o = ypk.attach_input(L["o"], name=f"layer_{li}_o_proj")
         ypk.linear_with_residual_layer(input=attn_out, weight=w_o, residual=x, output=attn_proj_out,
                                        grid_dim=(h // 64, 1, 1), block_dim=(128, 1, 1))
@@ -300,6 +311,10 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
     ypk.argmax_reduce_layer(input=(argmax_part_value, argmax_part_index), output=argmax_out,
                             grid_dim=(1, 1, 1), block_dim=(128, 1, 1),
                             vocab_offset=rank * vslice if vocab_parallel else 0, exchange=vocab_parallel)
+    if spec_decode_config is not None:
+        ypk.verify_layer_dispatcher(spec_decode_config=spec_decode_config, spec_tokens=spec_tokens,
+                                    target_output=argmax_out, grid_dim=(1, 1, 1),
+                                    block_dim=(128, 1, 1))
     state = {"meta": meta, "k_cache": k_cache, "v_cache": v_cache, "cos": cos, "sin": sin,
              "lm_head": lm_head, "vocab_slice": (rank * vslice if vocab_parallel else 0, vslice),
              "tensors": {"argmax_in": argmax_in, "attn_out": attn_out}}

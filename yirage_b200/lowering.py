@@ -251,6 +251,21 @@ def fuse(regs: List[RegisteredTask], default_eps: float, fuse_norm: bool = True)
                                attrs={"vocab_offset": rt.attrs.get("vocab_offset", 0),
                                       "exchange": rt.attrs.get("exchange", False)}))
             i += 1
+        elif name == "find_ngram_partial":
+            toks, o = rt.operands
+            out.append(FusedOp("ngram_partial", [rt], {"tokens": toks, "out": o},
+                               attrs={"ngram_size": rt.params[0]}))
+            i += 1
+        elif name == "find_ngram_global":
+            part, toks, o = rt.operands
+            out.append(FusedOp("ngram_global", [rt], {"partial": part, "tokens": toks, "out": o},
+                               attrs={"ngram_size": rt.params[0], "spec_length": rt.params[1]}))
+            i += 1
+        elif name == "target_verify_greedy":
+            spec, target, o = rt.operands
+            out.append(FusedOp("verify", [rt], {"spec": spec, "target": target, "out": o},
+                               attrs={"spec_length": rt.attrs.get("spec_length")}))
+            i += 1
         elif name == "allreduce":
             x, buf, o = rt.operands
             out.append(FusedOp("allreduce", [rt], {"in": x, "buf": buf, "out": o},
@@ -264,9 +279,10 @@ def fuse(regs: List[RegisteredTask], default_eps: float, fuse_norm: bool = True)
 # --------------------------------------------------------------------- flagged hand-off
 _OUTPUT_KEYS = {"embed": ("out",), "linear": ("out",), "attention": ("out",), "rmsnorm": ("out",),
                 "silu_mul": ("out",), "argmax_partial": ("val", "idx"), "argmax_reduce": ("out",),
-                "allreduce": ("out",)}
+                "allreduce": ("out",), "ngram_partial": ("out",), "ngram_global": ("out",),
+                "verify": ("out",)}
 # operands that are not activations produced inside the iteration
-_STATIC_KEYS = {"w", "norm_w", "table", "ids", "k_cache", "v_cache", "cos", "sin", "buf"}
+_STATIC_KEYS = {"w", "norm_w", "table", "k_cache", "v_cache", "cos", "sin", "buf", "tokens"}
 
 
 def _op_outputs(op):
@@ -860,6 +876,54 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                 ts.iarg[12] = ARGMAX_TAG_ID
             ts.worker = 0
             tasks.append(ts)
+        elif op.kind == "ngram_partial":
+            part = op.t["out"]
+            if part.dtype != int32 and part.dtype != int64:
+                raise ValueError("find_ngram_partial: the partial results are integers")
+            # the reference sizes this buffer [requests, 96] int64; here it is read as int32
+            # [max_requests][nparts] with as many parts as fit, one task each
+            words = part.nbytes // 4
+            nparts = max(1, min(W, words // max(1, max_requests)))
+            op.attrs["nparts"] = nparts
+            for p in range(nparts):
+                ts = TaskSpec(N.TASK_NGRAM_PARTIAL, op_id=oi)
+                ts.ptr[0] = (part, 0)
+                ts.iarg[:3] = [p, nparts, int(op.attrs["ngram_size"])]
+                ts.worker = (rr + p) % W
+                tasks.append(ts)
+            rr += nparts
+        elif op.kind == "ngram_global":
+            part, ids = op.t["partial"], op.t["out"]
+            nparts = None
+            for prev in reversed(ops[:oi]):
+                if prev.kind == "ngram_partial" and prev.t["out"] is part:
+                    nparts = prev.attrs["nparts"]
+                    break
+            if nparts is None:
+                raise ValueError("find_ngram_global without the find_ngram_partial that feeds it")
+            if ids.dtype != int64 or ids.nbytes < max_tokens * 8:
+                raise ValueError("find_ngram_global: the draft ids are int64, one per token slot")
+            ts = TaskSpec(N.TASK_NGRAM_GLOBAL, op_id=oi)
+            ts.ptr[0], ts.ptr[1] = (part, 0), (ids, 0)
+            ts.iarg[:2] = [nparts, int(op.attrs["ngram_size"])]
+            ts.worker = rr % W
+            tasks.append(ts)
+            rr += 1
+            op.attrs["ids"] = ids
+        elif op.kind == "verify":
+            spec_len = op.attrs.get("spec_length")
+            if spec_len is None:
+                for prev in reversed(ops[:oi]):
+                    if prev.kind == "ngram_global" and prev.t["out"] is op.t["spec"]:
+                        spec_len = prev.attrs["spec_length"]
+                        break
+            if not spec_len:
+                raise ValueError("target_verify_greedy: the draft length is unknown")
+            ts = TaskSpec(N.TASK_VERIFY, op_id=oi)
+            ts.ptr[0], ts.ptr[1] = (op.t["spec"], 0), (op.t["target"], 0)
+            ts.iarg[0] = int(spec_len)
+            ts.worker = 0
+            tasks.append(ts)
         elif op.kind == "rmsnorm":
             x, nw, o = op.t["x"], op.t["w"], op.t["out"]
             ntask = min(max_tokens, W)
@@ -1028,11 +1092,13 @@ def simulate(g: LoweredGraph, iterations: int = 2):
 _REF_TASK_TYPE = {  # TaskType numbers of the reference (runtime_header.h:62-124)
     N.TASK_EMBED: 101, N.TASK_LINEAR: 253, N.TASK_ATTENTION: 257, N.TASK_ARGMAX_PARTIAL: 259,
     N.TASK_ARGMAX_REDUCE: 258, N.TASK_RMSNORM: 154, N.TASK_SILU_MUL: 118, N.TASK_ALLREDUCE: 107,
+    N.TASK_NGRAM_PARTIAL: 112, N.TASK_NGRAM_GLOBAL: 113, N.TASK_VERIFY: 114,
 }
 REF_TASK_NAMES = {101: "TASK_EMBEDDING", 253: "TASK_LINEAR_SM100", 252: "TASK_LINEAR_WITH_RESIDUAL_SM100",
                   257: "TASK_ATTN_SM100", 259: "TASK_ARGMAX_PARTIAL_SM100",
                   258: "TASK_ARGMAX_REDUCE_SM100", 154: "TASK_RMS_NORM_HOPPER", 118: "TASK_SILU_MUL",
-                  107: "TASK_REDUCE"}
+                  107: "TASK_REDUCE", 112: "TASK_FIND_NGRAM_PARTIAL", 113: "TASK_FIND_NGRAM_GLOBAL",
+                  114: "TASK_TARGET_VERIFY_GREEDY"}
 EVENT_INVALID_ID = 0x7ffffffffffffffe     # runtime_header.h:55: "no event"
 EVENT_LAUNCH_DEPENDENT_TASKS = 903        # runtime_header.h:126-134
 EVENT_END_OF_TASK_GRAPH = 910
@@ -1040,7 +1106,8 @@ _JSON_DTYPES = (940, 941, 965)            # fp16, bf16, int64: what the referenc
 # pointer slots of ypk_task that a task writes, by task type (the rest are inputs)
 _OUTPUT_SLOTS = {N.TASK_EMBED: (2,), N.TASK_LINEAR: (2,), N.TASK_ATTENTION: (3,),
                  N.TASK_ARGMAX_PARTIAL: (1, 2), N.TASK_ARGMAX_REDUCE: (2,), N.TASK_RMSNORM: (2,),
-                 N.TASK_SILU_MUL: (1,), N.TASK_ALLREDUCE: (2,)}
+                 N.TASK_SILU_MUL: (1,), N.TASK_ALLREDUCE: (2,), N.TASK_NGRAM_PARTIAL: (0,),
+                 N.TASK_NGRAM_GLOBAL: (1,), N.TASK_VERIFY: ()}
 
 
 # pointer slots that hold runtime-internal buffers (flagged-word copies, exchange areas, scratch)

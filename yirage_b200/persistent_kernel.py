@@ -83,6 +83,8 @@ class PersistentKernel:
         self.use_nvshmem = world_size > 1
         self.spec_decode_config = spec_decode_config
         self.use_cutlass_kernel = use_cutlass_kernel
+        self._spec_decode_handlers = {"promptlookup": self.prompt_lookup_spec_handler}
+        self._spec_verify_handlers = {"promptlookup": self.prompt_lookup_verify_handler}
         # The reference's rmsnorm task hard-codes eps = 1e-6 (task_register.cc:1186); that
         # stays the default so unchanged callers see the same numbers.  Set this attribute
         # (or pass eps= to rmsnorm_layer) to use the model's own epsilon.
@@ -278,12 +280,91 @@ class PersistentKernel:
                        [getattr(self, "argmax_partial_output_size", 0)],
                        vocab_offset=int(vocab_offset), exchange=bool(exchange))
 
-    # builders of the reference that lie outside the decode hot path
+    # ------------------------------------------------------------------ speculative decoding
+    # Prompt lookup (persistent_kernel.py:1013-1136 of the reference).  The reference serves one
+    # request with it; here every request of the batch that is past its prompt brings its last
+    # token plus `spec_length` draft slots per iteration when the token budget allows, the
+    # draft ids take the place of the input ids in front of the embedding, and the batcher
+    # advances each request by what the verification accepted.
+    def find_ngram_partial_layer(self, input: DTensor, output: DTensor, grid_dim: tuple,
+                                 block_dim: tuple, ngram_size: int = 3):
+        assert input.num_dims == 2      # (requests, max_seq_length): the token matrix
+        assert output.num_dims == 2     # (requests, tasks)
+        self._register("find_ngram_partial", [(input, (-1, -1, -1), -1), (output, (1, -1, -1), -1)],
+                       grid_dim, block_dim, [ngram_size])
+
+    def find_ngram_global_layer(self, input: tuple, output: DTensor, grid_dim: tuple,
+                                block_dim: tuple, ngram_size: int = 3, spec_length: int = 5):
+        assert len(input) == 2
+        partial_results, tokens = input
+        assert partial_results.num_dims == 2 and tokens.num_dims == 2 and output.num_dims == 2
+        self._register("find_ngram_global",
+                       [(partial_results, (-1, -1, -1), -1), (tokens, (-1, -1, -1), -1),
+                        (output, (-1, -1, -1), -1)], grid_dim, block_dim, [ngram_size, spec_length])
+
+    def prompt_lookup_spec_handler(self, spec_decode_config, tokens: DTensor, grid_dim: tuple,
+                                   block_dim: tuple):
+        partial = self.new_tensor(dims=(max(tokens.dim(0), self.max_num_batched_requests), 96),
+                                  dtype=int64, name="partial_ngram_output", io_category="cuda_tensor")
+        self.find_ngram_partial_layer(input=tokens, output=partial, grid_dim=grid_dim,
+                                      block_dim=block_dim, ngram_size=spec_decode_config.ngram_size)
+        # one id per token slot of the iteration (the reference: one row of spec_length + 1)
+        spec_tokens = self.new_tensor(dims=(self.max_num_batched_tokens, 1), dtype=int64,
+                                      name="spec_tokens", io_category="cuda_tensor")
+        self.find_ngram_global_layer(input=(partial, tokens), output=spec_tokens, grid_dim=(1, 1, 1),
+                                     block_dim=(128, 1, 1), ngram_size=spec_decode_config.ngram_size,
+                                     spec_length=spec_decode_config.spec_length)
+        return spec_tokens
+
+    def draft_forward_layer_dispatcher(self, spec_decode_config, tokens: DTensor, grid_dim: tuple,
+                                       block_dim: tuple):
+        handler = self._spec_decode_handlers.get(spec_decode_config.method)
+        if handler is None:
+            raise ValueError(f"Invalid spec decode method: {spec_decode_config.method}")
+        return handler(spec_decode_config, tokens, grid_dim, block_dim)
+
+    def target_verify_greedy_layer(self, input: tuple, output: DTensor, grid_dim: tuple,
+                                   block_dim: tuple, spec_length: int = None):
+        assert len(input) == 2
+        spec_tokens, target_tokens = input
+        assert spec_tokens.num_dims == 2 and target_tokens.num_dims == 2 and output.num_dims == 2
+        self._register("target_verify_greedy",
+                       [(spec_tokens, (-1, -1, -1), -1), (target_tokens, (-1, -1, -1), -1),
+                        (output, (-1, -1, -1), -1)], grid_dim, block_dim, spec_length=spec_length)
+
+    def prompt_lookup_verify_handler(self, spec_decode_config, spec_tokens: DTensor,
+                                     target_output: DTensor, grid_dim: tuple, block_dim: tuple):
+        verify_out = self.new_tensor(dims=(1, 1), dtype=int64, name="verify_out",
+                                     io_category="cuda_tensor")
+        self.target_verify_greedy_layer(input=(spec_tokens, target_output), output=verify_out,
+                                        grid_dim=grid_dim, block_dim=block_dim,
+                                        spec_length=spec_decode_config.spec_length)
+        return verify_out
+
+    def verify_layer_dispatcher(self, spec_decode_config, spec_tokens: DTensor,
+                                target_output: DTensor, grid_dim: tuple = (1, 1, 1),
+                                block_dim: tuple = (128, 1, 1)):
+        handler = self._spec_verify_handlers.get(spec_decode_config.method)
+        if handler is None:
+            raise ValueError(f"Invalid spec decode method: {spec_decode_config.method}")
+        return handler(spec_decode_config, spec_tokens, target_output, grid_dim, block_dim)
+
+    def single_batch_extend_attention_layer(self, input: DTensor, k_cache: DTensor, v_cache: DTensor,
+                                            q_norm: DTensor, k_norm: DTensor, cos_pos_embed: DTensor,
+                                            sin_pos_embed: DTensor, output: DTensor, grid_dim: tuple,
+                                            block_dim: tuple):
+        """The reference's attention for the spec_length + 1 tokens of its one request
+        (tasks/ampere/single_batch_extend.cuh); the paged attention task here takes several new
+        tokens per request, so this is the same operator over all request slots."""
+        self.paged_attention_layer(input, k_cache, v_cache, q_norm, k_norm, cos_pos_embed,
+                                   sin_pos_embed, output,
+                                   (self.max_num_batched_requests, k_cache.dim(2), 1), block_dim)
+
+    # builders of the reference that are outside the decode hot path
     def _not_built(self, what):
         raise NotImplementedError(f"{what} is outside the decode hot path of this build")
 
     def attention_layer(self, *a, **k): self._not_built("attention_layer (contiguous KV)")
-    def single_batch_extend_attention_layer(self, *a, **k): self._not_built("speculative extend attention")
     def tensor_init_layer(self, *a, **k): self._not_built("tensor_init_layer (MoE)")
     def moe_topk_softmax_routing_layer(self, *a, **k): self._not_built("MoE routing")
     def moe_w13_linear_layer(self, *a, **k): self._not_built("MoE expert linear")
@@ -293,11 +374,6 @@ class PersistentKernel:
     def identity_layer(self, *a, **k): self._not_built("identity_layer")
     def silu_mul_linear_with_residual_layer(self, *a, **k): self._not_built("silu_mul_linear_with_residual_layer")
     def argmax_layer(self, *a, **k): self._not_built("single-task argmax_layer")
-    def find_ngram_partial_layer(self, *a, **k): self._not_built("prompt-lookup speculative decoding")
-    def find_ngram_global_layer(self, *a, **k): self._not_built("prompt-lookup speculative decoding")
-    def target_verify_greedy_layer(self, *a, **k): self._not_built("speculative verification")
-    def draft_forward_layer_dispatcher(self, *a, **k): self._not_built("speculative decoding")
-    def verify_layer_dispatcher(self, *a, **k): self._not_built("speculative decoding")
 
     # ------------------------------------------------------------------ lowering / compile
     def _scratch_tensor(self, dims, dt, name, symmetric=False):
