@@ -67,6 +67,9 @@ enum ypk_task_type {
   YPK_TASK_NGRAM_PARTIAL = 9, /* prompt lookup: earliest match per slice  */
   YPK_TASK_NGRAM_GLOBAL = 10, /* prompt lookup: drafts into the input ids */
   YPK_TASK_VERIFY = 11,       /* greedy verification of the drafts        */
+  YPK_TASK_MOE_TOPK = 12,     /* router: softmax, top-k, active experts   */
+  YPK_TASK_MOE_SILU_MUL = 13, /* silu(gate)*up per active expert slot     */
+  YPK_TASK_MOE_COMBINE = 14,  /* residual + sum_j weight_j * expert out_j */
   YPK_TASK_TYPE_COUNT
 };
 
@@ -106,6 +109,12 @@ enum ypk_task_type {
                                   iterations of one or two tokens; otherwise wait for
                                   dep_event and read the plain tensor (ptr[0])             */
 
+#define YPK_F_MOE 0x4000u      /* LINEAR over the weights of an expert chosen at run time: ptr[5] =
+                                  active-expert list int32 [E + 1] (count at [E]) as MOE_TOPK
+                                  leaves it, iarg[10] = slot of that list the task serves,
+                                  iarg[11] = E, iarg[12] = weight rows per expert; the task is
+                                  skipped when the slot is beyond the count.  Plain 16-bit rows
+                                  in and out (no flagged words, no norm, no split along K) */
 #define YPK_F_TRIG_WIDE 0x2000u /* publish trig_event only in iterations of more than two tokens:
                                   its only waiters carry YPK_F_LL_OPT (they count those
                                   iterations, not all, towards the event's value)          */
@@ -162,6 +171,21 @@ enum ypk_task_type {
  *          none); the embedding reads ids.  VERIFY: ptr = {ids, model outputs int64
  *          [max_tokens]}: num_new_tokens[request] = accepted drafts + 1; the batcher advances
  *          the request by that many tokens.
+ * Mixture of experts (tasks/blackwell/topk_softmax_sm100.cuh, moe_linear_sm100.cuh,
+ *          mul_sum_add_sm100.cuh of the reference).  Expert work is laid out by *active slot*:
+ *          slot a of an iteration is the a-th expert (ascending id) that some token selected.
+ *          MOE_TOPK: ptr = {router logits 16-bit [tokens][E], weights fp32 [max_tokens][k],
+ *          routing int32 [E][max_tokens] (k index + 1 of the token at that expert, 0: none),
+ *          active list int32 [E + 1], slot of (token, k index) int32 [max_tokens][k]};
+ *          iarg = {E, k, ld of the logits}: softmax over the experts in fp32, the k largest in
+ *          order (lowest id on ties), weights divided by their sum.
+ *          LINEAR with YPK_F_MOE: the expert projections, one task per (slot, row slab), x and
+ *          out being the slot's [max_tokens][width] block.  MOE_SILU_MUL: ptr = {in 16-bit
+ *          [slots][max_tokens][2 I], out [slots][max_tokens][I], active list}; iarg = {I, E,
+ *          slot0, nslots}.  MOE_COMBINE: ptr = {expert outputs [slots][max_tokens][H], weights,
+ *          slot of (token, k index), residual [tokens][H], out [tokens][H]}; iarg = {H, k,
+ *          col0, ncols, ld residual, ld out}: fp32 sum in k order on top of the residual, one
+ *          rounding.
  * ARGMAX_REDUCE: ptr = {part_val, part_idx, out(int64)}; iarg = {nparts}; with
  *          YPK_F_LL_PUSH (vocabulary split over the ranks) ptr[3] = exchange buffer
  *          [world][max_tokens][2] flagged words in the symmetric arena, iarg = {nparts,

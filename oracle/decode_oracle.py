@@ -87,6 +87,52 @@ def gated_mlp(x, w_gate, w_up, w_down, rounding=None):
     return linear(silu_mul(g, u, rounding), w_down, rounding=rounding)
 
 
+def moe_topk_softmax(gate_logits, k: int, renormalize: bool = True):
+    """Routing of a mixture-of-experts layer (topk_softmax_task_impl,
+    tasks/blackwell/topk_softmax_sm100.cuh:63-303, registered with renormalize = true,
+    src/kernel/task_register.cc:2119-2133): softmax over all experts in fp32, the k largest
+    probabilities in order (lowest expert index on ties), divided by their sum.
+    Returns (weights [T, k] fp32, experts [T, k] int64)."""
+    p = torch.softmax(gate_logits.float(), dim=-1)
+    T, E = p.shape
+    weights = torch.zeros(T, k)
+    experts = torch.zeros(T, k, dtype=torch.int64)
+    for t in range(T):
+        row = p[t].clone()
+        for j in range(k):
+            m = row.max()
+            e = int((row == m).nonzero()[0])      # lowest index among equals
+            weights[t, j], experts[t, j] = m, e
+            row[e] = -10000.0
+    if renormalize:
+        weights = weights / weights.sum(dim=-1, keepdim=True)
+    return weights, experts
+
+
+def moe_mlp(x, gate_w, w13, w2, k: int, residual, rounding=None):
+    """Mixture-of-experts MLP as the reference's task sequence computes it
+    (demo/qwen3/demo_30B_A3B.py:598-645): router logits (a linear operator, 16-bit output),
+    top-k softmax routing, per selected expert w13 = [gate; up] -> silu(gate) * up -> w2,
+    then residual + sum_j weight_j * out_j accumulated in fp32 in slot order and rounded once
+    (mul_sum_add_sm100_task_impl, tasks/blackwell/mul_sum_add_sm100.cuh:24-47).
+    gate_w [E, H]; w13 [E, 2I, H]; w2 [E, H, I]."""
+    logits = linear(x, gate_w, rounding=rounding or "bf16")   # moe_gate_out is a 16-bit tensor
+    weights, experts = moe_topk_softmax(logits, k)
+    T = x.shape[0]
+    inter = w13.shape[1] // 2
+    out = torch.zeros(T, w2.shape[1])
+    for t in range(T):
+        acc = residual[t].float().clone()
+        for j in range(k):
+            e = int(experts[t, j])
+            mid = linear(x[t:t + 1], w13[e], rounding=rounding)
+            act = silu_mul(mid[:, :inter], mid[:, inter:], rounding)
+            o = linear(act, w2[e], rounding=rounding)
+            acc = acc + o[0].float() * weights[t, j]
+        out[t] = acc
+    return rnd(out, rounding)
+
+
 def rope_tables(head_dim: int, theta: float, max_pos: int):
     """cos/sin tables [max_pos, head_dim] in bf16: fp32 angles pos * theta^(-2i/d), the half
     table repeated twice (modeling_llama3.py:71-89 with the default rope init of
@@ -357,7 +403,8 @@ def verify_greedy(bs: BatchState, output_tokens: List[int]):
 class LlamaWeights:
     """Per-rank weights of a Llama-style decoder, layout as torch.nn.Linear ([out, in])."""
     embed: torch.Tensor
-    layers: List[dict]     # input_norm, q, k, v, o, post_norm, gate, up, down
+    layers: List[dict]     # input_norm, q, k, v, o, post_norm, gate, up, down; a mixture-of-
+                           # experts layer has moe_gate [E, H], w13 [E, 2I, H], w2 [E, H, I] instead
     final_norm: torch.Tensor
     lm_head: torch.Tensor
     num_q_heads: int
@@ -365,6 +412,7 @@ class LlamaWeights:
     head_dim: int
     eps: float
     rope_theta: float
+    experts_per_token: int = 0
 
 
 def paged_attention_step(q, k_new, v_new, k_cache, v_cache, pages, seq_len, page_size,
@@ -444,6 +492,9 @@ def decode_iteration(w: LlamaWeights, bs: BatchState, k_caches, v_caches, cos, s
                                              qk_eps=w.eps)
         x = linear(attn.reshape(ntok, -1), L["o"], residual=x, rounding=rounding)
         h = rmsnorm(x, L["post_norm"], w.eps, rounding)
+        if "moe_gate" in L:
+            x = moe_mlp(h, L["moe_gate"], L["w13"], L["w2"], w.experts_per_token, x, rounding)
+            continue
         g = linear(h, L["gate"], rounding=rounding)
         u = linear(h, L["up"], rounding=rounding)
         x = linear(silu_mul(g, u, rounding), L["down"], residual=x, rounding=rounding)

@@ -198,6 +198,19 @@ def test_prompt_lookup_speculative_decoding():
                    std=0.05, min_exact=0.6, spec=(2, 3))
 
 
+def test_mixture_of_experts_decode():
+    """Qwen3-MoE layer sequence (demo/qwen3/demo_30B_A3B.py:564-645): router, top-k softmax,
+    expert projections over the experts the iteration's tokens selected, weighted sum on top
+    of the residual, with q/k norm in attention as that model has it."""
+    shape = llama.LlamaShape(hidden_size=256, intermediate_size=128, num_hidden_layers=2,
+                             num_attention_heads=2, num_key_value_heads=1, vocab_size=512,
+                             rms_norm_eps=1e-6, rope_theta=1000000.0, qk_norm=True,
+                             num_experts=16, experts_per_token=4)
+    run_generation([11], 30, max_requests=1, max_tokens=8, max_pages=1, shape=shape, std=0.05)
+    run_generation([9, 3, 14], 28, max_requests=2, max_tokens=8, max_pages=2, shape=shape, seed=5,
+                   std=0.05)
+
+
 def test_sequence_crosses_page_boundaries():
     run_generation([60], 140, max_requests=1, max_tokens=8, max_pages=3)
 

@@ -167,11 +167,23 @@ def test_out_of_scope_builders_say_so():
     _, ypk = small_graph()
     with pytest.raises(NotImplementedError):
         ypk.moe_topk_softmax_routing_layer()
-    with pytest.raises(NotImplementedError):
-        yr.PersistentKernel(mode="online", world_size=1, mpi_rank=0, num_workers=1,
-                            num_local_schedulers=0, num_remote_schedulers=0, max_seq_length=1,
-                            max_num_batched_requests=1, max_num_batched_tokens=1, max_num_pages=1,
-                            page_size=64, eos_token_id=0, meta_tensors={})
+
+
+def test_online_mode_is_the_one_request_case_of_the_batcher():
+    """MODE_ONLINE of the reference (persistent_kernel.cuh:325-352) serves one request."""
+    i32 = dict(dtype=torch.int32)
+    def meta(requests):
+        return {"tokens": torch.zeros(requests, 64, dtype=torch.int64),
+                "qo_indptr_buffer": torch.zeros(2, **i32), "paged_kv_indptr_buffer": torch.zeros(2, **i32),
+                "paged_kv_indices_buffer": torch.zeros(1, **i32),
+                "paged_kv_last_page_len_buffer": torch.zeros(1, **i32)}
+    kw = dict(mode="online", world_size=1, mpi_rank=0, num_workers=1, num_local_schedulers=0,
+              num_remote_schedulers=0, max_seq_length=64, max_num_batched_requests=1,
+              max_num_batched_tokens=8, max_num_pages=1, page_size=64, eos_token_id=0)
+    ypk = yr.PersistentKernel(meta_tensors=meta(1), **kw)
+    assert ypk.online and ypk.mode == "offline" and ypk.total_num_requests == 1
+    with pytest.raises(ValueError):
+        yr.PersistentKernel(meta_tensors=meta(2), **kw)
 
 
 # TaskType / EventType numbers of the reference (persistent_kernel/runtime_header.h:62-134) and
@@ -550,4 +562,38 @@ def test_prompt_lookup_graph_lowers_and_validates(native_lib):
     doc = json.loads(lowering.to_json(g))
     assert {112, 113, 114} <= {t["task_type"] for t in doc["all_tasks"]}
     ypk.compile(dry_run=True)          # the native library checks the new task kinds
+    ypk.finalize()
+
+
+def test_mixture_of_experts_graph_lowers_and_validates(native_lib):
+    """Qwen3-MoE layer (demo/qwen3/demo_30B_A3B.py:564-645): router, top-k routing, expert
+    projections as LINEAR tasks per (active slot, row slab) whose weights are picked at run time,
+    activation, weighted sum.  One token's experts must be able to fill the machine."""
+    shape = llama.LlamaShape(hidden_size=256, intermediate_size=128, num_hidden_layers=2,
+                             num_attention_heads=2, num_key_value_heads=1, vocab_size=512,
+                             num_experts=16, experts_per_token=4)
+    w = llama.init_weights(shape, "cpu", 0)
+    assert w["layers"][0]["w13"].shape == (16, 256, 256) and w["layers"][0]["w2"].shape == (16, 256, 128)
+    tokens = torch.zeros(2, 64, dtype=torch.int64)
+    ypk, _ = llama.build_decode_kernel(
+        shape, w, tokens=tokens, prompt_lengths=torch.tensor([5, 7], dtype=torch.int32),
+        max_num_batched_requests=2, max_num_batched_tokens=8, max_num_pages=2, page_size=64,
+        compile=False)
+    g = ypk.lower(148)
+    kinds = [o.kind for o in g.ops]
+    i = kinds.index("moe_topk")
+    assert kinds[i - 2:i + 5] == ["rmsnorm", "linear", "moe_topk", "moe_linear", "moe_silu_mul",
+                                  "moe_linear", "moe_combine"]
+    w13 = [t for t in g.tasks if t.type == N.TASK_LINEAR and t.flags & N.F_MOE and t.op_id == i + 1]
+    slots = sorted({t.iarg[10] for t in w13})
+    assert slots == list(range(16)), "min(experts, max_tokens * experts per token) active slots"
+    first = [t for t in w13 if t.iarg[10] < 4]          # the slots one token uses
+    assert len({t.worker for t in first}) == len(first) >= 32
+    rows = sorted((t.iarg[1], t.iarg[2]) for t in w13 if t.iarg[10] == 0)
+    assert rows[0][0] == 0 and sum(n for _, n in rows) == 256 and all(t.iarg[12] == 256 for t in w13)
+    assert all(t.ptr[2][1] == t.iarg[10] * 8 * 256 * 2 for t in w13), "one [max_tokens, rows] block per slot"
+    assert set(lowering.simulate(g, iterations=2)) == {2}
+    doc = json.loads(lowering.to_json(g))
+    assert {254, 255, 260, 261} <= {t["task_type"] for t in doc["all_tasks"]}
+    ypk.compile(dry_run=True)
     ypk.finalize()

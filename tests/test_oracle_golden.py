@@ -243,3 +243,36 @@ def test_speculative_greedy_decoding_gives_the_tokens_of_plain_greedy_decoding()
     assert torch.equal(t0, t3)
     assert it3 < it0, "some drafts must have been accepted on this seed"
     assert bs.step == [47, 47] and bs.tail - bs.head == 4
+
+
+def test_moe_routing_is_softmax_then_topk_renormalised():
+    """topk_softmax_task_impl (tasks/blackwell/topk_softmax_sm100.cuh:63-303) with renormalize =
+    true: probabilities over all experts, the k largest in order, divided by their sum; equal
+    probabilities go to the lower expert id."""
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(5, 32, generator=g)
+    w, e = O.moe_topk_softmax(logits, 4)
+    p = torch.softmax(logits, -1)
+    tv, ti = p.topk(4)
+    assert torch.equal(e, ti) and torch.allclose(w, tv / tv.sum(-1, keepdim=True))
+    assert torch.allclose(w.sum(-1), torch.ones(5))
+    w, e = O.moe_topk_softmax(torch.zeros(1, 8), 3)
+    assert e.tolist() == [[0, 1, 2]] and torch.allclose(w, torch.full((1, 3), 1 / 3))
+
+
+def test_moe_mlp_equals_a_dense_sum_over_the_selected_experts():
+    g = torch.Generator().manual_seed(1)
+    T, H, I, E, K = 3, 32, 16, 8, 2
+    x, res = torch.randn(T, H, generator=g), torch.randn(T, H, generator=g)
+    gate_w = torch.randn(E, H, generator=g)
+    w13, w2 = torch.randn(E, 2 * I, H, generator=g) * 0.2, torch.randn(E, H, I, generator=g) * 0.2
+    got = O.moe_mlp(x, gate_w, w13, w2, K, res, rounding=None)
+    wts, exps = O.moe_topk_softmax((x @ gate_w.t()).to(torch.bfloat16), K)
+    want = res.clone()
+    for t in range(T):
+        for j in range(K):
+            e = int(exps[t, j])
+            mid = x[t] @ w13[e].t()
+            act = torch.nn.functional.silu(mid[:I]) * mid[I:]
+            want[t] += wts[t, j] * (act @ w2[e].t())
+    assert torch.allclose(got, want, atol=1e-4, rtol=1e-4)

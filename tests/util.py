@@ -34,7 +34,8 @@ def oracle_weights(shape, w):
         embed=c(w["embed"]), layers=[{k: c(v) for k, v in L.items()} for L in w["layers"]],
         final_norm=c(w["final_norm"]), lm_head=c(w["lm_head"]),
         num_q_heads=shape.num_attention_heads, num_kv_heads=shape.num_key_value_heads,
-        head_dim=shape.head_dim, eps=shape.rms_norm_eps, rope_theta=shape.rope_theta)
+        head_dim=shape.head_dim, eps=shape.rms_norm_eps, rope_theta=shape.rope_theta,
+        experts_per_token=getattr(shape, "experts_per_token", 0))
 
 
 def replay_against_oracle(shape, ow, device_tokens, prompt_lens, *, max_seq, max_requests,

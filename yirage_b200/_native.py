@@ -23,19 +23,21 @@ F16, BF16, F32, I32, I64 = 940, 941, 942, 955, 965
 # enum ypk_task_type
 (TASK_NOP, TASK_EMBED, TASK_LINEAR, TASK_ATTENTION, TASK_ARGMAX_PARTIAL, TASK_ARGMAX_REDUCE,
  TASK_RMSNORM, TASK_SILU_MUL, TASK_ALLREDUCE, TASK_NGRAM_PARTIAL, TASK_NGRAM_GLOBAL,
- TASK_VERIFY) = range(12)
+ TASK_VERIFY, TASK_MOE_TOPK, TASK_MOE_SILU_MUL, TASK_MOE_COMBINE) = range(15)
 
 TASK_NAMES = {
     TASK_NOP: "nop", TASK_EMBED: "embedding", TASK_LINEAR: "linear", TASK_ATTENTION: "attention",
     TASK_ARGMAX_PARTIAL: "argmax_partial", TASK_ARGMAX_REDUCE: "argmax_reduce",
     TASK_RMSNORM: "rmsnorm", TASK_SILU_MUL: "silu_mul", TASK_ALLREDUCE: "allreduce",
     TASK_NGRAM_PARTIAL: "find_ngram_partial", TASK_NGRAM_GLOBAL: "find_ngram_global",
-    TASK_VERIFY: "target_verify_greedy",
+    TASK_VERIFY: "target_verify_greedy", TASK_MOE_TOPK: "moe_topk_softmax",
+    TASK_MOE_SILU_MUL: "moe_silu_mul", TASK_MOE_COMBINE: "moe_mul_sum_add",
 }
 
 F_NORM, F_RESIDUAL, F_SILU_MUL, F_F16, F_ROPE, F_NORM_NOWEIGHT = 0x1, 0x2, 0x4, 0x8, 0x10, 0x40
 F_QK_NORM = 0x20
 F_QTILES = 0x80
+F_MOE = 0x4000
 F_LL_IN, F_LL_RES, F_LL_OUT, F_LL_PUSH, F_LL_OPT = 0x100, 0x200, 0x400, 0x800, 0x1000
 F_TRIG_WIDE = 0x2000
 

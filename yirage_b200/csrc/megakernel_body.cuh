@@ -153,6 +153,15 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
         __syncwarp();
         wc.task = ti;
         const ypk_task &t = misc->ptask;
+        if (t.type == YPK_TASK_LINEAR && (t.flags & YPK_F_MOE)) {
+          // the expert whose rows are streamed is known once the router has run
+          int go = 1;
+          if (lane == 0) go = moe_resolve(wc, rt, &misc->ptask, iter, true);
+          go = __shfl_sync(0xffffffffu, go, 0);
+          __syncwarp();   // lane 0 rewrote the task copy
+          if (go < 0) ok = false;
+          if (go <= 0) continue;
+        }
         if (t.type == YPK_TASK_LINEAR || t.type == YPK_TASK_ATTENTION) {
           const ProdRet r = run_produce<WIDE>(&rt, misc, smem, worker, ti, batch, pos, policy);
           pos = r.pos;
@@ -190,6 +199,10 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
           ok = misc->flag != 0;
         }
         if (prec) prec[2] = globaltimer();
+        if (ok && t.type == YPK_TASK_LINEAR && (t.flags & YPK_F_MOE)) {
+          if (tid == 0) moe_resolve(wc, rt, &misc->ctask, iter, false);   // may turn the task into a NOP
+          consumer_bar();
+        }
         if (ok) {
           if (t.type == YPK_TASK_LINEAR) {
             if (WIDE && linear_uses_umma(rt, t, batch)) {

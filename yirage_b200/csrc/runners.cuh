@@ -85,6 +85,9 @@ __device__ __noinline__ bool run_small(const Runtime *rt, Misc *misc, int worker
     case YPK_TASK_NGRAM_PARTIAL: ngram_partial_task(*rt, t, &misc->flag); break;
     case YPK_TASK_NGRAM_GLOBAL: ngram_global_task(*rt, t, batch); break;
     case YPK_TASK_VERIFY: verify_greedy_task(*rt, t); break;
+    case YPK_TASK_MOE_TOPK: moe_topk_task(*rt, t, batch); break;
+    case YPK_TASK_MOE_SILU_MUL: moe_silu_mul_task(*rt, t, batch); break;
+    case YPK_TASK_MOE_COMBINE: moe_combine_task(*rt, t, batch); break;
     case YPK_TASK_ALLREDUCE:
       if constexpr (!TP) {
         wc.failed = true;   // single-GPU kernels have no all-reduce (the host never picks them then)

@@ -241,6 +241,168 @@ __device__ __forceinline__ void silu_mul_task(const ypk_task &t, int batch) {
   }
 }
 
+// ------------------------------------------------------------ mixture of experts
+// MOE_TOPK (one task): router of a mixture-of-experts layer (topk_softmax_task_impl,
+// tasks/blackwell/topk_softmax_sm100.cuh:63-303, renormalize = true): a warp per token.
+__device__ __forceinline__ void moe_topk_task(const Runtime &rt, const ypk_task &t, int batch) {
+  const uint16_t *logits = reinterpret_cast<const uint16_t *>(t.ptr[0]);
+  float *weights = reinterpret_cast<float *>(t.ptr[1]);
+  int *routing = reinterpret_cast<int *>(t.ptr[2]);
+  int *active = reinterpret_cast<int *>(t.ptr[3]);
+  int *tok_slot = reinterpret_cast<int *>(t.ptr[4]);
+  const int E = t.iarg[0], K = t.iarg[1], ld = t.iarg[2], MT = rt.max_tok;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr int kPerLane = 32;            // up to 1024 experts
+  for (int i = tid; i < E * MT; i += kConsumerThreads) routing[i] = 0;
+  consumer_bar();
+  for (int b = warp; b < batch; b += kConsumerWarps) {
+    float p[kPerLane];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int e = lane + i * 32;
+      p[i] = e < E ? cvt_one<false>(__ldcg(logits + size_t(b) * ld + e)) : -INFINITY;
+      mx = fmaxf(mx, p[i]);
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      p[i] = lane + i * 32 < E ? expf(p[i] - mx) : -1.f;
+      sum += fmaxf(p[i], 0.f);
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i)
+      if (p[i] >= 0.f) p[i] *= inv;
+    float wsum = 0.f, mine = 0.f;
+    int mine_e = -1;
+    for (int j = 0; j < K; ++j) {
+      float best = -1.f;
+      int be = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < kPerLane; ++i) {
+        if (p[i] > best) {       // ascending ids within a lane: the first of equals stays
+          best = p[i];
+          be = lane + i * 32;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+        if (ov > best || (ov == best && oe < be)) {
+          best = ov;
+          be = oe;
+        }
+      }
+      wsum += best;
+      if (lane == j) {
+        mine = best;
+        mine_e = be;
+      }
+#pragma unroll
+      for (int i = 0; i < kPerLane; ++i)
+        if (lane + i * 32 == be) p[i] = -1.f;      // taken
+    }
+    if (lane < K) {
+      weights[size_t(b) * K + lane] = mine / wsum;
+      routing[size_t(mine_e) * MT + b] = lane + 1;
+      tok_slot[size_t(b) * K + lane] = mine_e;     // expert id for now, slot below
+    }
+  }
+  consumer_bar();
+  // active experts in ascending order (the reference appends them in atomic order)
+  if (warp == 0) {
+    int count = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      bool used = false;
+      if (e < E)
+        for (int b = 0; b < batch && !used; ++b) used = routing[size_t(e) * MT + b] != 0;
+      const unsigned m = __ballot_sync(0xffffffffu, used);
+      if (used) active[count + __popc(m & ((1u << lane) - 1u))] = e;
+      count += __popc(m);
+    }
+    if (lane == 0) active[E] = count;
+  }
+  consumer_bar();
+  for (int i = tid; i < batch * K; i += kConsumerThreads) {
+    const int e = tok_slot[i];
+    int lo = 0, hi = active[E] - 1;               // position of e in the ascending list
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (active[mid] < e) lo = mid + 1; else hi = mid;
+    }
+    tok_slot[i] = lo;
+  }
+}
+
+// LINEAR with YPK_F_MOE: called by one thread on the shared-memory copy of the task before
+// the task runs.  Points the weight operand at the rows of the expert in active slot
+// iarg[10]; a slot beyond the iteration's count turns the copy into a NOP.  The producer warp
+// (`wait` true) first waits for the event the task depends on: the router runs earlier in the
+// same iteration.  Returns 1: run, 0: skip, -1: the wait gave up.
+static __device__ __noinline__ int moe_resolve(WaitCtx &wc, const Runtime &rt, ypk_task *t,
+                                               long long iter, bool wait) {
+  if (wait && t->dep_event >= 0) {
+    const unsigned long long need =
+        static_cast<unsigned long long>(t->dep_count) * static_cast<unsigned long long>(iter);
+    if (!wait_counter(wc, rt.events + t->dep_event, need, t->dep_event)) return -1;
+  }
+  const int *active = reinterpret_cast<const int *>(t->ptr[5]);
+  const int slot = t->iarg[10], E = t->iarg[11];
+  if (slot >= __ldcg(active + E)) {
+    t->type = YPK_TASK_NOP;
+    return 0;
+  }
+  const long long expert = __ldcg(active + slot);
+  t->ptr[1] += static_cast<unsigned long long>(expert) * static_cast<unsigned long long>(t->iarg[12]) *
+               static_cast<unsigned long long>(t->iarg[4]) * 2ull;
+  return 1;
+}
+
+// MOE_SILU_MUL: out[slot][b][i] = silu(in[slot][b][i]) * in[slot][b][I + i] for the active
+// slots this task owns, with the rounding points of silu_mul_task.
+__device__ __forceinline__ void moe_silu_mul_task(const Runtime &rt, const ypk_task &t, int batch) {
+  const uint16_t *in = reinterpret_cast<const uint16_t *>(t.ptr[0]);
+  uint16_t *out = reinterpret_cast<uint16_t *>(t.ptr[1]);
+  const int *active = reinterpret_cast<const int *>(t.ptr[2]);
+  const int I = t.iarg[0], E = t.iarg[1], slot0 = t.iarg[2], nslots = t.iarg[3], MT = rt.max_tok;
+  const int count = __ldcg(active + E);
+  for (int s = slot0; s < min(slot0 + nslots, count); ++s) {
+    for (int i = threadIdx.x; i < batch * I; i += kConsumerThreads) {
+      const int b = i / I, c = i - b * I;
+      const uint16_t *row = in + (size_t(s) * MT + b) * 2 * I;
+      const float g = cvt_one<false>(__ldcg(row + c)), u = cvt_one<false>(__ldcg(row + I + c));
+      const float sg = bf16_round(g / (1.0f + __expf(-g)));
+      out[(size_t(s) * MT + b) * I + c] = cvt_out<false>(sg * u);
+    }
+  }
+}
+
+// MOE_COMBINE: out[b][c] = round(residual[b][c] + sum_j weight[b][j] * expert_out[slot(b, j)][b][c])
+// (mul_sum_add_sm100_task_impl, tasks/blackwell/mul_sum_add_sm100.cuh:24-47).
+__device__ __forceinline__ void moe_combine_task(const Runtime &rt, const ypk_task &t, int batch) {
+  const uint16_t *eo = reinterpret_cast<const uint16_t *>(t.ptr[0]);
+  const float *weights = reinterpret_cast<const float *>(t.ptr[1]);
+  const int *tok_slot = reinterpret_cast<const int *>(t.ptr[2]);
+  const uint16_t *res = reinterpret_cast<const uint16_t *>(t.ptr[3]);
+  uint16_t *out = reinterpret_cast<uint16_t *>(t.ptr[4]);
+  const int H = t.iarg[0], K = t.iarg[1], col0 = t.iarg[2], ncols = t.iarg[3], ldr = t.iarg[4],
+            ldo = t.iarg[5], MT = rt.max_tok;
+  for (int i = threadIdx.x; i < batch * ncols; i += kConsumerThreads) {
+    const int b = i / ncols, c = col0 + (i - b * ncols);
+    float acc = cvt_one<false>(__ldcg(res + size_t(b) * ldr + c));
+    for (int j = 0; j < K; ++j) {
+      const int s = __ldcg(tok_slot + size_t(b) * K + j);
+      acc += cvt_one<false>(__ldcg(eo + (size_t(s) * MT + b) * H + c)) * __ldcg(weights + size_t(b) * K + j);
+    }
+    out[size_t(b) * ldo + c] = cvt_out<false>(acc);
+  }
+}
+
 // ------------------------------------------------------------ prompt-lookup drafts
 // Speculative decoding by prompt lookup (the reference's find_ngram_partial / find_ngram_global
 // / target_verify_greedy tasks, tasks/speculative_decoding/prompt_lookup.cuh:22-132 and

@@ -188,6 +188,18 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
       need[0] = rows(ldx, mb, K); align[0] = 16; required[0] = true;
       need[1] = rows(ldw, row0 + nrows, K); align[1] = 16; required[1] = true;
       need[2] = rows(ldo, mb, ocols0 + ocols); align[2] = 2; required[2] = true;
+      if (in.flags & YPK_F_MOE) {
+        // the weights of one of E experts, picked at run time from the active list
+        const int E = a[11], per = a[12], slot = a[10];
+        if (in.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT | YPK_F_RESIDUAL | YPK_F_SILU_MUL | YPK_F_LL_IN |
+                        YPK_F_LL_RES | YPK_F_LL_OUT | YPK_F_LL_PUSH | YPK_F_LL_OPT) || a[13] || a[14] || a[15])
+          return fail(h, YPK_ERR_UNSUPPORTED, "task %d: an expert LINEAR task is a plain projection", ti);
+        if (E < 1 || slot < 0 || slot >= E || per < row0 + nrows)
+          return fail(h, YPK_ERR_INVALID, "task %d: expert LINEAR slot %d of %d experts, %d rows each", ti,
+                      slot, E, per);
+        need[1] = rows(ldw, (E - 1) * per + row0 + nrows, K);
+        need[5] = uint64_t(E + 1) * 4; align[5] = 4; required[5] = true;
+      }
       if (in.flags & YPK_F_NORM) { need[3] = uint64_t(K) * 2; align[3] = 16; required[3] = true; }
       if (in.flags & YPK_F_RESIDUAL) {
         need[4] = rows(ldr, mb, ocols0 + ocols); align[4] = 2; required[4] = true;
@@ -327,6 +339,38 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
           return fail(h, YPK_ERR_INVALID, "task %d: ARGMAX_REDUCE exchange for rank %d of %d", ti, a[3], a[2]);
         need[3] = uint64_t(a[2]) * mb * 16; align[3] = 16; required[3] = true;
       }
+      break;
+    }
+    case YPK_TASK_MOE_TOPK: {
+      const int E = a[0], K = a[1], ld = a[2];
+      if (E < 1 || E > 1024 || K < 1 || K > 32 || K > E || ld < E)
+        return fail(h, YPK_ERR_UNSUPPORTED, "task %d: MOE_TOPK over %d experts, top %d (up to 1024 / 32)", ti, E, K);
+      need[0] = rows(ld, mb, E); align[0] = 2; required[0] = true;
+      need[1] = uint64_t(mb) * K * 4; align[1] = 4; required[1] = true;
+      need[2] = uint64_t(E) * mb * 4; align[2] = 4; required[2] = true;
+      need[3] = uint64_t(E + 1) * 4; align[3] = 4; required[3] = true;
+      need[4] = uint64_t(mb) * K * 4; align[4] = 4; required[4] = true;
+      break;
+    }
+    case YPK_TASK_MOE_SILU_MUL: {
+      const int I = a[0], E = a[1], slot0 = a[2], nslots = a[3];
+      if (I < 1 || E < 1 || slot0 < 0 || nslots < 1)
+        return fail(h, YPK_ERR_INVALID, "task %d: MOE_SILU_MUL shape", ti);
+      need[0] = uint64_t(slot0 + nslots) * mb * 2 * I * 2; align[0] = 2; required[0] = true;
+      need[1] = uint64_t(slot0 + nslots) * mb * I * 2; align[1] = 2; required[1] = true;
+      need[2] = uint64_t(E + 1) * 4; align[2] = 4; required[2] = true;
+      break;
+    }
+    case YPK_TASK_MOE_COMBINE: {
+      const int H = a[0], K = a[1], col0 = a[2], ncols = a[3], ldr = a[4], ldo = a[5];
+      if (H < 1 || K < 1 || col0 < 0 || ncols < 1 || col0 + ncols > H || ldr < H || ldo < H)
+        return fail(h, YPK_ERR_INVALID, "task %d: MOE_COMBINE shape", ti);
+      // the expert outputs are [slots][max_tokens][H]; a token's slots are below the count
+      need[0] = uint64_t(mb) * H * 2; align[0] = 2; required[0] = true;
+      need[1] = uint64_t(mb) * K * 4; align[1] = 4; required[1] = true;
+      need[2] = uint64_t(mb) * K * 4; align[2] = 4; required[2] = true;
+      need[3] = rows(ldr, mb, H); align[3] = 2; required[3] = true;
+      need[4] = rows(ldo, mb, H); align[4] = 2; required[4] = true;
       break;
     }
     case YPK_TASK_NGRAM_PARTIAL: {
@@ -911,6 +955,7 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
     ypk_task &t = resolved[size_t(i)];
     if (t.type != YPK_TASK_LINEAR) continue;
     t.iarg[9] = -1;
+    if (t.flags & YPK_F_MOE) continue;   // the expert's rows are picked at run time: GEMV paths only
     const int K = t.iarg[0], nrows = t.iarg[2], ldw = t.iarg[4];
     const bool silu_ok = !(t.flags & YPK_F_SILU_MUL) || (t.iarg[1] % (2 * kSiluGran) == 0);
     if (!umma_possible || K % kUmmaKBlock != 0 || nrows > kMaxAccRows || ldw % 8 != 0 ||
@@ -929,7 +974,7 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
   std::vector<WeightKey> xkeys;
   for (int i = 0; i < num_tasks && umma_possible; ++i) {
     ypk_task &t = resolved[size_t(i)];
-    if (t.type != YPK_TASK_LINEAR) continue;
+    if (t.type != YPK_TASK_LINEAR || (t.flags & YPK_F_MOE)) continue;
     t.iarg[11] = -1;
     if (t.iarg[9] < 0 || (t.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT))) continue;
     const int K = t.iarg[0], ldx = t.iarg[3];

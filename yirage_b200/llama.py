@@ -28,6 +28,8 @@ class LlamaShape:
     rms_norm_eps: float = 1e-5
     rope_theta: float = 500000.0
     qk_norm: bool = False          # RMSNorm of q and k heads inside attention (Qwen3)
+    num_experts: int = 0           # > 0: every MLP is a mixture of experts (Qwen3-MoE), whose
+    experts_per_token: int = 0     # experts have intermediate_size columns each
 
     @staticmethod
     def llama3_8b():
@@ -40,6 +42,14 @@ class LlamaShape:
         return LlamaShape(hidden_size=4096, intermediate_size=12288, num_hidden_layers=36,
                           num_attention_heads=32, num_key_value_heads=8, vocab_size=151936,
                           rms_norm_eps=1e-6, rope_theta=1000000.0, qk_norm=True)
+
+    @staticmethod
+    def qwen3_30b_a3b():
+        """Qwen3-30B-A3B: 128 experts of 768 columns, 8 per token (demo/qwen3/demo_30B_A3B.py)."""
+        return LlamaShape(hidden_size=2048, intermediate_size=768, num_hidden_layers=48,
+                          num_attention_heads=32, num_key_value_heads=4, vocab_size=151936,
+                          rms_norm_eps=1e-6, rope_theta=1000000.0, qk_norm=True, num_experts=128,
+                          experts_per_token=8)
 
     @staticmethod
     def llama3_70b():
@@ -103,10 +113,18 @@ def init_weights(shape: LlamaShape, device, seed: int, world_size: int = 1, rank
             "v": rows_shard(full(hkv * d, h)),
             "o": cols_shard(full(h, hq * d)),
             "post_norm": torch.ones(h, device=device, dtype=dtype),
-            "gate": rows_shard(full(f, h)),
-            "up": rows_shard(full(f, h)),
-            "down": cols_shard(full(h, f)),
         }
+        if shape.num_experts:
+            if world_size != 1:
+                raise NotImplementedError("mixture-of-experts weights are built for one GPU")
+            E = shape.num_experts
+            L["moe_gate"] = full(E, h)
+            # experts stacked as the demo does: [gate rows; up rows] per expert, then down
+            L["w13"] = torch.stack([full(2 * f, h) for _ in range(E)])
+            L["w2"] = torch.stack([full(h, f) for _ in range(E)])
+        else:
+            L.update(gate=rows_shard(full(f, h)), up=rows_shard(full(f, h)),
+                     down=cols_shard(full(h, f)))
         if shape.qk_norm:
             L["q_norm"] = (1.0 + 0.1 * torch.randn(d, generator=g, device=device)).to(dtype)
             L["k_norm"] = (1.0 + 0.1 * torch.randn(d, generator=g, device=device)).to(dtype)
@@ -243,6 +261,7 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
     ypk.embed_layer(input=x_tok, weight=embed_w, output=embed_out, grid_dim=(1, 1, 1),
                     block_dim=(128, 1, 1), input_source=1)
     x = embed_out
+    moe = None
     for li, L in enumerate(weights["layers"]):
         w_norm = ypk.attach_input(L["input_norm"], name=f"layer_{li}_input_layernorm")
         w_q = ypk.attach_input(L["q"], name=f"layer_{li}_q_proj")
@@ -275,6 +294,42 @@ def build_decode_kernel(shape: LlamaShape, weights: Dict, *, tokens: torch.Tenso
                                 grid_dim=(h // 64, 1, 1), block_dim=(128, 1, 1))
             x = attn_allreduce_out
         w_norm2 = ypk.attach_input(L["post_norm"], name=f"layer_{li}_post_attn_layernorm")
+        if "moe_gate" in L:
+            # demo/qwen3/demo_30B_A3B.py:564-645
+            E, topk = shape.num_experts, shape.experts_per_token
+            if moe is None:
+                moe = {
+                    "gate_out": tmp("moe_gate_out", E),
+                    "routing": ypk.new_tensor(dims=(E, MT), dtype=core.int32, name="moe_routing_indices"),
+                    "mask": ypk.new_tensor(dims=(E + 1,), dtype=core.int32, name="moe_mask"),
+                    "topk_weight": ypk.new_tensor(dims=(MT, topk), dtype=core.float32, name="moe_topk_weight"),
+                    "mid": ypk.new_tensor(dims=(MT, topk, 2 * inter), dtype=core.bfloat16, name="moe_mlp_mid"),
+                    "act": ypk.new_tensor(dims=(MT, topk, inter), dtype=core.bfloat16, name="moe_silu_mul_out"),
+                    "out": ypk.new_tensor(dims=(MT, topk, h), dtype=core.bfloat16, name="moe_mlp_out"),
+                }
+            w_router = ypk.attach_input(L["moe_gate"], name=f"layer_{li}_moe_gate")
+            w13 = ypk.attach_input(L["w13"], name=f"layer_{li}_gateup_proj")
+            w2 = ypk.attach_input(L["w2"], name=f"layer_{li}_down_proj")
+            ypk.rmsnorm_layer(input=x, weight=w_norm2, output=rmsnorm_out, grid_dim=(MT, 1, 1),
+                              block_dim=(128, 1, 1))
+            ypk.linear_layer(input=rmsnorm_out, weight=w_router, output=moe["gate_out"],
+                             grid_dim=(1, 1, 1), block_dim=(128, 1, 1))
+            ypk.moe_topk_softmax_routing_layer(
+                input=moe["gate_out"], output=(moe["topk_weight"], moe["routing"], moe["mask"]),
+                grid_dim=(1, 1, 1), block_dim=(256, 1, 1))
+            ypk.moe_w13_linear_layer(input=rmsnorm_out, weight=w13, moe_routing_indices=moe["routing"],
+                                     moe_mask=moe["mask"], output=moe["mid"], grid_dim=(1, _divisor(2 * inter, 12), 1),
+                                     block_dim=(256, 1, 1))
+            ypk.moe_silu_mul_layer(input=moe["mid"], output=moe["act"], grid_dim=(MT, topk, 1),
+                                   block_dim=(256, 1, 1))
+            ypk.moe_w2_linear_layer(input=moe["act"], weight=w2, moe_routing_indices=moe["routing"],
+                                    moe_mask=moe["mask"], output=moe["out"], grid_dim=(1, _divisor(h, 16), 1),
+                                    block_dim=(256, 1, 1))
+            ypk.moe_mul_sum_add_layer(input=moe["out"], weight=moe["topk_weight"], residual=x,
+                                      output=mlp_out, grid_dim=(MT, max(1, h // 256), 1),
+                                      block_dim=(256, 1, 1))
+            x = mlp_out
+            continue
         w_gate = ypk.attach_input(L["gate"], name=f"layer_{li}_gate_proj")
         w_up = ypk.attach_input(L["up"], name=f"layer_{li}_up_proj")
         groups = _gate_up_groups(inter)

@@ -117,7 +117,7 @@ class LoweredGraph:
         return len(self.tasks)
 
 
-_SUFFIXES = ("_sm100", "_hopper", "_swapAB", "_cutlass")
+_SUFFIXES = ("_sm100", "_sm90", "_hopper", "_swapAB", "_cutlass")
 
 
 def canonical_name(name: str) -> str:
@@ -137,14 +137,14 @@ def canonical_name(name: str) -> str:
 def _reads(rt: RegisteredTask) -> List[DTensor]:
     name = canonical_name(rt.name)
     ops = rt.operands
-    n_out = {"argmax_partial": 2}.get(name, 1)
+    n_out = {"argmax_partial": 2, "moe_topk_softmax": 3}.get(name, 1)
     return [t for t in ops[: len(ops) - n_out] if t is not None]
 
 
 def _writes(rt: RegisteredTask) -> List[DTensor]:
     name = canonical_name(rt.name)
     ops = rt.operands
-    n_out = {"argmax_partial": 2}.get(name, 1)
+    n_out = {"argmax_partial": 2, "moe_topk_softmax": 3}.get(name, 1)
     return [t for t in ops[len(ops) - n_out:] if t is not None]
 
 
@@ -251,6 +251,23 @@ def fuse(regs: List[RegisteredTask], default_eps: float, fuse_norm: bool = True)
                                attrs={"vocab_offset": rt.attrs.get("vocab_offset", 0),
                                       "exchange": rt.attrs.get("exchange", False)}))
             i += 1
+        elif name == "moe_topk_softmax":
+            x, wts, routing, mask = rt.operands
+            out.append(FusedOp("moe_topk", [rt], {"in": x, "weights": wts, "routing": routing, "mask": mask}))
+            i += 1
+        elif name in ("moe_w13_linear", "moe_w2_linear"):
+            x, w, routing, mask, o = rt.operands
+            out.append(FusedOp("moe_linear", [rt], {"x": x, "w": w, "routing": routing, "mask": mask, "out": o},
+                               attrs={"which": "w13" if name == "moe_w13_linear" else "w2"}))
+            i += 1
+        elif name == "moe_silu_mul":
+            x, o = rt.operands
+            out.append(FusedOp("moe_silu_mul", [rt], {"in": x, "out": o}))
+            i += 1
+        elif name == "moe_mul_sum_add":
+            x, wts, res, o = rt.operands
+            out.append(FusedOp("moe_combine", [rt], {"in": x, "weights": wts, "res": res, "out": o}))
+            i += 1
         elif name == "find_ngram_partial":
             toks, o = rt.operands
             out.append(FusedOp("ngram_partial", [rt], {"tokens": toks, "out": o},
@@ -280,7 +297,8 @@ def fuse(regs: List[RegisteredTask], default_eps: float, fuse_norm: bool = True)
 _OUTPUT_KEYS = {"embed": ("out",), "linear": ("out",), "attention": ("out",), "rmsnorm": ("out",),
                 "silu_mul": ("out",), "argmax_partial": ("val", "idx"), "argmax_reduce": ("out",),
                 "allreduce": ("out",), "ngram_partial": ("out",), "ngram_global": ("out",),
-                "verify": ("out",)}
+                "verify": ("out",), "moe_topk": ("weights", "routing", "mask"), "moe_linear": ("out",),
+                "moe_silu_mul": ("out",), "moe_combine": ("out",)}
 # operands that are not activations produced inside the iteration
 _STATIC_KEYS = {"w", "norm_w", "table", "k_cache", "v_cache", "cos", "sin", "buf", "tokens"}
 
@@ -613,6 +631,8 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
     attn_scratch = None
     attn_tag_ids = set()
     splitk_bufs: Dict[tuple, tuple] = {}
+    moe_bufs: Dict[tuple, object] = {}    # scratch of the mixture-of-experts operators, by shape
+    moe_state: Dict[str, object] = {}     # the routing the expert operators of a layer work under
     prev_event, prev_count = -1, 0
 
     for oi, op in enumerate(ops):
@@ -876,6 +896,114 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                 ts.iarg[12] = ARGMAX_TAG_ID
             ts.worker = 0
             tasks.append(ts)
+        elif op.kind == "moe_topk":
+            x, wts, routing, mask = op.t["in"], op.t["weights"], op.t["routing"], op.t["mask"]
+            E, topk = x.dims[1], wts.dims[1]
+            if not (_is16(x) and wts.dtype == float32 and routing.dtype == int32 and mask.dtype == int32):
+                raise ValueError("moe_topk_softmax: 16-bit logits, fp32 weights, int32 routing and mask")
+            if routing.dims != (E, max_tokens) or mask.dims[0] != E + 1 or wts.dims[0] != max_tokens:
+                raise ValueError("moe_topk_softmax: routing is [experts, max_tokens], mask [experts + 1], "
+                                 "weights [max_tokens, experts per token]")
+            # Expert work is laid out by active slot (the a-th expert, ascending, that some token
+            # of the iteration selected); the buffers are shared by all layers.
+            key = ("moe", E, topk)
+            if key not in moe_bufs:
+                moe_bufs[key] = {"slot": scratch((max_tokens, topk), int32, "moe_token_slot"),
+                                 "slots": min(E, max_tokens * topk), "E": E, "topk": topk}
+            moe_state.update(moe_bufs[key], mask=mask, weights=wts)
+            ts = TaskSpec(N.TASK_MOE_TOPK, op_id=oi)
+            ts.ptr[0], ts.ptr[1], ts.ptr[2], ts.ptr[3] = (x, 0), (wts, 0), (routing, 0), (mask, 0)
+            ts.ptr[4] = (moe_state["slot"], 0)
+            ts.iarg[:3] = [E, topk, x.dims[1]]
+            ts.worker = rr % W
+            tasks.append(ts)
+            rr += 1
+        elif op.kind == "moe_linear":
+            x, w, o = op.t["x"], op.t["w"], op.t["out"]
+            if not moe_state or op.t["mask"] is not moe_state["mask"]:
+                raise ValueError("an expert projection needs the routing of the moe_topk_softmax before it")
+            if len(w.dims) != 3 or not _is16(w) or w.dims[0] != moe_state["E"]:
+                raise ValueError("expert weights are [experts, rows, K], 16-bit")
+            E, Nrows, K = w.dims
+            S, MT = moe_state["slots"], max_tokens
+            if K % 64:
+                raise NotImplementedError(f"linear needs K % 64 == 0 (got {K})")
+            which = op.attrs["which"]
+            # per slot an [max_tokens, width] block in and out, whatever the caller's tensors
+            # look like (the reference's are [tokens, experts per token, width])
+            bkey = (which, S, MT, Nrows)
+            if bkey not in moe_bufs:
+                moe_bufs[bkey] = scratch((S * MT, Nrows), w.dtype, f"moe_{which}_out")
+            out_buf = moe_bufs[bkey]
+            moe_state[which + "_out"] = out_buf
+            if which == "w13":
+                if x.dims[1] != K:
+                    raise ValueError("moe_w13: input width != K")
+                xin = lambda a: (x, 0)
+                ldx = x.dims[1]
+            else:
+                act = moe_state.get("act")
+                if act is None or act.dims[1] != K:
+                    raise ValueError("moe_w2 needs the moe_silu_mul before it")
+                xin = lambda a: (act, a * MT * K * 2)
+                ldx = K
+            # enough slabs per slot that one token's experts fill the machine
+            nslab = max(1, min((W + moe_state["topk"] - 1) // moe_state["topk"], (Nrows + 15) // 16))
+            per = ((Nrows + nslab - 1) // nslab + 15) // 16 * 16
+            k = 0
+            for a in range(S):
+                for r0 in range(0, Nrows, per):
+                    ts = TaskSpec(N.TASK_LINEAR, flags=N.F_MOE, op_id=oi)
+                    ts.ptr[0], ts.ptr[1], ts.ptr[2] = xin(a), (w, 0), (out_buf, a * MT * Nrows * 2)
+                    ts.ptr[5] = (moe_state["mask"], 0)
+                    ts.iarg[:8] = [K, r0, min(per, Nrows - r0), ldx, K, Nrows, 0, 0]
+                    ts.iarg[8] = 1 if which == "w2" else 0    # (only tells the two apart in the JSON)
+                    ts.iarg[9] = -1
+                    ts.iarg[10], ts.iarg[11], ts.iarg[12] = a, E, Nrows
+                    ts.worker = (rr + k) % W
+                    ts.weight_bytes = 0      # data dependent: not part of the static balance
+                    tasks.append(ts)
+                    k += 1
+            rr += k
+        elif op.kind == "moe_silu_mul":
+            src = moe_state.get("w13_out")
+            if src is None:
+                raise ValueError("moe_silu_mul needs the moe_w13_linear before it")
+            S, MT, I = moe_state["slots"], max_tokens, src.dims[1] // 2
+            bkey = ("act", S, MT, I)
+            if bkey not in moe_bufs:
+                moe_bufs[bkey] = scratch((S * MT, I), src.dtype, "moe_silu_mul_out")
+            moe_state["act"] = moe_bufs[bkey]
+            ntask = min(W, S)
+            per = (S + ntask - 1) // ntask
+            for k in range(ntask):
+                ts = TaskSpec(N.TASK_MOE_SILU_MUL, op_id=oi)
+                ts.ptr[0], ts.ptr[1], ts.ptr[2] = (src, 0), (moe_state["act"], 0), (moe_state["mask"], 0)
+                ts.iarg[:4] = [I, moe_state["E"], k * per, min(per, S - k * per)]
+                ts.worker = (rr + k) % W
+                if ts.iarg[3] > 0:
+                    tasks.append(ts)
+            rr += ntask
+        elif op.kind == "moe_combine":
+            src = moe_state.get("w2_out")
+            res, o = op.t["res"], op.t["out"]
+            if src is None or op.t["weights"] is not moe_state["weights"]:
+                raise ValueError("moe_mul_sum_add needs the moe_w2_linear and the routing weights before it")
+            H = src.dims[1]
+            if res.dims[1] != H or o.dims[1] != H:
+                raise ValueError("moe_mul_sum_add: residual and output are [tokens, hidden]")
+            ntask = max(1, min(W, H // 64))
+            cols = (H // ntask + 7) // 8 * 8
+            k = 0
+            for c in range(0, H, cols):
+                ts = TaskSpec(N.TASK_MOE_COMBINE, op_id=oi)
+                ts.ptr[0], ts.ptr[1], ts.ptr[2] = (src, 0), (moe_state["weights"], 0), (moe_state["slot"], 0)
+                ts.ptr[3], ts.ptr[4] = (res, 0), (o, 0)
+                ts.iarg[:6] = [H, moe_state["topk"], c, min(cols, H - c), res.dims[1], o.dims[1]]
+                ts.worker = (rr + k) % W
+                tasks.append(ts)
+                k += 1
+            rr += k
         elif op.kind == "ngram_partial":
             part = op.t["out"]
             if part.dtype != int32 and part.dtype != int64:
@@ -1093,12 +1221,15 @@ _REF_TASK_TYPE = {  # TaskType numbers of the reference (runtime_header.h:62-124
     N.TASK_EMBED: 101, N.TASK_LINEAR: 253, N.TASK_ATTENTION: 257, N.TASK_ARGMAX_PARTIAL: 259,
     N.TASK_ARGMAX_REDUCE: 258, N.TASK_RMSNORM: 154, N.TASK_SILU_MUL: 118, N.TASK_ALLREDUCE: 107,
     N.TASK_NGRAM_PARTIAL: 112, N.TASK_NGRAM_GLOBAL: 113, N.TASK_VERIFY: 114,
+    N.TASK_MOE_TOPK: 260, N.TASK_MOE_SILU_MUL: 118, N.TASK_MOE_COMBINE: 261,
 }
 REF_TASK_NAMES = {101: "TASK_EMBEDDING", 253: "TASK_LINEAR_SM100", 252: "TASK_LINEAR_WITH_RESIDUAL_SM100",
                   257: "TASK_ATTN_SM100", 259: "TASK_ARGMAX_PARTIAL_SM100",
                   258: "TASK_ARGMAX_REDUCE_SM100", 154: "TASK_RMS_NORM_HOPPER", 118: "TASK_SILU_MUL",
                   107: "TASK_REDUCE", 112: "TASK_FIND_NGRAM_PARTIAL", 113: "TASK_FIND_NGRAM_GLOBAL",
-                  114: "TASK_TARGET_VERIFY_GREEDY"}
+                  114: "TASK_TARGET_VERIFY_GREEDY", 254: "TASK_MOE_W13_LINEAR_SM100",
+                  255: "TASK_MOE_W2_LINEAR_SM100", 260: "TASK_MOE_TOPK_SOFTMAX_SM100",
+                  261: "TASK_MOE_MUL_SUM_ADD_SM100"}
 EVENT_INVALID_ID = 0x7ffffffffffffffe     # runtime_header.h:55: "no event"
 EVENT_LAUNCH_DEPENDENT_TASKS = 903        # runtime_header.h:126-134
 EVENT_END_OF_TASK_GRAPH = 910
@@ -1107,7 +1238,8 @@ _JSON_DTYPES = (940, 941, 965)            # fp16, bf16, int64: what the referenc
 _OUTPUT_SLOTS = {N.TASK_EMBED: (2,), N.TASK_LINEAR: (2,), N.TASK_ATTENTION: (3,),
                  N.TASK_ARGMAX_PARTIAL: (1, 2), N.TASK_ARGMAX_REDUCE: (2,), N.TASK_RMSNORM: (2,),
                  N.TASK_SILU_MUL: (1,), N.TASK_ALLREDUCE: (2,), N.TASK_NGRAM_PARTIAL: (0,),
-                 N.TASK_NGRAM_GLOBAL: (1,), N.TASK_VERIFY: ()}
+                 N.TASK_NGRAM_GLOBAL: (1,), N.TASK_VERIFY: (), N.TASK_MOE_TOPK: (1, 2, 3, 4),
+                 N.TASK_MOE_SILU_MUL: (1,), N.TASK_MOE_COMBINE: (4,)}
 
 
 # pointer slots that hold runtime-internal buffers (flagged-word copies, exchange areas, scratch)
@@ -1119,6 +1251,8 @@ def ref_task_type(ts: TaskSpec) -> int:
     """TaskType number of the reference task this task stands for (runtime_header.h:62-124)."""
     if ts.type == N.TASK_LINEAR and (ts.flags & N.F_RESIDUAL):
         return 252
+    if ts.type == N.TASK_LINEAR and (ts.flags & N.F_MOE):
+        return 255 if ts.iarg[8] else 254      # w2 / w13 expert projections
     return _REF_TASK_TYPE.get(ts.type, ts.type)
 
 

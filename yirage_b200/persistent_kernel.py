@@ -61,8 +61,17 @@ class PersistentKernel:
         self._is_compiled = False
         if mode not in valid_persistent_kernel_modes:
             raise ValueError(f"Invalid persistent kernel mode: {mode}")
-        if mode == "online":
-            raise NotImplementedError("online serving mode is outside the decode hot path")
+        # "online" is the reference's one-request mode (MODE_ONLINE batcher,
+        # persistent_kernel.cuh:325-352: step[0] advances by num_new_tokens[0] per iteration until
+        # max_seq_length or EOS).  The on-device batcher here does the same for its one slot, so
+        # online mode is the offline path with exactly one request; the caller may preset
+        # step[0] after reset() to continue a sequence whose first tokens are already cached.
+        self.online = mode == "online"
+        if self.online:
+            if max_num_batched_requests != 1 or meta_tensors["tokens"].shape[0] != 1:
+                raise ValueError("online mode serves one request: max_num_batched_requests and "
+                                 "tokens.shape[0] must be 1")
+            mode = "offline"
         self.mode = mode
         self.world_size = world_size
         self.mpi_rank = mpi_rank
@@ -360,17 +369,68 @@ class PersistentKernel:
                                    sin_pos_embed, output,
                                    (self.max_num_batched_requests, k_cache.dim(2), 1), block_dim)
 
+    # ------------------------------------------------------------------ mixture of experts
+    # The reference's builders (persistent_kernel.py:612-800; graph demo/qwen3/demo_30B_A3B.py:
+    # 564-645).  Expert work is laid out by active slot here (lowering.py), so the caller's
+    # [tokens, experts per token, width] intermediates only fix the shapes; the runtime keeps
+    # its own per-slot buffers.
+    def moe_topk_softmax_routing_layer(self, input: DTensor, output: tuple, grid_dim: tuple,
+                                       block_dim: tuple):
+        assert input.num_dims == 2 and len(output) == 3     # (tokens, experts)
+        weights, routing, mask = output
+        assert weights.num_dims == 2 and routing.num_dims == 2 and mask.num_dims == 1
+        self._register("moe_topk_softmax_sm100",
+                       [(input, (0, -1, -1), -1), (weights, (0, -1, -1), -1),
+                        (routing, (-1, -1, -1), -1), (mask, (-1, -1, -1), -1)], grid_dim, block_dim)
+
+    def _moe_linear(self, name, input, weight, moe_routing_indices, moe_mask, output, grid_dim, block_dim):
+        assert weight.num_dims == 3 and output.num_dims == 3
+        assert moe_routing_indices.num_dims == 2 and moe_mask.num_dims == 1
+        self._register(name, [(input, (-1, -1, -1), -1), (weight, (-1, 1, -1), 2),
+                              (moe_routing_indices, (-1, -1, -1), -1), (moe_mask, (-1, -1, -1), -1),
+                              (output, (-1, 2, -1), -1)], grid_dim, block_dim)
+
+    def moe_w13_linear_layer(self, input: DTensor, weight: DTensor, moe_routing_indices: DTensor,
+                             moe_mask: DTensor, output: DTensor, grid_dim: tuple, block_dim: tuple):
+        assert input.num_dims == 2      # (tokens, hidden)
+        self._moe_linear("moe_w13_linear_sm100", input, weight, moe_routing_indices, moe_mask,
+                         output, grid_dim, block_dim)
+
+    def moe_silu_mul_layer(self, input: DTensor, output: DTensor, grid_dim: tuple, block_dim: tuple):
+        assert input.num_dims == 3 and output.num_dims == 3
+        self._register("moe_silu_mul", [(input, (0, 1, -1), -1), (output, (0, 1, -1), -1)],
+                       grid_dim, block_dim)
+
+    def moe_w2_linear_layer(self, input: DTensor, weight: DTensor, moe_routing_indices: DTensor,
+                            moe_mask: DTensor, output: DTensor, grid_dim: tuple, block_dim: tuple):
+        assert input.num_dims == 3      # (tokens, experts per token, intermediate)
+        self._moe_linear("moe_w2_linear_sm100", input, weight, moe_routing_indices, moe_mask,
+                         output, grid_dim, block_dim)
+
+    def moe_mul_sum_add_layer(self, input: DTensor, weight: DTensor, residual: DTensor,
+                              output: DTensor, grid_dim: tuple, block_dim: tuple):
+        assert input.num_dims == 3 and weight.num_dims == 2
+        assert residual.num_dims == 2 and output.num_dims == 2
+        self._register("moe_mul_sum_add_sm100",
+                       [(input, (0, 2, -1), -1), (weight, (0, -1, -1), -1),
+                        (residual, (0, 1, -1), -1), (output, (0, 1, -1), -1)], grid_dim, block_dim)
+
+    def splitk_linear_layer(self, input: DTensor, weight: DTensor, output: DTensor, grid_dim: tuple,
+                            block_dim: tuple):
+        """The reference's router projection split along K; the same product as linear_layer
+        (the task cutter here decides about splits itself)."""
+        self.linear_layer(input, weight, output, grid_dim, block_dim)
+
+    def tensor_init_layer(self, *args, **kwargs):
+        """The reference zeroes the split-K accumulation target with this task; nothing here
+        accumulates into a graph tensor across tasks, so there is nothing to initialise."""
+        return None
+
     # builders of the reference that are outside the decode hot path
     def _not_built(self, what):
         raise NotImplementedError(f"{what} is outside the decode hot path of this build")
 
     def attention_layer(self, *a, **k): self._not_built("attention_layer (contiguous KV)")
-    def tensor_init_layer(self, *a, **k): self._not_built("tensor_init_layer (MoE)")
-    def moe_topk_softmax_routing_layer(self, *a, **k): self._not_built("MoE routing")
-    def moe_w13_linear_layer(self, *a, **k): self._not_built("MoE expert linear")
-    def moe_w2_linear_layer(self, *a, **k): self._not_built("MoE expert linear")
-    def moe_mul_sum_add_layer(self, *a, **k): self._not_built("MoE combine")
-    def splitk_linear_layer(self, *a, **k): self._not_built("split-K linear (MoE)")
     def identity_layer(self, *a, **k): self._not_built("identity_layer")
     def silu_mul_linear_with_residual_layer(self, *a, **k): self._not_built("silu_mul_linear_with_residual_layer")
     def argmax_layer(self, *a, **k): self._not_built("single-task argmax_layer")
