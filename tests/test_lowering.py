@@ -166,7 +166,9 @@ def test_unfusable_patterns_stay_separate():
 def test_out_of_scope_builders_say_so():
     _, ypk = small_graph()
     with pytest.raises(NotImplementedError):
-        ypk.moe_topk_softmax_routing_layer()
+        ypk.attention_layer()            # contiguous-KV attention of the reference's older demos
+    with pytest.raises(NotImplementedError):
+        ypk.identity_layer()
 
 
 def test_online_mode_is_the_one_request_case_of_the_batcher():
