@@ -186,7 +186,8 @@ enum ypk_task_type {
  *          slot of (token, k index), residual [tokens][H], out [tokens][H]}; iarg = {H, k,
  *          col0, ncols, ld residual, ld out}: fp32 sum in k order on top of the residual, one
  *          rounding.
- * ARGMAX_REDUCE: ptr = {part_val, part_idx, out(int64)}; iarg = {nparts}; with
+ * ARGMAX_REDUCE: ptr = {part_val, part_idx, out(int64)}; iarg = {nparts}, iarg[4] = row pitch
+ *          of the partial buffers (0: nparts); with
  *          YPK_F_LL_PUSH (vocabulary split over the ranks) ptr[3] = exchange buffer
  *          [world][max_tokens][2] flagged words in the symmetric arena, iarg = {nparts,
  *          first vocabulary row of this rank's slice, world, rank}, iarg[12] = tag id

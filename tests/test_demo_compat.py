@@ -86,3 +86,94 @@ def test_reference_demo_builds_its_graph_unchanged(monkeypatch, tmp_path, native
     assert len(j["all_tasks"]) == ypk.lower().num_tasks
     assert os.path.exists(tmp_path / "kernel_0.cu")
     ypk.finalize()
+
+
+QWEN_DEMO = os.path.join(REF, "demo", "qwen3", "demo.py")
+
+
+class _Built(Exception):
+    """Raised by the patched compile(): the script has built its graph; what follows needs a GPU."""
+    def __init__(self, ypk):
+        self.ypk = ypk
+
+
+def fake_qwen3(hidden, inter, layers, hq, hkv, vocab, max_pages, page_size):
+    m = fake_llama(hidden, inter, layers, hq, hkv, vocab, max_pages, page_size)
+    for layer in m.model.layers:
+        layer.self_attn.q_norm = types.SimpleNamespace(weight=torch.ones(128, dtype=torch.bfloat16))
+        layer.self_attn.k_norm = types.SimpleNamespace(weight=torch.ones(128, dtype=torch.bfloat16))
+    m.config.eos_token_id = 151645
+    m.device = "cpu"
+    m.to = lambda *_a, **_k: m
+    cos = torch.zeros(1, 32768, 128, dtype=torch.bfloat16)
+    m.model.rotary_emb = lambda positions: (cos, cos.clone())
+    return m
+
+
+@pytest.mark.skipif(not os.path.exists(QWEN_DEMO), reason="reference tree not mounted")
+@pytest.mark.parametrize("spec", [None, "promptlookup"])
+def test_reference_qwen3_demo_builds_its_graph_unchanged(monkeypatch, tmp_path, native_lib, spec):
+    """demo/qwen3/demo.py is a flat script: it is run as __main__, unchanged, with stand-ins for
+    what is not on this machine (the Hugging Face model and tokenizer, a GPU).  It builds the
+    dense Qwen3 graph (q/k norm inside attention) and, with --spec-decode promptlookup, the
+    draft and verification operators through the reference's own dispatcher calls."""
+    import runpy
+    import transformers
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    monkeypatch.syspath_prepend(root)
+    monkeypatch.chdir(tmp_path)
+    model = fake_qwen3(4096, 12288, 2, 32, 8, 151936, 16, 4096)
+    models = types.ModuleType("models")
+    mq = types.ModuleType("models.modeling_qwen3")
+    mq.Qwen3ForCausalLM = types.SimpleNamespace(from_pretrained=lambda *a, **k: model)
+    models.modeling_qwen3 = mq
+    monkeypatch.setitem(sys.modules, "models", models)
+    monkeypatch.setitem(sys.modules, "models.modeling_qwen3", mq)
+
+    class Tok:
+        def apply_chat_template(self, messages, **kw):
+            return "prompt"
+        def __call__(self, texts, **kw):
+            enc = types.SimpleNamespace(input_ids=torch.arange(3, 24).unsqueeze(0))
+            enc.to = lambda *_a, **_k: enc
+            return enc
+    monkeypatch.setattr(transformers, "AutoTokenizer", types.SimpleNamespace(from_pretrained=lambda *a, **k: Tok()))
+
+    import yirage as yr
+    from yirage_b200.persistent_kernel import PersistentKernel
+    for fn in ("zeros", "empty", "full"):
+        real = getattr(torch, fn)
+        monkeypatch.setattr(torch, fn, (lambda real: lambda *a, **k: real(*a, **{**k, "device": "cpu"}))(real))
+    monkeypatch.setattr(torch.cuda, "set_device", lambda *_a, **_k: None)
+    monkeypatch.setattr(torch.cuda, "Event", lambda *_a, **_k: types.SimpleNamespace())
+    monkeypatch.setattr(yr, "get_configurations_from_gpu", lambda rank: (128, 80))
+    real_compile = PersistentKernel.compile
+
+    def compile_and_stop(self, **kw):
+        real_compile(self, dry_run=True)
+        raise _Built(self)
+    monkeypatch.setattr(PersistentKernel, "compile", compile_and_stop)
+    argv = [QWEN_DEMO, "--use-yirage", "--max-num-batched-requests", "2"]
+    if spec:
+        # the script's grids for the spec_length + 1 tokens of its request assume that many slots
+        argv = [QWEN_DEMO, "--use-yirage", "--max-num-batched-requests", "1", "--max-num-batched-tokens", "6",
+                "--spec-decode", spec, "--ngram-size", "3", "--spec-length", "5"]
+    monkeypatch.setattr(sys, "argv", argv)
+    try:
+        with pytest.raises(_Built) as built:
+            runpy.run_path(QWEN_DEMO, run_name="__main__")          # the file itself
+    finally:
+        torch.set_default_dtype(torch.float32)                  # the script switches it to bf16
+    ypk = built.value.ypk
+    assert ypk._is_compiled
+    g = ypk.lower()
+    kinds = [o.kind for o in g.ops]
+    layer = ["linear", "attention", "linear", "linear", "linear"]
+    head = ["ngram_partial", "ngram_global", "embed"] if spec else ["embed"]
+    tail = ["linear", "argmax_partial", "argmax_reduce"] + (["verify"] if spec else [])
+    assert kinds == head + layer * 2 + tail
+    from yirage_b200 import _native as N
+    att = [t for t in g.tasks if t.type == N.TASK_ATTENTION]
+    assert att and all(t.flags & N.F_QK_NORM for t in att)
+    assert os.path.exists(tmp_path / "task_graph_0.json")
+    ypk.finalize()

@@ -169,6 +169,9 @@ class CyTBGraph:
         dims = list(inp.dtensor.dims)
         for axis, d in enumerate(inp.input_map):
             if d >= 0:
+                if dims[d] == 1:
+                    continue        # a dimension of one entry is not cut (the reference's own
+                                    # speculative-decoding demo maps its [tokens, 1] output so)
                 if dims[d] % self.grid_dim[axis]:
                     raise ValueError(
                         f"dimension {d} ({dims[d]}) is not divisible by grid {self.grid_dim[axis]}")

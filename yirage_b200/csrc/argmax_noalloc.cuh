@@ -63,6 +63,7 @@ __global__ void __launch_bounds__(kConsumerThreads) argmax_noalloc_kernel(
   r.ptr[1] = reinterpret_cast<uint64_t>(pidx);
   r.ptr[2] = reinterpret_cast<uint64_t>(out);
   r.iarg[0] = kNoAllocParts;
+  r.iarg[4] = 0;   // partial rows are exactly that wide
   r.flags = 0;   // no cross-rank exchange: the wait context and the runtime are never touched
   WaitCtx none{nullptr, nullptr, 0, -1, false};
   argmax_reduce_task<false>(none, nullptr, r, batch, 0);

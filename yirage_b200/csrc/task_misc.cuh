@@ -77,14 +77,15 @@ __device__ __forceinline__ bool argmax_reduce_task(WaitCtx &wc, const Runtime *r
   const long long *pidx = reinterpret_cast<const long long *>(t.ptr[1]);
   long long *out = reinterpret_cast<long long *>(t.ptr[2]);
   const int nparts = t.iarg[0];
+  const int ldp = t.iarg[4] > 0 ? t.iarg[4] : nparts;   // row pitch of the partial buffers
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   LLPoll poll;
   for (int b = warp; b < batch; b += kConsumerWarps) {
     float best = -INFINITY;
     long long bidx = 0x7fffffffffffffffll;
     for (int p = lane; p < nparts; p += 32) {
-      const float v = cvt_one<false>(__ldcg(pval + size_t(b) * nparts + p));
-      const long long i = __ldcg(pidx + size_t(b) * nparts + p);
+      const float v = cvt_one<false>(__ldcg(pval + size_t(b) * ldp + p));
+      const long long i = __ldcg(pidx + size_t(b) * ldp + p);
       if (v > best || (v == best && i < bidx)) {
         best = v;
         bidx = i;

@@ -329,10 +329,10 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
       break;
     }
     case YPK_TASK_ARGMAX_REDUCE: {
-      const int nparts = a[0];
-      if (nparts <= 0) return fail(h, YPK_ERR_INVALID, "task %d: ARGMAX_REDUCE nparts", ti);
-      need[0] = uint64_t(mb) * nparts * 2; align[0] = 2; required[0] = true;
-      need[1] = uint64_t(mb) * nparts * 8; align[1] = 8; required[1] = true;
+      const int nparts = a[0], ldp = a[4] > 0 ? a[4] : a[0];
+      if (nparts <= 0 || ldp < nparts) return fail(h, YPK_ERR_INVALID, "task %d: ARGMAX_REDUCE nparts", ti);
+      need[0] = uint64_t(mb) * ldp * 2; align[0] = 2; required[0] = true;
+      need[1] = uint64_t(mb) * ldp * 8; align[1] = 8; required[1] = true;
       need[2] = uint64_t(mb) * 8; align[2] = 8; required[2] = true;
       if (in.flags & YPK_F_LL_PUSH) {   // vocabulary split over the ranks: winners are exchanged
         if (a[2] != h->cfg.world_size || a[3] != h->cfg.rank || a[2] < 2 || a[2] > 8 || a[1] < 0)

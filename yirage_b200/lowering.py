@@ -879,15 +879,12 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                 if prev.kind == "argmax_partial" and prev.t["val"] is pv:
                     nparts = prev.attrs["nparts"]
                     break
-            if nparts is None or nparts != pv.dims[1]:
-                if nparts is None:
-                    nparts = pv.dims[1]
-                elif nparts != pv.dims[1]:
-                    raise NotImplementedError(
-                        "argmax partial buffers must be exactly as wide as the task count")
+            if nparts is None:
+                nparts = pv.dims[1]
             ts = TaskSpec(N.TASK_ARGMAX_REDUCE, op_id=oi)
             ts.ptr[0], ts.ptr[1], ts.ptr[2] = (pv, 0), (pi, 0), (o, 0)
             ts.iarg[0] = nparts
+            ts.iarg[4] = pv.dims[1]      # row pitch: only the first nparts columns were written
             if op.attrs.get("exchange") and world_size > 1:
                 xbuf = scratch((world_size, max_tokens, 2), int64, "argmax_exchange", symmetric=True)
                 ts.flags |= N.F_LL_PUSH
