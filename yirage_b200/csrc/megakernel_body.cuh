@@ -50,7 +50,7 @@ __device__ __forceinline__ unsigned long long make_word(long long iter, unsigned
 // partial sums to peers).  WIDE: more than 8 tokens per iteration (16-token and tcgen05
 // LINEAR paths, TMEM).  What a configuration cannot run is not called from its variant:
 // <false, false> one GPU decode, <true, false> tensor-parallel decode, <true, true> the rest.
-template <bool TP, bool WIDE>
+template <bool TP, bool WIDE, bool MOE = false>
 __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
   extern __shared__ __align__(1024) char smem[];
   Misc *misc = reinterpret_cast<Misc *>(smem + kOffMisc);
@@ -153,7 +153,7 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
         __syncwarp();
         wc.task = ti;
         const ypk_task &t = misc->ptask;
-        if (t.type == YPK_TASK_LINEAR && (t.flags & YPK_F_MOE)) {
+        if (MOE && t.type == YPK_TASK_LINEAR && (t.flags & YPK_F_MOE)) {
           // the expert whose rows are streamed is known once the router has run
           int go = 1;
           if (lane == 0) go = moe_resolve(wc, rt, &misc->ptask, iter, true);
@@ -199,7 +199,7 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
           ok = misc->flag != 0;
         }
         if (prec) prec[2] = globaltimer();
-        if (ok && t.type == YPK_TASK_LINEAR && (t.flags & YPK_F_MOE)) {
+        if (MOE && ok && t.type == YPK_TASK_LINEAR && (t.flags & YPK_F_MOE)) {
           if (tid == 0) moe_resolve(wc, rt, &misc->ctask, iter, false);   // may turn the task into a NOP
           consumer_bar();
         }

@@ -64,6 +64,7 @@ struct ypk_handle {
   bool attn_plain = false, attn_qtiles = false;   // kinds of ATTENTION task in the graph
   int pause_below = 0;
   int spec_len = 0;                    // draft tokens per decoding request (a VERIFY task sets it)
+  bool has_moe = false;                // some LINEAR task picks its expert at run time
   bool graph_loaded = false;
   // device state
   ypk_task *d_tasks = nullptr;
@@ -197,8 +198,11 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
         if (E < 1 || slot < 0 || slot >= E || per < row0 + nrows)
           return fail(h, YPK_ERR_INVALID, "task %d: expert LINEAR slot %d of %d experts, %d rows each", ti,
                       slot, E, per);
+        if (h->cfg.world_size != 1)
+          return fail(h, YPK_ERR_UNSUPPORTED, "task %d: mixture-of-experts graphs are built for one GPU", ti);
         need[1] = rows(ldw, (E - 1) * per + row0 + nrows, K);
         need[5] = uint64_t(E + 1) * 4; align[5] = 4; required[5] = true;
+        h->has_moe = true;
       }
       if (in.flags & YPK_F_NORM) { need[3] = uint64_t(K) * 2; align[3] = 16; required[3] = true; }
       if (in.flags & YPK_F_RESIDUAL) {
@@ -614,9 +618,10 @@ int ypk_create(const ypk_config *cfg, ypk_handle **out) {
     delete h;
     return rc;
   }
-  const void *variants[3] = {(const void *)ypk_megakernel_decode,
+  const void *variants[4] = {(const void *)ypk_megakernel_decode,
                              (const void *)ypk_megakernel_decode_tp,
-                             (const void *)ypk_megakernel_wide};
+                             (const void *)ypk_megakernel_wide,
+                             (const void *)ypk_megakernel_moe};
   int per_sm = 1 << 30;
   for (const void *k : variants) {
     int n = 0;
@@ -898,6 +903,7 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
   h->max_new_tokens = h->attn_chunk = kMaxNewTokens;
   h->attn_plain = h->attn_qtiles = false;
   h->spec_len = 0;
+  h->has_moe = false;
   std::vector<ypk_task> resolved(static_cast<size_t>(num_tasks));
   std::vector<int> trig_count(size_t(num_events), 0), last_trig(size_t(num_events), -1);
   for (int i = 0; i < num_tasks; ++i) {
@@ -1187,9 +1193,10 @@ int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_
   // refuses to start otherwise instead of deadlocking.
   // The variant that carries no code this configuration cannot run (see ypk_megakernel).
   const bool wide = c.max_num_batched_tokens > kMaxBatch, tp = c.world_size > 1;
-  const void *kernel = wide ? (const void *)ypk_megakernel_wide
-                       : tp ? (const void *)ypk_megakernel_decode_tp
-                            : (const void *)ypk_megakernel_decode;
+  const void *kernel = h->has_moe ? (const void *)ypk_megakernel_moe
+                       : wide     ? (const void *)ypk_megakernel_wide
+                       : tp       ? (const void *)ypk_megakernel_decode_tp
+                                  : (const void *)ypk_megakernel_decode;
   CUDA_TRY(h, cudaLaunchCooperativeKernel(kernel, dim3(h->num_workers),
                                           dim3(kBlockThreads), args, kSmemBytes, st));
   h->stream = st;
