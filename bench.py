@@ -60,6 +60,9 @@ def parse():
                          "kernel on BASELINE configs[0..2] as a chain of independent copies")
     ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "llama3-70b"],
                     help="llama3-70b = BASELINE configs[4] (context 2048); needs --gpus >= 2")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print the per-operator device timeline of one decode iteration (rank 0) "
+                         "instead of the benchmark line; the recording itself costs ~0.3 %%")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
@@ -416,11 +419,12 @@ def run_ours(args):
     # One GPU, at most 8 token slots: the decode graph is paired with a 64-token graph over the
     # same requests and caches, which runs the prompt in the end-to-end measurement below.
     pair = None
-    use_pair = world == 1 and MT <= 8 and not args.no_e2e
+    use_pair = MT <= 8 and not args.no_e2e
     if use_pair and max_seq == gen_seq:
         pair = llama.build_prefill_decode_pair(
             shape, weights, tokens=tokens, prompt_lengths=plen, max_num_batched_requests=B,
-            max_num_pages=pages_per_req * B, page_size=page, prefill_tokens=64, decode_tokens=MT)
+            max_num_pages=pages_per_req * B, page_size=page, prefill_tokens=64, decode_tokens=MT,
+            world_size=world, rank=rank)
         ypk, st = pair.decode, pair.state
     else:
         ypk, st = llama.build_decode_kernel(
@@ -448,7 +452,8 @@ def run_ours(args):
                        max_num_pages=((gen_seq + page - 1) // page) * B, page_size=page)
             if use_pair:
                 pair2 = llama.build_prefill_decode_pair(shape, weights, prefill_tokens=64,
-                                                        decode_tokens=MT, **kw2)
+                                                        decode_tokens=MT, world_size=world,
+                                                        rank=rank, **kw2)
                 ypk2, st2 = pair2.decode, pair2.state
             else:
                 ypk2, st2 = llama.build_decode_kernel(shape, weights, max_num_batched_tokens=MT,
@@ -834,9 +839,65 @@ def run_kernel_workload(args):
         "clocks": r["clocks"], "gpu_launches": args.steps}), flush=True)
 
 
+def run_timeline(args):
+    """Per-operator device timeline of a decode iteration of the headline workload (first two
+    layers and the tail): span = from the previous operator's last task to this one's, wait /
+    exec = mean time a task waited for its dependency / ran, stage_in / stream / finish = the
+    LINEAR phases (inputs staged, weights streamed, epilogue).  Microseconds."""
+    from yirage_b200 import llama
+    dist = _dist()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=dev)
+    B = args.batch
+    MT = 8 if B <= 8 else 64
+    shape = llama.LlamaShape.llama3_8b()
+    if args.layers:
+        shape.num_hidden_layers = args.layers
+    max_seq = PROMPT_LEN + 12 * B + 64
+    g = torch.Generator().manual_seed(SEED)
+    tokens = torch.zeros(B, max_seq, dtype=torch.int64)
+    tokens[:, :PROMPT_LEN] = torch.randint(0, shape.vocab_size, (B, PROMPT_LEN), generator=g)
+    tokens = tokens.to(dev)
+    plen = torch.full((B,), PROMPT_LEN, dtype=torch.int32, device=dev)
+    weights = llama.init_weights(shape, dev, SEED, world_size=world, rank=rank)
+    prof = torch.zeros(3000 * 128, dtype=torch.int64, device=dev)
+    ypk, st = llama.build_decode_kernel(
+        shape, weights, tokens=tokens, prompt_lengths=plen, max_num_batched_requests=B,
+        max_num_batched_tokens=MT, max_num_pages=((max_seq + 63) // 64) * B, page_size=64,
+        world_size=world, rank=rank, profiler_tensor=prof)
+    ypk.set_pause_below(B)
+    ypk()
+    ypk.set_pause_below(0)
+    ypk(max_iterations=8)
+    torch.cuda.synchronize()
+    rows = ypk.profile_summary()
+    if rank == 0:
+        print(f"# llama3-8b decode, batch {B}, tp{world}, graph of {MT} token slots; microseconds")
+        print("op  kind            tasks   span   wait   exec  stage_in stream finish")
+        prev = 0.0
+        per_layer = (len(rows) - 4) // shape.num_hidden_layers if shape.num_hidden_layers else 0
+        for i, r in enumerate(rows):
+            if 1 + per_layer <= i < 1 + 2 * per_layer or i >= len(rows) - 3 or i == 0:
+                print(f"{r['op']:3d} {r['kind']:15s} {r['n']:5d} {(r['last_done'] - prev):6.1f} {r['wait']:6.1f} "
+                      f"{r['exec']:6.1f} {r.get('stage_in', 0):8.1f} {r.get('stream', 0):6.1f} {r.get('finish', 0):6.1f}")
+            prev = r["last_done"]
+        print(f"iteration: {rows[-1]['last_done']:.1f}")
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     args = parse()
-    if args.impl == "reference":
+    if args.timeline:
+        run_timeline(args)
+    elif args.impl == "reference":
         run_reference(args)
     elif args.workload != "decode":
         run_kernel_workload(args)

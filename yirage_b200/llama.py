@@ -419,9 +419,9 @@ def build_prefill_decode_pair(shape: LlamaShape, weights: Dict, *, tokens: torch
                               prompt_lengths: torch.Tensor, max_num_batched_requests: int,
                               max_num_pages: int, page_size: int, prefill_tokens: int = 64,
                               decode_tokens: int = 8, **kw) -> PrefillDecodePair:
-    """build_decode_kernel twice over shared meta tensors and caches (single GPU)."""
-    if kw.get("world_size", 1) != 1:
-        raise NotImplementedError("the prefill/decode pair is built for one GPU")
+    """build_decode_kernel twice over shared meta tensors and caches.  Under tensor
+    parallelism every rank builds both graphs in this order (compile() exchanges the arena
+    handles of each) and the ranks call run() together."""
     if not (decode_tokens <= 8 < prefill_tokens <= 64):
         raise ValueError("decode_tokens <= 8 < prefill_tokens <= 64")
     common = dict(tokens=tokens, prompt_lengths=prompt_lengths,
