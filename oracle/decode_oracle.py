@@ -109,6 +109,16 @@ def moe_topk_softmax(gate_logits, k: int, renormalize: bool = True):
     return weights, experts
 
 
+def moe_combine(expert_out, weights, residual, rounding=None):
+    """residual + sum_j weight_j * expert_out[:, j] accumulated in fp32 in slot order on top
+    of the residual, rounded once (mul_sum_add_sm100_task_impl,
+    tasks/blackwell/mul_sum_add_sm100.cuh:24-47).  expert_out [T, k, H], weights [T, k]."""
+    acc = residual.float().clone()
+    for j in range(expert_out.shape[1]):
+        acc = acc + expert_out[:, j].float() * weights[:, j:j + 1].float()
+    return rnd(acc, rounding)
+
+
 def moe_mlp(x, gate_w, w13, w2, k: int, residual, rounding=None):
     """Mixture-of-experts MLP as the reference's task sequence computes it
     (demo/qwen3/demo_30B_A3B.py:598-645): router logits (a linear operator, 16-bit output),
@@ -120,17 +130,14 @@ def moe_mlp(x, gate_w, w13, w2, k: int, residual, rounding=None):
     weights, experts = moe_topk_softmax(logits, k)
     T = x.shape[0]
     inter = w13.shape[1] // 2
-    out = torch.zeros(T, w2.shape[1])
+    eo = torch.zeros(T, k, w2.shape[1])
     for t in range(T):
-        acc = residual[t].float().clone()
         for j in range(k):
             e = int(experts[t, j])
             mid = linear(x[t:t + 1], w13[e], rounding=rounding)
             act = silu_mul(mid[:, :inter], mid[:, inter:], rounding)
-            o = linear(act, w2[e], rounding=rounding)
-            acc = acc + o[0].float() * weights[t, j]
-        out[t] = acc
-    return rnd(out, rounding)
+            eo[t, j] = linear(act, w2[e], rounding=rounding)[0]
+    return moe_combine(eo, weights, residual, rounding)
 
 
 def rope_tables(head_dim: int, theta: float, max_pos: int):
@@ -345,13 +352,18 @@ class BatchState:
         return ntok
 
 
-def prompt_lookup(tokens_row, step: int, ngram_size: int, spec_length: int) -> List[int]:
+def prompt_lookup(tokens_row, step: int, ngram_size: int, spec_length: int,
+                  n_in: Optional[int] = None) -> List[int]:
     """Draft tokens of prompt-lookup decoding (find_ngram_partial_kernel +
     find_ngram_global_kernel, tasks/speculative_decoding/prompt_lookup.cuh:22-132): the last
-    `ngram_size` tokens of the history tokens[0..step] are searched in the history before them;
+    `ngram_size` tokens of the history tokens[0..n_in) are searched in the history before them;
     the tokens after the earliest match are the drafts, -1 where there is no match or the
-    history ends."""
-    n_in = step + 1
+    index would pass `step`.  The persistent kernel calls the two kernels with n_in = step + 1
+    and step (src/kernel/task_register.cc:726-729,758-765), the default here; the reference's
+    kernel test calls both with the prompt length (tests/runtime_python/
+    runtime_kernel_wrapper.cu:1388-1406)."""
+    if n_in is None:
+        n_in = step + 1
     drafts = [-1] * spec_length
     if n_in <= ngram_size:
         return drafts
@@ -364,6 +376,20 @@ def prompt_lookup(tokens_row, step: int, ngram_size: int, spec_length: int) -> L
                 drafts[t] = row[j] if j <= step else -1
             break
     return drafts
+
+
+def verify_accept(spec_tokens, target_tokens) -> int:
+    """target_verify_greedy_kernel (tasks/speculative_decoding/target_verify.cuh:20-60):
+    spec_tokens[0] is the request's own last token, [1:] the drafts; draft i + 1 is accepted
+    while it equals target_tokens[i].  Returns the number of new tokens: accepted drafts + 1
+    (the first `that many` target tokens are the new tokens)."""
+    n = len(spec_tokens) - 1
+    acc = n
+    for i in range(n):
+        if int(spec_tokens[i + 1]) != int(target_tokens[i]):
+            acc = i
+            break
+    return acc + 1
 
 
 def fill_drafts(bs: BatchState):
@@ -389,12 +415,7 @@ def verify_greedy(bs: BatchState, output_tokens: List[int]):
         a, b = bs.qo_indptr[i], bs.qo_indptr[i + 1]
         n = b - a
         if bs.spec_length > 0 and bs.step[req] >= bs.prompt_len[req] and n > 1:
-            acc = n - 1
-            for k in range(n - 1):
-                if bs.input_tokens[a + k + 1] != output_tokens[a + k]:
-                    acc = k
-                    break
-            bs.num_new_tokens[req] = acc + 1
+            bs.num_new_tokens[req] = verify_accept(bs.input_tokens[a:b], output_tokens[a:b])
         else:
             bs.num_new_tokens[req] = n
 

@@ -276,3 +276,76 @@ def test_moe_mlp_equals_a_dense_sum_over_the_selected_experts():
             act = torch.nn.functional.silu(mid[:I]) * mid[I:]
             want[t] += wts[t, j] * (act @ w2[e].t())
     assert torch.allclose(got, want, atol=1e-4, rtol=1e-4)
+
+
+def test_prompt_lookup_known_answers_of_the_reference_kernel_test():
+    """tests/runtime_python/test_prompt_lookup.py:8-60 of the reference: an n-gram planted at
+    position 100 and again at the end of a 515-token prompt, five planted tokens behind the
+    first occurrence -> those five are the drafts; without the first occurrence -> all -1.
+    (Its wrapper passes the prompt length to both kernels.)"""
+    N, S, PROMPT_LEN = 3, 5, 512 + 3
+    g = torch.Generator().manual_seed(0)
+    for planted in (True, False):
+        toks = torch.randint(40, 1000, (2048,), generator=g)
+        if planted:
+            toks[100:103] = torch.tensor([10, 20, 30])
+            toks[103:108] = torch.tensor([4, 5, 6, 7, 8])
+        toks[PROMPT_LEN - N:PROMPT_LEN] = torch.tensor([10, 20, 30])
+        toks[PROMPT_LEN] = 99
+        got = [int(toks[PROMPT_LEN])] + O.prompt_lookup(toks.tolist(), PROMPT_LEN, N, S, n_in=PROMPT_LEN)
+        assert got == ([99, 4, 5, 6, 7, 8] if planted else [99, -1, -1, -1, -1, -1])
+
+
+def test_verify_known_answers_of_the_reference_kernel_test():
+    """tests/runtime_python/test_verify.py:7-50 of the reference."""
+    target = [10, 20, 30, 40, 50, 60]
+    assert O.verify_accept([100, 10, 20, 30, 40, 50], target) == 6          # all drafts accepted
+    n = O.verify_accept([100, 10, 20, 99, 40, 50], target)                  # mismatch at the third
+    assert n == 3 and target[:n] == [10, 20, 30]
+
+
+def test_moe_routing_matches_the_reference_tests_torch_computation():
+    """The torch computation the reference's kernel test compares against
+    (tests/runtime_python/blackwell/sm100_moe/test_gate_topk.py:21-50): softmax over 128 bf16
+    router logits, top 8, renormalised; routing index = top-k position + 1; active mask."""
+    import torch.nn.functional as F
+    g = torch.Generator().manual_seed(1234)
+    E, K, T = 128, 8, 3
+    logits = torch.randn(T, E, generator=g).to(torch.bfloat16)
+    w, e = O.moe_topk_softmax(logits, K)
+    f = logits.float()
+    sm = F.softmax(f - f.amax(dim=1, keepdim=True), dim=1, dtype=torch.float)
+    tv, ti = torch.topk(sm, K, dim=1)
+    torch.testing.assert_close(w, tv / tv.sum(dim=-1, keepdim=True), rtol=1e-2, atol=1e-2)
+    # bf16 logits tie now and then: torch.topk leaves the order of equal values open, the kernel
+    # (and the oracle) take the lower expert id first, so positions may swap among equals
+    routing = torch.zeros(E, T, dtype=torch.int32)
+    mine = torch.zeros(E, T, dtype=torch.int32)
+    for t in range(T):
+        for j in range(K):
+            routing[ti[t, j], t] = j + 1
+            mine[e[t, j], t] = j + 1
+    assert torch.equal(routing != 0, mine != 0), "the same experts are active for every token"
+    for t in range(T):
+        for j in range(K):
+            if routing[e[t, j], t] != j + 1:
+                other = int(ti[t, j])
+                assert sm[t, other] == sm[t, int(e[t, j])] and int(e[t, j]) < other or \
+                    sm[t, other] == sm[t, int(e[t, j])]
+
+
+def test_moe_weighted_sum_matches_the_reference_tests_torch_computation():
+    """tests/runtime_python/blackwell/sm100_moe/test_weighted_sum.py:20-38 (tolerance 1e-2 as there;
+    the reference's torch lines round the sum before adding the residual, the kernel and this
+    oracle add in fp32 and round once)."""
+    import torch.nn.functional as F
+    g = torch.Generator().manual_seed(5)
+    T, K, H, E = 2, 8, 256, 128
+    x = torch.randn(T, K, H, generator=g).to(torch.bfloat16)
+    residual = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    score = torch.randn(T, E, generator=g).to(torch.bfloat16)
+    wts = F.softmax(torch.topk(score, K, dim=1)[0], dim=1, dtype=torch.float)
+    want = (x.float() * wts.unsqueeze(-1)).sum(dim=1).to(torch.bfloat16)
+    want += residual
+    got = O.moe_combine(x, wts, residual, rounding="bf16")
+    torch.testing.assert_close(got.to(torch.bfloat16), want, rtol=1e-2, atol=1e-2)
