@@ -58,8 +58,10 @@ def parse():
                     choices=["decode", "rmsnorm_linear", "gated_mlp", "attention"],
                     help="decode = BASELINE configs[3] (the headline); the others time one task "
                          "kernel on BASELINE configs[0..2] as a chain of independent copies")
-    ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "llama3-70b"],
-                    help="llama3-70b = BASELINE configs[4] (context 2048); needs --gpus >= 2")
+    ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "llama3-70b", "qwen3-30b-a3b"],
+                    help="llama3-70b = BASELINE configs[4] (context 2048); needs --gpus >= 2.  "
+                         "qwen3-30b-a3b = the mixture-of-experts shape of the reference's "
+                         "demo/qwen3/demo_30B_A3B.py (no BASELINE config; one GPU)")
     ap.add_argument("--timeline", action="store_true",
                     help="print the per-operator device timeline of one decode iteration (rank 0) "
                          "instead of the benchmark line; the recording itself costs ~0.3 %%")
@@ -388,13 +390,17 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     K, W, B = args.steps, max(args.warmup, 3), args.batch
     big = args.model == "llama3-70b"
-    shape = llama.LlamaShape.llama3_70b() if big else llama.LlamaShape.llama3_8b()
+    moe = args.model == "qwen3-30b-a3b"
+    shape = (llama.LlamaShape.llama3_70b() if big else llama.LlamaShape.qwen3_30b_a3b() if moe
+             else llama.LlamaShape.llama3_8b())
+    if moe and world != 1:
+        raise SystemExit("the mixture-of-experts graph is built for one GPU")
     prompt_len = 2048 if big else PROMPT_LEN
     if big and world < 2:
         raise SystemExit("llama3-70b (140 GB of weights) is a tensor-parallel configuration: --gpus 2/4/8")
     if args.layers:
         shape.num_hidden_layers = args.layers
-    extras = not args.no_extras and not args.layers and not big
+    extras = not args.no_extras and not args.layers and not big and not moe
 
     parity = tp_parity_prelude(world, rank, dev) if (world > 1 and not args.no_extras) else None
 
@@ -586,7 +592,7 @@ def run_ours(args):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{args.model} decode, batch {B}, prompt {prompt_len}, greedy "
-                               f"(BASELINE configs[{4 if big else 3}])",
+                               + ("(no BASELINE config)" if moe else f"(BASELINE configs[{4 if big else 3}])"),
                    "layers": shape.num_hidden_layers, "page_size": page,
                    "parallelism": f"tp{world}" if world > 1 else "single",
                    "l2": f"weights streamed per iteration and GPU are {wbytes / 1e9:.1f} GB, far larger than the 126 MB L2"},

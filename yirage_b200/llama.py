@@ -61,7 +61,10 @@ class LlamaShape:
         h, f = self.hidden_size, self.intermediate_size
         qkv = (self.num_attention_heads + 2 * self.num_key_value_heads) * self.head_dim * h
         o = self.num_attention_heads * self.head_dim * h
-        per_layer = (qkv + o + 3 * f * h) // world_size
+        mlp = 3 * f * h
+        if self.num_experts:     # the router and the experts one token selects
+            mlp = self.num_experts * h + self.experts_per_token * 3 * f * h
+        per_layer = (qkv + o + mlp) // world_size
         v = padded_vocab or self.vocab_size
         return 2 * (self.num_hidden_layers * per_layer + v * h)
 

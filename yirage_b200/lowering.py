@@ -944,11 +944,16 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                     raise ValueError("moe_w2 needs the moe_silu_mul before it")
                 xin = lambda a: (act, a * MT * K * 2)
                 ldx = K
-            # enough slabs per slot that one token's experts fill the machine
-            nslab = max(1, min((W + moe_state["topk"] - 1) // moe_state["topk"], (Nrows + 15) // 16))
-            per = ((Nrows + nslab - 1) // nslab + 15) // 16 * 16
+            # Enough slabs per slot that one token's experts fill the machine; the slots only
+            # a second and later token can reach get fewer, larger slabs (a task whose slot is
+            # unused still costs its fetch).
+            topk = moe_state["topk"]
+            nslab = max(1, min((W + topk - 1) // topk, (Nrows + 15) // 16))
+            nslab_far = max((Nrows + MAX_TASK_ROWS - 1) // MAX_TASK_ROWS, nslab // 4, 1)
             k = 0
             for a in range(S):
+                ns = nslab if a < topk else nslab_far
+                per = ((Nrows + ns - 1) // ns + 15) // 16 * 16
                 for r0 in range(0, Nrows, per):
                     ts = TaskSpec(N.TASK_LINEAR, flags=N.F_MOE, op_id=oi)
                     ts.ptr[0], ts.ptr[1], ts.ptr[2] = xin(a), (w, 0), (out_buf, a * MT * Nrows * 2)
