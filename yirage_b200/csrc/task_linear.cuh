@@ -115,11 +115,22 @@ __device__ __forceinline__ void linear_splitk_finish(const LinearArgs &a, Misc *
   const int tid = threadIdx.x;
   const bool norm = (a.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT)) != 0;
   const size_t slot = size_t(a.ws_tok) * size_t(a.ws_ld);
+  // four neighbouring rows at a time where the workspace rows allow 16-byte accesses
+  const bool vec = ((a.nrows | a.ws_ld | a.row0) & 3) == 0;
   if constexpr (STORE_OWN) {
     float *mine = a.ws + size_t(a.split) * slot;
-    for (int idx = tid; idx < a.nrows * B; idx += kConsumerThreads) {
-      const int b = idx / a.nrows, r = idx - b * a.nrows;
-      __stcg(mine + size_t(b0 + b) * a.ws_ld + a.row0 + r, accs(r, b));
+    if (vec) {
+      const int nq = a.nrows >> 2;
+      for (int idx = tid; idx < nq * B; idx += kConsumerThreads) {
+        const int b = idx / nq, r = (idx - b * nq) * 4;
+        __stcg(reinterpret_cast<float4 *>(mine + size_t(b0 + b) * a.ws_ld + a.row0 + r),
+               make_float4(accs(r, b), accs(r + 1, b), accs(r + 2, b), accs(r + 3, b)));
+      }
+    } else {
+      for (int idx = tid; idx < a.nrows * B; idx += kConsumerThreads) {
+        const int b = idx / a.nrows, r = idx - b * a.nrows;
+        __stcg(mine + size_t(b0 + b) * a.ws_ld + a.row0 + r, accs(r, b));
+      }
     }
   }
   // partial sums of squares: [block][split][token]
@@ -151,7 +162,59 @@ __device__ __forceinline__ void linear_splitk_finish(const LinearArgs &a, Misc *
     return s;
   };
   uint16_t *out = reinterpret_cast<uint16_t *>(a.out);
-  if (a.flags & YPK_F_SILU_MUL) {
+  if (vec) {
+    // sums of four neighbouring rows: one 16-byte load per split
+    const int nq = a.nrows >> 2;
+    const bool silu = (a.flags & YPK_F_SILU_MUL) != 0, res = (a.flags & YPK_F_RESIDUAL) != 0;
+    for (int idx = tid; idx < nq * B; idx += kConsumerThreads) {
+      const int b = idx / nq, r = (idx - b * nq) * 4;
+      float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int sp = 0; sp < a.nsplit; ++sp) {
+        const float4 p = __ldcg(reinterpret_cast<const float4 *>(
+            a.ws + size_t(sp) * slot + size_t(b0 + b) * a.ws_ld + a.row0 + r));
+        t4.x += p.x; t4.y += p.y; t4.z += p.z; t4.w += p.w;
+      }
+      float v[4] = {t4.x, t4.y, t4.z, t4.w};
+      if (norm) {
+        const float rn = misc->rnorm_umma[b];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] *= rn;
+      }
+      uint16_t *orow = out + size_t(b0 + b) * a.ldout;
+      if (silu) {
+        // a granule of 2 gate + 2 up rows -> 2 outputs
+        const int col = a.out_col0 + ((a.row0 + r) >> 1);
+        const uint32_t o = uint32_t(cvt_out<F16>(silu_mul_ref(v[0], v[2]))) |
+                           (uint32_t(cvt_out<F16>(silu_mul_ref(v[1], v[3]))) << 16);
+        if ((col & 1) == 0) {
+          *reinterpret_cast<uint32_t *>(orow + col) = o;
+        } else {
+          orow[col] = uint16_t(o);
+          orow[col + 1] = uint16_t(o >> 16);
+        }
+      } else {
+        const int col = a.out_col0 + a.row0 + r;
+        const uint16_t *rrow = reinterpret_cast<const uint16_t *>(a.res) + size_t(b0 + b) * a.ldres;
+        if ((col & 3) == 0 && (!res || (a.ldres & 3) == 0) && (a.ldout & 3) == 0) {
+          if (res) {
+            const uint2 rv = __ldcg(reinterpret_cast<const uint2 *>(rrow + col));
+            const float2 f0 = unpack2(cvt_pair<F16>(rv.x)), f1 = unpack2(cvt_pair<F16>(rv.y));
+            v[0] += f0.x; v[1] += f0.y; v[2] += f1.x; v[3] += f1.y;
+          }
+          *reinterpret_cast<uint2 *>(orow + col) =
+              make_uint2(uint32_t(cvt_out<F16>(v[0])) | (uint32_t(cvt_out<F16>(v[1])) << 16),
+                         uint32_t(cvt_out<F16>(v[2])) | (uint32_t(cvt_out<F16>(v[3])) << 16));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float o = v[i];
+            if (res) o += cvt_one<F16>(__ldcg(rrow + col + i));
+            orow[col + i] = cvt_out<F16>(o);
+          }
+        }
+      }
+    }
+  } else if (a.flags & YPK_F_SILU_MUL) {
     const int ngr = a.nrows >> 2;   // granules of 2 gate + 2 up rows -> 2 outputs
     for (int idx = tid; idx < ngr * B; idx += kConsumerThreads) {
       const int b = idx / ngr, g = idx - b * ngr;
@@ -873,12 +936,24 @@ __device__ __forceinline__ void linear_epilogue_quads(const LinearArgs &a, const
     } else {
       const int col = a.out_col0 + a.row0 + r;
       const uint16_t *rrow = reinterpret_cast<const uint16_t *>(a.res) + size_t(b0 + b) * a.ldres;
+      const bool res = (a.flags & YPK_F_RESIDUAL) != 0;
+      if (r + 4 <= a.nrows && (col & 3) == 0 && (a.ldout & 3) == 0 && (!res || (a.ldres & 3) == 0)) {
+        if (res) {
+          const uint2 rv = __ldcg(reinterpret_cast<const uint2 *>(rrow + col));
+          const float2 f0 = unpack2(cvt_pair<F16>(rv.x)), f1 = unpack2(cvt_pair<F16>(rv.y));
+          v[0] += f0.x; v[1] += f0.y; v[2] += f1.x; v[3] += f1.y;
+        }
+        *reinterpret_cast<uint2 *>(orow + col) =
+            make_uint2(uint32_t(cvt_out<F16>(v[0])) | (uint32_t(cvt_out<F16>(v[1])) << 16),
+                       uint32_t(cvt_out<F16>(v[2])) | (uint32_t(cvt_out<F16>(v[3])) << 16));
+      } else {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        if (r + i < a.nrows) {
-          float o = v[i];
-          if (a.flags & YPK_F_RESIDUAL) o += cvt_one<F16>(__ldcg(rrow + col + i));
-          orow[col + i] = cvt_out<F16>(o);
+        for (int i = 0; i < 4; ++i) {
+          if (r + i < a.nrows) {
+            float o = v[i];
+            if (res) o += cvt_one<F16>(__ldcg(rrow + col + i));
+            orow[col + i] = cvt_out<F16>(o);
+          }
         }
       }
     }

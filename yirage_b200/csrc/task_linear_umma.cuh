@@ -189,6 +189,23 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
+// 32 columns per thread in one instruction (one wait for four 8-column groups)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, "
+      "%13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
 __device__ __forceinline__ void tcgen05_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
@@ -340,126 +357,50 @@ __device__ __forceinline__ void linear_consume_umma_group(WaitCtx &wc, char *sme
   const int ncol8 = Npad >> 3;
   const int gmid = (ncol8 + 1) >> 1;
   const int g0 = chalf == 0 ? 0 : gmid, g1 = chalf == 0 ? gmid : ncol8;
-  if (!wc.failed && B <= 32) {
-    // Few tokens: only the warps of the first one or two lane quarters can reach them (a warp
-    // reads its own quarter of the TMEM lanes), 16 threads each.  They move the accumulator
-    // to shared memory (the token ring is idle by now) and all 256 threads run the epilogue
-    // from there.
-    const int pitch = Npad + 4;                   // floats; rows stay 16-byte aligned
-    float *acc_s = reinterpret_cast<float *>(smem + kOffXs);   // [B][pitch] <= 32 x 260 x 4 B
-    if (lq * 16 < B) {                            // warp-uniform
-      for (int g = g0; g < g1; g += 2) {
-        if (g + 1 < g1) {
-          float v[16];
-          tmem_ld16(tmem + (uint32_t(lq * 32) << 16) + uint32_t(g * 8), v);
-          if (live) {
-            float4 *dst = reinterpret_cast<float4 *>(acc_s + tok * pitch + g * 8);
+  // The accumulator goes to shared memory (the token ring is idle by now), 32 tokens at a time:
+  // a warp reads its own quarter of the TMEM lanes, whose lower 16 lanes hold 16 tokens, so
+  // the two quarters of a half are read by four warps of 16 live threads; all 256 threads
+  // then run the epilogue (or leave the partial sums of a K range) from there.
+  const int pitch = Npad + 4;                   // floats; rows stay 16-byte aligned
+  float *acc_s = reinterpret_cast<float *>(smem + kOffXs);   // [32][pitch] <= 32 x 260 x 4 B
+  for (int half = 0; half * 32 < B && !wc.failed; ++half) {
+    if ((lq >> 1) == half && lq * 16 < B) {     // warp-uniform
+      float *dst_row = acc_s + ((lq & 1) * 16 + lane) * pitch;
+      int g = g0;
+      for (; g + 4 <= g1; g += 4) {
+        float v[32];
+        tmem_ld32(tmem + (uint32_t(lq * 32) << 16) + uint32_t(g * 8), v);
+        if (live) {
+          float4 *dst = reinterpret_cast<float4 *>(dst_row + g * 8);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-          }
-        } else {
-          float v[8];
-          tmem_ld8(tmem + (uint32_t(lq * 32) << 16) + uint32_t(g * 8), v);
-          if (live) {
-            float4 *dst = reinterpret_cast<float4 *>(acc_s + tok * pitch + g * 8);
-            dst[0] = make_float4(v[0], v[1], v[2], v[3]);
-            dst[1] = make_float4(v[4], v[5], v[6], v[7]);
-          }
+          for (int i = 0; i < 8; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        }
+      }
+      for (; g < g1; ++g) {
+        float v[8];
+        tmem_ld8(tmem + (uint32_t(lq * 32) << 16) + uint32_t(g * 8), v);
+        if (live) {
+          float4 *dst = reinterpret_cast<float4 *>(dst_row + g * 8);
+          dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+          dst[1] = make_float4(v[4], v[5], v[6], v[7]);
         }
       }
     }
     tcgen05_before_sync();
     consumer_bar();
+    const int bh = b0 + half * 32, Bh = min(32, B - half * 32);
     auto acc = [&](int r, int b) { return acc_s[b * pitch + r]; };
     if (a.nsplit > 1) {
-      linear_splitk_finish<F16, true>(a, misc, b0, B, ssum, acc);
+      linear_splitk_finish<F16, true>(a, misc, bh, Bh, ssum, acc);
     } else {
-      linear_epilogue_quads<F16>(a, misc, b0, B, false, acc);
+      linear_epilogue_quads<F16>(a, misc, bh, Bh, false, acc);
     }
-    return;
+    consumer_bar();   // the staging area is reused by the next half (and by the next task)
   }
-  if (!wc.failed) {
-    if (a.nsplit > 1) {
-      // partial sums of this K range -> the block's workspace slot, [token][row]
-      float *mine = a.ws + size_t(a.split) * size_t(a.ws_tok) * size_t(a.ws_ld);
-      for (int g = g0; g < g1; ++g) {
-        float v[8];
-        tmem_ld8(tmem + (uint32_t(lq * 32) << 16) + uint32_t(g * 8), v);
-        if (live) {
-          float *dst = mine + size_t(b0 + tok) * a.ws_ld + a.row0 + g * 8;
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            if (g * 8 + i < a.nrows) __stcg(dst + i, v[i]);
-        }
-      }
-    } else {
-      const float rn = (norm && live) ? ssum[tok] : 1.f;
-      uint16_t *orow = reinterpret_cast<uint16_t *>(a.out) + size_t(b0 + (live ? tok : 0)) * a.ldout;
-      const uint16_t *rrow =
-          reinterpret_cast<const uint16_t *>(a.res) + size_t(b0 + (live ? tok : 0)) * a.ldres;
-      for (int g = g0; g < g1; ++g) {
-        float v[8];
-        tmem_ld8(tmem + (uint32_t(lq * 32) << 16) + uint32_t(g * 8), v);
-        if (!live) continue;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] *= rn;
-        const int r = g * 8;                       // first row of the group inside the block
-        if (silu) {
-          // rows come as 2 gate + 2 up: {g0 g1 u0 u1 g2 g3 u2 u3} -> 4 outputs
-          const int col = a.out_col0 + ((a.row0 + r) >> 1);
-          const uint16_t o[4] = {
-              cvt_out<F16>(silu_mul_ref(v[0], v[2])), cvt_out<F16>(silu_mul_ref(v[1], v[3])),
-              cvt_out<F16>(silu_mul_ref(v[4], v[6])), cvt_out<F16>(silu_mul_ref(v[5], v[7]))};
-          const int nout = min(4, (a.nrows - r) >> 1);
-          if (nout == 4 && (col & 3) == 0) {
-            *reinterpret_cast<uint2 *>(orow + col) =
-                make_uint2(uint32_t(o[0]) | (uint32_t(o[1]) << 16), uint32_t(o[2]) | (uint32_t(o[3]) << 16));
-          } else {
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              if (i < nout) orow[col + i] = o[i];
-          }
-        } else {
-          const int col = a.out_col0 + a.row0 + r;
-          const int nout = min(8, a.nrows - r);
-          const bool res = (a.flags & YPK_F_RESIDUAL) != 0;
-          if (nout == 8 && (col & 7) == 0) {
-            if (res) {
-              const uint4 rv = __ldcg(reinterpret_cast<const uint4 *>(rrow + col));
-              const uint32_t rp[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float2 f = unpack2(cvt_pair<F16>(rp[i]));
-                v[2 * i] += f.x;
-                v[2 * i + 1] += f.y;
-              }
-            }
-            uint32_t o[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              o[i] = uint32_t(cvt_out<F16>(v[2 * i])) | (uint32_t(cvt_out<F16>(v[2 * i + 1])) << 16);
-            *reinterpret_cast<uint4 *>(orow + col) = make_uint4(o[0], o[1], o[2], o[3]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              if (i < nout) {
-                float val = v[i];
-                if (res) val += cvt_one<F16>(__ldcg(rrow + col + i));
-                orow[col + i] = cvt_out<F16>(val);
-              }
-            }
-          }
-        }
-      }
-    }
-  }
+  (void)silu;
+  (void)ncol8;
   // the next group's first MMA overwrites the accumulators: order these reads before it
   tcgen05_before_sync();
-  if (a.nsplit > 1 && !wc.failed) {
-    consumer_bar();
-    // own partials are in the workspace already: the finish only needs the arrival protocol
-    linear_splitk_finish<F16, false>(a, misc, b0, B, ssum, [](int, int) { return 0.f; });
-  }
 }
 
 __device__ __forceinline__ void linear_consume_umma(WaitCtx &wc, char *smem, Misc *misc,
