@@ -643,7 +643,8 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
             hidden = table.dims[1]
             if hidden % 8:
                 raise ValueError("embedding width must be a multiple of 8")
-            ntask = max(1, min(8, hidden // 1024))
+            # a few tasks at decode sizes; many tokens per iteration spread the copy wider
+            ntask = max(1, min(8, hidden // 1024)) if max_tokens <= 8 else max(1, min(32, W, hidden // 128))
             cols = hidden // ntask // 8 * 8
             c = 0
             for k in range(ntask):
