@@ -862,7 +862,8 @@ def run_timeline(args):
         dist.init_process_group("nccl", device_id=dev)
     B = args.batch
     MT = 8 if B <= 8 else 64
-    shape = llama.LlamaShape.llama3_8b()
+    shape = (llama.LlamaShape.qwen3_30b_a3b() if args.model == "qwen3-30b-a3b"
+             else llama.LlamaShape.llama3_8b())
     if args.layers:
         shape.num_hidden_layers = args.layers
     max_seq = PROMPT_LEN + 12 * B + 64
@@ -884,7 +885,7 @@ def run_timeline(args):
     torch.cuda.synchronize()
     rows = ypk.profile_summary()
     if rank == 0:
-        print(f"# llama3-8b decode, batch {B}, tp{world}, graph of {MT} token slots; microseconds")
+        print(f"# {args.model} decode, batch {B}, tp{world}, graph of {MT} token slots; microseconds")
         print("op  kind            tasks   span   wait   exec  stage_in stream finish")
         prev = 0.0
         per_layer = (len(rows) - 4) // shape.num_hidden_layers if shape.num_hidden_layers else 0
