@@ -949,7 +949,7 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
             # a second and later token can reach get fewer, larger slabs (a task whose slot is
             # unused still costs its fetch).
             topk = moe_state["topk"]
-            nslab = max(1, min((W + topk - 1) // topk, (Nrows + 15) // 16))
+            nslab = max(1, min(W // topk, (Nrows + 15) // 16))     # one token's pairs: at most one per worker
             nslab_far = max((Nrows + MAX_TASK_ROWS - 1) // MAX_TASK_ROWS, nslab // 4, 1)
             k = 0
             for a in range(S):
