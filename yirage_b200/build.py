@@ -1,11 +1,12 @@
 """Ahead-of-time build of the native library (sm_100a only, in-tree).
 
 `python -m yirage_b200.build` compiles every csrc/*.cu into yirage_b200/libypk.so with nvcc:
-the host side of the C ABI (ypk_abi.cu), the kernels (megakernel.cu) and one translation unit
-per task runner (run_*.cu), as relocatable device code linked at the end, so that each
-runner's register allocation depends on its own source only.  There is no per-model JIT:
-shapes travel in the task table at run time, unlike the reference which runs nvcc for every
-graph (python/yirage/persistent_kernel.py:1138-1318).
+the host side of the C ABI (ypk_abi.cu) and one translation unit per kernel variant
+(megakernel_decode.cu, megakernel_decode_tp.cu, megakernel_wide.cu, megakernel_moe.cu), each
+of which includes the task runners (runners.cuh) and so owns its copies of them; relocatable
+device code linked at the end.  There is no per-model JIT: shapes travel in the task table at
+run time, unlike the reference which runs nvcc for every graph
+(python/yirage/persistent_kernel.py:1138-1318).
 """
 import os
 import shutil
