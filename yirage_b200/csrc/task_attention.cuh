@@ -331,15 +331,20 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
   return r;
 }
 
+// [mt0, mt1): the 16-token blocks of the tile this warp takes (several warps can share a tile).
+// The blocks are taken one at a time in a loop that is NOT unrolled, each with its own step of
+// the running softmax: a task runs this code once, from a cold instruction cache, and the
+// time of the 64-token form unrolled was fetching instructions, not executing them.
 template <bool SWZ>
 __device__ __forceinline__ void attn_tile_mma_t(const char *qsm, const char *ksm, char *vsm,
                                                 int ntok, bool causal, int G, int lane,
-                                                AttnAccT &acc) {
+                                                AttnAccT &acc, int mt0 = 0, int mt1 = kKvTile / 16) {
   const float qscale = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
-  const int nk16 = (ntok + 15) >> 4;       // 16-token blocks with at least one valid token
+  const int nk16 = min(mt1, (ntok + 15) >> 4);   // end of the blocks with at least one valid token
   if (ntok < nk16 * 16) {
     // P is zero for the padding tokens of the last block, but 0 * (stale Inf/NaN) would
-    // poison the output: clear those V rows (see attn_tile_mma).
+    // poison the output: clear those V rows (see attn_tile_mma).  (Only the warp that takes
+    // the tile's last valid block gets here.)
     for (int i = lane; i < (nk16 * 16 - ntok) * (kHeadDim / 8); i += 32) {
       const int row = ntok + i / (kHeadDim / 8), c = i % (kHeadDim / 8);
       char *dst = SWZ ? vsm + (c >> 3) * kKvBoxBytes + row * 128 + (c & 7) * 16
@@ -355,13 +360,13 @@ __device__ __forceinline__ void attn_tile_mma_t(const char *qsm, const char *ksm
 #pragma unroll
   for (int p = 0; p < kHeadDim / 32; ++p)
     ldmatrix_x4(qf[p], qsm + sw * kKPitch + (p * 32 + (lane >> 3) * 8) * 2);
+  const int q0 = (lane & 3) * 2;
 
-  float st[kKvTile / 16][4];
-#pragma unroll
-  for (int mt = 0; mt < kKvTile / 16; ++mt) st[mt][0] = st[mt][1] = st[mt][2] = st[mt][3] = 0.f;
-#pragma unroll
-  for (int mt = 0; mt < kKvTile / 16; ++mt) {
-    if (mt < nk16) {
+#pragma unroll 1
+  for (int mt = mt0; mt < nk16; ++mt) {
+    // S^T block = K[16 tokens] Q^T
+    float st[4] = {0.f, 0.f, 0.f, 0.f};
+    {
       const int row = mt * 16 + ((lane >> 3) & 1) * 8 + sw;   // token of this lane's ldmatrix row
 #pragma unroll
       for (int half = 0; half < 2; ++half) {                   // 64 head dims at a time
@@ -378,62 +383,51 @@ __device__ __forceinline__ void attn_tile_mma_t(const char *qsm, const char *ksm
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int ks = half * 4 + j;                         // 16-dim step
-          mma_16816<false>(st[mt], kf[j], qf[ks >> 1][(ks & 1) * 2], qf[ks >> 1][(ks & 1) * 2 + 1]);
+          mma_16816<false>(st, kf[j], qf[ks >> 1][(ks & 1) * 2], qf[ks >> 1][(ks & 1) * 2 + 1]);
         }
       }
     }
-  }
-  // scale, mask, column max (a column = one query row)
-  const int q0 = (lane & 3) * 2;
-  float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-  for (int mt = 0; mt < kKvTile / 16; ++mt) {
+    // scale, mask, column max (a column = one query row)
+    float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int tok = mt * 16 + (lane >> 2) + ((e & 2) ? 8 : 0);
       const int tq = (q0 + (e & 1)) / G;
-      const bool vis = mt < nk16 && tok < ntok && (!causal || tok <= tq);
-      st[mt][e] = vis ? st[mt][e] * qscale : -INFINITY;
-      mx[e & 1] = fmaxf(mx[e & 1], st[mt][e]);
+      const bool vis = tok < ntok && (!causal || tok <= tq);
+      st[e] = vis ? st[e] * qscale : -INFINITY;
+      mx[e & 1] = fmaxf(mx[e & 1], st[e]);
     }
-  }
-  float corr[2];
+    float corr[2];
 #pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 4));
-    mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 8));
-    mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 16));
-    const float m_new = fmaxf(acc.m[j], mx[j]);
-    const float base = m_new == -INFINITY ? 0.f : m_new;   // nothing seen yet: exponent base 0
-    corr[j] = exp2f(acc.m[j] - base);
-    acc.m[j] = m_new;
-    mx[j] = base;
-    acc.l[j] *= corr[j];
-  }
-  // p = exp2(s - m), rounded to bf16, transposed into B fragments of the second product
-  uint32_t pb[kKvTile / 16][2];
-#pragma unroll
-  for (int mt = 0; mt < kKvTile / 16; ++mt) {
+    for (int j = 0; j < 2; ++j) {
+      mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 4));
+      mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 8));
+      mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 16));
+      const float m_new = fmaxf(acc.m[j], mx[j]);
+      const float base = m_new == -INFINITY ? 0.f : m_new;   // nothing seen yet: exponent base 0
+      corr[j] = exp2f(acc.m[j] - base);
+      acc.m[j] = m_new;
+      mx[j] = base;
+      acc.l[j] *= corr[j];
+    }
+    // p = exp2(s - m), rounded to bf16, transposed into the B fragment of the second product
     float pv[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) pv[e] = exp2f(st[mt][e] - mx[e & 1]);
+    for (int e = 0; e < 4; ++e) pv[e] = exp2f(st[e] - mx[e & 1]);
     acc.l[0] += pv[0] + pv[2];
     acc.l[1] += pv[1] + pv[3];
-    pb[mt][0] = movmatrix_trans(pack_bf16(pv[0], pv[1]));   // tokens mt*16 + 0..7
-    pb[mt][1] = movmatrix_trans(pack_bf16(pv[2], pv[3]));   // tokens mt*16 + 8..15
-  }
+    const uint32_t pb0 = movmatrix_trans(pack_bf16(pv[0], pv[1]));   // tokens mt*16 + 0..7
+    const uint32_t pb1 = movmatrix_trans(pack_bf16(pv[2], pv[3]));   // tokens mt*16 + 8..15
 #pragma unroll
-  for (int md = 0; md < kHeadDim / 16; ++md) {
-    acc.o[md][0] *= corr[0];
-    acc.o[md][1] *= corr[1];
-    acc.o[md][2] *= corr[0];
-    acc.o[md][3] *= corr[1];
-  }
-  // O^T += V^T P^T: V rows are the k dimension of an A operand, so they come transposed
-#pragma unroll
-  for (int kk = 0; kk < kKvTile / 16; ++kk) {
-    if (kk < nk16) {
-      const int row = kk * 16 + sw + ((lane >> 4) & 1) * 8;
+    for (int md = 0; md < kHeadDim / 16; ++md) {
+      acc.o[md][0] *= corr[0];
+      acc.o[md][1] *= corr[1];
+      acc.o[md][2] *= corr[0];
+      acc.o[md][3] *= corr[1];
+    }
+    // O^T += V^T P^T: V rows are the k dimension of an A operand, so they come transposed
+    {
+      const int row = mt * 16 + sw + ((lane >> 4) & 1) * 8;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t vf[4][4];
@@ -447,7 +441,7 @@ __device__ __forceinline__ void attn_tile_mma_t(const char *qsm, const char *ksm
           }
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) mma_16816<false>(acc.o[half * 4 + j], vf[j], pb[kk][0], pb[kk][1]);
+        for (int j = 0; j < 4; ++j) mma_16816<false>(acc.o[half * 4 + j], vf[j], pb0, pb1);
       }
     }
   }
@@ -520,10 +514,7 @@ static __device__ __noinline__ QkPair qk_norm_chunk(uint4 pk, uint4 ov, const ui
 
 // Rotate-half RoPE of 8 neighbouring head dims: `pk` the values at dims d0.., `ov` their
 // partners 64 dims away, cos / sin rows of [positions][128] 16-bit values.
-__device__ __forceinline__ uint4 rope_chunk(uint4 pk, uint4 ov, const uint16_t *cosp,
-                                            const uint16_t *sinp, int pos_t, int d0) {
-  const uint4 cv = __ldcg(reinterpret_cast<const uint4 *>(cosp + size_t(pos_t) * kHeadDim + d0));
-  const uint4 sv = __ldcg(reinterpret_cast<const uint4 *>(sinp + size_t(pos_t) * kHeadDim + d0));
+__device__ __forceinline__ uint4 rope_chunk(uint4 pk, uint4 ov, uint4 cv, uint4 sv, int d0) {
   const uint32_t pv[4] = {pk.x, pk.y, pk.z, pk.w}, po[4] = {ov.x, ov.y, ov.z, ov.w},
                  pc[4] = {cv.x, cv.y, cv.z, cv.w}, ps[4] = {sv.x, sv.y, sv.z, sv.w};
   uint32_t o[4];
@@ -606,6 +597,13 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
     // the page of the new token (k and v only): asked for ahead of the values it goes with
     int page = 0;
     if (hh >= G) page = __ldcg(rt.kv_indices + s.kv0 + pos_t / rt.page_size);
+    // the cos / sin row of the position is asked for ahead of the values as well: it is a
+    // new row every iteration (a trip to HBM for the first task that touches it)
+    uint4 cv = make_uint4(0u, 0u, 0u, 0u), sv = cv;
+    if (rot) {
+      cv = __ldcg(reinterpret_cast<const uint4 *>(cosp + size_t(pos_t) * kHeadDim + d0));
+      sv = __ldcg(reinterpret_cast<const uint4 *>(sinp + size_t(pos_t) * kHeadDim + d0));
+    }
     uint4 pk, ov = make_uint4(0u, 0u, 0u, 0u);
     if (ll_in) {
       // 8 dims = four words; the rotate-half partner's four with them, polled together
@@ -638,7 +636,7 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
       pk = n.pk;
       ov = n.ov;
     }
-    if (rot) pk = rope_chunk(pk, ov, cosp, sinp, pos_t, d0);
+    if (rot) pk = rope_chunk(pk, ov, cv, sv, d0);
     if (hh < G) {
       *reinterpret_cast<uint4 *>(qsm + (tk * G + hh) * kKPitch + d0 * 2) = pk;
     } else {
@@ -674,7 +672,10 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
           pk = n.pk;
           ov = n.ov;
         }
-        if (rot) pk = rope_chunk(pk, ov, cosp, sinp, pos_t, d0);
+        if (rot) {
+          pk = rope_chunk(pk, ov, __ldcg(reinterpret_cast<const uint4 *>(cosp + size_t(pos_t) * kHeadDim + d0)),
+                          __ldcg(reinterpret_cast<const uint4 *>(sinp + size_t(pos_t) * kHeadDim + d0)), d0);
+        }
         *reinterpret_cast<uint4 *>((hh == G ? knew : vnew) + tk * kKPitch + d0 * 2) = pk;
       }
     }
@@ -693,16 +694,27 @@ __device__ __forceinline__ void attention_consume_impl(WaitCtx &wc, char *smem, 
 
   // Every warp passes every stage (so that ring positions stay in step) but computes only
   // on the tiles it owns; the others are released as soon as they have landed.
+  // Decode form: a split of few tiles lets 2 or 4 warps share a tile, 32 or 16 tokens each (a
+  // tile costs a warp about 2 us, and the states of all eight warps are merged anyway); the
+  // last warp stays free for the new tokens.
+  int parts = 1;
+  if constexpr (DECODE) {
+    const int free_slots = nslots - (s.handles_new ? 1 : 0), ntile = s.tile1 - s.tile0;
+    parts = ntile * 4 <= free_slots ? 4 : (ntile * 2 <= free_slots ? 2 : 1);
+  }
   for (int tile = s.tile0; tile < s.tile1; ++tile) {
     const int ntok = min(kKvTile, s.cached - tile * kKvTile);
     const bool got = wait_mbar(wc, &misc->full_bar[pos.slot], pos.phase);
-    if (got && (tile - s.tile0) % nslots == slot) {
-      char *stage = smem + kOffRing + pos.slot * kStageBytes;
-      if constexpr (DECODE) {
-        attn_tile_mma_t<true>(qsm, stage, stage + kVOffset, ntok, false, G, lane, acc);
-      } else {
+    char *stage = smem + kOffRing + pos.slot * kStageBytes;
+    if constexpr (DECODE) {
+      const int u0 = (tile - s.tile0) * parts;       // parts > 1: every unit has a warp of its own
+      const bool mine = parts > 1 ? (slot >= u0 && slot < u0 + parts) : (u0 % nslots == slot);
+      const int per = (kKvTile / 16) / parts, b0 = parts > 1 ? (slot - u0) * per : 0;
+      if (got && mine && b0 * 16 < ntok)
+        attn_tile_mma_t<true>(qsm, stage, stage + kVOffset, ntok, false, G, lane, acc, b0, b0 + per);
+    } else {
+      if (got && (tile - s.tile0) % nslots == slot)
         attn_tile_mma<true>(qsm, stage, stage + kVOffset, ntok, false, G, mt * 16, lane, acc);
-      }
     }
     __syncwarp();
     if (lane == 0 && got) mbar_arrive(&misc->empty_bar[pos.slot]);

@@ -43,6 +43,13 @@ MAX_NEW_KEYS = 64            # kMaxNewKeys: new tokens of a request per iteratio
 MAX_ATTN_ROWS = 32           # kMaxAttnRows
 ATTN_ROW_FLOATS = HEAD_DIM + 4   # kAttnRowFloats in task_attention.cuh
 MAX_SPLITS = 16
+# A worker that ran an attention task of a graph of at most 8 tokens reaches the next LINEAR
+# operator late (the task takes 6-8 us from the moment q/k/v are there, the other workers spend
+# that time polling with their activations half staged): it is given this many weight bytes
+# less of that operator, ~3.4 us of streaming (measured on Llama-3-8B decode: 2.99 -> 2.96 ms
+# per token between 100 and 220 KB).
+ATTN_LOAD_BYTES = 160 * 1024
+ATTN_TILES_PER_SPLIT = 4     # kAttnTilesPerSplit in device_common.cuh
 ALLREDUCE_TILE = 256          # columns per ALLREDUCE task
 SILU_GRAN = 2                # kSiluGran: fused gate/up rows come as 2 gate + 2 up
 # Widest tensor handed over as flagged words.  A reader polls 2x the bytes with four 16-byte
@@ -796,7 +803,9 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
             qtiles = max_tokens > MAX_NEW_TOKENS
             chunk = min(MAX_NEW_TOKENS, MAX_ATTN_ROWS // G)
             nslots = query_tile_slots(max_requests, max_tokens, chunk) if qtiles else max_requests
-            nsplit = max(1, min(W // max(1, nslots * hkv), max_tiles, MAX_SPLITS))
+            # the device never activates more than ceil(tiles / ATTN_TILES_PER_SPLIT) splits
+            nsplit = max(1, min(W // max(1, nslots * hkv), -(-max_tiles // ATTN_TILES_PER_SPLIT),
+                                MAX_SPLITS))
             max_rows = min(G * MAX_NEW_TOKENS, MAX_ATTN_ROWS)
             if nsplit > 1:
                 # partial rows travel as 8-byte flagged words {fp32 bits, tag}: two floats each
@@ -851,6 +860,8 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                             ts.iarg[12] = device_tag(pid)
                         # splits of one (request, head) go to different workers
                         ts.worker = (rr + k) % W
+                        if max_tokens <= 8:
+                            loads[ts.worker] += ATTN_LOAD_BYTES
                         tasks.append(ts)
                         k += 1
             rr += k
