@@ -616,7 +616,8 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
         return ll_bufs[key]
 
     W = num_workers
-    loads = [0.0] * W
+    loads = [0.0] * W      # weight bytes per worker so far
+    late = [0.0] * W       # allowance of the next LINEAR operator (graphs of at most 8 tokens)
     tasks: List[TaskSpec] = []
     shuffles: List[dict] = []
     internal: List[DTensor] = []
@@ -752,7 +753,23 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                 _link(tasks, first, ev, plan, ops, oi, prev_event, prev_count)
                 prev_event, prev_count = ev, count
                 continue
-            counts = level_partition(units, unit_bytes, loads)
+            if max_tokens <= 8:
+                # Every operator of such a graph waits for all of its predecessor: what counts
+                # is the largest slab of THIS operator, so the rows are levelled per operator
+                # (against the allowance of workers that come late from an attention task);
+                # the bytes a worker has streamed so far only decide who gets the larger of
+                # two otherwise equal slabs.
+                counts = level_partition(units, unit_bytes, late)
+                groups: Dict[float, List[int]] = {}
+                for wk in range(W):
+                    groups.setdefault(late[wk], []).append(wk)
+                for members in groups.values():
+                    sizes = sorted((counts[wk] for wk in members), reverse=True)
+                    for wk, c in zip(sorted(members, key=lambda w_: loads[w_]), sizes):
+                        counts[wk] = c
+                late = [0.0] * W
+            else:
+                counts = level_partition(units, unit_bytes, loads)
             r = 0
             for wk in range(W):
                 nrows = counts[wk] * gran
@@ -861,7 +878,7 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                         # splits of one (request, head) go to different workers
                         ts.worker = (rr + k) % W
                         if max_tokens <= 8:
-                            loads[ts.worker] += ATTN_LOAD_BYTES
+                            late[ts.worker] += ATTN_LOAD_BYTES
                         tasks.append(ts)
                         k += 1
             rr += k
