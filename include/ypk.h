@@ -115,6 +115,18 @@ enum ypk_task_type {
                                   iarg[11] = E, iarg[12] = weight rows per expert; the task is
                                   skipped when the slot is beyond the count.  Plain 16-bit rows
                                   in and out (no flagged words, no norm, no split along K) */
+#define YPK_F_NORM_OUT 0x8000u  /* LINEAR of a graph of more than 8 tokens whose result feeds an
+                                  RMSNorm: besides its rows out[b, n] the task writes them
+                                  multiplied by that norm's weight, xg[b, n] = out[b, n] * g[n]
+                                  (ptr_aux = xg, same pitch as out; ptr[3] = g), and the sum of
+                                  out[b, n]^2 over its rows into ptr[6] = fp32
+                                  [row blocks][pitch] at block iarg[12] & 0xffff (pitch =
+                                  iarg[12] >> 16 tokens).  Tensor-core path only.             */
+#define YPK_F_NORM_PRE 0x10000u /* LINEAR that reads such an xg: the RMS factor of token b,
+                                  rsqrt(sum over the iarg[12] & 0xffff blocks of ptr[3] =
+                                  fp32 [blocks][pitch] / K + eps), is applied to the dot
+                                  products.  Together the two flags replace a RMSNORM operator
+                                  between two LINEAR operators.  Tensor-core path only.       */
 #define YPK_F_TRIG_WIDE 0x2000u /* publish trig_event only in iterations of more than two tokens:
                                   its only waiters carry YPK_F_LL_OPT (they count those
                                   iterations, not all, towards the event's value)          */
@@ -215,7 +227,7 @@ typedef struct ypk_task {
   uint64_t ptr[YPK_TASK_NPTR];
   int32_t iarg[YPK_TASK_NINT];
   float farg[YPK_TASK_NFLT];
-  int32_t reserved[2];
+  uint64_t ptr_aux;    /* ninth pointer operand (YPK_F_NORM_OUT), else 0       */
 } ypk_task;
 
 /* Serving parameters; the meta pointers are the ten caller-owned tensors the

@@ -92,3 +92,44 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(N, "LIB_PATH", str(tmp_path / "libypk.so"))
     with pytest.raises(ImportError):
         N.load()
+
+
+def test_carried_norm_operands_are_validated(native_lib):
+    """YPK_F_NORM_OUT / YPK_F_NORM_PRE: the ninth operand, the sums-of-squares buffer and the
+    graph size are checked when the graph is loaded."""
+    h = host_handle(max_tokens=64)
+    h.alloc(0, "x", 64 * 256 * 2)
+    h.alloc(1, "w", 64 * 256 * 2)
+    h.alloc(2, "out", 64 * 64 * 2)
+    h.alloc(3, "g", 64 * 2)
+    h.alloc(4, "ss", 64 * 4)
+    h.alloc(5, "xg", 64 * 64 * 2)
+
+    def task(flags, g=True, ssbuf=True, aux=True, ss=0 | (64 << 16)):
+        t = linear_task(K=256, nrows=64, flags=flags)
+        t.iarg[12] = ss
+        if g:
+            t.ptr[3] = N.ref(3)
+        if ssbuf:
+            t.ptr[6] = N.ref(4)
+        if aux:
+            t.ptr_aux = N.ref(5)
+        return t
+
+    h.load_graph([task(N.F_NORM_OUT)], 1, [0], [0, 1])
+    for bad, msg in ((task(N.F_NORM_OUT, aux=False), "operand 8 is required"),
+                     (task(N.F_NORM_OUT, ss=0 | (8 << 16)), "sums of squares for 8 tokens"),
+                     (task(N.F_NORM_OUT, ss=1 | (64 << 16)), "reaches byte"),   # block 1 of a one-row buffer
+                     (task(0, g=False, ssbuf=False), "takes no ninth operand"),
+                     (task(N.F_NORM_OUT | N.F_NORM_PRE), "NORM_PRE and NORM_OUT"),
+                     (task(N.F_NORM_OUT | N.F_NORM), "plain 16-bit rows")):
+        with pytest.raises(N.YpkError) as e:
+            h.load_graph([bad], 1, [0], [0, 1])
+        assert msg in str(e.value), str(e.value)
+    # graphs of at most 8 tokens have no such form
+    h8 = host_handle(max_tokens=8)
+    for slot, n in ((0, 8 * 256 * 2), (1, 64 * 256 * 2), (2, 8 * 64 * 2), (3, 128), (4, 32), (5, 8 * 64 * 2)):
+        h8.alloc(slot, f"t{slot}", n)
+    with pytest.raises(N.YpkError) as e:
+        h8.load_graph([task(N.F_NORM_OUT, ss=0 | (8 << 16))], 1, [0], [0, 1])
+    assert "more than 8 tokens" in str(e.value)

@@ -609,3 +609,48 @@ def test_mixture_of_experts_graph_lowers_and_validates(native_lib):
     assert {254, 255, 260, 261} <= {t["task_type"] for t in doc["all_tasks"]}
     ypk.compile(dry_run=True)
     ypk.finalize()
+
+
+def test_norm_between_two_linears_is_carried_in_wide_graphs(monkeypatch):
+    """Graphs of more than 8 tokens: linear(+residual) -> rmsnorm -> linear loses the RMSNORM
+    operator; the producer writes the scaled rows and the sums of squares per row block, the
+    consumer applies the RMS factor (reference: a separate norm task per layer half,
+    demo/llama3/demo.py:402-470)."""
+    def wide(layers=2):
+        shape = llama.LlamaShape(hidden_size=512, intermediate_size=1024, num_hidden_layers=layers,
+                                 num_attention_heads=8, num_key_value_heads=2, vocab_size=2048)
+        w = llama.init_weights(shape, "cpu", 0)
+        return llama.build_decode_kernel(
+            shape, w, tokens=torch.zeros(2, 128, dtype=torch.int64),
+            prompt_lengths=torch.tensor([5, 7], dtype=torch.int32), max_num_batched_requests=2,
+            max_num_batched_tokens=64, max_num_pages=8, page_size=64, compile=False)[0]
+
+    monkeypatch.delenv("YPK_TENSOR_CORE", raising=False)
+    ypk = wide()
+    g = ypk.lower(148)
+    kinds = [o.kind for o in g.ops]
+    assert kinds.count("rmsnorm") == 1            # only the one behind the embedding is left
+    prods = [i for i, o in enumerate(g.ops) if o.flags & N.F_NORM_OUT]
+    cons = [i for i, o in enumerate(g.ops) if o.flags & N.F_NORM_PRE]
+    assert len(prods) == len(cons) == 4 and all(c == p + 1 for p, c in zip(prods, cons))
+    for p, c in zip(prods, cons):
+        po, co = g.ops[p], g.ops[c]
+        assert po.flags & N.F_RESIDUAL and co.t["x"] is po.t["norm_out"] and co.t["ss_in"] is po.t["ss_out"]
+        pt = [ts for ts in g.tasks if ts.op_id == p]
+        ct = [ts for ts in g.tasks if ts.op_id == c]
+        nblk = po.attrs["ss_nblk"]
+        assert {ts.iarg[12] & 0xffff for ts in pt} == set(range(nblk))
+        assert all(ts.iarg[12] >> 16 == 64 and ts.ptr_aux[0] is po.t["norm_out"] and
+                   ts.ptr[3][0] is po.t["norm_out_w"] and ts.ptr[6][0] is po.t["ss_out"] for ts in pt)
+        assert all(ts.iarg[12] == (nblk | (64 << 16)) and ts.ptr[3][0] is po.t["ss_out"] for ts in ct)
+        # the consumer waits for the producer
+        assert all(ts.dep_event == pt[0].trig_event and ts.dep_count == len(pt) for ts in ct)
+    assert set(lowering.simulate(g, 2)) == {2}
+    ypk.compile(dry_run=True)                      # the native validation accepts the operands
+
+    # the GEMV passes have no such form: with the tensor cores switched off the norm stays
+    monkeypatch.setenv("YPK_TENSOR_CORE", "never")
+    g2 = wide().lower(148)
+    assert [o.kind for o in g2.ops].count("rmsnorm") == 5
+    assert not any(o.flags & (N.F_NORM_OUT | N.F_NORM_PRE) for o in g2.ops)
+

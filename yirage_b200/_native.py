@@ -40,6 +40,7 @@ F_QTILES = 0x80
 F_MOE = 0x4000
 F_LL_IN, F_LL_RES, F_LL_OUT, F_LL_PUSH, F_LL_OPT = 0x100, 0x200, 0x400, 0x800, 0x1000
 F_TRIG_WIDE = 0x2000
+F_NORM_OUT, F_NORM_PRE = 0x8000, 0x10000
 
 NPTR, NINT, NFLT = 8, 16, 4
 
@@ -58,7 +59,7 @@ class Task(C.Structure):
         ("ptr", C.c_uint64 * NPTR),
         ("iarg", C.c_int32 * NINT),
         ("farg", C.c_float * NFLT),
-        ("reserved", C.c_int32 * 2),
+        ("ptr_aux", C.c_uint64),
     ]
 
 

@@ -52,6 +52,11 @@ struct LinearArgs {
   int x_tmap;   // tensor map of x for the tensor-core path (graphs of more than 8 tokens), or -1
   float *ws, *ws_ss;
   unsigned int *ws_cnt;
+  // RMSNorm carried across two operators (YPK_F_NORM_OUT / YPK_F_NORM_PRE): the scaled copy
+  // of the result, the sums of squares per (row block, token) and their layout
+  char *xg;
+  float *ss_io;
+  int ss_blk, ss_pitch;   // producer: its block; consumer: the number of blocks
 };
 
 __device__ __forceinline__ LinearArgs linear_args(const ypk_task &t, const Runtime *rt = nullptr,
@@ -91,12 +96,57 @@ __device__ __forceinline__ LinearArgs linear_args(const ypk_task &t, const Runti
   a.cnt_idx = t.iarg[10];           // row block's counter (the tag fields are free in wide graphs)
   a.ws = a.ws_ss = nullptr;
   a.ws_cnt = nullptr;
+  a.xg = reinterpret_cast<char *>(t.ptr_aux);
+  a.ss_io = reinterpret_cast<float *>((t.flags & YPK_F_NORM_OUT) ? t.ptr[6] : t.ptr[3]);
+  a.ss_blk = t.iarg[12] & 0xffff;
+  a.ss_pitch = t.iarg[12] >> 16;
   if (a.nsplit > 1) {
     a.ws = reinterpret_cast<float *>(t.ptr[5]);
     a.ws_ss = reinterpret_cast<float *>(t.ptr[6]);
     a.ws_cnt = reinterpret_cast<unsigned int *>(t.ptr[7]);
   }
   return a;
+}
+
+// ---- RMSNorm carried across two operators ---------------------------------------------------
+// YPK_F_NORM_OUT: four neighbouring finished values of token row `b_abs` (v, before rounding)
+// at output column `col`: stores them times the following norm's weight into xg and returns
+// the sum of their squares, both from the values as rounded for `out`.
+template <bool F16>
+__device__ __forceinline__ float norm_out_quad(const LinearArgs &a, int b_abs, int col, const float (&v)[4],
+                                               int n) {
+  const uint16_t *g = reinterpret_cast<const uint16_t *>(a.norm_w);
+  uint16_t *xrow = reinterpret_cast<uint16_t *>(a.xg) + size_t(b_abs) * a.ldout;
+  float sq = 0.f;
+  uint16_t o[4] = {0, 0, 0, 0};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (i < n) {
+      const float r = cvt_one<F16>(cvt_out<F16>(v[i]));
+      sq += r * r;
+      o[i] = cvt_out<F16>(r * cvt_one<F16>(__ldg(g + col + i)));
+    }
+  }
+  if (n == 4 && (col & 3) == 0 && (a.ldout & 3) == 0) {
+    *reinterpret_cast<uint2 *>(xrow + col) =
+        make_uint2(uint32_t(o[0]) | (uint32_t(o[1]) << 16), uint32_t(o[2]) | (uint32_t(o[3]) << 16));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (i < n) xrow[col + i] = o[i];
+  }
+  return sq;
+}
+// ... and the sums of squares of the task's rows per token: sq_s[b * nq + q] holds the share
+// of quad q; added in quad order, so the result does not depend on the thread schedule.
+__device__ __forceinline__ void norm_out_sums(const LinearArgs &a, const float *sq_s, int nq, int b0, int B) {
+  consumer_bar();
+  const int tid = threadIdx.x;
+  if (tid < B) {
+    float s = 0.f;
+    for (int q = 0; q < nq; ++q) s += sq_s[tid * nq + q];
+    __stcg(a.ss_io + size_t(a.ss_blk) * a.ss_pitch + b0 + tid, s);
+  }
 }
 
 // ---- split along K ------------------------------------------------------------------------
@@ -109,11 +159,17 @@ __device__ __forceinline__ LinearArgs linear_args(const ypk_task &t, const Runti
 // never reset: the nsplit-th, 2*nsplit-th, ... arrival is the last of its iteration.
 // `accs(r, b)` = this task's own partial for row r of the block and token b.
 // STORE_OWN false: the caller has written its partials to its slot already.
+// `sq_s`: shared scratch of B * nrows / 4 floats for YPK_F_NORM_OUT (nullptr: a path that such
+// tasks never take).  With YPK_F_NORM_PRE the caller has put the RMS factors of tokens
+// b0 .. b0 + B into misc->rnorm_umma.
 template <bool F16, bool STORE_OWN, typename AccFn>
 __device__ __forceinline__ void linear_splitk_finish(const LinearArgs &a, Misc *misc, int b0, int B,
-                                                     const float *ss_part, AccFn accs) {
+                                                     const float *ss_part, AccFn accs,
+                                                     float *sq_s = nullptr) {
   const int tid = threadIdx.x;
   const bool norm = (a.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT)) != 0;
+  const bool pre = (a.flags & YPK_F_NORM_PRE) != 0;
+  const bool nout = (a.flags & YPK_F_NORM_OUT) != 0 && sq_s != nullptr;
   const size_t slot = size_t(a.ws_tok) * size_t(a.ws_ld);
   // four neighbouring rows at a time where the workspace rows allow 16-byte accesses
   const bool vec = ((a.nrows | a.ws_ld | a.row0) & 3) == 0;
@@ -175,7 +231,7 @@ __device__ __forceinline__ void linear_splitk_finish(const LinearArgs &a, Misc *
         t4.x += p.x; t4.y += p.y; t4.z += p.z; t4.w += p.w;
       }
       float v[4] = {t4.x, t4.y, t4.z, t4.w};
-      if (norm) {
+      if (norm || pre) {
         const float rn = misc->rnorm_umma[b];
 #pragma unroll
         for (int i = 0; i < 4; ++i) v[i] *= rn;
@@ -207,20 +263,21 @@ __device__ __forceinline__ void linear_splitk_finish(const LinearArgs &a, Misc *
         } else {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            float o = v[i];
-            if (res) o += cvt_one<F16>(__ldcg(rrow + col + i));
-            orow[col + i] = cvt_out<F16>(o);
+            if (res) v[i] += cvt_one<F16>(__ldcg(rrow + col + i));
+            orow[col + i] = cvt_out<F16>(v[i]);
           }
         }
+        if (nout) sq_s[idx] = norm_out_quad<F16>(a, b0 + b, col, v, 4);
       }
     }
+    if (nout) norm_out_sums(a, sq_s, nq, b0, B);
   } else if (a.flags & YPK_F_SILU_MUL) {
     const int ngr = a.nrows >> 2;   // granules of 2 gate + 2 up rows -> 2 outputs
     for (int idx = tid; idx < ngr * B; idx += kConsumerThreads) {
       const int b = idx / ngr, g = idx - b * ngr;
       float v[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] = total(g * 4 + i, b) * (norm ? misc->rnorm_umma[b] : 1.f);
+      for (int i = 0; i < 4; ++i) v[i] = total(g * 4 + i, b) * ((norm || pre) ? misc->rnorm_umma[b] : 1.f);
       const int col = a.out_col0 + ((a.row0 + g * 4) >> 1);
       uint16_t *orow = out + size_t(b0 + b) * a.ldout;
       orow[col] = cvt_out<F16>(silu_mul_ref(v[0], v[2]));
@@ -230,7 +287,7 @@ __device__ __forceinline__ void linear_splitk_finish(const LinearArgs &a, Misc *
     for (int idx = tid; idx < a.nrows * B; idx += kConsumerThreads) {
       const int b = idx / a.nrows, r = idx - b * a.nrows;
       float v = total(r, b);
-      if (norm) v *= misc->rnorm_umma[b];
+      if (norm || pre) v *= misc->rnorm_umma[b];
       const int col = a.out_col0 + a.row0 + r;
       if (a.flags & YPK_F_RESIDUAL)
         v += cvt_one<F16>(__ldcg(reinterpret_cast<const uint16_t *>(a.res) + size_t(b0 + b) * a.ldres + col));
@@ -915,8 +972,9 @@ __device__ __forceinline__ void linear_consume_group(WaitCtx &wc, char *smem, Mi
 // factors, if any, are in misc->rnorm_umma.
 template <bool F16, typename AccFn>
 __device__ __forceinline__ void linear_epilogue_quads(const LinearArgs &a, const Misc *misc, int b0,
-                                                      int B, bool norm, AccFn acc) {
+                                                      int B, bool norm, AccFn acc, float *sq_s = nullptr) {
   const bool silu = (a.flags & YPK_F_SILU_MUL) != 0;
+  const bool nout = (a.flags & YPK_F_NORM_OUT) != 0 && sq_s != nullptr && !silu;
   const int nquads = (a.nrows + 3) >> 2;
   for (int it = threadIdx.x; it < nquads * B; it += kConsumerThreads) {
     const int b = it / nquads, r = (it - b * nquads) * 4;
@@ -950,14 +1008,15 @@ __device__ __forceinline__ void linear_epilogue_quads(const LinearArgs &a, const
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           if (r + i < a.nrows) {
-            float o = v[i];
-            if (res) o += cvt_one<F16>(__ldcg(rrow + col + i));
-            orow[col + i] = cvt_out<F16>(o);
+            if (res) v[i] += cvt_one<F16>(__ldcg(rrow + col + i));
+            orow[col + i] = cvt_out<F16>(v[i]);
           }
         }
       }
+      if (nout) sq_s[it] = norm_out_quad<F16>(a, b0 + b, col, v, min(4, a.nrows - r));
     }
   }
+  if (nout) norm_out_sums(a, sq_s, nquads, b0, B);
 }
 
 // ------------------------------------------------------------------ 16 tokens per pass

@@ -80,6 +80,8 @@ struct UmmaWalk {
 // one 16-token GEMV pass, 64 tokens 0.67 ms against 2.36 ms for four passes);
 // YPK_TENSOR_CORE=never keeps the GEMV passes.
 __device__ __forceinline__ bool linear_uses_umma(const Runtime &rt, const ypk_task &t, int batch) {
+  // a norm carried across two operators exists on this path only (the host has checked the maps)
+  if (t.flags & (YPK_F_NORM_OUT | YPK_F_NORM_PRE)) return true;
   if (batch <= 2 || t.iarg[9] < 0 || t.iarg[11] < 0 || rt.umma_policy == 2) return false;
   return (t.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT)) == 0;
 }
@@ -256,6 +258,13 @@ __device__ __forceinline__ void linear_consume_umma_group(WaitCtx &wc, char *sme
   const uint32_t tmem = misc->tmem_base;
   // sums of squares over this task's K range, turned into the RMS factors in place
   float *ssum = misc->rnorm_umma;
+  // a norm carried over from the producing operator (YPK_F_NORM_PRE) / on to the next one
+  // (YPK_F_NORM_OUT); their scratch is the part of the GEMV area this path does not use
+  const bool norm_pre = (a.flags & YPK_F_NORM_PRE) != 0;
+  float rn_reg[2] = {0.f, 0.f};
+  // (behind the accumulator staging area; the token ring, which covers it, is idle by then)
+  float *sq_s = reinterpret_cast<float *>(smem + kOffPart);     // [32 tokens][rows / 4]
+  static_assert(kUmmaMaxBatch == 64 && 32 * (kMaxAccRows / 4) * 4 <= kPartBytes, "norm scratch");
 
   if (warp == 0) {
     // ------------------------------------------------------------ MMA issuer
@@ -335,6 +344,21 @@ __device__ __forceinline__ void linear_consume_umma_group(WaitCtx &wc, char *sme
       pos.advance();   // keep the weight-ring position in step with the issuer
     }
   } else {
+    if (warp == 2 && norm_pre) {
+      // RMS factors of the group's tokens from the sums of squares the producing operator
+      // left per row block (this warp has nothing else to do while the MMAs run): lane l
+      // keeps those of tokens l and l + 32
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int t = hh * 32 + lane;
+        if (t < B) {
+          float ssum_t = 0.f;
+          for (int blk = 0; blk < a.ss_blk; ++blk)
+            ssum_t += __ldcg(a.ss_io + size_t(blk) * a.ss_pitch + b0 + t);
+          rn_reg[hh] = rsqrtf(ssum_t / float(a.K) + a.eps);
+        }
+      }
+    }
     for (int si = 0; si < walk.stages; ++si) pos.advance();
   }
   for (int u = 0; u < nkb; ++u) us.advance();
@@ -390,10 +414,12 @@ __device__ __forceinline__ void linear_consume_umma_group(WaitCtx &wc, char *sme
     consumer_bar();
     const int bh = b0 + half * 32, Bh = min(32, B - half * 32);
     auto acc = [&](int r, int b) { return acc_s[b * pitch + r]; };
+    if (norm_pre && warp == 2 && lane < Bh) misc->rnorm_umma[lane] = half == 0 ? rn_reg[0] : rn_reg[1];   // read after a barrier
     if (a.nsplit > 1) {
-      linear_splitk_finish<F16, true>(a, misc, bh, Bh, ssum, acc);
+      linear_splitk_finish<F16, true>(a, misc, bh, Bh, ssum, acc, sq_s);
     } else {
-      linear_epilogue_quads<F16>(a, misc, bh, Bh, false, acc);
+      if (norm_pre) consumer_bar();
+      linear_epilogue_quads<F16>(a, misc, bh, Bh, norm_pre, acc, sq_s);
     }
     consumer_bar();   // the staging area is reused by the next half (and by the next task)
   }

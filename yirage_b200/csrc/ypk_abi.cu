@@ -163,6 +163,7 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
   const int32_t *a = in.iarg;
   uint64_t need[YPK_TASK_NPTR] = {0}, align[YPK_TASK_NPTR] = {0};
   bool required[YPK_TASK_NPTR] = {false};
+  uint64_t need_aux = 0, align_aux = 0;   // the ninth operand (ptr_aux)
   auto rows = [](int ld, int n, int cols) -> uint64_t {  // bytes spanned by n rows of 16-bit
     return n <= 0 ? 0 : (uint64_t(n - 1) * ld + cols) * 2u;
   };
@@ -226,6 +227,31 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
         need[7] = uint64_t(cnt + 1) * ((ws_tok + 15) / 16) * 4; align[7] = 4; required[7] = true;
       } else if (klen != K) {
         return fail(h, YPK_ERR_INVALID, "task %d: a K range needs a split count", ti);
+      }
+      // RMSNorm carried across two operators (graphs of more than 8 tokens, tensor-core path)
+      if (in.flags & (YPK_F_NORM_OUT | YPK_F_NORM_PRE)) {
+        const int blk = a[12] & 0xffff, pitch = a[12] >> 16;
+        if (mb <= kMaxBatch || (in.flags & (YPK_F_NORM | YPK_F_NORM_NOWEIGHT | YPK_F_MOE | YPK_F_LL_IN |
+                                            YPK_F_LL_RES | YPK_F_LL_OUT | YPK_F_LL_PUSH | YPK_F_LL_OPT)))
+          return fail(h, YPK_ERR_UNSUPPORTED,
+                      "task %d: a norm carried across operators needs a graph of more than %d tokens and "
+                      "plain 16-bit rows", ti, kMaxBatch);
+        if (pitch < mb)
+          return fail(h, YPK_ERR_INVALID, "task %d: sums of squares for %d tokens, the graph has %d", ti,
+                      pitch, mb);
+        if (in.flags & YPK_F_NORM_OUT) {
+          if (silu || row0 % 4 || nrows % 4 || oc0 % 4 || ldo % 4)
+            return fail(h, YPK_ERR_INVALID, "task %d: NORM_OUT needs rows and columns in fours, no SILU_MUL", ti);
+          need[3] = uint64_t(ocols0 + ocols) * 2; align[3] = 2; required[3] = true;
+          need[6] = uint64_t(blk + 1) * pitch * 4; align[6] = 4; required[6] = true;
+          need_aux = rows(ldo, mb, ocols0 + ocols); align_aux = 8;
+        }
+        if (in.flags & YPK_F_NORM_PRE) {
+          if (in.flags & YPK_F_NORM_OUT)
+            return fail(h, YPK_ERR_UNSUPPORTED, "task %d: NORM_PRE and NORM_OUT on one task", ti);
+          if (blk < 1) return fail(h, YPK_ERR_INVALID, "task %d: NORM_PRE over no row blocks", ti);
+          need[3] = uint64_t(blk) * pitch * 4; align[3] = 4; required[3] = true;
+        }
       }
       // flagged-word copies: 4 bytes per value ([max_tokens][ld / 2] 8-byte words)
       const uint32_t ll = in.flags & (YPK_F_LL_IN | YPK_F_LL_RES | YPK_F_LL_OUT | YPK_F_LL_PUSH);
@@ -462,6 +488,15 @@ int check_task(ypk_handle *h, int ti, const ypk_task &in, ypk_task *out) {
       return fail(h, YPK_ERR_INVALID, "task %d (type %d): operand %d is required", ti, in.type, p);
     int rc = resolve(h, ti, p, in.ptr[p], need[p], align[p], &out->ptr[p]);
     if (rc) return rc;
+  }
+  out->ptr_aux = 0;
+  if (need_aux) {
+    if (in.ptr_aux == 0)
+      return fail(h, YPK_ERR_INVALID, "task %d (type %d): operand 8 is required", ti, in.type);
+    int rc = resolve(h, ti, 8, in.ptr_aux, need_aux, align_aux, &out->ptr_aux);
+    if (rc) return rc;
+  } else if (in.ptr_aux != 0) {
+    return fail(h, YPK_ERR_INVALID, "task %d (type %d): takes no ninth operand", ti, in.type);
   }
   if ((in.type == YPK_TASK_LINEAR && (in.flags & YPK_F_LL_PUSH)) ||
       (in.type == YPK_TASK_ARGMAX_REDUCE && (in.flags & YPK_F_LL_PUSH)) ||
@@ -989,6 +1024,14 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
       ++k;
     if (k == xkeys.size()) xkeys.push_back({t.ptr[0], K, ldx, h->cfg.max_num_batched_tokens});
     t.iarg[11] = int(keys.size() + wkeys.size() + k);
+  }
+  for (int i = 0; i < num_tasks; ++i) {
+    const ypk_task &t = resolved[size_t(i)];
+    if (t.type == YPK_TASK_LINEAR && (t.flags & (YPK_F_NORM_OUT | YPK_F_NORM_PRE)) &&
+        (!umma_possible || t.iarg[9] < 0 || t.iarg[11] < 0))
+      return fail(h, YPK_ERR_UNSUPPORTED,
+                  "task %d: a norm carried across operators exists on the tensor-core path only, "
+                  "which this task's shape or alignment rules out", i);
   }
   h->end_event = tasks[num_tasks - 1].trig_event;
   h->end_count = h->end_event >= 0 ? trig_count[size_t(h->end_event)] : 0;

@@ -93,6 +93,7 @@ class TaskSpec:
     flags: int = 0
     op_id: int = 0
     ptr: List[Optional[Tuple[DTensor, int]]] = field(default_factory=lambda: [None] * N.NPTR)
+    ptr_aux: Optional[Tuple[DTensor, int]] = None           # ninth operand (F_NORM_OUT)
     iarg: List[int] = field(default_factory=lambda: [0] * N.NINT)
     farg: List[float] = field(default_factory=lambda: [0.0] * N.NFLT)
     dep_event: int = -1
@@ -301,13 +302,13 @@ def fuse(regs: List[RegisteredTask], default_eps: float, fuse_norm: bool = True)
 
 
 # --------------------------------------------------------------------- flagged hand-off
-_OUTPUT_KEYS = {"embed": ("out",), "linear": ("out",), "attention": ("out",), "rmsnorm": ("out",),
+_OUTPUT_KEYS = {"embed": ("out",), "linear": ("out", "norm_out", "ss_out"), "attention": ("out",), "rmsnorm": ("out",),
                 "silu_mul": ("out",), "argmax_partial": ("val", "idx"), "argmax_reduce": ("out",),
                 "allreduce": ("out",), "ngram_partial": ("out",), "ngram_global": ("out",),
                 "verify": ("out",), "moe_topk": ("weights", "routing", "mask"), "moe_linear": ("out",),
                 "moe_silu_mul": ("out",), "moe_combine": ("out",)}
 # operands that are not activations produced inside the iteration
-_STATIC_KEYS = {"w", "norm_w", "table", "k_cache", "v_cache", "cos", "sin", "buf", "tokens"}
+_STATIC_KEYS = {"w", "norm_w", "norm_out_w", "table", "k_cache", "v_cache", "cos", "sin", "buf", "tokens"}
 
 
 def _op_outputs(op):
@@ -493,6 +494,76 @@ def splitk_plan(nrows: int, K: int, gran: int, W: int):
     return None
 
 
+def carry_norms(ops: List[FusedOp]) -> List[FusedOp]:
+    """Graphs of more than 8 tokens keep every RMSNorm an operator of its own (`fuse`), which
+    costs two operators per layer.  Where the norm sits between two LINEAR operators,
+    linear(+residual) -> rmsnorm -> linear, it is carried across them instead: the first
+    writes, besides its rows, the rows times the norm weight and the sums of their squares
+    per row block (F_NORM_OUT), the second reads that copy as its input and applies the RMS
+    factor to its dot products (F_NORM_PRE), the order of operations of the fused norm of
+    narrow graphs.  The RMSNORM operator disappears.  Tensor-core path only: set
+    YPK_TENSOR_CORE=never to keep the operators apart."""
+    import os
+    if os.environ.get("YPK_TENSOR_CORE", "") == "never":
+        return ops
+    out: List[FusedOp] = []
+    i, n = 0, len(ops)
+    while i < n:
+        a = ops[i]
+        nm = ops[i + 1] if i + 1 < n else None
+        b = ops[i + 2] if i + 2 < n else None
+        ok = (a.kind == "linear" and nm is not None and b is not None and nm.kind == "rmsnorm"
+              and b.kind == "linear" and not (a.flags & (N.F_SILU_MUL | N.F_NORM | N.F_NORM_NOWEIGHT | N.F_NORM_PRE))
+              and not (b.flags & (N.F_NORM | N.F_NORM_NOWEIGHT)) and nm.t["w"] is not None
+              and nm.t["x"] is a.t["out"] and b.t["x"] is nm.t["out"]
+              and a.t["w"].dims[0] % 8 == 0 and a.t["w"].dims[1] % 64 == 0
+              and a.t["out"].dims == nm.t["out"].dims and nm.t["w"].dims == (a.t["out"].dims[1],))
+        if ok:
+            # nobody else may read the normalised rows
+            readers, _ = _readers(ops, i + 1, nm.t["out"])
+            ok = readers == [(i + 2, "x")]
+        if not ok:
+            out.append(a)
+            i += 1
+            continue
+        a.flags |= N.F_NORM_OUT
+        a.t["norm_out"], a.t["norm_out_w"] = nm.t["out"], nm.t["w"]
+        a.src = list(a.src) + list(nm.src)
+        b.flags |= N.F_NORM_PRE
+        b.attrs["eps"] = nm.attrs["eps"]
+        b.attrs["norm_from"] = a
+        out.append(a)
+        i += 2          # the rmsnorm operator is dropped; b is looked at next (it may carry on)
+    return out
+
+
+def _carry_operands(op, op_tasks, splitk, flags, max_tokens, scratch, norm_bufs):
+    """Operands of a carried norm (see carry_norms) on the tasks of a LINEAR operator.  The
+    producer's row blocks are its tasks, or with a split along K the blocks its splits share;
+    every block owns a row [max_tokens] of the sums-of-squares buffer."""
+    if flags & N.F_NORM_OUT:
+        for k, ts in enumerate(op_tasks):
+            ts.iarg[12] = (ts.iarg[10] if splitk else k) | (max_tokens << 16)
+        nblk = max(ts.iarg[12] & 0xffff for ts in op_tasks) + 1
+        if nblk > 0xffff:
+            raise NotImplementedError("a carried norm over more than 65535 row blocks")
+        key = (op.t["out"].dims[1], nblk)
+        if key not in norm_bufs:
+            norm_bufs[key] = scratch((nblk * max_tokens,), float32, f"norm_ss_{key[0]}x{nblk}")
+        op.t["ss_out"] = norm_bufs[key]
+        op.attrs["ss_nblk"] = nblk
+        for ts in op_tasks:
+            ts.ptr[3] = (op.t["norm_out_w"], 0)
+            ts.ptr[6] = (op.t["ss_out"], 0)
+            ts.ptr_aux = (op.t["norm_out"], 0)
+    if flags & N.F_NORM_PRE:
+        prod = op.attrs["norm_from"]
+        op.t["ss_in"] = prod.t["ss_out"]
+        for ts in op_tasks:
+            ts.ptr[3] = (op.t["ss_in"], 0)
+            ts.iarg[12] = prod.attrs["ss_nblk"] | (max_tokens << 16)
+
+
 # --------------------------------------------------------------------------- lowering
 def _all_flagged(plan, ops, oi):
     """True if every activation operator `oi` reads arrives as flagged words."""
@@ -598,6 +669,8 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
     Where no tensor travels as flagged words the events follow the tensors
     (`tensor_dependencies`): independent operators do not wait for each other."""
     ops = fuse(regs, default_eps, fuse_norm=max_tokens <= 8)
+    if max_tokens > 8 and world_size == 1:
+        ops = carry_norms(ops)
     if handoff == "auto":
         handoff = "ll" if max_tokens <= 8 else "event"
     if handoff == "ll" and max_tokens > 8:
@@ -639,6 +712,7 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
     attn_scratch = None
     attn_tag_ids = set()
     splitk_bufs: Dict[tuple, tuple] = {}
+    norm_bufs: Dict[tuple, DTensor] = {}  # sums of squares of carried norms, by (width, blocks)
     moe_bufs: Dict[tuple, object] = {}    # scratch of the mixture-of-experts operators, by shape
     moe_state: Dict[str, object] = {}     # the routing the expert operators of a layer work under
     prev_event, prev_count = -1, 0
@@ -688,6 +762,8 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
             if "out" in ll:
                 flags |= N.F_LL_OUT | (N.F_LL_PUSH if ll["out"][2] else 0)
             gran = 2 * SILU_GRAN if silu else (2 if (flags & (N.F_LL_OUT | N.F_LL_RES)) else 1)
+            if flags & N.F_NORM_OUT:
+                gran = 4          # the carried norm is written four rows at a time
             if w.kind == "shuffled" and id(w) not in shuffled_done:
                 srcs = w.sources
                 if silu:
@@ -749,6 +825,7 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                         loads[ts.worker] += ts.weight_bytes
                         tasks.append(ts)
                         ti_local += 1
+                _carry_operands(op, tasks[first:], True, flags, max_tokens, scratch, norm_bufs)
                 count = len(tasks) - first
                 _link(tasks, first, ev, plan, ops, oi, prev_event, prev_count)
                 prev_event, prev_count = ev, count
@@ -801,6 +878,7 @@ def lower(regs: List[RegisteredTask], *, num_workers: int, max_tokens: int, max_
                     r += take
                     nrows -= take
             assert r == Nrows
+            _carry_operands(op, tasks[first:], False, flags, max_tokens, scratch, norm_bufs)
         elif op.kind == "attention":
             qkv, kc, vc, o = op.t["qkv"], op.t["k_cache"], op.t["v_cache"], op.t["out"]
             hq, hkv = op.attrs["num_q_heads"], op.attrs["num_kv_heads"]
@@ -1323,6 +1401,8 @@ def to_json(g: LoweredGraph) -> str:
                 inputs.append(o)
         inputs += [operand(p) for p in ts.logical_in]
         outputs += [operand(p) for p in ts.logical_out]
+        if ts.ptr_aux is not None:     # the rows times the weight of the norm that follows
+            outputs.append(operand(ts.ptr_aux))
         tasks.append({
             "task_type": ref_task_type(ts),
             "variant_id": 0,

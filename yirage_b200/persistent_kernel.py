@@ -561,6 +561,7 @@ class PersistentKernel:
             t.dep_event, t.dep_count, t.trig_event = ts.dep_event, ts.dep_count, ts.trig_event
             for i, p in enumerate(ts.ptr):
                 t.ptr[i] = N.ref(p[0].guid, p[1]) if p is not None else 0
+            t.ptr_aux = N.ref(ts.ptr_aux[0].guid, ts.ptr_aux[1]) if ts.ptr_aux is not None else 0
             for i, v in enumerate(ts.iarg):
                 t.iarg[i] = v
             for i, v in enumerate(ts.farg):
