@@ -139,6 +139,17 @@ def test_long_prompts_take_up_to_64_tokens_per_iteration():
     assert st.iterations < 150 // 8 + 170
 
 
+def test_carried_norm_with_row_slab_producers(monkeypatch):
+    """Graphs of more than 8 tokens carry the norm between two LINEAR operators across them.
+    With K = 256 the producers (o_proj, down) are plain row slabs, one task per row block,
+    instead of row blocks x K ranges as in the other 64-token cases."""
+    shape = llama.LlamaShape(hidden_size=256, intermediate_size=256, num_hidden_layers=3,
+                             num_attention_heads=2, num_key_value_heads=1, vocab_size=2000,
+                             rms_norm_eps=1e-5)
+    monkeypatch.delenv("YPK_TENSOR_CORE", raising=False)
+    run_generation([70, 23, 9], 90, max_requests=2, max_tokens=64, max_pages=6, shape=shape)
+
+
 def test_prefill_graph_hands_over_to_decode_graph():
     """Prompts on a 64-token graph, decoding on an 8-token graph over the same requests, pages
     and caches (ypk_set_pause_below / ypk_adopt_batch), against one oracle run whose batcher
