@@ -113,8 +113,8 @@ __device__ __forceinline__ LinearArgs linear_args(const ypk_task &t, const Runti
 // at output column `col`: stores them times the following norm's weight into xg and returns
 // the sum of their squares, both from the values as rounded for `out`.
 template <bool F16>
-__device__ __forceinline__ float norm_out_quad(const LinearArgs &a, int b_abs, int col, const float (&v)[4],
-                                               int n) {
+static __device__ __noinline__ float norm_out_quad(const LinearArgs &a, int b_abs, int col, const float (&v)[4],
+                                            int n) {
   const uint16_t *g = reinterpret_cast<const uint16_t *>(a.norm_w);
   uint16_t *xrow = reinterpret_cast<uint16_t *>(a.xg) + size_t(b_abs) * a.ldout;
   float sq = 0.f;
@@ -139,7 +139,7 @@ __device__ __forceinline__ float norm_out_quad(const LinearArgs &a, int b_abs, i
 }
 // ... and the sums of squares of the task's rows per token: sq_s[b * nq + q] holds the share
 // of quad q; added in quad order, so the result does not depend on the thread schedule.
-__device__ __forceinline__ void norm_out_sums(const LinearArgs &a, const float *sq_s, int nq, int b0, int B) {
+static __device__ __noinline__ void norm_out_sums(const LinearArgs &a, const float *sq_s, int nq, int b0, int B) {
   consumer_bar();
   const int tid = threadIdx.x;
   if (tid < B) {
@@ -192,19 +192,22 @@ __device__ __forceinline__ void linear_splitk_finish(const LinearArgs &a, Misc *
   // partial sums of squares: [block][split][token]
   float *ssb = a.ws_ss + (size_t(a.cnt_idx) * a.nsplit) * a.ws_tok;
   if (norm && tid < B) __stcg(ssb + size_t(a.split) * a.ws_tok + b0 + tid, ss_part[tid]);
-  __threadfence();
+  // The barrier orders every thread's stores before thread 0, whose gpu-scope release on the
+  // counter is cumulative over them; the last arriver's acquire, passed on by the next
+  // barrier, lets its threads read the other splits' slots.  (A __threadfence() by all 256
+  // threads here cost about a microsecond per task.)
   consumer_bar();
   if (tid == 0) {
     // one counter per (row block, group of 16 tokens): a task passes here once per group
     unsigned int *ctr = a.ws_cnt + size_t(a.cnt_idx) * size_t((a.ws_tok + 15) >> 4) + (b0 >> 4);
-    const unsigned old = atomicAdd(ctr, 1u);
+    unsigned old;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(ctr) : "memory");
     misc->flag = ((old + 1u) % unsigned(a.nsplit)) == 0u ? 1 : 0;
   }
   consumer_bar();
   const bool last = misc->flag != 0;
   consumer_bar();   // flag is read by everybody before anyone can rewrite it
   if (!last) return;
-  __threadfence();
   if (norm && tid < B) {
     float s = 0.f;
     for (int sp = 0; sp < a.nsplit; ++sp) s += __ldcg(ssb + size_t(sp) * a.ws_tok + b0 + tid);

@@ -261,9 +261,6 @@ __device__ __forceinline__ void linear_consume_umma_group(WaitCtx &wc, char *sme
   // a norm carried over from the producing operator (YPK_F_NORM_PRE) / on to the next one
   // (YPK_F_NORM_OUT); their scratch is the part of the GEMV area this path does not use
   const bool norm_pre = (a.flags & YPK_F_NORM_PRE) != 0;
-  float rn_reg[2] = {0.f, 0.f};
-  // (behind the accumulator staging area; the token ring, which covers it, is idle by then)
-  float *sq_s = reinterpret_cast<float *>(smem + kOffPart);     // [32 tokens][rows / 4]
   static_assert(kUmmaMaxBatch == 64 && 32 * (kMaxAccRows / 4) * 4 <= kPartBytes, "norm scratch");
 
   if (warp == 0) {
@@ -346,17 +343,14 @@ __device__ __forceinline__ void linear_consume_umma_group(WaitCtx &wc, char *sme
   } else {
     if (warp == 2 && norm_pre) {
       // RMS factors of the group's tokens from the sums of squares the producing operator
-      // left per row block (this warp has nothing else to do while the MMAs run): lane l
-      // keeps those of tokens l and l + 32
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        const int t = hh * 32 + lane;
-        if (t < B) {
-          float ssum_t = 0.f;
-          for (int blk = 0; blk < a.ss_blk; ++blk)
-            ssum_t += __ldcg(a.ss_io + size_t(blk) * a.ss_pitch + b0 + t);
-          rn_reg[hh] = rsqrtf(ssum_t / float(a.K) + a.eps);
-        }
+      // left per row block (this warp has nothing else to do while the MMAs run).
+      // (misc->rnorm_umma has a slot per token of the group; nothing else uses it in a task
+      // with a carried norm until the epilogue, which reads the slots of its 32 tokens at 0..31)
+      for (int t = lane; t < B; t += 32) {
+        float ssum_t = 0.f;
+        for (int blk = 0; blk < a.ss_blk; ++blk)
+          ssum_t += __ldcg(a.ss_io + size_t(blk) * a.ss_pitch + b0 + t);
+        misc->rnorm_umma[t] = rsqrtf(ssum_t / float(a.K) + a.eps);
       }
     }
     for (int si = 0; si < walk.stages; ++si) pos.advance();
@@ -414,7 +408,10 @@ __device__ __forceinline__ void linear_consume_umma_group(WaitCtx &wc, char *sme
     consumer_bar();
     const int bh = b0 + half * 32, Bh = min(32, B - half * 32);
     auto acc = [&](int r, int b) { return acc_s[b * pitch + r]; };
-    if (norm_pre && warp == 2 && lane < Bh) misc->rnorm_umma[lane] = half == 0 ? rn_reg[0] : rn_reg[1];   // read after a barrier
+    // scratch of a norm carried on (behind the accumulator staging area; the token ring, which
+    // covers it, is idle by now)
+    float *sq_s = reinterpret_cast<float *>(smem + kOffPart);     // [32 tokens][rows / 4]
+    if (norm_pre && half == 1 && tid < Bh) misc->rnorm_umma[tid] = misc->rnorm_umma[32 + tid];   // read after a barrier
     if (a.nsplit > 1) {
       linear_splitk_finish<F16, true>(a, misc, bh, Bh, ssum, acc, sq_s);
     } else {
