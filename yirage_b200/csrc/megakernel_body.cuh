@@ -213,11 +213,16 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
               wc.failed = r.failed;
               ++umma_done;
             } else if (t.flags & (YPK_F_LL_IN | YPK_F_LL_RES | YPK_F_LL_OUT)) {
-              const TaskRet r =
-                  batch > 2 ? run_linear<true, TP, true>(&rt, misc, smem, worker, ti, wc.failed, batch, iter, pos)
-                            : run_linear<true, TP, false>(&rt, misc, smem, worker, ti, wc.failed, batch, iter, pos);
-              pos = r.pos;
-              wc.failed = r.failed;
+              if (!WIDE && batch <= 2) {
+                // the one- and two-token form of the flagged-word path is part of this loop:
+                // a call costs about a microsecond per task (registers saved and restored
+                // through local memory, which misses the small L1 left beside the ring)
+                linear_consume_groups<true, TP, false>(wc, smem, misc, rt, misc->ctask, batch, iter, pos);
+              } else {
+                const TaskRet r = run_linear<true, TP, true>(&rt, misc, smem, worker, ti, wc.failed, batch, iter, pos);
+                pos = r.pos;
+                wc.failed = r.failed;
+              }
             } else if (WIDE && (batch > kMaxBatch || t.iarg[15] != 0)) {
               // more than 8 tokens, or a task that covers a K range only (the 16-token pass
               // is the GEMV path that can leave partial sums for the split along K)

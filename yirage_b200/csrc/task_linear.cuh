@@ -109,14 +109,16 @@ __device__ __forceinline__ LinearArgs linear_args(const ypk_task &t, const Runti
 }
 
 // ---- RMSNorm carried across two operators ---------------------------------------------------
-// YPK_F_NORM_OUT: four neighbouring finished values of token row `b_abs` (v, before rounding)
-// at output column `col`: stores them times the following norm's weight into xg and returns
-// the sum of their squares, both from the values as rounded for `out`.
+// YPK_F_NORM_OUT: up to four neighbouring finished values (before rounding) of a token row at
+// output column `col`: stores them times the following norm's weight `g` into the row `xrow`
+// of the scaled copy and returns the sum of their squares, both from the values as rounded
+// for `out`.
+// (Out of line and with plain arguments: taking the LinearArgs by reference would give the
+// struct an address, i.e. a home in local memory, for every LINEAR task.)
 template <bool F16>
-static __device__ __noinline__ float norm_out_quad(const LinearArgs &a, int b_abs, int col, const float (&v)[4],
-                                            int n) {
-  const uint16_t *g = reinterpret_cast<const uint16_t *>(a.norm_w);
-  uint16_t *xrow = reinterpret_cast<uint16_t *>(a.xg) + size_t(b_abs) * a.ldout;
+static __device__ __noinline__ float norm_out_quad(const uint16_t *g, uint16_t *xrow, int col, float v0,
+                                                   float v1, float v2, float v3, int n, bool vec) {
+  const float v[4] = {v0, v1, v2, v3};
   float sq = 0.f;
   uint16_t o[4] = {0, 0, 0, 0};
 #pragma unroll
@@ -127,7 +129,7 @@ static __device__ __noinline__ float norm_out_quad(const LinearArgs &a, int b_ab
       o[i] = cvt_out<F16>(r * cvt_one<F16>(__ldg(g + col + i)));
     }
   }
-  if (n == 4 && (col & 3) == 0 && (a.ldout & 3) == 0) {
+  if (vec && n == 4) {
     *reinterpret_cast<uint2 *>(xrow + col) =
         make_uint2(uint32_t(o[0]) | (uint32_t(o[1]) << 16), uint32_t(o[2]) | (uint32_t(o[3]) << 16));
   } else {
@@ -139,13 +141,14 @@ static __device__ __noinline__ float norm_out_quad(const LinearArgs &a, int b_ab
 }
 // ... and the sums of squares of the task's rows per token: sq_s[b * nq + q] holds the share
 // of quad q; added in quad order, so the result does not depend on the thread schedule.
-static __device__ __noinline__ void norm_out_sums(const LinearArgs &a, const float *sq_s, int nq, int b0, int B) {
+// `dst` = the block's row of the sums-of-squares buffer at the first token.
+static __device__ __noinline__ void norm_out_sums(float *dst, const float *sq_s, int nq, int B) {
   consumer_bar();
   const int tid = threadIdx.x;
   if (tid < B) {
     float s = 0.f;
     for (int q = 0; q < nq; ++q) s += sq_s[tid * nq + q];
-    __stcg(a.ss_io + size_t(a.ss_blk) * a.ss_pitch + b0 + tid, s);
+    __stcg(dst + tid, s);
   }
 }
 
@@ -270,10 +273,13 @@ __device__ __forceinline__ void linear_splitk_finish(const LinearArgs &a, Misc *
             orow[col + i] = cvt_out<F16>(v[i]);
           }
         }
-        if (nout) sq_s[idx] = norm_out_quad<F16>(a, b0 + b, col, v, 4);
+        if (nout)
+          sq_s[idx] = norm_out_quad<F16>(reinterpret_cast<const uint16_t *>(a.norm_w),
+                                         reinterpret_cast<uint16_t *>(a.xg) + size_t(b0 + b) * a.ldout, col,
+                                         v[0], v[1], v[2], v[3], 4, (col & 3) == 0 && (a.ldout & 3) == 0);
       }
     }
-    if (nout) norm_out_sums(a, sq_s, nq, b0, B);
+    if (nout) norm_out_sums(a.ss_io + size_t(a.ss_blk) * a.ss_pitch + b0, sq_s, nq, B);
   } else if (a.flags & YPK_F_SILU_MUL) {
     const int ngr = a.nrows >> 2;   // granules of 2 gate + 2 up rows -> 2 outputs
     for (int idx = tid; idx < ngr * B; idx += kConsumerThreads) {
@@ -1016,10 +1022,14 @@ __device__ __forceinline__ void linear_epilogue_quads(const LinearArgs &a, const
           }
         }
       }
-      if (nout) sq_s[it] = norm_out_quad<F16>(a, b0 + b, col, v, min(4, a.nrows - r));
+      if (nout)
+        sq_s[it] = norm_out_quad<F16>(reinterpret_cast<const uint16_t *>(a.norm_w),
+                                      reinterpret_cast<uint16_t *>(a.xg) + size_t(b0 + b) * a.ldout, col,
+                                      v[0], v[1], v[2], v[3], min(4, a.nrows - r),
+                                      (col & 3) == 0 && (a.ldout & 3) == 0);
     }
   }
-  if (nout) norm_out_sums(a, sq_s, nquads, b0, B);
+  if (nout) norm_out_sums(a.ss_io + size_t(a.ss_blk) * a.ss_pitch + b0, sq_s, nquads, B);
 }
 
 // ------------------------------------------------------------------ 16 tokens per pass
