@@ -237,9 +237,14 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
               wc.failed = r.failed;
             }
           } else if (t.type == YPK_TASK_ATTENTION) {
-            const TaskRet r = run_attention(&rt, misc, smem, worker, ti, wc.failed, iter, pos);
-            pos = r.pos;
-            wc.failed = r.failed;
+            if (!WIDE) {
+              // (one call level less: the two forms of the task are functions of their own)
+              attention_consume(wc, smem, misc, rt, misc->ctask, iter, pos);
+            } else {
+              const TaskRet r = run_attention(&rt, misc, smem, worker, ti, wc.failed, iter, pos);
+              pos = r.pos;
+              wc.failed = r.failed;
+            }
           } else {
             wc.failed = run_small<TP>(&rt, misc, worker, ti, wc.failed, batch, iter);
           }
