@@ -94,6 +94,10 @@ struct __align__(16) Misc {
   unsigned long long xempty_bar[kUmmaUnits];
   unsigned long long acc_bar;    // every MMA of the current task has completed
   float rnorm_umma[kUmmaMaxBatch];
+  // arguments of the MMA issuer of the tensor-core LINEAR path (umma_issue), which is a
+  // function of its own and takes them from here rather than through the call stack
+  int is_nrows, is_nkb, is_task, is_failed;
+  uint32_t is_slot, is_phase, is_xslot, is_xphase;
   alignas(16) ypk_task ctask;    // consumer copy of the current task (copied 16 bytes at a time)
   alignas(16) ypk_task ptask;                // producer copy of the current task
 };

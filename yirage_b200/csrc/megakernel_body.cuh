@@ -206,11 +206,7 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
         if (ok) {
           if (t.type == YPK_TASK_LINEAR) {
             if (WIDE && linear_uses_umma(rt, t, batch)) {
-              const TaskRetU r =
-                  run_linear_umma(&rt, misc, smem, worker, ti, wc.failed, batch, pos, ustate);
-              pos = r.pos;
-              ustate = r.us;
-              wc.failed = r.failed;
+              linear_consume_umma(wc, smem, misc, misc->ctask, batch, pos, ustate);
               ++umma_done;
             } else if (t.flags & (YPK_F_LL_IN | YPK_F_LL_RES | YPK_F_LL_OUT)) {
               if (!WIDE && batch <= 2) {

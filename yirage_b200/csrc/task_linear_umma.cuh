@@ -241,6 +241,91 @@ __device__ __forceinline__ void cp_async_wait_pending(int n) {
   }
 }
 
+// ------------------------------------------------------------------ MMA issuer
+// Warp 0 of the consumers, all lanes; lane 0 issues.  Walks the weight stages of the task
+// from ring position (is_slot, is_phase) and the token units from (is_xslot, is_xphase) of
+// the misc area; leaves the warp's failure state in is_failed.
+template <bool F16>
+static __device__ __noinline__ void umma_issue(const Runtime *rt, Misc *misc, char *smem) {
+  const int lane = threadIdx.x & 31;
+  const int nrows = misc->is_nrows, nkb = misc->is_nkb;
+  uint32_t slot = misc->is_slot, phase = misc->is_phase, xslot = misc->is_xslot, xphase = misc->is_xphase;
+  WaitCtx wc{rt, misc, int(blockIdx.x), misc->is_task, misc->is_failed != 0};
+  if (nrows <= 0 || nrows > kMaxAccRows || nkb <= 0 || slot >= uint32_t(kStages) ||
+      xslot >= uint32_t(kUmmaUnits)) {
+    // arguments that cannot be: give up (recorded as event -9) instead of walking them
+    if (lane == 0) {
+      raise_abort(wc, YPK_ERR_STATE, -9);
+      misc->is_failed = 1;
+    }
+    __syncwarp();
+    return;
+  }
+  char *xring = smem + kOffXs;
+  const int nbox = umma_nbox(nrows), kbs = umma_stage_kblocks(nrows);
+  const UmmaWalk walk(nkb, kbs, wc.worker);
+  const uint32_t tmem = misc->tmem_base;
+  const uint32_t idesc = umma_instr_desc(kUmmaMaxBatch, umma_npad(nrows), F16);
+  // timeline (lane 0): [4] first stage in hand, [5] last MMA issued, [6] / [7] ns spent
+  // waiting for weight stages / token units
+  unsigned long long *prec = lane == 0 ? misc->prof_rec : nullptr;
+  unsigned long long wait_w = 0, wait_x = 0;
+  for (int si = 0; si < walk.stages; ++si) {
+    int kb, nk;
+    walk.stage(si, kb, nk);
+    unsigned long long tw = prec ? globaltimer() : 0ull;
+    const bool got = wait_mbar(wc, &misc->full_bar[slot], phase);
+    if (prec) {
+      const unsigned long long now = globaltimer();
+      wait_w += now - tw;
+      if (si == 0) prec[4] = now;
+    }
+    const char *stage = smem + kOffRing + slot * kStageBytes;
+    for (int j = 0; j < nk; ++j) {
+      tw = prec ? globaltimer() : 0ull;
+      const bool xok = wait_mbar(wc, &misc->xfull_bar[xslot], xphase);
+      if (prec) wait_x += globaltimer() - tw;
+      if (got && xok && lane == 0) {
+        tcgen05_after_sync();
+        const unsigned long long ad = umma_smem_desc(xring + xslot * kUmmaUnitBytes, 1024);
+        const unsigned long long bd = umma_smem_desc(stage + j * nbox * kUmmaBoxBytes, 1024);
+#pragma unroll
+        for (int kk = 0; kk < kUmmaKBlock / 16; ++kk) {
+          // 32 bytes per 16-wide K step inside the swizzle atom: +2 in the address field
+          umma_f16(tmem, ad + 2ull * kk, bd + 2ull * kk, idesc, si + j > 0 || kk > 0);
+        }
+        umma_commit(&misc->xempty_bar[xslot]);   // the unit is free once these have run
+      }
+      if (++xslot == uint32_t(kUmmaUnits)) {
+        xslot = 0;
+        xphase ^= 1u;
+      }
+    }
+    if (got && !wc.failed) {
+      if (lane == 0) {
+        umma_commit(&misc->empty_bar[slot]);   // one of the 8 arrivals, when the MMAs are done
+      } else if (lane < kConsumerWarps) {
+        mbar_arrive(&misc->empty_bar[slot]);   // the other 7: nothing else reads the stage
+      }
+    }
+    __syncwarp();
+    if (++slot == uint32_t(kStages)) {
+      slot = 0;
+      phase ^= 1u;
+    }
+  }
+  if (lane == 0) {
+    umma_commit(&misc->acc_bar);
+    misc->is_failed = wc.failed ? 1 : 0;
+  }
+  if (prec) {
+    prec[5] = globaltimer();
+    prec[6] = wait_w;
+    prec[7] = wait_x;
+  }
+  __syncwarp();
+}
+
 // ------------------------------------------------------------------ consumer
 // One group of B <= 64 tokens starting at token b0.
 template <bool F16>
@@ -265,57 +350,25 @@ __device__ __forceinline__ void linear_consume_umma_group(WaitCtx &wc, char *sme
 
   if (warp == 0) {
     // ------------------------------------------------------------ MMA issuer
-    const uint32_t idesc = umma_instr_desc(kUmmaMaxBatch, Npad, F16);
-    // timeline (lane 0): [4] first stage in hand, [5] last MMA issued, [6] / [7] ns spent
-    // waiting for weight stages / token units
-    unsigned long long *prec = lane == 0 ? misc->prof_rec : nullptr;
-    unsigned long long wait_w = 0, wait_x = 0;
-    UmmaState xu = us;
-    for (int si = 0; si < walk.stages; ++si) {
-      int kb, nk;
-      walk.stage(si, kb, nk);
-      unsigned long long tw = prec ? globaltimer() : 0ull;
-      const bool got = wait_mbar(wc, &misc->full_bar[pos.slot], pos.phase);
-      if (prec) {
-        const unsigned long long now = globaltimer();
-        wait_w += now - tw;
-        if (si == 0) prec[4] = now;
-      }
-      const char *stage = smem + kOffRing + pos.slot * kStageBytes;
-      for (int j = 0; j < nk; ++j) {
-        tw = prec ? globaltimer() : 0ull;
-        const bool xok = wait_mbar(wc, &misc->xfull_bar[xu.xslot], xu.xphase);
-        if (prec) wait_x += globaltimer() - tw;
-        if (got && xok && lane == 0) {
-          tcgen05_after_sync();
-          const unsigned long long ad = umma_smem_desc(xring + xu.xslot * kUmmaUnitBytes, 1024);
-          const unsigned long long bd = umma_smem_desc(stage + j * nbox * kUmmaBoxBytes, 1024);
-#pragma unroll
-          for (int kk = 0; kk < kUmmaKBlock / 16; ++kk) {
-            // 32 bytes per 16-wide K step inside the swizzle atom: +2 in the address field
-            umma_f16(tmem, ad + 2ull * kk, bd + 2ull * kk, idesc, si + j > 0 || kk > 0);
-          }
-          umma_commit(&misc->xempty_bar[xu.xslot]);   // the unit is free once these have run
-        }
-        xu.advance();
-      }
-      if (got && !wc.failed) {
-        if (lane == 0) {
-          umma_commit(&misc->empty_bar[pos.slot]);   // one of the 8 arrivals, when the MMAs are done
-        } else if (lane < kConsumerWarps) {
-          mbar_arrive(&misc->empty_bar[pos.slot]);   // the other 7: nothing else reads the stage
-        }
-      }
-      __syncwarp();
-      pos.advance();
-    }
-    if (lane == 0) umma_commit(&misc->acc_bar);
-    if (prec) {
-      prec[5] = globaltimer();
-      prec[6] = wait_w;
-      prec[7] = wait_x;
+    // A function of its own, so that its registers are allocated for the issue loop alone
+    // (as part of this function the loop ran up to 12 % slower, depending on what the
+    // epilogues below happened to need), with its arguments in shared memory: passed on the
+    // call stack they cost about a microsecond per task.
+    if (lane == 0) {
+      misc->is_nrows = a.nrows;
+      misc->is_nkb = nkb;
+      misc->is_task = wc.task;
+      misc->is_failed = wc.failed ? 1 : 0;
+      misc->is_slot = pos.slot;
+      misc->is_phase = pos.phase;
+      misc->is_xslot = us.xslot;
+      misc->is_xphase = us.xphase;
     }
     __syncwarp();
+    umma_issue<F16>(wc.rt, misc, smem);
+    __syncwarp();
+    wc.failed = misc->is_failed != 0;
+    for (int si = 0; si < walk.stages; ++si) pos.advance();
   } else if (warp == 1) {
     // ------------------------------------------------------------ token loader
     // One tiled-TMA box of 64 token rows x one k-block per unit, in the issuer's order.  The
