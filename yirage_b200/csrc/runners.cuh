@@ -10,6 +10,11 @@
 //
 // Convention: the ring position and the failure state go in and come back by value;
 // `failed` true = a bounded wait inside the task gave up.
+//
+// A call is not free here (about a microsecond per task: what is saved around it or passed on
+// the stack lives in local memory and comes back from L2, the L1 beside the 227 KB ring being
+// too small to hold it), so the worker loop inlines the bodies of its hottest tasks instead of
+// calling their runners: see megakernel_body.cuh.
 #pragma once
 #include "device_common.cuh"
 #include "task_allreduce.cuh"
