@@ -215,7 +215,9 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
                 // through local memory, which misses the small L1 left beside the ring)
                 linear_consume_groups<true, TP, false>(wc, smem, misc, rt, misc->ctask, batch, iter, pos);
               } else {
-                const TaskRet r = run_linear<true, TP, true>(&rt, misc, smem, worker, ti, wc.failed, batch, iter, pos);
+                const TaskRet r =
+                    batch > 2 ? run_linear<true, TP, true>(&rt, misc, smem, worker, ti, wc.failed, batch, iter, pos)
+                              : run_linear<true, TP, false>(&rt, misc, smem, worker, ti, wc.failed, batch, iter, pos);
                 pos = r.pos;
                 wc.failed = r.failed;
               }
