@@ -160,6 +160,7 @@ struct Runtime {
   // iteration: {iteration << 32 | task, t_fetch, t_dependency_met, t_done, t_inputs_staged,
   // t_last_stage_consumed, 0, 0} (globaltimer ns; the last two only for LINEAR tasks)
   const void *tmaps;   // array of 128-byte TMA tensor maps (K/V caches, LINEAR weights), or null
+  int num_tmaps;       // their number
   int use_tmem;        // allocate tensor memory: some LINEAR task can take the tcgen05 path
   int umma_policy;     // 0 / 1 = whenever eligible, 2 = never
   int umma_depth;      // token units the stagers keep in flight (YPK_UMMA_DEPTH, default 4)

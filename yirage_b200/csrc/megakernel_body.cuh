@@ -74,6 +74,16 @@ __device__ __forceinline__ void megakernel_body(const Runtime &rt) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  // The tensor maps live in global memory and were written by the host (a copy before the
+  // launch): a thread has to acquire each of them through the tensor-map proxy before it hands
+  // it to the TMA unit, or the unit may still hold an older map that lived at the same address
+  // (a graph loaded earlier into memory the allocator has since handed out again).  Every
+  // thread does it for every map once, here.
+  for (int m = 0; m < rt.num_tmaps; ++m) {
+    asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(
+                     static_cast<const char *>(rt.tmaps) + size_t(m) * 128)
+                 : "memory");
+  }
   // Accumulator columns of the tensor-core LINEAR path: taken once, for the kernel's lifetime.
   if (WIDE && rt.use_tmem) {
     if (warp == 0) tmem_alloc(misc);

@@ -74,6 +74,7 @@ struct ypk_handle {
   uint64_t arena_bytes = 0, arena_used = 0;
   char *peer_arena[8] = {nullptr};   // peers' arenas mapped through CUDA IPC (own at [rank])
   void *d_tmaps = nullptr;       // CUtensorMap[], one per distinct K / V cache tensor
+  int num_tmaps = 0;
   std::vector<uint64_t> tmap_keys;  // device address of the cache each map describes
   bool use_tmem = false;            // some LINEAR task has a weight tensor map
   int umma_policy = 0;              // YPK_TENSOR_CORE: auto (by estimated cost) / always / never
@@ -581,6 +582,7 @@ int encode_weight_tmap(ypk_handle *h, void *base, int rows, int K, int ldw, CUte
 void free_graph(ypk_handle *h) {
   if (!h->host_only && h->d_tmaps) cudaFree(h->d_tmaps);
   h->d_tmaps = nullptr;
+  h->num_tmaps = 0;
   h->tmap_keys.clear();
   if (!h->host_only) {
     if (h->d_tasks) cudaFree(h->d_tasks);
@@ -1058,6 +1060,7 @@ int ypk_load_graph(ypk_handle *h, const ypk_task *tasks, int32_t num_tasks, int3
     CUDA_TRY(h, cudaMalloc(&h->d_tmaps, sizeof(CUtensorMap) * maps.size()));
     CUDA_TRY(h, cudaMemcpy(h->d_tmaps, maps.data(), sizeof(CUtensorMap) * maps.size(),
                            cudaMemcpyHostToDevice));
+    h->num_tmaps = int(maps.size());
   }
   h->tmap_keys = keys;
   h->tasks.swap(resolved);
@@ -1187,6 +1190,7 @@ int ypk_launch_async(ypk_handle *h, void *stream, int32_t max_iterations, int32_
   rt.end_event = h->end_event;
   rt.end_count = h->end_count;
   rt.tmaps = h->d_tmaps;
+  rt.num_tmaps = h->d_tmaps ? h->num_tmaps : 0;
   rt.use_tmem = h->use_tmem ? 1 : 0;
   rt.umma_policy = h->umma_policy;
   { const char *d = getenv("YPK_UMMA_DEPTH"); rt.umma_depth = d ? std::min(5, std::max(1, atoi(d))) : 4; }
