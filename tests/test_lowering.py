@@ -654,3 +654,52 @@ def test_norm_between_two_linears_is_carried_in_wide_graphs(monkeypatch):
     assert [o.kind for o in g2.ops].count("rmsnorm") == 5
     assert not any(o.flags & (N.F_NORM_OUT | N.F_NORM_PRE) for o in g2.ops)
 
+
+
+def _meta_llama3_8b_weights(shape):
+    """Weights of the right shapes on the meta device: lowering looks at shapes only."""
+    h, f, d = shape.hidden_size, shape.intermediate_size, shape.head_dim
+    hq, hkv = shape.num_attention_heads, shape.num_key_value_heads
+    e = lambda r, c: torch.empty(r, c, dtype=torch.bfloat16, device="meta")
+    v = lambda n: torch.empty(n, dtype=torch.bfloat16, device="meta")
+    w = {"embed": e(shape.vocab_size, h), "layers": [], "final_norm": v(h), "lm_head": e(shape.vocab_size, h)}
+    for _ in range(shape.num_hidden_layers):
+        w["layers"].append({"input_norm": v(h), "q": e(hq * d, h), "k": e(hkv * d, h), "v": e(hkv * d, h),
+                            "o": e(h, hq * d), "post_norm": v(h), "gate": e(f, h), "up": e(f, h),
+                            "down": e(h, f)})
+    return w
+
+
+def test_llama3_8b_rows_are_levelled_per_operator_and_attention_workers_get_less():
+    """Every operator of a graph of at most 8 tokens waits for all tasks of its predecessor, so
+    what counts is the largest slab of each operator: slabs differ by one granule at most,
+    except behind attention, where the workers that ran an attention task get fewer rows.  No
+    task is made for a split of the KV sequence that the context bound rules out."""
+    shape = llama.LlamaShape.llama3_8b()
+    shape.num_hidden_layers = 2
+    ypk, _ = llama.build_decode_kernel(
+        shape, _meta_llama3_8b_weights(shape), tokens=torch.zeros(1, 564, dtype=torch.int64, device="meta"),
+        prompt_lengths=torch.zeros(1, dtype=torch.int32, device="meta"), max_num_batched_requests=1,
+        max_num_batched_tokens=8, max_num_pages=9, page_size=64, compile=False)
+    g = ypk.lower(148)
+    kinds = [o.kind for o in g.ops]
+    att = kinds.index("attention")
+    att_tasks = [ts for ts in g.tasks if ts.op_id == att]
+    # 564 tokens = 9 tiles of 64: at most ceil(9 / 4) = 3 splits are ever active
+    assert len(att_tasks) == shape.num_key_value_heads * 3 and {ts.iarg[3] for ts in att_tasks} == {3}
+    for oi, op in enumerate(g.ops):
+        if op.kind != "linear":
+            continue
+        rows = [0] * 148
+        for ts in g.tasks:
+            if ts.op_id == oi:
+                rows[ts.worker] += ts.iarg[2]
+        gran = 4 if op.flags & N.F_SILU_MUL else 2
+        if kinds[oi - 1] == "attention":
+            att_workers = {ts.worker for ts in g.tasks if ts.op_id == oi - 1}
+            others = [r for w_, r in enumerate(rows) if w_ not in att_workers]
+            late = [rows[w_] for w_ in att_workers]
+            assert max(others) - min(others) <= gran and max(late) < min(others)
+        else:
+            assert max(rows) - min(rows) <= gran, (oi, min(rows), max(rows))
+    assert set(lowering.simulate(g, 2)) == {2}
