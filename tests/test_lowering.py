@@ -703,3 +703,38 @@ def test_llama3_8b_rows_are_levelled_per_operator_and_attention_workers_get_less
         else:
             assert max(rows) - min(rows) <= gran, (oi, min(rows), max(rows))
     assert set(lowering.simulate(g, 2)) == {2}
+
+
+def test_norm_with_two_readers_or_under_tensor_parallelism_is_not_carried():
+    """The carried form needs the normalised rows to have exactly one reader, a LINEAR: the
+    mixture-of-experts layer reads them twice (router and experts), and under tensor
+    parallelism an all-reduce sits between the producing LINEAR and the norm."""
+    moe = llama.LlamaShape(hidden_size=256, intermediate_size=128, num_hidden_layers=2,
+                           num_attention_heads=2, num_key_value_heads=1, vocab_size=512,
+                           qk_norm=True, num_experts=16, experts_per_token=4)
+    w = llama.init_weights(moe, "cpu", 0)
+    ypk = llama.build_decode_kernel(
+        moe, w, tokens=torch.zeros(2, 64, dtype=torch.int64), prompt_lengths=torch.tensor([5, 7], dtype=torch.int32),
+        max_num_batched_requests=2, max_num_batched_tokens=16, max_num_pages=4, page_size=64, compile=False)[0]
+    g = ypk.lower(148)
+    for i, op in enumerate(g.ops):
+        if op.flags & N.F_NORM_OUT:
+            nxt = g.ops[i + 1]
+            assert nxt.kind == "linear" and nxt.flags & N.F_NORM_PRE and nxt.t["x"] is op.t["norm_out"]
+            readers = [j for j, o in enumerate(g.ops)
+                       if any(t is op.t["norm_out"] for _, t in lowering._op_inputs(o))]
+            assert readers == [i + 1]
+    # the post-attention norm of a mixture-of-experts layer feeds the router and the experts
+    assert [o.kind for o in g.ops].count("rmsnorm") >= moe.num_hidden_layers
+    assert set(lowering.simulate(g, 2)) == {2}
+
+    shape = llama.LlamaShape(hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                             num_attention_heads=8, num_key_value_heads=2, vocab_size=2048)
+    tp = llama.build_decode_kernel(
+        shape, llama.init_weights(shape, "cpu", 0, world_size=2, rank=0),
+        tokens=torch.zeros(2, 64, dtype=torch.int64), prompt_lengths=torch.tensor([5, 7], dtype=torch.int32),
+        max_num_batched_requests=2, max_num_batched_tokens=64, max_num_pages=4, page_size=64,
+        world_size=2, rank=0, compile=False)[0]
+    g2 = tp.lower(148)
+    assert "allreduce" in [o.kind for o in g2.ops]
+    assert not any(o.flags & (N.F_NORM_OUT | N.F_NORM_PRE) for o in g2.ops)
