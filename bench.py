@@ -605,7 +605,7 @@ def run_ours(args):
                      # 0.998 x the algorithmic bytes of the captured launch; the traffic grows
                      # with the weights streamed, so the ratio carries over to the full launch
                      "traffic": DRAM_TRAFFIC_RATIO * alg * K,
-                     "traffic_note": "scaled from the ncu capture of the 4-layer case (ratio 0.998), per launch of K iterations",
+                     "traffic_note": "scaled from the ncu capture of the 4-layer case (read + write = 1.000 x the algorithmic bytes), per launch of K iterations",
                      "kernel": "ypk_megakernel (one launch covers all K iterations)"},
         "clocks": clocks,
         "gpu_launches": 1,
